@@ -1,0 +1,202 @@
+"""Sharded, reshardable checkpoints.
+
+Layout (the reference defines no model-checkpoint format; it only describes Megatron's distributed
+checkpoint — sharded-tensor descriptors, parallel save, load under a different layout,
+``moe/MegatronCore_MoE_reading_notes.md:724-728``)::
+
+    <root>/step_000020/
+        meta.json                  resolved config, mesh, step, data cursor, loss curve, tensor index
+        rank_00000.pt              this rank's tensors (weights, optimizer moments, RNG state)
+    <root>/latest                  text file naming the newest complete step directory
+
+Every logical tensor is stored as pieces ``{fqn, global_shape, flat_start, flat_len}``: a piece is a
+contiguous range of the flattened *global* tensor (for expert tensors the global tensor spans all
+experts).  Loading walks the pieces that intersect what the new layout owns, so a checkpoint written
+under one ``dp/ep/pp`` loads under another.  Directories are written under a temporary name and
+renamed, so a killed save never leaves a half checkpoint that looks complete.
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+
+def _barrier():
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def _global_view(group, name: str, shape: tuple, e_rank: int, e_size: int, is_expert: bool):
+    """Global shape and the flat offset of this rank's copy of the parameter inside it."""
+    if is_expert:
+        gshape = (shape[0] * e_size,) + tuple(shape[1:])
+        per = 1
+        for s in shape:
+            per *= s
+        return gshape, e_rank * per
+    return tuple(shape), 0
+
+
+def _owned_pieces(trainer):
+    """Yield ``(kind, fqn, global_shape, global_flat_start, length, source_tensor_slice_fn)`` for
+    every piece of every parameter that this rank's shards own."""
+    mesh = trainer.mesh
+    for g in trainer.engine.all_groups():
+        lo = g.rank * g.shard_numel if g.sharded else 0
+        hi = lo + (g.shard_numel if g.sharded else g.total)
+        for (fqn, shape, off, numel), p in zip(g.param_slices(), g.params):
+            a, b = max(off, lo), min(off + numel, hi)
+            if a >= b:
+                continue
+            is_exp = getattr(p, "is_expert", False)
+            gshape, base = _global_view(g, fqn, shape, mesh.ep_rank, mesh.ep, is_exp)
+            yield g, fqn, gshape, base + (a - off), b - a, a - lo
+
+
+def _is_writer(trainer, g) -> bool:
+    """Unsharded groups are replicated across their data ranks: only the first replica writes."""
+    if g.sharded:
+        return True
+    if g.replica_group is None:
+        return True
+    return dist.get_rank(g.replica_group) == 0
+
+
+def save_checkpoint(trainer, root: str) -> str:
+    mesh = trainer.mesh
+    root_p = Path(root)
+    final = root_p / f"step_{trainer.step:06d}"
+    tmp = root_p / f".tmp_step_{trainer.step:06d}"
+    if mesh.rank == 0:
+        if tmp.exists():
+            shutil.rmtree(tmp)
+        tmp.mkdir(parents=True, exist_ok=True)
+    _barrier()
+    opt = trainer.optimizer
+    tensors, index = {}, []
+    for g, fqn, gshape, gstart, length, soff in _owned_pieces(trainer):
+        if not _is_writer(trainer, g):
+            continue
+        key = f"{fqn}@{gstart}"
+        rec = {"fqn": fqn, "global_shape": list(gshape), "start": gstart, "len": length, "key": key}
+        tensors[f"w/{key}"] = g.shard[soff:soff + length].detach().cpu().clone()
+        for mom_name, mom in (("m", opt.m[g.name]), ("v", opt.v[g.name])):
+            tensors[f"{mom_name}/{key}"] = mom.data[soff:soff + length].detach().cpu().clone()
+            if mom.kind == "fp8":
+                # scales are per 128 elements of the shard; pieces start on 128-element boundaries
+                tensors[f"{mom_name}s/{key}"] = mom.scale[soff // 128:(soff + length + 127) // 128].cpu().clone()
+        index.append(rec)
+    buffers = {}
+    for u in trainer.engine.units:
+        for bn, b in u.module.named_buffers():
+            buffers[f"{u.name}.{bn}"] = b.detach().cpu().clone()
+    payload = {"tensors": tensors, "index": index, "buffers": buffers,
+               "opt_step": opt.step_count, "prev_norm": opt._prev_norm,
+               "torch_rng": torch.get_rng_state()}
+    torch.save(payload, tmp / f"rank_{mesh.rank:05d}.pt")
+    _barrier()
+    if mesh.rank == 0:
+        meta = {"format": "system_lab_b200.ckpt.v1", "step": trainer.step, "world": mesh.world,
+                "mesh": {"pp": mesh.pp, "dp": mesh.dp, "cp": mesh.cp, "ep": mesh.ep},
+                "data_cursor": trainer.data.cursor, "loss_curve": trainer.loss_curve,
+                "optimizer_state_dtype": trainer.cfg.precision.optimizer_state_dtype,
+                "config": trainer.cfg.to_dict()}
+        (tmp / "meta.json").write_text(json.dumps(meta, indent=2))
+        if final.exists():
+            shutil.rmtree(final)
+        os.replace(tmp, final)
+        (root_p / "latest.tmp").write_text(final.name)
+        os.replace(root_p / "latest.tmp", root_p / "latest")
+        _prune(root_p, trainer.cfg.checkpoint.keep_last)
+    _barrier()
+    return str(final)
+
+
+def _prune(root: Path, keep: int) -> None:
+    if keep <= 0:
+        return
+    steps = sorted(p for p in root.glob("step_*") if p.is_dir())
+    for p in steps[:-keep]:
+        shutil.rmtree(p, ignore_errors=True)
+
+
+def resolve(path: str) -> Path:
+    p = Path(path)
+    if (p / "meta.json").exists():
+        return p
+    latest = p / "latest"
+    if latest.exists():
+        return p / latest.read_text().strip()
+    raise FileNotFoundError(f"no checkpoint under {path}")
+
+
+def load_checkpoint(trainer, path: str) -> None:
+    ck = resolve(path)
+    meta = json.loads((ck / "meta.json").read_text())
+    if meta.get("format") != "system_lab_b200.ckpt.v1":
+        raise ValueError(f"unknown checkpoint format in {ck}")
+    same_layout = (meta["world"] == trainer.mesh.world and
+                   meta["mesh"] == {"pp": trainer.mesh.pp, "dp": trainer.mesh.dp, "cp": trainer.mesh.cp,
+                                    "ep": trainer.mesh.ep})
+    own = ck / f"rank_{trainer.mesh.rank:05d}.pt"
+    files = sorted(ck.glob("rank_*.pt"))
+    if same_layout:                       # own file first; others only if a replica did not write
+        files = [own] + [f for f in files if f != own]
+    opt = trainer.optimizer
+    if not same_layout and meta.get("optimizer_state_dtype") == "fp8":
+        raise ValueError("resharding 8-bit optimizer state is not supported; load under the saved layout")
+    want = list(_owned_pieces(trainer))
+    filled = {id(g): 0 for g, *_ in want}
+    buffers_done = False
+    need_total = {id(g): 0 for g, *_ in want}
+    for g, _, _, _, length, _ in want:
+        need_total[id(g)] += length
+    for f in files:
+        if all(filled[k] >= need_total[k] for k in filled) and buffers_done:
+            break
+        payload = torch.load(f, map_location="cpu", weights_only=False)
+        by_fqn: dict[str, list] = {}
+        for rec in payload["index"]:
+            by_fqn.setdefault(rec["fqn"], []).append(rec)
+        for g, fqn, gshape, gstart, length, soff in want:
+            for rec in by_fqn.get(fqn, ()):
+                a, b = max(gstart, rec["start"]), min(gstart + length, rec["start"] + rec["len"])
+                if a >= b:
+                    continue
+                src = slice(a - rec["start"], b - rec["start"])
+                dst = slice(soff + (a - gstart), soff + (b - gstart))
+                g.shard[dst].copy_(payload["tensors"][f"w/{rec['key']}"][src])
+                for mom_name, mom in (("m", opt.m[g.name]), ("v", opt.v[g.name])):
+                    mom.data[dst].copy_(payload["tensors"][f"{mom_name}/{rec['key']}"][src])
+                    if mom.kind == "fp8":
+                        sc = payload["tensors"][f"{mom_name}s/{rec['key']}"]
+                        mom.scale[dst.start // 128:dst.start // 128 + sc.numel()].copy_(sc)
+                filled[id(g)] += b - a
+        if not buffers_done:
+            for u in trainer.engine.units:
+                for bn, b in u.module.named_buffers():
+                    k = f"{u.name}.{bn}"
+                    if k in payload["buffers"]:
+                        b.copy_(payload["buffers"][k])
+            buffers_done = True
+        if same_layout and f == own:
+            torch.set_rng_state(payload["torch_rng"])
+        opt.step_count = payload["opt_step"]
+        opt._prev_norm = payload.get("prev_norm")
+    # replicas of unsharded groups did not write: they read the writer's pieces above (same fqn ranges)
+    for g in trainer.engine.all_groups():
+        need = sum(l for gg, _, _, _, l, _ in want if gg is g)
+        if filled[id(g)] < need:
+            raise ValueError(f"checkpoint {ck} does not cover group {g.name}: {filled[id(g)]}/{need} elements")
+        if not g.sharded:
+            if g.shard is not g.full:
+                g.full.copy_(g.shard)
+    trainer.step = meta["step"]
+    trainer.data.cursor = meta["data_cursor"]
+    trainer.loss_curve = list(meta.get("loss_curve", []))
+    _barrier()

@@ -1,0 +1,290 @@
+"""Typed configuration.
+
+Field names follow the Megatron/Primus knob vocabulary that the reference's run
+notes quote (``notes/2026-04/2026-04-19_gptoss_01_mlperf_best_e2e_run.md:60-110``,
+``notes/2026-04/2026-04-28_gptoss_27_mlperf_legal_baseline.md:165-177``) so a
+user of those launch scripts recognises every knob.
+
+Design rules, each one a pitfall recorded by the reference:
+
+* Booleans are parsed strictly: the *string* ``"false"`` is False, anything that
+  is not a recognised boolean literal is an error
+  (``notes/2026-04/2026-04-24_gptoss_20_truthy_flag_fix.md``: env substitution
+  produced a truthy ``"false"``).
+* One resolution order: dataclass defaults < preset < YAML file < ``key=value``
+  command line overrides.  Nothing else (no env var, no runtime ``setattr``)
+  may change a value (``notes/2026-04/2026-04-25_gptoss_22_*:20-44``).
+* The resolved config is dumped next to the run so what ran is what is written
+  (``notes/mlperf-llama/*meeting_summary_en.md:35,49-57``).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field, fields, is_dataclass
+from pathlib import Path
+from typing import Any, get_type_hints
+
+_TRUE = {"true", "1", "yes", "on"}
+_FALSE = {"false", "0", "no", "off"}
+
+
+class ConfigError(ValueError):
+    pass
+
+
+def parse_bool(v: Any) -> bool:
+    """Strict boolean parse; rejects anything that is not a boolean literal."""
+    if isinstance(v, bool):
+        return v
+    if isinstance(v, int) and v in (0, 1):
+        return bool(v)
+    if isinstance(v, str):
+        s = v.strip().lower()
+        if s in _TRUE:
+            return True
+        if s in _FALSE:
+            return False
+    raise ConfigError(f"not a boolean literal: {v!r}")
+
+
+@dataclass
+class ModelConfig:
+    name: str = "simplemoe-tiny"
+    num_layers: int = 2
+    hidden_size: int = 256
+    num_attention_heads: int = 4
+    num_query_groups: int = 4            # KV heads (GQA)
+    kv_channels: int = 64                # head_dim
+    vocab_size: int = 1024
+    seq_length: int = 128
+    rotary_base: float = 10000.0
+    norm_epsilon: float = 1e-6
+    init_method_std: float = 0.02
+    tie_embeddings: bool = False
+    # attention flavour: "gqa" (multi/grouped query) or "mla" (DeepSeek latent attention)
+    attention_type: str = "gqa"
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    sliding_window: int = 0              # 0 = full causal; >0 on alternate layers (GPT-OSS style)
+    # dense FFN (used by the first `first_k_dense` layers and by non-MoE models)
+    ffn_hidden_size: int = 1024
+    first_k_dense: int = 0
+    # MoE
+    num_experts: int = 8
+    moe_router_topk: int = 2
+    moe_ffn_hidden_size: int = 512
+    moe_shared_expert_intermediate_size: int = 0
+    moe_router_score_function: str = "softmax"   # softmax | sigmoid
+    moe_router_load_balancing_type: str = "aux_loss"  # aux_loss | bias | none
+    moe_aux_loss_coeff: float = 0.0
+    moe_router_bias_update_rate: float = 1e-3
+    moe_router_dtype: str = "fp32"
+    moe_router_topk_scaling_factor: float = 1.0
+    moe_norm_topk_prob: bool = True
+    moe_token_dispatcher_type: str = "fused"     # fused (peer-memory kernels) | alltoall (NCCL baseline)
+    moe_grouped_gemm: bool = True
+    moe_permute_fusion: bool = True
+    moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
+
+
+@dataclass
+class ParallelConfig:
+    tensor_model_parallel_size: int = 1
+    pipeline_model_parallel_size: int = 1
+    virtual_pipeline_model_parallel_size: int = 1
+    expert_model_parallel_size: int = 1
+    context_parallel_size: int = 1
+    fsdp: bool = True                    # shard params/grads/optimizer state over the data axis
+    use_distributed_optimizer: bool = True
+    overlap_grad_reduce: bool = True
+    overlap_param_gather: bool = True
+    grad_reduce_in_bf16: bool = True
+    ddp_bucket_size: int = 40_000_000    # elements
+    ddp_average_in_collective: bool = True
+    num_distributed_optimizer_instances: int = 1
+    fsdp_fused_collectives: bool = True  # peer-memory all-gather / reduce-scatter kernels instead of NCCL
+
+
+@dataclass
+class PrecisionConfig:
+    params_dtype: str = "fp32"           # fp32 | bf16
+    fp8: bool = False                    # fp8 expert GEMMs
+    fp8_recipe: str = "blockwise"        # blockwise (1x128 act, 128x128 weight) | tensorwise | delayed
+    num_layers_at_start_in_bf16: int = 0
+    num_layers_at_end_in_bf16: int = 0
+    master_weights: bool = True          # fp32 master copy when params are bf16
+    optimizer_state_dtype: str = "fp32"  # fp32 | bf16 | fp8 (block scaled 8-bit moments)
+    recompute_granularity: str = "none"  # none | selective | full
+
+
+@dataclass
+class TrainConfig:
+    micro_batch_size: int = 4
+    global_batch_size: int = 8
+    train_iters: int = 20
+    seed: int = 0
+    lr: float = 3e-4
+    min_lr: float = 0.0
+    lr_warmup_iters: int = 0
+    lr_decay_iters: int = 0
+    lr_decay_style: str = "constant"     # constant | cosine | linear
+    weight_decay: float = 0.1
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-8
+    clip_grad: float = 1.0
+    optimizer_in_backward: bool = False  # apply AdamW per layer during backward (no grad buffer kept)
+    eval_interval: int = 0
+    eval_iters: int = 0
+    log_interval: int = 1
+    check_for_nan_in_loss_and_grad: bool = True
+    data: str = "synthetic"              # synthetic uniform-random token ids
+    device: str = "auto"                 # auto | cpu | cuda
+    use_cuda_kernels: str = "auto"       # auto | true | false : hand written sm_100a ops vs PyTorch oracle path
+    hang_timeout_s: float = 300.0
+    mllog: bool = False
+
+
+@dataclass
+class CheckpointConfig:
+    save: str = ""
+    load: str = ""
+    save_interval: int = 0
+    disable_last_saving: bool = False
+    keep_last: int = 2
+
+
+@dataclass
+class ProfileConfig:
+    profile: bool = False
+    profile_step_start: int = 16
+    profile_step_end: int = 18
+    profile_ranks: list = field(default_factory=lambda: [0])
+    torch_profiler_with_stack: bool = False
+    torch_profiler_record_shapes: bool = False
+    trace_dir: str = "traces"
+    snapshot_path: str = ""              # write the tuner Snapshot JSON here at run end
+
+
+@dataclass
+class Config:
+    model: ModelConfig = field(default_factory=ModelConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    precision: PrecisionConfig = field(default_factory=PrecisionConfig)
+    train: TrainConfig = field(default_factory=TrainConfig)
+    checkpoint: CheckpointConfig = field(default_factory=CheckpointConfig)
+    profile: ProfileConfig = field(default_factory=ProfileConfig)
+
+    # ---- construction -------------------------------------------------
+    @staticmethod
+    def from_dict(d: dict) -> "Config":
+        cfg = Config()
+        cfg.update(d)
+        return cfg
+
+    @staticmethod
+    def load(path: str | Path | None = None, overrides: list[str] | None = None,
+             preset: str | None = None) -> "Config":
+        from .models.presets import PRESETS
+        cfg = Config()
+        if preset:
+            if preset not in PRESETS:
+                raise ConfigError(f"unknown preset {preset!r}; have {sorted(PRESETS)}")
+            cfg.update(PRESETS[preset])
+        if path:
+            import yaml
+            text = Path(path).read_text()
+            data = yaml.safe_load(text) or {}
+            if "preset" in data:
+                p = data.pop("preset")
+                if p not in PRESETS:
+                    raise ConfigError(f"unknown preset {p!r}")
+                cfg.update(PRESETS[p])
+            cfg.update(data)
+        for ov in overrides or []:
+            if "=" not in ov:
+                raise ConfigError(f"override must be key=value, got {ov!r}")
+            k, v = ov.split("=", 1)
+            cfg.set(k.strip(), v.strip())
+        cfg.validate()
+        return cfg
+
+    def update(self, d: dict) -> None:
+        for k, v in d.items():
+            if is_dataclass(getattr(self, k, None)) and isinstance(v, dict):
+                for kk, vv in v.items():
+                    self.set(f"{k}.{kk}", vv)
+            else:
+                self.set(k, v)
+
+    def _find(self, key: str):
+        """Resolve ``section.name`` or a bare leaf name that is unique across sections."""
+        if "." in key:
+            sec, name = key.split(".", 1)
+            if not hasattr(self, sec):
+                raise ConfigError(f"unknown config section {sec!r}")
+            obj = getattr(self, sec)
+            if not any(f.name == name for f in fields(obj)):
+                raise ConfigError(f"unknown config key {key!r}")
+            return obj, name
+        hits = [(getattr(self, s.name), key) for s in fields(self)
+                if any(f.name == key for f in fields(getattr(self, s.name)))]
+        if not hits:
+            raise ConfigError(f"unknown config key {key!r}")
+        if len(hits) > 1:
+            raise ConfigError(f"ambiguous config key {key!r}; qualify it with a section")
+        return hits[0]
+
+    def set(self, key: str, value: Any) -> None:
+        obj, name = self._find(key)
+        hint = get_type_hints(type(obj))[name]
+        setattr(obj, name, _coerce(value, hint, key))
+
+    def get(self, key: str) -> Any:
+        obj, name = self._find(key)
+        return getattr(obj, name)
+
+    # ---- output ---------------------------------------------------------
+    def to_dict(self) -> dict:
+        return dataclasses.asdict(self)
+
+    def dump(self, path: str | Path) -> None:
+        Path(path).parent.mkdir(parents=True, exist_ok=True)
+        Path(path).write_text(json.dumps(self.to_dict(), indent=2, sort_keys=True))
+
+    # ---- legality (the tuner's constraint rules use the same function) ---
+    def validate(self, world_size: int | None = None) -> None:
+        from .pilot.constraints import check_config
+        problems = [p for p in check_config(self, world_size) if p["severity"] == "error"]
+        if problems:
+            raise ConfigError("; ".join(p["message"] for p in problems))
+
+
+def _coerce(value: Any, hint: Any, key: str) -> Any:
+    if hint is bool:
+        return parse_bool(value)
+    if hint is int:
+        if isinstance(value, bool):
+            raise ConfigError(f"{key}: expected int, got bool")
+        if isinstance(value, str):
+            return int(value.replace("_", ""))
+        if isinstance(value, float) and value != int(value):
+            raise ConfigError(f"{key}: expected int, got {value}")
+        return int(value)
+    if hint is float:
+        if isinstance(value, bool):
+            raise ConfigError(f"{key}: expected float, got bool")
+        return float(value)
+    if hint is str:
+        if value is None:
+            return ""
+        return str(value)
+    if hint is list or getattr(hint, "__origin__", None) is list:
+        if isinstance(value, str):
+            value = json.loads(value) if value.startswith("[") else [int(x) for x in value.split(",") if x]
+        return list(value)
+    return value

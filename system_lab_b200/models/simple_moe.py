@@ -1,0 +1,309 @@
+"""SimpleMoE decoder family: GQA or MLA attention, dense or MoE SwiGLU feed-forward, RMSNorm, RoPE.
+
+One class covers the tiny plumbing model, the Qwen3-30B-A3B shape, the DeepSeek-V3 shaped proxy
+(MLA, shared expert, sigmoid router with bias balancing, first layer dense) and the GPT-OSS-20B
+shape (sliding window on alternate layers) the reference profiles
+(``notes/2026-04/2026-04-21_gptoss_13_attn_bwd_recompile_postmortem.md:19-26``).
+
+Per layer data flow (the fused residual+norm form of
+``notes/2026-04/2026-04-24_gptoss_17_fused_residual_rmsnorm_impl.md:43-83``)::
+
+    a      = attention(rmsnorm(x))
+    y, h   = rmsnorm_residual(a, x)          # h = x + a ; y = norm(h)
+    out    = h + ffn(y)
+
+MoE feed-forward (gate probability applied inside SwiGLU so no expert output has to be kept for
+the router gradient, ``moe/MegatronCore_MoE_reading_notes.md:201-218``)::
+
+    w, idx = router_topk(y @ Wr.T)           # fp32
+    xe, pe = dispatch(y, w)                  # expert-major rows on the owning rank
+    ye     = grouped_linear(swiglu_probs(grouped_linear(xe, W1), pe), W2)
+    ffn    = combine(ye) (+ shared expert)
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import reference as ref
+
+
+def _seed_for(base_seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{base_seed}:{name}".encode()).digest()
+    return int.from_bytes(h[:7], "little")
+
+
+def seeded_normal_(t: torch.Tensor, std: float, base_seed: int, name: str) -> None:
+    """Fill ``t`` with N(0, std) from a generator keyed by the parameter's *global* name, so the
+    same logical weight gets the same values under every parallel layout."""
+    g = torch.Generator(device=t.device)
+    g.manual_seed(_seed_for(base_seed, name))
+    if t.dtype in (torch.float32, torch.float64) or t.is_cuda:
+        t.normal_(0.0, std, generator=g)
+    else:
+        t.copy_(torch.empty(t.shape, dtype=torch.float32, device=t.device).normal_(0.0, std, generator=g))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+class GQAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None):
+        super().__init__()
+        self.nq, self.nkv, self.d = cfg.num_attention_heads, cfg.num_query_groups, cfg.kv_channels
+        h = cfg.hidden_size
+        self.wqkv = nn.Parameter(torch.empty((self.nq + 2 * self.nkv) * self.d, h))
+        self.wo = nn.Parameter(torch.empty(h, self.nq * self.d))
+        self.window = cfg.sliding_window if (cfg.sliding_window and layer_idx % 2 == 0) else 0
+        self.cp_group = cp_group
+
+    def forward(self, x, cos, sin):
+        b, s, _ = x.shape
+        qkv = F.linear(x, self.wqkv.to(x.dtype))
+        q, k, v = qkv.split([self.nq * self.d, self.nkv * self.d, self.nkv * self.d], dim=-1)
+        q = ops.rope(q.reshape(b, s, self.nq, self.d), cos, sin)
+        k = ops.rope(k.reshape(b, s, self.nkv, self.d), cos, sin)
+        v = v.reshape(b, s, self.nkv, self.d)
+        if self.cp_group is not None:
+            from ..parallel.cp import ulysses_attention
+            o = ulysses_attention(q, k, v, self.cp_group, window=self.window)
+        else:
+            o = ops.causal_attention(q, k, v, None, self.window)
+        return F.linear(o.reshape(b, s, self.nq * self.d), self.wo.to(x.dtype))
+
+
+class MLAttention(nn.Module):
+    """Multi-head latent attention (DeepSeek-V3): low-rank q and kv projections, a shared rotary
+    key of ``qk_rope_head_dim`` and per-head no-position keys of ``qk_nope_head_dim``."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None):
+        super().__init__()
+        h, nh = cfg.hidden_size, cfg.num_attention_heads
+        self.nh, self.nope, self.rope_d, self.vd = nh, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        self.q_lora, self.kv_lora = cfg.q_lora_rank, cfg.kv_lora_rank
+        qk = self.nope + self.rope_d
+        if self.q_lora:
+            self.wq_a = nn.Parameter(torch.empty(self.q_lora, h))
+            self.q_norm = RMSNorm(self.q_lora, cfg.norm_epsilon)
+            self.wq_b = nn.Parameter(torch.empty(nh * qk, self.q_lora))
+        else:
+            self.wq = nn.Parameter(torch.empty(nh * qk, h))
+        self.wkv_a = nn.Parameter(torch.empty(self.kv_lora + self.rope_d, h))
+        self.kv_norm = RMSNorm(self.kv_lora, cfg.norm_epsilon)
+        self.wkv_b = nn.Parameter(torch.empty(nh * (self.nope + self.vd), self.kv_lora))
+        self.wo = nn.Parameter(torch.empty(h, nh * self.vd))
+        self.scale = 1.0 / math.sqrt(qk)
+        self.cp_group = cp_group
+
+    def forward(self, x, cos, sin):
+        b, s, _ = x.shape
+        dt = x.dtype
+        if self.q_lora:
+            q = F.linear(self.q_norm(F.linear(x, self.wq_a.to(dt))), self.wq_b.to(dt))
+        else:
+            q = F.linear(x, self.wq.to(dt))
+        q = q.reshape(b, s, self.nh, self.nope + self.rope_d)
+        q_nope, q_rope = q.split([self.nope, self.rope_d], dim=-1)
+        kv_a = F.linear(x, self.wkv_a.to(dt))
+        c_kv, k_rope = kv_a.split([self.kv_lora, self.rope_d], dim=-1)
+        kv = F.linear(self.kv_norm(c_kv), self.wkv_b.to(dt)).reshape(b, s, self.nh, self.nope + self.vd)
+        k_nope, v = kv.split([self.nope, self.vd], dim=-1)
+        q_rope = ops.rope(q_rope.contiguous(), cos, sin)
+        k_rope = ops.rope(k_rope.reshape(b, s, 1, self.rope_d).contiguous(), cos, sin)
+        qf = torch.cat([q_nope, q_rope], dim=-1)
+        kf = torch.cat([k_nope, k_rope.expand(b, s, self.nh, self.rope_d)], dim=-1)
+        if self.cp_group is not None:
+            from ..parallel.cp import ulysses_attention
+            o = ulysses_attention(qf, kf, v.contiguous(), self.cp_group, scale=self.scale)
+        else:
+            o = ops.causal_attention(qf, kf, v.contiguous(), self.scale, 0)
+        return F.linear(o.reshape(b, s, self.nh * self.vd), self.wo.to(dt))
+
+
+class DenseFFN(nn.Module):
+    def __init__(self, hidden: int, ffn: int):
+        super().__init__()
+        self.w1 = nn.Parameter(torch.empty(2 * ffn, hidden))   # [gate | up]
+        self.w2 = nn.Parameter(torch.empty(hidden, ffn))
+
+    def forward(self, x):
+        return F.linear(ops.swiglu(F.linear(x, self.w1.to(x.dtype))), self.w2.to(x.dtype))
+
+
+class MoEFFN(nn.Module):
+    """Routed experts (this rank owns ``num_experts / ep`` of them) plus an optional shared expert."""
+
+    def __init__(self, cfg: ModelConfig, ep_rank: int, ep_size: int, fp8: bool = False):
+        super().__init__()
+        h, f = cfg.hidden_size, cfg.moe_ffn_hidden_size
+        self.cfg = cfg
+        self.ep_rank, self.ep_size = ep_rank, ep_size
+        self.e_local = cfg.num_experts // ep_size
+        self.fp8 = fp8
+        self.router = nn.Parameter(torch.empty(cfg.num_experts, h))
+        self.experts_w1 = nn.Parameter(torch.empty(self.e_local, 2 * f, h))
+        self.experts_w2 = nn.Parameter(torch.empty(self.e_local, h, f))
+        self.experts_w1.is_expert = True
+        self.experts_w2.is_expert = True
+        if cfg.moe_router_load_balancing_type == "bias":
+            self.register_buffer("router_bias", torch.zeros(cfg.num_experts), persistent=True)
+        else:
+            self.router_bias = None
+        self.shared = DenseFFN(h, cfg.moe_shared_expert_intermediate_size) \
+            if cfg.moe_shared_expert_intermediate_size else None
+        self.dispatcher = None            # set by the engine (needs the process group)
+        self.aux = None                   # last aux loss (added to the objective by the trainer)
+        self.last_tokens_per_expert = None
+
+    def forward(self, x):
+        cfg = self.cfg
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        logits = F.linear(x2.float(), self.router.float())
+        w, idx, scores = ops.router_topk(logits, cfg.moe_router_topk, cfg.moe_router_score_function,
+                                         self.router_bias, cfg.moe_norm_topk_prob,
+                                         cfg.moe_router_topk_scaling_factor)
+        if cfg.moe_router_load_balancing_type == "aux_loss" and cfg.moe_aux_loss_coeff > 0 and self.training:
+            self.aux = ref.aux_loss(scores, idx, cfg.num_experts, cfg.moe_aux_loss_coeff)
+        d = self.dispatcher
+        plan = d.plan(idx)
+        self.last_tokens_per_expert = plan.tokens_per_expert_global
+        xe = d.dispatch_rows(plan, x2)
+        pe = d.dispatch_scalars(plan, w)
+        h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8)
+        act = ops.swiglu_probs(h1, pe)
+        ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8)
+        out = d.combine_rows(plan, ye)
+        if self.shared is not None:
+            out = out + self.shared(x2)
+        return out.reshape(shp)
+
+    @torch.no_grad()
+    def update_router_bias(self, global_tokens_per_expert: torch.Tensor) -> None:
+        """Aux-loss-free balancing: nudge under-loaded experts up, over-loaded down
+        (``moe/MegatronCore_MoE_reading_notes.md:686-698``)."""
+        if self.router_bias is None:
+            return
+        load = global_tokens_per_expert.float()
+        self.router_bias += self.cfg.moe_router_bias_update_rate * torch.sign(load.mean() - load)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, ep_rank: int, ep_size: int, fp8: bool = False,
+                 cp_group=None):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.eps = cfg.norm_epsilon
+        self.attn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
+        attn_cls = MLAttention if cfg.attention_type == "mla" else GQAttention
+        self.attn = attn_cls(cfg, layer_idx, cp_group)
+        self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
+        self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense
+        self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8) if self.is_moe else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size)
+
+    def forward(self, x, cos, sin):
+        a = self.attn(self.attn_norm(x), cos, sin)
+        y, h = ops.rmsnorm_residual(a, x, self.ffn_norm.weight, self.eps)
+        return h + self.ffn(y)
+
+
+class Embedding(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
+
+    def forward(self, tokens, dtype):
+        return F.embedding(tokens, self.weight).to(dtype)
+
+
+class Head(nn.Module):
+    """Final norm + vocabulary projection + next-token cross entropy (never stores full logits on
+    the kernel path)."""
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
+        self.weight = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
+
+    def forward(self, x, targets):
+        h = self.norm(x).reshape(-1, x.shape[-1])
+        return ops.linear_cross_entropy(h, self.weight.to(h.dtype), targets.reshape(-1))
+
+    def logits(self, x):
+        return F.linear(self.norm(x), self.weight.to(x.dtype))
+
+
+class SimpleMoE(nn.Module):
+    """The layers ``[layer_start, layer_end)`` of the decoder plus, on the first/last pipeline
+    stage, the embedding / head."""
+
+    def __init__(self, cfg: ModelConfig, *, ep_rank: int = 0, ep_size: int = 1, fp8: bool = False,
+                 layer_start: int = 0, layer_end: int | None = None, first_stage: bool = True,
+                 last_stage: bool = True, cp_group=None, cp_rank: int = 0, cp_size: int = 1):
+        super().__init__()
+        self.cfg = cfg
+        layer_end = cfg.num_layers if layer_end is None else layer_end
+        self.embed = Embedding(cfg) if first_stage else None
+        self.layers = nn.ModuleList(
+            [DecoderLayer(cfg, i, ep_rank, ep_size, fp8, cp_group) for i in range(layer_start, layer_end)])
+        self.head = Head(cfg) if last_stage else None
+        self.ep_rank, self.ep_size = ep_rank, ep_size
+        self.cp_rank, self.cp_size = cp_rank, cp_size
+        self.rope_dim = cfg.qk_rope_head_dim if cfg.attention_type == "mla" else cfg.kv_channels
+        self._rope_cache = {}
+
+    def rope_tables(self, seq_local: int, device):
+        key = (seq_local, str(device))
+        if key not in self._rope_cache:
+            # rotary positions of this rank's sequence chunk (context parallel shards the sequence)
+            self._rope_cache[key] = ref.rope_tables(seq_local, self.rope_dim, self.cfg.rotary_base, device,
+                                                    offset=self.cp_rank * seq_local)
+        return self._rope_cache[key]
+
+    @torch.no_grad()
+    def init_weights(self, seed: int) -> None:
+        """N(0, init_method_std) for matrices, ones for norm gains.  Expert tensors are filled one
+        global expert at a time so every expert-parallel layout sees the same values."""
+        std = self.cfg.init_method_std
+        for name, p in self.named_parameters():
+            gname = self._global_name(name)
+            if name.endswith("norm.weight") or ".q_norm." in name or ".kv_norm." in name:
+                p.fill_(1.0)
+            elif getattr(p, "is_expert", False):
+                e_local = p.shape[0]
+                for j in range(e_local):
+                    seeded_normal_(p[j], std, seed, f"{gname}.{self.ep_rank * e_local + j}")
+            else:
+                seeded_normal_(p, std, seed, gname)
+
+    def _global_name(self, name: str) -> str:
+        parts = name.split(".")
+        if parts[0] == "layers":
+            parts[1] = str(self.layers[int(parts[1])].layer_idx)
+        return ".".join(parts)
+
+    def forward(self, tokens_or_hidden, targets=None, dtype=torch.float32):
+        """Plain (engine-less) forward for tests and small runs: tokens -> loss or hidden."""
+        x = self.embed(tokens_or_hidden, dtype) if self.embed is not None else tokens_or_hidden
+        cos, sin = self.rope_tables(x.shape[1], x.device)
+        for layer in self.layers:
+            x = layer(x, cos, sin)
+        if self.head is None:
+            return x
+        return self.head(x, targets) if targets is not None else self.head.logits(x)
+
+    def moe_layers(self):
+        return [l.ffn for l in self.layers if l.is_moe]

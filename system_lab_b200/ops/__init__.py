@@ -1,0 +1,99 @@
+"""Public op surface.
+
+Each op has exactly two implementations: the hand written sm_100a kernel (``ops/cuda.py`` over
+``csrc/``) and the PyTorch oracle (``ops/reference.py``).  CUDA tensors take the kernel path; CPU
+tensors take the oracle.  ``set_kernel_mode("reference")`` forces the oracle on the GPU too — that is
+the measured library baseline (cuBLAS / ATen), never a silent fallback: if the extension is missing
+on a GPU machine the kernel path raises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import reference as ref
+
+_MODE = "auto"          # auto: kernels on CUDA tensors | reference: oracle everywhere
+
+
+def set_kernel_mode(mode: str) -> None:
+    global _MODE
+    if mode not in ("auto", "reference"):
+        raise ValueError(mode)
+    _MODE = mode
+
+
+def kernel_mode() -> str:
+    return _MODE
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    return _MODE == "auto" and t.is_cuda
+
+
+def _cuda():
+    from . import cuda
+    return cuda
+
+
+def rmsnorm(x, weight, eps=1e-6):
+    return _cuda().rmsnorm(x, weight, eps) if use_kernels(x) else ref.rmsnorm(x, weight, eps)
+
+
+def rmsnorm_residual(x, residual, weight, eps=1e-6):
+    if use_kernels(x):
+        return _cuda().rmsnorm_residual(x, residual, weight, eps)
+    return ref.rmsnorm_residual(x, residual, weight, eps)
+
+
+def rope(x, cos, sin):
+    return _cuda().rope(x, cos, sin) if use_kernels(x) else ref.rope(x, cos, sin)
+
+
+def swiglu(gate_up):
+    return _cuda().swiglu(gate_up) if use_kernels(gate_up) else ref.swiglu(gate_up)
+
+
+def swiglu_probs(gate_up, probs):
+    return _cuda().swiglu_probs(gate_up, probs) if use_kernels(gate_up) else ref.swiglu_probs(gate_up, probs)
+
+
+def router_topk(logits, topk, score_function="softmax", bias=None, norm_topk_prob=True, scaling_factor=1.0):
+    if use_kernels(logits):
+        return _cuda().router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
+    return ref.router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
+
+
+def grouped_linear(a, w, offsets, counts, fp8: bool = False):
+    """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``."""
+    if use_kernels(a):
+        return _cuda().grouped_linear(a, w, offsets, counts, fp8)
+    return _GroupedLinearRef.apply(a, w, offsets, counts)
+
+
+def causal_attention(q, k, v, scale=None, window=0):
+    if use_kernels(q):
+        return _cuda().causal_attention(q, k, v, scale, window)
+    return ref.causal_attention(q, k, v, scale, window)
+
+
+def linear_cross_entropy(h, weight, targets):
+    if use_kernels(h):
+        return _cuda().linear_cross_entropy(h, weight, targets)
+    return ref.linear_cross_entropy(h, weight, targets)
+
+
+class _GroupedLinearRef(torch.autograd.Function):
+    """Oracle grouped linear with explicit fwd/dgrad/wgrad (mirrors the three CUDA kernels)."""
+
+    @staticmethod
+    def forward(ctx, a, w, offsets, counts):
+        ctx.save_for_backward(a, w, offsets, counts)
+        return ref.grouped_gemm(a, w, offsets, counts)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, w, offsets, counts = ctx.saved_tensors
+        g = g.contiguous()
+        da = ref.grouped_gemm_dgrad(g, w, offsets, counts) if ctx.needs_input_grad[0] else None
+        dw = ref.grouped_gemm_wgrad(g, a, offsets, counts, out_dtype=w.dtype) if ctx.needs_input_grad[1] else None
+        return da, dw, None, None

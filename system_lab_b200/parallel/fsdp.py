@@ -1,0 +1,229 @@
+"""Fully sharded data parallel engine: flat, block-aligned parameter shards per layer.
+
+Design (B200-first; digests: ``moe/veScale_FSDP_reading_notes.md:74-100`` block-aligned ragged
+shards, ``moe/MegatronCore_MoE_reading_notes.md:266-284`` dual dense/expert mesh with persistent
+buffers):
+
+* A **unit** is one decoder layer (or the embedding, or the head).  Its parameters are packed into at
+  most two **flat groups**: dense parameters sharded over every data rank of the pipeline stage, and
+  expert parameters sharded over the ranks that own the same experts.
+* Every parameter starts on a multiple of 128 elements inside the flat buffer and the per-rank shard
+  length is a multiple of 128, so a 1x128 / 128x128 fp8 scale block never straddles two ranks and
+  every shard is 256-byte aligned for bulk copies.
+* The owned shard (fp32 master, or the bf16 weights themselves when ``master_weights`` is off) is the
+  source of truth.  ``gather()`` materialises the full flat buffer in the compute dtype and the
+  module's parameters are views into it; ``release()`` drops its storage.
+* Gradients are written by autograd straight into a flat gradient buffer (``p.grad`` are views),
+  reduce-scattered into the shard, accumulated over micro-batches in fp32 and consumed by the
+  fused AdamW kernel.
+
+With one rank in a group nothing is gathered or freed: the flat buffer is persistent.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+ALIGN = 128
+
+_DT = {"fp32": torch.float32, "bf16": torch.bfloat16}
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatGroup:
+    def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], group, group_size: int,
+                 group_rank: int, compute_dtype: torch.dtype, master_weights: bool, device: torch.device,
+                 comm=None):
+        self.name = name
+        self.group, self.world, self.rank = group, group_size, group_rank
+        self.compute_dtype = compute_dtype
+        self.device = device
+        self.comm = comm                          # optional fused peer-memory collectives
+        self.names = [n for n, _ in named_params]
+        self.params = [p for _, p in named_params]
+        self.shapes = [tuple(p.shape) for p in self.params]
+        self.offsets = []
+        off = 0
+        for p in self.params:
+            self.offsets.append(off)
+            off += _round_up(p.numel(), ALIGN)
+        self.total = _round_up(max(off, ALIGN), ALIGN * self.world)
+        self.shard_numel = self.total // self.world
+        self.sharded = self.world > 1
+        self.keep_master = master_weights and compute_dtype != torch.float32
+
+        # full buffer (compute dtype); parameters become views into it.  Parameters created on the
+        # meta device carry no values yet: the caller initialises the views, then calls finalize().
+        self.full = torch.zeros(self.total, dtype=compute_dtype, device=device)
+        hi_src = None
+        for p, o in zip(self.params, self.offsets):
+            if not p.is_meta:
+                self.full[o:o + p.numel()].copy_(p.detach().reshape(-1))
+                if self.keep_master and p.dtype == torch.float32:
+                    if hi_src is None:
+                        hi_src = torch.zeros(self.total, dtype=torch.float32, device=device)
+                    hi_src[o:o + p.numel()].copy_(p.detach().reshape(-1))
+        self._hi_src = hi_src
+        for i, (p, o, shp) in enumerate(zip(self.params, self.offsets, self.shapes)):
+            if p.is_meta:
+                newp = nn.Parameter(self.full[o:o + p.numel()].view(shp), requires_grad=p.requires_grad)
+                for attr in ("is_expert",):
+                    if hasattr(p, attr):
+                        setattr(newp, attr, getattr(p, attr))
+                self.params[i] = newp
+            else:
+                p.data = self.full[o:o + p.numel()].view(shp)
+        self.shard: torch.Tensor | None = None
+        self.grad_full: torch.Tensor | None = None
+        self.grad_shard: torch.Tensor | None = None     # fp32 accumulation over micro-batches
+        self.replica_group = None                       # unsharded data-parallel replicas (plain DDP)
+        self.gathered = True
+
+    def finalize(self) -> None:
+        """Take the owned shard (the optimizer's source of truth) from the initialised full buffer."""
+        lo = self.rank * self.shard_numel
+        if self.keep_master:
+            src = self._hi_src if self._hi_src is not None else self.full
+            self.shard = src[lo:lo + self.shard_numel].float().clone()
+        elif self.sharded:
+            self.shard = self.full[lo:lo + self.shard_numel].clone()
+        else:
+            self.shard = self.full                # single rank, no master: optimizer updates in place
+        self._hi_src = None
+        if self.sharded:
+            self.release()
+
+    # ---- parameters -------------------------------------------------------
+    def shard_in_compute_dtype(self) -> torch.Tensor:
+        return self.shard if self.shard.dtype == self.compute_dtype else self.shard.to(self.compute_dtype)
+
+    def gather(self) -> None:
+        if self.gathered:
+            return
+        if self.sharded:
+            st = self.full.untyped_storage()
+            if st.size() == 0:
+                st.resize_(self.total * self.full.element_size())
+            src = self.shard_in_compute_dtype()
+            # write through an alias with its own version counter: autograd may hold parameter views
+            # saved by a forward that ran before this (re-)gather, and the values are the same
+            dst = self.full.data
+            if self.comm is not None:
+                self.comm.all_gather(dst, src, self)
+            else:
+                dist.all_gather_into_tensor(dst, src.contiguous(), group=self.group)
+        self.gathered = True
+
+    def release(self) -> None:
+        if self.sharded and self.gathered:
+            self.full.untyped_storage().resize_(0)
+            self.gathered = False
+
+    def refresh_full_from_shard(self) -> None:
+        """After an optimizer step on an unsharded group with fp32 masters: recast into the compute copy."""
+        if not self.sharded and self.shard is not self.full:
+            self.full.data.copy_(self.shard)
+
+    # ---- gradients ----------------------------------------------------------
+    def prepare_grads(self) -> None:
+        if self.grad_full is None:
+            self.grad_full = torch.zeros(self.total, dtype=self.compute_dtype, device=self.device)
+        for p, o, shp in zip(self.params, self.offsets, self.shapes):
+            p.grad = self.grad_full[o:o + p.numel()].view(shp)
+
+    def reduce_grads(self, keep_full: bool = False) -> None:
+        """Sum ``grad_full`` over the group into this rank's fp32 ``grad_shard`` (accumulating)."""
+        if self.grad_full is None:
+            return
+        if self.sharded:
+            if self.comm is not None:
+                piece = self.comm.reduce_scatter(self.grad_full, self)
+            else:
+                piece = torch.empty(self.shard_numel, dtype=self.grad_full.dtype, device=self.device)
+                dist.reduce_scatter_tensor(piece, self.grad_full, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            piece = self.grad_full
+            if self.replica_group is not None:
+                dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.replica_group)
+        if self.grad_shard is None:
+            self.grad_shard = piece.float()
+        else:
+            self.grad_shard.add_(piece)
+        for p in self.params:
+            p.grad = None
+        self.grad_full = None
+
+    def zero_grad(self) -> None:
+        self.grad_shard = None
+        self.grad_full = None
+        for p in self.params:
+            p.grad = None
+
+    # ---- checkpoint views -----------------------------------------------------
+    def param_slices(self):
+        """Yield ``(name, shape, flat_offset, numel)`` for checkpoint resharding."""
+        for n, o, shp, p in zip(self.names, self.offsets, self.shapes, self.params):
+            yield n, shp, o, p.numel()
+
+
+class Unit:
+    """One FSDP unit: a module plus its flat groups."""
+
+    def __init__(self, name: str, module: nn.Module, groups: list[FlatGroup]):
+        self.name, self.module, self.groups = name, module, groups
+
+    def gather(self):
+        for g in self.groups:
+            g.gather()
+
+    def release(self):
+        for g in self.groups:
+            g.release()
+
+    def prepare_grads(self):
+        for g in self.groups:
+            g.prepare_grads()
+
+    def reduce_grads(self):
+        for g in self.groups:
+            g.reduce_grads()
+
+
+def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, master_weights: bool,
+               device: torch.device, fsdp: bool = True, dense_comm=None, expert_comm=None) -> Unit:
+    dense, expert = [], []
+    for n, p in module.named_parameters():
+        (expert if getattr(p, "is_expert", False) else dense).append((f"{name}.{n}", p))
+    groups = []
+    if dense:
+        if fsdp and mesh.data_size > 1:
+            groups.append(FlatGroup(f"{name}/dense", dense, mesh.data_group, mesh.data_size, mesh.data_rank,
+                                    compute_dtype, master_weights, device, dense_comm))
+        else:
+            g = FlatGroup(f"{name}/dense", dense, None, 1, 0, compute_dtype, master_weights, device)
+            g.replica_group = mesh.data_group if mesh.data_size > 1 else None
+            groups.append(g)
+    if expert:
+        if fsdp and mesh.edp > 1:
+            edp_rank = mesh.edp_rank * mesh.cp + mesh.cp_rank
+            groups.append(FlatGroup(f"{name}/expert", expert, mesh.edp_group, mesh.edp, edp_rank,
+                                    compute_dtype, master_weights, device, expert_comm))
+        else:
+            g = FlatGroup(f"{name}/expert", expert, None, 1, 0, compute_dtype, master_weights, device)
+            g.replica_group = mesh.edp_group if mesh.edp > 1 else None
+            groups.append(g)
+    # parameters that were on the meta device have been re-created as views: re-register them
+    for g in groups:
+        for full_name, p in zip(g.names, g.params):
+            rel = full_name[len(name) + 1:]
+            owner = module
+            *path, leaf = rel.split(".")
+            for part in path:
+                owner = getattr(owner, part)
+            if owner._parameters.get(leaf) is not p:
+                owner._parameters[leaf] = p
+    return Unit(name, module, groups)

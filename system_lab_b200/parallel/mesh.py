@@ -1,0 +1,142 @@
+"""Device mesh: ``world = pp x dp x cp`` with the expert-parallel group folded into ``dp``.
+
+Rank order (fastest varying last): ``rank = (pp_rank * dp + dp_rank) * cp + cp_rank`` and
+``dp_rank = edp_rank * ep + ep_rank``.  Attention-side parameters are sharded over all ``dp * cp``
+data ranks of a stage; expert parameters are owned by their ``ep`` rank and sharded over the
+``edp`` ranks that hold the same experts — the dual dense/expert mesh of
+``moe/MegatronCore_MoE_reading_notes.md:266-284`` and ``summary/torchtitan/*:98-113``.
+
+On an NVSwitch box every pair of GPUs has the same bandwidth, so the mapping is chosen for simple
+group arithmetic, not for locality.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class Mesh:
+    world: int
+    rank: int
+    pp: int
+    dp: int
+    cp: int
+    ep: int
+    pp_rank: int
+    dp_rank: int
+    cp_rank: int
+    ep_rank: int
+    edp_rank: int
+    data_group: object = None      # all dp*cp ranks of this stage (dense parameter shards, grad sync)
+    dp_group: object = None        # dp ranks with the same cp rank
+    ep_group: object = None        # expert all-to-all
+    edp_group: object = None       # ranks holding the same experts (expert parameter shards)
+    cp_group: object = None
+    pp_group: object = None
+    world_group: object = None
+    data_ranks: tuple = ()
+    ep_ranks: tuple = ()
+    edp_ranks: tuple = ()
+    pp_ranks: tuple = ()
+
+    @property
+    def edp(self) -> int:
+        return (self.dp // self.ep) * self.cp
+
+    @property
+    def data_size(self) -> int:
+        return self.dp * self.cp
+
+    @property
+    def data_rank(self) -> int:
+        return self.dp_rank * self.cp + self.cp_rank
+
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp - 1
+
+    def prev_stage_rank(self) -> int:
+        return self.pp_ranks[self.pp_rank - 1]
+
+    def next_stage_rank(self) -> int:
+        return self.pp_ranks[self.pp_rank + 1]
+
+
+def single_process_mesh() -> Mesh:
+    return Mesh(world=1, rank=0, pp=1, dp=1, cp=1, ep=1, pp_rank=0, dp_rank=0, cp_rank=0, ep_rank=0,
+                edp_rank=0, data_ranks=(0,), ep_ranks=(0,), edp_ranks=(0,), pp_ranks=(0,))
+
+
+def init_distributed(device: str = "auto", timeout_s: float = 600.0) -> tuple[int, int, torch.device]:
+    """Join the job described by RANK / WORLD_SIZE / MASTER_* (torchrun).  NCCL on GPUs, gloo on CPU."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = (device == "cuda") or (device == "auto" and torch.cuda.is_available())
+    if use_cuda:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+    else:
+        dev = torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        kw = dict(device_id=dev) if use_cuda else {}
+        dist.init_process_group("nccl" if use_cuda else "gloo", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    return rank, world, dev
+
+
+def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1) -> Mesh:
+    if not dist.is_initialized():
+        if pp * cp != 1:
+            raise ValueError("pp/cp > 1 needs an initialised process group")
+        return single_process_mesh()
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if world % (pp * cp):
+        raise ValueError(f"world={world} not divisible by pp*cp={pp * cp}")
+    dp = world // (pp * cp)
+    ep = min(ep, dp)
+    if dp % ep:
+        raise ValueError(f"dp={dp} not divisible by ep={ep}")
+    edp_n = dp // ep
+
+    def rid(p, d, c):
+        return (p * dp + d) * cp + c
+
+    cp_rank = rank % cp
+    dp_rank = (rank // cp) % dp
+    pp_rank = rank // (cp * dp)
+    ep_rank, edp_rank = dp_rank % ep, dp_rank // ep
+    m = Mesh(world=world, rank=rank, pp=pp, dp=dp, cp=cp, ep=ep, pp_rank=pp_rank, dp_rank=dp_rank,
+             cp_rank=cp_rank, ep_rank=ep_rank, edp_rank=edp_rank, world_group=dist.group.WORLD)
+
+    # every rank must create every group, in the same order
+    def mk(all_lists, mine_pred):
+        got, got_ranks = None, ()
+        for ranks in all_lists:
+            g = dist.new_group(ranks) if len(ranks) > 1 else None
+            if rank in ranks:
+                got, got_ranks = g, tuple(ranks)
+        return got, got_ranks
+
+    data_lists = [[rid(p, d, c) for d in range(dp) for c in range(cp)] for p in range(pp)]
+    m.data_group, m.data_ranks = mk(data_lists, None)
+    dp_lists = [[rid(p, d, c) for d in range(dp)] for p in range(pp) for c in range(cp)]
+    m.dp_group, _ = mk(dp_lists, None)
+    ep_lists = [[rid(p, g * ep + e, c) for e in range(ep)] for p in range(pp) for g in range(edp_n) for c in range(cp)]
+    m.ep_group, m.ep_ranks = mk(ep_lists, None)
+    edp_lists = [[rid(p, g * ep + e, c) for g in range(edp_n) for c in range(cp)] for p in range(pp) for e in range(ep)]
+    m.edp_group, m.edp_ranks = mk(edp_lists, None)
+    cp_lists = [[rid(p, d, c) for c in range(cp)] for p in range(pp) for d in range(dp)]
+    m.cp_group, _ = mk(cp_lists, None)
+    pp_lists = [[rid(p, d, c) for p in range(pp)] for d in range(dp) for c in range(cp)]
+    m.pp_group, m.pp_ranks = mk(pp_lists, None)
+    return m

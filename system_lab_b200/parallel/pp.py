@@ -1,0 +1,111 @@
+"""Pipeline parallel 1F1B schedule over point-to-point send/recv (NCCL on GPUs, gloo on CPU).
+
+Each stage runs ``min(pp - stage - 1, M)`` warm-up forwards, then alternates one forward and one
+backward, then drains.  Paired transfers (send forward + receive backward, send backward + receive
+forward) are posted together with ``batch_isend_irecv`` so neighbouring stages never wait on each
+other's send.  Bubble fraction is ``(pp-1)/(pp-1+M)`` (``pilot/README.v2.md:771``).
+
+Pipeline transfers stay on the library p2p path by design: they are small
+(``mbs x seq x hidden``) next to the expert all-to-all and overlap with compute.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def _p2p(ops_list):
+    if not ops_list:
+        return
+    for r in dist.batch_isend_irecv(ops_list):
+        r.wait()
+
+
+def pipeline_1f1b(engine, mesh, batches, scale: float, cfg) -> torch.Tensor:
+    """Run all micro-batches of one step through this stage.  Returns the summed (unscaled) loss on the
+    last stage and zero elsewhere."""
+    dev = engine.device
+    nmb = len(batches)
+    first, last = mesh.is_first_stage(), mesh.is_last_stage()
+    prev_r = mesh.prev_stage_rank() if not first else None
+    next_r = mesh.next_stage_rank() if not last else None
+    mbs, seq = batches[0][0].shape
+    act_shape = (mbs, seq, cfg.model.hidden_size)
+    dt = engine.compute_dtype
+    loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
+    pending = []            # (input hidden or None, output, aux list) awaiting backward
+
+    def new_act():
+        return torch.empty(act_shape, dtype=dt, device=dev)
+
+    def fwd(i, recv_buf):
+        tok, tgt = batches[i]
+        if first:
+            inp, x = None, tok
+        else:
+            inp = recv_buf.requires_grad_(True)
+            x = inp
+        out, aux = engine.stage_forward(x, tgt if last else None)
+        pending.append((inp, out, aux))
+        return out
+
+    def bwd(grad_out):
+        nonlocal loss_sum
+        inp, out, aux = pending.pop(0)
+        if last:
+            loss_sum = loss_sum + out.detach().float()
+            tensors, grads = [out], [torch.full_like(out, scale)]
+        else:
+            tensors, grads = [out], [grad_out]
+        for a in aux:
+            tensors.append(a)
+            grads.append(torch.full_like(a, scale))
+        torch.autograd.backward(tensors, grads)
+        return inp.grad if inp is not None else None
+
+    warm = min(mesh.pp - mesh.pp_rank - 1, nmb)
+    steady = nmb - warm
+    recv_f = None
+    if not first:
+        recv_f = new_act()
+        _p2p([dist.P2POp(dist.irecv, recv_f, prev_r)])
+    # warm-up forwards
+    for i in range(warm):
+        out = fwd(i, recv_f)
+        ops_l = []
+        if not last:
+            ops_l.append(dist.P2POp(dist.isend, out.detach().contiguous(), next_r))
+        more_fwd = (i + 1 < warm) or steady > 0
+        if not first and more_fwd:
+            recv_f = new_act()
+            ops_l.append(dist.P2POp(dist.irecv, recv_f, prev_r))
+        _p2p(ops_l)
+    # steady state: one forward, one backward
+    for j in range(steady):
+        i = warm + j
+        out = fwd(i, recv_f)
+        grad_out = None
+        ops_l = []
+        if not last:
+            grad_out = new_act()
+            ops_l.append(dist.P2POp(dist.isend, out.detach().contiguous(), next_r))
+            ops_l.append(dist.P2POp(dist.irecv, grad_out, next_r))
+        _p2p(ops_l)
+        gin = bwd(grad_out)
+        ops_l = []
+        if not first:
+            ops_l.append(dist.P2POp(dist.isend, gin.contiguous(), prev_r))
+            if j + 1 < steady:
+                recv_f = new_act()
+                ops_l.append(dist.P2POp(dist.irecv, recv_f, prev_r))
+        _p2p(ops_l)
+    # cool-down backwards
+    for _ in range(warm):
+        grad_out = None
+        if not last:
+            grad_out = new_act()
+            _p2p([dist.P2POp(dist.irecv, grad_out, next_r)])
+        gin = bwd(grad_out)
+        if not first:
+            _p2p([dist.P2POp(dist.isend, gin.contiguous(), prev_r)])
+    return loss_sum

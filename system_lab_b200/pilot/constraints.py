@@ -1,0 +1,189 @@
+"""Config legality rules and the memory model (the tuner's ``constraint.*`` tools).
+
+Behavioural spec: ``skills/pilot/constraints/config.md:29-150`` (legality rules and
+their stable output order), ``skills/pilot/constraints/oom.md:36-103`` (memory
+model and the 92 % HBM rule).  The reference ships these as prose plus stub tool
+handlers (``pilot/agent/worker_tools.py:268-307``); here they are executable and
+the trainer's own ``Config.validate`` calls the same function, so a plan the
+tuner accepts is a plan the trainer accepts.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+HBM_BYTES_B200 = 180 * 1024**3
+HBM_SAFE_FRACTION = 0.92
+
+_DTYPE_BYTES = {"fp32": 4, "bf16": 2, "fp16": 2, "fp8": 1}
+
+
+def _p(rule: str, message: str, hint: str = "", severity: str = "error") -> dict:
+    return {"rule": rule, "message": message, "hint": hint, "severity": severity}
+
+
+def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
+    """Return violations/warnings in the stable order: world size, model dims,
+    micro-batching, MoE, dtype/numerics, sequence length."""
+    m, p, pr, t = cfg.model, cfg.parallel, cfg.precision, cfg.train
+    tp, pp, ep, cp = (p.tensor_model_parallel_size, p.pipeline_model_parallel_size,
+                      p.expert_model_parallel_size, p.context_parallel_size)
+    out: list[dict] = []
+    # 1. world size
+    dp = None
+    if world_size is not None:
+        if world_size % (tp * pp * cp) != 0:
+            out.append(_p("world_size_match", f"tp*pp*cp={tp*pp*cp} does not divide world_size={world_size}",
+                          "rebalance one of {tp, pp, cp}"))
+        else:
+            dp = world_size // (tp * pp * cp)
+            if ep > world_size:
+                out.append(_p("ep_le_world_size", f"ep={ep} > world_size={world_size}"))
+            elif dp % ep != 0 and world_size % ep != 0:
+                out.append(_p("ep_divides_dp_or_world", f"ep={ep} divides neither dp={dp} nor world={world_size}",
+                              "pick ep from divisors(dp)"))
+    # 2. model dims
+    if m.num_attention_heads % tp:
+        out.append(_p("tp_divides_num_heads", f"num_attention_heads={m.num_attention_heads} % tp={tp} != 0"))
+    if m.num_query_groups % tp:
+        out.append(_p("tp_divides_kv_heads_for_gqa", f"num_query_groups={m.num_query_groups} % tp={tp} != 0"))
+    if m.num_attention_heads % max(m.num_query_groups, 1):
+        out.append(_p("heads_divisible_by_groups",
+                      f"num_attention_heads={m.num_attention_heads} % num_query_groups={m.num_query_groups} != 0"))
+    if m.num_layers % (pp * p.virtual_pipeline_model_parallel_size):
+        out.append(_p("pp_divides_num_layers", f"num_layers={m.num_layers} % (pp*vpp)="
+                      f"{pp * p.virtual_pipeline_model_parallel_size} != 0"))
+    if m.num_experts and m.num_experts % ep:
+        out.append(_p("ep_divides_num_experts", f"num_experts={m.num_experts} % ep={ep} != 0",
+                      "pick ep from divisors(num_experts)"))
+    if m.attention_type not in ("gqa", "mla"):
+        out.append(_p("attention_type", f"attention_type={m.attention_type!r} not in (gqa, mla)"))
+    if m.attention_type == "mla" and min(m.kv_lora_rank, m.qk_nope_head_dim, m.qk_rope_head_dim, m.v_head_dim) <= 0:
+        out.append(_p("mla_dims", "mla needs kv_lora_rank, qk_nope_head_dim, qk_rope_head_dim, v_head_dim > 0"))
+    # 3. micro-batching
+    if dp is not None:
+        denom = t.micro_batch_size * dp
+        if t.global_batch_size % denom:
+            out.append(_p("gbs_decomposes", f"global_batch_size={t.global_batch_size} is not a multiple of mbs*dp={denom}",
+                          "set gbs to a multiple of mbs x dp"))
+        else:
+            nmb = t.global_batch_size // denom
+            if nmb < pp:
+                out.append(_p("num_microbatch_geq_pp", f"num_microbatch={nmb} < pp={pp}"))
+            elif pp > 1 and nmb < 2 * pp:
+                out.append(_p("very_small_num_microbatch", f"num_microbatch={nmb} < 2*pp: bubble will dominate",
+                              "mbs down or gbs up", severity="warning"))
+            if t.optimizer_in_backward and nmb > 1:
+                out.append(_p("optimizer_in_backward_single_microbatch",
+                              "optimizer_in_backward needs exactly one micro-batch per step"))
+    if p.virtual_pipeline_model_parallel_size > 1 and pp == 1:
+        out.append(_p("vpp_requires_pp_gt_1", "vpp > 1 needs pp > 1"))
+    # 4. MoE
+    if m.num_experts and m.moe_router_topk > m.num_experts:
+        out.append(_p("top_k_le_num_experts", f"topk={m.moe_router_topk} > num_experts={m.num_experts}"))
+    if m.moe_router_score_function not in ("softmax", "sigmoid"):
+        out.append(_p("router_score_function", f"unknown score function {m.moe_router_score_function!r}"))
+    if m.moe_token_dispatcher_type not in ("fused", "alltoall"):
+        out.append(_p("dispatcher_type", f"unknown dispatcher {m.moe_token_dispatcher_type!r}"))
+    # 5. dtype / numerics
+    if pr.params_dtype not in ("fp32", "bf16"):
+        out.append(_p("params_dtype", f"params_dtype={pr.params_dtype!r} not in (fp32, bf16)"))
+    if pr.optimizer_state_dtype not in ("fp32", "bf16", "fp8"):
+        out.append(_p("optimizer_state_dtype", f"optimizer_state_dtype={pr.optimizer_state_dtype!r}"))
+    if pr.fp8 and pr.fp8_recipe not in ("blockwise", "tensorwise", "delayed"):
+        out.append(_p("fp8_recipe", f"fp8_recipe={pr.fp8_recipe!r}"))
+    if pr.fp8 and pr.optimizer_state_dtype != "fp32":
+        out.append(_p("optim_state_dtype_for_dtype",
+                      "fp8 compute with non-fp32 optimizer state: updates may stall", severity="warning"))
+    if pr.recompute_granularity not in ("none", "selective", "full"):
+        out.append(_p("recompute_granularity", f"recompute_granularity={pr.recompute_granularity!r}"))
+    # 6. sequence length
+    if cp > 1 and m.seq_length % cp:
+        out.append(_p("cp_divides_seq_len", f"seq_length={m.seq_length} % cp={cp} != 0"))
+    if cp > 1 and m.num_attention_heads % cp:
+        out.append(_p("cp_divides_heads", f"head-sharded context parallel needs num_attention_heads % cp == 0"))
+    return out
+
+
+# --------------------------------------------------------------------------
+# parameter counts and the memory model
+# --------------------------------------------------------------------------
+def param_counts(m: Any) -> dict:
+    """Parameter counts of the decoder described by ``ModelConfig`` (elements)."""
+    h = m.hidden_size
+    if m.attention_type == "mla":
+        qk = m.qk_nope_head_dim + m.qk_rope_head_dim
+        nh = m.num_attention_heads
+        q = (h * m.q_lora_rank + m.q_lora_rank + m.q_lora_rank * nh * qk) if m.q_lora_rank else h * nh * qk
+        kv = h * (m.kv_lora_rank + m.qk_rope_head_dim) + m.kv_lora_rank \
+            + m.kv_lora_rank * nh * (m.qk_nope_head_dim + m.v_head_dim)
+        attn = q + kv + nh * m.v_head_dim * h
+    else:
+        d = m.kv_channels
+        attn = h * m.num_attention_heads * d + 2 * h * m.num_query_groups * d + m.num_attention_heads * d * h
+    norms = 2 * h
+    dense_ffn = 3 * h * m.ffn_hidden_size
+    expert = 3 * h * m.moe_ffn_hidden_size
+    shared = 3 * h * m.moe_shared_expert_intermediate_size
+    router = h * m.num_experts + (m.num_experts if m.moe_router_load_balancing_type == "bias" else 0)
+    n_moe = max(m.num_layers - m.first_k_dense, 0) if m.num_experts else 0
+    n_dense = m.num_layers - n_moe
+    embed = m.vocab_size * h * (1 if m.tie_embeddings else 2) + h
+    non_expert = (attn + norms) * m.num_layers + dense_ffn * n_dense + (router + shared) * n_moe + embed
+    experts = expert * m.num_experts * n_moe
+    active = non_expert + expert * m.moe_router_topk * n_moe
+    return {"total": non_expert + experts, "non_expert": non_expert, "experts": experts,
+            "active_per_token": active, "per_layer_expert": expert * m.num_experts,
+            "per_layer_non_expert": attn + norms + router + shared}
+
+
+def bytes_per_param(pr: Any, optimizer_in_backward: bool = False) -> float:
+    """Resident bytes per (sharded) parameter: weight + master + grad + two moments."""
+    w = _DTYPE_BYTES[pr.params_dtype]
+    master = 4 if (pr.params_dtype != "fp32" and pr.master_weights) else 0
+    grad = 0 if optimizer_in_backward else (2 if pr.params_dtype == "bf16" else 4)
+    mom = {"fp32": 8.0, "bf16": 4.0, "fp8": 2.0 + 8.0 / 128}[pr.optimizer_state_dtype]
+    return w + master + grad + mom
+
+
+def estimate_memory(cfg: Any, world_size: int) -> dict:
+    """Per-GPU peak memory estimate (bytes) of one training step.
+
+    ``Mem_peak = params + grads + optimizer state + activations + transient buffers``
+    (``skills/pilot/execution-model/SKILL.md:28-35``).  Expert parameters are
+    sharded over ``ep`` and then over the remaining data ranks (``edp``); everything
+    else over all data ranks when FSDP is on.
+    """
+    m, p, pr, t = cfg.model, cfg.parallel, cfg.precision, cfg.train
+    pc = param_counts(m)
+    pp = p.pipeline_model_parallel_size
+    dp = max(world_size // (pp * p.tensor_model_parallel_size * p.context_parallel_size), 1)
+    ep = min(p.expert_model_parallel_size, dp)
+    edp = max(dp // ep, 1)
+    shard_dense = dp if p.fsdp else 1
+    shard_exp = ep * (edp if p.fsdp else 1)
+    bpp = bytes_per_param(pr, t.optimizer_in_backward)
+    state = (pc["non_expert"] / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
+    wbytes = _DTYPE_BYTES[pr.params_dtype]
+    # transient: one layer's gathered params (+ its grads when optimizer runs in backward)
+    layer_params = pc["per_layer_non_expert"] + pc["per_layer_expert"] / ep
+    transient = layer_params * wbytes * (2 if p.fsdp else 0) + (layer_params * 2 if t.optimizer_in_backward else 0)
+    tokens = t.micro_batch_size * m.seq_length // p.context_parallel_size
+    h = m.hidden_size
+    act_b = 2 if pr.params_dtype == "bf16" else 4
+    layers_here = m.num_layers // pp
+    slots = tokens * m.moe_router_topk
+    f = m.moe_ffn_hidden_size
+    per_layer_full = tokens * h * act_b * 10 + slots * (2 * h + 3 * f) * act_b
+    if pr.recompute_granularity == "full":
+        acts = layers_here * tokens * h * act_b + per_layer_full
+    elif pr.recompute_granularity == "selective":
+        acts = layers_here * (tokens * h * act_b * 6 + slots * h * act_b)
+    else:
+        acts = layers_here * per_layer_full
+    logits = tokens * m.vocab_size * 4 / 4 + tokens * h * act_b * 2     # chunked cross entropy: quarter at a time
+    total = state + transient + acts + logits
+    cap = HBM_BYTES_B200
+    return {"state_bytes": state, "transient_bytes": transient, "activation_bytes": acts,
+            "logits_bytes": logits, "total_bytes": total, "hbm_bytes": cap,
+            "fraction": total / cap, "fits": total <= HBM_SAFE_FRACTION * cap,
+            "bytes_per_param": bpp}

@@ -1,0 +1,51 @@
+"""``python -m system_lab_b200.train --config cfg.yaml [--preset NAME] [key=value ...]``
+
+Resolution order: defaults < preset < YAML < ``key=value`` overrides; the resolved config is
+written to ``<save dir or cwd>/resolved_config.json`` before the first step.  Under ``torchrun`` each
+process drives one GPU (NCCL); without GPUs the same command runs on CPU ranks over gloo.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import sys
+from pathlib import Path
+
+from .config import Config
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser("system_lab_b200.train")
+    ap.add_argument("--config", default=None, help="YAML file")
+    ap.add_argument("--preset", default=None, help="named preset (see models/presets.py)")
+    ap.add_argument("--resume", default=None, help="checkpoint directory (or its parent) to resume from")
+    ap.add_argument("--print-config", action="store_true", help="print the resolved config and exit")
+    ap.add_argument("overrides", nargs="*", help="key=value overrides")
+    args = ap.parse_args(argv)
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)-7s %(name)s :: %(message)s")
+    cfg = Config.load(args.config, args.overrides, args.preset)
+    if args.print_config:
+        print(json.dumps(cfg.to_dict(), indent=2, sort_keys=True))
+        return 0
+    from .trainer.loop import Trainer
+    tr = Trainer(cfg)
+    if tr.mesh.rank == 0:
+        out_dir = Path(cfg.checkpoint.save or ".")
+        cfg.dump(out_dir / "resolved_config.json")
+    resume = args.resume or cfg.checkpoint.load
+    if resume:
+        tr.load_checkpoint(resume)
+    snap = tr.fit(max(cfg.train.train_iters - tr.step, 0))
+    if tr.mesh.rank == 0:
+        m = snap["metrics"]
+        print(json.dumps({"final_loss": tr.loss_curve[-1] if tr.loss_curve else None, "tps": m["tps"],
+                          "step_time_ms": m["step_time_ms"], "steps": tr.step}))
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

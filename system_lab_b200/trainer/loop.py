@@ -1,0 +1,215 @@
+"""Training loop: micro-batches → (pipeline) forward/backward → sharded AdamW → metrics.
+
+Public API (also what ``bench.py`` times end to end)::
+
+    trainer = Trainer(cfg)                # joins the torchrun job, builds mesh/engine/optimizer
+    out = trainer.train_step()            # one optimizer step on the next synthetic global batch
+    trainer.fit()                         # cfg.train.train_iters steps with logging/checkpoints
+
+Per-iteration log line carries what the reference's trainer printed
+(``notes/2026-04/2026-04-19_gptoss_01_mlperf_best_e2e_run.md:116-131``): elapsed ms, TFLOP/s/GPU,
+tokens/s/GPU, lm loss, grad norm, NaN/skipped iterations, device memory.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..config import Config
+from ..parallel.engine import Engine
+from ..parallel.mesh import Mesh, build_mesh, init_distributed
+from ..pilot.constraints import param_counts
+from .data import SyntheticData
+from .optim import ShardedAdamW, lr_at
+
+log = logging.getLogger("system_lab_b200.train")
+
+
+def model_flops_per_token(m) -> float:
+    """Training FLOPs per token (forward + backward = 3x forward): dense matmuls on the *active*
+    parameters plus causal attention."""
+    pc = param_counts(m)
+    embed = m.vocab_size * m.hidden_size            # the lookup is not a matmul
+    matmul = 2.0 * (pc["active_per_token"] - embed - m.hidden_size)
+    if m.attention_type == "mla":
+        d_qk, d_v = m.qk_nope_head_dim + m.qk_rope_head_dim, m.v_head_dim
+    else:
+        d_qk = d_v = m.kv_channels
+    attn = 2.0 * m.seq_length * m.num_attention_heads * (d_qk + d_v) / 2.0 * m.num_layers
+    return 3.0 * (matmul + attn)
+
+
+class NumericalError(RuntimeError):
+    """Loss or gradient norm is NaN/Inf (failure kind NUMERICAL)."""
+
+
+class Trainer:
+    def __init__(self, cfg: Config, mesh: Mesh | None = None, device: torch.device | None = None):
+        self.cfg = cfg
+        if mesh is None:
+            rank, world, device = init_distributed(cfg.train.device, timeout_s=max(cfg.train.hang_timeout_s, 60))
+            cfg.validate(world)
+            mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
+                              cfg.parallel.context_parallel_size)
+        self.mesh, self.device = mesh, device or torch.device("cpu")
+        mode = cfg.train.use_cuda_kernels
+        if mode == "false" or self.device.type != "cuda":
+            ops.set_kernel_mode("reference")
+        else:
+            ops.set_kernel_mode("auto")
+        torch.manual_seed(cfg.train.seed)
+        self.engine = Engine(cfg, mesh, self.device)
+        t = cfg.train
+        self.optimizer = ShardedAdamW(self.engine, lr=t.lr, beta1=t.adam_beta1, beta2=t.adam_beta2, eps=t.adam_eps,
+                                      weight_decay=t.weight_decay, clip_grad=t.clip_grad,
+                                      state_dtype=cfg.precision.optimizer_state_dtype)
+        if t.optimizer_in_backward:
+            self.engine.optimizer = self.optimizer
+        self.data = SyntheticData(cfg.model.vocab_size, cfg.model.seq_length, t.global_batch_size,
+                                  t.micro_batch_size, mesh.dp_rank, mesh.dp, mesh.cp_rank, mesh.cp, t.seed,
+                                  pin=self.device.type == "cuda")
+        self.step = 0
+        self.loss_curve: list[float] = []
+        self.step_times_ms: list[float] = []
+        self.nan_iters = 0
+        self.flops_per_token = model_flops_per_token(cfg.model)
+        self.tokens_per_step = t.global_batch_size * cfg.model.seq_length
+        self._tpe_accum = None
+        self.events = None
+        if t.mllog:
+            from .mllog import MLLogger
+            self.events = MLLogger(enabled=mesh.rank == 0)
+
+    # ---- one optimizer step ---------------------------------------------------------------
+    def train_step(self, batches=None) -> dict:
+        """Runs one full step.  ``batches``: optional list of host ``(tokens, targets)`` micro-batches;
+        by default the next synthetic global batch.  Returns ``{"loss": device scalar, "grad_norm": ...}``."""
+        cfg, mesh = self.cfg, self.mesh
+        step = self.step + 1
+        if batches is None:
+            batches = self.data.microbatches(self.step)
+        nmb = len(batches)
+        dev = self.device
+        dev_batches = [(tok.to(dev, non_blocking=True), tgt.to(dev, non_blocking=True)) for tok, tgt in batches]
+        lr = lr_at(step, lr=cfg.train.lr, min_lr=cfg.train.min_lr, warmup=cfg.train.lr_warmup_iters,
+                   decay_iters=cfg.train.lr_decay_iters, style=cfg.train.lr_decay_style)
+        in_bwd = cfg.train.optimizer_in_backward
+        if in_bwd:
+            self.optimizer.begin_step(lr)
+        scale = 1.0 / (nmb * mesh.data_size)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
+        if mesh.pp > 1:
+            from ..parallel.pp import pipeline_1f1b
+            loss_sum = pipeline_1f1b(self.engine, mesh, dev_batches, scale, cfg)
+        else:
+            for tok, tgt in dev_batches:
+                loss, aux = self.engine.stage_forward(tok, tgt)
+                total = loss * scale
+                for a in aux:
+                    total = total + a * scale
+                total.backward()
+                loss_sum = loss_sum + loss.detach().float()
+        grad_norm = self.optimizer.end_step_in_backward() if in_bwd else self.optimizer.step(lr)
+        self._update_router_bias()
+        # mean loss over micro-batches and data ranks (reported from the last pipeline stage)
+        loss_mean = loss_sum / nmb
+        if dist.is_initialized() and mesh.world > 1:
+            if mesh.pp > 1:
+                # only last-stage ranks hold a loss; others contribute zero
+                dist.all_reduce(loss_mean)
+                loss_mean = loss_mean / mesh.data_size
+            else:
+                dist.all_reduce(loss_mean)
+                loss_mean = loss_mean / mesh.world
+        self.step = step
+        return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
+
+    def _update_router_bias(self) -> None:
+        m = self.cfg.model
+        ffns = self.engine.moe_ffns()
+        if not ffns:
+            return
+        counts = [f.last_tokens_per_expert for f in ffns if f.last_tokens_per_expert is not None]
+        if not counts:
+            return
+        tpe = torch.stack(counts).float()
+        if dist.is_initialized() and self.mesh.data_size > 1:
+            dist.all_reduce(tpe, group=self.mesh.data_group)
+        self._tpe_accum = tpe if self._tpe_accum is None else self._tpe_accum + tpe
+        if m.moe_router_load_balancing_type == "bias":
+            for f, c in zip(ffns, tpe):
+                f.update_router_bias(c)
+
+    # ---- full run ----------------------------------------------------------------------------
+    def fit(self, iters: int | None = None) -> dict:
+        cfg, t = self.cfg, self.cfg.train
+        iters = t.train_iters if iters is None else iters
+        is_cuda = self.device.type == "cuda"
+        if self.events:
+            self.events.start(cfg)
+        prof = None
+        if cfg.profile.profile and self.mesh.rank in cfg.profile.profile_ranks:
+            from ..observe.profiler import StepProfiler
+            prof = StepProfiler(cfg.profile, self.mesh.rank)
+        target = self.step + iters
+        while self.step < target:
+            if is_cuda:
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if prof:
+                prof.step_begin(self.step + 1)
+            out = self.train_step()
+            loss = float(out["loss"])              # host read: also the step's device sync
+            gn = float(out["grad_norm"])
+            if prof:
+                prof.step_end(self.step)
+            dt_ms = (time.perf_counter() - t0) * 1e3
+            self.step_times_ms.append(dt_ms)
+            self.loss_curve.append(loss)
+            bad = not (loss == loss and abs(loss) != float("inf") and gn == gn and gn != float("inf"))
+            if bad:
+                self.nan_iters += 1
+                if t.check_for_nan_in_loss_and_grad:
+                    raise NumericalError(f"step {self.step}: loss={loss} grad_norm={gn}")
+            if self.mesh.rank == 0 and (self.step % max(t.log_interval, 1) == 0):
+                self._log_line(dt_ms, loss, gn, out["lr"])
+            ck = cfg.checkpoint
+            if ck.save and ck.save_interval and self.step % ck.save_interval == 0:
+                self.save_checkpoint(ck.save)
+        if cfg.checkpoint.save and not cfg.checkpoint.disable_last_saving:
+            self.save_checkpoint(cfg.checkpoint.save)
+        if self.events:
+            self.events.stop(self.tokens_per_step * self.step)
+        snap = self.snapshot()
+        if cfg.profile.snapshot_path and self.mesh.rank == 0:
+            Path(cfg.profile.snapshot_path).parent.mkdir(parents=True, exist_ok=True)
+            Path(cfg.profile.snapshot_path).write_text(json.dumps(snap, indent=2))
+        return snap
+
+    def _log_line(self, dt_ms: float, loss: float, gn: float, lr: float) -> None:
+        tps_gpu = self.tokens_per_step / (dt_ms / 1e3) / self.mesh.world
+        tflops = tps_gpu * self.flops_per_token / 1e12
+        mem = torch.cuda.max_memory_allocated() / 2**30 if self.device.type == "cuda" else 0.0
+        log.info("iteration %6d | elapsed ms/iter %9.1f | TFLOP/s/GPU %7.1f | tokens/s/GPU %9.0f | lm loss %.6f | "
+                 "grad norm %.4f | lr %.3e | nan iters %d | mem GiB %.1f",
+                 self.step, dt_ms, tflops, tps_gpu, loss, gn, lr, self.nan_iters, mem)
+
+    # ---- the tuner's Snapshot (metric contract: skills/pilot/workflow/observe.md:36-112) ------------
+    def snapshot(self) -> dict:
+        from ..observe.snapshot import build_snapshot
+        return build_snapshot(self)
+
+    # ---- checkpoints -----------------------------------------------------------------------------
+    def save_checkpoint(self, root: str) -> str:
+        from ..ckpt.sharded import save_checkpoint
+        return save_checkpoint(self, root)
+
+    def load_checkpoint(self, path: str) -> None:
+        from ..ckpt.sharded import load_checkpoint
+        load_checkpoint(self, path)

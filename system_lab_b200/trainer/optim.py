@@ -1,0 +1,191 @@
+"""Sharded AdamW over the engine's flat groups, with global-norm clipping.
+
+Every flat group owns one contiguous shard, so the optimizer is a handful of large launches of the
+fused kernel (``csrc/adamw.cu``) instead of the per-parameter ``multi_tensor_apply`` tail the
+reference traces show (``notes/2026-04/2026-04-22_gptoss_15_*:119-131``, 369 L2-norm launches per
+iteration in ``notes/2026-04/2026-04-21_gptoss_09_*:102-108``).  The clip coefficient stays on the
+device: no ``.item()`` in the step.
+
+Moments may be stored in fp32, bf16 or block-scaled 8 bit (e4m3 per 128 elements; the second
+moment is stored as its square root to halve the exponent range it needs).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import reference as ref
+from ..parallel.engine import Engine
+
+
+class _Moment:
+    """One optimizer moment for a flat shard in the configured storage format."""
+
+    def __init__(self, n: int, kind: str, device, sqrt_domain: bool = False):
+        self.kind, self.n, self.sqrt_domain = kind, n, sqrt_domain
+        if kind == "fp32":
+            self.data = torch.zeros(n, dtype=torch.float32, device=device)
+        elif kind == "bf16":
+            self.data = torch.zeros(n, dtype=torch.bfloat16, device=device)
+        else:
+            self.data = torch.zeros(n, dtype=torch.float8_e4m3fn, device=device)
+            self.scale = torch.zeros(n // 128, dtype=torch.float32, device=device)
+
+    def load(self) -> torch.Tensor:
+        if self.kind == "fp32":
+            return self.data
+        if self.kind == "bf16":
+            x = self.data.float()
+        else:
+            x = ref.dequant_1x128(self.data, self.scale)
+        return x * x if self.sqrt_domain else x
+
+    def store(self, x: torch.Tensor) -> None:
+        if self.kind == "fp32":
+            if x is not self.data:
+                self.data.copy_(x)
+            return
+        if self.sqrt_domain:
+            x = x.sqrt()
+        if self.kind == "bf16":
+            self.data.copy_(x)
+        else:
+            q, s = ref.quant_1x128(x)
+            self.data.copy_(q)
+            self.scale.copy_(s)
+
+    def state(self) -> dict:
+        d = {"data": self.data}
+        if self.kind == "fp8":
+            d["scale"] = self.scale
+        return d
+
+
+class ShardedAdamW:
+    def __init__(self, engine: Engine, *, lr: float, beta1: float, beta2: float, eps: float,
+                 weight_decay: float, clip_grad: float, state_dtype: str = "fp32"):
+        self.engine = engine
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.weight_decay, self.clip_grad = weight_decay, clip_grad
+        self.state_dtype = state_dtype
+        self.step_count = 0
+        self.m, self.v = {}, {}
+        dev = engine.device
+        for g in engine.all_groups():
+            n = g.shard.numel()
+            self.m[g.name] = _Moment(n, state_dtype, dev)
+            self.v[g.name] = _Moment(n, state_dtype, dev, sqrt_domain=(state_dtype != "fp32"))
+        self.last_grad_norm: torch.Tensor | None = None
+        self._prev_norm: torch.Tensor | None = None     # for delayed clipping in optimizer-in-backward mode
+        self._sq_accum: torch.Tensor | None = None
+
+    # ---- gradient norm ------------------------------------------------------------
+    def _replication(self, g) -> int:
+        if g.sharded or g.replica_group is None:
+            return 1
+        return dist.get_world_size(g.replica_group)
+
+    def global_grad_norm(self) -> torch.Tensor:
+        dev = self.engine.device
+        sq = torch.zeros((), dtype=torch.float32, device=dev)
+        for g in self.engine.all_groups():
+            if g.grad_shard is not None:
+                sq = sq + g.grad_shard.float().pow(2).sum() / self._replication(g)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(sq)
+        return sq.sqrt()
+
+    def _clip_coef(self, norm: torch.Tensor) -> torch.Tensor:
+        if self.clip_grad <= 0:
+            return torch.ones((), dtype=torch.float32, device=self.engine.device)
+        return torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0)
+
+    # ---- update -----------------------------------------------------------------------
+    def _update_group(self, g, coef: torch.Tensor, lr: float) -> None:
+        if g.grad_shard is None:
+            return
+        from .. import ops
+        if ops.use_kernels(g.shard):
+            from ..ops import cuda as cops
+            cops.adamw_flat(g, self.m[g.name], self.v[g.name], coef, lr=lr, beta1=self.beta1, beta2=self.beta2,
+                            eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
+        else:
+            p32 = g.shard.float() if g.shard.dtype != torch.float32 else g.shard
+            m, v = self.m[g.name].load(), self.v[g.name].load()
+            m = m.clone() if m is not self.m[g.name].data else m
+            v = v.clone() if v is not self.v[g.name].data else v
+            ref.adamw_step(p32, g.grad_shard * coef, m, v, lr=lr, beta1=self.beta1, beta2=self.beta2,
+                           eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
+            self.m[g.name].store(m)
+            self.v[g.name].store(v)
+            if p32 is not g.shard:
+                g.shard.copy_(p32)
+            g.refresh_full_from_shard()
+        g.grad_shard = None
+
+    def begin_step(self, lr: float | None = None) -> None:
+        """Call before backward when the update runs inside backward."""
+        self.step_count += 1
+        self._cur_lr = self.lr if lr is None else lr
+        self._sq_accum = torch.zeros((), dtype=torch.float32, device=self.engine.device)
+
+    def step_unit(self, unit) -> None:
+        """optimizer-in-backward: update one unit as soon as its gradients are reduced.  Clipping uses
+        the previous step's global norm (the current one is not known until backward ends)."""
+        coef = self._clip_coef(self._prev_norm) if self._prev_norm is not None else \
+            torch.ones((), dtype=torch.float32, device=self.engine.device)
+        for g in unit.groups:
+            if g.grad_shard is not None:
+                self._sq_accum = self._sq_accum + g.grad_shard.float().pow(2).sum() / self._replication(g)
+            self._update_group(g, coef, self._cur_lr)
+
+    def end_step_in_backward(self) -> torch.Tensor:
+        sq = self._sq_accum
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(sq)
+        self._prev_norm = self.last_grad_norm = sq.sqrt()
+        return self.last_grad_norm
+
+    def step(self, lr: float | None = None) -> torch.Tensor:
+        self.step_count += 1
+        lr = self.lr if lr is None else lr
+        norm = self.global_grad_norm()
+        self.last_grad_norm = norm
+        coef = self._clip_coef(norm)
+        for g in self.engine.all_groups():
+            self._update_group(g, coef, lr)
+        return norm
+
+    # ---- checkpoint -----------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return {"step": self.step_count,
+                "m": {k: m.state() for k, m in self.m.items()},
+                "v": {k: v.state() for k, v in self.v.items()},
+                "prev_norm": self._prev_norm}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = sd["step"]
+        for k, st in sd["m"].items():
+            for f, t in st.items():
+                getattr(self.m[k], f).copy_(t)
+        for k, st in sd["v"].items():
+            for f, t in st.items():
+                getattr(self.v[k], f).copy_(t)
+        self._prev_norm = sd.get("prev_norm")
+
+
+def lr_at(step: int, *, lr: float, min_lr: float, warmup: int, decay_iters: int, style: str) -> float:
+    """Learning rate for 1-based ``step``.  ``constant`` ignores decay; a launcher default must never
+    silently change the schedule (``notes/2026-04/2026-04-28_gptoss_27_mlperf_legal_baseline.md:193-214``)."""
+    if warmup > 0 and step <= warmup:
+        return lr * step / warmup
+    if style == "constant" or decay_iters <= 0:
+        return lr
+    t = min(max(step - warmup, 0) / max(decay_iters - warmup, 1), 1.0)
+    if style == "cosine":
+        return min_lr + 0.5 * (lr - min_lr) * (1 + math.cos(math.pi * t))
+    if style == "linear":
+        return lr + (min_lr - lr) * t
+    raise ValueError(f"unknown lr_decay_style {style!r}")
