@@ -1,0 +1,568 @@
+// Bandwidth-bound fused ops: RMSNorm (+residual) fwd/bwd, SwiGLU(*probs) fwd/bwd without the
+// concatenated gradient, RoPE, 1x128 / 128x128 fp8 quantisation, squared L2 norm and the flat AdamW
+// step.  All activations are bf16, all arithmetic is fp32, every access is a 16-byte vector.
+//
+// Reference analogues: Triton RMSNorm with fp32 row partials for dgamma
+// (notes/2026-04/2026-04-20_gptoss_02_triton_rmsnorm_optimization.md:47-62), fused residual+RMSNorm
+// (notes/2026-04/2026-04-24_gptoss_17_fused_residual_rmsnorm_impl.md:43-83), SwiGLU*probs forward and
+// no-cat backward (notes/2026-04/2026-04-25_gptoss_23_swiglu_nocat_triton_verify.md:92-113).
+#include "common.cuh"
+
+namespace slab {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV_LIMIT = 8;   // vec8 chunks per thread: H <= 256*8*8 = 16384
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// y = (x [+ res]) * rstd * w ; optionally writes xpr = x + res and rstd.  One block per row (grid-stride).
+template <bool RESIDUAL, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ xpr, float* __restrict__ rstd_out, int rows, int H, float eps) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * H);
+    const bf16x8* rr = RESIDUAL ? reinterpret_cast<const bf16x8*>(res + (size_t)r * H) : nullptr;
+    float vals[NORM_MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        unpack8(xr[c], vals[i]);
+        if (RESIDUAL) {
+          float rv[8];
+          unpack8(rr[c], rv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += rv[j];
+          // the normalised value is computed from the fp32 sum; the stored sum is its bf16 rounding
+          reinterpret_cast<bf16x8*>(xpr + (size_t)r * H)[c] = pack8(vals[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[r] = rstd;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float wv[8], o[8];
+        unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
+        reinterpret_cast<bf16x8*>(y + (size_t)r * H)[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (g*w) - x * rstd^3 * mean(g*w*x) [+ gres] ; dw partial per block (fp32 [gridDim, H]).
+template <bool ADD_RES, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                   const __nv_bfloat16* __restrict__ gres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int H) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  float dw[NORM_MAXV][8];
+  float wv[NORM_MAXV][8];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+    if (c < nvec) unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
+  }
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float rstd = rstd_in[r];
+    float xv[NORM_MAXV][8], gv[NORM_MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        unpack8(reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c], xv[i]);
+        unpack8(reinterpret_cast<const bf16x8*>(g + (size_t)r * H)[c], gv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dw[i][j] += gv[i][j] * xv[i][j] * rstd;
+          gv[i][j] *= wv[i][j];
+          dot += gv[i][j] * xv[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red);
+    const float coef = dot * rstd * rstd * rstd / H;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * rstd - xv[i][j] * coef;
+        if (ADD_RES) {
+          float e[8];
+          unpack8(reinterpret_cast<const bf16x8*>(gres + (size_t)r * H)[c], e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        reinterpret_cast<bf16x8*>(dx + (size_t)r * H)[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      float* dst = dw_partial + (size_t)blockIdx.x * H + c * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+    }
+  }
+}
+
+// out[p, H] = sum over partial rows; converts to bf16.
+__global__ void colsum_to_bf16_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nrows,
+                                      int H) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int r = 0; r < nrows; ++r) s += partial[(size_t)r * H + c];
+  out[c] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------ SwiGLU (* probs)
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ probs,
+                                  __nv_bfloat16* __restrict__ out, long rows, int F) {
+  const int fv = F >> 3;
+  const long total = rows * fv;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long r = i / fv;
+    int c = int(i - r * fv);
+    float g[8], u[8], o[8];
+    const bf16x8* row = reinterpret_cast<const bf16x8*>(gu + r * 2 * F);
+    unpack8(row[c], g);
+    unpack8(row[fv + c], u);
+    const float p = probs ? probs[r] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] * sigmoidf_(g[j]) * u[j] * p;
+    reinterpret_cast<bf16x8*>(out + r * F)[c] = pack8(o);
+  }
+}
+
+// One warp per row: writes d_gate | d_up into the two halves of dgu and the row sum d_probs.
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
+                                  const float* __restrict__ probs, __nv_bfloat16* __restrict__ dgu,
+                                  float* __restrict__ dprobs, long rows, int F) {
+  const int fv = F >> 3;
+  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long r = blockIdx.x * (long)warps + (threadIdx.x >> 5); r < rows; r += (long)gridDim.x * warps) {
+    const bf16x8* grow = reinterpret_cast<const bf16x8*>(gu + r * 2 * F);
+    const bf16x8* drow = reinterpret_cast<const bf16x8*>(dout + r * F);
+    bf16x8* orow = reinterpret_cast<bf16x8*>(dgu + r * 2 * F);
+    const float p = probs ? probs[r] : 1.f;
+    float dp = 0.f;
+    for (int c = lane; c < fv; c += 32) {
+      float g[8], u[8], d[8], dg[8], du[8];
+      unpack8(grow[c], g);
+      unpack8(grow[fv + c], u);
+      unpack8(drow[c], d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float s = sigmoidf_(g[j]);
+        float act = g[j] * s;
+        dp += d[j] * act * u[j];
+        float dpd = d[j] * p;
+        du[j] = dpd * act;
+        dg[j] = dpd * u[j] * s * (1.f + g[j] * (1.f - s));
+      }
+      orow[c] = pack8(dg);
+      orow[fv + c] = pack8(du);
+    }
+    if (dprobs) {
+      dp = warp_sum(dp);
+      if (lane == 0) dprobs[r] = dp;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (half-split), out of place
+// x: [B, S, Hh, D] ; cos/sin: [S, D/2] fp32 ; sign = +1 forward, -1 backward.
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+                            const float* __restrict__ sn, __nv_bfloat16* __restrict__ y, long n_rows, int S, int Hh,
+                            int D, float sign) {
+  const int d2 = D >> 1;
+  const int vec_per_row = d2 >> 3;           // vec8 chunks per half row
+  const long total = n_rows * vec_per_row;   // n_rows = B*S*Hh
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long row = i / vec_per_row;
+    int c = int(i - row * vec_per_row);
+    int s = int((row / Hh) % S);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    float a[8], b[8], co[8], si[8], oa[8], ob[8];
+    unpack8(xr[c], a);
+    unpack8(xr[vec_per_row + c], b);
+    const float4* cp = reinterpret_cast<const float4*>(cs + (size_t)s * d2 + c * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sn + (size_t)s * d2 + c * 8);
+    float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    co[0] = c0.x; co[1] = c0.y; co[2] = c0.z; co[3] = c0.w; co[4] = c1.x; co[5] = c1.y; co[6] = c1.z; co[7] = c1.w;
+    si[0] = s0.x; si[1] = s0.y; si[2] = s0.z; si[3] = s0.w; si[4] = s1.x; si[5] = s1.y; si[6] = s1.z; si[7] = s1.w;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float sj = si[j] * sign;
+      oa[j] = a[j] * co[j] - b[j] * sj;
+      ob[j] = b[j] * co[j] + a[j] * sj;
+    }
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+    yr[c] = pack8(oa);
+    yr[vec_per_row + c] = pack8(ob);
+  }
+}
+
+// ------------------------------------------------------------------ fp8 block quantisation
+// 1x128: one warp per (row, 128-column block): 4 elements per lane.
+__global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ q,
+                                   float* __restrict__ scale, long rows, int H) {
+  const int nb = H >> 7;
+  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long total = rows * nb;
+  for (long w = blockIdx.x * (long)warps + (threadIdx.x >> 5); w < total; w += (long)gridDim.x * warps) {
+    long r = w / nb;
+    int b = int(w - r * nb);
+    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(x + r * H + b * 128 + lane * 4);
+    float2 v0 = __bfloat1622float2(src[0]), v1 = __bfloat1622float2(src[1]);
+    float amax = fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v1.x), fabsf(v1.y)));
+    amax = fmaxf(warp_max(amax), 1e-12f);
+    const float sc = amax / 448.f;
+    const float inv = 448.f / amax;
+    __nv_fp8_e4m3 o[4] = {__nv_fp8_e4m3(v0.x * inv), __nv_fp8_e4m3(v0.y * inv), __nv_fp8_e4m3(v1.x * inv),
+                          __nv_fp8_e4m3(v1.y * inv)};
+    *reinterpret_cast<uint32_t*>(q + r * H + b * 128 + lane * 4) = *reinterpret_cast<uint32_t*>(o);
+    if (lane == 0) scale[r * nb + b] = sc;
+  }
+}
+
+// 128x128: one block (256 threads) per weight block.
+__global__ void __launch_bounds__(256)
+quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale,
+                     int N, int K) {
+  __shared__ float red[32];
+  const int kb = blockIdx.x, nb = blockIdx.y;
+  const long mat = blockIdx.z;
+  const __nv_bfloat16* base = w + mat * (long)N * K + (long)nb * 128 * K + kb * 128;
+  float vals[8][8];
+  float amax = 0.f;
+  // 128 rows x 16 vec8 = 2048 vec8 chunks, 8 per thread
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int idx = threadIdx.x + i * 256;
+    int r = idx >> 4, c = idx & 15;
+    unpack8(*reinterpret_cast<const bf16x8*>(base + (long)r * K + c * 8), vals[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vals[i][j]));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  amax = fmaxf(amax, 1e-12f);
+  const float inv = 448.f / amax;
+  if (threadIdx.x == 0) scale[mat * (long)(N / 128) * (K / 128) + (long)nb * (K / 128) + kb] = amax / 448.f;
+  __nv_fp8_e4m3* qb = q + mat * (long)N * K + (long)nb * 128 * K + kb * 128;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int idx = threadIdx.x + i * 256;
+    int r = idx >> 4, c = idx & 15;
+    __nv_fp8_e4m3 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __nv_fp8_e4m3(vals[i][j] * inv);
+    *reinterpret_cast<uint2*>(qb + (long)r * K + c * 8) = *reinterpret_cast<uint2*>(o);
+  }
+}
+
+// ------------------------------------------------------------------ squared L2 norm (fp32 input)
+__global__ void sumsq_kernel(const float* __restrict__ g, long n, float scale, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long nv = n >> 2;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    float4 v = reinterpret_cast<const float4*>(g)[i];
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long i = nv << 2; i < n; ++i) s += g[i] * g[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s * scale);
+}
+
+// ------------------------------------------------------------------ flat AdamW
+// One thread handles 4 consecutive elements; a 128-element block (one fp8 scale) is one warp.
+// P: master/weight dtype (float or bf16).  State kinds: 0 fp32, 1 bf16, 2 fp8 (e4m3 + per-128 fp32
+// scale; v is stored as sqrt(v)).  `coef` is the clip coefficient on the device (no host sync).
+struct AdamArgs {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;
+};
+
+template <typename P, int KIND>
+__global__ void adamw_kernel(P* __restrict__ p, const float* __restrict__ g, void* __restrict__ m_raw,
+                             void* __restrict__ v_raw, float* __restrict__ m_scale, float* __restrict__ v_scale,
+                             __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ coef, long n,
+                             AdamArgs a) {
+  const float c = coef ? *coef : 1.f;
+  const long nq = n >> 2;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nq; i += (long)gridDim.x * blockDim.x) {
+    const long e0 = i << 2;
+    float gv[4], mv[4], vv[4], pv[4];
+    {
+      float4 t = reinterpret_cast<const float4*>(g)[i];
+      gv[0] = t.x * c; gv[1] = t.y * c; gv[2] = t.z * c; gv[3] = t.w * c;
+    }
+    if (sizeof(P) == 4) {
+      float4 t = reinterpret_cast<const float4*>(p)[i];
+      pv[0] = t.x; pv[1] = t.y; pv[2] = t.z; pv[3] = t.w;
+    } else {
+      const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(p) + 2 * i;
+      float2 t0 = __bfloat1622float2(pp[0]), t1 = __bfloat1622float2(pp[1]);
+      pv[0] = t0.x; pv[1] = t0.y; pv[2] = t1.x; pv[3] = t1.y;
+    }
+    if (KIND == 0) {
+      float4 t = reinterpret_cast<const float4*>(m_raw)[i];
+      mv[0] = t.x; mv[1] = t.y; mv[2] = t.z; mv[3] = t.w;
+      t = reinterpret_cast<const float4*>(v_raw)[i];
+      vv[0] = t.x; vv[1] = t.y; vv[2] = t.z; vv[3] = t.w;
+    } else if (KIND == 1) {
+      const __nv_bfloat162* mp = reinterpret_cast<const __nv_bfloat162*>(m_raw) + 2 * i;
+      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(v_raw) + 2 * i;
+      float2 t0 = __bfloat1622float2(mp[0]), t1 = __bfloat1622float2(mp[1]);
+      mv[0] = t0.x; mv[1] = t0.y; mv[2] = t1.x; mv[3] = t1.y;
+      t0 = __bfloat1622float2(vp[0]); t1 = __bfloat1622float2(vp[1]);
+      vv[0] = t0.x * t0.x; vv[1] = t0.y * t0.y; vv[2] = t1.x * t1.x; vv[3] = t1.y * t1.y;
+    } else {
+      const float ms = m_scale[e0 >> 7], vs = v_scale[e0 >> 7];
+      uint32_t mq = reinterpret_cast<const uint32_t*>(m_raw)[i], vq = reinterpret_cast<const uint32_t*>(v_raw)[i];
+      const __nv_fp8_e4m3* m8 = reinterpret_cast<const __nv_fp8_e4m3*>(&mq);
+      const __nv_fp8_e4m3* v8 = reinterpret_cast<const __nv_fp8_e4m3*>(&vq);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mv[j] = float(m8[j]) * ms;
+        float s = float(v8[j]) * vs;
+        vv[j] = s * s;
+      }
+    }
+    float m_amax = 0.f, v_amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mv[j] = a.beta1 * mv[j] + (1.f - a.beta1) * gv[j];
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gv[j] * gv[j];
+      const float denom = sqrtf(vv[j] / a.bc2) + a.eps;
+      pv[j] = pv[j] * (1.f - a.lr * a.wd) - a.lr * (mv[j] / a.bc1) / denom;
+      if (KIND != 0) vv[j] = sqrtf(vv[j]);        // stored in the sqrt domain
+      m_amax = fmaxf(m_amax, fabsf(mv[j]));
+      v_amax = fmaxf(v_amax, vv[j]);
+    }
+    if (sizeof(P) == 4) {
+      reinterpret_cast<float4*>(p)[i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    } else {
+      __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(p) + 2 * i;
+      pp[0] = __floats2bfloat162_rn(pv[0], pv[1]);
+      pp[1] = __floats2bfloat162_rn(pv[2], pv[3]);
+    }
+    if (out_bf16) {
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(out_bf16) + 2 * i;
+      op[0] = __floats2bfloat162_rn(pv[0], pv[1]);
+      op[1] = __floats2bfloat162_rn(pv[2], pv[3]);
+    }
+    if (KIND == 0) {
+      reinterpret_cast<float4*>(m_raw)[i] = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      reinterpret_cast<float4*>(v_raw)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    } else if (KIND == 1) {
+      __nv_bfloat162* mp = reinterpret_cast<__nv_bfloat162*>(m_raw) + 2 * i;
+      __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(v_raw) + 2 * i;
+      mp[0] = __floats2bfloat162_rn(mv[0], mv[1]);
+      mp[1] = __floats2bfloat162_rn(mv[2], mv[3]);
+      vp[0] = __floats2bfloat162_rn(vv[0], vv[1]);
+      vp[1] = __floats2bfloat162_rn(vv[2], vv[3]);
+    } else {
+      // a warp covers exactly one 128-element scale block (n is a multiple of 128, blockDim of 32)
+      m_amax = fmaxf(warp_max(m_amax), 1e-30f);
+      v_amax = fmaxf(warp_max(v_amax), 1e-30f);
+      const float mi = 448.f / m_amax, vi = 448.f / v_amax;
+      __nv_fp8_e4m3 mo[4], vo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mo[j] = __nv_fp8_e4m3(mv[j] * mi);
+        vo[j] = __nv_fp8_e4m3(vv[j] * vi);
+      }
+      reinterpret_cast<uint32_t*>(m_raw)[i] = *reinterpret_cast<uint32_t*>(mo);
+      reinterpret_cast<uint32_t*>(v_raw)[i] = *reinterpret_cast<uint32_t*>(vo);
+      if ((threadIdx.x & 31) == 0) {
+        m_scale[e0 >> 7] = m_amax / 448.f;
+        v_scale[e0 >> 7] = v_amax / 448.f;
+      }
+    }
+  }
+}
+
+static inline int grid_for(long work_items, int threads, int per_sm = 8) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long blocks = (work_items + threads - 1) / threads;
+  long cap = (long)sms * per_sm;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+}  // namespace slab
+
+using namespace slab;
+
+template <int MAXV>
+static void launch_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xpr, float* rstd,
+                               int rows, int H, float eps, int grid, cudaStream_t st) {
+  if (res)
+    rmsnorm_fwd_kernel<true, MAXV><<<grid, NORM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+        (__nv_bfloat16*)xpr, rstd, rows, H, eps);
+  else
+    rmsnorm_fwd_kernel<false, MAXV><<<grid, NORM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr, rstd, rows, H, eps);
+}
+
+extern "C" int slab_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xpr, float* rstd,
+                                int rows, int H, float eps, cudaStream_t st) {
+  if (H % 8 || H > NORM_THREADS * NORM_MAXV_LIMIT * 8) return -100;
+  int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (grid < 1) return 0;
+  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  if (chunks <= 1) launch_rmsnorm_fwd<1>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
+  else if (chunks <= 2) launch_rmsnorm_fwd<2>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
+  else if (chunks <= 4) launch_rmsnorm_fwd<4>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
+  else launch_rmsnorm_fwd<8>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
+  return (int)cudaGetLastError();
+}
+
+// dw_partial: fp32 [nblocks, H] scratch owned by the caller; nblocks = slab_rmsnorm_bwd_blocks(rows).
+extern "C" int slab_rmsnorm_bwd_blocks(int rows) { return rows < 148 * 2 ? (rows < 1 ? 1 : rows) : 148 * 2; }
+
+template <int MAXV>
+static void launch_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, const void* gres,
+                               void* dx, float* dw_partial, int rows, int H, int grid, cudaStream_t st) {
+  if (gres)
+    rmsnorm_bwd_kernel<true, MAXV><<<grid, NORM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)gres,
+        (__nv_bfloat16*)dx, dw_partial, rows, H);
+  else
+    rmsnorm_bwd_kernel<false, MAXV><<<grid, NORM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, nullptr,
+        (__nv_bfloat16*)dx, dw_partial, rows, H);
+}
+
+extern "C" int slab_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, const void* gres,
+                                void* dx, float* dw_partial, void* dw, int rows, int H, cudaStream_t st) {
+  if (H % 8 || H > NORM_THREADS * NORM_MAXV_LIMIT * 8) return -100;
+  int grid = slab_rmsnorm_bwd_blocks(rows);
+  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  if (chunks <= 1) launch_rmsnorm_bwd<1>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
+  else if (chunks <= 2) launch_rmsnorm_bwd<2>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
+  else if (chunks <= 4) launch_rmsnorm_bwd<4>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
+  else launch_rmsnorm_bwd<8>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
+  colsum_to_bf16_kernel<<<(H + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, grid, H);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_swiglu_fwd(const void* gu, const float* probs, void* out, long rows, int F, cudaStream_t st) {
+  if (F % 8) return -100;
+  if (rows == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, probs,
+                                                                    (__nv_bfloat16*)out, rows, F);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_swiglu_bwd(const void* dout, const void* gu, const float* probs, void* dgu, float* dprobs,
+                               long rows, int F, cudaStream_t st) {
+  if (F % 8) return -100;
+  if (rows == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu,
+                                                               probs, (__nv_bfloat16*)dgu, dprobs, rows, F);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_rope(const void* x, const float* cs, const float* sn, void* y, long n_rows, int S, int Hh, int D,
+                         float sign, cudaStream_t st) {
+  if (D % 16) return -100;
+  if (n_rows == 0) return 0;
+  rope_kernel<<<grid_for(n_rows * (D / 16), 256), 256, 0, st>>>((const __nv_bfloat16*)x, cs, sn, (__nv_bfloat16*)y,
+                                                                 n_rows, S, Hh, D, sign);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_quant_1x128(const void* x, void* q, float* scale, long rows, int H, cudaStream_t st) {
+  if (H % 128) return -100;
+  if (rows == 0) return 0;
+  quant_1x128_kernel<<<grid_for(rows * (H / 128) * 32, 256), 256, 0, st>>>((const __nv_bfloat16*)x,
+                                                                            (__nv_fp8_e4m3*)q, scale, rows, H);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_quant_128x128(const void* w, void* q, float* scale, int mats, int N, int K, cudaStream_t st) {
+  if (N % 128 || K % 128) return -100;
+  dim3 grid(K / 128, N / 128, mats);
+  quant_128x128_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_fp8_e4m3*)q, scale, N, K);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_sumsq(const float* g, long n, float scale, float* out, cudaStream_t st) {
+  if (n == 0) return 0;
+  sumsq_kernel<<<grid_for(n / 4 + 1, 256, 4), 256, 0, st>>>(g, n, scale, out);
+  return (int)cudaGetLastError();
+}
+
+// p_is_bf16: weights updated in place are bf16 (no fp32 master); state_kind: 0 fp32, 1 bf16, 2 fp8.
+// n must be a multiple of 128.
+extern "C" int slab_adamw(void* p, int p_is_bf16, const float* g, void* m, void* v, float* m_scale, float* v_scale,
+                          void* out_bf16, const float* coef, long n, int state_kind, float lr, float beta1,
+                          float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t st) {
+  if (n % 128) return -100;
+  if (n == 0) return 0;
+  AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2};
+  int grid = grid_for(n / 4, 256);
+#define LAUNCH(P, KIND)                                                                                        \
+  adamw_kernel<P, KIND><<<grid, 256, 0, st>>>((P*)p, g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a)
+  if (p_is_bf16) {
+    if (state_kind == 0) LAUNCH(__nv_bfloat16, 0);
+    else if (state_kind == 1) LAUNCH(__nv_bfloat16, 1);
+    else LAUNCH(__nv_bfloat16, 2);
+  } else {
+    if (state_kind == 0) LAUNCH(float, 0);
+    else if (state_kind == 1) LAUNCH(float, 1);
+    else LAUNCH(float, 2);
+  }
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}

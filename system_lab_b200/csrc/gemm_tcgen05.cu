@@ -1,0 +1,379 @@
+// Dropless grouped expert GEMM for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by
+// TMA (no cluster multicast), persistent warp-specialised CTAs.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane, also
+// owns the TMEM allocation), warps 2..5 = epilogue (each drains its 32 TMEM lanes to global memory).
+// Two TMEM accumulators (2 x BN fp32 columns) let the epilogue of tile i overlap the main loop of
+// tile i+1.  All waits are bounded (see common.cuh).
+//
+// Three modes share one kernel; rows are grouped by expert, every segment starts at a multiple of 128
+// rows and padding rows are zero (the dispatch kernels guarantee both):
+//   FWD    C[r, n]   = sum_k A[r, k]  * B[e, n, k]      A: acts  [R, K]   B: weights [E, N, K]
+//   DGRAD  C[r, k]   = sum_n A[r, n]  * B[e, n, k]      A: dY    [R, N]   B: weights [E, N, K] (MN-major operand)
+//   WGRAD  C[e, n, k]= sum_r A[r, n]  * B[r, k]         A: dY    [R, N]   B: acts    [R, K]   (both MN-major,
+//                                                       reduction length = rows of expert e)
+// Reference analogue: the hand written MFMA grouped GEMM (128x128x32 tiles, double buffered LDS,
+// notes/2026-04/2026-04-10-mfma-gemm-optimization.md:35-109) and the variable-K wgrad kernel of
+// notes/2026-04/2026-04-21_gptoss_10_moe_fp8_grouped_gemm_diagnosis.md:64-85.
+#include "common.cuh"
+
+namespace slab {
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum { MODE_FWD = 0, MODE_DGRAD = 1, MODE_WGRAD = 2 };
+
+struct GemmParams {
+  const int* seg_offsets;   // [E] first row of each expert segment (multiple of 128)
+  const int* seg_counts;    // [E] valid rows
+  int E;
+  int R;                    // rows of the row-grouped operands
+  int N;                    // weights' N
+  int K;                    // weights' K
+  __nv_bfloat16* C;
+  int accumulate;           // WGRAD: add into C instead of overwriting
+  int* status;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 1024 + 4 * 520;   // barriers + tile prefix table
+};
+
+// Tile walk: experts in order; inside an expert the M index runs fastest so CTAs that run at the same
+// time share the expert's weight tile in L2.
+struct TileInfo {
+  int e, m_idx, n_idx, row0, ksteps;
+};
+
+template <int MODE, int BN>
+__device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmParams& p, int n_tiles, TileInfo& ti) {
+  int E = p.E;
+  if (t >= prefix[E]) return false;
+  int lo = 0, hi = E;            // largest e with prefix[e] <= t
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= t) lo = mid; else hi = mid;
+  }
+  int e = lo;
+  int local = t - prefix[e];
+  ti.e = e;
+  if (MODE == MODE_WGRAD) {
+    int m_tiles = p.N / BM;                   // output rows = weights' N
+    ti.m_idx = local % m_tiles;
+    ti.n_idx = local / m_tiles;
+    ti.row0 = p.seg_offsets[e];
+    ti.ksteps = (p.seg_counts[e] + BK - 1) / BK;
+  } else {
+    int m_tiles = (p.seg_counts[e] + BM - 1) / BM;
+    ti.m_idx = local % m_tiles;
+    ti.n_idx = local / m_tiles;
+    ti.row0 = p.seg_offsets[e] + ti.m_idx * BM;
+    ti.ksteps = ((MODE == MODE_FWD) ? p.K : p.N) / BK;
+  }
+  return true;
+}
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int STAGES = L::STAGES;
+  constexpr bool A_MN = (MODE == MODE_WGRAD);
+  constexpr bool B_MN = (MODE != MODE_FWD);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* prefix = reinterpret_cast<int*>(smem + L::BAR_OFFSET + 1024);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // output tiles per expert along the non-grouped axis
+  const int out_cols = (MODE == MODE_FWD) ? p.N : p.K;
+  const int n_tiles = (out_cols + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      prefix[e] = acc;
+      int per = (MODE == MODE_WGRAD) ? (p.N / BM) : ((p.seg_counts[e] + BM - 1) / BM);
+      acc += per * n_tiles;
+    }
+    prefix[p.E] = acc;
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      TileInfo ti;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
+        for (int ks = 0; ks < ti.ksteps; ++ks) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          if (MODE == MODE_FWD) {
+            tma_load_2d(a_dst, &tmap_a, &full_bar[s], ks * BK, ti.row0);
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], ks * BK, ti.e * p.N + ti.n_idx * BN);
+          } else if (MODE == MODE_DGRAD) {
+            tma_load_2d(a_dst, &tmap_a, &full_bar[s], ks * BK, ti.row0);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tmap_b, &full_bar[s], ti.n_idx * BN + j * 64, ti.e * p.N + ks * BK);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, &tmap_a, &full_bar[s], ti.m_idx * BM + j * 64, ti.row0 + ks * BK);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tmap_b, &full_bar[s], ti.n_idx * BN + j * 64, ti.row0 + ks * BK);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      TileInfo ti;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
+        if (ti.ksteps == 0) continue;
+        const int buf = it & 1;
+        if (!mbar_wait(&tempty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int ks = 0; ks < ti.ksteps; ++ks) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+            // K-major: 32 bytes per UMMA_K inside the 128-byte swizzle row; MN-major: 16 k-rows of 128 bytes
+            const uint64_t adesc = A_MN ? make_smem_desc(a_addr + k4 * 2048, 8192, 1024, 2)
+                                        : make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + k4 * 2048, 8192, 1024, 2)
+                                        : make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (ks | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);          // frees the stage when these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[buf]);           // accumulator complete
+        ++it;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int lg = warp & 3;                    // TMEM lane group this warp may read
+    int it = 0;
+    TileInfo ti;
+    for (int t = blockIdx.x; get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
+      const int r_in_tile = lg * 32 + lane;
+      __nv_bfloat16* c_row;
+      bool row_ok;
+      int col0 = ti.n_idx * BN;
+      int ldc;
+      if (MODE == MODE_WGRAD) {
+        ldc = p.K;
+        int n = ti.m_idx * BM + r_in_tile;
+        row_ok = n < p.N;
+        c_row = p.C + ((size_t)ti.e * p.N + n) * ldc;
+      } else {
+        ldc = out_cols;
+        int r = ti.row0 + r_in_tile;
+        row_ok = r < p.R;
+        c_row = p.C + (size_t)r * ldc;
+      }
+      if (ti.ksteps == 0) {                     // empty expert (WGRAD): gradient is zero
+        if (row_ok && !p.accumulate) {
+          for (int c = 0; c < BN; c += 8)
+            if (col0 + c < out_cols) *reinterpret_cast<uint4*>(c_row + col0 + c) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int buf = it & 1;
+      if (!mbar_wait(&tfull_bar[buf], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            int col = col0 + c + g * 8;
+            if (col < out_cols) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]);
+              bf16x8* dst = reinterpret_cast<bf16x8*>(c_row + col);
+              if (MODE == MODE_WGRAD && p.accumulate) {
+                float o[8];
+                unpack8(*dst, o);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] += o[i];
+              }
+              *dst = pack8(f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      ++it;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is handed on
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols]; box = [box_rows, box_cols]; 128-byte swizzle.
+static int make_map_bf16(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         uint32_t box_cols) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int MODE, int BN>
+static int launch(const void* A, const void* B, const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  CUtensorMap ma, mb;
+  int rc;
+  if (MODE == MODE_FWD) {
+    if ((rc = make_map_bf16(&ma, A, p.R, p.K, BM, BK))) return rc;
+    if ((rc = make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BN, BK))) return rc;
+  } else if (MODE == MODE_DGRAD) {
+    if ((rc = make_map_bf16(&ma, A, p.R, p.N, BM, BK))) return rc;
+    if ((rc = make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BK, 64))) return rc;
+  } else {
+    if ((rc = make_map_bf16(&ma, A, p.R, p.N, BK, 64))) return rc;
+    if ((rc = make_map_bf16(&mb, B, p.R, p.K, BK, 64))) return rc;
+  }
+  static bool attr_set = false;
+  auto kern = grouped_gemm_kernel<MODE, BN>;
+  if (!attr_set) {
+    SLAB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL + 1024));
+    attr_set = true;
+  }
+  kern<<<grid, GEMM_THREADS, L::TOTAL + 1024, stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace slab
+
+// mode: 0 fwd, 1 dgrad, 2 wgrad.  Shapes: see the header comment.  Requires K % 64 == 0, N % 64 == 0
+// (N % 128 == 0 for wgrad), at most 512 experts.  `status` is a device int the kernel sets on a
+// bounded-wait timeout (0 = ok).  Returns a CUDA/driver error code (0 = launched).
+extern "C" int slab_grouped_gemm_bf16(int mode, const void* A, const void* B, void* C, const int* seg_offsets,
+                                      const int* seg_counts, int E, int R, int N, int K, int accumulate,
+                                      int block_n, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace slab;
+  if (E > 512 || K % 64 || N % 64 || (mode == MODE_WGRAD && N % 128)) return -100;
+  GemmParams p{seg_offsets, seg_counts, E, R, N, K, static_cast<__nv_bfloat16*>(C), accumulate, status};
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  const bool wide = block_n != 128;
+  switch (mode) {
+    case MODE_FWD:
+      return wide ? launch<MODE_FWD, 256>(A, B, p, grid, stream) : launch<MODE_FWD, 128>(A, B, p, grid, stream);
+    case MODE_DGRAD:
+      return wide ? launch<MODE_DGRAD, 256>(A, B, p, grid, stream) : launch<MODE_DGRAD, 128>(A, B, p, grid, stream);
+    case MODE_WGRAD:
+      return wide ? launch<MODE_WGRAD, 256>(A, B, p, grid, stream) : launch<MODE_WGRAD, 128>(A, B, p, grid, stream);
+  }
+  return -101;
+}

@@ -177,7 +177,10 @@ class MoEFFN(nn.Module):
                                          self.router_bias, cfg.moe_norm_topk_prob,
                                          cfg.moe_router_topk_scaling_factor)
         if cfg.moe_router_load_balancing_type == "aux_loss" and cfg.moe_aux_loss_coeff > 0 and self.training:
-            self.aux = ref.aux_loss(scores, idx, cfg.num_experts, cfg.moe_aux_loss_coeff)
+            if scores is None:          # the fused router kernel returns only the selection and its weights
+                scores = torch.softmax(logits, -1) if cfg.moe_router_score_function == "softmax" \
+                    else torch.sigmoid(logits)
+            self.aux = ref.aux_loss(scores, idx.long(), cfg.num_experts, cfg.moe_aux_loss_coeff)
         d = self.dispatcher
         plan = d.plan(idx)
         self.last_tokens_per_expert = plan.tokens_per_expert_global

@@ -1,0 +1,49 @@
+"""Causal attention on the GPU.
+
+Order of preference: the hand written kernel (``csrc/attention.cu``) when it is built and the shape is
+one it covers; otherwise the library flash attention (the measured baseline: cuDNN / flash-attn,
+64.3 ms per step in the reference's B200 trace, ``docs/b200-vs-mi355x-ep8-gbs16-trace.html:433``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+_IMPL = "auto"          # auto | library
+
+
+def set_attention_impl(name: str) -> None:
+    global _IMPL
+    _IMPL = name
+
+
+def _library(q, k, v, scale, window):
+    d, dv = q.shape[-1], v.shape[-1]
+    if d == dv and d <= 256 and q.dtype in (torch.bfloat16, torch.float16):
+        try:
+            from flash_attn import flash_attn_func
+            win = (window - 1, 0) if window > 0 else (-1, -1)
+            return flash_attn_func(q, k, v, softmax_scale=scale, causal=True, window_size=win)
+        except ImportError:
+            pass
+    b, s, hq, _ = q.shape
+    hkv = k.shape[2]
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if window > 0:
+        i = torch.arange(s, device=q.device)
+        mask = (i[None, :] <= i[:, None]) & (i[None, :] > i[:, None] - window)
+        o = F.scaled_dot_product_attention(qt, kt, vt, attn_mask=mask, scale=scale, enable_gqa=hq != hkv)
+    else:
+        o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, scale=scale, enable_gqa=hq != hkv)
+    return o.transpose(1, 2)
+
+
+def causal_attention(q, k, v, scale=None, window: int = 0):
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if _IMPL == "auto":
+        from . import attention_kernel
+        if attention_kernel.supports(q, k, v, window):
+            return attention_kernel.attention(q, k, v, scale, window)
+    return _library(q, k, v, scale, window)

@@ -1,0 +1,443 @@
+"""Kernel path of the op surface: ctypes bindings to ``lib/libslab_kernels.so`` wrapped in autograd
+Functions.  bf16 activations only; a call with another dtype goes to the oracle explicitly (fp32
+models are a CPU/plumbing configuration).  Missing library on a GPU machine is an error, never a
+silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libslab_kernels.so"
+_lib = None
+
+# p: pointer, i: int32, l: int64, f: float, s: stream
+_SIGS = {
+    "slab_rmsnorm_fwd": "ppppppiifs",
+    "slab_rmsnorm_bwd_blocks": "i",
+    "slab_rmsnorm_bwd": "ppppppppiis",
+    "slab_swiglu_fwd": "ppplis",
+    "slab_swiglu_bwd": "ppppplis",
+    "slab_rope": "ppppliiifs",
+    "slab_quant_1x128": "ppplis",
+    "slab_quant_128x128": "pppiiis",
+    "slab_sumsq": "plfps",
+    "slab_adamw": "pi" + "p" * 7 + "li" + "f" * 7 + "s",
+    "slab_router_topk": "ppppiiiiifs",
+    "slab_ce_fwd_bwd": "pppiifs",
+    "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
+}
+_CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_long, "f": ctypes.c_float, "s": ctypes.c_void_p}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise KernelError(f"{_LIB_PATH} is missing: run `python -m system_lab_b200.csrc.build` "
+                              "(or __graft_entry__.build()) before using the CUDA ops")
+        _lib = ctypes.CDLL(str(_LIB_PATH))
+        for name, sig in _SIGS.items():
+            fn = getattr(_lib, name, None)
+            if fn is None:
+                continue
+            fn.argtypes = [_CT[c] for c in sig]
+            fn.restype = ctypes.c_int
+    return _lib
+
+
+def register(name: str, sig: str) -> None:
+    """Used by other modules (dispatch, attention) to declare their entry points."""
+    _SIGS[name] = sig
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = [_CT[c] for c in sig]
+        fn.restype = ctypes.c_int
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        return t.data_ptr()
+    return t
+
+
+# kernels launched per entry point (entry points not listed launch one); LAUNCHES[0] counts launches
+_KERNELS_PER_CALL = {"slab_rmsnorm_bwd": 2}
+LAUNCHES = [0]
+
+
+def call(name: str, *args) -> int:
+    fn = getattr(lib(), name)
+    LAUNCHES[0] += _KERNELS_PER_CALL.get(name, 1)
+    rc = fn(*[_ptr(a) for a in args])
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+    return rc
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_STATUS = {}
+_STATUS_NAMES = {1: "TIMEOUT_FULL", 2: "TIMEOUT_EMPTY", 3: "TIMEOUT_TMEM_FULL", 4: "TIMEOUT_TMEM_EMPTY",
+                 5: "TIMEOUT_PEER_FLAG", 6: "BAD_INDEX", 7: "CAPACITY"}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the kernels write on a bounded-wait timeout or a failed bounds check."""
+    key = str(device)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+class DeviceHang(RuntimeError):
+    """A kernel's bounded wait ran out (failure kind HANG): the kernel returned, the context is usable."""
+
+
+def check_status(device=None) -> None:
+    """Host read of the status word; raises a typed error.  Call between steps, not per kernel."""
+    for key, t in _STATUS.items():
+        if device is not None and key != str(device):
+            continue
+        v = int(t.item())
+        if v:
+            t.zero_()
+            raise DeviceHang(f"device kernel reported {_STATUS_NAMES.get(v, v)} on {key}")
+
+
+def _bf16(*ts) -> bool:
+    return all(t is None or t.dtype == torch.bfloat16 for t in ts)
+
+
+# ------------------------------------------------------------------------------ RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).contiguous()
+        rows, h = x2.shape
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        call("slab_rmsnorm_fwd", x2, None, w, y, None, rstd, rows, h, float(eps), stream())
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.shp = shp
+        return y.reshape(shp)
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, w, rstd = ctx.saved_tensors
+        rows, h = x2.shape
+        g2 = g.reshape(rows, h).contiguous()
+        nb = lib().slab_rmsnorm_bwd_blocks(rows)
+        part = torch.empty(nb, h, dtype=torch.float32, device=g.device)
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(w)
+        call("slab_rmsnorm_bwd", g2, x2, w, rstd, None, dx, part, dw, rows, h, stream())
+        return dx.reshape(ctx.shp), dw, None
+
+
+class _RMSNormResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).contiguous()
+        r2 = res.reshape(-1, shp[-1]).contiguous()
+        rows, h = x2.shape
+        y = torch.empty_like(x2)
+        xpr = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        call("slab_rmsnorm_fwd", x2, r2, w, y, xpr, rstd, rows, h, float(eps), stream())
+        ctx.save_for_backward(xpr, w, rstd)
+        ctx.shp = shp
+        return y.reshape(shp), xpr.reshape(shp)
+
+    @staticmethod
+    def backward(ctx, gy, gxpr):
+        xpr, w, rstd = ctx.saved_tensors
+        rows, h = xpr.shape
+        gy2 = gy.reshape(rows, h).contiguous()
+        gx2 = gxpr.reshape(rows, h).contiguous() if gxpr is not None else None
+        nb = lib().slab_rmsnorm_bwd_blocks(rows)
+        part = torch.empty(nb, h, dtype=torch.float32, device=gy.device)
+        dx = torch.empty_like(xpr)
+        dw = torch.empty_like(w)
+        call("slab_rmsnorm_bwd", gy2, xpr, w, rstd, gx2, dx, part, dw, rows, h, stream())
+        dx = dx.reshape(ctx.shp)
+        return dx, dx, dw, None          # the same tensor is the gradient of x and of the residual
+
+
+def rmsnorm(x, w, eps):
+    if not _bf16(x, w):
+        return ref.rmsnorm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+def rmsnorm_residual(x, res, w, eps):
+    if not _bf16(x, res, w):
+        return ref.rmsnorm_residual(x, res, w, eps)
+    return _RMSNormResidual.apply(x, res, w, eps)
+
+
+# ------------------------------------------------------------------------------ RoPE
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        b, s, hh, d = x.shape
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        ctx.save_for_backward(cos, sin)
+        call("slab_rope", xc, cos, sin, y, b * s * hh, s, hh, d, 1.0, stream())
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        b, s, hh, d = g.shape
+        gc = g.contiguous()
+        out = torch.empty_like(gc)
+        call("slab_rope", gc, cos, sin, out, b * s * hh, s, hh, d, -1.0, stream())
+        return out, None, None
+
+
+def rope(x, cos, sin):
+    if not _bf16(x) or x.shape[-1] % 16:
+        return ref.rope(x, cos, sin)
+    return _Rope.apply(x, cos.contiguous(), sin.contiguous())
+
+
+# ------------------------------------------------------------------------------ SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu, probs):
+        shp = gu.shape
+        g2 = gu.reshape(-1, shp[-1]).contiguous()
+        rows, f2 = g2.shape
+        out = torch.empty(rows, f2 // 2, dtype=gu.dtype, device=gu.device)
+        call("slab_swiglu_fwd", g2, probs, out, rows, f2 // 2, stream())
+        ctx.save_for_backward(g2, probs)
+        ctx.shp = shp
+        return out.reshape(*shp[:-1], f2 // 2)
+
+    @staticmethod
+    def backward(ctx, g):
+        g2, probs = ctx.saved_tensors
+        rows, f2 = g2.shape
+        gc = g.reshape(rows, f2 // 2).contiguous()
+        dgu = torch.empty_like(g2)
+        dp = torch.empty(rows, dtype=torch.float32, device=g.device) if probs is not None else None
+        call("slab_swiglu_bwd", gc, g2, probs, dgu, dp, rows, f2 // 2, stream())
+        return dgu.reshape(ctx.shp), dp
+
+
+def swiglu(gate_up):
+    if not _bf16(gate_up) or gate_up.shape[-1] % 16:
+        return ref.swiglu(gate_up)
+    return _SwiGLU.apply(gate_up, None)
+
+
+def swiglu_probs(gate_up, probs):
+    if not _bf16(gate_up) or gate_up.shape[-1] % 16:
+        return ref.swiglu_probs(gate_up, probs)
+    return _SwiGLU.apply(gate_up, probs.float().contiguous())
+
+
+# ------------------------------------------------------------------------------ router
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, topk, score_function, bias, norm, scaling):
+        t, e = logits.shape
+        lc = logits.contiguous()
+        w = torch.empty(t, topk, dtype=torch.float32, device=logits.device)
+        idx = torch.empty(t, topk, dtype=torch.int32, device=logits.device)
+        call("slab_router_topk", lc, bias, w, idx, t, e, topk, 0 if score_function == "softmax" else 1,
+             1 if norm else 0, float(scaling), stream())
+        ctx.save_for_backward(lc, idx)
+        ctx.cfg = (score_function, norm, scaling)
+        ctx.mark_non_differentiable(idx)
+        return w, idx
+
+    @staticmethod
+    def backward(ctx, gw, _gidx):
+        logits, idx = ctx.saved_tensors
+        score_function, norm, scaling = ctx.cfg
+        with torch.enable_grad():
+            lg = logits.detach().requires_grad_(True)
+            scores = torch.softmax(lg, -1) if score_function == "softmax" else torch.sigmoid(lg)
+            w = torch.gather(scores, 1, idx.long())
+            if norm:
+                w = w / (w.sum(-1, keepdim=True) + 1e-20)
+            w = w * scaling
+            (gl,) = torch.autograd.grad(w, lg, gw)
+        return gl, None, None, None, None, None
+
+
+def router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor):
+    lf = logits.float()
+    w, idx = _RouterTopK.apply(lf, topk, score_function, bias.float().contiguous() if bias is not None else None,
+                               norm_topk_prob, scaling_factor)
+    return w, idx, None
+
+
+# ------------------------------------------------------------------------------ grouped GEMM
+def _check_segments(offsets, counts):
+    if offsets.dtype != torch.int32:
+        offsets = offsets.to(torch.int32)
+    if counts.dtype != torch.int32:
+        counts = counts.to(torch.int32)
+    return offsets.contiguous(), counts.contiguous()
+
+
+def grouped_gemm_raw(mode: int, a, b, offsets, counts, n: int, k: int, out=None, accumulate=False,
+                     block_n: int = 256, max_ctas: int = 0):
+    """mode 0: out[R,N] = a[R,K] @ b[e]^T ; 1: out[R,K] = a[R,N] @ b[e] ; 2: out[E,N,K] = a[R,N]^T @ b[R,K]."""
+    e = offsets.numel()
+    r = a.shape[0]
+    if out is None:
+        if mode == 0:
+            out = torch.empty(r, n, dtype=torch.bfloat16, device=a.device)
+        elif mode == 1:
+            out = torch.empty(r, k, dtype=torch.bfloat16, device=a.device)
+        else:
+            out = torch.empty(e, n, k, dtype=torch.bfloat16, device=a.device)
+    call("slab_grouped_gemm_bf16", mode, a, b, out, offsets, counts, e, r, n, k, 1 if accumulate else 0,
+         block_n, max_ctas, status_word(a.device), stream())
+    return out
+
+
+def _pick_bn(cols: int) -> int:
+    return 256 if cols % 256 == 0 or cols > 1024 else 128
+
+
+class _GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, w, offsets, counts):
+        e, n, k = w.shape
+        a = a.contiguous()
+        w = w.contiguous()
+        out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, block_n=_pick_bn(n))
+        ctx.save_for_backward(a, w, offsets, counts)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        a, w, offsets, counts = ctx.saved_tensors
+        e, n, k = w.shape
+        g = g.contiguous()
+        da = dw = None
+        if ctx.needs_input_grad[0]:
+            da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, block_n=_pick_bn(k))
+        if ctx.needs_input_grad[1]:
+            dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
+        return da, dw, None, None
+
+
+def grouped_linear(a, w, offsets, counts, fp8: bool = False):
+    e, n, k = w.shape
+    if not _bf16(a, w) or k % 64 or n % 128:
+        from . import _GroupedLinearRef
+        return _GroupedLinearRef.apply(a, w, offsets, counts)
+    offsets, counts = _check_segments(offsets, counts)
+    return _GroupedLinear.apply(a, w, offsets, counts)
+
+
+# ------------------------------------------------------------------------------ attention
+def causal_attention(q, k, v, scale, window):
+    from .attention import causal_attention as impl
+    return impl(q, k, v, scale, window)
+
+
+# ------------------------------------------------------------------------------ linear + cross entropy
+class _LinearCE(torch.autograd.Function):
+    """loss = mean CE(h @ W^T, targets), chunked over rows: logits of one chunk are produced by a
+    library GEMM, turned into their own gradient in place by one kernel, and consumed by the two
+    gradient GEMMs before the next chunk; the full [tokens, vocab] matrix never exists."""
+
+    @staticmethod
+    def forward(ctx, h, weight, targets, chunk_rows):
+        n, hd = h.shape
+        v = weight.shape[0]
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=h.device)
+        dh = torch.empty_like(h)
+        dw = torch.zeros_like(weight)
+        gscale = 1.0 / n
+        for lo in range(0, n, chunk_rows):
+            hi = min(lo + chunk_rows, n)
+            logits = h[lo:hi] @ weight.t()
+            call("slab_ce_fwd_bwd", logits, targets[lo:hi].contiguous(), loss_sum, hi - lo, v, gscale, stream())
+            torch.mm(logits, weight, out=dh[lo:hi])
+            dw.addmm_(logits.t(), h[lo:hi])
+        ctx.save_for_backward(dh, dw)
+        return (loss_sum / n).squeeze(0)
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        return dh * g.to(dh.dtype), dw * g.to(dw.dtype), None, None
+
+
+def linear_cross_entropy(h, weight, targets, chunk_rows: int = 4096):
+    if not _bf16(h, weight) or weight.shape[0] % 8:
+        return ref.linear_cross_entropy(h, weight, targets)
+    return _LinearCE.apply(h.contiguous(), weight.contiguous(), targets.contiguous(), chunk_rows)
+
+
+# ------------------------------------------------------------------------------ quantisation
+def quant_1x128(x):
+    if not _bf16(x):
+        return ref.quant_1x128(x)
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1]).contiguous()
+    q = torch.empty(x2.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(x2.shape[0], shp[-1] // 128, dtype=torch.float32, device=x.device)
+    call("slab_quant_1x128", x2, q, s, x2.shape[0], shp[-1], stream())
+    return q.reshape(shp), s.reshape(*shp[:-1], shp[-1] // 128)
+
+
+def quant_128x128(w):
+    if not _bf16(w):
+        return ref.quant_128x128(w)
+    *lead, n, k = w.shape
+    mats = 1
+    for d in lead:
+        mats *= d
+    wc = w.contiguous()
+    q = torch.empty(wc.shape, dtype=torch.float8_e4m3fn, device=w.device)
+    s = torch.empty(*lead, n // 128, k // 128, dtype=torch.float32, device=w.device)
+    call("slab_quant_128x128", wc, q, s, mats, n, k, stream())
+    return q, s
+
+
+# ------------------------------------------------------------------------------ optimizer
+def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    call("slab_sumsq", g, g.numel(), float(scale), out, stream())
+
+
+_KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
+
+
+def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step) -> None:
+    """Fused AdamW on one flat shard: reads the fp32 gradient shard, updates moments (any storage
+    format) and the master/weight shard, and writes the bf16 compute copy in the same pass."""
+    p = group.shard
+    n = p.numel()
+    out_bf16 = None
+    if not group.sharded and group.shard is not group.full:
+        out_bf16 = group.full.data           # unsharded with fp32 masters: refresh the compute copy in-kernel
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, group.grad_shard, m.data, v.data,
+         getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, n, _KIND[m.kind],
+         float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2), stream())

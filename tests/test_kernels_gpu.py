@@ -1,0 +1,183 @@
+"""CUDA kernels vs the plain PyTorch fp32 oracle of the same op (forward and backward)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cops():
+    from system_lab_b200.ops import cuda
+    cuda.lib()
+    return cuda
+
+
+def _close(a, b, rtol, atol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4e} (tol rtol={rtol} atol={atol})"
+
+
+@pytest.mark.parametrize("rows,h", [(37, 256), (512, 2048), (64, 2880), (33, 7168)])
+def test_rmsnorm_fwd_bwd(cops, rows, h):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16)
+    y = cops.rmsnorm(x, w, 1e-6)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = ref.rmsnorm(xf, wf, 1e-6)
+    yr.backward(g.float())
+    _close(y, yr, 1e-2, 1e-2)
+    _close(x.grad, xf.grad, 2e-2, 2e-2)
+    _close(w.grad, wf.grad, 2e-2, 0.05 * rows ** 0.5)
+
+
+@pytest.mark.parametrize("rows,h", [(129, 2048), (40, 2880)])
+def test_rmsnorm_residual_fwd_bwd(cops, rows, h):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(1)
+    x = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    gy = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16)
+    gx = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16)
+    y, xpr = cops.rmsnorm_residual(x, r, w, 1e-6)
+    torch.autograd.backward([y, xpr], [gy, gx])
+    xf, rf, wf = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    yr, xr = ref.rmsnorm_residual(xf, rf, wf, 1e-6)
+    torch.autograd.backward([yr, xr], [gy.float(), gx.float()])
+    _close(y, yr, 1e-2, 1e-2)
+    _close(xpr, xr, 1e-2, 1e-2)
+    _close(x.grad, xf.grad, 2e-2, 3e-2)
+    _close(r.grad, rf.grad, 2e-2, 3e-2)
+    _close(w.grad, wf.grad, 2e-2, 0.05 * rows ** 0.5)
+
+
+@pytest.mark.parametrize("rows,f,with_probs", [(100, 768, True), (257, 2048, True), (64, 512, False)])
+def test_swiglu_fwd_bwd(cops, rows, f, with_probs):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(2)
+    gu = torch.randn(rows, 2 * f, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    p = torch.rand(rows, device="cuda", requires_grad=True) if with_probs else None
+    g = torch.randn(rows, f, device="cuda", dtype=torch.bfloat16)
+    out = cops.swiglu_probs(gu, p) if with_probs else cops.swiglu(gu)
+    out.backward(g)
+    guf = gu.detach().float().requires_grad_(True)
+    pf = p.detach().clone().requires_grad_(True) if with_probs else None
+    outr = ref.swiglu_probs(guf, pf) if with_probs else ref.swiglu(guf)
+    outr.backward(g.float())
+    _close(out, outr, 1e-2, 1e-2)
+    _close(gu.grad, guf.grad, 2e-2, 2e-2)
+    if with_probs:
+        _close(p.grad, pf.grad, 2e-2, 0.05 * f ** 0.5)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_rope_fwd_bwd(cops, d):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(3)
+    b, s, hh = 2, 96, 5
+    x = torch.randn(b, s, hh, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = ref.rope_tables(s, d, 1e6, "cuda")
+    g = torch.randn_like(x)
+    y = cops.rope(x, cos, sin)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_(True)
+    yr = ref.rope(xf, cos, sin)
+    yr.backward(g.float())
+    _close(y, yr, 1e-2, 1e-2)
+    _close(x.grad, xf.grad, 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("score,e,k,bias", [("softmax", 128, 8, False), ("sigmoid", 256, 8, True), ("softmax", 8, 2, False)])
+def test_router_topk(cops, score, e, k, bias):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(4)
+    t = 333
+    logits = torch.randn(t, e, device="cuda", requires_grad=True)
+    b = 0.1 * torch.randn(e, device="cuda") if bias else None
+    w, idx, _ = cops.router_topk(logits, k, score, b, True, 2.5)
+    gw = torch.randn_like(w)
+    w.backward(gw)
+    lr = logits.detach().clone().requires_grad_(True)
+    wr, idxr, _ = ref.router_topk(lr, k, score, b, True, 2.5)
+    wr.backward(gw)
+    assert torch.equal(idx.long().sort(-1).values, idxr.sort(-1).values)
+    order, order_r = idx.long().argsort(-1), idxr.argsort(-1)
+    _close(torch.gather(w, 1, order), torch.gather(wr, 1, order_r), 1e-4, 1e-5)
+    _close(logits.grad, lr.grad, 1e-3, 1e-5)
+
+
+def test_quant_roundtrip(cops):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(5)
+    x = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16) * 3
+    q, s = cops.quant_1x128(x)
+    qr, sr = ref.quant_1x128(x)
+    _close(s, sr, 1e-6, 0)
+    _close(ref.dequant_1x128(q, s), ref.dequant_1x128(qr, sr), 0.07, 1e-6)
+    _close(ref.dequant_1x128(q, s), x, 0.07, 1e-3)
+    w = torch.randn(3, 256, 384, device="cuda", dtype=torch.bfloat16) * 0.02
+    qw, sw = cops.quant_128x128(w)
+    qwr, swr = ref.quant_128x128(w)
+    _close(sw, swr, 1e-6, 0)
+    _close(ref.dequant_128x128(qw, sw), w, 0.07, 1e-5)
+
+
+def test_ce_matches_reference(cops):
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(6)
+    n, hd, v = 700, 256, 1024
+    h = torch.randn(n, hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(v, hd, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    tgt = torch.randint(0, v, (n,), device="cuda")
+    loss = cops.linear_cross_entropy(h, w, tgt, chunk_rows=256)
+    (loss * 3.0).backward()
+    hf, wf = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lr = ref.linear_cross_entropy(hf, wf, tgt)
+    (lr * 3.0).backward()
+    assert abs(loss.item() - lr.item()) < 2e-2
+    _close(h.grad, hf.grad, 5e-2, 2e-4)
+    _close(w.grad, wf.grad, 5e-2, 2e-4)
+
+
+@pytest.mark.parametrize("kind", ["fp32", "bf16", "fp8"])
+@pytest.mark.parametrize("p_dtype", [torch.float32, torch.bfloat16])
+def test_adamw_flat(cops, kind, p_dtype):
+    from system_lab_b200.ops import reference as ref
+    from system_lab_b200.trainer.optim import _Moment
+    torch.manual_seed(7)
+    n = 128 * 37
+
+    class G:
+        pass
+    g = G()
+    g.shard = (0.02 * torch.randn(n, device="cuda")).to(p_dtype)
+    g.full = g.shard
+    g.sharded = True
+    p_ref = g.shard.float().clone()
+    m_ref, v_ref = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    m, v = _Moment(n, kind, "cuda"), _Moment(n, kind, "cuda", sqrt_domain=(kind != "fp32"))
+    coef = torch.tensor(0.5, device="cuda")
+    for step in range(1, 4):
+        grad = torch.randn(n, device="cuda") * 1e-2
+        g.grad_shard = grad.clone()
+        cops.adamw_flat(g, m, v, coef, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        ref.adamw_step(p_ref, grad * 0.5, m_ref, v_ref, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                       weight_decay=0.1, step=step)
+    tol = {"fp32": 1e-5, "bf16": 3e-2, "fp8": 0.3}[kind]
+    if p_dtype == torch.bfloat16:
+        tol = max(tol, 2e-2)
+    # compare the *update* (p - p0 is O(lr)); relative tolerance on the parameter itself
+    _close(g.shard, p_ref, tol, 1e-2 * tol + (1e-3 if p_dtype == torch.bfloat16 else 0))
+
+
+def test_sumsq(cops):
+    x = torch.randn(1_000_003, device="cuda")
+    out = torch.zeros(1, device="cuda")
+    cops.sumsq(x, 0.5, out)
+    assert abs(out.item() - 0.5 * x.double().pow(2).sum().item()) / out.item() < 1e-4
