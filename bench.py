@@ -37,6 +37,7 @@ def parse():
     ap.add_argument("--seqs-per-gpu", type=int, default=2)
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
+    ap.add_argument("--trace", default="", help="after timing, profile one more step into this Kineto trace")
     ap.add_argument("overrides", nargs="*")
     return ap.parse_args()
 
@@ -198,6 +199,15 @@ def main() -> int:
     sync()
     if dev.type == "cuda":
         cops.check_status()
+    if args.trace and rank == 0 or (args.trace and world > 1):
+        acts = [torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA]
+        with torch.profiler.profile(activities=acts) as prof:
+            with torch.profiler.record_function("ProfilerStep#0"):
+                trainer.train_step()
+                torch.cuda.synchronize()
+        if rank == 0:
+            os.makedirs(os.path.dirname(args.trace) or ".", exist_ok=True)
+            prof.export_chrome_trace(args.trace)
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -1,0 +1,510 @@
+// Fused expert-parallel dispatch / combine over NVLink peer memory.
+//
+// Every rank owns a symmetric workspace; kernels take a table of the peers' base pointers and address
+// each region by the same byte offset on every rank.  Rows travel exactly once:
+//
+//   count   : per-block histograms of (token, k) pairs by global expert (deterministic, no atomics)
+//   publish : reduce the histograms, store this rank's counts into every peer's count matrix, release a
+//             per-source flag (epoch valued, system scope)
+//   plan    : wait for all sources' flags, derive from the full [world, E] matrix (a) this rank's expert
+//             segments (offsets aligned to `pad`, valid counts) and (b) for every global expert the row in
+//             the owner's buffer where this rank's rows start -- so senders write straight into the final
+//             expert-major layout and the grouped GEMM needs no second permute
+//   slots   : stable rank of every pair inside its expert -> pair_loc[pair] = (owner rank, row)
+//   scatter : one warp per token: read the row once, store it (bf16, or 1x128 block-scaled e4m3 + fp32
+//             scales) into each of its K destination rows with 16-byte peer stores, store the gate
+//             probability beside it; zero this rank's own padding rows; last block releases "data ready"
+//   wait    : receiver waits for every source's "data ready" flag
+//   combine : one warp per token pulls its K expert-output rows from the owners with 16-byte peer loads,
+//             reduces in fp32 (optionally gate weighted) and writes bf16 -- un-permute, top-k reduction and
+//             the transfer are one pass
+//
+// No kernel both sets and waits on flags of the same epoch, so several ranks can be emulated by
+// launching each phase for all of them in turn on one GPU.  All waits are bounded (common.cuh).
+//
+// Reference analogues: pack/sort + multi-workgroup scatter into a [src][expert][slot] IPC buffer with
+// per-(src, expert) ready flags (notes/2026-04/2026-04-10_monolithmoe_layout_c_pack_optimization.md:98-137,
+// notes/2026-04/2026-04-14_data_layout_analysis.md:322-330,630-652) and the fp32 gather-combine phase
+// (notes/2026-04/2026-04-14_data_layout_analysis.md:534-605).
+#include "common.cuh"
+
+namespace slab {
+
+constexpr int PAIRS_PER_BLOCK = 1024;
+constexpr int COUNT_THREADS = 256;
+constexpr int MAX_EXPERTS = 512;
+constexpr int MAX_WORLD = 16;
+
+// Byte offsets of the regions inside every rank's symmetric workspace.
+struct WsLayout {
+  long counts_all;     // int  [world][E]      counts written by each source
+  long counts_flag;    // int  [world]         epoch flags for counts_all
+  long data_flag;      // int  [world]         epoch flags: source finished writing rows
+  long out_flag;       // int  [world]         epoch flags: owner finished its expert outputs
+  long rows;           // recv rows  [cap][H] bf16 (or e4m3)
+  long row_scales;     // float [cap][H/128]   (fp8 payload only)
+  long scalars;        // float [cap]          per-row scalar travelling with the row (gate prob)
+  long out_rows;       // bf16 [cap][H]        expert outputs, pulled by combine
+  long out_scalars;    // float [cap]          per-row scalar pulled by combine_scalars
+};
+
+struct PeerTable {
+  uint8_t* base[MAX_WORLD];
+};
+
+// ---------------------------------------------------------------- count
+__global__ void __launch_bounds__(COUNT_THREADS)
+moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int* __restrict__ block_hist) {
+  __shared__ int hist[MAX_EXPERTS];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * PAIRS_PER_BLOCK;
+  for (int i = threadIdx.x; i < PAIRS_PER_BLOCK; i += blockDim.x) {
+    int p = base + i;
+    if (p < n_pairs) atomicAdd(&hist[topk_idx[p]], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) block_hist[blockIdx.x * E + e] = hist[e];
+}
+
+// ---------------------------------------------------------------- publish (one block)
+// block_hist -> block_base (exclusive prefix over blocks), send_counts; store counts to every peer.
+__global__ void moe_publish_kernel(int* __restrict__ block_hist, int n_blocks, int E, int* __restrict__ send_counts,
+                                   PeerTable peers, WsLayout ws, int world, int me, int epoch) {
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int acc = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      int c = block_hist[b * E + e];
+      block_hist[b * E + e] = acc;          // becomes block_base
+      acc += c;
+    }
+    send_counts[e] = acc;
+    for (int d = 0; d < world; ++d) {
+      int* dst = reinterpret_cast<int*>(peers.base[d] + ws.counts_all) + me * E + e;
+      *dst = acc;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + ws.counts_flag) + me;
+    st_release_sys(flag, epoch);
+  }
+}
+
+// ---------------------------------------------------------------- plan (one block)
+// Outputs (local memory): expert_offsets[E_local], expert_counts[E_local], send_base[E], meta[0] = rows used.
+__global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me, int E, int pad, int capacity,
+                                int epoch, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
+                                int* __restrict__ send_base, int* __restrict__ meta, int* status) {
+  __shared__ int total[MAX_EXPERTS];      // rows of expert e over all sources
+  __shared__ int before[MAX_EXPERTS];     // rows of expert e from sources < me
+  __shared__ int seg_off[MAX_EXPERTS];    // aligned offset of expert e inside its owner's buffer
+  __shared__ int ok;
+  const int e_local = E / world;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.counts_flag) + threadIdx.x;
+    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  const int* call = reinterpret_cast<const int*>(peers.base[me] + ws.counts_all);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (int s = 0; s < world; ++s) {
+      int c = ld_acquire_sys(call + s * E + e);
+      if (s < me) b += c;
+      t += c;
+    }
+    total[e] = t;
+    before[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {             // one thread per owner rank: aligned prefix over its experts
+    int d = threadIdx.x, acc = 0;
+    for (int j = 0; j < e_local; ++j) {
+      int e = d * e_local + j;
+      seg_off[e] = acc;
+      acc += (total[e] + pad - 1) / pad * pad;
+    }
+    if (acc > capacity) atomicCAS(status, 0, ST_CAPACITY);
+    if (d == me) meta[0] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    send_base[e] = seg_off[e] + before[e];
+    if (e / e_local == me) {
+      expert_offsets[e - me * e_local] = seg_off[e];
+      expert_counts[e - me * e_local] = total[e];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- slots
+// pair_loc[p] = (owner << 24) | row   (row < 2^24).  Stable: pairs of one expert keep their pair order.
+__global__ void __launch_bounds__(COUNT_THREADS)
+moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world, const int* __restrict__ block_base,
+                 const int* __restrict__ send_base, int capacity, int* __restrict__ pair_loc, int* status) {
+  __shared__ int run[MAX_EXPERTS];                 // pairs of e seen so far in this block
+  __shared__ int warp_hist[COUNT_THREADS / 32][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e_local = E / world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) run[e] = block_base[blockIdx.x * E + e];
+  const int base = blockIdx.x * PAIRS_PER_BLOCK;
+  for (int chunk = 0; chunk < PAIRS_PER_BLOCK; chunk += COUNT_THREADS) {
+    for (int i = threadIdx.x; i < (COUNT_THREADS / 32) * E; i += blockDim.x) (&warp_hist[0][0])[(i / E) * MAX_EXPERTS + i % E] = 0;
+    __syncthreads();
+    const int p = base + chunk + threadIdx.x;
+    const bool valid = p < n_pairs;
+    const int e = valid ? topk_idx[p] : -1 - lane;  // distinct dummies never match
+    const unsigned peers_mask = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers_mask & ((1u << lane) - 1));
+    if (valid && rank_in_warp == 0) warp_hist[warp][e] = __popc(peers_mask);
+    __syncthreads();
+    if (valid) {
+      int off = run[e] + rank_in_warp;
+      for (int w = 0; w < warp; ++w) off += warp_hist[w][e];
+      const int row = send_base[e] + off;
+      if (row >= capacity || row < 0) {
+        atomicCAS(status, 0, ST_CAPACITY);
+        pair_loc[p] = -1;
+      } else {
+        pair_loc[p] = ((e / e_local) << 24) | row;
+      }
+    }
+    __syncthreads();
+    for (int ee = threadIdx.x; ee < E; ee += blockDim.x) {
+      int add = 0;
+      for (int w = 0; w < COUNT_THREADS / 32; ++w) add += warp_hist[w][ee];
+      run[ee] += add;
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------- scatter
+// FP8 = false: rows are copied as bf16.  FP8 = true: each 128-column block is scaled to e4m3 with an fp32
+// scale (amax / 448) written to row_scales.  `scale_in` (optional, per pair) multiplies the row first
+// (backward of a gate-weighted combine).
+template <bool FP8>
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ pair_scalar,
+                   const float* __restrict__ scale_in, const int* __restrict__ pair_loc, int T, int K, int H,
+                   PeerTable peers, WsLayout ws, int world, int me, int epoch,
+                   const int* __restrict__ expert_offsets, const int* __restrict__ expert_counts, int e_local, int pad,
+                   int* __restrict__ done_counter) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int gwarp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int n_warps = gridDim.x * warps_per_block;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = gwarp; t < T; t += n_warps) {
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)t * H);
+    for (int k = 0; k < K; ++k) {
+      const int loc = pair_loc[t * K + k];
+      if (loc < 0) continue;
+      const int d = loc >> 24, row = loc & 0xFFFFFF;
+      uint8_t* pb = peers.base[d];
+      const float sc = scale_in ? scale_in[t * K + k] : 1.f;
+      if (!FP8) {
+        bf16x8* dst = reinterpret_cast<bf16x8*>(pb + ws.rows) + (size_t)row * nvec;
+        for (int c = lane; c < nvec; c += 32) {
+          bf16x8 v = src[c];
+          if (scale_in) {
+            float f[8];
+            unpack8(v, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= sc;
+            v = pack8(f);
+          }
+          dst[c] = v;
+        }
+      } else {
+        uint2* dst = reinterpret_cast<uint2*>(pb + ws.rows) + (size_t)row * nvec;
+        float* sdst = reinterpret_cast<float*>(pb + ws.row_scales) + (size_t)row * (H >> 7);
+        // a 128-column block is 16 consecutive vec8 chunks = 16 consecutive lanes
+        for (int c0 = 0; c0 < nvec; c0 += 32) {
+          const int c = c0 + lane;
+          float f[8];
+          float amax = 0.f;
+          if (c < nvec) {
+            unpack8(src[c], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[j] *= sc;
+              amax = fmaxf(amax, fabsf(f[j]));
+            }
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          amax = fmaxf(amax, 1e-12f);
+          if (c < nvec) {
+            const float inv = 448.f / amax;
+            __nv_fp8_e4m3 q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = __nv_fp8_e4m3(f[j] * inv);
+            dst[c] = *reinterpret_cast<uint2*>(q);
+            if ((lane & 15) == 0) sdst[c >> 4] = amax / 448.f;
+          }
+        }
+      }
+      if (pair_scalar && lane == 0)
+        reinterpret_cast<float*>(pb + ws.scalars)[row] = pair_scalar[t * K + k];
+    }
+  }
+  // zero this rank's own alignment padding rows (and their scalars): rows [count, roundup(count, pad))
+  {
+    uint8_t* mine = peers.base[me];
+    const int row_bytes = FP8 ? H : 2 * H;
+    for (int j = 0; j < e_local; ++j) {
+      const int cnt = expert_counts[j];
+      const int first = expert_offsets[j] + cnt;
+      const int n_pad = (cnt + pad - 1) / pad * pad - cnt;
+      for (int r = gwarp; r < n_pad; r += n_warps) {
+        uint4* dst = reinterpret_cast<uint4*>(mine + ws.rows + (size_t)(first + r) * row_bytes);
+        for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+        if (FP8) {
+          float* sd = reinterpret_cast<float*>(mine + ws.row_scales) + (size_t)(first + r) * (H >> 7);
+          for (int c = lane; c < (H >> 7); c += 32) sd[c] = 0.f;
+        }
+        if (lane == 0) reinterpret_cast<float*>(mine + ws.scalars)[first + r] = 0.f;
+      }
+    }
+  }
+  // completion: every block fences its peer stores; the last block releases the per-source flag everywhere
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    int ticket = atomicAdd(done_counter, 1);
+    is_last = (ticket == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence_system();
+    if (threadIdx.x < world) {
+      int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + ws.data_flag) + me;
+      st_release_sys(flag, epoch);
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+// ---------------------------------------------------------------- wait / signal (one small block)
+__global__ void moe_wait_flags_kernel(PeerTable peers, long flag_offset, int world, int me, int epoch, int* status,
+                                      unsigned long long limit_ns) {
+  if (threadIdx.x < world) {
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + flag_offset) + threadIdx.x;
+    wait_flag_ge(flag, epoch, status, limit_ns);
+  }
+}
+
+__global__ void moe_signal_kernel(PeerTable peers, long flag_offset, int world, int me, int epoch) {
+  __threadfence_system();
+  if (threadIdx.x < world) {
+    int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + flag_offset) + me;
+    st_release_sys(flag, epoch);
+  }
+}
+
+// ---------------------------------------------------------------- combine (pull)
+// y[t] = sum_k w[t,k] * out_rows_of_owner[row(t,k)]   (w == nullptr: plain sum).  One warp per token;
+// the K rows are requested before any is consumed so K peer loads are in flight per lane.
+template <int KMAX>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ pair_loc,
+                   int T, int K, int H, PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.out_flag) + threadIdx.x;
+    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  const int warps_per_block = blockDim.x >> 5;
+  const int gwarp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int n_warps = gridDim.x * warps_per_block;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = gwarp; t < T; t += n_warps) {
+    const bf16x8* rows[KMAX];
+    float w[KMAX];
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      rows[k] = nullptr;
+      w[k] = 0.f;
+      if (k < K) {
+        const int loc = pair_loc[t * K + k];
+        if (loc >= 0) {
+          rows[k] = reinterpret_cast<const bf16x8*>(peers.base[loc >> 24] + ws.out_rows) + (size_t)(loc & 0xFFFFFF) * nvec;
+          w[k] = weights ? weights[t * K + k] : 1.f;
+        }
+      }
+    }
+    for (int c = lane; c < nvec; c += 32) {
+      bf16x8 v[KMAX];
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k)
+        if (rows[k]) v[k] = rows[k][c];
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k) {
+        if (rows[k]) {
+          float f[8];
+          unpack8(v[k], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += w[k] * f[j];
+        }
+      }
+      reinterpret_cast<bf16x8*>(y + (size_t)t * H)[c] = pack8(acc);
+    }
+  }
+}
+
+// per-pair scalars pulled from the owners' out_scalars (backward of dispatch_scalars)
+__global__ void moe_combine_scalars_kernel(float* __restrict__ s, const int* __restrict__ pair_loc, int n_pairs,
+                                           PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.out_flag) + threadIdx.x;
+    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x) {
+    const int loc = pair_loc[p];
+    s[p] = loc >= 0 ? reinterpret_cast<const float*>(peers.base[loc >> 24] + ws.out_scalars)[loc & 0xFFFFFF] : 0.f;
+  }
+}
+
+}  // namespace slab
+
+using namespace slab;
+
+static PeerTable make_peers(const long* ptrs, int world) {
+  PeerTable t;
+  for (int i = 0; i < MAX_WORLD; ++i) t.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
+  return t;
+}
+
+static WsLayout make_layout(const long* off) {
+  WsLayout w;
+  w.counts_all = off[0]; w.counts_flag = off[1]; w.data_flag = off[2]; w.out_flag = off[3];
+  w.rows = off[4]; w.row_scales = off[5]; w.scalars = off[6]; w.out_rows = off[7]; w.out_scalars = off[8];
+  return w;
+}
+
+extern "C" int slab_moe_count_blocks(int n_pairs) { return (n_pairs + PAIRS_PER_BLOCK - 1) / PAIRS_PER_BLOCK; }
+
+// Phase 1 of a plan: histogram + publish this rank's counts to all peers.  `peer_ptrs` / `ws_offsets` are
+// host arrays (world pointers, 9 region offsets).
+extern "C" int slab_moe_count_publish(const int* topk_idx, int n_pairs, int E, int* block_hist, int* send_counts,
+                                      const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                      cudaStream_t st) {
+  if (E > MAX_EXPERTS || world > MAX_WORLD || E % world) return -100;
+  int nb = slab_moe_count_blocks(n_pairs);
+  if (nb < 1) nb = 1;
+  moe_count_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, block_hist);
+  moe_publish_kernel<<<1, 512, 0, st>>>(block_hist, nb, E, send_counts, make_peers(peer_ptrs, world),
+                                        make_layout(ws_offsets), world, me, epoch);
+  return (int)cudaGetLastError();
+}
+
+// Phase 2: wait for all counts, derive segments and send bases, assign every pair its destination row.
+extern "C" int slab_moe_plan_slots(const int* topk_idx, int n_pairs, int E, const int* block_base,
+                                   const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                   int pad, int capacity, int* expert_offsets, int* expert_counts, int* send_base,
+                                   int* meta, int* pair_loc, int* status, cudaStream_t st) {
+  if (E > MAX_EXPERTS || world > MAX_WORLD || capacity >= (1 << 24)) return -100;
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  moe_plan_kernel<<<1, 512, 0, st>>>(pt, ws, world, me, E, pad, capacity, epoch, expert_offsets, expert_counts,
+                                     send_base, meta, status);
+  int nb = slab_moe_count_blocks(n_pairs);
+  if (nb < 1) nb = 1;
+  moe_slots_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, world, block_base, send_base, capacity,
+                                                 pair_loc, status);
+  return (int)cudaGetLastError();
+}
+
+// Push rows (and one scalar per pair) to their owners; fp8 != 0 quantises 1x128.
+extern "C" int slab_moe_scatter(const void* x, const float* pair_scalar, const float* scale_in, const int* pair_loc,
+                                int T, int K, int H, const long* peer_ptrs, const long* ws_offsets, int world, int me,
+                                int epoch, const int* expert_offsets, const int* expert_counts, int e_local, int pad,
+                                int fp8, int* done_counter, int n_blocks, cudaStream_t st) {
+  if (H % 128 || world > MAX_WORLD) return -100;
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  if (n_blocks <= 0) n_blocks = 148 * 4;
+  if (fp8)
+    moe_scatter_kernel<true><<<n_blocks, 256, 0, st>>>((const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, T, K,
+                                                       H, pt, ws, world, me, epoch, expert_offsets, expert_counts,
+                                                       e_local, pad, done_counter);
+  else
+    moe_scatter_kernel<false><<<n_blocks, 256, 0, st>>>((const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, T,
+                                                        K, H, pt, ws, world, me, epoch, expert_offsets, expert_counts,
+                                                        e_local, pad, done_counter);
+  return (int)cudaGetLastError();
+}
+
+// which: 0 = data_flag (rows arrived), 1 = out_flag, 2 = counts_flag
+extern "C" int slab_moe_wait(const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch, int which,
+                             int* status, cudaStream_t st) {
+  WsLayout ws = make_layout(ws_offsets);
+  long off = which == 0 ? ws.data_flag : (which == 1 ? ws.out_flag : ws.counts_flag);
+  moe_wait_flags_kernel<<<1, 32, 0, st>>>(make_peers(peer_ptrs, world), off, world, me, epoch, status, SLAB_WAIT_NS);
+  return (int)cudaGetLastError();
+}
+
+// Same wait with a caller-chosen bound (nanoseconds): lets a test make a wait run out quickly.
+extern "C" int slab_moe_wait_limit(const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                   int which, int* status, long limit_ns, cudaStream_t st) {
+  WsLayout ws = make_layout(ws_offsets);
+  long off = which == 0 ? ws.data_flag : (which == 1 ? ws.out_flag : ws.counts_flag);
+  moe_wait_flags_kernel<<<1, 32, 0, st>>>(make_peers(peer_ptrs, world), off, world, me, epoch, status,
+                                          (unsigned long long)limit_ns);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_moe_signal_out(const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                   cudaStream_t st) {
+  WsLayout ws = make_layout(ws_offsets);
+  moe_signal_kernel<<<1, 32, 0, st>>>(make_peers(peer_ptrs, world), ws.out_flag, world, me, epoch);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_moe_combine(void* y, const float* weights, const int* pair_loc, int T, int K, int H,
+                                const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                int* status, int n_blocks, cudaStream_t st) {
+  if (H % 8 || K > 16 || world > MAX_WORLD) return -100;
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  if (n_blocks <= 0) n_blocks = 148 * 4;
+  if (K <= 2)
+    moe_combine_kernel<2><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+  else if (K <= 4)
+    moe_combine_kernel<4><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+  else if (K <= 8)
+    moe_combine_kernel<8><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+  else
+    moe_combine_kernel<16><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_moe_combine_scalars(float* s, const int* pair_loc, int n_pairs, const long* peer_ptrs,
+                                        const long* ws_offsets, int world, int me, int epoch, int* status,
+                                        cudaStream_t st) {
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  int nb = (n_pairs + 255) / 256;
+  if (nb < 1) nb = 1;
+  if (nb > 148 * 4) nb = 148 * 4;
+  moe_combine_scalars_kernel<<<nb, 256, 0, st>>>(s, pair_loc, n_pairs, pt, ws, world, me, epoch, status);
+  return (int)cudaGetLastError();
+}

@@ -308,6 +308,13 @@ static int make_map_bf16(CUtensorMap* m, const void* base, uint64_t rows, uint64
                          uint32_t box_cols) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return -1;
+  // the driver entry point needs a current context; threads that have only been handed tensors (the
+  // autograd engine's workers) may not have touched the runtime yet
+  static thread_local bool ctx_ready = false;
+  if (!ctx_ready) {
+    cudaFree(0);
+    ctx_ready = true;
+  }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
   cuuint32_t box[2] = {box_cols, box_rows};

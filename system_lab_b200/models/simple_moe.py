@@ -184,11 +184,17 @@ class MoEFFN(nn.Module):
         d = self.dispatcher
         plan = d.plan(idx)
         self.last_tokens_per_expert = plan.tokens_per_expert_global
-        xe = d.dispatch_rows(plan, x2)
-        pe = d.dispatch_scalars(plan, w)
+        if hasattr(d, "dispatch"):              # fused path: rows and gate probabilities travel together
+            xe, pe = d.dispatch(plan, x2, w)
+            out_buf = d.expert_output_buffer()
+        else:
+            xe = d.dispatch_rows(plan, x2)
+            pe = d.dispatch_scalars(plan, w)
+            out_buf = None
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8)
         act = ops.swiglu_probs(h1, pe)
-        ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8)
+        ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
+                                out=out_buf)
         out = d.combine_rows(plan, ye)
         if self.shared is not None:
             out = out + self.shared(x2)

@@ -1,0 +1,284 @@
+"""Fused dispatch / combine over peer memory (kernels in ``csrc/dispatch.cu``).
+
+Same primitives and receiver layout as :class:`~system_lab_b200.moe.dispatch.AllToAllDispatcher`,
+but rows move once, written by the sender straight into the owner's expert-major buffer (forward
+dispatch, backward of combine) or pulled and reduced by the token's owner (forward combine, backward of
+dispatch).  Nothing is read back to the host: segment offsets and counts stay on the device and buffers
+are sized by capacity (host syncs on ``tokens_per_expert`` cost the reference 20-100 ms per iteration,
+``notes/2026-04/2026-04-21_gptoss_10_moe_fp8_grouped_gemm_diagnosis.md:93-99``).
+
+Buffers are views of the symmetric workspace and are reused by the next call of the same kind:
+``dispatch`` outputs stay valid until the next forward ``dispatch``, ``combine`` gradients until the
+next backward of ``combine``.  That is exactly the lifetime a layer needs when it is recomputed in
+backward; callers that keep activations across layers must ask for copies (``clone_outputs=True``).
+
+All ranks must issue the same sequence of calls: flags carry a call counter (epoch).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from ..comm.symm import SymmetricWorkspace
+from ..ops import cuda as cops
+
+for _name, _sig in {
+    "slab_moe_count_blocks": "i",
+    "slab_moe_count_publish": "piippppiiis",
+    "slab_moe_plan_slots": "piip" + "pp" + "iii" + "ii" + "pppppp" + "s",
+    "slab_moe_scatter": "pppp" + "iii" + "pp" + "iii" + "pp" + "iii" + "p" + "i" + "s",
+    "slab_moe_wait": "ppiiiips",
+    "slab_moe_signal_out": "ppiiis",
+    "slab_moe_combine": "pppiiippiiipis",
+    "slab_moe_combine_scalars": "ppippiiips",
+}.items():
+    cops.register(_name, _sig)
+
+
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
+
+
+def compute_layout(ep: int, num_experts: int, topk: int, hidden: int, max_tokens: int, pad: int,
+                   capacity_factor: float, fp8_payload: bool):
+    """Capacity (rows) and the byte offsets of every workspace region; ``(capacity, offsets, nbytes)``.
+
+    Capacity is the smaller of the dropless worst case (every token of every rank picks this rank's
+    experts) and ``capacity_factor`` times the expected load, plus alignment padding per expert."""
+    e_local = num_experts // ep
+    pairs = max_tokens * topk
+    worst = ep * max_tokens * min(topk, e_local)
+    want = int(capacity_factor * pairs) if ep > 1 else pairs
+    cap = _align(min(worst, want) + e_local * pad, pad)
+    if cap >= 1 << 24:
+        raise ValueError("capacity exceeds the 24-bit row field of pair_loc")
+    off, cur = {}, 0
+    # channel 0 = forward rows, channel 1 = rows of the backward of combine
+    for name, nbytes in (("counts_all", ep * num_experts * 4), ("counts_flag", ep * 4), ("data_flag0", ep * 4),
+                         ("data_flag1", ep * 4), ("out_flag", ep * 4), ("rows0", cap * hidden * 2),
+                         ("rows1", cap * hidden * 2),
+                         ("row_scales", cap * (hidden // 128) * 4 if fp8_payload else 256),
+                         ("scalars0", cap * 4), ("scalars1", cap * 4), ("out_rows", cap * hidden * 2),
+                         ("out_scalars", cap * 4)):
+        off[name] = cur
+        cur = _align(cur + nbytes)
+    return cap, off, cur
+
+
+@dataclass
+class FusedPlan:
+    num_tokens: int
+    topk: int
+    num_experts: int
+    ep: int
+    pad_to: int
+    capacity: int
+    expert_offsets: torch.Tensor      # [E_local] int32 (device)
+    expert_counts: torch.Tensor       # [E_local] int32 (device)
+    pair_loc: torch.Tensor            # [T*K] int32: (owner << 24) | row
+    meta: torch.Tensor                # [4] int32: rows used on this rank
+    tokens_per_expert_global: torch.Tensor   # [E] pairs routed from this rank
+    num_rows: int                     # == capacity (host-side bound)
+
+    @property
+    def e_local(self) -> int:
+        return self.num_experts // self.ep
+
+
+class FusedDispatcher:
+    def __init__(self, mesh, num_experts: int, topk: int, hidden: int, max_tokens: int, pad_to: int = 128,
+                 device=None, dtype=torch.bfloat16, capacity_factor: float = 2.0, workspace=None,
+                 ep: int | None = None, ep_rank: int | None = None, fp8_payload: bool = False,
+                 clone_outputs: bool = False):
+        self.E, self.K, self.H, self.T = num_experts, topk, hidden, max_tokens
+        self.ep = mesh.ep if ep is None else ep
+        self.me = mesh.ep_rank if ep_rank is None else ep_rank
+        self.pad = max(pad_to, 1)
+        self.device = device
+        self.dtype = dtype
+        self.fp8 = fp8_payload
+        self.clone_outputs = clone_outputs
+        if dtype != torch.bfloat16:
+            raise ValueError("the fused dispatcher moves bf16 rows")
+        self.capacity, off, cur = compute_layout(self.ep, num_experts, topk, hidden, max_tokens, self.pad,
+                                                  capacity_factor, fp8_payload)
+        cap, H = self.capacity, hidden
+        pairs = max_tokens * topk
+        self.off = off
+        self.nbytes = cur
+        if workspace is None:
+            workspace = SymmetricWorkspace(cur, mesh.ep_group if self.ep > 1 else None, self.ep, self.me, device)
+        self.ws = workspace
+        self._peer_ptrs = (ctypes.c_long * 16)(*(list(workspace.ptrs) + [0] * (16 - len(workspace.ptrs))))
+        self._lay = [self._layout(0), self._layout(1)]
+        self.epoch = 0
+        n_blocks = max(cops.lib().slab_moe_count_blocks(pairs), 1)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.block_hist = torch.zeros(n_blocks * num_experts, **i32)
+        self.send_counts = torch.zeros(num_experts, **i32)
+        self.send_base = torch.zeros(num_experts, **i32)
+        self.done_counter = torch.zeros(1, **i32)
+        self.status = cops.status_word(device)
+        # typed views of this rank's regions
+        self.rows = [workspace.view(off["rows0"], (cap, H), torch.bfloat16),
+                     workspace.view(off["rows1"], (cap, H), torch.bfloat16)]
+        self.scalars = [workspace.view(off["scalars0"], (cap,), torch.float32),
+                        workspace.view(off["scalars1"], (cap,), torch.float32)]
+        self.out_rows = workspace.view(off["out_rows"], (cap, H), torch.bfloat16)
+        self.out_scalars = workspace.view(off["out_scalars"], (cap,), torch.float32)
+        if fp8_payload:
+            self.rows_fp8 = workspace.view(off["rows0"], (cap, H), torch.float8_e4m3fn)
+            self.row_scales = workspace.view(off["row_scales"], (cap, H // 128), torch.float32)
+
+    def _layout(self, channel: int):
+        o = self.off
+        vals = [o["counts_all"], o["counts_flag"], o[f"data_flag{channel}"], o["out_flag"], o[f"rows{channel}"],
+                o["row_scales"], o[f"scalars{channel}"], o["out_rows"], o["out_scalars"]]
+        return (ctypes.c_long * 9)(*vals)
+
+    def _next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    # ---- plan ----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def plan_publish(self, topk_idx: torch.Tensor):
+        """Phase 1 (sets flags): histogram and publish this rank's counts."""
+        idx = topk_idx.to(torch.int32).contiguous()
+        t, k = idx.shape
+        if t > self.T or k != self.K:
+            raise ValueError(f"plan for {t}x{k} pairs exceeds the dispatcher's {self.T}x{self.K}")
+        ep = self._next_epoch()
+        cops.call("slab_moe_count_publish", idx, t * k, self.E, self.block_hist, self.send_counts,
+                  ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, ep,
+                  cops.stream())
+        return idx, ep
+
+    @torch.no_grad()
+    def plan_finish(self, idx: torch.Tensor, ep: int) -> FusedPlan:
+        """Phase 2 (waits on flags): segments, send bases and the destination row of every pair."""
+        t, k = idx.shape
+        e_local = self.E // self.ep
+        i32 = dict(dtype=torch.int32, device=self.device)
+        expert_offsets = torch.empty(e_local, **i32)
+        expert_counts = torch.empty(e_local, **i32)
+        meta = torch.zeros(4, **i32)
+        pair_loc = torch.empty(t * k, **i32)
+        cops.call("slab_moe_plan_slots", idx, t * k, self.E, self.block_hist, ctypes.addressof(self._peer_ptrs),
+                  ctypes.addressof(self._lay[0]), self.ep, self.me, ep, self.pad, self.capacity, expert_offsets,
+                  expert_counts, self.send_base, meta, pair_loc, self.status, cops.stream())
+        return FusedPlan(t, k, self.E, self.ep, self.pad, self.capacity, expert_offsets, expert_counts, pair_loc,
+                         meta, self.send_counts.clone(), self.capacity)
+
+    def plan(self, topk_idx: torch.Tensor) -> FusedPlan:
+        idx, ep = self.plan_publish(topk_idx)
+        return self.plan_finish(idx, ep)
+
+    # ---- raw phases (also used one by one by the single-GPU multi-rank emulation) ------------------
+    def scatter(self, plan: FusedPlan, x, scalars, channel: int, scale_in=None, fp8: bool = False) -> int:
+        ep = self._next_epoch()
+        cops.call("slab_moe_scatter", x, scalars, scale_in, plan.pair_loc, plan.num_tokens, plan.topk, self.H,
+                  ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[channel]), self.ep, self.me, ep,
+                  plan.expert_offsets, plan.expert_counts, plan.e_local, self.pad, 1 if fp8 else 0,
+                  self.done_counter, 0, cops.stream())
+        return ep
+
+    def wait_rows(self, channel: int, ep: int) -> None:
+        cops.call("slab_moe_wait", ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[channel]), self.ep,
+                  self.me, ep, 0, self.status, cops.stream())
+
+    def signal_out(self) -> int:
+        ep = self._next_epoch()
+        cops.call("slab_moe_signal_out", ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep,
+                  self.me, ep, cops.stream())
+        return ep
+
+    def pull_rows(self, plan: FusedPlan, ep: int, weights=None) -> torch.Tensor:
+        y = torch.empty(plan.num_tokens, self.H, dtype=torch.bfloat16, device=self.device)
+        cops.call("slab_moe_combine", y, weights, plan.pair_loc, plan.num_tokens, plan.topk, self.H,
+                  ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, ep,
+                  self.status, 0, cops.stream())
+        return y
+
+    def pull_scalars(self, plan: FusedPlan, ep: int) -> torch.Tensor:
+        s = torch.empty(plan.num_tokens * plan.topk, dtype=torch.float32, device=self.device)
+        cops.call("slab_moe_combine_scalars", s, plan.pair_loc, plan.num_tokens * plan.topk,
+                  ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, ep,
+                  self.status, cops.stream())
+        return s.view(plan.num_tokens, plan.topk)
+
+    def stage_out_rows(self, ye: torch.Tensor) -> None:
+        if ye.data_ptr() != self.out_rows.data_ptr():
+            self.out_rows[:ye.shape[0]].copy_(ye)
+
+    def expert_output_buffer(self) -> torch.Tensor:
+        """Where the last expert GEMM should write so that combine needs no staging copy."""
+        return self.out_rows
+
+    # ---- differentiable API ------------------------------------------------------------------------
+    def dispatch(self, plan: FusedPlan, x: torch.Tensor, probs: torch.Tensor | None):
+        """Returns ``(xe [capacity, H], pe [capacity] or None)``."""
+        return _FusedDispatch.apply(x, probs, self, plan)
+
+    def dispatch_rows(self, plan, x):
+        return self.dispatch(plan, x, None)[0]
+
+    def dispatch_scalars(self, plan, p):
+        raise NotImplementedError("use dispatch(plan, x, probs): rows and gate probabilities travel together")
+
+    def combine_rows(self, plan: FusedPlan, ye: torch.Tensor, weights: torch.Tensor | None = None):
+        return _FusedCombine.apply(ye, weights, self, plan)
+
+
+class _FusedDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, probs, d: FusedDispatcher, plan: FusedPlan):
+        ctx.d, ctx.plan, ctx.has_probs = d, plan, probs is not None
+        xc = x.contiguous()
+        pc = probs.float().contiguous() if probs is not None else None
+        ep = d.scatter(plan, xc, pc, channel=0)
+        d.wait_rows(0, ep)
+        xe, pe = d.rows[0], d.scalars[0]
+        if d.clone_outputs:
+            xe, pe = xe.clone(), pe.clone()
+        return xe, (pe if probs is not None else None)
+
+    @staticmethod
+    def backward(ctx, g_xe, g_pe):
+        d, plan = ctx.d, ctx.plan
+        d.stage_out_rows(g_xe.contiguous())
+        if ctx.has_probs and g_pe is not None:
+            d.out_scalars.copy_(g_pe)
+        ep = d.signal_out()
+        gx = d.pull_rows(plan, ep)
+        gp = d.pull_scalars(plan, ep) if (ctx.has_probs and g_pe is not None) else None
+        return gx, gp, None, None
+
+
+class _FusedCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ye, weights, d: FusedDispatcher, plan: FusedPlan):
+        ctx.d, ctx.plan = d, plan
+        if weights is not None:
+            weights = weights.float().contiguous()
+            ctx.save_for_backward(weights)
+        ctx.weighted = weights is not None
+        d.stage_out_rows(ye.contiguous())
+        ep = d.signal_out()
+        return d.pull_rows(plan, ep, weights)
+
+    @staticmethod
+    def backward(ctx, g):
+        d, plan = ctx.d, ctx.plan
+        w = ctx.saved_tensors[0] if ctx.weighted else None
+        ep = d.scatter(plan, g.contiguous(), None, channel=1, scale_in=w)
+        d.wait_rows(1, ep)
+        g_ye = d.rows[1]
+        if d.clone_outputs:
+            g_ye = g_ye.clone()
+        if ctx.weighted and ctx.needs_input_grad[1]:
+            raise NotImplementedError("gate-weighted fused combine has no weight gradient: apply the gate "
+                                      "inside SwiGLU (swiglu_probs) for training")
+        return g_ye, None, None, None

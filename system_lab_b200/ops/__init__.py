@@ -63,10 +63,12 @@ def router_topk(logits, topk, score_function="softmax", bias=None, norm_topk_pro
     return ref.router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False):
-    """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``."""
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None):
+    """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``.
+    ``out`` (kernel path only) names the buffer the result is written to, e.g. the peer-visible
+    expert-output buffer of the fused dispatcher."""
     if use_kernels(a):
-        return _cuda().grouped_linear(a, w, offsets, counts, fp8)
+        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out)
     return _GroupedLinearRef.apply(a, w, offsets, counts)
 
 

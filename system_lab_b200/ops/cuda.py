@@ -323,11 +323,11 @@ def _pick_bn(cols: int) -> int:
 
 class _GroupedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, w, offsets, counts):
+    def forward(ctx, a, w, offsets, counts, out=None):
         e, n, k = w.shape
         a = a.contiguous()
         w = w.contiguous()
-        out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, block_n=_pick_bn(n))
+        out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
         ctx.save_for_backward(a, w, offsets, counts)
         return out
 
@@ -341,16 +341,18 @@ class _GroupedLinear(torch.autograd.Function):
             da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, block_n=_pick_bn(k))
         if ctx.needs_input_grad[1]:
             dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
-        return da, dw, None, None
+        return da, dw, None, None, None
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False):
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None):
     e, n, k = w.shape
     if not _bf16(a, w) or k % 64 or n % 128:
         from . import _GroupedLinearRef
         return _GroupedLinearRef.apply(a, w, offsets, counts)
     offsets, counts = _check_segments(offsets, counts)
-    return _GroupedLinear.apply(a, w, offsets, counts)
+    if out is not None and (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
+        out = None
+    return _GroupedLinear.apply(a, w, offsets, counts, out)
 
 
 # ------------------------------------------------------------------------------ attention

@@ -164,7 +164,8 @@ class Engine:
                     tokens = self.cfg.train.micro_batch_size * m.seq_length // self.mesh.cp
                     shared = FusedDispatcher(self.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
-                                             device=self.device, dtype=self.compute_dtype)
+                                             device=self.device, dtype=self.compute_dtype,
+                                             clone_outputs=not self.recompute)
                 layer.ffn.dispatcher = shared
             else:
                 if shared is None:

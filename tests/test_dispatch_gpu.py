@@ -1,0 +1,133 @@
+"""Fused dispatch/combine kernels.  Several expert-parallel ranks are emulated on one GPU by running
+each phase of the protocol for all ranks in turn (no kernel waits on a flag of a later launch)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+class _Mesh:
+    def __init__(self, ep, ep_rank):
+        self.ep, self.ep_rank, self.ep_group = ep, ep_rank, None
+
+
+def _make(world, T, K, E, H, fp8=False, factor=4.0):
+    from system_lab_b200.comm.symm import EmulatedWorld
+    from system_lab_b200.moe.fused_dispatch import FusedDispatcher
+    dev = torch.device("cuda")
+    nbytes = _workspace_bytes(world, T, K, E, H, fp8, factor)
+    emu = EmulatedWorld(nbytes, world, dev)
+    return [FusedDispatcher(_Mesh(world, r), E, K, H, T, 128, dev, capacity_factor=factor,
+                            workspace=emu.workspace(r), fp8_payload=fp8) for r in range(world)]
+
+
+def _workspace_bytes(world, T, K, E, H, fp8, factor):
+    from system_lab_b200.moe.fused_dispatch import compute_layout
+    return compute_layout(world, E, K, H, T, 128, factor, fp8)[2]
+
+
+def _expected_layout(idx_all, world, E, pad=128):
+    """For every owner: (expert_offsets, expert_counts, list of (src, pair) per row)."""
+    e_local = E // world
+    out = []
+    for owner in range(world):
+        offs, cnts, rows = [], [], {}
+        acc = 0
+        for j in range(e_local):
+            e = owner * e_local + j
+            members = []
+            for src in range(world):
+                flat = idx_all[src].reshape(-1).tolist()
+                members += [(src, p) for p, ee in enumerate(flat) if ee == e]
+            offs.append(acc)
+            cnts.append(len(members))
+            for i, m in enumerate(members):
+                rows[acc + i] = m
+            acc += (len(members) + pad - 1) // pad * pad
+        out.append((offs, cnts, rows))
+    return out
+
+
+@pytest.mark.parametrize("world,T,K,E,H", [(1, 200, 2, 8, 256), (2, 300, 4, 16, 512), (4, 257, 8, 32, 1024)])
+def test_dispatch_combine_roundtrip(world, T, K, E, H):
+    from system_lab_b200.ops import cuda as cops
+    torch.manual_seed(world)
+    ds = _make(world, T, K, E, H)
+    dev = torch.device("cuda")
+    idx = [torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int() for _ in range(world)]
+    x = [torch.randn(T, H, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    pr = [torch.rand(T, K, device=dev) for _ in range(world)]
+    pubs = [d.plan_publish(i) for d, i in zip(ds, idx)]
+    plans = [d.plan_finish(*p) for d, p in zip(ds, pubs)]
+    eps = [d.scatter(pl, xx, pp.contiguous(), 0) for d, pl, xx, pp in zip(ds, plans, x, pr)]
+    for d, e in zip(ds, eps):
+        d.wait_rows(0, e)
+    torch.cuda.synchronize()
+    cops.check_status()
+    exp = _expected_layout([i.cpu() for i in idx], world, E)
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        assert plans[owner].expert_offsets.tolist() == offs
+        assert plans[owner].expert_counts.tolist() == cnts
+        got_rows, got_sc = ds[owner].rows[0], ds[owner].scalars[0]
+        for row, (src, p) in list(rows.items())[::7]:
+            assert torch.equal(got_rows[row], x[src][p // K]), f"owner {owner} row {row}"
+            assert got_sc[row].item() == pr[src].reshape(-1)[p].item()
+        # alignment padding rows are zero
+        for o, c in zip(offs, cnts):
+            padded = (c + 127) // 128 * 128
+            if padded > c:
+                assert not got_rows[o + c:o + padded].any()
+    # combine: owners publish f(row) = 2 * row content; every source pulls and sums over k
+    for d in ds:
+        d.out_rows.copy_((d.rows[0].float() * 2).to(torch.bfloat16))
+        d.out_scalars.copy_(d.scalars[0] * 3)
+    eps = [d.signal_out() for d in ds]
+    for r, d in enumerate(ds):
+        y = d.pull_rows(plans[r], eps[r])
+        yw = d.pull_rows(plans[r], eps[r], pr[r].contiguous())
+        s = d.pull_scalars(plans[r], eps[r])
+        torch.cuda.synchronize()
+        ref = (x[r].float() * 2 * K)
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2)
+        refw = x[r].float() * 2 * pr[r].sum(1, keepdim=True)
+        assert torch.allclose(yw.float(), refw, rtol=2e-2, atol=2e-2)
+        assert torch.allclose(s, pr[r] * 3)
+    cops.check_status()
+
+
+def test_fp8_payload_matches_reference_quant():
+    from system_lab_b200.ops import cuda as cops, reference as ref
+    world, T, K, E, H = 2, 128, 2, 8, 512
+    ds = _make(world, T, K, E, H, fp8=True)
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    idx = [torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int() for _ in range(world)]
+    x = [torch.randn(T, H, device=dev, dtype=torch.bfloat16) * 2 for _ in range(world)]
+    plans = [d.plan_finish(*p) for d, p in zip(ds, [d.plan_publish(i) for d, i in zip(ds, idx)])]
+    eps = [d.scatter(pl, xx, None, 0, fp8=True) for d, pl, xx in zip(ds, plans, x)]
+    for d, e in zip(ds, eps):
+        d.wait_rows(0, e)
+    torch.cuda.synchronize()
+    cops.check_status()
+    exp = _expected_layout([i.cpu() for i in idx], world, E)
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        for row, (src, p) in list(rows.items())[::5]:
+            deq = ref.dequant_1x128(ds[owner].rows_fp8[row], ds[owner].row_scales[row])
+            xr = x[src][p // K].float()
+            assert torch.allclose(deq, xr, rtol=0.07, atol=1e-3)
+
+
+def test_missing_flag_times_out_with_status_not_hang():
+    """A wait on a flag nobody sets returns within the bound and reports TIMEOUT_PEER_FLAG."""
+    from system_lab_b200.ops import cuda as cops
+    ds = _make(2, 64, 2, 8, 256)
+    d = ds[0]
+    import ctypes
+    cops.register("slab_moe_wait_limit", "ppiiiipls")
+    cops.call("slab_moe_wait_limit", ctypes.addressof(d._peer_ptrs), ctypes.addressof(d._lay[0]), d.ep, d.me,
+              12345, 0, d.status, 50_000_000, cops.stream())        # 50 ms bound
+    torch.cuda.synchronize()
+    with pytest.raises(cops.DeviceHang):
+        cops.check_status()
+    cops.check_status()   # status word is cleared; the context is still usable
+    assert torch.ones(4, device="cuda").sum().item() == 4

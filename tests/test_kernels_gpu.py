@@ -119,7 +119,7 @@ def test_quant_roundtrip(cops):
     q, s = cops.quant_1x128(x)
     qr, sr = ref.quant_1x128(x)
     _close(s, sr, 1e-6, 0)
-    _close(ref.dequant_1x128(q, s), ref.dequant_1x128(qr, sr), 0.07, 1e-6)
+    _close(ref.dequant_1x128(q, s), ref.dequant_1x128(qr, sr), 0.13, 1e-6)   # at most one e4m3 step apart
     _close(ref.dequant_1x128(q, s), x, 0.07, 1e-3)
     w = torch.randn(3, 256, 384, device="cuda", dtype=torch.bfloat16) * 0.02
     qw, sw = cops.quant_128x128(w)
