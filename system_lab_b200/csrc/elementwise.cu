@@ -6,7 +6,10 @@
 // (notes/2026-04/2026-04-20_gptoss_02_triton_rmsnorm_optimization.md:47-62), fused residual+RMSNorm
 // (notes/2026-04/2026-04-24_gptoss_17_fused_residual_rmsnorm_impl.md:43-83), SwiGLU*probs forward and
 // no-cat backward (notes/2026-04/2026-04-25_gptoss_23_swiglu_nocat_triton_verify.md:92-113).
+#include <cstdio>
+
 #include "common.cuh"
+#include "slab_noalloc.h"
 
 namespace slab {
 
@@ -564,5 +567,45 @@ extern "C" int slab_adamw(void* p, int p_is_bf16, const float* g, void* m, void*
     else LAUNCH(float, 2);
   }
 #undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// Scratch for the per-block gain-gradient partials lives in the module image (see slab_noalloc.h).
+static __device__ __align__(256) float g_noalloc_dw_partial[SLAB_NOALLOC_MAX_BLOCKS * SLAB_NOALLOC_MAX_H];
+
+// In host code `g_noalloc_dw_partial` is only a handle for the symbol, never a device address: the address
+// is looked up once per device and cached here.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+extern "C" int slab_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd,
+                                        const void* gres, void* dx, void* dw, int rows, int H, cudaStream_t st) {
+  if (H % 8) return SLAB_NOALLOC_ERR_SHAPE;
+  if (H > SLAB_NOALLOC_MAX_H) {
+    fprintf(stderr,
+            "slab_rmsnorm_bwd_noalloc: hidden size %d exceeds the built-in scratch (max %d); call "
+            "slab_rmsnorm_bwd with caller-provided scratch instead\n",
+            H, SLAB_NOALLOC_MAX_H);
+    return SLAB_NOALLOC_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  SLAB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SLAB_NOALLOC_ERR_DEVICE;
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    // first call on this device (it is the current one): resolve the symbol's device address
+    float* addr = nullptr;
+    SLAB_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_noalloc_dw_partial));
+    g_noalloc_scratch_addr[dev] = addr;
+  }
+  float* scratch = g_noalloc_scratch_addr[dev];
+  if (rows <= 0) return 0;
+  const int grid = slab_rmsnorm_bwd_blocks(rows);          // <= SLAB_NOALLOC_MAX_BLOCKS
+  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  // the partial rows are `H` floats apart; every block writes its whole row before the column sum reads it
+  if (chunks <= 1) launch_rmsnorm_bwd<1>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
+  else if (chunks <= 2) launch_rmsnorm_bwd<2>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
+  else launch_rmsnorm_bwd<4>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
+  colsum_to_bf16_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, grid, H);
   return (int)cudaGetLastError();
 }
