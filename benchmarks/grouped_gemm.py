@@ -30,7 +30,14 @@ def make_counts(slots: int, experts: int, zipf: bool, seed: int = 0) -> torch.Te
     return torch.bincount(idx, minlength=experts).int()
 
 
-def time_cuda(fn, iters: int = 10, warmup: int = 3, flush=None) -> float:
+ONLY = [""]
+WARMUP = [3]
+
+
+def time_cuda(fn, iters: int = 10, warmup: int = 3, flush=None, name: str = ""):
+    if ONLY[0] and name != ONLY[0]:
+        return None
+    warmup = WARMUP[0]
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -58,7 +65,11 @@ def main():
     ap.add_argument("--baseline", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
+    ap.add_argument("--only", default="", help="run a single op, e.g. 'fc1 fwd' (for profiler captures)")
+    ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
+    ONLY[0] = args.only
+    WARMUP[0] = args.warmup
     from system_lab_b200.ops import cuda as cops
     dev = torch.device("cuda")
     peaks = {}
@@ -89,24 +100,27 @@ def main():
     results = {}
 
     def rec(name, ms, flops):
+        if ms is None:
+            return
         tf = flops / ms / 1e9
         results[name] = {"ms": ms, "tflops": tf, "frac_of_peak": tf / peak_tf}
         print(f"{name:28s} {ms:8.3f} ms  {tf:8.1f} TFLOP/s  {tf / peak_tf:5.2f} of {peak_src} bf16 peak")
 
     fl1 = 2.0 * valid * (2 * f) * h
     fl2 = 2.0 * valid * h * f
-    rec("fc1 fwd", time_cuda(lambda: cops.grouped_gemm_raw(0, x, w1, off_d, cnt_d, 2 * f, h), args.iters, flush=flush), fl1)
-    rec("fc2 fwd", time_cuda(lambda: cops.grouped_gemm_raw(0, act, w2, off_d, cnt_d, h, f), args.iters, flush=flush), fl2)
-    rec("fc1 dgrad", time_cuda(lambda: cops.grouped_gemm_raw(1, dy1, w1, off_d, cnt_d, 2 * f, h), args.iters, flush=flush), fl1)
-    rec("fc2 dgrad", time_cuda(lambda: cops.grouped_gemm_raw(1, dy2, w2, off_d, cnt_d, h, f), args.iters, flush=flush), fl2)
-    rec("fc1 wgrad", time_cuda(lambda: cops.grouped_gemm_raw(2, dy1, x, off_d, cnt_d, 2 * f, h), args.iters, flush=flush), fl1)
-    rec("fc2 wgrad", time_cuda(lambda: cops.grouped_gemm_raw(2, dy2, act, off_d, cnt_d, h, f), args.iters, flush=flush), fl2)
-    fwd_ms = results["fc1 fwd"]["ms"] + results["fc2 fwd"]["ms"]
-    all_ms = sum(r["ms"] for r in results.values())
-    rec("forward (fc1+fc2)", fwd_ms, fl1 + fl2)
-    rec("forward+backward", all_ms, 3 * (fl1 + fl2))
+    rec("fc1_fwd", time_cuda(lambda: cops.grouped_gemm_raw(0, x, w1, off_d, cnt_d, 2 * f, h), args.iters, flush=flush, name="fc1_fwd"), fl1)
+    rec("fc2_fwd", time_cuda(lambda: cops.grouped_gemm_raw(0, act, w2, off_d, cnt_d, h, f), args.iters, flush=flush, name="fc2_fwd"), fl2)
+    rec("fc1_dgrad", time_cuda(lambda: cops.grouped_gemm_raw(1, dy1, w1, off_d, cnt_d, 2 * f, h), args.iters, flush=flush, name="fc1_dgrad"), fl1)
+    rec("fc2_dgrad", time_cuda(lambda: cops.grouped_gemm_raw(1, dy2, w2, off_d, cnt_d, h, f), args.iters, flush=flush, name="fc2_dgrad"), fl2)
+    rec("fc1_wgrad", time_cuda(lambda: cops.grouped_gemm_raw(2, dy1, x, off_d, cnt_d, 2 * f, h), args.iters, flush=flush, name="fc1_wgrad"), fl1)
+    rec("fc2_wgrad", time_cuda(lambda: cops.grouped_gemm_raw(2, dy2, act, off_d, cnt_d, h, f), args.iters, flush=flush, name="fc2_wgrad"), fl2)
+    if not args.only:
+        fwd_ms = results["fc1_fwd"]["ms"] + results["fc2_fwd"]["ms"]
+        all_ms = sum(r["ms"] for r in results.values())
+        rec("forward (fc1+fc2)", fwd_ms, fl1 + fl2)
+        rec("forward+backward", all_ms, 3 * (fl1 + fl2))
     cops.check_status()
-    if args.baseline:
+    if args.baseline and not args.only:
         cl = counts.tolist()
         ol = offsets.tolist()
 

@@ -212,22 +212,25 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const 
   }
 }
 
-// ------------------------------------------------------------------ RoPE (half-split), out of place
-// x: [B, S, Hh, D] ; cos/sin: [S, D/2] fp32 ; sign = +1 forward, -1 backward.
-__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
-                            const float* __restrict__ sn, __nv_bfloat16* __restrict__ y, long n_rows, int S, int Hh,
-                            int D, float sign) {
+// ------------------------------------------------------------------ RoPE (half-split)
+// x: rows of `Hh` heads x D, `row_stride` elements apart (a packed qkv buffer rotates only its first Hh
+// heads); cos/sin: [S, D/2] fp32; sign = +1 forward, -1 backward.  y may alias x (in place).
+__global__ void rope_kernel(const __nv_bfloat16* x, const float* __restrict__ cs, const float* __restrict__ sn,
+                            __nv_bfloat16* y, long n_tok, int S, int Hh, int D, long row_stride_x,
+                            long row_stride_y, float sign) {
   const int d2 = D >> 1;
-  const int vec_per_row = d2 >> 3;           // vec8 chunks per half row
-  const long total = n_rows * vec_per_row;   // n_rows = B*S*Hh
+  const int vec_per_half = d2 >> 3;          // vec8 chunks per half head
+  const long per_tok = (long)Hh * vec_per_half;
+  const long total = n_tok * per_tok;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    long row = i / vec_per_row;
-    int c = int(i - row * vec_per_row);
-    int s = int((row / Hh) % S);
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    long tok = i / per_tok;
+    int rem = int(i - tok * per_tok);
+    int head = rem / vec_per_half, c = rem - head * vec_per_half;
+    int s = int(tok % S);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + tok * row_stride_x + (long)head * D);
     float a[8], b[8], co[8], si[8], oa[8], ob[8];
     unpack8(xr[c], a);
-    unpack8(xr[vec_per_row + c], b);
+    unpack8(xr[vec_per_half + c], b);
     const float4* cp = reinterpret_cast<const float4*>(cs + (size_t)s * d2 + c * 8);
     const float4* sp = reinterpret_cast<const float4*>(sn + (size_t)s * d2 + c * 8);
     float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
@@ -239,9 +242,9 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __
       oa[j] = a[j] * co[j] - b[j] * sj;
       ob[j] = b[j] * co[j] + a[j] * sj;
     }
-    bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + tok * row_stride_y + (long)head * D);
     yr[c] = pack8(oa);
-    yr[vec_per_row + c] = pack8(ob);
+    yr[vec_per_half + c] = pack8(ob);
   }
 }
 
@@ -310,16 +313,26 @@ quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, __nv_fp8_e4m3* __restr
 }
 
 // ------------------------------------------------------------------ squared L2 norm (fp32 input)
-__global__ void sumsq_kernel(const float* __restrict__ g, long n, float scale, float* __restrict__ out) {
+template <typename G>
+__global__ void sumsq_kernel(const G* __restrict__ g, long n, float scale, float* __restrict__ out) {
   __shared__ float red[32];
   float s = 0.f;
   const long nv = n >> 2;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
-    float4 v = reinterpret_cast<const float4*>(g)[i];
-    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (sizeof(G) == 4) {
+      float4 v = reinterpret_cast<const float4*>(g)[i];
+      s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    } else {
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(g) + 2 * i;
+      float2 a = __bfloat1622float2(gp[0]), b = __bfloat1622float2(gp[1]);
+      s += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (long i = nv << 2; i < n; ++i) s += g[i] * g[i];
+    for (long i = nv << 2; i < n; ++i) {
+      float v = float(g[i]);
+      s += v * v;
+    }
   s = block_sum(s, red);
   if (threadIdx.x == 0) atomicAdd(out, s * scale);
 }
@@ -332,8 +345,8 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
 };
 
-template <typename P, int KIND>
-__global__ void adamw_kernel(P* __restrict__ p, const float* __restrict__ g, void* __restrict__ m_raw,
+template <typename P, int KIND, typename G>
+__global__ void adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_raw,
                              void* __restrict__ v_raw, float* __restrict__ m_scale, float* __restrict__ v_scale,
                              __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ coef, long n,
                              AdamArgs a) {
@@ -342,9 +355,13 @@ __global__ void adamw_kernel(P* __restrict__ p, const float* __restrict__ g, voi
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nq; i += (long)gridDim.x * blockDim.x) {
     const long e0 = i << 2;
     float gv[4], mv[4], vv[4], pv[4];
-    {
+    if (sizeof(G) == 4) {
       float4 t = reinterpret_cast<const float4*>(g)[i];
       gv[0] = t.x * c; gv[1] = t.y * c; gv[2] = t.z * c; gv[3] = t.w * c;
+    } else {
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(g) + 2 * i;
+      float2 t0 = __bfloat1622float2(gp[0]), t1 = __bfloat1622float2(gp[1]);
+      gv[0] = t0.x * c; gv[1] = t0.y * c; gv[2] = t1.x * c; gv[3] = t1.y * c;
     }
     if (sizeof(P) == 4) {
       float4 t = reinterpret_cast<const float4*>(p)[i];
@@ -516,12 +533,13 @@ extern "C" int slab_swiglu_bwd(const void* dout, const void* gu, const float* pr
   return (int)cudaGetLastError();
 }
 
-extern "C" int slab_rope(const void* x, const float* cs, const float* sn, void* y, long n_rows, int S, int Hh, int D,
-                         float sign, cudaStream_t st) {
-  if (D % 16) return -100;
-  if (n_rows == 0) return 0;
-  rope_kernel<<<grid_for(n_rows * (D / 16), 256), 256, 0, st>>>((const __nv_bfloat16*)x, cs, sn, (__nv_bfloat16*)y,
-                                                                 n_rows, S, Hh, D, sign);
+// n_tok = B*S tokens, each with Hh heads of D starting at x + tok*row_stride_x (strides in elements).
+extern "C" int slab_rope(const void* x, const float* cs, const float* sn, void* y, long n_tok, int S, int Hh, int D,
+                         long row_stride_x, long row_stride_y, float sign, cudaStream_t st) {
+  if (D % 16 || row_stride_x % 8 || row_stride_y % 8) return -100;
+  if (n_tok == 0) return 0;
+  rope_kernel<<<grid_for(n_tok * Hh * (D / 16), 256), 256, 0, st>>>((const __nv_bfloat16*)x, cs, sn, (__nv_bfloat16*)y,
+                                                                     n_tok, S, Hh, D, row_stride_x, row_stride_y, sign);
   return (int)cudaGetLastError();
 }
 
@@ -540,33 +558,43 @@ extern "C" int slab_quant_128x128(const void* w, void* q, float* scale, int mats
   return (int)cudaGetLastError();
 }
 
-extern "C" int slab_sumsq(const float* g, long n, float scale, float* out, cudaStream_t st) {
+// out += scale * sum(g^2); g is fp32 (g_is_bf16 == 0) or bf16.
+extern "C" int slab_sumsq(const void* g, int g_is_bf16, long n, float scale, float* out, cudaStream_t st) {
   if (n == 0) return 0;
-  sumsq_kernel<<<grid_for(n / 4 + 1, 256, 4), 256, 0, st>>>(g, n, scale, out);
+  if (g_is_bf16)
+    sumsq_kernel<__nv_bfloat16><<<grid_for(n / 4 + 1, 256, 4), 256, 0, st>>>((const __nv_bfloat16*)g, n, scale, out);
+  else
+    sumsq_kernel<float><<<grid_for(n / 4 + 1, 256, 4), 256, 0, st>>>((const float*)g, n, scale, out);
   return (int)cudaGetLastError();
 }
 
-// p_is_bf16: weights updated in place are bf16 (no fp32 master); state_kind: 0 fp32, 1 bf16, 2 fp8.
-// n must be a multiple of 128.
-extern "C" int slab_adamw(void* p, int p_is_bf16, const float* g, void* m, void* v, float* m_scale, float* v_scale,
-                          void* out_bf16, const float* coef, long n, int state_kind, float lr, float beta1,
-                          float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t st) {
+// p_is_bf16: weights updated in place are bf16 (no fp32 master); g_is_bf16: gradient dtype;
+// state_kind: 0 fp32, 1 bf16, 2 fp8.  n must be a multiple of 128.
+template <typename P, typename G>
+static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scale, float* v_scale, void* out_bf16,
+                         const float* coef, long n, int state_kind, AdamArgs a, int grid, cudaStream_t st) {
+  if (state_kind == 0)
+    adamw_kernel<P, 0, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+  else if (state_kind == 1)
+    adamw_kernel<P, 1, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+  else
+    adamw_kernel<P, 2, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+}
+
+extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
+                          float* v_scale, void* out_bf16, const float* coef, long n, int state_kind, float lr,
+                          float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t st) {
   if (n % 128) return -100;
   if (n == 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2};
   int grid = grid_for(n / 4, 256);
-#define LAUNCH(P, KIND)                                                                                        \
-  adamw_kernel<P, KIND><<<grid, 256, 0, st>>>((P*)p, g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a)
   if (p_is_bf16) {
-    if (state_kind == 0) LAUNCH(__nv_bfloat16, 0);
-    else if (state_kind == 1) LAUNCH(__nv_bfloat16, 1);
-    else LAUNCH(__nv_bfloat16, 2);
+    if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
+    else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
   } else {
-    if (state_kind == 0) LAUNCH(float, 0);
-    else if (state_kind == 1) LAUNCH(float, 1);
-    else LAUNCH(float, 2);
+    if (g_is_bf16) launch_adamw<float, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
+    else launch_adamw<float, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
   }
-#undef LAUNCH
   return (int)cudaGetLastError();
 }
 

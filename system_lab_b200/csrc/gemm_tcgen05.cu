@@ -38,15 +38,22 @@ struct GemmParams {
   int* status;
 };
 
+// Shared memory map (exactly the 227 KB a CTA may have): [0, 3072) barriers, TMEM slot, abort flag and the
+// tile prefix table; then the operand ring; then two 16 KB staging buffers for the TMA store of the output.
 template <int BN>
 struct SmemLayout {
+  static constexpr int CTRL_BYTES = 3072;
+  static constexpr int PREFIX_OFFSET = 256;                   // ints: up to 512 experts + 1
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 1024 + 4 * 520;   // barriers + tile prefix table
+  static constexpr int RING_OFFSET = CTRL_BYTES;
+  static constexpr int STORE_OFFSET = RING_OFFSET + STAGES * STAGE_BYTES;
+  static constexpr int STORE_BYTES = BM * 64 * 2;             // 128 rows x 64 bf16 columns
+  static constexpr int TOTAL = STORE_OFFSET + 2 * STORE_BYTES;
 };
+static_assert(SmemLayout<256>::TOTAL <= 232448 && SmemLayout<128>::TOTAL <= 232448, "shared memory budget");
 
 // Tile walk: experts in order; inside an expert the M index runs fastest so CTAs that run at the same
 // time share the expert's weight tile in L2.
@@ -85,20 +92,25 @@ __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmPar
 template <int MODE, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using L = SmemLayout<BN>;
   constexpr int STAGES = L::STAGES;
   constexpr bool A_MN = (MODE == MODE_WGRAD);
   constexpr bool B_MN = (MODE != MODE_FWD);
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {                 // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_INDEX);
+    return;
+  }
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* prefix = reinterpret_cast<int*>(smem + L::BAR_OFFSET + 1024);
+  int* prefix = reinterpret_cast<int*>(smem + L::PREFIX_OFFSET);
+  uint8_t* ring = smem + L::RING_OFFSET;
+  uint8_t* store_buf = smem + L::STORE_OFFSET;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -126,6 +138,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     prefix[p.E] = acc;
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 2 * BN);
@@ -146,7 +159,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int t = blockIdx.x; ok && get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
         for (int ks = 0; ks < ti.ksteps; ++ks) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* a_dst = ring + s * L::STAGE_BYTES;
           uint8_t* b_dst = a_dst + L::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], L::STAGE_BYTES);
           if (MODE == MODE_FWD) {
@@ -187,7 +200,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int ks = 0; ks < ti.ksteps; ++ks) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(ring + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
 #pragma unroll
           for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
@@ -208,67 +221,91 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
+    // TMEM -> registers -> bf16 -> swizzled shared staging (64 columns at a time, two buffers) -> TMA store.
+    // Rows/columns outside the output tensor are clipped by the TMA unit.  The accumulate variant of wgrad
+    // (beta = 1) reads and writes global memory directly instead.
     const int lg = warp & 3;                    // TMEM lane group this warp may read
+    const bool store_thread = (warp == 2 && lane == 0);
+    const int r_in_tile = lg * 32 + lane;
     int it = 0;
+    int chunk_ctr = 0;                          // staging buffer toggles per 64-column chunk
     TileInfo ti;
     for (int t = blockIdx.x; get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
-      const int r_in_tile = lg * 32 + lane;
-      __nv_bfloat16* c_row;
-      bool row_ok;
-      int col0 = ti.n_idx * BN;
-      int ldc;
-      if (MODE == MODE_WGRAD) {
-        ldc = p.K;
-        int n = ti.m_idx * BM + r_in_tile;
-        row_ok = n < p.N;
-        c_row = p.C + ((size_t)ti.e * p.N + n) * ldc;
-      } else {
-        ldc = out_cols;
-        int r = ti.row0 + r_in_tile;
-        row_ok = r < p.R;
-        c_row = p.C + (size_t)r * ldc;
+      const int col0 = ti.n_idx * BN;
+      const int tile_row = (MODE == MODE_WGRAD) ? (ti.e * p.N + ti.m_idx * BM) : ti.row0;
+      const bool direct = (MODE == MODE_WGRAD) && p.accumulate;
+      __nv_bfloat16* c_row = p.C + (size_t)(tile_row + r_in_tile) * out_cols;
+      const bool row_ok = (MODE == MODE_WGRAD) ? (ti.m_idx * BM + r_in_tile < p.N) : (tile_row + r_in_tile < p.R);
+      const bool empty = (ti.ksteps == 0);      // expert without rows (wgrad): the gradient is zero
+      if (empty && direct) continue;
+      int buf = 0;
+      if (!empty) {
+        buf = it & 1;
+        if (!mbar_wait(&tfull_bar[buf], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+        tc_fence_after();
       }
-      if (ti.ksteps == 0) {                     // empty expert (WGRAD): gradient is zero
-        if (row_ok && !p.accumulate) {
-          for (int c = 0; c < BN; c += 8)
-            if (col0 + c < out_cols) *reinterpret_cast<uint4*>(c_row + col0 + c) = make_uint4(0, 0, 0, 0);
-        }
-        continue;
-      }
-      const int buf = it & 1;
-      if (!mbar_wait(&tfull_bar[buf], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
-      tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c, v);
-        tmem_ld_wait();
-        if (row_ok) {
+      for (int c = 0; c < BN; c += 64) {
+        uint32_t v[64];
+        if (!empty) {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(taddr + c, lo);
+          tmem_ld_32x32(taddr + c + 32, hi);
+          tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            int col = col0 + c + g * 8;
-            if (col < out_cols) {
-              float f[8];
+          for (int i = 0; i < 32; ++i) { v[i] = lo[i]; v[32 + i] = hi[i]; }
+        } else {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]);
-              bf16x8* dst = reinterpret_cast<bf16x8*>(c_row + col);
-              if (MODE == MODE_WGRAD && p.accumulate) {
-                float o[8];
+          for (int i = 0; i < 64; ++i) v[i] = 0u;
+        }
+        if (direct) {
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const int col = col0 + c + g * 8;
+              if (col < out_cols) {
+                float f[8], o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]);
+                bf16x8* dst = reinterpret_cast<bf16x8*>(c_row + col);
                 unpack8(*dst, o);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] += o[i];
+                *dst = pack8(f);
               }
-              *dst = pack8(f);
             }
           }
+          continue;
         }
+        uint8_t* sb = store_buf + (chunk_ctr & 1) * L::STORE_BYTES;
+        // the TMA store that last read this buffer (two chunks ago) must have finished reading it
+        if (store_thread) tma_store_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]);
+          // 128-byte swizzle: 16-byte chunk g of row r lives at chunk (g ^ (r & 7))
+          *reinterpret_cast<bf16x8*>(sb + r_in_tile * 128 + ((g ^ (r_in_tile & 7)) << 4)) = pack8(f);
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (store_thread) {
+          tma_store_2d(&tmap_c, sb, col0 + c, tile_row);
+          tma_store_commit();
+        }
+        ++chunk_ctr;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
-      ++it;
+      if (!empty) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        ++it;
+      }
     }
+    if (store_thread) tma_store_wait<0>();      // all output written before the CTA retires
   }
 
   // ---------------------------------------------------------------- teardown
@@ -350,13 +387,19 @@ static int launch(const void* A, const void* B, const GemmParams& p, int grid, c
     if ((rc = make_map_bf16(&ma, A, p.R, p.N, BK, 64))) return rc;
     if ((rc = make_map_bf16(&mb, B, p.R, p.K, BK, 64))) return rc;
   }
+  CUtensorMap mc;
+  if (MODE == MODE_WGRAD) {
+    if ((rc = make_map_bf16(&mc, p.C, (uint64_t)p.E * p.N, p.K, BM, 64))) return rc;
+  } else {
+    if ((rc = make_map_bf16(&mc, p.C, p.R, (MODE == MODE_FWD) ? p.N : p.K, BM, 64))) return rc;
+  }
   static bool attr_set = false;
   auto kern = grouped_gemm_kernel<MODE, BN>;
   if (!attr_set) {
-    SLAB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL + 1024));
+    SLAB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_set = true;
   }
-  kern<<<grid, GEMM_THREADS, L::TOTAL + 1024, stream>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
   return (int)cudaGetLastError();
 }
 

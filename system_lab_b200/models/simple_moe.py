@@ -73,10 +73,11 @@ class GQAttention(nn.Module):
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
         qkv = F.linear(x, self.wqkv.to(x.dtype))
+        qkv = ops.rope_packed(qkv, cos, sin, self.nq + self.nkv, self.d)      # q and k heads, one pass
         q, k, v = qkv.split([self.nq * self.d, self.nkv * self.d, self.nkv * self.d], dim=-1)
-        q = ops.rope(q.reshape(b, s, self.nq, self.d), cos, sin)
-        k = ops.rope(k.reshape(b, s, self.nkv, self.d), cos, sin)
-        v = v.reshape(b, s, self.nkv, self.d)
+        q = q.unflatten(-1, (self.nq, self.d))
+        k = k.unflatten(-1, (self.nkv, self.d))
+        v = v.unflatten(-1, (self.nkv, self.d))
         if self.cp_group is not None:
             from ..parallel.cp import ulysses_attention
             o = ulysses_attention(q, k, v, self.cp_group, window=self.window)
@@ -172,7 +173,7 @@ class MoEFFN(nn.Module):
         cfg = self.cfg
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        logits = F.linear(x2.float(), self.router.float())
+        logits = ops.router_logits(x2, self.router)
         w, idx, scores = ops.router_topk(logits, cfg.moe_router_topk, cfg.moe_router_score_function,
                                          self.router_bias, cfg.moe_norm_topk_prob,
                                          cfg.moe_router_topk_scaling_factor)
@@ -191,7 +192,8 @@ class MoEFFN(nn.Module):
             xe = d.dispatch_rows(plan, x2)
             pe = d.dispatch_scalars(plan, w)
             out_buf = None
-        h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8)
+        h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
+                                dgrad_out=out_buf)
         act = ops.swiglu_probs(h1, pe)
         ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 out=out_buf)

@@ -57,18 +57,38 @@ def swiglu_probs(gate_up, probs):
     return _cuda().swiglu_probs(gate_up, probs) if use_kernels(gate_up) else ref.swiglu_probs(gate_up, probs)
 
 
+def router_logits(x, router_weight):
+    """fp32 router logits ``x @ Wr^T``.  On the GPU the product runs on tensor cores from bf16 operands
+    with fp32 accumulation and fp32 output; the oracle casts both operands to fp32 first."""
+    if use_kernels(x) and x.dtype == torch.bfloat16 and router_weight.dtype == torch.bfloat16:
+        return _cuda().router_logits(x, router_weight)
+    return torch.nn.functional.linear(x.float(), router_weight.float())
+
+
 def router_topk(logits, topk, score_function="softmax", bias=None, norm_topk_prob=True, scaling_factor=1.0):
     if use_kernels(logits):
         return _cuda().router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
     return ref.router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None):
+def rope_packed(qkv, cos, sin, n_heads: int, head_dim: int):
+    """Rotate the first ``n_heads`` heads of each row of a packed ``[B, S, W]`` projection (q and k of a
+    fused qkv).  The kernel path rotates in place; the oracle path builds a new tensor."""
+    if use_kernels(qkv):
+        out = _cuda().rope_packed(qkv, cos, sin, n_heads, head_dim)
+        if out is not None:
+            return out
+    b, s, w = qkv.shape
+    rot = ref.rope(qkv[..., :n_heads * head_dim].reshape(b, s, n_heads, head_dim), cos, sin)
+    return torch.cat([rot.reshape(b, s, n_heads * head_dim), qkv[..., n_heads * head_dim:]], dim=-1)
+
+
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None):
     """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``.
     ``out`` (kernel path only) names the buffer the result is written to, e.g. the peer-visible
     expert-output buffer of the fused dispatcher."""
     if use_kernels(a):
-        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out)
+        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out)
     return _GroupedLinearRef.apply(a, w, offsets, counts)
 
 

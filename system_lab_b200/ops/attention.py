@@ -19,8 +19,29 @@ def set_attention_impl(name: str) -> None:
     _IMPL = name
 
 
+_CUDNN_OK = [None]        # None: untried, True/False afterwards
+
+
+def _cudnn_sdpa(q, k, v, scale):
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    hq, hkv = q.shape[2], k.shape[2]
+    with sdpa_kernel([SDPBackend.CUDNN_ATTENTION]):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                                           scale=scale, enable_gqa=hq != hkv)
+    return o.transpose(1, 2)
+
+
 def _library(q, k, v, scale, window):
     d, dv = q.shape[-1], v.shape[-1]
+    if q.is_cuda and window == 0 and q.dtype in (torch.bfloat16, torch.float16) and _CUDNN_OK[0] is not False:
+        try:
+            o = _cudnn_sdpa(q, k, v, scale)
+            _CUDNN_OK[0] = True
+            return o
+        except RuntimeError:
+            if _CUDNN_OK[0]:
+                raise
+            _CUDNN_OK[0] = False
     if d == dv and d <= 256 and q.dtype in (torch.bfloat16, torch.float16):
         try:
             from flash_attn import flash_attn_func

@@ -23,11 +23,11 @@ _SIGS = {
     "slab_rmsnorm_bwd": "ppppppppiis",
     "slab_swiglu_fwd": "ppplis",
     "slab_swiglu_bwd": "ppppplis",
-    "slab_rope": "ppppliiifs",
+    "slab_rope": "ppppliiillfs",
     "slab_quant_1x128": "ppplis",
     "slab_quant_128x128": "pppiiis",
-    "slab_sumsq": "plfps",
-    "slab_adamw": "pi" + "p" * 7 + "li" + "f" * 7 + "s",
+    "slab_sumsq": "pilfps",
+    "slab_adamw": "pipi" + "p" * 6 + "li" + "f" * 7 + "s",
     "slab_router_topk": "ppppiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
@@ -199,7 +199,7 @@ class _Rope(torch.autograd.Function):
         xc = x.contiguous()
         y = torch.empty_like(xc)
         ctx.save_for_backward(cos, sin)
-        call("slab_rope", xc, cos, sin, y, b * s * hh, s, hh, d, 1.0, stream())
+        call("slab_rope", xc, cos, sin, y, b * s, s, hh, d, hh * d, hh * d, 1.0, stream())
         return y
 
     @staticmethod
@@ -208,7 +208,7 @@ class _Rope(torch.autograd.Function):
         b, s, hh, d = g.shape
         gc = g.contiguous()
         out = torch.empty_like(gc)
-        call("slab_rope", gc, cos, sin, out, b * s * hh, s, hh, d, -1.0, stream())
+        call("slab_rope", gc, cos, sin, out, b * s, s, hh, d, hh * d, hh * d, -1.0, stream())
         return out, None, None
 
 
@@ -216,6 +216,35 @@ def rope(x, cos, sin):
     if not _bf16(x) or x.shape[-1] % 16:
         return ref.rope(x, cos, sin)
     return _Rope.apply(x, cos.contiguous(), sin.contiguous())
+
+
+class _RopePackedInplace(torch.autograd.Function):
+    """Rotates the first ``n_heads`` heads of every row of a packed ``[B, S, W]`` buffer in place (the q and
+    k heads of a fused qkv projection); the remaining columns (v) are untouched."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_heads, d):
+        b, s, w = qkv.shape
+        ctx.save_for_backward(cos, sin)
+        ctx.meta = (n_heads, d)
+        call("slab_rope", qkv, cos, sin, qkv, b * s, s, n_heads, d, w, w, 1.0, stream())
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        n_heads, d = ctx.meta
+        g = g.contiguous()
+        b, s, w = g.shape
+        call("slab_rope", g, cos, sin, g, b * s, s, n_heads, d, w, w, -1.0, stream())
+        return g, None, None, None, None
+
+
+def rope_packed(qkv, cos, sin, n_heads, d):
+    if not _bf16(qkv) or d % 16 or not qkv.is_contiguous():
+        return None
+    return _RopePackedInplace.apply(qkv, cos.contiguous(), sin.contiguous(), n_heads, d)
 
 
 # ------------------------------------------------------------------------------ SwiGLU
@@ -284,6 +313,23 @@ class _RouterTopK(torch.autograd.Function):
         return gl, None, None, None, None, None
 
 
+class _RouterLogits(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        gb = g.to(torch.bfloat16)
+        return gb @ w, gb.t() @ x
+
+
+def router_logits(x, w):
+    return _RouterLogits.apply(x, w)
+
+
 def router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor):
     lf = logits.float()
     w, idx = _RouterTopK.apply(lf, topk, score_function, bias.float().contiguous() if bias is not None else None,
@@ -322,13 +368,23 @@ def _pick_bn(cols: int) -> int:
 
 
 class _GroupedLinear(torch.autograd.Function):
+    """``out = a @ w[e]^T`` per expert segment.  Two fusions on the backward side:
+
+    * if the weight carries ``main_grad`` (a view of the flat gradient buffer set by the FSDP engine), wgrad
+      writes or accumulates straight into it and autograd sees no weight gradient (no zero fill, no add);
+    * ``dgrad_out`` names the buffer the input gradient is written to (the dispatcher's peer-visible
+      buffer, so the backward of dispatch needs no staging copy).
+    """
+
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, out=None):
+    def forward(ctx, a, w, offsets, counts, out=None, dgrad_out=None):
         e, n, k = w.shape
         a = a.contiguous()
-        w = w.contiguous()
+        w = w.contiguous() if not w.is_contiguous() else w
         out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
         ctx.save_for_backward(a, w, offsets, counts)
+        ctx.w_ref = w
+        ctx.dgrad_out = dgrad_out
         return out
 
     @staticmethod
@@ -338,13 +394,24 @@ class _GroupedLinear(torch.autograd.Function):
         g = g.contiguous()
         da = dw = None
         if ctx.needs_input_grad[0]:
-            da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, block_n=_pick_bn(k))
+            do = ctx.dgrad_out
+            if do is not None and (do.shape[0] < g.shape[0] or do.shape[1] != k):
+                do = None
+            da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, out=do, block_n=_pick_bn(k))
+            if do is not None:
+                da = do[:g.shape[0]]
         if ctx.needs_input_grad[1]:
-            dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
-        return da, dw, None, None, None
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                grouped_gemm_raw(2, g, a, offsets, counts, n, k, out=mg, accumulate=ctx.w_ref.main_grad_written,
+                                 block_n=_pick_bn(k))
+                ctx.w_ref.main_grad_written = True
+            else:
+                dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
+        return da, dw, None, None, None, None
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None):
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None):
     e, n, k = w.shape
     if not _bf16(a, w) or k % 64 or n % 128:
         from . import _GroupedLinearRef
@@ -352,7 +419,8 @@ def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None):
     offsets, counts = _check_segments(offsets, counts)
     if out is not None and (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
         out = None
-    return _GroupedLinear.apply(a, w, offsets, counts, out)
+    res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out)
+    return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
 
 
 # ------------------------------------------------------------------------------ attention
@@ -424,22 +492,24 @@ def quant_128x128(w):
 
 # ------------------------------------------------------------------------------ optimizer
 def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
-    call("slab_sumsq", g, g.numel(), float(scale), out, stream())
+    """``out += scale * sum(g^2)`` for an fp32 or bf16 flat tensor (no host sync)."""
+    call("slab_sumsq", g, 1 if g.dtype == torch.bfloat16 else 0, g.numel(), float(scale), out, stream())
 
 
 _KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
 
 
 def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step) -> None:
-    """Fused AdamW on one flat shard: reads the fp32 gradient shard, updates moments (any storage
+    """Fused AdamW on one flat shard: reads the (fp32 or bf16) gradient shard, updates moments (any storage
     format) and the master/weight shard, and writes the bf16 compute copy in the same pass."""
     p = group.shard
     n = p.numel()
+    g = group.grad_shard
     out_bf16 = None
     if not group.sharded and group.shard is not group.full:
         out_bf16 = group.full.data           # unsharded with fp32 masters: refresh the compute copy in-kernel
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
-    call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, group.grad_shard, m.data, v.data,
-         getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, n, _KIND[m.kind],
+    call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, g, 1 if g.dtype == torch.bfloat16 else 0,
+         m.data, v.data, getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, n, _KIND[m.kind],
          float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2), stream())

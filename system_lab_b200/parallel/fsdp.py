@@ -129,16 +129,46 @@ class FlatGroup:
             self.full.data.copy_(self.shard)
 
     # ---- gradients ----------------------------------------------------------
+    def _fused_wgrad(self) -> bool:
+        """Expert groups on the kernel path: the wgrad GEMM writes straight into the flat gradient buffer."""
+        from .. import ops
+        return (self.compute_dtype == torch.bfloat16 and self.device.type == "cuda" and ops.kernel_mode() == "auto"
+                and all(getattr(p, "is_expert", False) for p in self.params))
+
     def prepare_grads(self) -> None:
+        fused = self._fused_wgrad()
         if self.grad_full is None:
-            self.grad_full = torch.zeros(self.total, dtype=self.compute_dtype, device=self.device)
+            alloc = torch.empty if fused else torch.zeros
+            self.grad_full = alloc(self.total, dtype=self.compute_dtype, device=self.device)
+            for p in self.params:
+                p.main_grad_written = False
         for p, o, shp in zip(self.params, self.offsets, self.shapes):
-            p.grad = self.grad_full[o:o + p.numel()].view(shp)
+            view = self.grad_full[o:o + p.numel()].view(shp)
+            if fused:
+                p.main_grad = view
+                p.grad = None
+            else:
+                p.grad = view
+
+    def _collect_fused_grads(self) -> None:
+        for p in self.params:
+            mg = getattr(p, "main_grad", None)
+            if mg is None:
+                continue
+            if p.grad is not None:                    # an op took the oracle path and returned a gradient
+                if p.main_grad_written:
+                    mg.add_(p.grad)
+                else:
+                    mg.copy_(p.grad)
+            elif not p.main_grad_written:
+                mg.zero_()
+            p.main_grad = None
 
     def reduce_grads(self, keep_full: bool = False) -> None:
-        """Sum ``grad_full`` over the group into this rank's fp32 ``grad_shard`` (accumulating)."""
+        """Sum ``grad_full`` over the group into this rank's ``grad_shard`` (fp32 once it accumulates)."""
         if self.grad_full is None:
             return
+        self._collect_fused_grads()
         if self.sharded:
             if self.comm is not None:
                 piece = self.comm.reduce_scatter(self.grad_full, self)
@@ -150,8 +180,10 @@ class FlatGroup:
             if self.replica_group is not None:
                 dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.replica_group)
         if self.grad_shard is None:
-            self.grad_shard = piece.float()
+            self.grad_shard = piece                    # consumed as is when there is one micro-batch
         else:
+            if self.grad_shard.dtype != torch.float32:
+                self.grad_shard = self.grad_shard.float()
             self.grad_shard.add_(piece)
         for p in self.params:
             p.grad = None

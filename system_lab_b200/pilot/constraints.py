@@ -84,6 +84,9 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
         out.append(_p("router_score_function", f"unknown score function {m.moe_router_score_function!r}"))
     if m.moe_token_dispatcher_type not in ("fused", "alltoall"):
         out.append(_p("dispatcher_type", f"unknown dispatcher {m.moe_token_dispatcher_type!r}"))
+    if m.num_experts and pr.params_dtype == "bf16" and m.moe_pad_expert_rows_to % 128:
+        out.append(_p("expert_rows_alignment", "bf16 models run the tcgen05 grouped GEMM, whose 128-row tiles need "
+                      f"moe_pad_expert_rows_to % 128 == 0 (got {m.moe_pad_expert_rows_to})"))
     # 5. dtype / numerics
     if pr.params_dtype not in ("fp32", "bf16"):
         out.append(_p("params_dtype", f"params_dtype={pr.params_dtype!r} not in (fp32, bf16)"))

@@ -87,15 +87,24 @@ class ShardedAdamW:
             return 1
         return dist.get_world_size(g.replica_group)
 
+    def _add_sumsq(self, acc: torch.Tensor, g) -> torch.Tensor:
+        """acc (1-element fp32 tensor) += sum(grad_shard^2) / replication."""
+        from .. import ops
+        if g.grad_shard is None:
+            return acc
+        if ops.use_kernels(g.grad_shard):
+            from ..ops import cuda as cops
+            cops.sumsq(g.grad_shard, 1.0 / self._replication(g), acc)
+            return acc
+        return acc + g.grad_shard.float().pow(2).sum() / self._replication(g)
+
     def global_grad_norm(self) -> torch.Tensor:
-        dev = self.engine.device
-        sq = torch.zeros((), dtype=torch.float32, device=dev)
+        sq = torch.zeros(1, dtype=torch.float32, device=self.engine.device)
         for g in self.engine.all_groups():
-            if g.grad_shard is not None:
-                sq = sq + g.grad_shard.float().pow(2).sum() / self._replication(g)
+            sq = self._add_sumsq(sq, g)
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(sq)
-        return sq.sqrt()
+        return sq.sqrt().squeeze(0)
 
     def _clip_coef(self, norm: torch.Tensor) -> torch.Tensor:
         if self.clip_grad <= 0:
@@ -116,7 +125,7 @@ class ShardedAdamW:
             m, v = self.m[g.name].load(), self.v[g.name].load()
             m = m.clone() if m is not self.m[g.name].data else m
             v = v.clone() if v is not self.v[g.name].data else v
-            ref.adamw_step(p32, g.grad_shard * coef, m, v, lr=lr, beta1=self.beta1, beta2=self.beta2,
+            ref.adamw_step(p32, g.grad_shard.float() * coef, m, v, lr=lr, beta1=self.beta1, beta2=self.beta2,
                            eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
             self.m[g.name].store(m)
             self.v[g.name].store(v)
@@ -129,7 +138,7 @@ class ShardedAdamW:
         """Call before backward when the update runs inside backward."""
         self.step_count += 1
         self._cur_lr = self.lr if lr is None else lr
-        self._sq_accum = torch.zeros((), dtype=torch.float32, device=self.engine.device)
+        self._sq_accum = torch.zeros(1, dtype=torch.float32, device=self.engine.device)
 
     def step_unit(self, unit) -> None:
         """optimizer-in-backward: update one unit as soon as its gradients are reduced.  Clipping uses
@@ -137,15 +146,14 @@ class ShardedAdamW:
         coef = self._clip_coef(self._prev_norm) if self._prev_norm is not None else \
             torch.ones((), dtype=torch.float32, device=self.engine.device)
         for g in unit.groups:
-            if g.grad_shard is not None:
-                self._sq_accum = self._sq_accum + g.grad_shard.float().pow(2).sum() / self._replication(g)
+            self._sq_accum = self._add_sumsq(self._sq_accum, g)
             self._update_group(g, coef, self._cur_lr)
 
     def end_step_in_backward(self) -> torch.Tensor:
         sq = self._sq_accum
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(sq)
-        self._prev_norm = self.last_grad_norm = sq.sqrt()
+        self._prev_norm = self.last_grad_norm = sq.sqrt().squeeze(0)
         return self.last_grad_norm
 
     def step(self, lr: float | None = None) -> torch.Tensor:
