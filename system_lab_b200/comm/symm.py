@@ -21,6 +21,7 @@ class SymmetricWorkspace:
         self.multicast_ptr = 0
         if world > 1:
             import torch.distributed._symmetric_memory as symm
+            group = group if group is not None else dist.group.WORLD
             self.buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
             self.buf.zero_()
             self.handle = symm.rendezvous(self.buf, group)
@@ -41,7 +42,9 @@ class SymmetricWorkspace:
         for s in shape:
             n *= s
         nb = n * torch.empty((), dtype=dtype).element_size()
-        return self.buf[offset:offset + nb].view(dtype).view(*shape)
+        # `.data` gives an alias with its own autograd version counter: a kernel or copy that writes one
+        # region must not invalidate tensors autograd saved from another region of the same workspace
+        return self.buf[offset:offset + nb].view(dtype).view(*shape).data
 
 
 class EmulatedWorld:

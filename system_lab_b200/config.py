@@ -89,6 +89,7 @@ class ModelConfig:
     moe_grouped_gemm: bool = True
     moe_permute_fusion: bool = True
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
+    moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
 
 
 @dataclass

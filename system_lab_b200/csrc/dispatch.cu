@@ -96,7 +96,8 @@ __global__ void moe_publish_kernel(int* __restrict__ block_hist, int n_blocks, i
 // Outputs (local memory): expert_offsets[E_local], expert_counts[E_local], send_base[E], meta[0] = rows used.
 __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me, int E, int pad, int capacity,
                                 int epoch, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
-                                int* __restrict__ send_base, int* __restrict__ meta, int* status) {
+                                int* __restrict__ send_base, int* __restrict__ meta, int* status,
+                                unsigned long long limit_ns) {
   __shared__ int total[MAX_EXPERTS];      // rows of expert e over all sources
   __shared__ int before[MAX_EXPERTS];     // rows of expert e from sources < me
   __shared__ int seg_off[MAX_EXPERTS];    // aligned offset of expert e inside its owner's buffer
@@ -106,10 +107,18 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
   __syncthreads();
   if (threadIdx.x < world) {
     const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.counts_flag) + threadIdx.x;
-    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+    if (!wait_flag_ge(flag, epoch, status, limit_ns)) ok = 0;
   }
   __syncthreads();
-  if (!ok) return;
+  if (!ok) {
+    // fail safe: an empty plan (no rows anywhere), so every later kernel of this layer does nothing
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      send_base[e] = -(1 << 30);
+      if (e < e_local) { expert_offsets[e] = 0; expert_counts[e] = 0; }
+    }
+    if (threadIdx.x == 0) meta[0] = 0;
+    return;
+  }
   const int* call = reinterpret_cast<const int*>(peers.base[me] + ws.counts_all);
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int t = 0, b = 0;
@@ -168,7 +177,7 @@ moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world
       for (int w = 0; w < warp; ++w) off += warp_hist[w][e];
       const int row = send_base[e] + off;
       if (row >= capacity || row < 0) {
-        atomicCAS(status, 0, ST_CAPACITY);
+        if (row >= capacity) atomicCAS(status, 0, ST_CAPACITY);
         pair_loc[p] = -1;
       } else {
         pair_loc[p] = ((e / e_local) << 24) | row;
@@ -188,7 +197,7 @@ moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world
 // FP8 = false: rows are copied as bf16.  FP8 = true: each 128-column block is scaled to e4m3 with an fp32
 // scale (amax / 448) written to row_scales.  `scale_in` (optional, per pair) multiplies the row first
 // (backward of a gate-weighted combine).
-template <bool FP8>
+template <bool FP8, int VPL>
 __global__ void __launch_bounds__(256)
 moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ pair_scalar,
                    const float* __restrict__ scale_in, const int* __restrict__ pair_loc, int T, int K, int H,
@@ -201,7 +210,14 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = gwarp; t < T; t += n_warps) {
+    // the token's row is read once into registers (VPL 16-byte chunks per lane) and stored K times
     const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)t * H);
+    bf16x8 regs[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) regs[i] = src[c];
+    }
     for (int k = 0; k < K; ++k) {
       const int loc = pair_loc[t * K + k];
       if (loc < 0) continue;
@@ -210,27 +226,32 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
       const float sc = scale_in ? scale_in[t * K + k] : 1.f;
       if (!FP8) {
         bf16x8* dst = reinterpret_cast<bf16x8*>(pb + ws.rows) + (size_t)row * nvec;
-        for (int c = lane; c < nvec; c += 32) {
-          bf16x8 v = src[c];
-          if (scale_in) {
-            float f[8];
-            unpack8(v, f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] *= sc;
-            v = pack8(f);
+        for (int i = 0; i < VPL; ++i) {
+          const int c = lane + 32 * i;
+          if (c < nvec) {
+            bf16x8 v = regs[i];
+            if (scale_in) {
+              float f[8];
+              unpack8(v, f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] *= sc;
+              v = pack8(f);
+            }
+            dst[c] = v;
           }
-          dst[c] = v;
         }
       } else {
         uint2* dst = reinterpret_cast<uint2*>(pb + ws.rows) + (size_t)row * nvec;
         float* sdst = reinterpret_cast<float*>(pb + ws.row_scales) + (size_t)row * (H >> 7);
         // a 128-column block is 16 consecutive vec8 chunks = 16 consecutive lanes
-        for (int c0 = 0; c0 < nvec; c0 += 32) {
-          const int c = c0 + lane;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+          const int c = lane + 32 * i;
           float f[8];
           float amax = 0.f;
           if (c < nvec) {
-            unpack8(src[c], f);
+            unpack8(regs[i], f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               f[j] *= sc;
@@ -315,21 +336,26 @@ __global__ void moe_signal_kernel(PeerTable peers, long flag_offset, int world, 
 template <int KMAX>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ pair_loc,
-                   int T, int K, int H, PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status) {
+                   int T, int K, int H, PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status,
+                   unsigned long long limit_ns) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
     const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.out_flag) + threadIdx.x;
-    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+    if (!wait_flag_ge(flag, epoch, status, limit_ns)) ok = 0;
   }
   __syncthreads();
-  if (!ok) return;
   const int warps_per_block = blockDim.x >> 5;
   const int gwarp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int n_warps = gridDim.x * warps_per_block;
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
+  if (!ok) {                                   // fail safe: defined (zero) output, error already in the status word
+    for (int t = gwarp; t < T; t += n_warps)
+      for (int c = lane; c < nvec; c += 32) reinterpret_cast<uint4*>(y + (size_t)t * H)[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
   for (int t = gwarp; t < T; t += n_warps) {
     const bf16x8* rows[KMAX];
     float w[KMAX];
@@ -367,17 +393,18 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weig
 
 // per-pair scalars pulled from the owners' out_scalars (backward of dispatch_scalars)
 __global__ void moe_combine_scalars_kernel(float* __restrict__ s, const int* __restrict__ pair_loc, int n_pairs,
-                                           PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status) {
+                                           PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status,
+                                           unsigned long long limit_ns) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
     const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.out_flag) + threadIdx.x;
-    if (!wait_flag_ge(flag, epoch, status)) ok = 0;
+    if (!wait_flag_ge(flag, epoch, status, limit_ns)) ok = 0;
   }
   __syncthreads();
-  if (!ok) return;
   for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x) {
+    if (!ok) { s[p] = 0.f; continue; }
     const int loc = pair_loc[p];
     s[p] = loc >= 0 ? reinterpret_cast<const float*>(peers.base[loc >> 24] + ws.out_scalars)[loc & 0xFFFFFF] : 0.f;
   }
@@ -386,6 +413,16 @@ __global__ void moe_combine_scalars_kernel(float* __restrict__ s, const int* __r
 }  // namespace slab
 
 using namespace slab;
+
+// How long a kernel waits for a flag another GPU sets before it gives up and reports TIMEOUT_PEER_FLAG.
+// Ranks legitimately drift apart by seconds (first-call library initialisation, stragglers), so the default
+// is generous; tests that make a wait run out on purpose pass their own short limit.
+static unsigned long long g_wait_limit_ns = 60ull * 1000000000ull;
+
+extern "C" int slab_moe_set_wait_limit_ms(long ms) {
+  g_wait_limit_ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+  return 0;
+}
 
 static PeerTable make_peers(const long* ptrs, int world) {
   PeerTable t;
@@ -425,7 +462,7 @@ extern "C" int slab_moe_plan_slots(const int* topk_idx, int n_pairs, int E, cons
   PeerTable pt = make_peers(peer_ptrs, world);
   WsLayout ws = make_layout(ws_offsets);
   moe_plan_kernel<<<1, 512, 0, st>>>(pt, ws, world, me, E, pad, capacity, epoch, expert_offsets, expert_counts,
-                                     send_base, meta, status);
+                                     send_base, meta, status, g_wait_limit_ns);
   int nb = slab_moe_count_blocks(n_pairs);
   if (nb < 1) nb = 1;
   moe_slots_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, world, block_base, send_base, capacity,
@@ -442,14 +479,22 @@ extern "C" int slab_moe_scatter(const void* x, const float* pair_scalar, const f
   PeerTable pt = make_peers(peer_ptrs, world);
   WsLayout ws = make_layout(ws_offsets);
   if (n_blocks <= 0) n_blocks = 148 * 4;
-  if (fp8)
-    moe_scatter_kernel<true><<<n_blocks, 256, 0, st>>>((const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, T, K,
-                                                       H, pt, ws, world, me, epoch, expert_offsets, expert_counts,
-                                                       e_local, pad, done_counter);
-  else
-    moe_scatter_kernel<false><<<n_blocks, 256, 0, st>>>((const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, T,
-                                                        K, H, pt, ws, world, me, epoch, expert_offsets, expert_counts,
-                                                        e_local, pad, done_counter);
+  const int vpl = (H / 8 + 31) / 32;
+#define SLAB_SCATTER(FP8, VPL)                                                                                    \
+  moe_scatter_kernel<FP8, VPL><<<n_blocks, 256, 0, st>>>((const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, \
+                                                          T, K, H, pt, ws, world, me, epoch, expert_offsets,         \
+                                                          expert_counts, e_local, pad, done_counter)
+  if (vpl > 32) return -100;                      // rows longer than 8192 columns are not covered
+  if (fp8) {
+    if (vpl <= 8) SLAB_SCATTER(true, 8);
+    else if (vpl <= 16) SLAB_SCATTER(true, 16);
+    else SLAB_SCATTER(true, 32);
+  } else {
+    if (vpl <= 8) SLAB_SCATTER(false, 8);
+    else if (vpl <= 16) SLAB_SCATTER(false, 16);
+    else SLAB_SCATTER(false, 32);
+  }
+#undef SLAB_SCATTER
   return (int)cudaGetLastError();
 }
 
@@ -458,7 +503,7 @@ extern "C" int slab_moe_wait(const long* peer_ptrs, const long* ws_offsets, int 
                              int* status, cudaStream_t st) {
   WsLayout ws = make_layout(ws_offsets);
   long off = which == 0 ? ws.data_flag : (which == 1 ? ws.out_flag : ws.counts_flag);
-  moe_wait_flags_kernel<<<1, 32, 0, st>>>(make_peers(peer_ptrs, world), off, world, me, epoch, status, SLAB_WAIT_NS);
+  moe_wait_flags_kernel<<<1, 32, 0, st>>>(make_peers(peer_ptrs, world), off, world, me, epoch, status, g_wait_limit_ns);
   return (int)cudaGetLastError();
 }
 
@@ -487,13 +532,13 @@ extern "C" int slab_moe_combine(void* y, const float* weights, const int* pair_l
   WsLayout ws = make_layout(ws_offsets);
   if (n_blocks <= 0) n_blocks = 148 * 4;
   if (K <= 2)
-    moe_combine_kernel<2><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+    moe_combine_kernel<2><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else if (K <= 4)
-    moe_combine_kernel<4><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+    moe_combine_kernel<4><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else if (K <= 8)
-    moe_combine_kernel<8><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+    moe_combine_kernel<8><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else
-    moe_combine_kernel<16><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status);
+    moe_combine_kernel<16><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   return (int)cudaGetLastError();
 }
 
@@ -505,6 +550,6 @@ extern "C" int slab_moe_combine_scalars(float* s, const int* pair_loc, int n_pai
   int nb = (n_pairs + 255) / 256;
   if (nb < 1) nb = 1;
   if (nb > 148 * 4) nb = 148 * 4;
-  moe_combine_scalars_kernel<<<nb, 256, 0, st>>>(s, pair_loc, n_pairs, pt, ws, world, me, epoch, status);
+  moe_combine_scalars_kernel<<<nb, 256, 0, st>>>(s, pair_loc, n_pairs, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   return (int)cudaGetLastError();
 }

@@ -157,8 +157,11 @@ __global__ void colsum_to_bf16_kernel(const float* __restrict__ partial, __nv_bf
 // ------------------------------------------------------------------ SwiGLU (* probs)
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// `rows_dev` (optional): device-side count of rows in use; rows beyond it are skipped (capacity-sized
+// expert buffers are mostly empty).
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ probs,
-                                  __nv_bfloat16* __restrict__ out, long rows, int F) {
+                                  __nv_bfloat16* __restrict__ out, long rows, int F, const int* __restrict__ rows_dev) {
+  if (rows_dev && *rows_dev < rows) rows = *rows_dev;
   const int fv = F >> 3;
   const long total = rows * fv;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -178,7 +181,8 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, const fl
 // One warp per row: writes d_gate | d_up into the two halves of dgu and the row sum d_probs.
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
                                   const float* __restrict__ probs, __nv_bfloat16* __restrict__ dgu,
-                                  float* __restrict__ dprobs, long rows, int F) {
+                                  float* __restrict__ dprobs, long rows, int F, const int* __restrict__ rows_dev) {
+  if (rows_dev && *rows_dev < rows) rows = *rows_dev;
   const int fv = F >> 3;
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -345,59 +349,101 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
 };
 
+// 16 consecutive elements per thread (16-byte accesses for every storage type); the 8 threads that share a
+// 128-element scale block are neighbouring lanes.  If `sq_out` is given the kernel also adds sum(g^2) of the
+// raw gradient to it (the global-norm accumulation of the optimizer-in-backward mode).
+template <typename T>
+__device__ __forceinline__ void load16(const T* base, long i, float (&f)[16]);
+template <>
+__device__ __forceinline__ void load16<float>(const float* base, long i, float (&f)[16]) {
+  const float4* p = reinterpret_cast<const float4*>(base) + 4 * i;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float4 t = p[k];
+    f[4 * k] = t.x; f[4 * k + 1] = t.y; f[4 * k + 2] = t.z; f[4 * k + 3] = t.w;
+  }
+}
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* base, long i, float (&f)[16]) {
+  const bf16x8* p = reinterpret_cast<const bf16x8*>(base) + 2 * i;
+  float a[8], b[8];
+  unpack8(p[0], a);
+  unpack8(p[1], b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { f[k] = a[k]; f[8 + k] = b[k]; }
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* base, long i, const float (&f)[16]);
+template <>
+__device__ __forceinline__ void store16<float>(float* base, long i, const float (&f)[16]) {
+  float4* p = reinterpret_cast<float4*>(base) + 4 * i;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) p[k] = make_float4(f[4 * k], f[4 * k + 1], f[4 * k + 2], f[4 * k + 3]);
+}
+template <>
+__device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* base, long i, const float (&f)[16]) {
+  bf16x8* p = reinterpret_cast<bf16x8*>(base) + 2 * i;
+  float a[8], b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { a[k] = f[k]; b[k] = f[8 + k]; }
+  p[0] = pack8(a);
+  p[1] = pack8(b);
+}
+
 template <typename P, int KIND, typename G>
-__global__ void adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_raw,
-                             void* __restrict__ v_raw, float* __restrict__ m_scale, float* __restrict__ v_scale,
-                             __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ coef, long n,
-                             AdamArgs a) {
+__global__ void __launch_bounds__(256)
+adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_raw, void* __restrict__ v_raw,
+             float* __restrict__ m_scale, float* __restrict__ v_scale, __nv_bfloat16* __restrict__ out_bf16,
+             const float* __restrict__ coef, float* __restrict__ sq_out, long n, AdamArgs a) {
+  __shared__ float red[32];
   const float c = coef ? *coef : 1.f;
-  const long nq = n >> 2;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nq; i += (long)gridDim.x * blockDim.x) {
-    const long e0 = i << 2;
-    float gv[4], mv[4], vv[4], pv[4];
-    if (sizeof(G) == 4) {
-      float4 t = reinterpret_cast<const float4*>(g)[i];
-      gv[0] = t.x * c; gv[1] = t.y * c; gv[2] = t.z * c; gv[3] = t.w * c;
-    } else {
-      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(g) + 2 * i;
-      float2 t0 = __bfloat1622float2(gp[0]), t1 = __bfloat1622float2(gp[1]);
-      gv[0] = t0.x * c; gv[1] = t0.y * c; gv[2] = t1.x * c; gv[3] = t1.y * c;
+  const long nq = n >> 4;
+  float sq = 0.f;
+  // warp-uniform trip count: lanes past the end idle through the body so the block-scale shuffles stay full-warp
+  for (long i0 = blockIdx.x * (long)blockDim.x + (threadIdx.x & ~31); i0 < nq; i0 += (long)gridDim.x * blockDim.x) {
+    const long i = i0 + (threadIdx.x & 31);
+    const bool act = i < nq;
+    if (!act && KIND != 2) continue;
+    if (!act) {                                  // nq is a multiple of 8, so whole 8-lane groups are idle together
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        __shfl_xor_sync(0xffffffffu, 0.f, o);
+        __shfl_xor_sync(0xffffffffu, 0.f, o);
+      }
+      continue;
     }
-    if (sizeof(P) == 4) {
-      float4 t = reinterpret_cast<const float4*>(p)[i];
-      pv[0] = t.x; pv[1] = t.y; pv[2] = t.z; pv[3] = t.w;
-    } else {
-      const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(p) + 2 * i;
-      float2 t0 = __bfloat1622float2(pp[0]), t1 = __bfloat1622float2(pp[1]);
-      pv[0] = t0.x; pv[1] = t0.y; pv[2] = t1.x; pv[3] = t1.y;
+    const long e0 = i << 4;
+    float gv[16], mv[16], vv[16], pv[16];
+    load16<G>(g, i, gv);
+    load16<P>(p, i, pv);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      sq += gv[j] * gv[j];
+      gv[j] *= c;
     }
     if (KIND == 0) {
-      float4 t = reinterpret_cast<const float4*>(m_raw)[i];
-      mv[0] = t.x; mv[1] = t.y; mv[2] = t.z; mv[3] = t.w;
-      t = reinterpret_cast<const float4*>(v_raw)[i];
-      vv[0] = t.x; vv[1] = t.y; vv[2] = t.z; vv[3] = t.w;
+      load16<float>(reinterpret_cast<const float*>(m_raw), i, mv);
+      load16<float>(reinterpret_cast<const float*>(v_raw), i, vv);
     } else if (KIND == 1) {
-      const __nv_bfloat162* mp = reinterpret_cast<const __nv_bfloat162*>(m_raw) + 2 * i;
-      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(v_raw) + 2 * i;
-      float2 t0 = __bfloat1622float2(mp[0]), t1 = __bfloat1622float2(mp[1]);
-      mv[0] = t0.x; mv[1] = t0.y; mv[2] = t1.x; mv[3] = t1.y;
-      t0 = __bfloat1622float2(vp[0]); t1 = __bfloat1622float2(vp[1]);
-      vv[0] = t0.x * t0.x; vv[1] = t0.y * t0.y; vv[2] = t1.x * t1.x; vv[3] = t1.y * t1.y;
+      load16<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(m_raw), i, mv);
+      load16<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(v_raw), i, vv);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) vv[j] *= vv[j];
     } else {
       const float ms = m_scale[e0 >> 7], vs = v_scale[e0 >> 7];
-      uint32_t mq = reinterpret_cast<const uint32_t*>(m_raw)[i], vq = reinterpret_cast<const uint32_t*>(v_raw)[i];
+      uint4 mq = reinterpret_cast<const uint4*>(m_raw)[i], vq = reinterpret_cast<const uint4*>(v_raw)[i];
       const __nv_fp8_e4m3* m8 = reinterpret_cast<const __nv_fp8_e4m3*>(&mq);
       const __nv_fp8_e4m3* v8 = reinterpret_cast<const __nv_fp8_e4m3*>(&vq);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 16; ++j) {
         mv[j] = float(m8[j]) * ms;
-        float s = float(v8[j]) * vs;
-        vv[j] = s * s;
+        float sv = float(v8[j]) * vs;
+        vv[j] = sv * sv;
       }
     }
     float m_amax = 0.f, v_amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 16; ++j) {
       mv[j] = a.beta1 * mv[j] + (1.f - a.beta1) * gv[j];
       vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gv[j] * gv[j];
       const float denom = sqrtf(vv[j] / a.bc2) + a.eps;
@@ -406,46 +452,43 @@ __global__ void adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* _
       m_amax = fmaxf(m_amax, fabsf(mv[j]));
       v_amax = fmaxf(v_amax, vv[j]);
     }
-    if (sizeof(P) == 4) {
-      reinterpret_cast<float4*>(p)[i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
-    } else {
-      __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(p) + 2 * i;
-      pp[0] = __floats2bfloat162_rn(pv[0], pv[1]);
-      pp[1] = __floats2bfloat162_rn(pv[2], pv[3]);
-    }
-    if (out_bf16) {
-      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(out_bf16) + 2 * i;
-      op[0] = __floats2bfloat162_rn(pv[0], pv[1]);
-      op[1] = __floats2bfloat162_rn(pv[2], pv[3]);
-    }
+    store16<P>(p, i, pv);
+    if (out_bf16) store16<__nv_bfloat16>(out_bf16, i, pv);
     if (KIND == 0) {
-      reinterpret_cast<float4*>(m_raw)[i] = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      reinterpret_cast<float4*>(v_raw)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      store16<float>(reinterpret_cast<float*>(m_raw), i, mv);
+      store16<float>(reinterpret_cast<float*>(v_raw), i, vv);
     } else if (KIND == 1) {
-      __nv_bfloat162* mp = reinterpret_cast<__nv_bfloat162*>(m_raw) + 2 * i;
-      __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(v_raw) + 2 * i;
-      mp[0] = __floats2bfloat162_rn(mv[0], mv[1]);
-      mp[1] = __floats2bfloat162_rn(mv[2], mv[3]);
-      vp[0] = __floats2bfloat162_rn(vv[0], vv[1]);
-      vp[1] = __floats2bfloat162_rn(vv[2], vv[3]);
+      store16<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(m_raw), i, mv);
+      store16<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(v_raw), i, vv);
     } else {
-      // a warp covers exactly one 128-element scale block (n is a multiple of 128, blockDim of 32)
-      m_amax = fmaxf(warp_max(m_amax), 1e-30f);
-      v_amax = fmaxf(warp_max(v_amax), 1e-30f);
-      const float mi = 448.f / m_amax, vi = 448.f / v_amax;
-      __nv_fp8_e4m3 mo[4], vo[4];
+      // 8 neighbouring lanes cover one 128-element scale block
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        mo[j] = __nv_fp8_e4m3(mv[j] * mi);
-        vo[j] = __nv_fp8_e4m3(vv[j] * vi);
+      for (int o = 4; o > 0; o >>= 1) {
+        m_amax = fmaxf(m_amax, __shfl_xor_sync(0xffffffffu, m_amax, o));
+        v_amax = fmaxf(v_amax, __shfl_xor_sync(0xffffffffu, v_amax, o));
       }
-      reinterpret_cast<uint32_t*>(m_raw)[i] = *reinterpret_cast<uint32_t*>(mo);
-      reinterpret_cast<uint32_t*>(v_raw)[i] = *reinterpret_cast<uint32_t*>(vo);
-      if ((threadIdx.x & 31) == 0) {
+      m_amax = fmaxf(m_amax, 1e-30f);
+      v_amax = fmaxf(v_amax, 1e-30f);
+      const float mi = 448.f / m_amax, vi = 448.f / v_amax;
+      uint4 mo, vo;
+      __nv_fp8_e4m3* m8 = reinterpret_cast<__nv_fp8_e4m3*>(&mo);
+      __nv_fp8_e4m3* v8 = reinterpret_cast<__nv_fp8_e4m3*>(&vo);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        m8[j] = __nv_fp8_e4m3(mv[j] * mi);
+        v8[j] = __nv_fp8_e4m3(vv[j] * vi);
+      }
+      reinterpret_cast<uint4*>(m_raw)[i] = mo;
+      reinterpret_cast<uint4*>(v_raw)[i] = vo;
+      if ((threadIdx.x & 7) == 0) {
         m_scale[e0 >> 7] = m_amax / 448.f;
         v_scale[e0 >> 7] = v_amax / 448.f;
       }
     }
+  }
+  if (sq_out) {
+    sq = block_sum(sq, red);
+    if (threadIdx.x == 0) atomicAdd(sq_out, sq);
   }
 }
 
@@ -516,20 +559,21 @@ extern "C" int slab_rmsnorm_bwd(const void* g, const void* x, const void* w, con
   return (int)cudaGetLastError();
 }
 
-extern "C" int slab_swiglu_fwd(const void* gu, const float* probs, void* out, long rows, int F, cudaStream_t st) {
+extern "C" int slab_swiglu_fwd(const void* gu, const float* probs, void* out, long rows, int F, const int* rows_dev,
+                               cudaStream_t st) {
   if (F % 8) return -100;
   if (rows == 0) return 0;
   swiglu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, probs,
-                                                                    (__nv_bfloat16*)out, rows, F);
+                                                                    (__nv_bfloat16*)out, rows, F, rows_dev);
   return (int)cudaGetLastError();
 }
 
 extern "C" int slab_swiglu_bwd(const void* dout, const void* gu, const float* probs, void* dgu, float* dprobs,
-                               long rows, int F, cudaStream_t st) {
+                               long rows, int F, const int* rows_dev, cudaStream_t st) {
   if (F % 8) return -100;
   if (rows == 0) return 0;
   swiglu_bwd_kernel<<<grid_for(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu,
-                                                               probs, (__nv_bfloat16*)dgu, dprobs, rows, F);
+                                                               probs, (__nv_bfloat16*)dgu, dprobs, rows, F, rows_dev);
   return (int)cudaGetLastError();
 }
 
@@ -572,28 +616,30 @@ extern "C" int slab_sumsq(const void* g, int g_is_bf16, long n, float scale, flo
 // state_kind: 0 fp32, 1 bf16, 2 fp8.  n must be a multiple of 128.
 template <typename P, typename G>
 static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scale, float* v_scale, void* out_bf16,
-                         const float* coef, long n, int state_kind, AdamArgs a, int grid, cudaStream_t st) {
+                         const float* coef, float* sq_out, long n, int state_kind, AdamArgs a, int grid,
+                         cudaStream_t st) {
   if (state_kind == 0)
-    adamw_kernel<P, 0, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+    adamw_kernel<P, 0, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
   else if (state_kind == 1)
-    adamw_kernel<P, 1, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+    adamw_kernel<P, 1, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
   else
-    adamw_kernel<P, 2, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, n, a);
+    adamw_kernel<P, 2, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
 }
 
 extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
-                          float* v_scale, void* out_bf16, const float* coef, long n, int state_kind, float lr,
-                          float beta1, float beta2, float eps, float wd, float bc1, float bc2, cudaStream_t st) {
+                          float* v_scale, void* out_bf16, const float* coef, float* sq_out, long n, int state_kind,
+                          float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                          cudaStream_t st) {
   if (n % 128) return -100;
   if (n == 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2};
-  int grid = grid_for(n / 4, 256);
+  int grid = grid_for(n / 16, 256);
   if (p_is_bf16) {
-    if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
-    else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
+    if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
+    else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
   } else {
-    if (g_is_bf16) launch_adamw<float, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
-    else launch_adamw<float, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, n, state_kind, a, grid, st);
+    if (g_is_bf16) launch_adamw<float, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
+    else launch_adamw<float, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
   }
   return (int)cudaGetLastError();
 }

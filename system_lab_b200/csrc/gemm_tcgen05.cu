@@ -61,6 +61,13 @@ struct TileInfo {
   int e, m_idx, n_idx, row0, ksteps;
 };
 
+// Rows of expert e that lie inside the operand (a corrupt plan must not turn into a runaway tile walk).
+__device__ __forceinline__ int seg_rows(const GemmParams& p, int e) {
+  const int off = p.seg_offsets[e], cnt = p.seg_counts[e];
+  if (off < 0 || off >= p.R || cnt <= 0) return 0;
+  return cnt < p.R - off ? cnt : p.R - off;
+}
+
 template <int MODE, int BN>
 __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmParams& p, int n_tiles, TileInfo& ti) {
   int E = p.E;
@@ -78,9 +85,9 @@ __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmPar
     ti.m_idx = local % m_tiles;
     ti.n_idx = local / m_tiles;
     ti.row0 = p.seg_offsets[e];
-    ti.ksteps = (p.seg_counts[e] + BK - 1) / BK;
+    ti.ksteps = (seg_rows(p, e) + BK - 1) / BK;
   } else {
-    int m_tiles = (p.seg_counts[e] + BM - 1) / BM;
+    int m_tiles = (seg_rows(p, e) + BM - 1) / BM;
     ti.m_idx = local % m_tiles;
     ti.n_idx = local / m_tiles;
     ti.row0 = p.seg_offsets[e] + ti.m_idx * BM;
@@ -132,7 +139,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int acc = 0;
     for (int e = 0; e < p.E; ++e) {
       prefix[e] = acc;
-      int per = (MODE == MODE_WGRAD) ? (p.N / BM) : ((p.seg_counts[e] + BM - 1) / BM);
+      int per = (MODE == MODE_WGRAD) ? (p.N / BM) : ((seg_rows(p, e) + BM - 1) / BM);
       acc += per * n_tiles;
     }
     prefix[p.E] = acc;

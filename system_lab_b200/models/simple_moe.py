@@ -194,7 +194,7 @@ class MoEFFN(nn.Module):
             out_buf = None
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 dgrad_out=out_buf)
-        act = ops.swiglu_probs(h1, pe)
+        act = ops.swiglu_probs(h1, pe, rows_dev=getattr(plan, "meta", None))
         ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 out=out_buf)
         out = d.combine_rows(plan, ye)

@@ -45,12 +45,13 @@ def compute_layout(ep: int, num_experts: int, topk: int, hidden: int, max_tokens
                    capacity_factor: float, fp8_payload: bool):
     """Capacity (rows) and the byte offsets of every workspace region; ``(capacity, offsets, nbytes)``.
 
-    Capacity is the smaller of the dropless worst case (every token of every rank picks this rank's
-    experts) and ``capacity_factor`` times the expected load, plus alignment padding per expert."""
+    ``capacity_factor <= 0`` sizes for the dropless worst case (every token of every rank picks this rank's
+    experts: nothing can overflow, whatever the router does).  A positive factor sizes for that multiple of
+    the balanced load instead; overflow is then detected by the plan kernel and reported as ``CAPACITY``."""
     e_local = num_experts // ep
     pairs = max_tokens * topk
     worst = ep * max_tokens * min(topk, e_local)
-    want = int(capacity_factor * pairs) if ep > 1 else pairs
+    want = int(capacity_factor * pairs) if (ep > 1 and capacity_factor > 0) else worst
     cap = _align(min(worst, want) + e_local * pad, pad)
     if cap >= 1 << 24:
         raise ValueError("capacity exceeds the 24-bit row field of pair_loc")
@@ -89,7 +90,7 @@ class FusedPlan:
 
 class FusedDispatcher:
     def __init__(self, mesh, num_experts: int, topk: int, hidden: int, max_tokens: int, pad_to: int = 128,
-                 device=None, dtype=torch.bfloat16, capacity_factor: float = 2.0, workspace=None,
+                 device=None, dtype=torch.bfloat16, capacity_factor: float = 0.0, workspace=None,
                  ep: int | None = None, ep_rank: int | None = None, fp8_payload: bool = False,
                  clone_outputs: bool = False):
         self.E, self.K, self.H, self.T = num_experts, topk, hidden, max_tokens

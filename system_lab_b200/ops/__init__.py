@@ -53,8 +53,10 @@ def swiglu(gate_up):
     return _cuda().swiglu(gate_up) if use_kernels(gate_up) else ref.swiglu(gate_up)
 
 
-def swiglu_probs(gate_up, probs):
-    return _cuda().swiglu_probs(gate_up, probs) if use_kernels(gate_up) else ref.swiglu_probs(gate_up, probs)
+def swiglu_probs(gate_up, probs, rows_dev=None):
+    if use_kernels(gate_up):
+        return _cuda().swiglu_probs(gate_up, probs, rows_dev)
+    return ref.swiglu_probs(gate_up, probs)
 
 
 def router_logits(x, router_weight):

@@ -21,13 +21,13 @@ _SIGS = {
     "slab_rmsnorm_fwd": "ppppppiifs",
     "slab_rmsnorm_bwd_blocks": "i",
     "slab_rmsnorm_bwd": "ppppppppiis",
-    "slab_swiglu_fwd": "ppplis",
-    "slab_swiglu_bwd": "ppppplis",
+    "slab_swiglu_fwd": "ppplips",
+    "slab_swiglu_bwd": "ppppplips",
     "slab_rope": "ppppliiillfs",
     "slab_quant_1x128": "ppplis",
     "slab_quant_128x128": "pppiiis",
     "slab_sumsq": "pilfps",
-    "slab_adamw": "pipi" + "p" * 6 + "li" + "f" * 7 + "s",
+    "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "s",
     "slab_router_topk": "ppppiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
@@ -250,37 +250,39 @@ def rope_packed(qkv, cos, sin, n_heads, d):
 # ------------------------------------------------------------------------------ SwiGLU
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gu, probs):
+    def forward(ctx, gu, probs, rows_dev):
         shp = gu.shape
         g2 = gu.reshape(-1, shp[-1]).contiguous()
         rows, f2 = g2.shape
         out = torch.empty(rows, f2 // 2, dtype=gu.dtype, device=gu.device)
-        call("slab_swiglu_fwd", g2, probs, out, rows, f2 // 2, stream())
-        ctx.save_for_backward(g2, probs)
+        call("slab_swiglu_fwd", g2, probs, out, rows, f2 // 2, rows_dev, stream())
+        ctx.save_for_backward(g2, probs, rows_dev)
         ctx.shp = shp
         return out.reshape(*shp[:-1], f2 // 2)
 
     @staticmethod
     def backward(ctx, g):
-        g2, probs = ctx.saved_tensors
+        g2, probs, rows_dev = ctx.saved_tensors
         rows, f2 = g2.shape
         gc = g.reshape(rows, f2 // 2).contiguous()
         dgu = torch.empty_like(g2)
         dp = torch.empty(rows, dtype=torch.float32, device=g.device) if probs is not None else None
-        call("slab_swiglu_bwd", gc, g2, probs, dgu, dp, rows, f2 // 2, stream())
-        return dgu.reshape(ctx.shp), dp
+        call("slab_swiglu_bwd", gc, g2, probs, dgu, dp, rows, f2 // 2, rows_dev, stream())
+        return dgu.reshape(ctx.shp), dp, None
 
 
 def swiglu(gate_up):
     if not _bf16(gate_up) or gate_up.shape[-1] % 16:
         return ref.swiglu(gate_up)
-    return _SwiGLU.apply(gate_up, None)
+    return _SwiGLU.apply(gate_up, None, None)
 
 
-def swiglu_probs(gate_up, probs):
+def swiglu_probs(gate_up, probs, rows_dev=None):
+    """``rows_dev``: optional device int32 holding the number of rows in use (rows past it are left
+    uninitialised: they are capacity slack no consumer reads)."""
     if not _bf16(gate_up) or gate_up.shape[-1] % 16:
         return ref.swiglu_probs(gate_up, probs)
-    return _SwiGLU.apply(gate_up, probs.float().contiguous())
+    return _SwiGLU.apply(gate_up, probs.float().contiguous(), rows_dev)
 
 
 # ------------------------------------------------------------------------------ router
@@ -499,7 +501,7 @@ def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
 _KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
 
 
-def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step) -> None:
+def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, sq_out=None) -> None:
     """Fused AdamW on one flat shard: reads the (fp32 or bf16) gradient shard, updates moments (any storage
     format) and the master/weight shard, and writes the bf16 compute copy in the same pass."""
     p = group.shard
@@ -511,5 +513,6 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step) 
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
     call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, g, 1 if g.dtype == torch.bfloat16 else 0,
-         m.data, v.data, getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, n, _KIND[m.kind],
+         m.data, v.data, getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, sq_out, n,
+         _KIND[m.kind],
          float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2), stream())

@@ -165,7 +165,8 @@ class Engine:
                     shared = FusedDispatcher(self.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,
-                                             clone_outputs=not self.recompute)
+                                             clone_outputs=not self.recompute,
+                                             capacity_factor=m.moe_capacity_factor)
                 layer.ffn.dispatcher = shared
             else:
                 if shared is None:

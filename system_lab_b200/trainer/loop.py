@@ -74,6 +74,8 @@ class Trainer:
         self.data = SyntheticData(cfg.model.vocab_size, cfg.model.seq_length, t.global_batch_size,
                                   t.micro_batch_size, mesh.dp_rank, mesh.dp, mesh.cp_rank, mesh.cp, t.seed,
                                   pin=self.device.type == "cuda")
+        if dist.is_initialized() and mesh.world > 1:
+            dist.barrier()                     # ranks leave construction together (peer kernels wait on each other)
         self.step = 0
         self.loss_curve: list[float] = []
         self.step_times_ms: list[float] = []

@@ -1,7 +1,7 @@
 """Sharded AdamW over the engine's flat groups, with global-norm clipping.
 
 Every flat group owns one contiguous shard, so the optimizer is a handful of large launches of the
-fused kernel (``csrc/adamw.cu``) instead of the per-parameter ``multi_tensor_apply`` tail the
+fused kernel (``csrc/elementwise.cu``) instead of the per-parameter ``multi_tensor_apply`` tail the
 reference traces show (``notes/2026-04/2026-04-22_gptoss_15_*:119-131``, 369 L2-norm launches per
 iteration in ``notes/2026-04/2026-04-21_gptoss_09_*:102-108``).  The clip coefficient stays on the
 device: no ``.item()`` in the step.
@@ -112,15 +112,23 @@ class ShardedAdamW:
         return torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0)
 
     # ---- update -----------------------------------------------------------------------
-    def _update_group(self, g, coef: torch.Tensor, lr: float) -> None:
+    def _update_group(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor | None = None) -> None:
+        """``sq_out``: also accumulate ``sum(grad^2) / replication`` of this group there (fused into the
+        kernel on the GPU path)."""
         if g.grad_shard is None:
             return
         from .. import ops
         if ops.use_kernels(g.shard):
             from ..ops import cuda as cops
+            fuse = sq_out is not None and self._replication(g) == 1
+            if sq_out is not None and not fuse:
+                self._add_sumsq(sq_out, g)
             cops.adamw_flat(g, self.m[g.name], self.v[g.name], coef, lr=lr, beta1=self.beta1, beta2=self.beta2,
-                            eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
+                            eps=self.eps, weight_decay=self.weight_decay, step=self.step_count,
+                            sq_out=sq_out if fuse else None)
         else:
+            if sq_out is not None:
+                sq_out += g.grad_shard.float().pow(2).sum() / self._replication(g)
             p32 = g.shard.float() if g.shard.dtype != torch.float32 else g.shard
             m, v = self.m[g.name].load(), self.v[g.name].load()
             m = m.clone() if m is not self.m[g.name].data else m
@@ -146,8 +154,7 @@ class ShardedAdamW:
         coef = self._clip_coef(self._prev_norm) if self._prev_norm is not None else \
             torch.ones((), dtype=torch.float32, device=self.engine.device)
         for g in unit.groups:
-            self._sq_accum = self._add_sumsq(self._sq_accum, g)
-            self._update_group(g, coef, self._cur_lr)
+            self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum)
 
     def end_step_in_backward(self) -> torch.Tensor:
         sq = self._sq_accum
