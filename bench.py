@@ -37,6 +37,8 @@ def parse():
     ap.add_argument("--seqs-per-gpu", type=int, default=2)
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
+    ap.add_argument("--balanced-routing", action="store_true",
+                    help="route by fixed random logits (load-balanced experts); recorded in config")
     ap.add_argument("--trace", default="", help="after timing, profile one more step into this Kineto trace")
     ap.add_argument("overrides", nargs="*")
     return ap.parse_args()
@@ -133,6 +135,8 @@ def main() -> int:
         ov.append(f"num_layers={args.layers}")
     if args.dispatcher:
         ov.append(f"moe_token_dispatcher_type={args.dispatcher}")
+    if args.balanced_routing:
+        ov.append("moe_router_force_load_balancing=true")
     cfg = Config.load(preset=args.preset, overrides=ov + list(args.overrides))
     plan = choose_memory_plan(cfg, n)
     cfg.validate(n)
@@ -208,6 +212,10 @@ def main() -> int:
         if rank == 0:
             os.makedirs(os.path.dirname(args.trace) or ".", exist_ok=True)
             prof.export_chrome_trace(args.trace)
+    load_ratio = None
+    if trainer._tpe_accum is not None:
+        per_rank = trainer._tpe_accum.float().reshape(trainer._tpe_accum.shape[0], mesh.ep, -1).sum(-1)
+        load_ratio = float((per_rank.max(1).values / per_rank.mean(1).clamp_min(1)).mean())
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -228,6 +236,8 @@ def main() -> int:
                        "seq_len": m.seq_length, "parallelism": f"fsdp+ep{mesh.ep}",
                        "memory_plan": plan, "recompute": cfg.precision.recompute_granularity,
                        "dispatcher": m.moe_token_dispatcher_type, "kernels": args.kernels,
+                       "routing": "forced-balanced" if m.moe_router_force_load_balancing else "learned-router",
+                       "ep_rank_load_max_over_mean": load_ratio,
                        "l2": "working set (weights + activations) is far larger than the 126 MB L2",
                        "tflops_per_gpu": value / n * trainer.flops_per_token / 1e12,
                        "final_loss": final_loss,

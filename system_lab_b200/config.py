@@ -89,6 +89,7 @@ class ModelConfig:
     moe_grouped_gemm: bool = True
     moe_permute_fusion: bool = True
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
+    moe_router_force_load_balancing: bool = False  # benchmarking aid: route by fixed random logits
     moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
 
 
@@ -272,14 +273,20 @@ def _coerce(value: Any, hint: Any, key: str) -> Any:
         if isinstance(value, bool):
             raise ConfigError(f"{key}: expected int, got bool")
         if isinstance(value, str):
-            return int(value.replace("_", ""))
+            try:
+                return int(value.replace("_", ""))
+            except ValueError:
+                raise ConfigError(f"{key}: expected int, got {value!r}") from None
         if isinstance(value, float) and value != int(value):
             raise ConfigError(f"{key}: expected int, got {value}")
         return int(value)
     if hint is float:
         if isinstance(value, bool):
             raise ConfigError(f"{key}: expected float, got bool")
-        return float(value)
+        try:
+            return float(value)
+        except (TypeError, ValueError):
+            raise ConfigError(f"{key}: expected float, got {value!r}") from None
     if hint is str:
         if value is None:
             return ""

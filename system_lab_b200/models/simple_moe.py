@@ -50,6 +50,18 @@ def seeded_normal_(t: torch.Tensor, std: float, base_seed: int, name: str) -> No
         t.copy_(torch.empty(t.shape, dtype=torch.float32, device=t.device).normal_(0.0, std, generator=g))
 
 
+_BALANCE_TABLES: dict = {}
+
+
+def _balance_table(like: torch.Tensor) -> torch.Tensor:
+    key = (tuple(like.shape), str(like.device))
+    if key not in _BALANCE_TABLES:
+        g = torch.Generator(device=like.device)
+        g.manual_seed(20240607)
+        _BALANCE_TABLES[key] = torch.rand(like.shape, generator=g, device=like.device, dtype=torch.float32)
+    return _BALANCE_TABLES[key]
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float):
         super().__init__()
@@ -174,6 +186,11 @@ class MoEFFN(nn.Module):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         logits = ops.router_logits(x2, self.router)
+        if cfg.moe_router_force_load_balancing:
+            # Random-init routers send most tokens to a few experts; for throughput measurements route by a fixed
+            # table of random logits instead (same table in forward and in the recomputed forward), keeping the
+            # router GEMM and its gradient path in the graph.
+            logits = _balance_table(logits) + (logits - logits.detach())
         w, idx, scores = ops.router_topk(logits, cfg.moe_router_topk, cfg.moe_router_score_function,
                                          self.router_bias, cfg.moe_norm_topk_prob,
                                          cfg.moe_router_topk_scaling_factor)
