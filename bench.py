@@ -105,10 +105,13 @@ def choose_memory_plan(cfg, world: int) -> dict:
         for k, v in prec.items():
             setattr(cfg.precision, k, v)
         cfg.train.optimizer_in_backward = in_bwd
-        est = estimate_memory(cfg, world)
-        last = {"name": name, "est_gb": round(est["total_bytes"] / 2**30, 1), "fits": est["fits"]}
-        if est["fits"]:
-            return last
+        for gran in ("selective", "full"):
+            cfg.precision.recompute_granularity = gran
+            est = estimate_memory(cfg, world)
+            last = {"name": name, "recompute": gran, "est_gb": round(est["total_bytes"] / 2**30, 1),
+                    "fits": est["fits"]}
+            if est["fits"]:
+                return last
     return last
 
 

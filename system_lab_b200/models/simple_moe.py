@@ -241,11 +241,20 @@ class DecoderLayer(nn.Module):
         self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
         self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense
         self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8) if self.is_moe else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size)
+        self.recompute_ffn = False        # set by the engine for recompute_granularity=selective
+
+    def _ffn_block(self, y, h):
+        return h + self.ffn(y)
 
     def forward(self, x, cos, sin):
         a = self.attn(self.attn_norm(x), cos, sin)
         y, h = ops.rmsnorm_residual(a, x, self.ffn_norm.weight, self.eps)
-        return h + self.ffn(y)
+        if self.recompute_ffn and torch.is_grad_enabled():
+            # selective recompute: attention activations are kept, the feed-forward block (for MoE layers the
+            # dispatch, both grouped GEMMs and the combine) is re-run in backward
+            from torch.utils.checkpoint import checkpoint
+            return checkpoint(self._ffn_block, y, h, use_reentrant=False)
+        return self._ffn_block(y, h)
 
 
 class Embedding(nn.Module):

@@ -102,7 +102,12 @@ class Engine:
         self.cfg, self.mesh, self.device = cfg, mesh, device
         m = cfg.model
         self.compute_dtype = _DT[cfg.precision.params_dtype]
-        self.recompute = cfg.precision.recompute_granularity == "full"
+        gran = cfg.precision.recompute_granularity
+        aux_on = m.moe_router_load_balancing_type == "aux_loss" and m.moe_aux_loss_coeff > 0
+        # selective = keep attention activations, re-run the feed-forward block in backward.  The aux loss leaves
+        # the MoE block through a side channel a nested checkpoint cannot carry, so it falls back to full.
+        self.selective = gran == "selective" and not aux_on
+        self.recompute = gran == "full" or (gran == "selective" and aux_on)
         pp = mesh.pp
         per_stage = m.num_layers // pp
         self.layer_start = mesh.pp_rank * per_stage
@@ -139,6 +144,8 @@ class Engine:
 
         self.embed_unit = add("embed", self.model.embed) if self.model.embed is not None else None
         self.layer_units = [add(f"layers.{l.layer_idx}", l) for l in self.model.layers]
+        for l in self.model.layers:
+            l.recompute_ffn = self.selective
         self.head_unit = add("head", self.model.head) if self.model.head is not None else None
         self._make_dispatchers()
 
@@ -165,7 +172,7 @@ class Engine:
                     shared = FusedDispatcher(self.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,
-                                             clone_outputs=not self.recompute,
+                                             clone_outputs=not (self.recompute or self.selective),
                                              capacity_factor=m.moe_capacity_factor)
                 layer.ffn.dispatcher = shared
             else:

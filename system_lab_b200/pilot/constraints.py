@@ -180,7 +180,14 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     if pr.recompute_granularity == "full":
         acts = layers_here * tokens * h * act_b + per_layer_full
     elif pr.recompute_granularity == "selective":
-        acts = layers_here * (tokens * h * act_b * 6 + slots * h * act_b)
+        # attention side kept per layer (x, normed x, packed qkv twice, attention output, residual, normed
+        # residual, layer output); one feed-forward block live at a time
+        if m.attention_type == "mla":
+            qkv_w = m.num_attention_heads * (2 * (m.qk_nope_head_dim + m.qk_rope_head_dim) + m.v_head_dim)
+        else:
+            qkv_w = (m.num_attention_heads + 2 * m.num_query_groups) * m.kv_channels
+        attn_keep = tokens * act_b * (7 * h + 2 * qkv_w)
+        acts = layers_here * attn_keep + per_layer_full
     else:
         acts = layers_here * per_layer_full
     logits = tokens * m.vocab_size * 4 / 4 + tokens * h * act_b * 2     # chunked cross entropy: quarter at a time

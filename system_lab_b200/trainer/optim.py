@@ -80,6 +80,8 @@ class ShardedAdamW:
         self.last_grad_norm: torch.Tensor | None = None
         self._prev_norm: torch.Tensor | None = None     # for delayed clipping in optimizer-in-backward mode
         self._sq_accum: torch.Tensor | None = None
+        self._side = None                 # side stream for in-backward updates
+        self._coef_for_step = None
 
     # ---- gradient norm ------------------------------------------------------------
     def _replication(self, g) -> int:
@@ -150,13 +152,33 @@ class ShardedAdamW:
 
     def step_unit(self, unit) -> None:
         """optimizer-in-backward: update one unit as soon as its gradients are reduced.  Clipping uses
-        the previous step's global norm (the current one is not known until backward ends)."""
-        coef = self._clip_coef(self._prev_norm) if self._prev_norm is not None else \
-            torch.ones((), dtype=torch.float32, device=self.engine.device)
-        for g in unit.groups:
-            self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum)
+        the previous step's global norm (the current one is not known until backward ends).
+
+        On the GPU the update runs on a side stream: AdamW is bound by HBM bandwidth while the next layer's
+        backward is bound by the tensor cores, so the two overlap; the step ends by joining the streams."""
+        dev = self.engine.device
+        if self._coef_for_step is None:
+            self._coef_for_step = self._clip_coef(self._prev_norm) if self._prev_norm is not None else \
+                torch.ones((), dtype=torch.float32, device=dev)
+        coef = self._coef_for_step
+        if dev.type != "cuda":
+            for g in unit.groups:
+                self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum)
+            return
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            for g in unit.groups:
+                if g.grad_shard is not None:
+                    g.grad_shard.record_stream(self._side)
+                self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum)
 
     def end_step_in_backward(self) -> torch.Tensor:
+        if self._side is not None:
+            torch.cuda.current_stream(self.engine.device).wait_stream(self._side)
+        self._coef_for_step = None
         sq = self._sq_accum
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(sq)

@@ -51,6 +51,11 @@ def test_full_recompute_matches(single_curve):
     assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
 
 
+def test_selective_recompute_matches(single_curve):
+    res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2", "recompute_granularity=selective"], 6)
+    assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+
+
 def test_dp2_ep1_fsdp_matches(single_curve):
     res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=1"], 6)
     assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
