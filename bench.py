@@ -215,6 +215,8 @@ def main() -> int:
         if rank == 0:
             os.makedirs(os.path.dirname(args.trace) or ".", exist_ok=True)
             prof.export_chrome_trace(args.trace)
+            with open(args.trace + ".cpu_ops.txt", "w") as f:
+                f.write(prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=40, max_name_column_width=60))
     load_ratio = None
     if trainer._tpe_accum is not None:
         per_rank = trainer._tpe_accum.float().reshape(trainer._tpe_accum.shape[0], mesh.ep, -1).sum(-1)

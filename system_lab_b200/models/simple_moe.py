@@ -229,6 +229,27 @@ class MoEFFN(nn.Module):
         self.router_bias += self.cfg.moe_router_bias_update_rate * torch.sign(load.mean() - load)
 
 
+class _Recompute(torch.autograd.Function):
+    """Run ``fn(*inputs)`` without keeping its graph; rebuild and back-propagate it in backward.  Parameter
+    gradients accumulate where the engine pointed them (``p.grad`` / ``main_grad`` views of the flat buffer).
+    A plain Function instead of ``torch.utils.checkpoint``: no per-tensor hooks on the hot path."""
+
+    @staticmethod
+    def forward(ctx, fn, *inputs):
+        ctx.fn = fn
+        ctx.save_for_backward(*inputs)
+        with torch.no_grad():
+            return fn(*inputs)
+
+    @staticmethod
+    def backward(ctx, g):
+        ins = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
+        with torch.enable_grad():
+            out = ctx.fn(*ins)
+        torch.autograd.backward(out, g)
+        return (None,) + tuple(t.grad for t in ins)
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, ep_rank: int, ep_size: int, fp8: bool = False,
                  cp_group=None):
@@ -252,8 +273,7 @@ class DecoderLayer(nn.Module):
         if self.recompute_ffn and torch.is_grad_enabled():
             # selective recompute: attention activations are kept, the feed-forward block (for MoE layers the
             # dispatch, both grouped GEMMs and the combine) is re-run in backward
-            from torch.utils.checkpoint import checkpoint
-            return checkpoint(self._ffn_block, y, h, use_reentrant=False)
+            return _Recompute.apply(self._ffn_block, y, h)
         return self._ffn_block(y, h)
 
 

@@ -116,7 +116,7 @@ class Orchestrator:
         fails = [r for r in state.reentry_log if r.get("stage") == state.current_stage.value]
         if fails:
             kind = fails[-1].get("kind")
-            same = sum(1 for r in state.reentry_log if r.get("kind") == kind)
+            same = state.failure_counts.get(kind, 0)
             if same >= MAX_SAME_FAILURE or kind in ("NUMERICAL",):
                 return {"name": "orchestrator_stop", "input": {"reason": "ABORT", "summary": f"{kind} x{same}"}}
         if state.current_stage == Stage.OBSERVE and state.budget_total.rounds and \
@@ -160,6 +160,7 @@ class Orchestrator:
             return self.store.apply_result(state, result)
         # failure: budget is still charged, the stage stays (retry) and the failure is logged for the guard
         kind = result.failure.kind if result.failure else "UNKNOWN"
+        state.failure_counts[kind] = state.failure_counts.get(kind, 0) + 1
         state.reentry_log.append({"stage": result.stage.value, "kind": kind, "round": state.round_id,
                                   "message": (result.failure.message if result.failure else "")[:200]})
         state.budget_used.total_tokens += int(result.cost.get("tokens_used", 0))

@@ -78,6 +78,7 @@ class OrchestratorState(BaseModel):
     stop_reason: str | None = None
     stage_history: list[dict[str, Any]] = Field(default_factory=list)
     reentry_log: list[dict[str, Any]] = Field(default_factory=list)
+    failure_counts: dict[str, int] = Field(default_factory=dict)   # per failure kind; survives trimming
 
     def budget_remaining(self) -> Budget:
         return self.budget_total.minus(self.budget_used)

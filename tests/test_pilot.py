@@ -1,0 +1,192 @@
+"""Tuner: schemas, state store, policy rules, dry-run and rule-based sessions."""
+import json
+
+import pytest
+
+from system_lab_b200.pilot import policy
+from system_lab_b200.pilot.agent.config import OrchestratorConfig
+from system_lab_b200.pilot.agent.orchestrator import Orchestrator
+from system_lab_b200.pilot.agent.schemas import (Budget, OrchestratorState, Stage, SubagentResult, SUBAGENT_STAGES,
+                                                 ORCHESTRATOR_INLINE_STAGES)
+from system_lab_b200.pilot.agent.skills import SkillLoader
+from system_lab_b200.pilot.agent.state import StateStore
+from system_lab_b200.pilot.agent.worker_tools import (ALL_TOOLS, STAGE_TOOL_MAP, ToolContext, check_env,
+                                                      handle_tool_call, tools_for_stage, write_knowledge)
+
+
+def test_schema_surface():
+    assert len(Stage) == 15 and len(ALL_TOOLS) == 13
+    assert Stage.OBSERVE.value == "OPTIMIZE_LOOP.OBSERVE"
+    assert not (SUBAGENT_STAGES & ORCHESTRATOR_INLINE_STAGES)
+    with pytest.raises(ValueError):
+        SubagentResult(stage=Stage.OBSERVE, worker_id="w", status="success", summary={"headline": "x" * 1300})
+    names = [t["name"] for t in tools_for_stage(Stage.REPLAN)]
+    assert "constraint_check" in names and "submit_run" not in names
+    assert all("return_subagent_result" in [t["name"] for t in v] for v in STAGE_TOOL_MAP.values())
+
+
+def test_state_store_checkpoint_order_trim_handoff(tmp_path):
+    st = StateStore(tmp_path / "s")
+    state = st.initial("s", Budget(gpu_h=1, rounds=2, wallclock_h=1, total_tokens=1000))
+    # several checkpoints within the same second must still resume in write order
+    for stage in (Stage.SETTLE, Stage.REPORT, Stage.OBSERVE):
+        state.current_stage = stage
+        st.checkpoint(state)
+    assert st.resume().current_stage == Stage.OBSERVE
+    state.stage_history = [{"i": i} for i in range(10)]
+    state.reentry_log = [{"i": i} for i in range(4)]
+    t = st.trim(state)
+    assert len(t.stage_history) == 3 and len(t.reentry_log) == 1
+    h = st.handoff(state, "ctx")
+    assert st.resume_from_handoff(h).session_id == "s"
+    res = SubagentResult(stage=Stage.SETTLE, worker_id="w", status="success", summary={"headline": "ok"},
+                         artifacts=[{"kind": "Champion", "ref": "r1_p0"}], cost={"tokens_used": 10, "gpu_h": 0.5},
+                         suggested_transition={"to": Stage.OBSERVE})
+    s2 = st.apply_result(state, res)
+    assert s2.champion_id == "r1_p0" and s2.round_id == 1 and s2.budget_used.gpu_h == 0.5
+    assert s2.current_stage == Stage.OBSERVE
+
+
+def test_skill_loader_placeholder_and_scope(tmp_path):
+    (tmp_path / "workflow").mkdir()
+    (tmp_path / "workflow" / "a.md").write_text("A")
+    sl = SkillLoader(tmp_path)
+    assert "PLACEHOLDER" in sl.read("missing.md")
+    txt = sl.read_scope(["workflow/*", "nothing/*"])
+    assert "### workflow/a.md" in txt and "NO MATCH" in txt
+
+
+def test_shipped_skill_pack_is_complete():
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1] / "system_lab_b200" / "pilot" / "skills"
+    for rel in ["SKILL.md", "workflow/state_machine.md", "workflow/orchestration.md", "workflow/observe.md",
+                "workflow/diagnose.md", "workflow/replan.md", "workflow/settle.md", "execution-model/SKILL.md",
+                "optimization/moe/SKILL.md", "constraints/oom.md", "env/SKILL.md", "knowledge/SKILL.md"]:
+        assert (root / rel).is_file(), rel
+
+
+def _snap(**m):
+    base = {"tps": 1000.0, "mem_peak_gb": 50.0, "has_nan": False}
+    base.update(m)
+    return {"status": "ok", "confidence_in_metrics": "high", "metrics": base}
+
+
+def test_diagnose_rule_order():
+    assert policy.diagnose(_snap())["bottleneck"] == "COMPUTE"
+    assert policy.diagnose(_snap(comm_ratio=0.3))["bottleneck"] == "COMM"
+    assert policy.diagnose(_snap(comm_ratio=0.22), multi_node=True)["bottleneck"] == "COMPUTE"
+    assert policy.diagnose(_snap(comm_ratio=0.3, bubble_ratio=0.2))["bottleneck"] == "PIPELINE"
+    assert policy.diagnose(_snap(bubble_ratio=0.2, expert_load_imbalance_pct=40))["bottleneck"] == "MOE_IMBALANCED"
+    assert policy.diagnose(_snap(expert_load_imbalance_pct=40, mem_peak_gb=170))["bottleneck"] == "MEMORY"
+    assert policy.diagnose(_snap(mem_reserved_to_alloc_ratio=1.5))["bottleneck"] == "MEMORY"
+
+
+def test_compare_loss_gates():
+    ref = [[i, 5.0 - 0.001 * i] for i in range(1, 301)]
+    good = [[i, l * 1.004] for i, l in ref]
+    bad = [[i, l * 1.05] for i, l in ref]
+    assert policy.compare_loss(good, ref)["pass"] and not policy.compare_loss(bad, ref)["pass"]
+    assert policy.compare_loss([[i, l * 1.015] for i, l in ref], ref, lite=True)["pass"]
+    assert not policy.compare_loss([[1, float("nan")]], ref)["pass"]
+    assert not policy.compare_loss(good[:50], ref)["enough_steps"]
+
+
+def test_early_stop_and_bubble_and_priority():
+    assert policy.early_stop({"completed_steps": 5, "has_nan": True}, champion_tps=1, predicted_tps=1) == "nan"
+    assert policy.early_stop({"completed_steps": 60, "tps": 80}, champion_tps=100, predicted_tps=None) \
+        == "tps_below_champion_85pct"
+    assert policy.early_stop({"completed_steps": 30, "tps": 80}, champion_tps=100, predicted_tps=None) is None
+    assert policy.early_stop({"completed_steps": 1, "mem_peak_gb": 178}, champion_tps=None, predicted_tps=None) \
+        == "oom_imminent"
+    assert policy.early_stop({"completed_steps": 1, "seconds_since_progress": 301}, champion_tps=None,
+                             predicted_tps=None) == "hang_5min"
+    assert policy.bubble_ratio(4, 8) == pytest.approx(3 / 11) and policy.bubble_ratio(1, 8) == 0
+    assert policy.priority(10, 0.8, 0.05, True, True) == pytest.approx(10 * 0.8 / 0.05 * 1.2 * 1.1)
+
+
+def test_replan_filters_and_settle():
+    g = policy.PlanGraph()
+    champ = policy.default_plan(8, mbs=2)
+    g.add(champ, "champion")
+    g.champion = champ["id"]
+    g.nodes[champ["id"]]["tps"] = 100.0
+    diag = {"bottleneck": "COMPUTE", "confidence": 0.8}
+    cands = policy.replan(champ, diag, g, check=lambda p: [], estimate_mem=lambda p: 100.0 if p["runtime"]["mbs"] > 2 else 50.0,
+                          round_id=1, top_k=3)
+    assert cands and all(c["plan"]["id"].startswith("r1_p") for c in cands)
+    cands2 = policy.replan(champ, diag, g, check=lambda p: [], estimate_mem=lambda p: 999.0, round_id=1)
+    assert cands2 == [] and g.exhausted_neighborhoods
+    for c in cands:
+        g.add(c["plan"], "pending", c["axis"])
+    res = [{"plan_id": cands[0]["plan"]["id"], "tps": 101.0, "status": "ok"}]
+    assert not policy.settle(g, res)["promoted"]                      # +1 % is below the 2 % bar
+    res = [{"plan_id": cands[0]["plan"]["id"], "tps": 110.0, "status": "ok", "correctness_ok": True}]
+    d = policy.settle(g, res)
+    assert d["promoted"] and d["hard_win"] and g.champion == cands[0]["plan"]["id"]
+    for _ in range(3):
+        d = policy.settle(g, [])
+    assert d["stop"] == "STAGNATION"
+
+
+def test_classify_failure():
+    assert policy.classify_failure(1, "torch.OutOfMemoryError: CUDA out of memory", False) == "OOM"
+    assert policy.classify_failure(1, "NumericalError: step 3: loss=nan", False) == "NUMERICAL"
+    assert policy.classify_failure(-9, "", True) == "TIMEOUT"
+    assert policy.classify_failure(1, "DeviceHang: device kernel reported TIMEOUT_PEER_FLAG", False) == "HANG"
+    assert policy.classify_failure(1, "ConfigError: ep=3", False) == "CONSTRAINT_VIOLATION"
+    assert policy.classify_failure(3, "boom", False) == "TOOL_ERROR"
+
+
+def test_env_check_and_knowledge(tmp_path):
+    assert not check_env({"NCCL_ALGO": "NVLS", "NCCL_NVLS_ENABLE": "0"})["valid"]
+    assert check_env({"NCCL_P2P_DISABLE": "1"})["warnings"]
+    k = tmp_path / "k.md"
+    rep = json.dumps({"rule": "fused dispatcher beats all_to_all at EP8", "evidence": "3.2x"})
+    assert write_knowledge(k, rep, "best")["entries"] == 1
+    write_knowledge(k, rep, "best")
+    write_knowledge(k, rep, "best")
+    txt = k.read_text()
+    assert "reproductions: 3" in txt and "confidence: high" in txt and txt.count("## ") == 1
+
+
+def test_constraint_tools_through_handlers(tmp_path):
+    st = StateStore(tmp_path / "s")
+    ctx = ToolContext(st, None, "qwen3-30b-a3b", [], world=8)
+    plan = policy.default_plan(8, mbs=2, gbs=16)
+    ref = st.write_artifact("Plan", "p.json", json.dumps(plan)).ref
+    assert handle_tool_call("constraint_check", {"plan_ref": ref}, ctx)["valid"]
+    mem = handle_tool_call("constraint_estimate_mem", {"plan_ref": ref}, ctx)
+    assert mem["fits"] and 40 < mem["mem_gb"] < 120
+    plan["parallelism"]["ep"] = 3
+    ref2 = st.write_artifact("Plan", "p2.json", json.dumps(plan)).ref
+    assert not handle_tool_call("constraint_check", {"plan_ref": ref2}, ctx)["valid"]
+
+
+def test_dry_run_session_walks_state_machine(tmp_path):
+    cfg = OrchestratorConfig("d", tmp_path / "d", tmp_path / "skills", Budget(gpu_h=1, rounds=2, wallclock_h=1,
+                                                                               total_tokens=10**6), dry_run=True)
+    orch = Orchestrator(cfg)
+    state = orch.run()
+    assert state.current_stage == Stage.REPORT and state.stop_reason == "BUDGET_EXCEEDED" and state.round_id == 2
+    files = sorted((tmp_path / "d" / "checkpoints").glob("s*.json"))
+    assert len(files) == 18
+    stages = [f.name.split("_", 2)[2].rsplit("_", 1)[0] for f in files]
+    assert stages[:5] == ["PROJECTION", "SMOKE", "BASELINE", "CORRECTNESS", "OBSERVE"] and stages[-1] == "REPORT"
+    # resuming a finished session is a no-op that stays terminal
+    assert Orchestrator(cfg).run().is_terminal()
+
+
+def test_failed_worker_aborts_after_three_same_failures(tmp_path):
+    cfg = OrchestratorConfig("f", tmp_path / "f", tmp_path / "skills", Budget(gpu_h=1, rounds=2, wallclock_h=1,
+                                                                               total_tokens=10**6), backend="rules")
+    orch = Orchestrator(cfg)             # no runner: every job-submitting stage fails with TOOL_ERROR
+
+    class _Broken:
+        def run(self, req):
+            from system_lab_b200.pilot.agent.subagent import _failed
+            return _failed(req.stage, "w", "TOOL_ERROR", "injected")
+    orch.worker = _Broken()
+    state = orch.run()
+    assert state.current_stage == Stage.ABORT and state.stop_reason == "ABORT"
+    assert len([r for r in json.loads((sorted((tmp_path / "f" / "checkpoints").glob("s*.json"))[-1]).read_text())
+                ["reentry_log"]]) >= 1
