@@ -63,6 +63,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=2048)
     ap.add_argument("--zipf", action="store_true")
     ap.add_argument("--baseline", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="also time the block-scaled fp8 forward kernels")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default="")
     ap.add_argument("--only", default="", help="run a single op, e.g. 'fc1 fwd' (for profiler captures)")
@@ -120,6 +121,18 @@ def main():
         rec("forward (fc1+fc2)", fwd_ms, fl1 + fl2)
         rec("forward+backward", all_ms, 3 * (fl1 + fl2))
     cops.check_status()
+    if args.fp8:
+        xq, xs = cops.quant_1x128(x)
+        aq, as_ = cops.quant_1x128(act)
+        w1q, w1s = cops.quant_128x128(w1)
+        w2q, w2s = cops.quant_128x128(w2)
+        rec("fc1_fwd_fp8", time_cuda(lambda: cops.grouped_gemm_fp8_raw(xq, xs, w1q, w1s, off_d, cnt_d), args.iters,
+                                     flush=flush, name="fc1_fwd_fp8"), fl1)
+        rec("fc2_fwd_fp8", time_cuda(lambda: cops.grouped_gemm_fp8_raw(aq, as_, w2q, w2s, off_d, cnt_d), args.iters,
+                                     flush=flush, name="fc2_fwd_fp8"), fl2)
+        rec("quant_1x128 x", time_cuda(lambda: cops.quant_1x128(x), args.iters, flush=flush, name="quant_x"), 0.0)
+        rec("quant_128x128 w1", time_cuda(lambda: cops.quant_128x128(w1), args.iters, flush=flush, name="quant_w1"), 0.0)
+        cops.check_status()
     if args.baseline and not args.only:
         cl = counts.tolist()
         ol = offsets.tolist()

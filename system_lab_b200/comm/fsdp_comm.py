@@ -1,0 +1,106 @@
+"""Peer-memory FSDP collectives (kernels in ``csrc/fsdp_comm.cu``): parameter all-gather and gradient
+reduce-scatter (+ cast, optionally + sharded AdamW) that pull slices straight from the peers' staging
+slots over NVLink instead of calling NCCL.
+
+One :class:`FsdpPeerComm` per shard group.  Its symmetric workspace holds ``NSLOT`` staging slots used in
+rotation; a slot is reused only after every peer acknowledged reading its previous content, so a fast
+rank can run at most ``NSLOT`` collectives ahead of the slowest.  The workspace grows (collectively) the
+first time a larger operand shows up.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import cuda as cops
+from .symm import SymmetricWorkspace
+
+NSLOT = 4
+_MAXW = 16
+
+for _name, _sig in {
+    "slab_fsdp_stage": "plppiiiiipps",
+    "slab_fsdp_all_gather": "plppiiiipps",
+    "slab_fsdp_reduce_scatter": "plppiiiifpps",
+    "slab_fsdp_reduce_scatter_adamw": "lppiiiif" + "ppppp" + "p" + "fffffff" + "pps",
+    "slab_fsdp_set_wait_limit_ms": "l",
+}.items():
+    cops.register(_name, _sig)
+
+
+class FsdpPeerComm:
+    def __init__(self, group, world: int, rank: int, device: torch.device, workspace_factory=None):
+        self.group, self.world, self.rank, self.device = group, world, rank, device
+        self.ws = None
+        self.slot_bytes = 0
+        self.epoch = 0
+        self.slot_last = [0] * NSLOT
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = cops.status_word(device)
+        self._factory = workspace_factory or (lambda nbytes: SymmetricWorkspace(nbytes, group, world, rank, device))
+
+    def _ensure(self, nbytes: int) -> None:
+        if self.ws is not None and nbytes <= self.slot_bytes:
+            return
+        self.slot_bytes = (max(nbytes, 1 << 20) + 255) // 256 * 256
+        self.ws = self._factory(4096 + NSLOT * self.slot_bytes)
+        self._ptrs = (ctypes.c_long * _MAXW)(*(list(self.ws.ptrs) + [0] * (_MAXW - len(self.ws.ptrs))))
+        self._lay = (ctypes.c_long * 4)(0, 1024, 4096, self.slot_bytes)
+        self.slot_last = [0] * NSLOT
+
+    def _next(self):
+        self.epoch += 1
+        slot = self.epoch % NSLOT
+        ack = self.slot_last[slot]
+        self.slot_last[slot] = self.epoch
+        return slot, self.epoch, ack
+
+    def _stage(self, src: torch.Tensor, slot: int, ep: int, ack: int) -> None:
+        cops.call("slab_fsdp_stage", src, src.numel() * src.element_size(), ctypes.addressof(self._ptrs),
+                  ctypes.addressof(self._lay), self.world, self.rank, slot, ep, ack, self.status, self.done,
+                  cops.stream())
+
+    # ---- the FlatGroup interface --------------------------------------------------------------------
+    def all_gather(self, dst: torch.Tensor, src: torch.Tensor, fg=None) -> None:
+        src = src.contiguous()
+        nbytes = src.numel() * src.element_size()
+        self._ensure(nbytes)
+        slot, ep, ack = self._next()
+        self._stage(src, slot, ep, ack)
+        cops.call("slab_fsdp_all_gather", dst, nbytes, ctypes.addressof(self._ptrs), ctypes.addressof(self._lay),
+                  self.world, self.rank, slot, ep, self.status, self.done, cops.stream())
+
+    def reduce_scatter(self, grad_full: torch.Tensor, fg=None, scale: float = 1.0) -> torch.Tensor:
+        """bf16 ``grad_full`` (``world * shard`` elements) -> fp32 sum of every rank's slice ``rank``."""
+        if grad_full.dtype != torch.bfloat16:
+            raise ValueError("peer reduce-scatter takes bf16 gradients")
+        shard = grad_full.numel() // self.world
+        self._ensure(grad_full.numel() * 2)
+        slot, ep, ack = self._next()
+        self._stage(grad_full, slot, ep, ack)
+        piece = torch.empty(shard, dtype=torch.float32, device=self.device)
+        cops.call("slab_fsdp_reduce_scatter", piece, shard, ctypes.addressof(self._ptrs), ctypes.addressof(self._lay),
+                  self.world, self.rank, slot, ep, float(scale), self.status, self.done, cops.stream())
+        return piece
+
+    def reduce_scatter_adamw(self, grad_full, master, m, v, out_bf16, coef, sq_out, *, lr, beta1, beta2, eps,
+                             weight_decay, step, scale: float = 1.0) -> None:
+        """Reduce-scatter fused with the AdamW update of this rank's fp32 master shard and moments."""
+        shard = grad_full.numel() // self.world
+        self._ensure(grad_full.numel() * 2)
+        slot, ep, ack = self._next()
+        self._stage(grad_full, slot, ep, ack)
+        cops.call("slab_fsdp_reduce_scatter_adamw", shard, ctypes.addressof(self._ptrs), ctypes.addressof(self._lay),
+                  self.world, self.rank, slot, ep, float(scale), master, m, v, out_bf16, coef, sq_out, float(lr),
+                  float(beta1), float(beta2), float(eps), float(weight_decay), float(1 - beta1 ** step),
+                  float(1 - beta2 ** step), self.status, self.done, cops.stream())
+
+
+def make_fsdp_comms(mesh, device):
+    """(dense_comm, expert_comm) for the engine; ``None`` where the group has a single rank."""
+    dense = FsdpPeerComm(mesh.data_group, mesh.data_size, mesh.data_rank, device) if mesh.data_size > 1 else None
+    expert = None
+    if mesh.edp > 1:
+        expert = FsdpPeerComm(mesh.edp_group, mesh.edp, mesh.edp_rank * mesh.cp + mesh.cp_rank, device)
+    return dense, expert

@@ -1,0 +1,255 @@
+// FSDP collectives over NVLink peer memory: parameter all-gather and gradient reduce-scatter (with the
+// bf16 -> fp32 cast and, optionally, the sharded AdamW update in the same pass).
+//
+// Each rank owns a symmetric workspace with NSLOT staging slots.  A collective is two launches:
+//   stage  : wait until every peer has acknowledged the previous use of the slot (flags of an older call),
+//            copy the local operand into the slot, fence, release a per-source "ready" flag on every peer;
+//   gather : wait for every source's flag, then pull the peers' slices with 16-byte loads straight into the
+//            destination (all-gather) or sum them in fp32 (reduce-scatter); the last block acknowledges the
+//            slot to every peer.
+// No kernel waits on a flag of its own call that it also sets, so ranks can be emulated phase by phase on
+// one GPU.  Waits are bounded (common.cuh) and fail safe: on a timeout the output is left untouched
+// (all-gather) or zero (reduce-scatter) and the status word carries the error.
+//
+// Reference analogues: per-bucket `reduce_scatter_tensor` / `all_gather_into_tensor` of the distributed
+// optimizer (notes/2026-04/2026-04-22_gptoss_12_*:38-56), in-collective averaging (:98-108), the in-place P2P
+// reduction sketched in moe/research_direction_C.md:236-257, and the multi_tensor Adam tail
+// (notes/2026-04/2026-04-22_gptoss_15_*:119-131).
+#include "common.cuh"
+
+namespace slab {
+
+constexpr int FS_MAX_WORLD = 16;
+
+struct FsPeers {
+  uint8_t* base[FS_MAX_WORLD];
+};
+
+// workspace layout (bytes): [0,256) ready flags (int[world]) per slot at slot*1024; acks at 512 + ...
+struct FsLayout {
+  long ready_flags;   // int [NSLOT][FS_MAX_WORLD]
+  long ack_flags;     // int [NSLOT][FS_MAX_WORLD]
+  long slots;         // byte offset of slot 0
+  long slot_bytes;
+};
+
+__global__ void __launch_bounds__(512)
+fsdp_stage_kernel(const uint4* __restrict__ src, long n16, FsPeers peers, FsLayout lay, int world, int me, int slot,
+                  int epoch, int ack_epoch, int* status, unsigned long long limit_ns, int* done_counter) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (ack_epoch > 0 && threadIdx.x < world) {
+    const int* ack = reinterpret_cast<const int*>(peers.base[me] + lay.ack_flags) + slot * FS_MAX_WORLD + threadIdx.x;
+    if (!wait_flag_ge(ack, ack_epoch, status, limit_ns)) ok = 0;
+  }
+  __syncthreads();
+  if (ok) {
+    uint4* dst = reinterpret_cast<uint4*>(peers.base[me] + lay.slots + slot * lay.slot_bytes);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n16; i += (long)gridDim.x * blockDim.x) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) is_last = (atomicAdd(done_counter, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (is_last) {
+    __threadfence_system();
+    if (threadIdx.x < world) {
+      int* flag = reinterpret_cast<int*>(peers.base[threadIdx.x] + lay.ready_flags) + slot * FS_MAX_WORLD + me;
+      st_release_sys(flag, epoch);
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+__device__ __forceinline__ bool fs_wait_ready(const FsPeers& peers, const FsLayout& lay, int world, int me, int slot,
+                                              int epoch, int* status, unsigned long long limit_ns, int* ok_smem) {
+  if (threadIdx.x == 0) *ok_smem = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + lay.ready_flags) + slot * FS_MAX_WORLD + threadIdx.x;
+    if (!wait_flag_ge(flag, epoch, status, limit_ns)) *ok_smem = 0;
+  }
+  __syncthreads();
+  return *ok_smem != 0;
+}
+
+__device__ __forceinline__ void fs_ack(const FsPeers& peers, const FsLayout& lay, int world, int me, int slot,
+                                       int epoch, int* done_counter) {
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) is_last = (atomicAdd(done_counter, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (is_last) {
+    if (threadIdx.x < world) {
+      int* ack = reinterpret_cast<int*>(peers.base[threadIdx.x] + lay.ack_flags) + slot * FS_MAX_WORLD + me;
+      st_release_sys(ack, epoch);
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+// dst[r * n16 + i] = peer r's staged shard[i]
+__global__ void __launch_bounds__(512)
+fsdp_gather_kernel(uint4* __restrict__ dst, long n16, FsPeers peers, FsLayout lay, int world, int me, int slot,
+                   int epoch, int* status, unsigned long long limit_ns, int* done_counter) {
+  __shared__ int ok;
+  if (fs_wait_ready(peers, lay, world, me, slot, epoch, status, limit_ns, &ok)) {
+    const long total = n16 * world;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+      const int r = int(i / n16);
+      const long j = i - r * n16;
+      dst[i] = reinterpret_cast<const uint4*>(peers.base[r] + lay.slots + slot * lay.slot_bytes)[j];
+    }
+  }
+  fs_ack(peers, lay, world, me, slot, epoch, done_counter);
+}
+
+struct FsAdam {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;
+};
+
+// piece[i] = scale * sum_r peer r's staged grad[me * n8 * 8 + i]  (bf16 in, fp32 accumulate).
+// FUSE_ADAM: instead of writing the reduced gradient, apply AdamW to the fp32 master shard / fp32 moments and
+// write the bf16 compute copy; sum(g^2) goes to sq_out.
+template <bool FUSE_ADAM>
+__global__ void __launch_bounds__(512)
+fsdp_reduce_scatter_kernel(float* __restrict__ piece, long n8, FsPeers peers, FsLayout lay, int world, int me, int slot,
+                           int epoch, float scale, float* __restrict__ master, float* __restrict__ m,
+                           float* __restrict__ v, __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ coef,
+                           float* __restrict__ sq_out, FsAdam a, int* status, unsigned long long limit_ns,
+                           int* done_counter) {
+  __shared__ int ok;
+  __shared__ float red[32];
+  const bool good = fs_wait_ready(peers, lay, world, me, slot, epoch, status, limit_ns, &ok);
+  float sq = 0.f;
+  const float c = (FUSE_ADAM && coef) ? *coef : 1.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (good) {
+      for (int r = 0; r < world; ++r) {
+        const bf16x8* src = reinterpret_cast<const bf16x8*>(peers.base[r] + lay.slots + slot * lay.slot_bytes) + (long)me * n8 + i;
+        float f[8];
+        unpack8(*src, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= scale;
+    if (!FUSE_ADAM) {
+      float4* o = reinterpret_cast<float4*>(piece) + 2 * i;
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else if (good) {
+      float4* pm = reinterpret_cast<float4*>(master) + 2 * i;
+      float4* mm = reinterpret_cast<float4*>(m) + 2 * i;
+      float4* vm = reinterpret_cast<float4*>(v) + 2 * i;
+      float p8[8], m8[8], v8[8];
+      *reinterpret_cast<float4*>(p8) = pm[0]; *reinterpret_cast<float4*>(p8 + 4) = pm[1];
+      *reinterpret_cast<float4*>(m8) = mm[0]; *reinterpret_cast<float4*>(m8 + 4) = mm[1];
+      *reinterpret_cast<float4*>(v8) = vm[0]; *reinterpret_cast<float4*>(v8 + 4) = vm[1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        sq += acc[j] * acc[j];
+        const float g = acc[j] * c;
+        m8[j] = a.beta1 * m8[j] + (1.f - a.beta1) * g;
+        v8[j] = a.beta2 * v8[j] + (1.f - a.beta2) * g * g;
+        p8[j] = p8[j] * (1.f - a.lr * a.wd) - a.lr * (m8[j] / a.bc1) / (sqrtf(v8[j] / a.bc2) + a.eps);
+      }
+      pm[0] = *reinterpret_cast<float4*>(p8); pm[1] = *reinterpret_cast<float4*>(p8 + 4);
+      mm[0] = *reinterpret_cast<float4*>(m8); mm[1] = *reinterpret_cast<float4*>(m8 + 4);
+      vm[0] = *reinterpret_cast<float4*>(v8); vm[1] = *reinterpret_cast<float4*>(v8 + 4);
+      reinterpret_cast<bf16x8*>(out_bf16)[i] = pack8(p8);
+    }
+  }
+  if (FUSE_ADAM && sq_out) {
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+      atomicAdd(sq_out, t);
+    }
+  }
+  fs_ack(peers, lay, world, me, slot, epoch, done_counter);
+}
+
+}  // namespace slab
+
+using namespace slab;
+
+static unsigned long long g_fs_limit_ns = 60ull * 1000000000ull;
+
+extern "C" int slab_fsdp_set_wait_limit_ms(long ms) {
+  g_fs_limit_ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+  return 0;
+}
+
+static FsPeers fs_peers(const long* ptrs, int world) {
+  FsPeers p;
+  for (int i = 0; i < FS_MAX_WORLD; ++i) p.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
+  return p;
+}
+static FsLayout fs_layout(const long* o) {
+  FsLayout l;
+  l.ready_flags = o[0]; l.ack_flags = o[1]; l.slots = o[2]; l.slot_bytes = o[3];
+  return l;
+}
+static int fs_grid(long items) {
+  long b = (items + 511) / 512;
+  return (int)(b < 1 ? 1 : (b > 296 ? 296 : b));
+}
+
+// Copy `nbytes` (multiple of 16) from src into this rank's staging slot and publish it.  `ack_epoch` is the
+// epoch of the previous call that used this slot (0: none).
+extern "C" int slab_fsdp_stage(const void* src, long nbytes, const long* peer_ptrs, const long* layout, int world,
+                               int me, int slot, int epoch, int ack_epoch, int* status, int* done_counter,
+                               cudaStream_t st) {
+  if (nbytes % 16 || world > FS_MAX_WORLD) return -100;
+  FsLayout l = fs_layout(layout);
+  if (nbytes > l.slot_bytes) return -101;
+  fsdp_stage_kernel<<<fs_grid(nbytes / 16), 512, 0, st>>>((const uint4*)src, nbytes / 16, fs_peers(peer_ptrs, world), l,
+                                                          world, me, slot, epoch, ack_epoch, status, g_fs_limit_ns,
+                                                          done_counter);
+  return (int)cudaGetLastError();
+}
+
+// dst (world * shard_bytes) <- every peer's staged shard
+extern "C" int slab_fsdp_all_gather(void* dst, long shard_bytes, const long* peer_ptrs, const long* layout, int world,
+                                    int me, int slot, int epoch, int* status, int* done_counter, cudaStream_t st) {
+  if (shard_bytes % 16 || world > FS_MAX_WORLD) return -100;
+  fsdp_gather_kernel<<<fs_grid(shard_bytes / 16 * world), 512, 0, st>>>((uint4*)dst, shard_bytes / 16,
+                                                                        fs_peers(peer_ptrs, world), fs_layout(layout),
+                                                                        world, me, slot, epoch, status, g_fs_limit_ns,
+                                                                        done_counter);
+  return (int)cudaGetLastError();
+}
+
+// piece (fp32, shard_numel) <- scale * sum over peers of their staged bf16 gradient slice `me`.
+extern "C" int slab_fsdp_reduce_scatter(float* piece, long shard_numel, const long* peer_ptrs, const long* layout,
+                                        int world, int me, int slot, int epoch, float scale, int* status,
+                                        int* done_counter, cudaStream_t st) {
+  if (shard_numel % 8 || world > FS_MAX_WORLD) return -100;
+  FsAdam a{};
+  fsdp_reduce_scatter_kernel<false><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
+      piece, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, nullptr,
+      nullptr, nullptr, nullptr, nullptr, nullptr, a, status, g_fs_limit_ns, done_counter);
+  return (int)cudaGetLastError();
+}
+
+// Reduce-scatter fused with the sharded AdamW step (fp32 master / moments, bf16 compute copy out).
+extern "C" int slab_fsdp_reduce_scatter_adamw(long shard_numel, const long* peer_ptrs, const long* layout, int world,
+                                              int me, int slot, int epoch, float scale, float* master, float* m,
+                                              float* v, void* out_bf16, const float* coef, float* sq_out, float lr,
+                                              float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                                              int* status, int* done_counter, cudaStream_t st) {
+  if (shard_numel % 8 || world > FS_MAX_WORLD) return -100;
+  FsAdam a{lr, beta1, beta2, eps, wd, bc1, bc2};
+  fsdp_reduce_scatter_kernel<true><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
+      nullptr, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, master,
+      m, v, (__nv_bfloat16*)out_bf16, coef, sq_out, a, status, g_fs_limit_ns, done_counter);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,294 @@
+// Block-scaled fp8 (e4m3) grouped expert GEMM, forward:  C[r, n] = sum_k A[r, k] * B[e, n, k]  with
+//   A: [R, K] e4m3, scales sa [R, K/128] fp32 (1x128 blocks along K, as written by the fused dispatch or the
+//      quantising SwiGLU), B: [E, N, K] e4m3, scales sb [E, N/128, K/128] fp32 (128x128 blocks), C bf16.
+//
+// tcgen05.mma kind::f8f6f4 (128x128x32 per instruction) accumulates one 128-wide K block into a TMEM buffer;
+// because the scale changes every K block the partial sum is promoted outside the tensor core: the four
+// epilogue warps read the 128x128 fp32 partial with tcgen05.ld, multiply by sa[row, kb] * sb[e, nb, kb] and
+// add into register accumulators while the MMA warp already fills the next TMEM buffer (4 buffers of 128
+// columns).  Operands arrive by TMA (128-byte swizzle: one 128-element fp8 row per swizzle row), 6 stages,
+// no cluster multicast.  The output goes through swizzled shared staging and a TMA store.
+//
+// Reference analogues: the fused fp8 grouped GEMM with dequantising epilogue (`acc *= sa*sb`,
+// summary/fp8_expert_gemm_optimization.md:84-116) and the blockwise recipe that was the slowest variant there
+// (notes/2026-04/2026-04-21_gptoss_10_moe_fp8_grouped_gemm_diagnosis.md:74-85).
+#include "common.cuh"
+
+namespace slab {
+
+constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128, F8_UK = 32, F8_STAGES = 6, F8_TBUF = 4;
+constexpr int F8_THREADS = 192;
+constexpr int F8_CTRL = 3072, F8_PREFIX_OFF = 256;
+constexpr int F8_A_BYTES = F8_BM * F8_BK, F8_B_BYTES = F8_BN * F8_BK, F8_STAGE = F8_A_BYTES + F8_B_BYTES;
+constexpr int F8_STORE_OFF = F8_CTRL + F8_STAGES * F8_STAGE;
+constexpr int F8_STORE_BYTES = F8_BM * 64 * 2;
+constexpr int F8_SMEM = F8_STORE_OFF + 2 * F8_STORE_BYTES;
+static_assert(F8_SMEM <= 232448, "shared memory budget");
+
+struct Fp8Params {
+  const int* seg_offsets;
+  const int* seg_counts;
+  const float* sa;       // [R, K/128]
+  const float* sb;       // [E, N/128, K/128]
+  int E, R, N, K;
+  int* status;
+};
+
+__device__ __forceinline__ int f8_seg_rows(const Fp8Params& p, int e) {
+  const int off = p.seg_offsets[e], cnt = p.seg_counts[e];
+  if (off < 0 || off >= p.R || cnt <= 0) return 0;
+  return cnt < p.R - off ? cnt : p.R - off;
+}
+
+struct F8Tile {
+  int e, m_idx, n_idx, row0;
+};
+
+__device__ __forceinline__ bool f8_get_tile(int t, const int* prefix, const Fp8Params& p, F8Tile& ti) {
+  if (t >= prefix[p.E]) return false;
+  int lo = 0, hi = p.E;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int local = t - prefix[lo];
+  const int m_tiles = (f8_seg_rows(p, lo) + F8_BM - 1) / F8_BM;
+  ti.e = lo;
+  ti.m_idx = local % m_tiles;
+  ti.n_idx = local / m_tiles;
+  ti.row0 = p.seg_offsets[lo] + ti.m_idx * F8_BM;
+  return true;
+}
+
+__global__ void __launch_bounds__(F8_THREADS, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, const Fp8Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_INDEX);
+    return;
+  }
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty_bar = full_bar + F8_STAGES;
+  uint64_t* tfull_bar = empty_bar + F8_STAGES;
+  uint64_t* tempty_bar = tfull_bar + F8_TBUF;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + F8_TBUF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* prefix = reinterpret_cast<int*>(smem + F8_PREFIX_OFF);
+  uint8_t* ring = smem + F8_CTRL;
+  uint8_t* store_buf = smem + F8_STORE_OFF;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (p.N + F8_BN - 1) / F8_BN;
+  const int kblocks = p.K / F8_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F8_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < F8_TBUF; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      prefix[e] = acc;
+      acc += ((f8_seg_rows(p, e) + F8_BM - 1) / F8_BM) * n_tiles;
+    }
+    prefix[p.E] = acc;
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, F8_TBUF * F8_BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {                                   // ---------------- TMA producer
+      int s = 0;
+      uint32_t ph = 0;
+      F8Tile ti;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && f8_get_tile(t, prefix, p, ti); t += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a_dst = ring + s * F8_STAGE;
+          mbar_arrive_expect_tx(&full_bar[s], F8_STAGE);
+          tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * F8_BK, ti.row0);
+          tma_load_2d(a_dst + F8_A_BYTES, &tmap_b, &full_bar[s], kb * F8_BK, ti.e * p.N + ti.n_idx * F8_BN);
+          if (++s == F8_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                                   // ---------------- MMA issuer: one TMEM buffer per K block
+      constexpr uint32_t idesc = make_idesc(0, 0, 0, 0, F8_BM, F8_BN);     // e4m3 x e4m3, K-major both
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t it = 0;                                 // K blocks issued so far (selects the TMEM buffer)
+      F8Tile ti;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && f8_get_tile(t, prefix, p, ti); t += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t buf = it % F8_TBUF;
+          if (!mbar_wait(&tempty_bar[buf], ((it / F8_TBUF) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(ring + s * F8_STAGE);
+          const uint32_t b_addr = a_addr + F8_A_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < F8_BK / F8_UK; ++k4) {
+            const uint64_t adesc = make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+            const uint64_t bdesc = make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+            umma_f8(tmem_base + buf * F8_BN, adesc, bdesc, idesc, k4 != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+          umma_commit(&tfull_bar[buf]);
+          if (++s == F8_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: promote every K block with its scales, then store the tile
+    const int lg = warp & 3;
+    const bool store_thread = (warp == 2 && lane == 0);
+    const int r_in_tile = lg * 32 + lane;
+    const int sa_ld = kblocks;
+    const int nb_total = p.N / 128;
+    uint32_t it = 0;
+    int chunk_ctr = 0;
+    F8Tile ti;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && f8_get_tile(t, prefix, p, ti); t += gridDim.x) {
+      float acc[F8_BN];
+#pragma unroll
+      for (int i = 0; i < F8_BN; ++i) acc[i] = 0.f;
+      const int row = ti.row0 + r_in_tile;
+      const float* sa_row = p.sa + (size_t)(row < p.R ? row : 0) * sa_ld;
+      const float* sb_row = p.sb + ((size_t)ti.e * nb_total + ti.n_idx) * kblocks;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const uint32_t buf = it % F8_TBUF;
+        const float sc = (row < p.R ? __ldg(sa_row + kb) : 0.f) * __ldg(sb_row + kb);
+        if (!mbar_wait(&tfull_bar[buf], (it / F8_TBUF) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * F8_BN;
+#pragma unroll
+        for (int c = 0; c < F8_BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc, acc[c + i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      }
+      if (!ok) break;
+      const int col0 = ti.n_idx * F8_BN;
+#pragma unroll
+      for (int c = 0; c < F8_BN; c += 64) {
+        uint8_t* sb = store_buf + (chunk_ctr & 1) * F8_STORE_BYTES;
+        if (store_thread) tma_store_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = acc[c + g * 8 + i];
+          *reinterpret_cast<bf16x8*>(sb + r_in_tile * 128 + ((g ^ (r_in_tile & 7)) << 4)) = pack8(f);
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (store_thread) {
+          tma_store_2d(&tmap_c, sb, col0 + c, ti.row0);
+          tma_store_commit();
+        }
+        ++chunk_ctr;
+      }
+    }
+    if (store_thread) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, F8_TBUF * F8_BN);
+  }
+}
+
+}  // namespace slab
+
+// ---------------------------------------------------------------- host side
+namespace slab {
+
+typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn8 f8_encode() {
+  static EncodeTiledFn8 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn8>(p);
+  }
+  return fn;
+}
+
+// row-major [rows, cols] of `esize`-byte elements, box [box_rows, box_cols], 128-byte swizzle
+static int f8_make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esize, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn8 enc = f8_encode();
+  if (!enc) return -1;
+  static thread_local bool ctx_ready = false;
+  if (!ctx_ready) {
+    cudaFree(0);
+    ctx_ready = true;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)esize};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
+}
+
+}  // namespace slab
+
+// Forward only.  Requires K % 128 == 0, N % 128 == 0, E <= 512; expert segments start on multiples of 128 rows.
+extern "C" int slab_grouped_gemm_fp8(const void* A, const float* sa, const void* B, const float* sb, void* C,
+                                     const int* seg_offsets, const int* seg_counts, int E, int R, int N, int K,
+                                     int max_ctas, int* status, cudaStream_t stream) {
+  using namespace slab;
+  if (E > 512 || K % 128 || N % 128) return -100;
+  Fp8Params p{seg_offsets, seg_counts, sa, sb, E, R, N, K, status};
+  CUtensorMap ma, mb, mc;
+  int rc;
+  if ((rc = f8_make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, R, K, F8_BM, F8_BK))) return rc;
+  if ((rc = f8_make_map(&mb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K, F8_BN, F8_BK))) return rc;
+  if ((rc = f8_make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, F8_BM, 64))) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    SLAB_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM));
+    attr_set = true;
+  }
+  int dev = 0, grid = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev);
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  grouped_gemm_fp8_kernel<<<grid, F8_THREADS, F8_SMEM, stream>>>(ma, mb, mc, p);
+  return (int)cudaGetLastError();
+}

@@ -31,6 +31,7 @@ _SIGS = {
     "slab_router_topk": "ppppiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
+    "slab_grouped_gemm_fp8": "p" * 7 + "iiiii" + "ps",
 }
 _CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_long, "f": ctypes.c_float, "s": ctypes.c_void_p}
 
@@ -362,6 +363,18 @@ def grouped_gemm_raw(mode: int, a, b, offsets, counts, n: int, k: int, out=None,
             out = torch.empty(e, n, k, dtype=torch.bfloat16, device=a.device)
     call("slab_grouped_gemm_bf16", mode, a, b, out, offsets, counts, e, r, n, k, 1 if accumulate else 0,
          block_n, max_ctas, status_word(a.device), stream())
+    return out
+
+
+def grouped_gemm_fp8_raw(a_q, sa, b_q, sb, offsets, counts, out=None, max_ctas: int = 0):
+    """Block-scaled fp8 forward: ``out[R, N] = (a_q * sa) @ (b_q[e] * sb[e])^T`` with ``a_q [R, K]`` e4m3 +
+    ``sa [R, K/128]`` and ``b_q [E, N, K]`` e4m3 + ``sb [E, N/128, K/128]``; bf16 result."""
+    e, n, k = b_q.shape
+    r = a_q.shape[0]
+    if out is None:
+        out = torch.empty(r, n, dtype=torch.bfloat16, device=a_q.device)
+    call("slab_grouped_gemm_fp8", a_q, sa, b_q, sb, out, offsets, counts, e, r, n, k, max_ctas,
+         status_word(a_q.device), stream())
     return out
 
 

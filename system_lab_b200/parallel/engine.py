@@ -153,7 +153,7 @@ class Engine:
     def _make_comms(self):
         """Peer-memory collectives for FSDP when running on GPUs with the fused path enabled."""
         if (self.device.type == "cuda" and self.cfg.parallel.fsdp_fused_collectives
-                and self.cfg.parallel.fsdp and self.mesh.world > 1):
+                and self.cfg.parallel.fsdp and self.mesh.world > 1 and self.compute_dtype == torch.bfloat16):
             from ..comm.fsdp_comm import make_fsdp_comms
             return make_fsdp_comms(self.mesh, self.device)
         return None, None

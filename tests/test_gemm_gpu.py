@@ -77,3 +77,19 @@ def test_autograd_grouped_linear():
     _check(out, ref.grouped_gemm(a.detach(), w.detach(), off, cnt), "fwd")
     _check(a.grad, ref.grouped_gemm_dgrad(dy, w.detach(), off, cnt), "dgrad")
     _check(w.grad, ref.grouped_gemm_wgrad(dy, a.detach(), off, cnt), "wgrad")
+
+
+@pytest.mark.parametrize("counts,n,k", [([128], 128, 128), ([100, 0, 300, 129], 512, 256), ([5, 700, 64, 1], 768, 2048)])
+def test_fp8_block_scaled_forward(counts, n, k):
+    from system_lab_b200.ops import cuda, reference as ref
+    a, dy, w, off, cnt = _inputs(counts, n, k, 5)
+    aq, sa = cuda.quant_1x128(a)
+    wq, sw = cuda.quant_128x128(w)
+    out = cuda.grouped_gemm_fp8_raw(aq, sa.contiguous(), wq, sw.contiguous(), off, cnt)
+    # oracle on the *dequantised* operands: isolates the kernel from the quantisation error
+    exp = ref.grouped_gemm(ref.dequant_1x128(aq, sa), ref.dequant_128x128(wq, sw), off, cnt)
+    _check(out, exp, "fp8 fwd")
+    # and the end-to-end error against the bf16 operands stays at the fp8 level
+    full = ref.grouped_gemm(a, w, off, cnt)
+    rel = (out.float() - full.float()).norm() / full.float().norm()
+    assert rel < 0.06, rel
