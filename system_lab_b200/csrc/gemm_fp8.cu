@@ -17,7 +17,7 @@
 namespace slab {
 
 constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128, F8_UK = 32, F8_STAGES = 6, F8_TBUF = 4;
-constexpr int F8_THREADS = 192;
+constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 2 x 4 epilogue warps (each group owns 64 columns)
 constexpr int F8_CTRL = 3072, F8_PREFIX_OFF = 256;
 constexpr int F8_A_BYTES = F8_BM * F8_BK, F8_B_BYTES = F8_BN * F8_BK, F8_STAGE = F8_A_BYTES + F8_B_BYTES;
 constexpr int F8_STORE_OFF = F8_CTRL + F8_STAGES * F8_STAGE;
@@ -83,7 +83,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < F8_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < F8_TBUF; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    for (int b = 0; b < F8_TBUF; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 8); }
     *abort_flag = 0;
     fence_mbar_init();
     int acc = 0;
@@ -151,62 +151,105 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
     }
   } else {
-    // ---------------- epilogue warps: promote every K block with its scales, then store the tile
+    // ---------------- epilogue warps: promote every K block with its scales, then store the tile.
+    // Two groups of four warps; group `half` owns output columns [64*half, 64*half + 64) of the tile.
     const int lg = warp & 3;
-    const bool store_thread = (warp == 2 && lane == 0);
+    const int half = (warp - 2) >> 2;
+    const bool store_thread = ((warp == 2 || warp == 6) && lane == 0);
     const int r_in_tile = lg * 32 + lane;
-    const int sa_ld = kblocks;
     const int nb_total = p.N / 128;
+    uint8_t* sbuf = store_buf + half * F8_STORE_BYTES;
     uint32_t it = 0;
-    int chunk_ctr = 0;
     F8Tile ti;
     bool ok = true;
     for (int t = blockIdx.x; ok && f8_get_tile(t, prefix, p, ti); t += gridDim.x) {
-      float acc[F8_BN];
+      float acc[64];
 #pragma unroll
-      for (int i = 0; i < F8_BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 64; ++i) acc[i] = 0.f;
       const int row = ti.row0 + r_in_tile;
-      const float* sa_row = p.sa + (size_t)(row < p.R ? row : 0) * sa_ld;
+      const float* sa_row = p.sa + (size_t)(row < p.R ? row : 0) * kblocks;
       const float* sb_row = p.sb + ((size_t)ti.e * nb_total + ti.n_idx) * kblocks;
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+      // Software pipeline: the TMEM load of K block kb+1 is in flight while block kb is folded into the
+      // accumulators (tcgen05.wait::ld waits for every outstanding load, so the wait sits after the FMAs).
+      uint32_t va0[32], va1[32], vb0[32], vb1[32];
+      float sc_a = (row < p.R ? __ldg(sa_row) : 0.f) * __ldg(sb_row), sc_b = 0.f;
+      {
         const uint32_t buf = it % F8_TBUF;
-        const float sc = (row < p.R ? __ldg(sa_row + kb) : 0.f) * __ldg(sb_row + kb);
         if (!mbar_wait(&tfull_bar[buf], (it / F8_TBUF) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * F8_BN;
-#pragma unroll
-        for (int c = 0; c < F8_BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc, acc[c + i]);
-        }
+        const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * F8_BN + half * 64;
+        tmem_ld_32x32(taddr, va0);
+        tmem_ld_32x32(taddr + 32, va1);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        ++it;
+      }
+      for (int kb = 0; kb < kblocks; kb += 2) {
+        const bool has_b = kb + 1 < kblocks;
+        if (has_b) {                                     // issue the load of block kb+1 ...
+          const uint32_t buf = it % F8_TBUF;
+          sc_b = (row < p.R ? __ldg(sa_row + kb + 1) : 0.f) * __ldg(sb_row + kb + 1);
+          if (!mbar_wait(&tfull_bar[buf], (it / F8_TBUF) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * F8_BN + half * 64;
+          tmem_ld_32x32(taddr, vb0);
+          tmem_ld_32x32(taddr + 32, vb1);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {                   // ... fold block kb meanwhile
+          acc[i] = fmaf(__uint_as_float(va0[i]), sc_a, acc[i]);
+          acc[32 + i] = fmaf(__uint_as_float(va1[i]), sc_a, acc[32 + i]);
+        }
+        if (has_b) {
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[it % F8_TBUF]);
+          ++it;
+        }
+        const bool has_a = kb + 2 < kblocks;
+        if (has_a) {                                     // load block kb+2 while folding block kb+1
+          const uint32_t buf = it % F8_TBUF;
+          sc_a = (row < p.R ? __ldg(sa_row + kb + 2) : 0.f) * __ldg(sb_row + kb + 2);
+          if (!mbar_wait(&tfull_bar[buf], (it / F8_TBUF) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + (uint32_t(lg * 32) << 16) + buf * F8_BN + half * 64;
+          tmem_ld_32x32(taddr, va0);
+          tmem_ld_32x32(taddr + 32, va1);
+        }
+        if (has_b) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            acc[i] = fmaf(__uint_as_float(vb0[i]), sc_b, acc[i]);
+            acc[32 + i] = fmaf(__uint_as_float(vb1[i]), sc_b, acc[32 + i]);
+          }
+        }
+        if (has_a) {
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[it % F8_TBUF]);
+          ++it;
+        }
       }
       if (!ok) break;
-      const int col0 = ti.n_idx * F8_BN;
+      // this group's 64 columns: swizzled staging (one buffer per group) -> TMA store
+      if (store_thread) tma_store_wait_read<0>();
+      if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
-      for (int c = 0; c < F8_BN; c += 64) {
-        uint8_t* sb = store_buf + (chunk_ctr & 1) * F8_STORE_BYTES;
-        if (store_thread) tma_store_wait_read<1>();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int g = 0; g < 8; ++g) {
+        float f[8];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          float f[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = acc[c + g * 8 + i];
-          *reinterpret_cast<bf16x8*>(sb + r_in_tile * 128 + ((g ^ (r_in_tile & 7)) << 4)) = pack8(f);
-        }
-        fence_proxy_async();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (store_thread) {
-          tma_store_2d(&tmap_c, sb, col0 + c, ti.row0);
-          tma_store_commit();
-        }
-        ++chunk_ctr;
+        for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i];
+        *reinterpret_cast<bf16x8*>(sbuf + r_in_tile * 128 + ((g ^ (r_in_tile & 7)) << 4)) = pack8(f);
+      }
+      fence_proxy_async();
+      if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (store_thread) {
+        tma_store_2d(&tmap_c, sbuf, ti.n_idx * F8_BN + half * 64, ti.row0);
+        tma_store_commit();
       }
     }
     if (store_thread) tma_store_wait<0>();

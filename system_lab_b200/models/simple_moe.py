@@ -50,6 +50,10 @@ def seeded_normal_(t: torch.Tensor, std: float, base_seed: int, name: str) -> No
         t.copy_(torch.empty(t.shape, dtype=torch.float32, device=t.device).normal_(0.0, std, generator=g))
 
 
+# True while a layer's forward is being re-run inside backward (activation recompute): statistics that are
+# collected once per micro-batch (expert load) skip the replay.
+RECOMPUTE_PHASE = [False]
+
 _BALANCE_TABLES: dict = {}
 
 
@@ -180,6 +184,7 @@ class MoEFFN(nn.Module):
         self.dispatcher = None            # set by the engine (needs the process group)
         self.aux = None                   # last aux loss (added to the objective by the trainer)
         self.last_tokens_per_expert = None
+        self.step_tokens_per_expert = None   # summed over the micro-batches of the current step
 
     def forward(self, x):
         cfg = self.cfg
@@ -202,6 +207,10 @@ class MoEFFN(nn.Module):
         d = self.dispatcher
         plan = d.plan(idx)
         self.last_tokens_per_expert = plan.tokens_per_expert_global
+        if not RECOMPUTE_PHASE[0]:
+            c = plan.tokens_per_expert_global
+            self.step_tokens_per_expert = c.clone() if self.step_tokens_per_expert is None \
+                else self.step_tokens_per_expert + c
         if hasattr(d, "dispatch"):              # fused path: rows and gate probabilities travel together
             xe, pe = d.dispatch(plan, x2, w)
             out_buf = d.expert_output_buffer()
@@ -244,8 +253,12 @@ class _Recompute(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         ins = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
-        with torch.enable_grad():
-            out = ctx.fn(*ins)
+        prev, RECOMPUTE_PHASE[0] = RECOMPUTE_PHASE[0], True
+        try:
+            with torch.enable_grad():
+                out = ctx.fn(*ins)
+        finally:
+            RECOMPUTE_PHASE[0] = prev
         torch.autograd.backward(out, g)
         return (None,) + tuple(t.grad for t in ins)
 

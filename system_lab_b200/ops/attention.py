@@ -33,6 +33,11 @@ def _cudnn_sdpa(q, k, v, scale):
 
 def _library(q, k, v, scale, window):
     d, dv = q.shape[-1], v.shape[-1]
+    if q.is_cuda and dv < d:
+        # latent attention has a narrower value head (128) than query/key head (192): the fused library kernels
+        # want equal widths, so pad V with zero columns and drop them from the output
+        vp = torch.nn.functional.pad(v, (0, d - dv))
+        return _library(q, k, vp, scale, window)[..., :dv]
     if q.is_cuda and window == 0 and q.dtype in (torch.bfloat16, torch.float16) and _CUDNN_OK[0] is not False:
         try:
             o = _cudnn_sdpa(q, k, v, scale)

@@ -80,10 +80,15 @@ class _UnitFn(torch.autograd.Function):
         unit.gather()
         engine.after_gather(unit, forward=False)
         if ctx.recompute:
-            with torch.enable_grad():
-                xin = ctx.x.detach().requires_grad_(True) if ctx.x_needs_grad else ctx.x
-                out_inner = unit.module(xin, *ctx.extra)
-                aux = engine.pop_aux(unit)
+            from ..models import simple_moe
+            simple_moe.RECOMPUTE_PHASE[0] = True
+            try:
+                with torch.enable_grad():
+                    xin = ctx.x.detach().requires_grad_(True) if ctx.x_needs_grad else ctx.x
+                    out_inner = unit.module(xin, *ctx.extra)
+                    aux = engine.pop_aux(unit)
+            finally:
+                simple_moe.RECOMPUTE_PHASE[0] = False
             inner = (out_inner,) if aux is None else (out_inner, aux)
         else:
             xin, inner = ctx.xin, ctx.inner

@@ -137,8 +137,10 @@ class Trainer:
         ffns = self.engine.moe_ffns()
         if not ffns:
             return
-        counts = [f.last_tokens_per_expert for f in ffns if f.last_tokens_per_expert is not None]
-        if not counts:
+        counts = [f.step_tokens_per_expert for f in ffns if f.step_tokens_per_expert is not None]
+        for f in ffns:
+            f.step_tokens_per_expert = None
+        if len(counts) != len(ffns):
             return
         tpe = torch.stack(counts).float()
         if dist.is_initialized() and self.mesh.data_size > 1:

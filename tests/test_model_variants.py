@@ -1,0 +1,36 @@
+"""Model family coverage on CPU: MLA + shared expert + sigmoid/bias router (DeepSeek-V3 shaped), sliding window
+(GPT-OSS shaped), dense-first layers; single process vs pipeline x expert parallel."""
+import pytest
+
+from tests.distutil import run_ranks
+
+DSV3_TINY = ["attention_type=mla", "q_lora_rank=48", "kv_lora_rank=32", "qk_nope_head_dim=16", "qk_rope_head_dim=8",
+             "v_head_dim=16", "num_layers=4", "first_k_dense=1", "ffn_hidden_size=256",
+             "moe_shared_expert_intermediate_size=128", "moe_router_score_function=sigmoid",
+             "moe_router_load_balancing_type=bias", "moe_router_topk_scaling_factor=2.5", "global_batch_size=8",
+             "micro_batch_size=2"]
+
+
+def _train(rank, world, overrides, steps):
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu"])
+    tr = Trainer(cfg)
+    out = [float(tr.train_step()["loss"]) for _ in range(steps)]
+    bias = [f.router_bias.abs().sum().item() for f in tr.engine.moe_ffns() if f.router_bias is not None]
+    return out, bias
+
+
+def test_dsv3_shape_single_vs_pp2_ep2():
+    (single, bias), = run_ranks(_train, 1, DSV3_TINY + ["expert_model_parallel_size=1"], 4)
+    assert all(abs(l - 6.93) < 0.4 for l in single)
+    assert bias and all(b > 0 for b in bias)                 # aux-loss-free balancing moved the bias
+    res = run_ranks(_train, 4, DSV3_TINY + ["expert_model_parallel_size=2", "pipeline_model_parallel_size=2"], 4)
+    assert res[0][0] == pytest.approx(single, rel=5e-5, abs=5e-5)
+
+
+def test_sliding_window_and_aux_loss_run():
+    ov = ["sliding_window=16", "moe_aux_loss_coeff=0.01", "expert_model_parallel_size=2", "global_batch_size=8",
+          "micro_batch_size=2", "recompute_granularity=selective"]
+    res = run_ranks(_train, 2, ov, 3)
+    assert all(abs(l - 6.93) < 0.4 for l in res[0][0])
