@@ -196,6 +196,8 @@ def load_checkpoint(trainer, path: str) -> None:
         if not g.sharded:
             if g.shard is not g.full:
                 g.full.copy_(g.shard)
+        elif getattr(g, "shard_lp", None) is not None:
+            g.shard_lp.copy_(g.shard)
     trainer.step = meta["step"]
     trainer.data.cursor = meta["data_cursor"]
     trainer.loss_curve = list(meta.get("loss_curve", []))

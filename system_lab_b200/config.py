@@ -108,7 +108,7 @@ class ParallelConfig:
     ddp_bucket_size: int = 40_000_000    # elements
     ddp_average_in_collective: bool = True
     num_distributed_optimizer_instances: int = 1
-    fsdp_fused_collectives: bool = False # peer-memory all-gather / reduce-scatter kernels instead of NCCL
+    fsdp_fused_collectives: bool = True  # peer-memory all-gather / reduce-scatter kernels instead of NCCL
 
 
 @dataclass

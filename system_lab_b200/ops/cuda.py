@@ -523,6 +523,8 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, 
     out_bf16 = None
     if not group.sharded and group.shard is not group.full:
         out_bf16 = group.full.data           # unsharded with fp32 masters: refresh the compute copy in-kernel
+    elif getattr(group, "shard_lp", None) is not None:
+        out_bf16 = group.shard_lp            # sharded: the copy the next all-gather publishes
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
     call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, g, 1 if g.dtype == torch.bfloat16 else 0,

@@ -199,8 +199,11 @@ class Engine:
         return aux
 
     def after_unit_backward(self, unit: Unit) -> None:
-        unit.reduce_grads()
-        if self.optimizer is not None and self.cfg.train.optimizer_in_backward:
+        in_bwd = self.optimizer is not None and self.cfg.train.optimizer_in_backward
+        for g in unit.groups:
+            if not (in_bwd and self.optimizer.fusable(g)):
+                g.reduce_grads()              # fusable groups are reduced inside the optimizer kernel
+        if in_bwd:
             self.optimizer.step_unit(unit)
 
     # ---- running one micro-batch through this pipeline stage --------------------------------

@@ -94,12 +94,37 @@ class FlatGroup:
         else:
             self.shard = self.full                # single rank, no master: optimizer updates in place
         self._hi_src = None
+        # sharded groups with fp32 masters keep a compute-dtype copy of the shard (written by the optimizer
+        # kernel in the same pass as the master) so a gather never has to cast
+        self.shard_lp = self.shard.to(self.compute_dtype) if (self.sharded and self.keep_master) else None
         if self.sharded:
             self.release()
 
     # ---- parameters -------------------------------------------------------
     def shard_in_compute_dtype(self) -> torch.Tensor:
+        if getattr(self, "shard_lp", None) is not None:
+            return self.shard_lp
         return self.shard if self.shard.dtype == self.compute_dtype else self.shard.to(self.compute_dtype)
+
+    def sync_low_precision(self) -> None:
+        """Refresh the compute-dtype copies after the master shard changed outside the fused kernel."""
+        if getattr(self, "shard_lp", None) is not None:
+            self.shard_lp.copy_(self.shard)
+        self.refresh_full_from_shard()
+
+    def can_fuse_rs_adamw(self) -> bool:
+        """Reduce-scatter + cast + AdamW in one peer-memory kernel: needs the peer comm, bf16 gradients and an
+        fp32 master shard."""
+        return (self.sharded and self.comm is not None and self.keep_master and self.grad_full is not None
+                and self.grad_full.dtype == torch.bfloat16 and self.grad_shard is None)
+
+    def take_grad_full(self) -> torch.Tensor:
+        """Hand the flat gradient buffer to a fused reduce-scatter+update (nothing is left to reduce)."""
+        self._collect_fused_grads()
+        g, self.grad_full = self.grad_full, None
+        for p in self.params:
+            p.grad = None
+        return g
 
     def gather(self) -> None:
         if self.gathered:

@@ -114,6 +114,17 @@ class ShardedAdamW:
         return torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0)
 
     # ---- update -----------------------------------------------------------------------
+    def fusable(self, g) -> bool:
+        return self.state_dtype == "fp32" and g.device.type == "cuda" and g.can_fuse_rs_adamw()
+
+    def _fused_rs_update(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor) -> None:
+        """One kernel: pull every rank's gradient slice over NVLink, sum in fp32, AdamW on the master shard and
+        moments, write the bf16 shard the next all-gather will publish."""
+        grad_full = g.take_grad_full()
+        g.comm.reduce_scatter_adamw(grad_full, g.shard, self.m[g.name].data, self.v[g.name].data, g.shard_lp, coef,
+                                    sq_out, lr=lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
+                                    weight_decay=self.weight_decay, step=self.step_count)
+
     def _update_group(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor | None = None) -> None:
         """``sq_out``: also accumulate ``sum(grad^2) / replication`` of this group there (fused into the
         kernel on the GPU path)."""
@@ -141,7 +152,7 @@ class ShardedAdamW:
             self.v[g.name].store(v)
             if p32 is not g.shard:
                 g.shard.copy_(p32)
-            g.refresh_full_from_shard()
+            g.sync_low_precision()
         g.grad_shard = None
 
     def begin_step(self, lr: float | None = None) -> None:
@@ -169,6 +180,9 @@ class ShardedAdamW:
             self._side = torch.cuda.Stream(device=dev)
         main = torch.cuda.current_stream(dev)
         self._side.wait_stream(main)
+        for g in unit.groups:
+            if self.fusable(g):                          # peers wait on this kernel: keep it on the main stream
+                self._fused_rs_update(g, coef, self._cur_lr, self._sq_accum)
         with torch.cuda.stream(self._side):
             for g in unit.groups:
                 if g.grad_shard is not None:

@@ -116,6 +116,34 @@ def train_equivalence(rank, world):
     return out
 
 
+def fsdp_comm_equivalence(rank, world):
+    """Peer-memory all-gather / reduce-scatter vs NCCL under FSDP with experts sharded too (ep=1)."""
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    out, mesh, dev = {}, None, None
+    for fused, in_bwd in (("false", "false"), ("true", "false"), ("false", "true"), ("true", "true")):
+        cfg = Config.load(preset="qwen3-30b-a3b", overrides=[
+            "num_layers=2", "num_experts=8", "seq_length=256", "vocab_size=2048", "micro_batch_size=2",
+            f"global_batch_size={2 * world}", "expert_model_parallel_size=1", "recompute_granularity=full",
+            "device=cuda", f"fsdp_fused_collectives={fused}", f"optimizer_in_backward={in_bwd}"])
+        tr = Trainer(cfg) if mesh is None else Trainer(cfg, mesh=mesh, device=dev)
+        mesh, dev = tr.mesh, tr.device
+        out[fused + in_bwd] = [float(tr.train_step()["loss"]) for _ in range(4)]
+        torch.cuda.synchronize()
+        cops.check_status()
+        del tr
+    return out
+
+
+def test_fsdp_peer_collectives_match_nccl():
+    world = min(torch.cuda.device_count(), 4)
+    for r in _run("fsdp_comm_equivalence", world):
+        assert r["truefalse"] == pytest.approx(r["falsefalse"], rel=2e-2, abs=5e-2)
+        # optimizer inside backward: reduce-scatter + cast + AdamW in one peer-memory kernel vs NCCL + AdamW
+        assert r["truetrue"] == pytest.approx(r["falsetrue"], rel=2e-2, abs=5e-2)
+
+
 def test_fused_dispatch_matches_nccl_baseline():
     world = min(torch.cuda.device_count(), 4)
     assert all(_run("dispatch_equivalence", world))
