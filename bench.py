@@ -35,6 +35,11 @@ def parse():
     ap.add_argument("--preset", default="qwen3-30b-a3b")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (invalid as a result)")
     ap.add_argument("--seqs-per-gpu", type=int, default=2)
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (DeepSeek-V3 proxy: 2)")
+    ap.add_argument("--ep", type=int, default=0, help="expert parallel size (default: all data ranks)")
+    ap.add_argument("--gbs", type=int, default=0, help="global batch in sequences (default: seqs-per-gpu x N)")
+    ap.add_argument("--mbs", type=int, default=0, help="micro-batch in sequences (default: seqs-per-gpu)")
+    ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
     ap.add_argument("--balanced-routing", action="store_true",
@@ -90,7 +95,7 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def choose_memory_plan(cfg, world: int) -> dict:
+def choose_memory_plan(cfg, world: int, force: str = "") -> dict:
     """Highest-fidelity optimizer/weight layout that fits 92 % of 180 GB per GPU."""
     from system_lab_b200.pilot.constraints import estimate_memory
     plans = [
@@ -102,6 +107,8 @@ def choose_memory_plan(cfg, world: int) -> dict:
     ]
     last = None
     for name, prec, in_bwd in plans:
+        if force and name != force:
+            continue
         for k, v in prec.items():
             setattr(cfg.precision, k, v)
         cfg.train.optimizer_in_backward = in_bwd
@@ -132,8 +139,10 @@ def main() -> int:
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
     n = world
-    ov = [f"global_batch_size={args.seqs_per_gpu * n}", f"micro_batch_size={args.seqs_per_gpu}",
-          f"expert_model_parallel_size={n}", "clip_grad=1.0", f"use_cuda_kernels={args.kernels}"]
+    dp = n // args.pp
+    ov = [f"global_batch_size={args.gbs or args.seqs_per_gpu * n}", f"micro_batch_size={args.mbs or args.seqs_per_gpu}",
+          f"expert_model_parallel_size={args.ep or dp}", f"pipeline_model_parallel_size={args.pp}", "clip_grad=1.0",
+          f"use_cuda_kernels={args.kernels}"]
     if args.layers:
         ov.append(f"num_layers={args.layers}")
     if args.dispatcher:
@@ -141,7 +150,7 @@ def main() -> int:
     if args.balanced_routing:
         ov.append("moe_router_force_load_balancing=true")
     cfg = Config.load(preset=args.preset, overrides=ov + list(args.overrides))
-    plan = choose_memory_plan(cfg, n)
+    plan = choose_memory_plan(cfg, n, args.plan)
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
                       cfg.parallel.context_parallel_size)
@@ -238,7 +247,7 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": m.name, "num_layers": m.num_layers, "hidden": m.hidden_size,
                        "num_experts": m.num_experts, "topk": m.moe_router_topk, "global_batch": cfg.train.global_batch_size,
-                       "seq_len": m.seq_length, "parallelism": f"fsdp+ep{mesh.ep}",
+                       "seq_len": m.seq_length, "parallelism": f"fsdp+ep{mesh.ep}" + (f"+pp{mesh.pp}" if mesh.pp > 1 else ""),
                        "memory_plan": plan, "recompute": cfg.precision.recompute_granularity,
                        "dispatcher": m.moe_token_dispatcher_type, "kernels": args.kernels,
                        "routing": "forced-balanced" if m.moe_router_force_load_balancing else "learned-router",

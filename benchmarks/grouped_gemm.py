@@ -130,6 +130,15 @@ def main():
                                      flush=flush, name="fc1_fwd_fp8"), fl1)
         rec("fc2_fwd_fp8", time_cuda(lambda: cops.grouped_gemm_fp8_raw(aq, as_, w2q, w2s, off_d, cnt_d), args.iters,
                                      flush=flush, name="fc2_fwd_fp8"), fl2)
+        xr, xrs = cops.quant_rowwise(x)
+        ar, ars = cops.quant_rowwise(act)
+        w1r, w1rs = cops.quant_rowwise(w1)
+        w2r, w2rs = cops.quant_rowwise(w2)
+        rec("fc1_fwd_fp8_rowwise", time_cuda(lambda: cops.grouped_gemm_fp8_rowwise_raw(xr, xrs, w1r, w1rs, off_d, cnt_d),
+                                             args.iters, flush=flush, name="fc1_fwd_fp8_rowwise"), fl1)
+        rec("fc2_fwd_fp8_rowwise", time_cuda(lambda: cops.grouped_gemm_fp8_rowwise_raw(ar, ars, w2r, w2rs, off_d, cnt_d),
+                                             args.iters, flush=flush, name="fc2_fwd_fp8_rowwise"), fl2)
+        rec("quant_rowwise x", time_cuda(lambda: cops.quant_rowwise(x), args.iters, flush=flush, name="quant_row_x"), 0.0)
         rec("quant_1x128 x", time_cuda(lambda: cops.quant_1x128(x), args.iters, flush=flush, name="quant_x"), 0.0)
         rec("quant_128x128 w1", time_cuda(lambda: cops.quant_128x128(w1), args.iters, flush=flush, name="quant_w1"), 0.0)
         cops.check_status()

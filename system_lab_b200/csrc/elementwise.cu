@@ -276,6 +276,37 @@ __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8
   }
 }
 
+// Row-wise: one scale per row (activations: per token; weights viewed as [E*N, K]: per output channel).
+// One warp per row, two passes over the row (the second pass hits L1/L2).
+__global__ void quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ q,
+                                     float* __restrict__ scale, long rows, int H) {
+  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (long r = blockIdx.x * (long)warps + (threadIdx.x >> 5); r < rows; r += (long)gridDim.x * warps) {
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(x + r * H);
+    float amax = 0.f;
+    for (int c = lane; c < nvec; c += 32) {
+      float v[8];
+      unpack8(src[c], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    }
+    amax = fmaxf(warp_max(amax), 1e-12f);
+    const float inv = 448.f / amax;
+    uint2* dst = reinterpret_cast<uint2*>(q + r * H);
+    for (int c = lane; c < nvec; c += 32) {
+      float v[8];
+      unpack8(src[c], v);
+      __nv_fp8_e4m3 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __nv_fp8_e4m3(v[j] * inv);
+      dst[c] = *reinterpret_cast<uint2*>(o);
+    }
+    if (lane == 0) scale[r] = amax / 448.f;
+  }
+}
+
 // 128x128: one block (256 threads) per weight block.
 __global__ void __launch_bounds__(256)
 quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale,
@@ -592,6 +623,14 @@ extern "C" int slab_quant_1x128(const void* x, void* q, float* scale, long rows,
   if (rows == 0) return 0;
   quant_1x128_kernel<<<grid_for(rows * (H / 128) * 32, 256), 256, 0, st>>>((const __nv_bfloat16*)x,
                                                                             (__nv_fp8_e4m3*)q, scale, rows, H);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_quant_rowwise(const void* x, void* q, float* scale, long rows, int H, cudaStream_t st) {
+  if (H % 8) return -100;
+  if (rows == 0) return 0;
+  quant_rowwise_kernel<<<grid_for(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)q, scale,
+                                                                 rows, H);
   return (int)cudaGetLastError();
 }
 

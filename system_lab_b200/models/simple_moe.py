@@ -221,9 +221,12 @@ class MoEFFN(nn.Module):
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 dgrad_out=out_buf)
         act = ops.swiglu_probs(h1, pe, rows_dev=getattr(plan, "meta", None))
+        # In a recomputed forward nothing reads the block's result (it only feeds a residual add), so the second
+        # expert GEMM and the combine exchange are skipped: their autograd nodes are all that backward needs.
+        dead = RECOMPUTE_PHASE[0]
         ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
-                                out=out_buf)
-        out = d.combine_rows(plan, ye)
+                                out=out_buf, dead=dead)
+        out = d.combine_rows(plan, ye, dead=dead)
         if self.shared is not None:
             out = out + self.shared(x2)
         return out.reshape(shp)

@@ -135,9 +135,12 @@ class AllToAllDispatcher:
     def dispatch_scalars(self, plan: RoutingPlan, p: torch.Tensor) -> torch.Tensor:
         return _DispatchScalars.apply(p, self, plan)
 
-    def combine_rows(self, plan: RoutingPlan, ye: torch.Tensor, weights: torch.Tensor | None = None) -> torch.Tensor:
+    def combine_rows(self, plan: RoutingPlan, ye: torch.Tensor, weights: torch.Tensor | None = None,
+                     dead: bool = False) -> torch.Tensor:
+        """``dead``: the caller only needs the autograd node (a recomputed forward whose result nobody reads), so
+        the exchange is skipped and the returned values are unspecified.  Every rank must pass the same flag."""
         if weights is None:
-            return _CombineRows.apply(ye, self, plan)
+            return _CombineRows.apply(ye, self, plan, dead)
         return _CombineRowsWeighted.apply(ye, weights, self, plan)
 
     def combine_scalars(self, plan: RoutingPlan, se: torch.Tensor) -> torch.Tensor:
@@ -173,8 +176,10 @@ class _DispatchScalars(torch.autograd.Function):
 
 class _CombineRows(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ye, d, plan):
+    def forward(ctx, ye, d, plan, dead=False):
         ctx.d, ctx.plan = d, plan
+        if dead:
+            return ye.new_zeros(plan.num_tokens, ye.shape[-1])
         back = d._return_pairs(plan, ye)
         return back.reshape(plan.num_tokens, plan.topk, -1).float().sum(1).to(ye.dtype)
 
@@ -183,7 +188,7 @@ class _CombineRows(torch.autograd.Function):
         d, plan = ctx.d, ctx.plan
         t, k = plan.num_tokens, plan.topk
         pairs = g[:, None, :].expand(t, k, g.shape[-1]).reshape(t * k, -1)
-        return d._send_pairs(plan, pairs), None, None
+        return d._send_pairs(plan, pairs), None, None, None
 
 
 class _CombineRowsWeighted(torch.autograd.Function):

@@ -229,8 +229,11 @@ class FusedDispatcher:
     def dispatch_scalars(self, plan, p):
         raise NotImplementedError("use dispatch(plan, x, probs): rows and gate probabilities travel together")
 
-    def combine_rows(self, plan: FusedPlan, ye: torch.Tensor, weights: torch.Tensor | None = None):
-        return _FusedCombine.apply(ye, weights, self, plan)
+    def combine_rows(self, plan: FusedPlan, ye: torch.Tensor, weights: torch.Tensor | None = None,
+                     dead: bool = False):
+        """``dead``: only the autograd node is wanted (recomputed forward whose result nobody reads): no signal, no
+        wait, no pull; the returned values are unspecified.  Every rank of the group must pass the same flag."""
+        return _FusedCombine.apply(ye, weights, self, plan, dead and weights is None)
 
 
 class _FusedDispatch(torch.autograd.Function):
@@ -260,12 +263,14 @@ class _FusedDispatch(torch.autograd.Function):
 
 class _FusedCombine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ye, weights, d: FusedDispatcher, plan: FusedPlan):
+    def forward(ctx, ye, weights, d: FusedDispatcher, plan: FusedPlan, dead: bool = False):
         ctx.d, ctx.plan = d, plan
         if weights is not None:
             weights = weights.float().contiguous()
             ctx.save_for_backward(weights)
         ctx.weighted = weights is not None
+        if dead:
+            return torch.empty(plan.num_tokens, d.H, dtype=torch.bfloat16, device=d.device)
         d.stage_out_rows(ye.contiguous())
         ep = d.signal_out()
         return d.pull_rows(plan, ep, weights)
@@ -282,4 +287,4 @@ class _FusedCombine(torch.autograd.Function):
         if ctx.weighted and ctx.needs_input_grad[1]:
             raise NotImplementedError("gate-weighted fused combine has no weight gradient: apply the gate "
                                       "inside SwiGLU (swiglu_probs) for training")
-        return g_ye, None, None, None
+        return g_ye, None, None, None, None

@@ -85,13 +85,14 @@ def rope_packed(qkv, cos, sin, n_heads: int, head_dim: int):
     return torch.cat([rot.reshape(b, s, n_heads * head_dim), qkv[..., n_heads * head_dim:]], dim=-1)
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None):
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None, dead: bool = False):
     """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``.
     ``out`` (kernel path only) names the buffer the result is written to, e.g. the peer-visible
-    expert-output buffer of the fused dispatcher."""
+    expert-output buffer of the fused dispatcher.  ``dead``: only the autograd node is wanted (a recomputed
+    forward whose result nobody reads); the product is not computed and the returned values are unspecified."""
     if use_kernels(a):
-        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out)
-    return _GroupedLinearRef.apply(a, w, offsets, counts)
+        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out, dead)
+    return _GroupedLinearRef.apply(a, w, offsets, counts, dead)
 
 
 def causal_attention(q, k, v, scale=None, window=0):
@@ -110,8 +111,10 @@ class _GroupedLinearRef(torch.autograd.Function):
     """Oracle grouped linear with explicit fwd/dgrad/wgrad (mirrors the three CUDA kernels)."""
 
     @staticmethod
-    def forward(ctx, a, w, offsets, counts):
+    def forward(ctx, a, w, offsets, counts, dead=False):
         ctx.save_for_backward(a, w, offsets, counts)
+        if dead:
+            return a.new_zeros(a.shape[0], w.shape[1])
         return ref.grouped_gemm(a, w, offsets, counts)
 
     @staticmethod
@@ -120,4 +123,4 @@ class _GroupedLinearRef(torch.autograd.Function):
         g = g.contiguous()
         da = ref.grouped_gemm_dgrad(g, w, offsets, counts) if ctx.needs_input_grad[0] else None
         dw = ref.grouped_gemm_wgrad(g, a, offsets, counts, out_dtype=w.dtype) if ctx.needs_input_grad[1] else None
-        return da, dw, None, None
+        return da, dw, None, None, None

@@ -26,12 +26,14 @@ _SIGS = {
     "slab_rope": "ppppliiillfs",
     "slab_quant_1x128": "ppplis",
     "slab_quant_128x128": "pppiiis",
+    "slab_quant_rowwise": "ppplis",
     "slab_sumsq": "pilfps",
     "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "s",
     "slab_router_topk": "ppppiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
     "slab_grouped_gemm_fp8": "p" * 7 + "iiiii" + "ps",
+    "slab_grouped_gemm_fp8_rowwise": "p" * 7 + "iiiii" + "ps",
 }
 _CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_long, "f": ctypes.c_float, "s": ctypes.c_void_p}
 
@@ -378,6 +380,19 @@ def grouped_gemm_fp8_raw(a_q, sa, b_q, sb, offsets, counts, out=None, max_ctas: 
     return out
 
 
+def grouped_gemm_fp8_rowwise_raw(a_q, sa, b_q, sb, offsets, counts, out=None, max_ctas: int = 0):
+    """Row-scaled fp8 forward: ``out[r, n] = sa[r] * sb[e, n] * sum_k a_q[r, k] * b_q[e, n, k]`` with one scale
+    per activation row (``sa [R]``) and one per expert output channel (``sb [E, N]``); bf16 result.  The scales
+    are constant along K, so the kernel accumulates all of K in TMEM at the fp8 tensor rate."""
+    e, n, k = b_q.shape
+    r = a_q.shape[0]
+    if out is None:
+        out = torch.empty(r, n, dtype=torch.bfloat16, device=a_q.device)
+    call("slab_grouped_gemm_fp8_rowwise", a_q, sa, b_q, sb, out, offsets, counts, e, r, n, k, max_ctas,
+         status_word(a_q.device), stream())
+    return out
+
+
 def _pick_bn(cols: int) -> int:
     return 256 if cols % 256 == 0 or cols > 1024 else 128
 
@@ -392,11 +407,14 @@ class _GroupedLinear(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, out=None, dgrad_out=None):
+    def forward(ctx, a, w, offsets, counts, out=None, dgrad_out=None, dead=False):
         e, n, k = w.shape
         a = a.contiguous()
         w = w.contiguous() if not w.is_contiguous() else w
-        out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
+        if dead:           # node only: the caller never reads the product
+            out = out if out is not None else torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
+        else:
+            out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
         ctx.save_for_backward(a, w, offsets, counts)
         ctx.w_ref = w
         ctx.dgrad_out = dgrad_out
@@ -423,18 +441,18 @@ class _GroupedLinear(torch.autograd.Function):
                 ctx.w_ref.main_grad_written = True
             else:
                 dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
-        return da, dw, None, None, None, None
+        return da, dw, None, None, None, None, None
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None):
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None, dead: bool = False):
     e, n, k = w.shape
     if not _bf16(a, w) or k % 64 or n % 128:
         from . import _GroupedLinearRef
-        return _GroupedLinearRef.apply(a, w, offsets, counts)
+        return _GroupedLinearRef.apply(a, w, offsets, counts, dead)
     offsets, counts = _check_segments(offsets, counts)
     if out is not None and (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
         out = None
-    res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out)
+    res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead)
     return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
 
 
@@ -489,6 +507,18 @@ def quant_1x128(x):
     s = torch.empty(x2.shape[0], shp[-1] // 128, dtype=torch.float32, device=x.device)
     call("slab_quant_1x128", x2, q, s, x2.shape[0], shp[-1], stream())
     return q.reshape(shp), s.reshape(*shp[:-1], shp[-1] // 128)
+
+
+def quant_rowwise(x):
+    """e4m3 with one fp32 scale per row of the last dimension: returns ``(q, scale[...])``."""
+    if not _bf16(x):
+        return ref.quant_rowwise(x)
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1]).contiguous()
+    q = torch.empty(x2.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    call("slab_quant_rowwise", x2, q, s, x2.shape[0], shp[-1], stream())
+    return q.reshape(shp), s.reshape(shp[:-1])
 
 
 def quant_128x128(w):

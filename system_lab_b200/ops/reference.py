@@ -130,6 +130,14 @@ def quant_128x128(w: torch.Tensor):
     return q.reshape(*lead, n, k), scale
 
 
+def quant_rowwise(x: torch.Tensor):
+    """One scale per row of the last dimension.  Returns ``(q fp8, scale [...] fp32)`` with ``x ~= q * scale``."""
+    amax = x.float().abs().amax(-1).clamp_min(1e-12)
+    scale = amax / FP8_MAX
+    q = (x.float() / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
 def dequant_1x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     *lead, h = q.shape
     return (q.float().reshape(*lead, h // 128, 128) * scale.unsqueeze(-1)).reshape(*lead, h)

@@ -139,11 +139,12 @@ def param_counts(m: Any) -> dict:
             "per_layer_non_expert": attn + norms + router + shared}
 
 
-def bytes_per_param(pr: Any, optimizer_in_backward: bool = False) -> float:
-    """Resident bytes per (sharded) parameter: weight + master + grad + two moments."""
+def bytes_per_param(pr: Any, optimizer_in_backward: bool = False, microbatches: int = 1) -> float:
+    """Resident bytes per (sharded) parameter: weight + master + grad + two moments.  Gradients of a single
+    micro-batch are consumed in the compute dtype; accumulation over several micro-batches is fp32."""
     w = _DTYPE_BYTES[pr.params_dtype]
     master = 4 if (pr.params_dtype != "fp32" and pr.master_weights) else 0
-    grad = 0 if optimizer_in_backward else (2 if pr.params_dtype == "bf16" else 4)
+    grad = 0 if optimizer_in_backward else (2 if (pr.params_dtype == "bf16" and microbatches <= 1) else 4)
     mom = {"fp32": 8.0, "bf16": 4.0, "fp8": 2.0 + 8.0 / 128}[pr.optimizer_state_dtype]
     return w + master + grad + mom
 
@@ -164,7 +165,8 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     edp = max(dp // ep, 1)
     shard_dense = dp if p.fsdp else 1
     shard_exp = ep * (edp if p.fsdp else 1)
-    bpp = bytes_per_param(pr, t.optimizer_in_backward)
+    nmb = max(t.global_batch_size // max(t.micro_batch_size * dp, 1), 1)
+    bpp = bytes_per_param(pr, t.optimizer_in_backward, nmb)
     state = (pc["non_expert"] / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
     wbytes = _DTYPE_BYTES[pr.params_dtype]
     # transient: one layer's gathered params (+ its grads when optimizer runs in backward)

@@ -93,3 +93,21 @@ def test_fp8_block_scaled_forward(counts, n, k):
     full = ref.grouped_gemm(a, w, off, cnt)
     rel = (out.float() - full.float()).norm() / full.float().norm()
     assert rel < 0.06, rel
+
+
+@pytest.mark.parametrize("counts,n,k", [([128], 256, 128), ([100, 0, 300, 129], 512, 256), ([5, 700, 64, 1], 768, 2048),
+                                        ([130, 250], 2880, 384), ([77], 64, 128)])
+def test_fp8_row_scaled_forward(counts, n, k):
+    from system_lab_b200.ops import cuda, reference as ref
+    a, dy, w, off, cnt = _inputs(counts, n, k, 6)
+    aq, sa = cuda.quant_rowwise(a)
+    wq, sw = cuda.quant_rowwise(w)
+    aq_ref, sa_ref = ref.quant_rowwise(a)
+    torch.testing.assert_close(sa, sa_ref, rtol=1e-5, atol=0)
+    assert (aq.float() - aq_ref.float()).abs().max() <= 0.13 * aq_ref.float().abs().max()
+    out = cuda.grouped_gemm_fp8_rowwise_raw(aq, sa, wq, sw.contiguous(), off, cnt)
+    exp = ref.grouped_gemm(aq.float() * sa[:, None], wq.float() * sw[..., None], off, cnt)
+    _check(out, exp, "fp8 rowwise fwd")
+    full = ref.grouped_gemm(a, w, off, cnt)
+    rel = (out.float() - full.float()).norm() / full.float().norm()
+    assert rel < 0.06, rel

@@ -1,0 +1,63 @@
+"""VRAM verdict / bucket table and the HTML report generator (CPU)."""
+import json
+
+from system_lab_b200.config import Config
+from system_lab_b200.observe import report_html, vram
+
+
+def test_vram_verdict_thresholds():
+    mk = lambda r, retires=0: vram.health(vram.VramSample(50, 100, r, retires, 192.0))
+    assert mk(150)["verdict"] == "OK"
+    assert mk(150, retires=2)["verdict"] == "PRESSURE"
+    assert mk(0.96 * 192)["verdict"] == "TIGHT"
+    assert mk(0.985 * 192)["verdict"] == "CRITICAL"
+    h = mk(150)
+    assert abs(h["frag_pct"] - 100 * 50 / 150) < 1e-6 and abs(h["headroom_gb"] - 42.0) < 1e-6
+
+
+def test_vram_buckets_moe_sum_and_unaccounted_rule():
+    cfg = Config.load(preset="qwen3-30b-a3b", overrides=["params_dtype=bf16", "global_batch_size=16", "micro_batch_size=2",
+                                                          "expert_model_parallel_size=8", "recompute_granularity=selective"])
+    b = vram.decompose(cfg, 8)
+    assert b.mode == "C"
+    names = [r["bucket"] for r in b.rows]
+    assert "MoE expert weights" in names and "Dense weights" in names
+    total = sum(r["gb"] for r in b.rows)
+    ok = vram.decompose(cfg, 8, vram.VramSample(0, total * 1.05, total * 1.2, 0, 192.0))
+    assert ok.consistent and abs(ok.unaccounted_gb - 0.05 * total) < 1e-6
+    bad = vram.decompose(cfg, 8, vram.VramSample(0, total * 1.5, total * 1.6, 0, 192.0))
+    assert not bad.consistent
+    assert "unaccounted" in vram.format_table(vram.health(vram.VramSample(0, total * 1.5, total * 1.6, 0, 192.0)), bad)
+
+
+def test_vram_modes():
+    dense = Config.load(preset="simplemoe-tiny", overrides=["num_experts=0"])
+    assert vram.pick_mode(dense) == "B"
+    assert vram.pick_mode(dense, trainable_fraction=0.001) == "A"
+    rows = [r["bucket"] for r in vram.decompose(dense, 1).rows]
+    assert rows[:4] == ["Weights", "Master copy", "Adam state (m + v)", "Gradients"]
+
+
+def _breakdown(scale=1.0):
+    return {"trace": "x/t.json", "window": "ProfilerStep#0", "window_ms": 100.0 * scale,
+            "stream_busy_ms": {"7": 80.0 * scale, "9": 20.0},
+            "compute_busy_pct": 90.0, "idle_pct": 2.0, "comm_ms": 10.0, "comm_hidden_pct": 70.0,
+            "comm_ratio_exposed": 0.03, "category_ms": {"slab_grouped_gemm": 40.0 * scale, "attn_kernel": 20.0, "<odd&name>": 1.0},
+            "top_kernels": [{"name": "void slab::k<1>(int*)", "ms": 40.0, "count": 96}],
+            "time_bins": [{"slab_grouped_gemm": 0.5, "attn_kernel": 0.2}, {"attn_kernel": 0.4}]}
+
+
+def test_html_single_and_comparison(tmp_path):
+    bench = {"value": 12345.0, "n_gpus": 8, "dtype": "bf16", "mem_peak_gb": 77.0,
+             "config": {"model": "m", "parallelism": "fsdp+ep8", "global_batch": 16, "seq_len": 4096, "tflops_per_gpu": 500.0}}
+    page = report_html.render_single(_breakdown(), bench)
+    assert page.startswith("<!doctype html>") and "slab_grouped_gemm" in page and "12,345" in page
+    assert "&lt;odd&amp;name&gt;" in page and "<odd&name>" not in page          # names are escaped
+    assert "<script" not in page
+    cmp_page = report_html.render_comparison(_breakdown(), _breakdown(0.5), "a", "b")
+    assert "2.00x" in cmp_page and "-20.00" in cmp_page
+    p1, p2, out = tmp_path / "a.json", tmp_path / "b.json", tmp_path / "o" / "r.html"
+    p1.write_text(json.dumps(_breakdown()))
+    p2.write_text("log line\n" + json.dumps(_breakdown(0.5)))
+    assert report_html.main([str(p1), "--against", str(p2), "--names", "x,y", "-o", str(out)]) == 0
+    assert out.exists() and "x vs y" in out.read_text()
