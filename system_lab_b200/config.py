@@ -91,6 +91,7 @@ class ModelConfig:
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
     moe_router_force_load_balancing: bool = False  # benchmarking aid: route by fixed random logits
     moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
+    moe_combine_push: bool = False       # expert GEMM epilogues push result rows to the token owners (fused combine)
 
 
 @dataclass

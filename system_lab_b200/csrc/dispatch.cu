@@ -46,6 +46,9 @@ struct WsLayout {
   long scalars;        // float [cap]          per-row scalar travelling with the row (gate prob)
   long out_rows;       // bf16 [cap][H]        expert outputs, pulled by combine
   long out_scalars;    // float [cap]          per-row scalar pulled by combine_scalars
+  long origin;         // int   [cap]          (source rank << 24) | pair index of every received row; < 0: not kept
+  long comb;           // bf16  [T*K][H]       pair-major rows pushed back by the owners' GEMM epilogues
+  long push_flag;      // int   [world]        epoch flags: owner finished pushing its rows
 };
 
 struct PeerTable {
@@ -273,6 +276,8 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
       }
       if (pair_scalar && lane == 0)
         reinterpret_cast<float*>(pb + ws.scalars)[row] = pair_scalar[t * K + k];
+      if (ws.origin >= 0 && lane == 0)           // lets the owner's GEMM epilogue push this row's result straight back
+        reinterpret_cast<int*>(pb + ws.origin)[row] = (me << 24) | (t * K + k);
     }
   }
   // zero this rank's own alignment padding rows (and their scalars): rows [count, roundup(count, pad))
@@ -333,7 +338,9 @@ __global__ void moe_signal_kernel(PeerTable peers, long flag_offset, int world, 
 // ---------------------------------------------------------------- combine (pull)
 // y[t] = sum_k w[t,k] * out_rows_of_owner[row(t,k)]   (w == nullptr: plain sum).  One warp per token;
 // the K rows are requested before any is consumed so K peer loads are in flight per lane.
-template <int KMAX>
+// PUSHED: the rows were already written into this rank's pair-major `comb` region by the owners' GEMM epilogues
+// (row of pair (t, k) = t*K + k); the kernel waits for the owners' push flags and reduces local memory.
+template <int KMAX, bool PUSHED>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ pair_loc,
                    int T, int K, int H, PeerTable peers, WsLayout ws, int world, int me, int epoch, int* status,
@@ -342,7 +349,7 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weig
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
-    const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.out_flag) + threadIdx.x;
+    const int* flag = reinterpret_cast<const int*>(peers.base[me] + (PUSHED ? ws.push_flag : ws.out_flag)) + threadIdx.x;
     if (!wait_flag_ge(flag, epoch, status, limit_ns)) ok = 0;
   }
   __syncthreads();
@@ -366,7 +373,9 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ weig
       if (k < K) {
         const int loc = pair_loc[t * K + k];
         if (loc >= 0) {
-          rows[k] = reinterpret_cast<const bf16x8*>(peers.base[loc >> 24] + ws.out_rows) + (size_t)(loc & 0xFFFFFF) * nvec;
+          rows[k] = PUSHED
+              ? reinterpret_cast<const bf16x8*>(peers.base[me] + ws.comb) + (size_t)(t * K + k) * nvec
+              : reinterpret_cast<const bf16x8*>(peers.base[loc >> 24] + ws.out_rows) + (size_t)(loc & 0xFFFFFF) * nvec;
           w[k] = weights ? weights[t * K + k] : 1.f;
         }
       }
@@ -434,13 +443,14 @@ static WsLayout make_layout(const long* off) {
   WsLayout w;
   w.counts_all = off[0]; w.counts_flag = off[1]; w.data_flag = off[2]; w.out_flag = off[3];
   w.rows = off[4]; w.row_scales = off[5]; w.scalars = off[6]; w.out_rows = off[7]; w.out_scalars = off[8];
+  w.origin = off[9]; w.comb = off[10]; w.push_flag = off[11];
   return w;
 }
 
 extern "C" int slab_moe_count_blocks(int n_pairs) { return (n_pairs + PAIRS_PER_BLOCK - 1) / PAIRS_PER_BLOCK; }
 
 // Phase 1 of a plan: histogram + publish this rank's counts to all peers.  `peer_ptrs` / `ws_offsets` are
-// host arrays (world pointers, 9 region offsets).
+// host arrays (world pointers, 12 region offsets).
 extern "C" int slab_moe_count_publish(const int* topk_idx, int n_pairs, int E, int* block_hist, int* send_counts,
                                       const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
                                       cudaStream_t st) {
@@ -532,13 +542,32 @@ extern "C" int slab_moe_combine(void* y, const float* weights, const int* pair_l
   WsLayout ws = make_layout(ws_offsets);
   if (n_blocks <= 0) n_blocks = 148 * 4;
   if (K <= 2)
-    moe_combine_kernel<2><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+    moe_combine_kernel<2, false><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else if (K <= 4)
-    moe_combine_kernel<4><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+    moe_combine_kernel<4, false><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else if (K <= 8)
-    moe_combine_kernel<8><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+    moe_combine_kernel<8, false><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   else
-    moe_combine_kernel<16><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+    moe_combine_kernel<16, false><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, weights, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+  return (int)cudaGetLastError();
+}
+
+// Reduce the K pushed rows of every token (see PUSHED above); `epoch` is the push epoch of the producing GEMM.
+extern "C" int slab_moe_reduce_pairs(void* y, const int* pair_loc, int T, int K, int H, const long* peer_ptrs,
+                                     const long* ws_offsets, int world, int me, int epoch, int* status, int n_blocks,
+                                     cudaStream_t st) {
+  if (H % 8 || K > 16 || world > MAX_WORLD) return -100;
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  if (n_blocks <= 0) n_blocks = 148 * 4;
+  if (K <= 2)
+    moe_combine_kernel<2, true><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, nullptr, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+  else if (K <= 4)
+    moe_combine_kernel<4, true><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, nullptr, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+  else if (K <= 8)
+    moe_combine_kernel<8, true><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, nullptr, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
+  else
+    moe_combine_kernel<16, true><<<n_blocks, 256, 0, st>>>((__nv_bfloat16*)y, nullptr, pair_loc, T, K, H, pt, ws, world, me, epoch, status, g_wait_limit_ns);
   return (int)cudaGetLastError();
 }
 

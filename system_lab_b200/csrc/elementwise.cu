@@ -668,11 +668,14 @@ static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scal
 extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
                           float* v_scale, void* out_bf16, const float* coef, float* sq_out, long n, int state_kind,
                           float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
-                          cudaStream_t st) {
+                          int ctas_per_sm, cudaStream_t st) {
+  // ctas_per_sm bounds the resident footprint of this grid-stride kernel.  A kernel that fills every thread slot
+  // of every SM (8 x 256) keeps CTAs of kernels launched later on other streams from being scheduled until it
+  // exits; an update that runs beside the backward pass asks for 2-3 and leaves the rest to the compute stream.
   if (n % 128) return -100;
   if (n == 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2};
-  int grid = grid_for(n / 16, 256);
+  int grid = grid_for(n / 16, 256, ctas_per_sm > 0 && ctas_per_sm < 8 ? ctas_per_sm : 8);
   if (p_is_bf16) {
     if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
     else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);

@@ -36,6 +36,14 @@ struct GemmParams {
   __nv_bfloat16* C;
   int accumulate;           // WGRAD: add into C instead of overwriting
   int* status;
+  // push epilogue (FWD / DGRAD): every output row goes straight to the rank its token came from
+  const int* origin;        // [R] (source rank << 24) | pair index, written by the senders' scatter
+  uint8_t* peer[16];        // base of every rank's symmetric workspace
+  long comb_off;            // byte offset of the pair-major [pairs][out_cols] bf16 region in a workspace
+  long flag_off;            // byte offset of the int[world] push flags in a workspace
+  int world, me, epoch;
+  int pairs;                // rows of the pair-major region (a row origin outside it is reported, not written)
+  int* counter;             // CTAs that finished pushing (reset by the last one)
 };
 
 // Shared memory map (exactly the 227 KB a CTA may have): [0, 3072) barriers, TMEM slot, abort flag and the
@@ -96,7 +104,12 @@ __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmPar
   return true;
 }
 
-template <int MODE, int BN>
+// PUSH (FWD / DGRAD only): the epilogue does not store the tile to C.  Each staged 128x64 chunk is written row
+// by row (128 contiguous bytes per row) into the `comb` region of the rank that owns the row's token, at the
+// row's pair index, over NVLink with plain peer stores: the transfer of tile i overlaps the MMAs of tile i+1.
+// When the last CTA has fenced its stores it releases this rank's push flag on every peer; the token owners
+// wait for all flags and reduce their K rows locally (moe_combine_kernel<., true>).
+template <int MODE, int BN, bool PUSH = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
@@ -118,6 +131,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   int* prefix = reinterpret_cast<int*>(smem + L::PREFIX_OFFSET);
   uint8_t* ring = smem + L::RING_OFFSET;
   uint8_t* store_buf = smem + L::STORE_OFFSET;
+  int* origin_s = reinterpret_cast<int*>(smem + 2048);   // PUSH: 2 x 128 row origins (needs E <= 256: prefix ends < 2048)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -236,6 +250,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int r_in_tile = lg * 32 + lane;
     int it = 0;
     int chunk_ctr = 0;                          // staging buffer toggles per 64-column chunk
+    int tile_ctr = 0;
     TileInfo ti;
     for (int t = blockIdx.x; get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
       const int col0 = ti.n_idx * BN;
@@ -245,6 +260,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = (MODE == MODE_WGRAD) ? (ti.m_idx * BM + r_in_tile < p.N) : (tile_row + r_in_tile < p.R);
       const bool empty = (ti.ksteps == 0);      // expert without rows (wgrad): the gradient is zero
       if (empty && direct) continue;
+      int* org_tile = origin_s + (tile_ctr & 1) * BM;
+      if (PUSH) {
+        // padding rows of the segment have no owner; the table is double buffered because a warp may start the
+        // next tile while another still pushes the last chunk of this one
+        const int valid = seg_rows(p, ti.e) - ti.m_idx * BM;
+        org_tile[r_in_tile] = (r_in_tile < valid && row_ok) ? p.origin[tile_row + r_in_tile] : -1;
+        ++tile_ctr;
+      }
       int buf = 0;
       if (!empty) {
         buf = it & 1;
@@ -287,7 +310,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         uint8_t* sb = store_buf + (chunk_ctr & 1) * L::STORE_BYTES;
         // the TMA store that last read this buffer (two chunks ago) must have finished reading it
-        if (store_thread) tma_store_wait_read<1>();
+        if (!PUSH && store_thread) tma_store_wait_read<1>();
         asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -297,9 +320,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // 128-byte swizzle: 16-byte chunk g of row r lives at chunk (g ^ (r & 7))
           *reinterpret_cast<bf16x8*>(sb + r_in_tile * 128 + ((g ^ (r_in_tile & 7)) << 4)) = pack8(f);
         }
-        fence_proxy_async();
+        if (!PUSH) fence_proxy_async();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (store_thread) {
+        if (PUSH) {
+          // 1024 16-byte vectors per chunk, 8 per thread; 8 consecutive lanes write one row's 128 bytes
+          const int et = threadIdx.x - 64;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int idx = q * 128 + et;
+            const int row = idx >> 3, seg = idx & 7;
+            const int org = org_tile[row];
+            const int col = col0 + c + seg * 8;
+            if (org >= 0 && col < out_cols) {
+              const int src = org >> 24, pair = org & 0xFFFFFF;
+              if (src >= p.world || pair >= p.pairs) {         // corrupt table: report, never write
+                atomicCAS(p.status, 0, ST_BAD_INDEX);
+                continue;
+              }
+              const uint4 val = *reinterpret_cast<const uint4*>(sb + row * 128 + ((seg ^ (row & 7)) << 4));
+              uint8_t* dst = p.peer[src] + p.comb_off + ((size_t)pair * out_cols + col) * 2;
+              *reinterpret_cast<uint4*>(dst) = val;
+            }
+          }
+        } else if (store_thread) {
           tma_store_2d(&tmap_c, sb, col0 + c, tile_row);
           tma_store_commit();
         }
@@ -312,7 +355,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ++it;
       }
     }
-    if (store_thread) tma_store_wait<0>();      // all output written before the CTA retires
+    if (PUSH) {
+      // completion: every thread fences its peer stores, the last CTA releases this rank's flag on every peer
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (store_thread) {
+        const int ticket = atomicAdd(p.counter, 1);
+        if (ticket == (int)gridDim.x - 1) {
+          *p.counter = 0;
+          __threadfence_system();
+          for (int r = 0; r < p.world; ++r)
+            st_release_sys(reinterpret_cast<int*>(p.peer[r] + p.flag_off) + p.me, p.epoch);
+        }
+      }
+    } else if (store_thread) {
+      tma_store_wait<0>();                      // all output written before the CTA retires
+    }
   }
 
   // ---------------------------------------------------------------- teardown
@@ -379,7 +437,7 @@ static int sm_count() {
   return n;
 }
 
-template <int MODE, int BN>
+template <int MODE, int BN, bool PUSH = false>
 static int launch(const void* A, const void* B, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   CUtensorMap ma, mb;
@@ -395,13 +453,15 @@ static int launch(const void* A, const void* B, const GemmParams& p, int grid, c
     if ((rc = make_map_bf16(&mb, B, p.R, p.K, BK, 64))) return rc;
   }
   CUtensorMap mc;
-  if (MODE == MODE_WGRAD) {
+  if (PUSH) {
+    mc = ma;                                  // the push epilogue stores with plain peer writes: no output map
+  } else if (MODE == MODE_WGRAD) {
     if ((rc = make_map_bf16(&mc, p.C, (uint64_t)p.E * p.N, p.K, BM, 64))) return rc;
   } else {
     if ((rc = make_map_bf16(&mc, p.C, p.R, (MODE == MODE_FWD) ? p.N : p.K, BM, 64))) return rc;
   }
   static bool attr_set = false;
-  auto kern = grouped_gemm_kernel<MODE, BN>;
+  auto kern = grouped_gemm_kernel<MODE, BN, PUSH>;
   if (!attr_set) {
     SLAB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_set = true;
@@ -433,4 +493,35 @@ extern "C" int slab_grouped_gemm_bf16(int mode, const void* A, const void* B, vo
       return wide ? launch<MODE_WGRAD, 256>(A, B, p, grid, stream) : launch<MODE_WGRAD, 128>(A, B, p, grid, stream);
   }
   return -101;
+}
+
+// Forward (mode 0) or dgrad (mode 1) whose result rows are pushed to the ranks that own the rows' tokens instead
+// of being stored locally.  `origin[r]` = (source rank << 24) | pair index for every valid row, `peer_ptrs` the
+// workspace base of every rank, `comb_off` / `flag_off` byte offsets inside a workspace of the pair-major
+// [pairs][out_cols] bf16 region and of the int[world] push flags.  `counter` is a zero-initialised device int.
+// The caller's matching reduction waits for `epoch` on all flags.  At most 256 experts per rank.
+extern "C" int slab_grouped_gemm_bf16_push(int mode, const void* A, const void* B, const int* seg_offsets,
+                                           const int* seg_counts, int E, int R, int N, int K, int block_n,
+                                           int max_ctas, const int* origin, const long* peer_ptrs, long comb_off,
+                                           long flag_off, int world, int me, int epoch, int pairs, int* counter,
+                                           int* status, cudaStream_t stream) {
+  using namespace slab;
+  if (E > 256 || K % 64 || N % 64 || world > 16 || world < 1 || me < 0 || me >= world) return -100;
+  if (mode != MODE_FWD && mode != MODE_DGRAD) return -101;
+  GemmParams p{seg_offsets, seg_counts, E, R, N, K, nullptr, 0, status};
+  p.origin = origin;
+  for (int i = 0; i < 16; ++i) p.peer[i] = i < world ? reinterpret_cast<uint8_t*>(peer_ptrs[i]) : nullptr;
+  p.comb_off = comb_off;
+  p.flag_off = flag_off;
+  p.world = world;
+  p.me = me;
+  p.epoch = epoch;
+  p.pairs = pairs;
+  p.counter = counter;
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  const bool wide = block_n != 128;
+  if (mode == MODE_FWD)
+    return wide ? launch<MODE_FWD, 256, true>(A, B, p, grid, stream) : launch<MODE_FWD, 128, true>(A, B, p, grid, stream);
+  return wide ? launch<MODE_DGRAD, 256, true>(A, B, p, grid, stream) : launch<MODE_DGRAD, 128, true>(A, B, p, grid, stream);
 }

@@ -213,7 +213,9 @@ class MoEFFN(nn.Module):
                 else self.step_tokens_per_expert + c
         if hasattr(d, "dispatch"):              # fused path: rows and gate probabilities travel together
             xe, pe = d.dispatch(plan, x2, w)
-            out_buf = d.expert_output_buffer()
+            # push mode: the GEMM epilogues write result rows into the token owners' memory themselves;
+            # otherwise the GEMMs write the peer-visible buffer the owners pull from
+            out_buf = d.push_target(plan) if (d.push and ops.use_kernels(x2)) else d.expert_output_buffer()
         else:
             xe = d.dispatch_rows(plan, x2)
             pe = d.dispatch_scalars(plan, w)

@@ -33,6 +33,8 @@ for _name, _sig in {
     "slab_moe_signal_out": "ppiiis",
     "slab_moe_combine": "pppiiippiiipis",
     "slab_moe_combine_scalars": "ppippiiips",
+    "slab_moe_reduce_pairs": "ppiiippiiipis",
+    "slab_grouped_gemm_bf16_push": "ipppp" + "iiii" + "ii" + "pp" + "ll" + "iiii" + "pp" + "s",
 }.items():
     cops.register(_name, _sig)
 
@@ -62,7 +64,8 @@ def compute_layout(ep: int, num_experts: int, topk: int, hidden: int, max_tokens
                          ("rows1", cap * hidden * 2),
                          ("row_scales", cap * (hidden // 128) * 4 if fp8_payload else 256),
                          ("scalars0", cap * 4), ("scalars1", cap * 4), ("out_rows", cap * hidden * 2),
-                         ("out_scalars", cap * 4)):
+                         ("out_scalars", cap * 4), ("origin", cap * 4), ("comb", pairs * hidden * 2),
+                         ("push_flag", ep * 4)):
         off[name] = cur
         cur = _align(cur + nbytes)
     return cap, off, cur
@@ -82,6 +85,7 @@ class FusedPlan:
     meta: torch.Tensor                # [4] int32: rows used on this rank
     tokens_per_expert_global: torch.Tensor   # [E] pairs routed from this rank
     num_rows: int                     # == capacity (host-side bound)
+    origin: torch.Tensor | None = None       # [capacity] int32: (source rank << 24) | pair index of received rows
 
     @property
     def e_local(self) -> int:
@@ -92,7 +96,7 @@ class FusedDispatcher:
     def __init__(self, mesh, num_experts: int, topk: int, hidden: int, max_tokens: int, pad_to: int = 128,
                  device=None, dtype=torch.bfloat16, capacity_factor: float = 0.0, workspace=None,
                  ep: int | None = None, ep_rank: int | None = None, fp8_payload: bool = False,
-                 clone_outputs: bool = False):
+                 clone_outputs: bool = False, push: bool = False):
         self.E, self.K, self.H, self.T = num_experts, topk, hidden, max_tokens
         self.ep = mesh.ep if ep is None else ep
         self.me = mesh.ep_rank if ep_rank is None else ep_rank
@@ -101,6 +105,10 @@ class FusedDispatcher:
         self.dtype = dtype
         self.fp8 = fp8_payload
         self.clone_outputs = clone_outputs
+        # push: expert GEMM epilogues write result rows straight into the token owners' memory (see PushTarget)
+        self.push = push
+        self.push_epoch = 0
+        self._pending_push = {}           # GEMM mode (0 fwd / 1 dgrad) -> push epoch not yet reduced by its consumer
         if dtype != torch.bfloat16:
             raise ValueError("the fused dispatcher moves bf16 rows")
         self.capacity, off, cur = compute_layout(self.ep, num_experts, topk, hidden, max_tokens, self.pad,
@@ -129,6 +137,9 @@ class FusedDispatcher:
                         workspace.view(off["scalars1"], (cap,), torch.float32)]
         self.out_rows = workspace.view(off["out_rows"], (cap, H), torch.bfloat16)
         self.out_scalars = workspace.view(off["out_scalars"], (cap,), torch.float32)
+        self.origin = workspace.view(off["origin"], (cap,), torch.int32)
+        self.comb = workspace.view(off["comb"], (pairs, H), torch.bfloat16)
+        self.push_counter = torch.zeros(1, **i32)
         if fp8_payload:
             self.rows_fp8 = workspace.view(off["rows0"], (cap, H), torch.float8_e4m3fn)
             self.row_scales = workspace.view(off["row_scales"], (cap, H // 128), torch.float32)
@@ -136,8 +147,10 @@ class FusedDispatcher:
     def _layout(self, channel: int):
         o = self.off
         vals = [o["counts_all"], o["counts_flag"], o[f"data_flag{channel}"], o["out_flag"], o[f"rows{channel}"],
-                o["row_scales"], o[f"scalars{channel}"], o["out_rows"], o["out_scalars"]]
-        return (ctypes.c_long * 9)(*vals)
+                o["row_scales"], o[f"scalars{channel}"], o["out_rows"], o["out_scalars"],
+                o["origin"] if channel == 0 else -1,       # only forward rows are ever pushed back
+                o["comb"], o["push_flag"]]
+        return (ctypes.c_long * 12)(*vals)
 
     def _next_epoch(self) -> int:
         self.epoch += 1
@@ -210,6 +223,17 @@ class FusedDispatcher:
                   self.status, cops.stream())
         return s.view(plan.num_tokens, plan.topk)
 
+    def reduce_pairs(self, plan: FusedPlan, push_epoch: int) -> torch.Tensor:
+        """Sum of the K rows the owners pushed for every token (waits for all owners' push flags)."""
+        y = torch.empty(plan.num_tokens, self.H, dtype=torch.bfloat16, device=self.device)
+        cops.call("slab_moe_reduce_pairs", y, plan.pair_loc, plan.num_tokens, plan.topk, self.H,
+                  ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, push_epoch,
+                  self.status, 0, cops.stream())
+        return y
+
+    def push_target(self, plan: FusedPlan) -> "PushTarget":
+        return PushTarget(self, plan)
+
     def stage_out_rows(self, ye: torch.Tensor) -> None:
         if ye.data_ptr() != self.out_rows.data_ptr():
             self.out_rows[:ye.shape[0]].copy_(ye)
@@ -236,6 +260,29 @@ class FusedDispatcher:
         return _FusedCombine.apply(ye, weights, self, plan, dead and weights is None)
 
 
+class PushTarget:
+    """Destination of an expert GEMM whose epilogue pushes every result row to the rank that owns the row's
+    token (``csrc/gemm_tcgen05.cu``, PUSH epilogue).  Passed as ``out=`` (second expert GEMM, forward combine)
+    or ``dgrad_out=`` (first expert GEMM, backward of dispatch) of ``ops.grouped_linear``.  ``launch`` runs the
+    GEMM and records the push epoch the matching ``reduce_pairs`` has to wait for."""
+
+    def __init__(self, d: "FusedDispatcher", plan: FusedPlan):
+        self.d, self.plan = d, plan
+        self.epoch = 0
+
+    def launch(self, mode: int, a: torch.Tensor, b: torch.Tensor, offsets, counts, n: int, k: int, block_n: int):
+        d = self.d
+        out_cols = n if mode == 0 else k
+        if out_cols != d.H:
+            raise ValueError(f"pushed rows are {out_cols} wide, the dispatcher moves {d.H}")
+        d.push_epoch += 1
+        self.epoch = d.push_epoch
+        d._pending_push[mode] = self.epoch
+        cops.call("slab_grouped_gemm_bf16_push", mode, a, b, offsets, counts, offsets.numel(), a.shape[0], n, k,
+                  block_n, 0, self.plan.origin, ctypes.addressof(d._peer_ptrs), d.off["comb"], d.off["push_flag"],
+                  d.ep, d.me, self.epoch, d.T * d.K, d.push_counter, d.status, cops.stream())
+
+
 class _FusedDispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs, d: FusedDispatcher, plan: FusedPlan):
@@ -245,18 +292,22 @@ class _FusedDispatch(torch.autograd.Function):
         ep = d.scatter(plan, xc, pc, channel=0)
         d.wait_rows(0, ep)
         xe, pe = d.rows[0], d.scalars[0]
+        plan.origin = d.origin
         if d.clone_outputs:
             xe, pe = xe.clone(), pe.clone()
+            plan.origin = d.origin.clone()
         return xe, (pe if probs is not None else None)
 
     @staticmethod
     def backward(ctx, g_xe, g_pe):
         d, plan = ctx.d, ctx.plan
-        d.stage_out_rows(g_xe.contiguous())
+        pushed = d._pending_push.pop(1, None)             # epoch if the fc1 dgrad already pushed its rows to the owners
+        if pushed is None:
+            d.stage_out_rows(g_xe.contiguous())
         if ctx.has_probs and g_pe is not None:
             d.out_scalars.copy_(g_pe)
         ep = d.signal_out()
-        gx = d.pull_rows(plan, ep)
+        gx = d.reduce_pairs(plan, pushed) if pushed is not None else d.pull_rows(plan, ep)
         gp = d.pull_scalars(plan, ep) if (ctx.has_probs and g_pe is not None) else None
         return gx, gp, None, None
 
@@ -271,6 +322,11 @@ class _FusedCombine(torch.autograd.Function):
         ctx.weighted = weights is not None
         if dead:
             return torch.empty(plan.num_tokens, d.H, dtype=torch.bfloat16, device=d.device)
+        pushed = d._pending_push.pop(0, None)             # epoch if the fc2 GEMM already pushed its rows to the owners
+        if pushed is not None:
+            if weights is not None:
+                raise NotImplementedError("pushed rows are reduced unweighted: apply the gate inside SwiGLU")
+            return d.reduce_pairs(plan, pushed)
         d.stage_out_rows(ye.contiguous())
         ep = d.signal_out()
         return d.pull_rows(plan, ep, weights)

@@ -188,7 +188,9 @@ def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: i
             lo, hi = w0 + b * bin_w, w0 + (b + 1) * bin_w
             mix[b][cat] += max(0.0, min(e, hi) - max(s, lo))
     total_kernel = sum(by_cat.values())
+    gaps = _gap_report(kernels, w0, w1, by_stream)
     return {
+        "main_stream_gaps": gaps,
         "trace": path, "window": window, "window_ms": span / 1e3,
         "stream_busy_ms": {k: v / 1e3 for k, v in sorted(stream_busy.items(), key=lambda kv: -kv[1])},
         "oversubscription_pct": 100.0 * (sum(stream_busy.values()) / max(_union_len(comp_iv + comm_iv), 1e-9) - 1.0),
@@ -209,6 +211,62 @@ def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: i
     }
 
 
+def _short(name: str) -> str:
+    name = name.split("(")[0]
+    for pre in ("void ", "slab::", "at::native::"):
+        name = name.replace(pre, "")
+    return name[:60]
+
+
+def _gap_report(kernels, w0: float, w1: float, by_stream: dict, min_gap_us: float = 5.0, top: int = 12) -> dict:
+    """Idle gaps of the busiest stream inside the window: how much of the step the critical stream spends
+    not running anything, how much of that another stream covers, and which kernel pairs the gaps sit between
+    (a large total under one pair points at a host sync, an event wait or launch latency at that spot)."""
+    if not by_stream:
+        return {}
+    main = max(by_stream, key=lambda k: _union_len(by_stream[k]))
+    evs = sorted((max(ts, w0), min(ts + dur, w1), name) for ts, dur, name, st in kernels
+                 if st == main and min(ts + dur, w1) > max(ts, w0))
+    others = sorted(iv for st, ivs in by_stream.items() if st != main for iv in ivs)
+    o_starts = [iv[0] for iv in others]
+
+    def covered(a: float, b: float) -> float:
+        tot, i = 0.0, max(bisect.bisect_left(o_starts, a) - 64, 0)
+        ivs = []
+        while i < len(others) and others[i][0] < b:
+            if others[i][1] > a:
+                ivs.append((max(others[i][0], a), min(others[i][1], b)))
+            i += 1
+        return _union_len(ivs) if ivs else tot
+
+    pairs, pair_n = defaultdict(float), defaultdict(int)
+    total = cov = 0.0
+    hist = {"5-20us": 0.0, "20-100us": 0.0, "100us-1ms": 0.0, ">1ms": 0.0}
+    end, prev = (evs[0][0], "window start") if evs else (w0, "window start")
+    end = w0
+    for s, e, name in evs:
+        g = s - end
+        if g >= min_gap_us:
+            total += g
+            cov += covered(end, s)
+            key = f"{_short(prev)} -> {_short(name)}"
+            pairs[key] += g
+            pair_n[key] += 1
+            hist["5-20us" if g < 20 else "20-100us" if g < 100 else "100us-1ms" if g < 1000 else ">1ms"] += g
+        if e > end:
+            end, prev = e, name
+    tail = w1 - end
+    if tail >= min_gap_us:
+        total += tail
+        cov += covered(end, w1)
+        pairs[f"{_short(prev)} -> window end"] += tail
+        pair_n[f"{_short(prev)} -> window end"] += 1
+    return {"stream": str(main), "gap_ms": total / 1e3, "gap_covered_by_other_streams_ms": cov / 1e3,
+            "by_size_ms": {k: v / 1e3 for k, v in hist.items()},
+            "top_pairs": [{"between": k, "ms": v / 1e3, "count": pair_n[k]}
+                          for k, v in sorted(pairs.items(), key=lambda kv: -kv[1])[:top]]}
+
+
 def format_report(r: dict) -> str:
     out = [f"trace   : {r['trace']}", f"window  : {r['window']}  ({r['window_ms']:.2f} ms)",
            f"compute busy {r['compute_busy_pct']:.1f} %   idle {r['idle_pct']:.1f} %   "
@@ -220,6 +278,12 @@ def format_report(r: dict) -> str:
     out += [f"  {k:20s} {v:9.2f}  {r['category_pct_of_kernel_time'][k]:5.1f} %" for k, v in r["category_ms"].items()]
     out += ["", "top kernels:"]
     out += [f"  {k['ms']:9.2f} ms  x{k['count']:<5d} {k['name']}" for k in r["top_kernels"]]
+    g = r.get("main_stream_gaps") or {}
+    if g:
+        out += ["", f"idle gaps of stream {g['stream']}: {g['gap_ms']:.2f} ms "
+                    f"({g['gap_covered_by_other_streams_ms']:.2f} ms of it covered by other streams); by gap size: "
+                    + ", ".join(f"{k} {v:.2f}" for k, v in g["by_size_ms"].items())]
+        out += [f"  {p['ms']:9.2f} ms  x{p['count']:<5d} {p['between']}" for p in g["top_pairs"]]
     return "\n".join(out)
 
 

@@ -28,7 +28,7 @@ _SIGS = {
     "slab_quant_128x128": "pppiiis",
     "slab_quant_rowwise": "ppplis",
     "slab_sumsq": "pilfps",
-    "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "s",
+    "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "is",
     "slab_router_topk": "ppppiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
@@ -411,8 +411,15 @@ class _GroupedLinear(torch.autograd.Function):
         e, n, k = w.shape
         a = a.contiguous()
         w = w.contiguous() if not w.is_contiguous() else w
-        if dead:           # node only: the caller never reads the product
-            out = out if out is not None else torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
+        push = out if hasattr(out, "launch") else None      # a dispatcher PushTarget: rows go to the token owners
+        if push is not None:
+            out = None
+        if dead or push is not None:
+            # node only: the caller never reads the product (recomputed forward), or the rows leave through the
+            # push epilogue; either way the returned tensor is a shape carrier without storage behind every row
+            if push is not None and not dead:
+                push.launch(0, a, w, offsets, counts, n, k, _pick_bn(n))
+            out = out if out is not None else torch.empty(1, dtype=torch.bfloat16, device=a.device).expand(a.shape[0], n)
         else:
             out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
         ctx.save_for_backward(a, w, offsets, counts)
@@ -428,11 +435,15 @@ class _GroupedLinear(torch.autograd.Function):
         da = dw = None
         if ctx.needs_input_grad[0]:
             do = ctx.dgrad_out
-            if do is not None and (do.shape[0] < g.shape[0] or do.shape[1] != k):
-                do = None
-            da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, out=do, block_n=_pick_bn(k))
-            if do is not None:
-                da = do[:g.shape[0]]
+            if hasattr(do, "launch"):                  # PushTarget: the input gradient goes to the token owners
+                do.launch(1, g, w, offsets, counts, n, k, _pick_bn(k))
+                da = torch.empty(1, dtype=torch.bfloat16, device=g.device).expand(g.shape[0], k)
+            else:
+                if do is not None and (do.shape[0] < g.shape[0] or do.shape[1] != k):
+                    do = None
+                da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, out=do, block_n=_pick_bn(k))
+                if do is not None:
+                    da = do[:g.shape[0]]
         if ctx.needs_input_grad[1]:
             mg = getattr(ctx.w_ref, "main_grad", None)
             if mg is not None:
@@ -450,7 +461,8 @@ def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out
         from . import _GroupedLinearRef
         return _GroupedLinearRef.apply(a, w, offsets, counts, dead)
     offsets, counts = _check_segments(offsets, counts)
-    if out is not None and (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
+    if out is not None and not hasattr(out, "launch") and \
+            (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
         out = None
     res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead)
     return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
@@ -544,9 +556,11 @@ def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
 _KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
 
 
-def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, sq_out=None) -> None:
+def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, sq_out=None,
+               ctas_per_sm: int = 0) -> None:
     """Fused AdamW on one flat shard: reads the (fp32 or bf16) gradient shard, updates moments (any storage
-    format) and the master/weight shard, and writes the bf16 compute copy in the same pass."""
+    format) and the master/weight shard, and writes the bf16 compute copy in the same pass.  ``ctas_per_sm``
+    (1..7) limits the kernel's resident CTAs so that it can run beside compute kernels of another stream."""
     p = group.shard
     n = p.numel()
     g = group.grad_shard
@@ -560,4 +574,5 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, 
     call("slab_adamw", p, 1 if p.dtype == torch.bfloat16 else 0, g, 1 if g.dtype == torch.bfloat16 else 0,
          m.data, v.data, getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, sq_out, n,
          _KIND[m.kind],
-         float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2), stream())
+         float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
+         int(ctas_per_sm), stream())

@@ -178,7 +178,7 @@ class Engine:
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,
                                              clone_outputs=not (self.recompute or self.selective),
-                                             capacity_factor=m.moe_capacity_factor)
+                                             capacity_factor=m.moe_capacity_factor, push=m.moe_combine_push)
                 layer.ffn.dispatcher = shared
             else:
                 if shared is None:

@@ -81,6 +81,7 @@ class ShardedAdamW:
         self._prev_norm: torch.Tensor | None = None     # for delayed clipping in optimizer-in-backward mode
         self._sq_accum: torch.Tensor | None = None
         self._side = None                 # side stream for in-backward updates
+        self.background_ctas = 2          # resident CTAs per SM of a side-stream update (of 8 thread-slot-filling ones)
         self._coef_for_step = None
 
     # ---- gradient norm ------------------------------------------------------------
@@ -125,9 +126,11 @@ class ShardedAdamW:
                                     sq_out, lr=lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
                                     weight_decay=self.weight_decay, step=self.step_count)
 
-    def _update_group(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor | None = None) -> None:
+    def _update_group(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor | None = None,
+                      background: bool = False) -> None:
         """``sq_out``: also accumulate ``sum(grad^2) / replication`` of this group there (fused into the
-        kernel on the GPU path)."""
+        kernel on the GPU path).  ``background``: the update shares the GPU with another stream's compute, so
+        its kernel keeps only a few CTAs resident per SM instead of filling every thread slot."""
         if g.grad_shard is None:
             return
         from .. import ops
@@ -138,7 +141,7 @@ class ShardedAdamW:
                 self._add_sumsq(sq_out, g)
             cops.adamw_flat(g, self.m[g.name], self.v[g.name], coef, lr=lr, beta1=self.beta1, beta2=self.beta2,
                             eps=self.eps, weight_decay=self.weight_decay, step=self.step_count,
-                            sq_out=sq_out if fuse else None)
+                            sq_out=sq_out if fuse else None, ctas_per_sm=self.background_ctas if background else 0)
         else:
             if sq_out is not None:
                 sq_out += g.grad_shard.float().pow(2).sum() / self._replication(g)
@@ -187,7 +190,7 @@ class ShardedAdamW:
             for g in unit.groups:
                 if g.grad_shard is not None:
                     g.grad_shard.record_stream(self._side)
-                self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum)
+                self._update_group(g, coef, self._cur_lr, sq_out=self._sq_accum, background=True)
 
     def end_step_in_backward(self) -> torch.Tensor:
         if self._side is not None:

@@ -131,3 +131,82 @@ def test_missing_flag_times_out_with_status_not_hang():
         cops.check_status()
     cops.check_status()   # status word is cleared; the context is still usable
     assert torch.ones(4, device="cuda").sum().item() == 4
+
+
+@pytest.mark.parametrize("world,T,K,E,H,F", [(1, 200, 2, 8, 256, 128), (2, 300, 4, 16, 512, 256), (4, 257, 8, 32, 1024, 192)])
+def test_gemm_push_epilogue_matches_pull_combine(world, T, K, E, H, F):
+    """Expert GEMMs whose epilogue pushes result rows to the token owners (forward: act @ w2^T, width H; dgrad:
+    dY @ w1, width H), reduced by the owners, against an fp32 oracle on the same bf16 inputs.  Ranks are
+    emulated phase by phase: every push GEMM finishes (and releases its flags) before any reduction starts."""
+    from system_lab_b200.ops import cuda as cops
+    torch.manual_seed(10 + world)
+    ds = _make(world, T, K, E, H)
+    dev = torch.device("cuda")
+    e_local = E // world
+    idx = [torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int() for _ in range(world)]
+    x = [torch.randn(T, H, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    pubs = [d.plan_publish(i) for d, i in zip(ds, idx)]
+    plans = [d.plan_finish(*p) for d, p in zip(ds, pubs)]
+    eps = [d.scatter(pl, xx, None, 0) for d, pl, xx in zip(ds, plans, x)]
+    for d, e in zip(ds, eps):
+        d.wait_rows(0, e)
+    for d, pl in zip(ds, plans):
+        pl.origin = d.origin
+    # the origin table names the sender and the pair of every received row
+    torch.cuda.synchronize()
+    exp = _expected_layout([i.cpu() for i in idx], world, E)
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        org = ds[owner].origin.cpu()
+        for row, (src, p) in list(rows.items())[::5]:
+            assert org[row].item() == (src << 24) | p
+    # ---- forward: per-owner activations [cap, F] (zero on padding rows), weights [e_local, H, F]
+    act = [torch.zeros(d.capacity, F, device=dev, dtype=torch.bfloat16) for d in ds]
+    w2 = [(0.05 * torch.randn(e_local, H, F, device=dev)).to(torch.bfloat16) for _ in range(world)]
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        for o, c in zip(offs, cnts):
+            act[owner][o:o + c] = torch.randn(c, F, device=dev)
+    for owner, d in enumerate(ds):
+        tgt = d.push_target(plans[owner])
+        tgt.launch(0, act[owner], w2[owner], plans[owner].expert_offsets, plans[owner].expert_counts, H, F, 256)
+        assert d._pending_push.pop(0) == tgt.epoch == 1
+    got = [d.reduce_pairs(pl, 1) for d, pl in zip(ds, plans)]
+    torch.cuda.synchronize()
+    cops.check_status()
+
+    def oracle(vals, weights, transpose):
+        # vals[owner][row] -> result row = vals @ W ; summed over the K pairs of every source token
+        want = [torch.zeros(T, H, device=dev) for _ in range(world)]
+        for owner, (offs, cnts, rows) in enumerate(exp):
+            for j, (o, c) in enumerate(zip(offs, cnts)):
+                if not c:
+                    continue
+                wj = weights[owner][j].float()
+                res = vals[owner][o:o + c].float() @ (wj.t() if transpose else wj)
+                res = res.to(torch.bfloat16).float()           # each pushed row is rounded to bf16 once
+                for i in range(c):
+                    src, p = rows[o + i]
+                    want[src][p // K] += res[i]
+        return want
+
+    want = oracle(act, w2, True)
+    for r in range(world):
+        err = (got[r].float() - want[r]).abs().max().item()
+        assert err <= 2e-2 * want[r].abs().max().item() + 1e-3, f"fwd rank {r}: {err}"
+    # ---- dgrad: dY [cap, 2F'] with N = 256 columns, weights [e_local, N, H]; result width H
+    N = 256
+    dy = [torch.zeros(d.capacity, N, device=dev, dtype=torch.bfloat16) for d in ds]
+    w1 = [(0.05 * torch.randn(e_local, N, H, device=dev)).to(torch.bfloat16) for _ in range(world)]
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        for o, c in zip(offs, cnts):
+            dy[owner][o:o + c] = torch.randn(c, N, device=dev)
+    for owner, d in enumerate(ds):
+        d.push_target(plans[owner]).launch(1, dy[owner], w1[owner], plans[owner].expert_offsets,
+                                           plans[owner].expert_counts, N, H, 128)
+        assert d._pending_push.pop(1) == 2
+    got = [d.reduce_pairs(pl, 2) for d, pl in zip(ds, plans)]
+    torch.cuda.synchronize()
+    cops.check_status()
+    want = oracle(dy, w1, False)
+    for r in range(world):
+        err = (got[r].float() - want[r]).abs().max().item()
+        assert err <= 2e-2 * want[r].abs().max().item() + 1e-3, f"dgrad rank {r}: {err}"

@@ -102,14 +102,17 @@ def train_equivalence(rank, world):
     from system_lab_b200.ops import cuda as cops
     from system_lab_b200.trainer.loop import Trainer
     out = {}
-    for disp in ("alltoall", "fused"):
+    # fused+push: the expert GEMM epilogues push result rows to the token owners (with the selective recompute
+    # that skips the dead second GEMM and combine in the recomputed forward)
+    for name, disp, push, gran in (("alltoall", "alltoall", "false", "full"), ("fused", "fused", "false", "full"),
+                                   ("fused+push", "fused", "true", "selective")):
         cfg = Config.load(preset="qwen3-30b-a3b", overrides=[
             "num_layers=2", "num_experts=16", "seq_length=512", "vocab_size=4096", "micro_batch_size=2",
-            f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}", "recompute_granularity=full",
-            "device=cuda", f"moe_token_dispatcher_type={disp}"])
-        tr = Trainer(cfg) if disp == "alltoall" else Trainer(cfg, mesh=mesh, device=dev)
+            f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}", f"recompute_granularity={gran}",
+            "device=cuda", f"moe_token_dispatcher_type={disp}", f"moe_combine_push={push}"])
+        tr = Trainer(cfg) if name == "alltoall" else Trainer(cfg, mesh=mesh, device=dev)
         mesh, dev = tr.mesh, tr.device
-        out[disp] = [float(tr.train_step()["loss"]) for _ in range(3)]
+        out[name] = [float(tr.train_step()["loss"]) for _ in range(3)]
         torch.cuda.synchronize()
         cops.check_status()
         del tr
@@ -154,3 +157,4 @@ def test_training_loss_matches_between_dispatchers():
     res = _run("train_equivalence", world)
     for r in res:
         assert r["fused"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
+        assert r["fused+push"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
