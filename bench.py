@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--ep", type=int, default=0, help="expert parallel size (default: all data ranks)")
     ap.add_argument("--gbs", type=int, default=0, help="global batch in sequences (default: seqs-per-gpu x N)")
     ap.add_argument("--mbs", type=int, default=0, help="micro-batch in sequences (default: seqs-per-gpu)")
+    ap.add_argument("--no-keep-dispatched", action="store_true",
+                    help="never keep dispatched rows for the recomputed block, even when memory allows")
     ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
@@ -95,7 +97,7 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def choose_memory_plan(cfg, world: int, force: str = "") -> dict:
+def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = True) -> dict:
     """Highest-fidelity optimizer/weight layout that fits 92 % of 180 GB per GPU."""
     from system_lab_b200.pilot.constraints import estimate_memory
     plans = [
@@ -118,6 +120,16 @@ def choose_memory_plan(cfg, world: int, force: str = "") -> dict:
             last = {"name": name, "recompute": gran, "est_gb": round(est["total_bytes"] / 2**30, 1),
                     "fits": est["fits"]}
             if est["fits"]:
+                if allow_keep and gran == "selective" and cfg.model.num_experts > 0 \
+                        and cfg.model.moe_keep_dispatched_factor == 0:
+                    # spare memory buys speed: keep every layer's dispatched rows so the recomputed block needs
+                    # no second plan exchange and dispatch; -1 = sized from the rows in use during the first step
+                    cfg.model.moe_keep_dispatched_factor = -1.0
+                    est2 = estimate_memory(cfg, world)
+                    if est2["total_bytes"] <= 0.75 * est2["hbm_bytes"]:       # optional: only with real headroom
+                        last.update(keep_dispatched="auto", est_gb=round(est2["total_bytes"] / 2**30, 1))
+                    else:
+                        cfg.model.moe_keep_dispatched_factor = 0.0
                 return last
     return last
 
@@ -150,7 +162,7 @@ def main() -> int:
     if args.balanced_routing:
         ov.append("moe_router_force_load_balancing=true")
     cfg = Config.load(preset=args.preset, overrides=ov + list(args.overrides))
-    plan = choose_memory_plan(cfg, n, args.plan)
+    plan = choose_memory_plan(cfg, n, args.plan, not args.no_keep_dispatched)
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
                       cfg.parallel.context_parallel_size)
@@ -262,6 +274,7 @@ def main() -> int:
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
+            "kept_dispatch_rows": trainer.kept_rows,
         }
         print(json.dumps(line))
     if world > 1:

@@ -91,7 +91,8 @@ class ModelConfig:
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
     moe_router_force_load_balancing: bool = False  # benchmarking aid: route by fixed random logits
     moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
-    moe_combine_push: bool = False       # expert GEMM epilogues push result rows to the token owners (fused combine)
+    moe_combine_push: bool = True        # expert GEMM epilogues push result rows to the token owners (fused combine)
+    moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = x balanced load, <0 = sized from the first step, 0 = off
 
 
 @dataclass

@@ -318,6 +318,14 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 }
 
+// Rows in use beyond a caller's fixed-size copy of the receive buffer are reported, never silently cut.
+__global__ void moe_check_rows_kernel(const int* __restrict__ meta, int limit, int* status, int* rows_seen) {
+  if (threadIdx.x == 0) {
+    if (rows_seen) atomicMax(rows_seen, meta[0]);             // high-water mark, read by the host between steps
+    if (limit > 0 && meta[0] > limit) atomicCAS(status, 0, ST_CAPACITY);
+  }
+}
+
 // ---------------------------------------------------------------- wait / signal (one small block)
 __global__ void moe_wait_flags_kernel(PeerTable peers, long flag_offset, int world, int me, int epoch, int* status,
                                       unsigned long long limit_ns) {
@@ -505,6 +513,11 @@ extern "C" int slab_moe_scatter(const void* x, const float* pair_scalar, const f
     else SLAB_SCATTER(false, 32);
   }
 #undef SLAB_SCATTER
+  return (int)cudaGetLastError();
+}
+
+extern "C" int slab_moe_check_rows(const int* meta, int limit, int* status, int* rows_seen, cudaStream_t st) {
+  moe_check_rows_kernel<<<1, 32, 0, st>>>(meta, limit, status, rows_seen);
   return (int)cudaGetLastError();
 }
 

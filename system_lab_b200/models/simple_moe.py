@@ -53,6 +53,9 @@ def seeded_normal_(t: torch.Tensor, std: float, base_seed: int, name: str) -> No
 # True while a layer's forward is being re-run inside backward (activation recompute): statistics that are
 # collected once per micro-batch (expert load) skip the replay.
 RECOMPUTE_PHASE = [False]
+# State a recomputed block keeps between its two runs: a dict owned by the autograd node, visible to the modules
+# inside the block while either run is in progress (None outside).
+KEPT = [None]
 
 _BALANCE_TABLES: dict = {}
 
@@ -182,6 +185,7 @@ class MoEFFN(nn.Module):
         self.shared = DenseFFN(h, cfg.moe_shared_expert_intermediate_size) \
             if cfg.moe_shared_expert_intermediate_size else None
         self.dispatcher = None            # set by the engine (needs the process group)
+        self.keep_dispatched = False      # set by the engine: a recomputed block reuses the rows of its first run
         self.aux = None                   # last aux loss (added to the objective by the trainer)
         self.last_tokens_per_expert = None
         self.step_tokens_per_expert = None   # summed over the micro-batches of the current step
@@ -205,13 +209,21 @@ class MoEFFN(nn.Module):
                     else torch.sigmoid(logits)
             self.aux = ref.aux_loss(scores, idx.long(), cfg.num_experts, cfg.moe_aux_loss_coeff)
         d = self.dispatcher
-        plan = d.plan(idx)
+        kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
+        reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
+        plan = kept["plan"] if reuse else d.plan(idx)
         self.last_tokens_per_expert = plan.tokens_per_expert_global
         if not RECOMPUTE_PHASE[0]:
             c = plan.tokens_per_expert_global
             self.step_tokens_per_expert = c.clone() if self.step_tokens_per_expert is None \
                 else self.step_tokens_per_expert + c
-        if hasattr(d, "dispatch"):              # fused path: rows and gate probabilities travel together
+        if reuse:
+            # the dispatched rows of the first run were kept: no plan exchange and no second dispatch, only the
+            # autograd link from the rows back to the tokens (its backward is the usual exchange of gradients)
+            xe, pe = d.redispatch_kept(plan, x2, w, kept["xe"], kept["pe"])
+            out_buf = d.push_target(plan) if (getattr(d, "push", False) and ops.use_kernels(x2)) else \
+                (d.expert_output_buffer() if hasattr(d, "expert_output_buffer") else None)
+        elif hasattr(d, "dispatch"):            # fused path: rows and gate probabilities travel together
             xe, pe = d.dispatch(plan, x2, w)
             # push mode: the GEMM epilogues write result rows into the token owners' memory themselves;
             # otherwise the GEMMs write the peer-visible buffer the owners pull from
@@ -220,6 +232,11 @@ class MoEFFN(nn.Module):
             xe = d.dispatch_rows(plan, x2)
             pe = d.dispatch_scalars(plan, w)
             out_buf = None
+        if kept is not None and not RECOMPUTE_PHASE[0] and not torch.is_grad_enabled():
+            kept["plan"] = plan
+            kept["xe"], kept["pe"] = d.keep_dispatched(plan, xe, pe)
+        elif getattr(d, "auto_keep", False) and not RECOMPUTE_PHASE[0]:
+            d.note_rows_in_use(plan)             # sizing information for the trainer's keep decision
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 dgrad_out=out_buf)
         act = ops.swiglu_probs(h1, pe, rows_dev=getattr(plan, "meta", None))
@@ -251,19 +268,27 @@ class _Recompute(torch.autograd.Function):
     @staticmethod
     def forward(ctx, fn, *inputs):
         ctx.fn = fn
+        ctx.kept = {}
         ctx.save_for_backward(*inputs)
-        with torch.no_grad():
-            return fn(*inputs)
+        KEPT[0] = ctx.kept
+        try:
+            with torch.no_grad():
+                return fn(*inputs)
+        finally:
+            KEPT[0] = None
 
     @staticmethod
     def backward(ctx, g):
         ins = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
         prev, RECOMPUTE_PHASE[0] = RECOMPUTE_PHASE[0], True
+        KEPT[0] = ctx.kept
         try:
             with torch.enable_grad():
                 out = ctx.fn(*ins)
         finally:
             RECOMPUTE_PHASE[0] = prev
+            KEPT[0] = None
+            ctx.kept = None
         torch.autograd.backward(out, g)
         return (None,) + tuple(t.grad for t in ins)
 

@@ -143,6 +143,18 @@ class AllToAllDispatcher:
             return _CombineRows.apply(ye, self, plan, dead)
         return _CombineRowsWeighted.apply(ye, weights, self, plan)
 
+    def keep_dispatched(self, plan: RoutingPlan, xe: torch.Tensor, pe: torch.Tensor | None):
+        """What a recomputed block keeps of its first dispatch (the all-to-all results are fresh tensors)."""
+        return xe.detach(), (pe.detach() if pe is not None else None)
+
+    def redispatch_kept(self, plan: RoutingPlan, x: torch.Tensor, probs: torch.Tensor | None, xs: torch.Tensor,
+                        ps: torch.Tensor | None):
+        """Differentiable stand-in for the two dispatch calls that moves nothing forward: returns the kept
+        rows / scalars; the backward passes are those of ``dispatch_rows`` / ``dispatch_scalars``."""
+        xe = _KeptRows.apply(x, xs, self, plan)
+        pe = _KeptScalars.apply(probs, ps, self, plan) if probs is not None else None
+        return xe, pe
+
     def combine_scalars(self, plan: RoutingPlan, se: torch.Tensor) -> torch.Tensor:
         return _CombineScalars.apply(se, self, plan)
 
@@ -160,6 +172,28 @@ class _DispatchRows(torch.autograd.Function):
         d, plan = ctx.d, ctx.plan
         back = d._return_pairs(plan, g.contiguous())
         return back.reshape(plan.num_tokens, plan.topk, -1).sum(1), None, None
+
+
+class _KeptRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, xs, d, plan):
+        ctx.d, ctx.plan = d, plan
+        return xs.view_as(xs)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _DispatchRows.backward(ctx, g) + (None,)
+
+
+class _KeptScalars(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, p, ps, d, plan):
+        ctx.d, ctx.plan = d, plan
+        return ps.view_as(ps)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _DispatchScalars.backward(ctx, g) + (None,)
 
 
 class _DispatchScalars(torch.autograd.Function):

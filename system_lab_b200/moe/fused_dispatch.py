@@ -34,6 +34,7 @@ for _name, _sig in {
     "slab_moe_combine": "pppiiippiiipis",
     "slab_moe_combine_scalars": "ppippiiips",
     "slab_moe_reduce_pairs": "ppiiippiiipis",
+    "slab_moe_check_rows": "pipps",
     "slab_grouped_gemm_bf16_push": "ipppp" + "iiii" + "ii" + "pp" + "ll" + "iiii" + "pp" + "s",
 }.items():
     cops.register(_name, _sig)
@@ -96,7 +97,7 @@ class FusedDispatcher:
     def __init__(self, mesh, num_experts: int, topk: int, hidden: int, max_tokens: int, pad_to: int = 128,
                  device=None, dtype=torch.bfloat16, capacity_factor: float = 0.0, workspace=None,
                  ep: int | None = None, ep_rank: int | None = None, fp8_payload: bool = False,
-                 clone_outputs: bool = False, push: bool = False):
+                 clone_outputs: bool = False, push: bool = False, keep_factor: float = 0.0):
         self.E, self.K, self.H, self.T = num_experts, topk, hidden, max_tokens
         self.ep = mesh.ep if ep is None else ep
         self.me = mesh.ep_rank if ep_rank is None else ep_rank
@@ -123,6 +124,14 @@ class FusedDispatcher:
         self._peer_ptrs = (ctypes.c_long * 16)(*(list(workspace.ptrs) + [0] * (16 - len(workspace.ptrs))))
         self._lay = [self._layout(0), self._layout(1)]
         self.epoch = 0
+        # Rows a recomputed block keeps of its first dispatch.  keep_factor > 0: that multiple of the balanced
+        # per-rank load, fixed; keep_factor < 0: decided by the trainer from the rows it saw in use during the
+        # first step (`set_keep_rows`), nothing is kept until then; 0: never.
+        self.auto_keep = keep_factor < 0
+        self.keep_rows = 0
+        if keep_factor > 0:
+            self.set_keep_rows(int(keep_factor * pairs))
+        self.rows_seen = torch.zeros(1, dtype=torch.int32, device=device)
         n_blocks = max(cops.lib().slab_moe_count_blocks(pairs), 1)
         i32 = dict(dtype=torch.int32, device=device)
         self.block_hist = torch.zeros(n_blocks * num_experts, **i32)
@@ -231,6 +240,32 @@ class FusedDispatcher:
                   self.status, 0, cops.stream())
         return y
 
+    def set_keep_rows(self, rows_in_use: int) -> int:
+        """Size the kept copy for ``rows_in_use`` received rows (plus per-expert alignment padding)."""
+        e_local = self.E // self.ep
+        want = rows_in_use + e_local * self.pad
+        self.keep_rows = min(self.capacity, (want + self.pad - 1) // self.pad * self.pad)
+        return self.keep_rows
+
+    def note_rows_in_use(self, plan: FusedPlan) -> None:
+        """Fold this plan's row count into the high-water mark the trainer reads between steps."""
+        cops.call("slab_moe_check_rows", plan.meta, 0, self.status, self.rows_seen, cops.stream())
+
+    def keep_dispatched(self, plan: FusedPlan, xe: torch.Tensor, pe: torch.Tensor | None):
+        """Copies of the received rows (first ``keep_rows``) and gate probabilities for a later
+        ``redispatch_kept``; more rows in use than ``keep_rows`` is reported as CAPACITY through the status
+        word.  The plan is made self-contained (its origin table no longer aliases the workspace)."""
+        n = self.keep_rows
+        cops.call("slab_moe_check_rows", plan.meta, n, self.status, self.rows_seen, cops.stream())
+        plan.origin = self.origin.clone()
+        return xe[:n].clone(), (pe[:n].clone() if pe is not None else None)
+
+    def redispatch_kept(self, plan: FusedPlan, x: torch.Tensor, probs: torch.Tensor | None, xs: torch.Tensor,
+                        ps: torch.Tensor | None):
+        """Differentiable stand-in for ``dispatch`` that moves nothing forward: returns the kept rows; its
+        backward is the backward of ``dispatch`` (gradients of the rows travel back to the tokens)."""
+        return _FusedKept.apply(x, probs, xs, ps, self, plan)
+
     def push_target(self, plan: FusedPlan) -> "PushTarget":
         return PushTarget(self, plan)
 
@@ -300,16 +335,32 @@ class _FusedDispatch(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g_xe, g_pe):
-        d, plan = ctx.d, ctx.plan
-        pushed = d._pending_push.pop(1, None)             # epoch if the fc1 dgrad already pushed its rows to the owners
-        if pushed is None:
-            d.stage_out_rows(g_xe.contiguous())
-        if ctx.has_probs and g_pe is not None:
-            d.out_scalars.copy_(g_pe)
-        ep = d.signal_out()
-        gx = d.reduce_pairs(plan, pushed) if pushed is not None else d.pull_rows(plan, ep)
-        gp = d.pull_scalars(plan, ep) if (ctx.has_probs and g_pe is not None) else None
-        return gx, gp, None, None
+        return _dispatch_backward(ctx, g_xe, g_pe) + (None, None)
+
+
+def _dispatch_backward(ctx, g_xe, g_pe):
+    """Gradients of the dispatched rows (and of the per-row gate probabilities) travel back to the tokens."""
+    d, plan = ctx.d, ctx.plan
+    pushed = d._pending_push.pop(1, None)             # epoch if the fc1 dgrad already pushed its rows to the owners
+    if pushed is None:
+        d.stage_out_rows(g_xe.contiguous())
+    if ctx.has_probs and g_pe is not None:
+        d.out_scalars[:g_pe.shape[0]].copy_(g_pe)
+    ep = d.signal_out()
+    gx = d.reduce_pairs(plan, pushed) if pushed is not None else d.pull_rows(plan, ep)
+    gp = d.pull_scalars(plan, ep) if (ctx.has_probs and g_pe is not None) else None
+    return gx, gp
+
+
+class _FusedKept(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, probs, xs, ps, d: FusedDispatcher, plan: FusedPlan):
+        ctx.d, ctx.plan, ctx.has_probs = d, plan, probs is not None
+        return xs.view_as(xs), (ps.view_as(ps) if (probs is not None and ps is not None) else None)
+
+    @staticmethod
+    def backward(ctx, g_xe, g_pe):
+        return _dispatch_backward(ctx, g_xe, g_pe) + (None, None, None, None)
 
 
 class _FusedCombine(torch.autograd.Function):
@@ -320,6 +371,7 @@ class _FusedCombine(torch.autograd.Function):
             weights = weights.float().contiguous()
             ctx.save_for_backward(weights)
         ctx.weighted = weights is not None
+        ctx.ye_rows = ye.shape[0]
         if dead:
             return torch.empty(plan.num_tokens, d.H, dtype=torch.bfloat16, device=d.device)
         pushed = d._pending_push.pop(0, None)             # epoch if the fc2 GEMM already pushed its rows to the owners
@@ -337,7 +389,7 @@ class _FusedCombine(torch.autograd.Function):
         w = ctx.saved_tensors[0] if ctx.weighted else None
         ep = d.scatter(plan, g.contiguous(), None, channel=1, scale_in=w)
         d.wait_rows(1, ep)
-        g_ye = d.rows[1]
+        g_ye = d.rows[1][:ctx.ye_rows]
         if d.clone_outputs:
             g_ye = g_ye.clone()
         if ctx.weighted and ctx.needs_input_grad[1]:

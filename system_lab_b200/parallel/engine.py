@@ -151,6 +151,8 @@ class Engine:
         self.layer_units = [add(f"layers.{l.layer_idx}", l) for l in self.model.layers]
         for l in self.model.layers:
             l.recompute_ffn = self.selective
+            if l.is_moe:
+                l.ffn.keep_dispatched = self.selective and cfg.model.moe_keep_dispatched_factor != 0
         self.head_unit = add("head", self.model.head) if self.model.head is not None else None
         self._make_dispatchers()
 
@@ -178,7 +180,9 @@ class Engine:
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,
                                              clone_outputs=not (self.recompute or self.selective),
-                                             capacity_factor=m.moe_capacity_factor, push=m.moe_combine_push)
+                                             capacity_factor=m.moe_capacity_factor,
+                                             push=m.moe_combine_push and self.mesh.ep > 1,   # nothing to overlap on one rank
+                                             keep_factor=m.moe_keep_dispatched_factor if self.selective else 0.0)
                 layer.ffn.dispatcher = shared
             else:
                 if shared is None:

@@ -190,6 +190,12 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
             qkv_w = (m.num_attention_heads + 2 * m.num_query_groups) * m.kv_channels
         attn_keep = tokens * act_b * (7 * h + 2 * qkv_w)
         acts = layers_here * attn_keep + per_layer_full
+        if m.num_experts > 0 and m.moe_keep_dispatched_factor != 0:
+            # dispatched rows (+ gate scalar, origin) of every MoE layer kept for the recomputed block
+            moe_layers = max(layers_here - (m.first_k_dense if pp == 1 else 0), 0)
+            kf = m.moe_keep_dispatched_factor if m.moe_keep_dispatched_factor > 0 else 2.0   # < 0: sized at run time
+            kept_rows = kf * slots + (m.num_experts // ep) * m.moe_pad_expert_rows_to
+            acts += moe_layers * kept_rows * (h * act_b + 8) * min(nmb, pp)
     else:
         acts = layers_here * per_layer_full
     logits = tokens * m.vocab_size * 4 / 4 + tokens * h * act_b * 2     # chunked cross entropy: quarter at a time

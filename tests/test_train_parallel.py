@@ -56,6 +56,14 @@ def test_selective_recompute_matches(single_curve):
     assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
 
 
+def test_selective_recompute_with_kept_dispatch_matches(single_curve):
+    """The recomputed block reuses the rows of its first dispatch (no second plan exchange / dispatch); with two
+    micro-batches per step the kept state must stay attached to the right autograd node."""
+    res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2", "recompute_granularity=selective",
+                                       "moe_keep_dispatched_factor=2.0"], 6)
+    assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+
+
 def test_dp2_ep1_fsdp_matches(single_curve):
     res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=1"], 6)
     assert res[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
