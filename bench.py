@@ -39,8 +39,9 @@ def parse():
     ap.add_argument("--ep", type=int, default=0, help="expert parallel size (default: all data ranks)")
     ap.add_argument("--gbs", type=int, default=0, help="global batch in sequences (default: seqs-per-gpu x N)")
     ap.add_argument("--mbs", type=int, default=0, help="micro-batch in sequences (default: seqs-per-gpu)")
-    ap.add_argument("--no-keep-dispatched", action="store_true",
-                    help="never keep dispatched rows for the recomputed block, even when memory allows")
+    ap.add_argument("--keep-dispatched", action="store_true",
+                    help="when memory allows, keep every layer's dispatched rows for the recomputed block (sized "
+                         "from the first step; a later step that needs more rows ends the run with CAPACITY)")
     ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
@@ -97,7 +98,7 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = True) -> dict:
+def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = False) -> dict:
     """Highest-fidelity optimizer/weight layout that fits 92 % of 180 GB per GPU."""
     from system_lab_b200.pilot.constraints import estimate_memory
     plans = [
@@ -162,7 +163,7 @@ def main() -> int:
     if args.balanced_routing:
         ov.append("moe_router_force_load_balancing=true")
     cfg = Config.load(preset=args.preset, overrides=ov + list(args.overrides))
-    plan = choose_memory_plan(cfg, n, args.plan, not args.no_keep_dispatched)
+    plan = choose_memory_plan(cfg, n, args.plan, args.keep_dispatched)
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
                       cfg.parallel.context_parallel_size)

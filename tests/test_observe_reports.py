@@ -61,3 +61,23 @@ def test_html_single_and_comparison(tmp_path):
     p2.write_text("log line\n" + json.dumps(_breakdown(0.5)))
     assert report_html.main([str(p1), "--against", str(p2), "--names", "x,y", "-o", str(out)]) == 0
     assert out.exists() and "x vs y" in out.read_text()
+
+
+def test_trace_gap_analysis(tmp_path):
+    """Idle gaps of the busiest stream: total, the part another stream covers, and the kernel pair they sit between."""
+    from system_lab_b200.observe import trace_breakdown as tb
+    ev = [{"ph": "X", "name": "ProfilerStep#0", "cat": "user_annotation", "ts": 0, "dur": 1000},
+          {"ph": "X", "name": "void slab::grouped_gemm_kernel<0, 256>(x)", "cat": "kernel", "ts": 10, "dur": 200, "args": {"stream": 7}},
+          {"ph": "X", "name": "void slab::adamw_kernel<f>(x)", "cat": "kernel", "ts": 250, "dur": 100, "args": {"stream": 9}},
+          {"ph": "X", "name": "void slab::swiglu_fwd_kernel(x)", "cat": "kernel", "ts": 400, "dur": 300, "args": {"stream": 7}}]
+    p = tmp_path / "t.json"
+    p.write_text(json.dumps({"traceEvents": ev}))
+    r = tb.analyze(str(p))
+    g = r["main_stream_gaps"]
+    assert g["stream"] == "7"
+    assert abs(g["gap_ms"] - 0.5) < 1e-6                       # 10 us head + 190 us between + 300 us tail
+    assert abs(g["gap_covered_by_other_streams_ms"] - 0.1) < 1e-6
+    top = g["top_pairs"][0]
+    assert top["between"].endswith("window end") and abs(top["ms"] - 0.3) < 1e-6
+    assert any("grouped_gemm_kernel" in x["between"] and "swiglu_fwd_kernel" in x["between"] for x in g["top_pairs"])
+    assert "idle gaps of stream 7" in tb.format_report(r)
