@@ -48,6 +48,19 @@ def build_snapshot(trainer, *, job_id: str = "", plan_id: str = "", session_id: 
         tpe = trainer._tpe_accum.float()
         per_layer = tpe.max(dim=1).values / tpe.min(dim=1).values.clamp_min(1.0) - 1.0
         imb = float(per_layer.mean() * 100.0)
+    expected = None
+    if cuda:
+        # analytic expectation for this config on B200 (achieved kernel rates, measured rank load): DIAGNOSE's
+        # "tps < 0.8 x expected" soft signal compares against it
+        from ..pilot.perf_model import expected_tps
+        ratio = 1.0
+        if moe and trainer._tpe_accum is not None and trainer.mesh.ep > 1:
+            per_rank = trainer._tpe_accum.float().reshape(trainer._tpe_accum.shape[0], trainer.mesh.ep, -1).sum(-1)
+            ratio = float((per_rank.max(1).values / per_rank.mean(1).clamp_min(1)).mean())
+        try:
+            expected = expected_tps(trainer.cfg, trainer.mesh.world, rank_load_ratio=ratio)
+        except (ZeroDivisionError, KeyError, ValueError):
+            expected = None
     comm = comm or {}
     completed = len(times)
     return {
@@ -59,6 +72,7 @@ def build_snapshot(trainer, *, job_id: str = "", plan_id: str = "", session_id: 
         "metrics": {
             "tps": (tok / (step_ms / 1e3)) if step_ms else None,
             "step_time_ms": step_ms,
+            "expected_tps": expected,
             "tps_ema_50": ema(tps_series[-50:]) if tps_series else None,
             "tps_ema_full": ema(tps_series) if tps_series else None,
             "tflops_per_gpu": (tok / (step_ms / 1e3) / trainer.mesh.world * trainer.flops_per_token / 1e12)

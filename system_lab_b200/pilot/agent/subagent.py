@@ -243,7 +243,7 @@ class RuleWorker:
 
     def _diagnose(self, req, wid):
         champ = self._load("ChampionSnapshot")
-        rep = policy.diagnose(champ)
+        rep = policy.diagnose(champ, expected_tps=(champ.get("metrics") or {}).get("expected_tps"))
         art = self._save("DiagnosisReport", "diag.json", rep)
         return self._ok(req.stage, wid, f"bottleneck {rep['bottleneck']} (conf {rep['confidence']:.1f})",
                         {"fired": rep["fired_rules"][:2]}, [art])

@@ -190,3 +190,31 @@ def test_failed_worker_aborts_after_three_same_failures(tmp_path):
     assert state.current_stage == Stage.ABORT and state.stop_reason == "ABORT"
     assert len([r for r in json.loads((sorted((tmp_path / "f" / "checkpoints").glob("s*.json"))[-1]).read_text())
                 ["reentry_log"]]) >= 1
+
+
+def test_perf_model_matches_measured_b200_steps():
+    """The analytic execution model reproduces the measured Qwen3-30B-A3B-shape step times on B200 (1, 2 and 8
+    GPUs) within 15 % and attributes the 8-GPU slowdown to dispatch traffic and rank imbalance."""
+    from system_lab_b200.config import Config
+    from system_lab_b200.pilot.perf_model import estimate_step, expected_tps
+    sel = ["params_dtype=bf16", "recompute_granularity=selective"]
+    n1 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
+        "global_batch_size=2", "micro_batch_size=2", "expert_model_parallel_size=1", "master_weights=false",
+        "optimizer_state_dtype=fp8", "optimizer_in_backward=true"])
+    n2 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
+        "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=2", "master_weights=false",
+        "optimizer_state_dtype=bf16"])
+    n8 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
+        "global_batch_size=16", "micro_batch_size=2", "expert_model_parallel_size=8"])
+    for cfg, world, ratio, measured_ms in ((n1, 1, 1.0, 351.5), (n2, 2, 1.1, 389.3), (n8, 8, 1.49, 482.8)):
+        e = estimate_step(cfg, world, rank_load_ratio=ratio)
+        assert abs(e.t_step / measured_ms - 1.0) < 0.15, (world, e.t_step, measured_ms)
+    e8 = estimate_step(n8, 8, rank_load_ratio=1.49)
+    assert e8.t_imbalance > 0.15 * e8.t_step and e8.t_dispatch > e8.t_fsdp
+    assert estimate_step(n8, 8).t_step < e8.t_step                      # balanced routing is faster
+    assert expected_tps(n8, 8) > expected_tps(n1, 1) * 4                 # more GPUs, more tokens per second
+    pp = Config.load(preset="deepseek-v3-proxy", overrides=sel + [
+        "global_batch_size=32", "micro_batch_size=1", "expert_model_parallel_size=4", "pipeline_model_parallel_size=2",
+        "master_weights=false", "optimizer_state_dtype=bf16"])
+    ep = estimate_step(pp, 8)
+    assert ep.t_bubble > 0 and 0.5 < ep.t_step / 1921.0 < 1.5
