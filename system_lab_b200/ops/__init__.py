@@ -92,7 +92,7 @@ def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out
     forward whose result nobody reads); the product is not computed and the returned values are unspecified."""
     if use_kernels(a):
         return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out, dead)
-    return _GroupedLinearRef.apply(a, w, offsets, counts, dead)
+    return _GroupedLinearRef.apply(a, w, offsets, counts, dead, fp8)
 
 
 def causal_attention(q, k, v, scale=None, window=0):
@@ -111,10 +111,22 @@ class _GroupedLinearRef(torch.autograd.Function):
     """Oracle grouped linear with explicit fwd/dgrad/wgrad (mirrors the three CUDA kernels)."""
 
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, dead=False):
+    def forward(ctx, a, w, offsets, counts, dead=False, fp8=False):
         ctx.save_for_backward(a, w, offsets, counts)
         if dead:
             return a.new_zeros(a.shape[0], w.shape[1])
+        if fp8:
+            # emulation of the fp8 forward: operands rounded to e4m3 with the recipe's scales, product in fp32;
+            # the backward stays on the unquantised operands, like the kernel path
+            if fp8 == "blockwise" and a.shape[1] % 128 == 0 and w.shape[1] % 128 == 0:
+                aq = ref.dequant_1x128(*ref.quant_1x128(a)).to(a.dtype)
+                wq = ref.dequant_128x128(*ref.quant_128x128(w)).to(w.dtype)
+            else:
+                qa, sa = ref.quant_rowwise(a)
+                qw, sw = ref.quant_rowwise(w)
+                aq = (qa.float() * sa.unsqueeze(-1)).to(a.dtype)
+                wq = (qw.float() * sw.unsqueeze(-1)).to(w.dtype)
+            return ref.grouped_gemm(aq, wq, offsets, counts)
         return ref.grouped_gemm(a, w, offsets, counts)
 
     @staticmethod
@@ -123,4 +135,4 @@ class _GroupedLinearRef(torch.autograd.Function):
         g = g.contiguous()
         da = ref.grouped_gemm_dgrad(g, w, offsets, counts) if ctx.needs_input_grad[0] else None
         dw = ref.grouped_gemm_wgrad(g, a, offsets, counts, out_dtype=w.dtype) if ctx.needs_input_grad[1] else None
-        return da, dw, None, None, None
+        return da, dw, None, None, None, None

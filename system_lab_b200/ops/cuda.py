@@ -455,7 +455,43 @@ class _GroupedLinear(torch.autograd.Function):
         return da, dw, None, None, None, None, None
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None, dead: bool = False):
+class _GroupedLinearFp8(torch.autograd.Function):
+    """Forward in e4m3 on the tensor cores' fp8 path, backward in bf16 on the saved bf16 operands (the reference's
+    fused fp8 grouped GEMM keeps dW in bf16 too, ``summary/fp8_expert_gemm_optimization.md:137-143``).  Operands
+    are quantised on the fly: activations per row, weights per output channel (``recipe == "rowwise"``, scales
+    constant along K so the kernel accumulates all of K in TMEM), or 1x128 / 128x128 blocks (``"blockwise"``)."""
+
+    @staticmethod
+    def forward(ctx, a, w, offsets, counts, recipe, out=None, dgrad_out=None):
+        e, n, k = w.shape
+        a = a.contiguous()
+        w = w.contiguous() if not w.is_contiguous() else w
+        if recipe == "blockwise":
+            aq, sa = quant_1x128(a)
+            wq, sw = quant_128x128(w)
+            out = grouped_gemm_fp8_raw(aq, sa.contiguous(), wq, sw.contiguous(), offsets, counts, out=out)
+        else:
+            aq, sa = quant_rowwise(a)
+            wq, sw = quant_rowwise(w)
+            out = grouped_gemm_fp8_rowwise_raw(aq, sa, wq, sw.contiguous(), offsets, counts, out=out)
+        ctx.save_for_backward(a, w, offsets, counts)
+        ctx.w_ref = w
+        ctx.dgrad_out = dgrad_out
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _GroupedLinear.backward(ctx, g)
+
+
+def _fp8_recipe(fp8) -> str:
+    """``fp8`` as passed down from the model: False / "" = bf16; True = the default recipe; a string names one."""
+    if not fp8:
+        return ""
+    return fp8 if isinstance(fp8, str) else "rowwise"
+
+
+def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, dead: bool = False):
     e, n, k = w.shape
     if not _bf16(a, w) or k % 64 or n % 128:
         from . import _GroupedLinearRef
@@ -464,7 +500,13 @@ def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out
     if out is not None and not hasattr(out, "launch") and \
             (out.dtype != torch.bfloat16 or out.shape[0] < a.shape[0] or out.shape[1] != n):
         out = None
-    res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead)
+    recipe = _fp8_recipe(fp8)
+    fp8_ok = recipe and not dead and not hasattr(out, "launch") and \
+        (k % 128 == 0 and n % (128 if recipe == "blockwise" else 64) == 0)
+    if fp8_ok:           # a pushed output stays on the bf16 kernel: the fp8 kernels store through TMA only
+        res = _GroupedLinearFp8.apply(a, w, offsets, counts, recipe, out, dgrad_out)
+    else:
+        res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead)
     return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
 
 

@@ -119,10 +119,12 @@ class Engine:
         self.layer_end = self.layer_start + per_stage
         with torch.device("meta"):
             self.model = SimpleMoE(
-                m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=cfg.precision.fp8,
+                m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=(cfg.precision.fp8_recipe if cfg.precision.fp8 else False),
                 layer_start=self.layer_start, layer_end=self.layer_end,
                 first_stage=mesh.is_first_stage(), last_stage=mesh.is_last_stage(),
-                cp_group=mesh.cp_group if mesh.cp > 1 else None, cp_rank=mesh.cp_rank, cp_size=mesh.cp)
+                cp_group=mesh.cp_group if mesh.cp > 1 else None, cp_rank=mesh.cp_rank, cp_size=mesh.cp,
+                bf16_first_layers=cfg.precision.num_layers_at_start_in_bf16,
+                bf16_last_layers=cfg.precision.num_layers_at_end_in_bf16)
         self.units: list[Unit] = []
         self.anchor = torch.zeros(1, device=device, requires_grad=True)
         self._aux_out: list[torch.Tensor] = []

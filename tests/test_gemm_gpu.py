@@ -111,3 +111,19 @@ def test_fp8_row_scaled_forward(counts, n, k):
     full = ref.grouped_gemm(a, w, off, cnt)
     rel = (out.float() - full.float()).norm() / full.float().norm()
     assert rel < 0.06, rel
+
+
+@pytest.mark.parametrize("recipe", ["rowwise", "blockwise"])
+def test_autograd_grouped_linear_fp8_forward_bf16_backward(recipe):
+    from system_lab_b200 import ops
+    from system_lab_b200.ops import reference as ref
+    a, dy, w, off, cnt = _inputs([200, 56, 0, 384], 512, 256, 7)
+    a.requires_grad_(True)
+    w.requires_grad_(True)
+    out = ops.grouped_linear(a, w, off, cnt, fp8=recipe)
+    out.backward(dy)
+    full = ref.grouped_gemm(a.detach(), w.detach(), off, cnt)
+    rel = (out.float() - full.float()).norm() / full.float().norm()
+    assert 1e-4 < rel < 0.06, rel                 # quantised, but within e4m3 noise of the bf16 product
+    _check(a.grad, ref.grouped_gemm_dgrad(dy, w.detach(), off, cnt), "dgrad")
+    _check(w.grad, ref.grouped_gemm_wgrad(dy, a.detach(), off, cnt), "wgrad")
