@@ -150,6 +150,8 @@ class TrainConfig:
     device: str = "auto"                 # auto | cpu | cuda
     use_cuda_kernels: str = "auto"       # auto | true | false : hand written sm_100a ops vs PyTorch oracle path
     hang_timeout_s: float = 300.0
+    heartbeat: bool = True               # ranks publish per-step heartbeats; a peer stuck for hang_timeout_s is reported
+    fault_injection: str = ""            # host-side test faults, e.g. "delay:rank=1,step=3,seconds=5;nan:rank=0,step=4"
     mllog: bool = False
 
 

@@ -36,7 +36,16 @@ def main(argv=None) -> int:
     resume = args.resume or cfg.checkpoint.load
     if resume:
         tr.load_checkpoint(resume)
-    snap = tr.fit(max(cfg.train.train_iters - tr.step, 0))
+    try:
+        snap = tr.fit(max(cfg.train.train_iters - tr.step, 0))
+    except BaseException as e:
+        # tell the peers at once (they would otherwise learn of it from a heartbeat or collective timeout)
+        if tr.heartbeat is not None:
+            tr.heartbeat.fail(f"{type(e).__name__}: {e}")
+        raise
+    finally:
+        if tr.heartbeat is not None:
+            tr.heartbeat.stop()
     if tr.mesh.rank == 0:
         m = snap["metrics"]
         print(json.dumps({"final_loss": tr.loss_curve[-1] if tr.loss_curve else None, "tps": m["tps"],

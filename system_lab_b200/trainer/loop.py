@@ -90,6 +90,12 @@ class Trainer:
         self._tpe_accum = None
         self._keep_decided = False
         self.kept_rows = 0
+        from .watchdog import FaultPlan, Heartbeat
+        self.faults = FaultPlan.parse(t.fault_injection)
+        self.heartbeat = None
+        if t.heartbeat and dist.is_initialized() and mesh.world > 1:
+            store = dist.PrefixStore("slab_heartbeat", dist.distributed_c10d._get_default_store())
+            self.heartbeat = Heartbeat(store, mesh.rank, mesh.world, t.hang_timeout_s).start()
         self.events = None
         if t.mllog:
             from .mllog import MLLogger
@@ -101,6 +107,12 @@ class Trainer:
         by default the next synthetic global batch.  Returns ``{"loss": device scalar, "grad_norm": ...}``."""
         cfg, mesh = self.cfg, self.mesh
         step = self.step + 1
+        flags = self.faults.before_step(mesh.rank, step) if self.faults.actions else {}
+        if self.heartbeat is not None:
+            if flags.get("mute"):
+                self.heartbeat.muted = True
+            self.heartbeat.check()             # a peer that hung or failed is reported before anything is launched
+            self.heartbeat.begin(step)
         if not self._keep_decided:
             self._decide_kept_rows()
         if batches is None:
@@ -138,7 +150,11 @@ class Trainer:
             else:
                 dist.all_reduce(loss_mean)
                 loss_mean = loss_mean / mesh.world
+        if flags.get("nan"):
+            loss_mean = loss_mean * float("nan")
         self.step = step
+        if self.heartbeat is not None:
+            self.heartbeat.beat(step)
         return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
 
     def _decide_kept_rows(self) -> None:
