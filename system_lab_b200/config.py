@@ -146,7 +146,9 @@ class TrainConfig:
     eval_iters: int = 0
     log_interval: int = 1
     check_for_nan_in_loss_and_grad: bool = True
-    data: str = "synthetic"              # synthetic uniform-random token ids
+    data: str = "synthetic"              # "synthetic" (uniform-random token ids) or the path of a token file
+    eval_data: str = ""                  # token file for evaluation ("" = held-out steps of `data`)
+    eval_target_loss: float = 0.0        # > 0: training stops when the evaluation loss reaches it
     device: str = "auto"                 # auto | cpu | cuda
     use_cuda_kernels: str = "auto"       # auto | true | false : hand written sm_100a ops vs PyTorch oracle path
     hang_timeout_s: float = 300.0

@@ -50,7 +50,7 @@ class _UnitFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, anchor, engine, unit, x, *extra):
         ctx.engine, ctx.unit, ctx.extra = engine, unit, extra
-        recompute = engine.recompute
+        recompute = engine.recompute or engine.inference      # forward-only passes keep no graph
         ctx.recompute = recompute
         unit.gather()
         engine.after_gather(unit, forward=True)
@@ -105,6 +105,7 @@ class _UnitFn(torch.autograd.Function):
 class Engine:
     def __init__(self, cfg: Config, mesh: Mesh, device: torch.device):
         self.cfg, self.mesh, self.device = cfg, mesh, device
+        self.inference = False               # set around forward-only passes (evaluation)
         m = cfg.model
         self.compute_dtype = _DT[cfg.precision.params_dtype]
         gran = cfg.precision.recompute_granularity

@@ -109,3 +109,28 @@ def pipeline_1f1b(engine, mesh, batches, scale: float, cfg) -> torch.Tensor:
         if not first:
             _p2p([dist.P2POp(dist.isend, gin.contiguous(), prev_r)])
     return loss_sum
+
+
+@torch.no_grad()
+def pipeline_forward_only(engine, mesh, batches, cfg) -> torch.Tensor:
+    """Evaluation pass: every micro-batch goes through the stages once, nothing is kept for backward.
+    Returns the summed loss on the last stage and zero elsewhere."""
+    dev = engine.device
+    first, last = mesh.is_first_stage(), mesh.is_last_stage()
+    prev_r = mesh.prev_stage_rank() if not first else None
+    next_r = mesh.next_stage_rank() if not last else None
+    mbs, seq = batches[0][0].shape
+    act_shape = (mbs, seq, cfg.model.hidden_size)
+    loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
+    for tok, tgt in batches:
+        if first:
+            x = tok
+        else:
+            x = torch.empty(act_shape, dtype=engine.compute_dtype, device=dev)
+            _p2p([dist.P2POp(dist.irecv, x, prev_r)])
+        out, _ = engine.stage_forward(x, tgt if last else None)
+        if last:
+            loss_sum = loss_sum + out.float()
+        else:
+            _p2p([dist.P2POp(dist.isend, out.contiguous(), next_r)])
+    return loss_sum

@@ -25,7 +25,7 @@ from ..config import Config
 from ..parallel.engine import Engine
 from ..parallel.mesh import Mesh, build_mesh, init_distributed
 from ..pilot.constraints import param_counts
-from .data import SyntheticData
+from .data import SyntheticData, make_data
 from .optim import ShardedAdamW, lr_at
 
 log = logging.getLogger("system_lab_b200.train")
@@ -76,9 +76,14 @@ class Trainer:
                                       state_dtype=cfg.precision.optimizer_state_dtype)
         if t.optimizer_in_backward:
             self.engine.optimizer = self.optimizer
-        self.data = SyntheticData(cfg.model.vocab_size, cfg.model.seq_length, t.global_batch_size,
-                                  t.micro_batch_size, mesh.dp_rank, mesh.dp, mesh.cp_rank, mesh.cp, t.seed,
-                                  pin=self.device.type == "cuda")
+        data_kw = dict(vocab_size=cfg.model.vocab_size, seq_length=cfg.model.seq_length,
+                       global_batch_size=t.global_batch_size, micro_batch_size=t.micro_batch_size,
+                       dp_rank=mesh.dp_rank, dp_size=mesh.dp, cp_rank=mesh.cp_rank, cp_size=mesh.cp, seed=t.seed,
+                       pin=self.device.type == "cuda")
+        self.data = make_data(t.data, **data_kw)
+        # evaluation batches: their own file, or steps of the training source that training never reaches
+        self.eval_data = make_data(t.eval_data, **data_kw) if t.eval_data else self.data
+        self.eval_curve: list[tuple[int, float]] = []
         if dist.is_initialized() and mesh.world > 1:
             dist.barrier()                     # ranks leave construction together (peer kernels wait on each other)
         self.step = 0
@@ -90,6 +95,7 @@ class Trainer:
         self._tpe_accum = None
         self._keep_decided = False
         self.kept_rows = 0
+        self.reached_target = False
         from .watchdog import FaultPlan, Heartbeat
         self.faults = FaultPlan.parse(t.fault_injection)
         self.heartbeat = None
@@ -156,6 +162,47 @@ class Trainer:
         if self.heartbeat is not None:
             self.heartbeat.beat(step)
         return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
+
+    EVAL_STEP_OFFSET = 1 << 40            # held-out region of the (seed, step) -> batch map
+
+    @torch.no_grad()
+    def evaluate(self, iters: int | None = None) -> float:
+        """Mean loss over ``iters`` held-out global batches (forward only, no dropout in this model family so no
+        mode switch is needed); identical on every rank."""
+        cfg, mesh, dev = self.cfg, self.mesh, self.device
+        iters = iters if iters is not None else max(cfg.train.eval_iters, 1)
+        offset = 0 if self.eval_data is not self.data else self.EVAL_STEP_OFFSET
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        count = 0
+        self.engine.inference = True
+        try:
+            total, count = self._eval_batches(iters, offset, total)
+        finally:
+            self.engine.inference = False
+        for f in self.engine.moe_ffns():                # evaluation tokens do not count towards router balancing
+            f.step_tokens_per_expert = None
+        mean = total / max(count, 1)
+        if dist.is_initialized() and mesh.world > 1:
+            dist.all_reduce(mean)
+            mean = mean / (mesh.data_size if mesh.pp > 1 else mesh.world)
+        return float(mean)
+
+    def _eval_batches(self, iters: int, offset: int, total: torch.Tensor):
+        cfg, mesh, dev = self.cfg, self.mesh, self.device
+        count = 0
+        for i in range(iters):
+            batches = [(a.to(dev), b.to(dev)) for a, b in self.eval_data.microbatches(offset + i)]
+            if self.eval_data is self.data:
+                self.data.cursor = self.step            # serving evaluation batches does not move the training cursor
+            if mesh.pp > 1:
+                from ..parallel.pp import pipeline_forward_only
+                total = total + pipeline_forward_only(self.engine, mesh, batches, cfg)
+            else:
+                for tok, tgt in batches:
+                    loss, _ = self.engine.stage_forward(tok, tgt)
+                    total = total + loss.float()
+            count += len(batches)
+        return total, count
 
     def _decide_kept_rows(self) -> None:
         """``moe_keep_dispatched_factor < 0``: after one full step, size the copy of the dispatched rows that the
@@ -237,6 +284,16 @@ class Trainer:
                     raise NumericalError(f"step {self.step}: loss={loss} grad_norm={gn}")
             if self.mesh.rank == 0 and (self.step % max(t.log_interval, 1) == 0):
                 self._log_line(dt_ms, loss, gn, out["lr"])
+            if t.eval_interval and self.step % t.eval_interval == 0:
+                ev = self.evaluate()
+                self.eval_curve.append((self.step, ev))
+                if self.mesh.rank == 0:
+                    print(f" validation loss at iteration {self.step:6d} | lm loss value: {ev:.6E}", flush=True)
+                if self.events:
+                    self.events.eval(ev, self.step * t.global_batch_size)
+                if t.eval_target_loss > 0 and ev <= t.eval_target_loss:
+                    self.reached_target = True
+                    break
             ck = cfg.checkpoint
             if ck.save and ck.save_interval and self.step % ck.save_interval == 0:
                 self.save_checkpoint(ck.save)
