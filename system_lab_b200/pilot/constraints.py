@@ -77,6 +77,9 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
                               "optimizer_in_backward needs exactly one micro-batch per step"))
     if p.virtual_pipeline_model_parallel_size > 1 and pp == 1:
         out.append(_p("vpp_requires_pp_gt_1", "vpp > 1 needs pp > 1"))
+    if p.virtual_pipeline_model_parallel_size > 1 and pp > 1:
+        out.append(_p("vpp_not_implemented", "the pipeline schedule is plain 1F1B: interleaved stages (vpp > 1) are "
+                      "not implemented, use more micro-batches to shrink the bubble"))
     # 4. MoE
     if m.num_experts and m.moe_router_topk > m.num_experts:
         out.append(_p("top_k_le_num_experts", f"topk={m.moe_router_topk} > num_experts={m.num_experts}"))
