@@ -41,6 +41,12 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
             elif dp % ep != 0 and world_size % ep != 0:
                 out.append(_p("ep_divides_dp_or_world", f"ep={ep} divides neither dp={dp} nor world={world_size}",
                               "pick ep from divisors(dp)"))
+    if tp > 1:
+        out.append(_p("tp_not_implemented", f"tensor_model_parallel_size={tp}: tensor parallelism is a config axis "
+                      "only (every measured configuration runs tp=1); shard with ep / fsdp / pp / cp instead"))
+    if p.num_distributed_optimizer_instances > 1:
+        out.append(_p("hsdp_not_implemented", "num_distributed_optimizer_instances > 1 (hybrid sharding across "
+                      "replicas) is out of scope for one NVSwitch box"))
     # 2. model dims
     if m.num_attention_heads % tp:
         out.append(_p("tp_divides_num_heads", f"num_attention_heads={m.num_attention_heads} % tp={tp} != 0"))
