@@ -239,10 +239,7 @@ def main() -> int:
             prof.export_chrome_trace(args.trace)
             with open(args.trace + ".cpu_ops.txt", "w") as f:
                 f.write(prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=40, max_name_column_width=60))
-    load_ratio = None
-    if trainer._tpe_accum is not None:
-        per_rank = trainer._tpe_accum.float().reshape(trainer._tpe_accum.shape[0], mesh.ep, -1).sum(-1)
-        load_ratio = float((per_rank.max(1).values / per_rank.mean(1).clamp_min(1)).mean())
+    load_ratio = trainer.rank_load_ratio()
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -276,6 +273,7 @@ def main() -> int:
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
             "kept_dispatch_rows": trainer.kept_rows,
+            "expert_relocations": trainer.relocator.history if trainer.relocator else [],
         }
         print(json.dumps(line))
     if world > 1:

@@ -91,6 +91,9 @@ class ModelConfig:
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
     moe_router_force_load_balancing: bool = False  # benchmarking aid: route by fixed random logits
     moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
+    moe_expert_relocation_interval: int = 0   # > 0: every that many steps, re-place experts on ranks by measured load
+    moe_expert_relocation_first_step: int = 0    # > 0: also decide once at this step (early skew of a fresh router)
+    moe_expert_relocation_min_gain: float = 0.05  # relative drop of max/mean rank load that justifies moving experts
     moe_combine_push: bool = True        # expert GEMM epilogues push result rows to the token owners (fused combine)
     moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = x balanced load, <0 = sized from the first step, 0 = off
 

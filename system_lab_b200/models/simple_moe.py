@@ -184,6 +184,9 @@ class MoEFFN(nn.Module):
             self.router_bias = None
         self.shared = DenseFFN(h, cfg.moe_shared_expert_intermediate_size) \
             if cfg.moe_shared_expert_intermediate_size else None
+        # logical (router) expert id -> physical slot (rank * E_local + local index); changed by expert relocation
+        self.register_buffer("expert_map", torch.arange(cfg.num_experts), persistent=True)
+        self.relocated = False
         self.dispatcher = None            # set by the engine (needs the process group)
         self.keep_dispatched = False      # set by the engine: a recomputed block reuses the rows of its first run
         self.aux = None                   # last aux loss (added to the objective by the trainer)
@@ -211,10 +214,14 @@ class MoEFFN(nn.Module):
         d = self.dispatcher
         kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
         reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
+        if self.relocated and not reuse:
+            idx = self.expert_map[idx.long()].to(idx.dtype)      # experts live where the placement put them
         plan = kept["plan"] if reuse else d.plan(idx)
         self.last_tokens_per_expert = plan.tokens_per_expert_global
         if not RECOMPUTE_PHASE[0]:
-            c = plan.tokens_per_expert_global
+            c = plan.tokens_per_expert_global                    # by physical slot
+            if self.relocated:
+                c = c[self.expert_map]                           # ... reported by logical expert
             self.step_tokens_per_expert = c.clone() if self.step_tokens_per_expert is None \
                 else self.step_tokens_per_expert + c
         if reuse:

@@ -53,10 +53,7 @@ def build_snapshot(trainer, *, job_id: str = "", plan_id: str = "", session_id: 
         # analytic expectation for this config on B200 (achieved kernel rates, measured rank load): DIAGNOSE's
         # "tps < 0.8 x expected" soft signal compares against it
         from ..pilot.perf_model import expected_tps
-        ratio = 1.0
-        if moe and trainer._tpe_accum is not None and trainer.mesh.ep > 1:
-            per_rank = trainer._tpe_accum.float().reshape(trainer._tpe_accum.shape[0], trainer.mesh.ep, -1).sum(-1)
-            ratio = float((per_rank.max(1).values / per_rank.mean(1).clamp_min(1)).mean())
+        ratio = (trainer.rank_load_ratio() or 1.0) if (moe and trainer.mesh.ep > 1) else 1.0
         try:
             expected = expected_tps(trainer.cfg, trainer.mesh.world, rank_load_ratio=ratio)
         except (ZeroDivisionError, KeyError, ValueError):

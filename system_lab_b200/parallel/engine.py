@@ -143,7 +143,10 @@ class Engine:
                     *path, leaf = bn.split(".")
                     for part in path:
                         owner = getattr(owner, part)
-                    owner._buffers[leaf] = torch.zeros(b.shape, dtype=b.dtype, device=device)
+                    if leaf == "expert_map":        # identity placement: logical expert l lives in slot l
+                        owner._buffers[leaf] = torch.arange(b.shape[0], dtype=b.dtype, device=device)
+                    else:
+                        owner._buffers[leaf] = torch.zeros(b.shape, dtype=b.dtype, device=device)
             init_unit_weights(module, name, std, seed, mesh.ep_rank)
             for g in u.groups:
                 g.finalize()

@@ -96,6 +96,15 @@ class Trainer:
         self._keep_decided = False
         self.kept_rows = 0
         self.reached_target = False
+        self.relocator = None
+        self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
+        if cfg.model.moe_expert_relocation_interval > 0 and cfg.model.num_experts > 0:
+            from ..moe.relocation import ExpertRelocator
+            if mesh.edp > 1 or mesh.cp > 1:
+                raise ValueError("moe_expert_relocation_interval needs ep == dp on the stage and cp == 1")
+            self.relocator = ExpertRelocator(self.engine, self.optimizer, mesh, cfg.model.moe_expert_relocation_interval,
+                                             cfg.model.moe_expert_relocation_min_gain,
+                                             cfg.model.moe_expert_relocation_first_step)
         from .watchdog import FaultPlan, Heartbeat
         self.faults = FaultPlan.parse(t.fault_injection)
         self.heartbeat = None
@@ -247,9 +256,28 @@ class Trainer:
         if dist.is_initialized() and self.mesh.data_size > 1:
             dist.all_reduce(tpe, group=self.mesh.data_group)
         self._tpe_accum = tpe if self._tpe_accum is None else self._tpe_accum + tpe
+        # load per expert-parallel rank under the placement that was in force during this step
+        e_local = tpe.shape[1] // max(self.mesh.ep, 1)
+        rank_of = torch.stack([f.expert_map for f in ffns]).to(tpe.device) // e_local
+        per_rank = torch.zeros(tpe.shape[0], self.mesh.ep, dtype=tpe.dtype, device=tpe.device).scatter_add_(1, rank_of, tpe)
+        self._rank_load_accum = per_rank if self._rank_load_accum is None else self._rank_load_accum + per_rank
         if m.moe_router_load_balancing_type == "bias":
             for f, c in zip(ffns, tpe):
                 f.update_router_bias(c)
+        if self.relocator is not None:
+            self.relocator.observe(tpe)
+            rec = self.relocator.maybe_relocate(self.step + 1)
+            if rec and self.mesh.rank == 0:
+                print(f" expert placement at iteration {rec['step']}: moved {rec['experts_moved']} experts, rank load "
+                      f"max/mean {rec['imbalance_before']:.3f} -> {rec['imbalance_after_predicted']:.3f} (predicted)",
+                      flush=True)
+
+    def rank_load_ratio(self) -> float | None:
+        """Mean over MoE layers of max/mean tokens per expert-parallel rank, over the steps so far."""
+        if self._rank_load_accum is None:
+            return None
+        pr = self._rank_load_accum.float()
+        return float((pr.max(1).values / pr.mean(1).clamp_min(1)).mean())
 
     # ---- full run ----------------------------------------------------------------------------
     def fit(self, iters: int | None = None) -> dict:
@@ -328,3 +356,6 @@ class Trainer:
     def load_checkpoint(self, path: str) -> None:
         from ..ckpt.sharded import load_checkpoint
         load_checkpoint(self, path)
+        for f in self.engine.moe_ffns():              # a checkpoint written after expert relocation carries its placement
+            ident = torch.arange(f.expert_map.numel(), device=f.expert_map.device)
+            f.relocated = bool((f.expert_map != ident).any())
