@@ -59,6 +59,8 @@ LEVERS: dict[str, list[dict]] = {
         {"axis": "parallelism.pp", "op": "halve", "gain": 6.0, "risk": "memory"},
     ],
     "MOE_IMBALANCED": [
+        {"axis": "moe.expert_relocation_interval", "op": "set", "values": [100], "gain": 12.0,
+         "note": "re-place experts on ranks by measured load; the math is unchanged"},
         {"axis": "moe.capacity_factor", "op": "set", "values": [1.25, 2.0], "gain": 3.0},
         {"axis": "moe.aux_loss_coeff", "op": "set", "values": [1e-3, 1e-2], "gain": 5.0},
         {"axis": "moe.load_balancing", "op": "set", "values": ["bias"], "gain": 5.0},
@@ -116,7 +118,8 @@ def default_plan(world: int, *, ep: int | None = None, mbs: int = 2, gbs: int | 
             "runtime": {"mbs": mbs, "gbs": gbs or mbs * world, "recompute": "full", "optimizer_in_backward": False},
             "precision": {"fp8": False, "optimizer_state_dtype": "fp32", "master_weights": True},
             "comm": {"dispatcher": "fused", "fsdp_fused_collectives": False, "bucket_size_mb": 160},
-            "moe": {"capacity_factor": 0.0, "aux_loss_coeff": 0.0, "load_balancing": "aux_loss"},
+            "moe": {"capacity_factor": 0.0, "aux_loss_coeff": 0.0, "load_balancing": "aux_loss",
+                    "expert_relocation_interval": 0},
             "env": {"diff": {}}}
 
 
@@ -131,7 +134,8 @@ def plan_to_overrides(plan: dict) -> tuple[list[str], dict[str, str]]:
           f"master_weights={str(pr['master_weights']).lower()}", f"moe_token_dispatcher_type={c['dispatcher']}",
           f"fsdp_fused_collectives={str(c['fsdp_fused_collectives']).lower()}",
           f"ddp_bucket_size={int(c['bucket_size_mb']) * 250_000}", f"moe_capacity_factor={mo['capacity_factor']}",
-          f"moe_aux_loss_coeff={mo['aux_loss_coeff']}", f"moe_router_load_balancing_type={mo['load_balancing']}"]
+          f"moe_aux_loss_coeff={mo['aux_loss_coeff']}", f"moe_router_load_balancing_type={mo['load_balancing']}",
+          f"moe_expert_relocation_interval={int(mo.get('expert_relocation_interval', 0))}"]
     return ov, {k: str(v) for k, v in plan.get("env", {}).get("diff", {}).items()}
 
 
