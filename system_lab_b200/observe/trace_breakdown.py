@@ -85,8 +85,60 @@ def _events(path: str):
     except ImportError:
         pass
     with opener(path, "rt") as f:
-        data = json.load(f)
-    yield from (data["traceEvents"] if isinstance(data, dict) else data)
+        yield from _stream_events(f)
+
+
+def _stream_events(f, chunk: int = 1 << 22):
+    """Incremental reader for ``{"traceEvents": [ {...}, ... ], ...}`` (or a bare list of events): decodes one
+    event object at a time from a sliding text buffer, so memory stays at a few MB whatever the trace size."""
+    dec = json.JSONDecoder()
+    buf, pos, eof = "", 0, False
+
+    def refill():
+        nonlocal buf, pos, eof
+        data = f.read(chunk)
+        if not data:
+            eof = True
+            return False
+        buf = buf[pos:] + data
+        pos = 0
+        return True
+
+    # find the start of the event array
+    while True:
+        if not buf and not refill():
+            return
+        stripped = buf.lstrip()
+        if stripped.startswith("["):
+            pos = buf.index("[") + 1
+            break
+        k = buf.find('"traceEvents"')
+        if k >= 0:
+            b = buf.find("[", k)
+            if b >= 0:
+                pos = b + 1
+                break
+        if not refill():
+            return
+    while True:
+        # skip separators
+        while True:
+            while pos < len(buf) and buf[pos] in " \t\r\n,":
+                pos += 1
+            if pos < len(buf) or not refill():
+                break
+        if pos >= len(buf) or buf[pos] == "]":
+            return
+        try:
+            obj, end = dec.raw_decode(buf, pos)
+        except json.JSONDecodeError:
+            if not refill():
+                raise
+            continue
+        yield obj
+        pos = end
+        if pos > chunk:
+            buf, pos = buf[pos:], 0
 
 
 def _union_len(intervals: list[tuple[float, float]]) -> float:

@@ -81,3 +81,19 @@ def test_trace_gap_analysis(tmp_path):
     assert top["between"].endswith("window end") and abs(top["ms"] - 0.3) < 1e-6
     assert any("grouped_gemm_kernel" in x["between"] and "swiglu_fwd_kernel" in x["between"] for x in g["top_pairs"])
     assert "idle gaps of stream 7" in tb.format_report(r)
+
+
+def test_trace_reader_streams_large_files_in_small_chunks(tmp_path):
+    import io
+    from system_lab_b200.observe import trace_breakdown as tb
+    events = [{"ph": "X", "name": f"kernel_{i} \"quoted\" [x] {{y}}", "cat": "kernel", "ts": i * 10, "dur": 5,
+               "args": {"stream": 7, "nested": {"a": [1, 2, {"b": "]"}]}}} for i in range(3000)]
+    doc = json.dumps({"schemaVersion": 1, "traceEvents": events, "displayTimeUnit": "ms"})
+    for chunk in (64, 1000, 1 << 20):
+        got = list(tb._stream_events(io.StringIO(doc), chunk=chunk))
+        assert got == events
+    assert list(tb._stream_events(io.StringIO(json.dumps(events[:10])), chunk=50)) == events[:10]     # bare list
+    assert list(tb._stream_events(io.StringIO('{"traceEvents": []}'))) == []
+    p = tmp_path / "t.json"
+    p.write_text(doc)
+    assert sum(1 for _ in tb._events(str(p))) == 3000
