@@ -360,16 +360,18 @@ class SimpleMoE(nn.Module):
     def __init__(self, cfg: ModelConfig, *, ep_rank: int = 0, ep_size: int = 1, fp8: bool = False,
                  layer_start: int = 0, layer_end: int | None = None, first_stage: bool = True,
                  last_stage: bool = True, cp_group=None, cp_rank: int = 0, cp_size: int = 1,
-                 bf16_first_layers: int = 0, bf16_last_layers: int = 0):
+                 bf16_first_layers: int = 0, bf16_last_layers: int = 0, layer_ids=None):
         super().__init__()
         self.cfg = cfg
         layer_end = cfg.num_layers if layer_end is None else layer_end
+        # layer_ids: explicit (possibly non-contiguous) global layer indices, for interleaved pipeline stages
+        ids = list(layer_ids) if layer_ids is not None else list(range(layer_start, layer_end))
         self.embed = Embedding(cfg) if first_stage else None
 
         def layer_fp8(i):          # the first / last layers of the whole decoder may be kept out of fp8
             return fp8 if bf16_first_layers <= i < cfg.num_layers - bf16_last_layers else False
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group) for i in range(layer_start, layer_end)])
+            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group) for i in ids])
         self.head = Head(cfg) if last_stage else None
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.cp_rank, self.cp_size = cp_rank, cp_size

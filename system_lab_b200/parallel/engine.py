@@ -115,13 +115,18 @@ class Engine:
         self.selective = gran == "selective" and not aux_on
         self.recompute = gran == "full" or (gran == "selective" and aux_on)
         pp = mesh.pp
-        per_stage = m.num_layers // pp
-        self.layer_start = mesh.pp_rank * per_stage
-        self.layer_end = self.layer_start + per_stage
+        # Virtual pipeline stages: the decoder is cut into pp * vpp equal blocks, block v lives on rank v % pp as
+        # that rank's chunk v // pp, so a micro-batch visits every rank vpp times (interleaved schedule).
+        self.vpp = max(cfg.parallel.virtual_pipeline_model_parallel_size, 1) if pp > 1 else 1
+        per_block = m.num_layers // (pp * self.vpp)
+        self.chunk_layer_ids = [list(range((c * pp + mesh.pp_rank) * per_block, (c * pp + mesh.pp_rank + 1) * per_block))
+                                for c in range(self.vpp)]
+        self.layer_start = self.chunk_layer_ids[0][0]
+        self.layer_end = self.chunk_layer_ids[-1][-1] + 1
         with torch.device("meta"):
             self.model = SimpleMoE(
                 m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=(cfg.precision.fp8_recipe if cfg.precision.fp8 else False),
-                layer_start=self.layer_start, layer_end=self.layer_end,
+                layer_ids=[i for ids in self.chunk_layer_ids for i in ids],
                 first_stage=mesh.is_first_stage(), last_stage=mesh.is_last_stage(),
                 cp_group=mesh.cp_group if mesh.cp > 1 else None, cp_rank=mesh.cp_rank, cp_size=mesh.cp,
                 bf16_first_layers=cfg.precision.num_layers_at_start_in_bf16,
@@ -220,22 +225,30 @@ class Engine:
     def run_unit(self, unit: Unit, x: torch.Tensor, *extra):
         return _UnitFn.apply(self.anchor, self, unit, x, *extra)
 
-    def stage_forward(self, inp: torch.Tensor, targets: torch.Tensor | None):
+    def stage_forward(self, inp: torch.Tensor, targets: torch.Tensor | None, chunk: int | None = None):
         """First stage: ``inp`` are token ids ``[B, S]``; later stages: hidden ``[B, S, H]``.
-        Returns ``(output, aux_losses)`` where output is the scalar loss on the last stage."""
+        Returns ``(output, aux_losses)`` where output is the scalar loss on the last stage.  ``chunk`` selects one
+        of this rank's virtual pipeline stages (None: all local layers, the non-interleaved case)."""
         aux_all = []
         x = inp
-        if self.embed_unit is not None:
+        first_chunk = chunk is None or chunk == 0
+        last_chunk = chunk is None or chunk == self.vpp - 1
+        if self.embed_unit is not None and first_chunk:
             x = self.run_unit(self.embed_unit, x, self.compute_dtype)
         cos, sin = self.model.rope_tables(x.shape[1], x.device)
-        for u in self.layer_units:
+        if chunk is None:
+            units = self.layer_units
+        else:
+            per = len(self.layer_units) // self.vpp
+            units = self.layer_units[chunk * per:(chunk + 1) * per]
+        for u in units:
             out = self.run_unit(u, x, cos, sin)
             if isinstance(out, tuple):
                 x, aux = out
                 aux_all.append(aux)
             else:
                 x = out
-        if self.head_unit is not None:
+        if self.head_unit is not None and last_chunk:
             x = self.run_unit(self.head_unit, x, targets)
         return x, aux_all
 

@@ -134,3 +134,87 @@ def pipeline_forward_only(engine, mesh, batches, cfg) -> torch.Tensor:
         else:
             _p2p([dist.P2POp(dist.isend, out.contiguous(), next_r)])
     return loss_sum
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Interleaved (virtual) pipeline stages.  The decoder is cut into pp * vpp blocks; block v runs on rank v % pp as
+# that rank's chunk v // pp.  Micro-batches go through in groups of pp: a rank runs chunk 0 for the whole group,
+# then chunk 1, ...; every rank therefore sends to its right neighbour and receives from its left neighbour in
+# one fixed order (group, chunk, micro-batch), which is also the order the neighbour consumes / produces, so
+# FIFO point-to-point channels need no tags.  All forwards of the step run before the backwards (the layers are
+# recomputed in backward, so what stays alive per micro-batch is one boundary activation per chunk); the bubble
+# shrinks to (pp-1) / (pp-1 + M*vpp) as for any interleaved schedule.
+def _vstage_order(nmb: int, pp: int, vpp: int, reverse_chunks: bool = False):
+    chunks = range(vpp - 1, -1, -1) if reverse_chunks else range(vpp)
+    for g0 in range(0, nmb, pp):
+        for c in chunks:
+            for i in range(g0, min(g0 + pp, nmb)):
+                yield c, i
+
+
+def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only: bool = False) -> torch.Tensor:
+    """All micro-batches of one step through this rank's ``vpp`` chunks.  Returns the summed (unscaled) loss on
+    the rank that holds the last block and zero elsewhere."""
+    dev, pp, vpp, r = engine.device, mesh.pp, engine.vpp, mesh.pp_rank
+    nmb = len(batches)
+    if nmb % pp:
+        raise ValueError(f"interleaved stages need micro-batches per step ({nmb}) to be a multiple of pp ({pp})")
+    right, left = mesh.pp_ranks[(r + 1) % pp], mesh.pp_ranks[(r - 1) % pp]
+    mbs, seq = batches[0][0].shape
+    act_shape = (mbs, seq, cfg.model.hidden_size)
+    dt = engine.compute_dtype
+    last_v = pp * vpp - 1
+    loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
+    kept = {}                         # (chunk, micro-batch) -> (input hidden or None, output, aux list)
+    sends = []                        # outstanding isend handles (buffers are referenced until waited)
+
+    def send(t, dst):
+        t = t.contiguous()
+        sends.append((dist.isend(t, dst), t))
+
+    def recv(src):
+        buf = torch.empty(act_shape, dtype=dt, device=dev)
+        dist.recv(buf, src)
+        return buf
+
+    # ---- forwards ---------------------------------------------------------------------------------------------------
+    for c, i in _vstage_order(nmb, pp, vpp):
+        v = c * pp + r
+        tok, tgt = batches[i]
+        if v == 0:
+            inp, x = None, tok
+        else:
+            inp = recv(left)
+            if not forward_only:
+                inp.requires_grad_(True)
+            x = inp
+        out, aux = engine.stage_forward(x, tgt if v == last_v else None, chunk=c)
+        if v == last_v:
+            if forward_only:
+                loss_sum = loss_sum + out.detach().float()
+        else:
+            send(out.detach(), right)
+        if not forward_only:
+            kept[(c, i)] = (inp, out, aux)
+    if forward_only:
+        for h, _ in sends:
+            h.wait()
+        return loss_sum
+    # ---- backwards: same groups, chunks from last to first ----------------------------------------------------------------
+    for c, i in _vstage_order(nmb, pp, vpp, reverse_chunks=True):
+        v = c * pp + r
+        inp, out, aux = kept.pop((c, i))
+        if v == last_v:
+            loss_sum = loss_sum + out.detach().float()
+            tensors, grads = [out], [torch.full_like(out, scale)]
+        else:
+            tensors, grads = [out], [recv(right)]
+        for a in aux:
+            tensors.append(a)
+            grads.append(torch.full_like(a, scale))
+        torch.autograd.backward(tensors, grads)
+        if v != 0:
+            send(inp.grad, left)
+    for h, _ in sends:
+        h.wait()
+    return loss_sum

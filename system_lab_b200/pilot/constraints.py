@@ -83,9 +83,11 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
                               "optimizer_in_backward needs exactly one micro-batch per step"))
     if p.virtual_pipeline_model_parallel_size > 1 and pp == 1:
         out.append(_p("vpp_requires_pp_gt_1", "vpp > 1 needs pp > 1"))
-    if p.virtual_pipeline_model_parallel_size > 1 and pp > 1:
-        out.append(_p("vpp_not_implemented", "the pipeline schedule is plain 1F1B: interleaved stages (vpp > 1) are "
-                      "not implemented, use more micro-batches to shrink the bubble"))
+    if p.virtual_pipeline_model_parallel_size > 1 and pp > 1 and dp is not None:
+        nmb_here = t.global_batch_size // max(t.micro_batch_size * dp, 1)
+        if nmb_here % pp:
+            out.append(_p("vpp_microbatches_multiple_of_pp", f"interleaved stages need micro-batches per step "
+                          f"({nmb_here}) to be a multiple of pp ({pp})"))
     # 4. MoE
     if m.num_experts and m.moe_router_topk > m.num_experts:
         out.append(_p("top_k_le_num_experts", f"topk={m.moe_router_topk} > num_experts={m.num_experts}"))

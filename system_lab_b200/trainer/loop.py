@@ -142,7 +142,10 @@ class Trainer:
             self.optimizer.begin_step(lr)
         scale = 1.0 / (nmb * mesh.data_size)
         loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
-        if mesh.pp > 1:
+        if mesh.pp > 1 and self.engine.vpp > 1:
+            from ..parallel.pp import pipeline_interleaved
+            loss_sum = pipeline_interleaved(self.engine, mesh, dev_batches, scale, cfg)
+        elif mesh.pp > 1:
             from ..parallel.pp import pipeline_1f1b
             loss_sum = pipeline_1f1b(self.engine, mesh, dev_batches, scale, cfg)
         else:
@@ -203,7 +206,10 @@ class Trainer:
             batches = [(a.to(dev), b.to(dev)) for a, b in self.eval_data.microbatches(offset + i)]
             if self.eval_data is self.data:
                 self.data.cursor = self.step            # serving evaluation batches does not move the training cursor
-            if mesh.pp > 1:
+            if mesh.pp > 1 and self.engine.vpp > 1:
+                from ..parallel.pp import pipeline_interleaved
+                total = total + pipeline_interleaved(self.engine, mesh, batches, 1.0, cfg, forward_only=True)
+            elif mesh.pp > 1:
                 from ..parallel.pp import pipeline_forward_only
                 total = total + pipeline_forward_only(self.engine, mesh, batches, cfg)
             else:

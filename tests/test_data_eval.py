@@ -70,3 +70,12 @@ def test_eval_is_layout_invariant(tmp_path):
     pp = run_ranks(_fit, 2, path, ["expert_model_parallel_size=1", "pipeline_model_parallel_size=2", "train_iters=5"],
                    timeout=400)
     assert pp[0][0] == pytest.approx(one, rel=2e-5) and pp[1][0] == pp[0][0]
+
+
+def test_eval_through_interleaved_pipeline_stages(tmp_path):
+    path = _write(tmp_path)
+    four = ["num_layers=4", "train_iters=2"]
+    (one, _, _, _, _), = run_ranks(_fit, 1, path, four + ["expert_model_parallel_size=1"], timeout=400)
+    vp = run_ranks(_fit, 2, path, four + ["expert_model_parallel_size=1", "pipeline_model_parallel_size=2",
+                                          "virtual_pipeline_model_parallel_size=2"], timeout=400)
+    assert vp[0][0] == pytest.approx(one, rel=2e-5) and vp[1][0] == vp[0][0]

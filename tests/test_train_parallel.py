@@ -105,3 +105,25 @@ def test_checkpoint_reshard_ws2_to_ws1(tmp_path):
     full = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2"], 3, ck, None, 3)
     resumed = run_ranks(_train, 1, BASE + ["expert_model_parallel_size=1"], 3, None, ck)
     assert resumed[0][0] == pytest.approx(full[0][0][3:], rel=2e-5, abs=2e-5)
+
+
+def test_interleaved_virtual_pipeline_matches():
+    """pp=2 with two virtual stages per rank (blocks 0,2 on rank 0 and 1,3 on rank 1) reproduces the single-process
+    curve of the same 4-layer model; so does pp=2 x ep=2 on four ranks, and evaluation goes through the same path."""
+    four = BASE + ["num_layers=4"]
+    (ref, _), = run_ranks(_train, 1, four + ["expert_model_parallel_size=1"], 5)
+    res = run_ranks(_train, 2, four + ["expert_model_parallel_size=1", "pipeline_model_parallel_size=2",
+                                       "virtual_pipeline_model_parallel_size=2"], 5)
+    assert res[0][0] == pytest.approx(ref, rel=2e-5, abs=2e-5) and res[1][0] == res[0][0]
+    res4 = run_ranks(_train, 4, four + ["expert_model_parallel_size=2", "pipeline_model_parallel_size=2",
+                                        "virtual_pipeline_model_parallel_size=2", "recompute_granularity=selective"], 5)
+    assert res4[0][0] == pytest.approx(ref, rel=2e-5, abs=2e-5)
+
+
+def test_interleaved_needs_microbatches_multiple_of_pp():
+    from system_lab_b200.config import Config, ConfigError
+    cfg = Config.load(preset="simplemoe-tiny", overrides=["num_layers=4", "global_batch_size=2", "micro_batch_size=2",
+                                                          "pipeline_model_parallel_size=2", "expert_model_parallel_size=1",
+                                                          "virtual_pipeline_model_parallel_size=2"])
+    with pytest.raises(ConfigError, match="multiple of pp"):
+        cfg.validate(2)
