@@ -43,6 +43,11 @@ class Mesh:
     ep_ranks: tuple = ()
     edp_ranks: tuple = ()
     pp_ranks: tuple = ()
+    # one-directional channels for the interleaved pipeline schedule: "up" carries messages from a lower to a
+    # higher stage index, "down" the rest, so two neighbours that both have a send at the head of their queues
+    # (possible with the wrap-around link) never wait on each other within one communicator
+    pp_group_up: object = None
+    pp_group_down: object = None
 
     @property
     def edp(self) -> int:
@@ -139,4 +144,6 @@ def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1) -> Mesh:
     m.cp_group, _ = mk(cp_lists, None)
     pp_lists = [[rid(p, d, c) for p in range(pp)] for d in range(dp) for c in range(cp)]
     m.pp_group, m.pp_ranks = mk(pp_lists, None)
+    m.pp_group_up, _ = mk(pp_lists, None)
+    m.pp_group_down, _ = mk(pp_lists, None)
     return m

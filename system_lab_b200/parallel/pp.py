@@ -168,13 +168,18 @@ def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only:
     kept = {}                         # (chunk, micro-batch) -> (input hidden or None, output, aux list)
     sends = []                        # outstanding isend handles (buffers are referenced until waited)
 
-    def send(t, dst):
-        t = t.contiguous()
-        sends.append((dist.isend(t, dst), t))
+    r_right, r_left = (r + 1) % pp, (r - 1) % pp
 
-    def recv(src):
+    def chan(src_stage: int, dst_stage: int):
+        return mesh.pp_group_up if dst_stage > src_stage else mesh.pp_group_down
+
+    def send(t, dst, dst_stage):
+        t = t.contiguous()
+        sends.append((dist.isend(t, dst, group=chan(r, dst_stage)), t))
+
+    def recv(src, src_stage):
         buf = torch.empty(act_shape, dtype=dt, device=dev)
-        dist.recv(buf, src)
+        dist.recv(buf, src, group=chan(src_stage, r))
         return buf
 
     # ---- forwards ---------------------------------------------------------------------------------------------------
@@ -184,7 +189,7 @@ def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only:
         if v == 0:
             inp, x = None, tok
         else:
-            inp = recv(left)
+            inp = recv(left, r_left)
             if not forward_only:
                 inp.requires_grad_(True)
             x = inp
@@ -193,7 +198,7 @@ def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only:
             if forward_only:
                 loss_sum = loss_sum + out.detach().float()
         else:
-            send(out.detach(), right)
+            send(out.detach(), right, r_right)
         if not forward_only:
             kept[(c, i)] = (inp, out, aux)
     if forward_only:
@@ -208,13 +213,13 @@ def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only:
             loss_sum = loss_sum + out.detach().float()
             tensors, grads = [out], [torch.full_like(out, scale)]
         else:
-            tensors, grads = [out], [recv(right)]
+            tensors, grads = [out], [recv(right, r_right)]
         for a in aux:
             tensors.append(a)
             grads.append(torch.full_like(a, scale))
         torch.autograd.backward(tensors, grads)
         if v != 0:
-            send(inp.grad, left)
+            send(inp.grad, left, r_left)
     for h, _ in sends:
         h.wait()
     return loss_sum
