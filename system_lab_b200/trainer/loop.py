@@ -334,7 +334,8 @@ class Trainer:
         if cfg.checkpoint.save and not cfg.checkpoint.disable_last_saving:
             self.save_checkpoint(cfg.checkpoint.save)
         if self.events:
-            self.events.stop(self.tokens_per_step * self.step)
+            ok = self.reached_target or not t.eval_target_loss
+            self.events.stop(self.tokens_per_step * self.step, status="success" if ok else "aborted")
         snap = self.snapshot()
         if cfg.profile.snapshot_path and self.mesh.rank == 0:
             Path(cfg.profile.snapshot_path).parent.mkdir(parents=True, exist_ok=True)
