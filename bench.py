@@ -40,8 +40,8 @@ def parse():
     ap.add_argument("--gbs", type=int, default=0, help="global batch in sequences (default: seqs-per-gpu x N)")
     ap.add_argument("--mbs", type=int, default=0, help="micro-batch in sequences (default: seqs-per-gpu)")
     ap.add_argument("--keep-dispatched", action="store_true",
-                    help="when memory allows, keep every layer's dispatched rows for the recomputed block (sized "
-                         "from the first step; a later step that needs more rows ends the run with CAPACITY)")
+                    help="when memory allows, keep every layer's dispatched rows for the recomputed block (exactly "
+                         "the rows in use: one host read of the row count per layer and forward pass)")
     ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
@@ -124,11 +124,11 @@ def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = Fals
                 if allow_keep and gran == "selective" and cfg.model.num_experts > 0 \
                         and cfg.model.moe_keep_dispatched_factor == 0:
                     # spare memory buys speed: keep every layer's dispatched rows so the recomputed block needs
-                    # no second plan exchange and dispatch; -1 = sized from the rows in use during the first step
+                    # no second plan exchange and dispatch; -1 = exactly the rows in use (one host read per layer)
                     cfg.model.moe_keep_dispatched_factor = -1.0
                     est2 = estimate_memory(cfg, world)
                     if est2["total_bytes"] <= 0.75 * est2["hbm_bytes"]:       # optional: only with real headroom
-                        last.update(keep_dispatched="auto", est_gb=round(est2["total_bytes"] / 2**30, 1))
+                        last.update(keep_dispatched="exact", est_gb=round(est2["total_bytes"] / 2**30, 1))
                     else:
                         cfg.model.moe_keep_dispatched_factor = 0.0
                 return last
@@ -272,7 +272,6 @@ def main() -> int:
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
-            "kept_dispatch_rows": trainer.kept_rows,
             "expert_relocations": trainer.relocator.history if trainer.relocator else [],
         }
         print(json.dumps(line))

@@ -95,7 +95,7 @@ class ModelConfig:
     moe_expert_relocation_first_step: int = 0    # > 0: also decide once at this step (early skew of a fresh router)
     moe_expert_relocation_min_gain: float = 0.05  # relative drop of max/mean rank load that justifies moving experts
     moe_combine_push: bool = True        # expert GEMM epilogues push result rows to the token owners (fused combine)
-    moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = x balanced load, <0 = sized from the first step, 0 = off
+    moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = fixed copy of x balanced load (no host sync, overflow is an error), <0 = exactly the rows in use (one host read per layer), 0 = off
 
 
 @dataclass

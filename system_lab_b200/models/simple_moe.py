@@ -242,8 +242,6 @@ class MoEFFN(nn.Module):
         if kept is not None and not RECOMPUTE_PHASE[0] and not torch.is_grad_enabled():
             kept["plan"] = plan
             kept["xe"], kept["pe"] = d.keep_dispatched(plan, xe, pe)
-        elif getattr(d, "auto_keep", False) and not RECOMPUTE_PHASE[0]:
-            d.note_rows_in_use(plan)             # sizing information for the trainer's keep decision
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 dgrad_out=out_buf)
         act = ops.swiglu_probs(h1, pe, rows_dev=getattr(plan, "meta", None))

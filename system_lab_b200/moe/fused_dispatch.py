@@ -124,11 +124,12 @@ class FusedDispatcher:
         self._peer_ptrs = (ctypes.c_long * 16)(*(list(workspace.ptrs) + [0] * (16 - len(workspace.ptrs))))
         self._lay = [self._layout(0), self._layout(1)]
         self.epoch = 0
-        # Rows a recomputed block keeps of its first dispatch.  keep_factor > 0: that multiple of the balanced
-        # per-rank load, fixed; keep_factor < 0: decided by the trainer from the rows it saw in use during the
-        # first step (`set_keep_rows`), nothing is kept until then; 0: never.
-        self.auto_keep = keep_factor < 0
-        self.keep_rows = 0
+        # Rows a recomputed block keeps of its first dispatch.  keep_factor > 0: a fixed copy of that multiple of
+        # the balanced per-rank load (no host sync; more rows in use than the copy holds is reported as CAPACITY);
+        # keep_factor < 0: exactly the rows in use, read back from the plan (one host sync per layer and forward
+        # pass, nothing can overflow); 0: never.
+        self.keep_exact = keep_factor < 0
+        self.keep_rows = cap if self.keep_exact else 0
         if keep_factor > 0:
             self.set_keep_rows(int(keep_factor * pairs))
         self.rows_seen = torch.zeros(1, dtype=torch.int32, device=device)
@@ -252,12 +253,16 @@ class FusedDispatcher:
         cops.call("slab_moe_check_rows", plan.meta, 0, self.status, self.rows_seen, cops.stream())
 
     def keep_dispatched(self, plan: FusedPlan, xe: torch.Tensor, pe: torch.Tensor | None):
-        """Copies of the received rows (first ``keep_rows``) and gate probabilities for a later
-        ``redispatch_kept``; more rows in use than ``keep_rows`` is reported as CAPACITY through the status
-        word.  The plan is made self-contained (its origin table no longer aliases the workspace)."""
-        n = self.keep_rows
-        cops.call("slab_moe_check_rows", plan.meta, n, self.status, self.rows_seen, cops.stream())
-        plan.origin = self.origin.clone()
+        """Copies of the received rows and gate probabilities for a later ``redispatch_kept``: exactly the rows in
+        use (``keep_exact``) or the first ``keep_rows`` (more rows in use is reported as CAPACITY through the status
+        word).  The plan is made self-contained (its origin table no longer aliases the workspace)."""
+        if self.keep_exact:
+            used = int(plan.meta[0].item())               # host sync: rows in use on this rank (padded segments)
+            n = min(max(used, self.pad), self.capacity)
+        else:
+            n = self.keep_rows
+            cops.call("slab_moe_check_rows", plan.meta, n, self.status, self.rows_seen, cops.stream())
+        plan.origin = self.origin[:n].clone() if self.keep_exact else self.origin.clone()
         return xe[:n].clone(), (pe[:n].clone() if pe is not None else None)
 
     def redispatch_kept(self, plan: FusedPlan, x: torch.Tensor, probs: torch.Tensor | None, xs: torch.Tensor,

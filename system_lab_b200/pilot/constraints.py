@@ -204,7 +204,7 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
         if m.num_experts > 0 and m.moe_keep_dispatched_factor != 0:
             # dispatched rows (+ gate scalar, origin) of every MoE layer kept for the recomputed block
             moe_layers = max(layers_here - (m.first_k_dense if pp == 1 else 0), 0)
-            kf = m.moe_keep_dispatched_factor if m.moe_keep_dispatched_factor > 0 else 2.0   # < 0: sized at run time
+            kf = m.moe_keep_dispatched_factor if m.moe_keep_dispatched_factor > 0 else 2.0   # < 0: exact rows, bounded here by 2x
             kept_rows = kf * slots + (m.num_experts // ep) * m.moe_pad_expert_rows_to
             acts += moe_layers * kept_rows * (h * act_b + 8) * min(nmb, pp)
     else:

@@ -45,11 +45,6 @@ def model_flops_per_token(m) -> float:
     return 3.0 * (matmul + attn)
 
 
-def cfg_nmb(cfg: Config, mesh: Mesh) -> int:
-    """Micro-batches per step on one data rank."""
-    return max(cfg.train.global_batch_size // max(cfg.train.micro_batch_size * mesh.dp, 1), 1)
-
-
 class NumericalError(RuntimeError):
     """Loss or gradient norm is NaN/Inf (failure kind NUMERICAL)."""
 
@@ -93,8 +88,6 @@ class Trainer:
         self.flops_per_token = model_flops_per_token(cfg.model)
         self.tokens_per_step = t.global_batch_size * cfg.model.seq_length
         self._tpe_accum = None
-        self._keep_decided = False
-        self.kept_rows = 0
         self.reached_target = False
         self.relocator = None
         self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
@@ -128,8 +121,6 @@ class Trainer:
                 self.heartbeat.muted = True
             self.heartbeat.check()             # a peer that hung or failed is reported before anything is launched
             self.heartbeat.begin(step)
-        if not self._keep_decided:
-            self._decide_kept_rows()
         if batches is None:
             batches = self.data.microbatches(self.step)
         nmb = len(batches)
@@ -218,35 +209,6 @@ class Trainer:
                     total = total + loss.float()
             count += len(batches)
         return total, count
-
-    def _decide_kept_rows(self) -> None:
-        """``moe_keep_dispatched_factor < 0``: after one full step, size the copy of the dispatched rows that the
-        recomputed feed-forward block keeps from 1.5x the largest row count seen on any rank, if the memory is
-        there.  Every rank must take the same decision (a rank that keeps its rows skips the second plan exchange
-        and dispatch), so the inputs are reduced over all ranks.  Costs one host sync, once."""
-        d = getattr(self.engine, "dispatcher", None)
-        if d is None or not getattr(d, "auto_keep", False):
-            self._keep_decided = True
-            return
-        if self.step < 1:
-            return
-        dev = self.device
-        seen = d.rows_seen.clone()
-        multi = dist.is_initialized() and self.mesh.world > 1
-        if multi:
-            dist.all_reduce(seen, op=dist.ReduceOp.MAX)
-        rows = min(int(int(seen.item()) * 1.5), d.capacity)
-        moe_layers = len(self.engine.moe_ffns())
-        in_flight = max(min(self.mesh.pp, cfg_nmb(self.cfg, self.mesh)), 1)
-        need = moe_layers * in_flight * (rows + d.E // d.ep * d.pad) * (d.H * 2 + 8)
-        free, _ = torch.cuda.mem_get_info(dev)
-        avail = free + torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
-        ok = torch.tensor([1 if (rows > 0 and need < 0.6 * avail) else 0], dtype=torch.int32, device=dev)
-        if multi:
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()):
-            self.kept_rows = d.set_keep_rows(rows)
-        self._keep_decided = True
 
     def _update_router_bias(self) -> None:
         m = self.cfg.model
