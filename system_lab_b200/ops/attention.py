@@ -47,7 +47,7 @@ def _library(q, k, v, scale, window):
             if _CUDNN_OK[0]:
                 raise
             _CUDNN_OK[0] = False
-    if d == dv and d <= 256 and q.dtype in (torch.bfloat16, torch.float16):
+    if q.is_cuda and d == dv and d <= 256 and q.dtype in (torch.bfloat16, torch.float16):
         try:
             from flash_attn import flash_attn_func
             win = (window - 1, 0) if window > 0 else (-1, -1)

@@ -322,6 +322,8 @@ class _RouterLogits(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
+        if not x.is_cuda:                      # the fp32-output GEMM variant exists on the GPU only
+            return x.float() @ w.float().t()
         return torch.mm(x, w.t(), out_dtype=torch.float32)
 
     @staticmethod

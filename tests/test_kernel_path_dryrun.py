@@ -1,0 +1,116 @@
+"""Dry run of the kernel route on CPU: every entry point of the kernel library is replaced by a recorder that
+launches nothing, so one training step of a tiny bf16 model walks the same Python code a GPU step does (autograd
+functions, push targets, kept dispatch, fp8 recipes, dead outputs of the recomputed block) and fails on any
+host-side mistake (wrong argument lists, wrong number of returned gradients, shape bookkeeping).  Numbers are
+meaningless here; the GPU suite checks those."""
+import pytest
+import torch
+
+
+@pytest.fixture
+def dry(monkeypatch):
+    from system_lab_b200 import ops
+    from system_lab_b200.ops import cuda as cops
+    try:
+        cops.lib()
+    except Exception as e:
+        pytest.skip(f"kernel library not built: {e}")
+    calls = []
+
+    def fake_call(name, *args):
+        assert name in cops._SIGS, f"unregistered entry point {name}"
+        assert len(args) == len(cops._SIGS[name]), (name, len(args), len(cops._SIGS[name]))
+        for a, kind in zip(args, cops._SIGS[name]):
+            if kind == "p":
+                assert a is None or isinstance(a, (torch.Tensor, int)), (name, type(a))
+            elif kind in "il":
+                assert isinstance(a, int) and not isinstance(a, bool), (name, kind, type(a), a)
+            elif kind == "f":
+                assert isinstance(a, (int, float)), (name, type(a))
+        for a in args:                    # index-like buffers must hold valid indices for the host-side torch ops
+            if isinstance(a, torch.Tensor) and a.dtype in (torch.int32, torch.int64):
+                a.data.zero_()
+        calls.append(name)
+        cops.LAUNCHES[0] += 1
+        return 0
+
+    monkeypatch.setattr(cops, "call", fake_call)
+    monkeypatch.setattr(cops, "stream", lambda: 0)
+    monkeypatch.setattr(ops, "use_kernels", lambda *t: True)
+    monkeypatch.setattr(ops, "set_kernel_mode", lambda mode: None)
+    return calls
+
+
+def _trainer(extra, dispatcher_kw=None):
+    from system_lab_b200.config import Config
+    from system_lab_b200.moe.fused_dispatch import FusedDispatcher
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "params_dtype=bf16", "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=1",
+        "hidden_size=256", "moe_ffn_hidden_size=128", "kv_channels=64", "device=cpu", "moe_pad_expert_rows_to=128"] + extra)
+    tr = Trainer(cfg)
+    m = cfg.model
+    d = FusedDispatcher(tr.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
+                        cfg.train.micro_batch_size * m.seq_length, 128, torch.device("cpu"),
+                        clone_outputs=not (tr.engine.recompute or tr.engine.selective), **(dispatcher_kw or {}))
+    for f in tr.engine.moe_ffns():
+        f.dispatcher = d
+    tr.engine.dispatcher = d
+    return tr, d
+
+
+@pytest.mark.parametrize("extra,kw", [
+    (["recompute_granularity=selective"], {}),
+    (["recompute_granularity=selective"], {"push": True}),
+    (["recompute_granularity=selective", "moe_keep_dispatched_factor=-1"], {"push": True, "keep_factor": -1.0}),
+    (["recompute_granularity=selective", "moe_keep_dispatched_factor=2"], {"keep_factor": 2.0}),
+    (["recompute_granularity=full"], {"push": True}),
+    (["recompute_granularity=none"], {"push": True}),
+    (["recompute_granularity=selective", "fp8=true", "fp8_recipe=rowwise"], {"push": True}),
+    (["recompute_granularity=selective", "fp8=true", "fp8_recipe=blockwise"], {}),
+    (["recompute_granularity=selective", "optimizer_in_backward=true", "master_weights=false",
+      "optimizer_state_dtype=fp8", "global_batch_size=2"], {}),
+    (["recompute_granularity=selective", "global_batch_size=8"], {"push": True}),          # four micro-batches
+])
+def test_one_step_walks_the_kernel_route(dry, extra, kw):
+    tr, d = _trainer(extra, kw)
+    out = tr.train_step()
+    assert out["loss"].shape == ()
+    names = set(dry)
+    assert {"slab_grouped_gemm_bf16", "slab_moe_scatter", "slab_moe_plan_slots", "slab_adamw"} <= names
+    if kw.get("push"):
+        assert "slab_grouped_gemm_bf16_push" in names and "slab_moe_reduce_pairs" in names
+        assert d._pending_push == {}                        # every push was consumed by its reduction
+        assert d.push_epoch == dry.count("slab_grouped_gemm_bf16_push") == dry.count("slab_moe_reduce_pairs")
+    if "fp8=true" in extra:
+        assert ("slab_grouped_gemm_fp8_rowwise" in names) or ("slab_grouped_gemm_fp8" in names)
+    gbs = next((int(x.split("=")[1]) for x in extra if x.startswith("global_batch_size=")), 4)
+    layers, nmb = 2, gbs // 2                                   # micro-batches of 2 sequences on one rank
+    scatters = dry.count("slab_moe_scatter")
+    if "moe_keep_dispatched_factor=-1" in extra or "moe_keep_dispatched_factor=2" in extra:
+        assert scatters == layers * nmb * 2                  # forward dispatch + backward of combine; no re-dispatch
+    elif "recompute_granularity=none" in extra:
+        assert scatters == layers * nmb * 2
+    else:
+        assert scatters == layers * nmb * 3                  # + the recomputed block's dispatch
+
+
+MLA = ["attention_type=mla", "q_lora_rank=64", "kv_lora_rank=64", "qk_nope_head_dim=32", "qk_rope_head_dim=32",
+       "v_head_dim=32", "moe_shared_expert_intermediate_size=128", "moe_router_score_function=sigmoid",
+       "moe_router_load_balancing_type=bias", "first_k_dense=1", "ffn_hidden_size=256", "num_layers=3"]
+
+
+@pytest.mark.parametrize("extra,kw", [
+    (MLA + ["recompute_granularity=selective"], {"push": True}),
+    (["sliding_window=16", "recompute_granularity=full", "num_layers=2"], {}),
+    (["moe_aux_loss_coeff=0.01", "recompute_granularity=selective"], {"push": True}),      # aux loss: falls back to full
+    (["moe_router_force_load_balancing=true", "recompute_granularity=selective"], {}),
+    (["moe_expert_relocation_interval=1", "moe_expert_relocation_min_gain=0.0", "recompute_granularity=selective"], {}),
+])
+def test_model_variants_walk_the_kernel_route(dry, extra, kw):
+    tr, d = _trainer(extra, kw)
+    for _ in range(2):
+        out = tr.train_step()
+        assert out["loss"].shape == ()
+    assert "slab_grouped_gemm_bf16" in set(dry) and d._pending_push == {}
+    tr.evaluate(1)
