@@ -114,6 +114,7 @@ class ParallelConfig:
     ddp_average_in_collective: bool = True
     num_distributed_optimizer_instances: int = 1
     fsdp_fused_collectives: bool = True  # peer-memory all-gather / reduce-scatter kernels instead of NCCL
+    fsdp_prefetch: bool = False          # gather the next unit's parameters on a side stream while this one computes
 
 
 @dataclass

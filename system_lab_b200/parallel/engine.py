@@ -54,6 +54,7 @@ class _UnitFn(torch.autograd.Function):
         ctx.recompute = recompute
         unit.gather()
         engine.after_gather(unit, forward=True)
+        engine.prefetch_neighbour(unit, +1)
         x_needs_grad = x.is_floating_point()
         if recompute:
             with torch.no_grad():
@@ -79,6 +80,7 @@ class _UnitFn(torch.autograd.Function):
         engine, unit = ctx.engine, ctx.unit
         unit.gather()
         engine.after_gather(unit, forward=False)
+        engine.prefetch_neighbour(unit, -1)
         if ctx.recompute:
             from ..models import simple_moe
             simple_moe.RECOMPUTE_PHASE[0] = True
@@ -166,6 +168,16 @@ class Engine:
                 l.ffn.keep_dispatched = self.selective and cfg.model.moe_keep_dispatched_factor != 0
         self.head_unit = add("head", self.model.head) if self.model.head is not None else None
         self._make_dispatchers()
+        self._unit_index = {u.name: i for i, u in enumerate(self.units)}
+        self._prefetch_stream = None
+        if cfg.parallel.fsdp_prefetch and dense_comm is not None and self.vpp == 1:
+            from ..comm.fsdp_comm import FsdpPeerComm
+            pf = FsdpPeerComm(mesh.data_group, mesh.data_size, mesh.data_rank, device)
+            for u in self.units:
+                for g in u.groups:
+                    if g.comm is dense_comm:
+                        g.prefetch_comm = pf
+            self._prefetch_stream = torch.cuda.Stream(device=device)
 
     # ---- construction helpers ---------------------------------------------------
     def _make_comms(self):
@@ -205,6 +217,15 @@ class Engine:
     # ---- hooks called from the autograd node -----------------------------------------
     def after_gather(self, unit: Unit, forward: bool) -> None:
         pass
+
+    def prefetch_neighbour(self, unit: Unit, direction: int) -> None:
+        """``fsdp_prefetch``: start gathering the unit that runs next (forward: the following one, backward: the
+        preceding one) on a side stream while this unit computes."""
+        if self._prefetch_stream is None:
+            return
+        i = self._unit_index.get(unit.name, -1) + direction
+        if 0 <= i < len(self.units):
+            self.units[i].prefetch(self._prefetch_stream)
 
     def pop_aux(self, unit: Unit):
         ffn = getattr(unit.module, "ffn", None)

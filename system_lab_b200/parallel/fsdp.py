@@ -82,6 +82,8 @@ class FlatGroup:
         self.grad_shard: torch.Tensor | None = None     # fp32 accumulation over micro-batches
         self.replica_group = None                       # unsharded data-parallel replicas (plain DDP)
         self.gathered = True
+        self.prefetch_comm = None                       # second peer-comm instance used only by prefetch()
+        self._pf_event = None                           # set while a prefetched gather is in flight
 
     def finalize(self) -> None:
         """Take the owned shard (the optimizer's source of truth) from the initialised full buffer."""
@@ -126,8 +128,31 @@ class FlatGroup:
             p.grad = None
         return g
 
+    def prefetch(self, stream) -> None:
+        """Start this group's all-gather on ``stream`` so that it runs beside the current unit's compute; the next
+        ``gather()`` only waits for it.  Uses its own peer workspace: the flag protocol of a comm instance assumes
+        one stream issues its calls in order."""
+        if not self.sharded or self.gathered or self._pf_event is not None or self.prefetch_comm is None:
+            return
+        st = self.full.untyped_storage()
+        if st.size() == 0:
+            st.resize_(self.total * self.full.element_size())      # allocated on the compute stream's pool
+        main = torch.cuda.current_stream(self.device)
+        stream.wait_stream(main)                                    # the shard (optimizer output) is final
+        src = self.shard_in_compute_dtype()
+        with torch.cuda.stream(stream):
+            self.prefetch_comm.all_gather(self.full.data, src, self)
+            ev = torch.cuda.Event()
+            ev.record(stream)
+        self._pf_event = ev
+
     def gather(self) -> None:
         if self.gathered:
+            return
+        if self._pf_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._pf_event)
+            self._pf_event = None
+            self.gathered = True
             return
         if self.sharded:
             st = self.full.untyped_storage()
@@ -236,6 +261,10 @@ class Unit:
     def gather(self):
         for g in self.groups:
             g.gather()
+
+    def prefetch(self, stream):
+        for g in self.groups:
+            g.prefetch(stream)
 
     def release(self):
         for g in self.groups:
