@@ -13,17 +13,36 @@ Every logical tensor is stored as pieces ``{fqn, global_shape, flat_start, flat_
 contiguous range of the flattened *global* tensor (for expert tensors the global tensor spans all
 experts).  Loading walks the pieces that intersect what the new layout owns, so a checkpoint written
 under one ``dp/ep/pp`` loads under another.  Directories are written under a temporary name and
-renamed, so a killed save never leaves a half checkpoint that looks complete.
+renamed, so a killed save never leaves a half checkpoint that looks complete.  Every rank file has a SHA-256
+sidecar; a file that fails its check (or cannot be unpickled) makes *all* ranks reject that step together and
+fall back to the previous complete one.
 """
 from __future__ import annotations
 
+import hashlib
 import json
+import logging
 import os
 import shutil
 from pathlib import Path
 
 import torch
 import torch.distributed as dist
+
+
+log = logging.getLogger(__name__)
+
+
+class CheckpointCorrupt(RuntimeError):
+    """A rank file is missing, fails its checksum or cannot be read."""
+
+
+def _sha256(path: Path) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for chunk in iter(lambda: f.read(1 << 24), b""):
+            h.update(chunk)
+    return h.hexdigest()
 
 
 def _barrier():
@@ -98,7 +117,9 @@ def save_checkpoint(trainer, root: str) -> str:
     payload = {"tensors": tensors, "index": index, "buffers": buffers,
                "opt_step": opt.step_count, "prev_norm": opt._prev_norm,
                "torch_rng": torch.get_rng_state()}
-    torch.save(payload, tmp / f"rank_{mesh.rank:05d}.pt")
+    mine = tmp / f"rank_{mesh.rank:05d}.pt"
+    torch.save(payload, mine)
+    mine.with_suffix(".sha256").write_text(_sha256(mine))
     _barrier()
     if mesh.rank == 0:
         meta = {"format": "system_lab_b200.ckpt.v1", "step": trainer.step, "world": mesh.world,
@@ -135,8 +156,47 @@ def resolve(path: str) -> Path:
     raise FileNotFoundError(f"no checkpoint under {path}")
 
 
-def load_checkpoint(trainer, path: str) -> None:
-    ck = resolve(path)
+def _candidates(path: str) -> list[Path]:
+    """The checkpoint ``path`` names (or its parent's ``latest``) followed by older complete steps beside it."""
+    first = resolve(path)
+    older = sorted((p for p in first.parent.glob("step_*") if p.is_dir() and (p / "meta.json").exists()
+                    and p.name < first.name), reverse=True)
+    return [first] + older
+
+
+def _agree(ok: bool, device) -> bool:
+    """True only if every rank says ok (one small all-reduce), so all ranks accept or reject a step together."""
+    if not (dist.is_initialized() and dist.get_world_size() > 1):
+        return ok
+    t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
+def load_checkpoint(trainer, path: str, fallback: bool = True) -> str:
+    """Load the newest usable checkpoint under ``path``; returns the directory that was loaded."""
+    cands = _candidates(path)
+    if not fallback:
+        cands = cands[:1]
+    last_err: Exception | None = None
+    for ck in cands:
+        err = None
+        try:
+            _load_one(trainer, ck)
+        except Exception as e:           # every rank must reach the agreement below, whatever went wrong here
+            err = e
+        if _agree(err is None, trainer.device):
+            if ck != cands[0] and trainer.mesh.rank == 0:
+                log.warning("loaded %s instead of %s", ck, cands[0])
+            _barrier()
+            return str(ck)
+        last_err = err or CheckpointCorrupt(f"{ck}: rejected by another rank")
+        if trainer.mesh.rank == 0:
+            log.warning("checkpoint %s is not usable (%s); trying an older one", ck, last_err)
+    raise CheckpointCorrupt(f"no usable checkpoint under {path}: {last_err}")
+
+
+def _load_one(trainer, ck: Path) -> None:
     meta = json.loads((ck / "meta.json").read_text())
     if meta.get("format") != "system_lab_b200.ckpt.v1":
         raise ValueError(f"unknown checkpoint format in {ck}")
@@ -152,14 +212,23 @@ def load_checkpoint(trainer, path: str) -> None:
         raise ValueError("resharding 8-bit optimizer state is not supported; load under the saved layout")
     want = list(_owned_pieces(trainer))
     filled = {id(g): 0 for g, *_ in want}
-    buffers_done = False
+    buffers_needed = {f"{u.name}.{bn}" for u in trainer.engine.units for bn, _ in u.module.named_buffers()}
+    buffers_done = not buffers_needed
     need_total = {id(g): 0 for g, *_ in want}
     for g, _, _, _, length, _ in want:
         need_total[id(g)] += length
     for f in files:
         if all(filled[k] >= need_total[k] for k in filled) and buffers_done:
             break
-        payload = torch.load(f, map_location="cpu", weights_only=False)
+        if not f.exists():
+            raise CheckpointCorrupt(f"{f} is missing")
+        side = f.with_suffix(".sha256")
+        if side.exists() and side.read_text().strip() != _sha256(f):
+            raise CheckpointCorrupt(f"{f} fails its SHA-256 check")
+        try:
+            payload = torch.load(f, map_location="cpu", weights_only=False)
+        except Exception as e:                                   # truncated or damaged pickle
+            raise CheckpointCorrupt(f"{f} cannot be read: {type(e).__name__}: {e}") from e
         by_fqn: dict[str, list] = {}
         for rec in payload["index"]:
             by_fqn.setdefault(rec["fqn"], []).append(rec)
@@ -181,9 +250,10 @@ def load_checkpoint(trainer, path: str) -> None:
             for u in trainer.engine.units:
                 for bn, b in u.module.named_buffers():
                     k = f"{u.name}.{bn}"
-                    if k in payload["buffers"]:
+                    if k in buffers_needed and k in payload["buffers"]:
                         b.copy_(payload["buffers"][k])
-            buffers_done = True
+                        buffers_needed.discard(k)
+            buffers_done = not buffers_needed
         if same_layout and f == own:
             torch.set_rng_state(payload["torch_rng"])
         opt.step_count = payload["opt_step"]
@@ -201,4 +271,3 @@ def load_checkpoint(trainer, path: str) -> None:
     trainer.step = meta["step"]
     trainer.data.cursor = meta["data_cursor"]
     trainer.loss_curve = list(meta.get("loss_curve", []))
-    _barrier()

@@ -127,3 +127,49 @@ def test_interleaved_needs_microbatches_multiple_of_pp():
                                                           "virtual_pipeline_model_parallel_size=2"])
     with pytest.raises(ConfigError, match="multiple of pp"):
         cfg.validate(2)
+
+
+def _ckpt_corruption(rank, world, root, phase):
+    from system_lab_b200.ckpt.sharded import CheckpointCorrupt
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=BASE + [f"expert_model_parallel_size={world}", "device=cpu",
+                                                                f"save={root}", "keep_last=3"])
+    tr = Trainer(cfg)
+    if phase == "write":
+        for _ in range(2):
+            tr.train_step()
+        tr.save_checkpoint(root)
+        w2 = float(torch.cat([g.shard.float().reshape(-1)[:64] for g in tr.engine.all_groups()]).double().sum())
+        for _ in range(2):
+            tr.train_step()
+        tr.save_checkpoint(root)
+        return w2
+    try:
+        tr.load_checkpoint(root)
+    except CheckpointCorrupt as e:
+        return ("corrupt", str(e)[:80])
+    w = float(torch.cat([g.shard.float().reshape(-1)[:64] for g in tr.engine.all_groups()]).double().sum())
+    return (tr.step, w)
+
+
+def test_corrupt_checkpoint_shard_is_detected_and_every_rank_falls_back_together(tmp_path):
+    """Host-side fault: one rank's file of the newest checkpoint is damaged.  Only that rank can see it, yet both
+    ranks must reject the step and load the previous one; with no older checkpoint the load fails with a typed error."""
+    import pathlib
+    root = str(tmp_path / "ck")
+    w2 = run_ranks(_ckpt_corruption, 2, root, "write")
+    newest = pathlib.Path(root) / "step_000004"
+    assert (newest / "rank_00001.sha256").exists()
+    clean = run_ranks(_ckpt_corruption, 2, root, "load")
+    assert [c[0] for c in clean] == [4, 4]
+    victim = newest / "rank_00001.pt"
+    data = bytearray(victim.read_bytes())
+    data[len(data) // 2] ^= 0xFF
+    victim.write_bytes(bytes(data))
+    res = run_ranks(_ckpt_corruption, 2, root, "load")
+    assert [r[0] for r in res] == [2, 2]                              # both ranks fell back to step 2
+    assert res[0][1] == pytest.approx(w2[0], rel=1e-12) and res[1][1] == pytest.approx(w2[1], rel=1e-12)
+    (pathlib.Path(root) / "step_000002" / "rank_00000.pt").write_bytes(b"not a checkpoint")
+    res = run_ranks(_ckpt_corruption, 2, root, "load")
+    assert [r[0] for r in res] == ["corrupt", "corrupt"]
