@@ -427,7 +427,9 @@ class _GroupedLinear(torch.autograd.Function):
         ctx.save_for_backward(a, w, offsets, counts)
         ctx.w_ref = w
         ctx.dgrad_out = dgrad_out
-        return out
+        # a caller-provided buffer may hold more rows than the operand (capacity-sized peer buffer, kept rows):
+        # the result, and therefore the gradient autograd hands back, has exactly the operand's rows
+        return out[:a.shape[0]] if out.shape[0] != a.shape[0] else out
 
     @staticmethod
     def backward(ctx, g):
@@ -479,7 +481,7 @@ class _GroupedLinearFp8(torch.autograd.Function):
         ctx.save_for_backward(a, w, offsets, counts)
         ctx.w_ref = w
         ctx.dgrad_out = dgrad_out
-        return out
+        return out[:a.shape[0]] if out.shape[0] != a.shape[0] else out
 
     @staticmethod
     def backward(ctx, g):

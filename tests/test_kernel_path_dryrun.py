@@ -64,6 +64,8 @@ def _trainer(extra, dispatcher_kw=None):
     (["recompute_granularity=selective"], {"push": True}),
     (["recompute_granularity=selective", "moe_keep_dispatched_factor=-1"], {"push": True, "keep_factor": -1.0}),
     (["recompute_granularity=selective", "moe_keep_dispatched_factor=2"], {"keep_factor": 2.0}),
+    (["recompute_granularity=selective", "moe_keep_dispatched_factor=-1"], {"keep_factor": -1.0}),   # kept rows < capacity, pull combine
+    (["recompute_granularity=selective", "moe_keep_dispatched_factor=0.25"], {"keep_factor": 0.25}),
     (["recompute_granularity=full"], {"push": True}),
     (["recompute_granularity=none"], {"push": True}),
     (["recompute_granularity=selective", "fp8=true", "fp8_recipe=rowwise"], {"push": True}),
@@ -87,7 +89,7 @@ def test_one_step_walks_the_kernel_route(dry, extra, kw):
     gbs = next((int(x.split("=")[1]) for x in extra if x.startswith("global_batch_size=")), 4)
     layers, nmb = 2, gbs // 2                                   # micro-batches of 2 sequences on one rank
     scatters = dry.count("slab_moe_scatter")
-    if "moe_keep_dispatched_factor=-1" in extra or "moe_keep_dispatched_factor=2" in extra:
+    if any(x.startswith("moe_keep_dispatched_factor=") for x in extra):
         assert scatters == layers * nmb * 2                  # forward dispatch + backward of combine; no re-dispatch
     elif "recompute_granularity=none" in extra:
         assert scatters == layers * nmb * 2
