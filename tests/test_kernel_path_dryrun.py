@@ -108,6 +108,12 @@ MLA = ["attention_type=mla", "q_lora_rank=64", "kv_lora_rank=64", "qk_nope_head_
     (["moe_aux_loss_coeff=0.01", "recompute_granularity=selective"], {"push": True}),      # aux loss: falls back to full
     (["moe_router_force_load_balancing=true", "recompute_granularity=selective"], {}),
     (["moe_expert_relocation_interval=1", "moe_expert_relocation_min_gain=0.0", "recompute_granularity=selective"], {}),
+    (MLA + ["recompute_granularity=selective", "moe_keep_dispatched_factor=-1"], {"push": True, "keep_factor": -1.0}),
+    (["recompute_granularity=selective", "moe_keep_dispatched_factor=-1", "fp8=true", "global_batch_size=8"],
+     {"keep_factor": -1.0}),
+    (["recompute_granularity=selective", "optimizer_in_backward=true", "global_batch_size=2",
+      "moe_keep_dispatched_factor=-1"], {"push": True, "keep_factor": -1.0}),
+    (["recompute_granularity=full", "fp8=true", "fp8_recipe=blockwise", "num_layers_at_start_in_bf16=1"], {"push": True}),
 ])
 def test_model_variants_walk_the_kernel_route(dry, extra, kw):
     tr, d = _trainer(extra, kw)
