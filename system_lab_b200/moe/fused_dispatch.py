@@ -248,10 +248,6 @@ class FusedDispatcher:
         self.keep_rows = min(self.capacity, (want + self.pad - 1) // self.pad * self.pad)
         return self.keep_rows
 
-    def note_rows_in_use(self, plan: FusedPlan) -> None:
-        """Fold this plan's row count into the high-water mark the trainer reads between steps."""
-        cops.call("slab_moe_check_rows", plan.meta, 0, self.status, self.rows_seen, cops.stream())
-
     def keep_dispatched(self, plan: FusedPlan, xe: torch.Tensor, pe: torch.Tensor | None):
         """Copies of the received rows and gate probabilities for a later ``redispatch_kept``: exactly the rows in
         use (``keep_exact``) or the first ``keep_rows`` (more rows in use is reported as CAPACITY through the status
