@@ -218,3 +218,22 @@ def test_perf_model_matches_measured_b200_steps():
         "master_weights=false", "optimizer_state_dtype=bf16"])
     ep = estimate_step(pp, 8)
     assert ep.t_bubble > 0 and 0.5 < ep.t_step / 1921.0 < 1.5
+
+
+def test_rules_backend_tunes_with_real_training_jobs(tmp_path):
+    """The whole loop with nothing canned: the rule-based policy decides, the job runner trains the tiny preset on
+    CPU for every plan, snapshots come from the trainer, diagnosis and re-planning from the policy tables."""
+    from system_lab_b200.pilot.agent.__main__ import main
+    rc = main(["--session", "t", "--state-dir", str(tmp_path), "--backend", "rules", "--max-rounds", "1",
+               "--device", "cpu", "--override", "train_iters=4", "--override", "global_batch_size=4"])
+    assert rc == 0
+    sess = tmp_path / "t"
+    arts = sorted(p.name for p in (sess / "artifacts").iterdir())
+    kinds = {a.split("_", 2)[2].split("_")[0] for a in arts}
+    assert {"ClusterProfile", "PlanGraph", "ChampionSnapshot", "DiagnosisReport", "CandidatePool", "Snapshot"} <= kinds
+    champ = json.loads(next((sess / "artifacts").glob("*ChampionSnapshot*")).read_text())
+    assert champ["status"] == "ok" and champ["metrics"]["tps"] > 0 and champ["loss"]["curve"]
+    jobs = sorted((sess / "jobs").iterdir())
+    assert len(jobs) >= 3 and all((j / "stdout.log").exists() for j in jobs)
+    last = json.loads(sorted((sess / "checkpoints").glob("s*.json"))[-1].read_text())
+    assert last["current_stage"] == "REPORT"
