@@ -167,9 +167,10 @@ class RuleWorker:
                               suggested_transition=Transition(to=to or _NEXT.get(stage, Stage.REPORT), reason="policy"),
                               cost={"tokens_used": 0, "gpu_h": gpu_h})
 
-    def _run_plan(self, plan: dict, steps: int, mode: str) -> dict:
+    def _run_plan(self, plan: dict, steps: int, mode: str, overrides=()) -> dict:
         ref = self._save("Plan", f"{plan['id']}.json", plan).ref
-        job = handle_tool_call("submit_run", {"plan_ref": ref, "cluster_id": "local", "max_steps": steps}, self.tools)
+        job = handle_tool_call("submit_run", {"plan_ref": ref, "cluster_id": "local", "max_steps": steps,
+                                              "overrides": list(overrides)}, self.tools)
         handle_tool_call("observe_snapshot", {"job_id": job["job_id"]}, self.tools)
         snap = self.tools.snapshots[job["job_id"]]
         snap["mode"] = mode
@@ -208,7 +209,16 @@ class RuleWorker:
     def _smoke(self, req, wid):
         graph = self._graph()
         plan = graph.nodes["r0_p0"]["plan"]
-        snap = self._run_plan(plan, self.SMOKE_STEPS, "smoke")
+        # same parallel layout, everything else shrunk: at most 4 layers (a multiple of pp x vpp), micro-batch 1,
+        # sequence at most 2048, full recompute
+        cfg = self.tools.plan_config(plan)
+        blocks = max(plan["parallelism"]["pp"] * plan["parallelism"].get("vpp", 1), 1)
+        layers = max(min(cfg.model.num_layers, 4) // blocks * blocks, blocks)
+        dp = plan["parallelism"]["dp"]
+        shrink = [f"num_layers={layers}", f"first_k_dense={min(cfg.model.first_k_dense, layers - 1)}",
+                  "micro_batch_size=1", f"global_batch_size={dp * max(plan['parallelism']['pp'], 1)}",
+                  f"seq_length={min(cfg.model.seq_length, 2048)}", "recompute_granularity=full"]
+        snap = self._run_plan(plan, self.SMOKE_STEPS, "smoke", shrink)
         if snap["status"] != "ok" or snap["metrics"].get("has_nan"):
             return _failed(req.stage, wid, snap.get("failure_kind", "UNKNOWN"), snap.get("log_tail", "")[-300:])
         return self._ok(req.stage, wid, f"smoke ok, {snap['completed_steps']} steps",
@@ -297,10 +307,46 @@ class RuleWorker:
                 r["loss_delta_pct"] = cmp_["delta_pct"]
         art = self._save("ExecuteResults", "results_checked.json", results)
         bad = [r["plan_id"] for r in results if r["status"] == "ok" and not r.get("correctness_ok", True)]
-        return self._ok(req.stage, wid, f"loss gate: {len(bad)} rejected", {"rejected": bad[:4]}, [art])
+        # a communication-bound champion with poor overlap also gets an environment sweep before settling
+        to = Stage.ENV_SWEEP if self._load("DiagnosisReport", {}).get("env_suspect") else None
+        return self._ok(req.stage, wid, f"loss gate: {len(bad)} rejected", {"rejected": bad[:4]}, [art], to=to)
 
     def _env_sweep(self, req, wid):
-        return self._ok(req.stage, wid, "env sweep skipped (no env-suspect signal)", {})
+        """Only when the diagnosis flagged the environment (communication-bound with poor overlap): a handful of
+        one-flag-at-a-time short runs on the champion; a winner joins this round's results as one more challenger."""
+        diag = self._load("DiagnosisReport", {})
+        if not diag.get("env_suspect"):
+            return self._ok(req.stage, wid, "env sweep skipped (no env-suspect signal)", {})
+        from .worker_tools import ENV_CATALOG
+        graph = self._graph()
+        champion = graph.nodes[graph.champion]["plan"]
+        cur = champion.get("env", {}).get("diff", {})
+        cands = {}
+        for flag, spec in ENV_CATALOG.items():
+            if spec["axis"] == "weakly_local" and flag.startswith("NCCL_") and len(cands) < 3:
+                value = next((v for v in spec["values"] if cur.get(flag) != v), None)
+                if value is not None:
+                    cands[flag] = value
+        ref = self._save("Plan", f"{champion['id']}_envbase.json", champion).ref
+        out = handle_tool_call("env_probe_sweep", {"base_plan_ref": ref, "candidate_envs": cands,
+                                                   "max_steps": self.CHALLENGER_STEPS}, self.tools)
+        art = self._save("EnvSweepResult", "envsweep.json", out)
+        best = max((r for r in out["results"] if r["status"] == "ok" and r["tps"]), key=lambda r: r["tps"], default=None)
+        champ_tps = graph.nodes[graph.champion].get("tps") or 0.0
+        arts = [art]
+        if best and best["tps"] > champ_tps * (1 + policy.EPS_PROMOTE):
+            q = json.loads(json.dumps(champion))
+            q["id"] = f"{champion['id']}_env"
+            q["parent"] = champion["id"]
+            q.setdefault("env", {}).setdefault("diff", {})[best["flag"]] = best["value"]
+            graph.add(q, "pending", axis=f"env.{best['flag']}")
+            results = self._load("ExecuteResults", [])
+            results.append({"plan_id": q["id"], "status": "ok", "tps": best["tps"], "curve": [], "failure_kind": None,
+                            "correctness_ok": True})          # an environment flag does not change the arithmetic
+            arts += [self._save("PlanGraph", "graph.json", graph.to_dict()),
+                     self._save("ExecuteResults", "results_env.json", results)]
+        return self._ok(req.stage, wid, f"env sweep: {len(out['results'])} probes, best {out['best_env_diff'] or 'none'}",
+                        {"best": out["best_env_diff"]}, arts)
 
     def _settle(self, req, wid):
         graph, results = self._graph(), self._load("ExecuteResults", [])

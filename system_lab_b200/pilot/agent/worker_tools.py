@@ -55,8 +55,10 @@ ENV_PROBE_SWEEP = _tool("env_probe_sweep", "Inner-loop sweep: structure fixed, e
                         ["base_plan_ref", "candidate_envs"])
 PROFILER_RUN = _tool("profiler_run", "Single-node profiling of micro-configs; returns a ProfilingResult ref.",
                      {"model_spec": _O, "configs": _O}, ["model_spec", "configs"])
-SUBMIT_RUN = _tool("submit_run", "Submit a training job for a plan; returns job_id.",
-                   {"plan_ref": _S, "cluster_id": _S, "max_steps": _I}, ["plan_ref", "cluster_id"])
+SUBMIT_RUN = _tool("submit_run", "Submit a training job for a plan; returns job_id.  `overrides`: extra trainer "
+                   "key=value strings for this job only (a smoke run shrinks the model with them).",
+                   {"plan_ref": _S, "cluster_id": _S, "max_steps": _I, "overrides": {"type": "array", "items": _S}},
+                   ["plan_ref", "cluster_id"])
 OBSERVE_SNAPSHOT = _tool("observe_snapshot", "Collect the job's runtime metrics; returns a Snapshot ref.",
                          {"job_id": _S}, ["job_id"])
 OBSERVE_COMPARE_LOSS = _tool("observe_compare_loss", "Correctness gate: compare a job's loss curve with a reference.",
@@ -156,6 +158,23 @@ class ToolContext:
         return cfg
 
 
+def _clock_state() -> dict | None:
+    """SM clock and throttle reasons of GPU 0 right now (read-only query; None when nvidia-smi is not there)."""
+    import subprocess
+    q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    try:
+        out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=10).stdout.strip().splitlines()[0]
+        f = [x.strip() for x in out.split(",")]
+        reasons = [n for n, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:])
+                   if v.lower() == "active"]
+        return {"sm_mhz": float(f[0]), "sm_max_mhz": float(f[1]), "reasons": reasons,
+                "throttled": any(r != "sw_power_cap" for r in reasons)}
+    except Exception:
+        return None
+
+
 def preflight(cluster_id: str) -> dict:
     """ClusterProfile (``skills/pilot/workflow/preflight.md:72-107``): compute peaks, HBM, intra-node bandwidth.
     Uses the driver-written measured peaks when present; measures a GEMM and a copy when a GPU is visible."""
@@ -183,6 +202,7 @@ def preflight(cluster_id: str) -> dict:
         e1.record()
         torch.cuda.synchronize()
         prof["peak_tflops_bf16_now"] = 10 * 2 * 8192**3 / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        prof["clocks_after_gemm"] = _clock_state()
         src = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
         dst = torch.empty_like(src)
         dst.copy_(src)
@@ -232,7 +252,8 @@ def handle_tool_call(tool_name: str, tool_input: dict[str, Any], ctx) -> Any:
                                                               "logits_bytes")}}
     if tool_name == "submit_run":
         plan = ctx.load_plan(tool_input["plan_ref"])
-        job_id = ctx.runner.submit(plan, int(tool_input.get("max_steps") or 50))
+        job_id = ctx.runner.submit(plan, int(tool_input.get("max_steps") or 50),
+                                   extra_overrides=list(tool_input.get("overrides") or []))
         return {"job_id": job_id}
     if tool_name == "observe_snapshot":
         job_id = tool_input["job_id"]

@@ -29,7 +29,8 @@ class JobRunner:
         self._n = 0
         self.procs: dict[str, subprocess.Popen] = {}
 
-    def submit(self, plan: dict, max_steps: int, *, mode: str = "challenger", timeout_s: float = 1800.0) -> str:
+    def submit(self, plan: dict, max_steps: int, *, mode: str = "challenger", timeout_s: float = 1800.0,
+               extra_overrides=()) -> str:
         self._n += 1
         job_id = f"job_{self._n:04d}_{plan.get('id', 'plan')}"
         d = self.jobs_dir / job_id
@@ -37,8 +38,8 @@ class JobRunner:
         ov, env_diff = policy.plan_to_overrides(plan)
         world = plan["parallelism"]["dp"] * plan["parallelism"]["pp"] * plan["parallelism"].get("cp", 1)
         nproc = min(world, self.nproc) if self.nproc > 1 else 1
-        ov = self.base_overrides + ov + [f"train_iters={max_steps}", f"snapshot_path={d / 'snapshot.json'}",
-                                         f"device={self.device}", "log_interval=1"]
+        ov = self.base_overrides + ov + list(extra_overrides) + [
+            f"train_iters={max_steps}", f"snapshot_path={d / 'snapshot.json'}", f"device={self.device}", "log_interval=1"]
         repo_root = str(Path(__file__).resolve().parents[2])
         if nproc > 1:
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",

@@ -237,3 +237,47 @@ def test_rules_backend_tunes_with_real_training_jobs(tmp_path):
     assert len(jobs) >= 3 and all((j / "stdout.log").exists() for j in jobs)
     last = json.loads(sorted((sess / "checkpoints").glob("s*.json"))[-1].read_text())
     assert last["current_stage"] == "REPORT"
+
+
+def test_env_sweep_runs_only_for_env_suspect_and_can_win(tmp_path):
+    """ENV_SWEEP in the rule-based backend: skipped without the signal; with it, one-flag probes run on the champion
+    and a flag that beats the champion by the promotion margin joins the round's results and the plan graph."""
+    from system_lab_b200.pilot import policy
+    from system_lab_b200.pilot.agent.schemas import SpawnRequest
+    from system_lab_b200.pilot.agent.subagent import RuleWorker
+
+    class FakeRunner:
+        def __init__(self):
+            self.plans = {}
+
+        def submit(self, plan, steps, **kw):
+            job = f"job{len(self.plans)}"
+            self.plans[job] = plan
+            return job
+
+        def wait(self, job):
+            env = self.plans[job].get("env", {}).get("diff", {})
+            return {"status": "ok", "metrics": {"tps": 1200.0 if env.get("NCCL_MIN_NCHANNELS") else 1000.0},
+                    "loss": {"curve": []}}
+
+    cfg = OrchestratorConfig("s", tmp_path, tmp_path / "skills", Budget(gpu_h=1, rounds=1, wallclock_h=1, total_tokens=10),
+                             backend="rules")
+    cfg.ensure_dirs()
+    st = StateStore(tmp_path)
+    runner = FakeRunner()
+    w = RuleWorker(cfg, st, ToolContext(st, runner, "simplemoe-tiny", (), world=1))
+    g = policy.PlanGraph()
+    g.add(policy.default_plan(1), "champion")
+    g.nodes["r0_p0"]["tps"], g.champion = 1000.0, "r0_p0"
+    w._save("PlanGraph", "graph.json", g.to_dict())
+    w._save("ExecuteResults", "r.json", [])
+    req = SpawnRequest(stage=Stage.ENV_SWEEP, input_refs={}, skill_scope=[], max_tokens=10, reason="t")
+    w._save("DiagnosisReport", "d.json", {"env_suspect": False})
+    assert "skipped" in w._env_sweep(req, "w").summary["headline"] and not runner.plans
+    w._save("DiagnosisReport", "d.json", {"env_suspect": True})
+    res = w._env_sweep(req, "w")
+    assert res.status == "success" and len(runner.plans) == 3
+    assert "r0_p0_env" in w._graph().nodes
+    assert w._load("ExecuteResults")[-1]["plan_id"] == "r0_p0_env"
+    dec = policy.settle(w._graph(), w._load("ExecuteResults"))
+    assert dec["promoted"] and dec["champion"] == "r0_p0_env"
