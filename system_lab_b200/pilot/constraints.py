@@ -95,6 +95,12 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
         out.append(_p("router_score_function", f"unknown score function {m.moe_router_score_function!r}"))
     if m.moe_token_dispatcher_type not in ("fused", "alltoall"):
         out.append(_p("dispatcher_type", f"unknown dispatcher {m.moe_token_dispatcher_type!r}"))
+    if m.moe_router_load_balancing_type not in ("aux_loss", "bias", "none"):
+        out.append(_p("load_balancing_type", f"unknown load balancing {m.moe_router_load_balancing_type!r}"))
+    if m.num_experts and m.moe_expert_relocation_interval > 0 and dp is not None and (ep != dp or cp > 1):
+        out.append(_p("expert_relocation_layout", "expert relocation moves whole experts between the ranks of one "
+                      f"expert-parallel group: it needs ep == dp on the stage and cp == 1 (ep={ep}, dp={dp}, cp={cp})",
+                      "set expert_model_parallel_size to dp"))
     if m.num_experts and pr.params_dtype == "bf16" and m.moe_pad_expert_rows_to % 128:
         out.append(_p("expert_rows_alignment", "bf16 models run the tcgen05 grouped GEMM, whose 128-row tiles need "
                       f"moe_pad_expert_rows_to % 128 == 0 (got {m.moe_pad_expert_rows_to})"))
