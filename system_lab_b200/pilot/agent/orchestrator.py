@@ -85,6 +85,12 @@ class Orchestrator:
                 state.current_stage, state.stop_reason = Stage.REPORT, "BUDGET_EXCEEDED"
                 self.store.checkpoint(state)
         log.info("orchestrator terminal: %s (%s)", state.current_stage.value, state.stop_reason)
+        if not self.cfg.dry_run and self.store.latest_artifact("TuningReport") is None:
+            from ..report import write_report
+            try:
+                log.info("report: %s", write_report(self.store, state))
+            except Exception as e:                   # a report must never turn a finished session into a crash
+                log.warning("could not write the tuning report: %s", e)
         return state
 
     def step(self, state: OrchestratorState) -> OrchestratorState:

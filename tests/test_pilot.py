@@ -237,6 +237,11 @@ def test_rules_backend_tunes_with_real_training_jobs(tmp_path):
     assert len(jobs) >= 3 and all((j / "stdout.log").exists() for j in jobs)
     last = json.loads(sorted((sess / "checkpoints").glob("s*.json"))[-1].read_text())
     assert last["current_stage"] == "REPORT"
+    rep = json.loads(next((sess / "artifacts").glob("*TuningReport_report.json")).read_text())
+    assert rep["champion"]["plan_id"] and rep["champion"]["baseline_tps"] > 0 and rep["outcome"]["rounds"] == 1
+    assert "r0" in rep["path"]["rounds"] and rep["reproduce"]["command"]
+    md = next((sess / "artifacts").glob("*TuningReport_report.md")).read_text()
+    assert md.startswith("# Tuning report") and "| round | plan |" in md
 
 
 def test_env_sweep_runs_only_for_env_suspect_and_can_win(tmp_path):
