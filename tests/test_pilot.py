@@ -286,3 +286,31 @@ def test_env_sweep_runs_only_for_env_suspect_and_can_win(tmp_path):
     assert w._load("ExecuteResults")[-1]["plan_id"] == "r0_p0_env"
     dec = policy.settle(w._graph(), w._load("ExecuteResults"))
     assert dec["promoted"] and dec["champion"] == "r0_p0_env"
+
+
+def test_mcp_tool_server_lists_and_calls_tools(tmp_path):
+    """The JSON-RPC tool server: initialize, tools/list (protocol-only tool hidden), a real tools/call, and an error
+    response for an unknown method — one request per line in, one response per line out."""
+    import io
+    from system_lab_b200.pilot.tools.mcp_server import serve
+    st = StateStore(tmp_path)
+    ctx = ToolContext(st, None, "simplemoe-tiny", (), world=1)
+    plan = policy.default_plan(1, mbs=2, gbs=4)
+    ref = st.write_artifact("Plan", "p.json", json.dumps(plan)).ref
+    reqs = [{"jsonrpc": "2.0", "id": 1, "method": "initialize"},
+            {"jsonrpc": "2.0", "method": "notifications/initialized"},
+            {"jsonrpc": "2.0", "id": 2, "method": "tools/list"},
+            {"jsonrpc": "2.0", "id": 3, "method": "tools/call", "params": {"name": "constraint_check",
+                                                                           "arguments": {"plan_ref": ref}}},
+            {"jsonrpc": "2.0", "id": 4, "method": "tools/call", "params": {"name": "constraint_check_env",
+                                                                           "arguments": {"env_diff": {"NCCL_ALGO": "NVLS", "NCCL_NVLS_ENABLE": "0"}}}},
+            {"jsonrpc": "2.0", "id": 5, "method": "nope"}]
+    out = io.StringIO()
+    serve(ctx, stdin=io.StringIO("\n".join(json.dumps(r) for r in reqs) + "\nnot json\n"), stdout=out)
+    resp = [json.loads(l) for l in out.getvalue().splitlines()]
+    assert [r["id"] for r in resp] == [1, 2, 3, 4, 5]                # the notification got no response
+    names = [t["name"] for t in resp[1]["result"]["tools"]]
+    assert "submit_run" in names and "return_subagent_result" not in names and len(names) == len(ALL_TOOLS) - 1
+    assert json.loads(resp[2]["result"]["content"][0]["text"])["valid"] is True
+    assert json.loads(resp[3]["result"]["content"][0]["text"])["valid"] is False
+    assert "error" in resp[4] and "unknown method" in resp[4]["error"]["message"]
