@@ -44,8 +44,7 @@ def main(argv=None) -> int:
             tr.heartbeat.fail(f"{type(e).__name__}: {e}")
         raise
     finally:
-        if tr.heartbeat is not None:
-            tr.heartbeat.stop()
+        tr.close()
     if tr.mesh.rank == 0:
         m = snap["metrics"]
         print(json.dumps({"final_loss": tr.loss_curve[-1] if tr.loss_curve else None, "tps": m["tps"],

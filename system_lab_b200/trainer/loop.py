@@ -109,6 +109,18 @@ class Trainer:
             from .mllog import MLLogger
             self.events = MLLogger(enabled=mesh.rank == 0)
 
+    def close(self) -> None:
+        """Stop background helpers (the heartbeat watchdog thread).  Safe to call more than once."""
+        hb, self.heartbeat = getattr(self, "heartbeat", None), None
+        if hb is not None:
+            hb.stop()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
     # ---- one optimizer step ---------------------------------------------------------------
     def train_step(self, batches=None) -> dict:
         """Runs one full step.  ``batches``: optional list of host ``(tokens, targets)`` micro-batches;
