@@ -121,6 +121,10 @@ class _GroupedLinearRef(torch.autograd.Function):
             if fp8 == "blockwise" and a.shape[1] % 128 == 0 and w.shape[1] % 128 == 0:
                 aq = ref.dequant_1x128(*ref.quant_1x128(a)).to(a.dtype)
                 wq = ref.dequant_128x128(*ref.quant_128x128(w)).to(w.dtype)
+            elif fp8 == "tensorwise":
+                qa, sa = ref.quant_tensorwise(a)
+                qw, sw = ref.quant_tensorwise(w)
+                aq, wq = (qa.float() * sa).to(a.dtype), (qw.float() * sw).to(w.dtype)
             else:
                 qa, sa = ref.quant_rowwise(a)
                 qw, sw = ref.quant_rowwise(w)

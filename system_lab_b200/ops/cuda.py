@@ -474,6 +474,12 @@ class _GroupedLinearFp8(torch.autograd.Function):
             aq, sa = quant_1x128(a)
             wq, sw = quant_128x128(w)
             out = grouped_gemm_fp8_raw(aq, sa.contiguous(), wq, sw.contiguous(), offsets, counts, out=out)
+        elif recipe == "tensorwise":
+            # one scale per tensor: a special case of the row-scaled kernel (all row / channel scales equal)
+            aq, s_a = quant_tensorwise(a)
+            wq, s_w = quant_tensorwise(w)
+            out = grouped_gemm_fp8_rowwise_raw(aq, s_a.expand(a.shape[0]).contiguous(), wq,
+                                               s_w.expand(e, n).contiguous(), offsets, counts, out=out)
         else:
             aq, sa = quant_rowwise(a)
             wq, sw = quant_rowwise(w)
@@ -506,7 +512,7 @@ def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, d
         out = None
     recipe = _fp8_recipe(fp8)
     fp8_ok = recipe and not dead and not hasattr(out, "launch") and \
-        (k % 128 == 0 and n % (128 if recipe == "blockwise" else 64) == 0)
+        (k % 128 == 0 and n % (128 if recipe == "blockwise" else 64) == 0)          # rowwise / tensorwise share a kernel
     if fp8_ok:           # a pushed output stays on the bf16 kernel: the fp8 kernels store through TMA only
         res = _GroupedLinearFp8.apply(a, w, offsets, counts, recipe, out, dgrad_out)
     else:
@@ -577,6 +583,12 @@ def quant_rowwise(x):
     s = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
     call("slab_quant_rowwise", x2, q, s, x2.shape[0], shp[-1], stream())
     return q.reshape(shp), s.reshape(shp[:-1])
+
+
+def quant_tensorwise(x):
+    """e4m3 with a single fp32 scale for the whole tensor (current scaling: the scale comes from this tensor's own
+    absolute maximum, no history).  Library elementwise kernels; the row-scaled recipe is the fused one."""
+    return ref.quant_tensorwise(x)
 
 
 def quant_128x128(w):

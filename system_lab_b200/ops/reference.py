@@ -138,6 +138,14 @@ def quant_rowwise(x: torch.Tensor):
     return q, scale
 
 
+def quant_tensorwise(x: torch.Tensor):
+    """One scale for the whole tensor.  Returns ``(q fp8, scale 0-d fp32)`` with ``x ~= q * scale``."""
+    amax = x.detach().abs().amax().float().clamp_min(1e-12)
+    scale = amax / FP8_MAX
+    q = (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
 def dequant_1x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     *lead, h = q.shape
     return (q.float().reshape(*lead, h // 128, 128) * scale.unsqueeze(-1)).reshape(*lead, h)

@@ -109,7 +109,7 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
         out.append(_p("params_dtype", f"params_dtype={pr.params_dtype!r} not in (fp32, bf16)"))
     if pr.optimizer_state_dtype not in ("fp32", "bf16", "fp8"):
         out.append(_p("optimizer_state_dtype", f"optimizer_state_dtype={pr.optimizer_state_dtype!r}"))
-    if pr.fp8 and pr.fp8_recipe not in ("rowwise", "blockwise"):
+    if pr.fp8 and pr.fp8_recipe not in ("rowwise", "tensorwise", "blockwise"):
         out.append(_p("fp8_recipe", f"fp8_recipe={pr.fp8_recipe!r}"))
     if pr.fp8 and pr.optimizer_state_dtype != "fp32":
         out.append(_p("optim_state_dtype_for_dtype",

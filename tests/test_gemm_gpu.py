@@ -113,7 +113,7 @@ def test_fp8_row_scaled_forward(counts, n, k):
     assert rel < 0.06, rel
 
 
-@pytest.mark.parametrize("recipe", ["rowwise", "blockwise"])
+@pytest.mark.parametrize("recipe", ["rowwise", "tensorwise", "blockwise"])
 def test_autograd_grouped_linear_fp8_forward_bf16_backward(recipe):
     from system_lab_b200 import ops
     from system_lab_b200.ops import reference as ref

@@ -70,6 +70,7 @@ def _trainer(extra, dispatcher_kw=None):
     (["recompute_granularity=none"], {"push": True}),
     (["recompute_granularity=selective", "fp8=true", "fp8_recipe=rowwise"], {"push": True}),
     (["recompute_granularity=selective", "fp8=true", "fp8_recipe=blockwise"], {}),
+    (["recompute_granularity=selective", "fp8=true", "fp8_recipe=tensorwise"], {"push": True}),
     (["recompute_granularity=selective", "optimizer_in_backward=true", "master_weights=false",
       "optimizer_state_dtype=fp8", "global_batch_size=2"], {}),
     (["recompute_granularity=selective", "global_batch_size=8"], {"push": True}),          # four micro-batches

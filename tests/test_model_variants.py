@@ -55,7 +55,7 @@ def test_fp8_expert_forward_tracks_the_unquantised_model():
 
     ref_l, ref_f = run([])
     assert not any(ref_f)
-    for recipe in ("rowwise", "blockwise"):
+    for recipe in ("rowwise", "tensorwise", "blockwise"):
         l, f = run(["fp8=true", f"fp8_recipe={recipe}"])
         assert all(f)
         assert l != ref_l                                       # the forward really is quantised
