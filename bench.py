@@ -166,7 +166,7 @@ def main() -> int:
     plan = choose_memory_plan(cfg, n, args.plan, args.keep_dispatched)
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
-                      cfg.parallel.context_parallel_size)
+                      cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances)
     trainer = Trainer(cfg, mesh=mesh, device=dev)
     from system_lab_b200.ops import cuda as cops
     tokens_per_step = trainer.tokens_per_step

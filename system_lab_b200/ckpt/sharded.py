@@ -78,9 +78,8 @@ def _owned_pieces(trainer):
 
 
 def _is_writer(trainer, g) -> bool:
-    """Unsharded groups are replicated across their data ranks: only the first replica writes."""
-    if g.sharded:
-        return True
+    """Groups replicated across data ranks (unsharded ones, or the blocks of hybrid sharding): only the first
+    replica writes."""
     if g.replica_group is None:
         return True
     return dist.get_rank(g.replica_group) == 0

@@ -99,8 +99,15 @@ class FsdpPeerComm:
 
 def make_fsdp_comms(mesh, device):
     """(dense_comm, expert_comm) for the engine; ``None`` where the group has a single rank."""
-    dense = FsdpPeerComm(mesh.data_group, mesh.data_size, mesh.data_rank, device) if mesh.data_size > 1 else None
+    if mesh.replicas > 1:          # hybrid sharding: the peer collectives span one block of the data axis
+        dense = (FsdpPeerComm(mesh.data_shard_group, mesh.data_shard_size, mesh.data_shard_rank, device)
+                 if mesh.data_shard_size > 1 else None)
+    else:
+        dense = FsdpPeerComm(mesh.data_group, mesh.data_size, mesh.data_rank, device) if mesh.data_size > 1 else None
     expert = None
-    if mesh.edp > 1:
+    if mesh.edp_replicas > 1:
+        if mesh.edp_shard_size > 1:
+            expert = FsdpPeerComm(mesh.edp_shard_group, mesh.edp_shard_size, mesh.edp_shard_rank, device)
+    elif mesh.edp > 1:
         expert = FsdpPeerComm(mesh.edp_group, mesh.edp, mesh.edp_rank * mesh.cp + mesh.cp_rank, device)
     return dense, expert

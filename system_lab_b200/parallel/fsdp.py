@@ -80,7 +80,8 @@ class FlatGroup:
         self.shard: torch.Tensor | None = None
         self.grad_full: torch.Tensor | None = None
         self.grad_shard: torch.Tensor | None = None     # fp32 accumulation over micro-batches
-        self.replica_group = None                       # unsharded data-parallel replicas (plain DDP)
+        self.replica_group = None                       # ranks holding the same shard (plain DDP when unsharded,
+                                                        # the cross-replica axis of hybrid sharding when sharded)
         self.gathered = True
         self.prefetch_comm = None                       # second peer-comm instance used only by prefetch()
         self._pf_event = None                           # set while a prefetched gather is in flight
@@ -118,7 +119,8 @@ class FlatGroup:
         """Reduce-scatter + cast + AdamW in one peer-memory kernel: needs the peer comm, bf16 gradients and an
         fp32 master shard."""
         return (self.sharded and self.comm is not None and self.keep_master and self.grad_full is not None
-                and self.grad_full.dtype == torch.bfloat16 and self.grad_shard is None)
+                and self.grad_full.dtype == torch.bfloat16 and self.grad_shard is None
+                and self.replica_group is None)      # hybrid sharding sums across replicas between the two halves
 
     def take_grad_full(self) -> torch.Tensor:
         """Hand the flat gradient buffer to a fused reduce-scatter+update (nothing is left to reduce)."""
@@ -227,8 +229,8 @@ class FlatGroup:
                 dist.reduce_scatter_tensor(piece, self.grad_full, op=dist.ReduceOp.SUM, group=self.group)
         else:
             piece = self.grad_full
-            if self.replica_group is not None:
-                dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.replica_group)
+        if self.replica_group is not None:
+            dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.replica_group)
         if self.grad_shard is None:
             self.grad_shard = piece                    # consumed as is when there is one micro-batch
         else:
@@ -286,7 +288,14 @@ def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, m
         (expert if getattr(p, "is_expert", False) else dense).append((f"{name}.{n}", p))
     groups = []
     if dense:
-        if fsdp and mesh.data_size > 1:
+        if fsdp and mesh.replicas > 1 and mesh.data_shard_size > 1:
+            # hybrid sharding (``num_distributed_optimizer_instances`` of ``notes/2026-04/2026-04-20_gptoss_14_*``):
+            # shard inside the block, replicate across blocks
+            g = FlatGroup(f"{name}/dense", dense, mesh.data_shard_group, mesh.data_shard_size, mesh.data_shard_rank,
+                          compute_dtype, master_weights, device, dense_comm)
+            g.replica_group = mesh.data_repl_group
+            groups.append(g)
+        elif fsdp and mesh.data_size > 1 and mesh.replicas == 1:
             groups.append(FlatGroup(f"{name}/dense", dense, mesh.data_group, mesh.data_size, mesh.data_rank,
                                     compute_dtype, master_weights, device, dense_comm))
         else:
@@ -294,7 +303,12 @@ def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, m
             g.replica_group = mesh.data_group if mesh.data_size > 1 else None
             groups.append(g)
     if expert:
-        if fsdp and mesh.edp > 1:
+        if fsdp and mesh.edp_replicas > 1 and mesh.edp_shard_size > 1:
+            g = FlatGroup(f"{name}/expert", expert, mesh.edp_shard_group, mesh.edp_shard_size, mesh.edp_shard_rank,
+                          compute_dtype, master_weights, device, expert_comm)
+            g.replica_group = mesh.edp_repl_group
+            groups.append(g)
+        elif fsdp and mesh.edp > 1 and mesh.edp_replicas == 1:
             edp_rank = mesh.edp_rank * mesh.cp + mesh.cp_rank
             groups.append(FlatGroup(f"{name}/expert", expert, mesh.edp_group, mesh.edp, edp_rank,
                                     compute_dtype, master_weights, device, expert_comm))

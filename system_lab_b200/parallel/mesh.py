@@ -48,6 +48,19 @@ class Mesh:
     # (possible with the wrap-around link) never wait on each other within one communicator
     pp_group_up: object = None
     pp_group_down: object = None
+    # hybrid sharding (``replicas`` > 1): parameters are sharded inside a block of ``data_size / replicas``
+    # consecutive data ranks and replicated across the blocks; gradients are reduce-scattered inside the block and
+    # all-reduced across the blocks.  The same split applies to the expert-data axis when it divides.
+    replicas: int = 1
+    data_shard_group: object = None
+    data_shard_size: int = 0
+    data_shard_rank: int = 0
+    data_repl_group: object = None
+    edp_shard_group: object = None
+    edp_shard_size: int = 0
+    edp_shard_rank: int = 0
+    edp_repl_group: object = None
+    edp_replicas: int = 1
 
     @property
     def edp(self) -> int:
@@ -99,7 +112,23 @@ def init_distributed(device: str = "auto", timeout_s: float = 600.0) -> tuple[in
     return rank, world, dev
 
 
-def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1) -> Mesh:
+def _hybrid_split(lists, replicas: int, rank: int):
+    """Split every rank list into ``replicas`` consecutive blocks.  Returns, for this rank, ``(shard_group,
+    shard_size, shard_rank, replica_group)``: its block, and the ranks at its position of every block.  Every rank
+    creates every group, in the same order."""
+    got = (None, 1, 0, None)
+    for ranks in lists:
+        size = len(ranks) // replicas
+        blocks = [ranks[b * size:(b + 1) * size] for b in range(replicas)]
+        shard_groups = [dist.new_group(b) if len(b) > 1 else None for b in blocks]
+        repl_groups = [dist.new_group([b[i] for b in blocks]) for i in range(size)]
+        if rank in ranks:
+            at = ranks.index(rank)
+            got = (shard_groups[at // size], size, at % size, repl_groups[at % size])
+    return got
+
+
+def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1) -> Mesh:
     if not dist.is_initialized():
         if pp * cp != 1:
             raise ValueError("pp/cp > 1 needs an initialised process group")
@@ -146,4 +175,15 @@ def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1) -> Mesh:
     m.pp_group, m.pp_ranks = mk(pp_lists, None)
     m.pp_group_up, _ = mk(pp_lists, None)
     m.pp_group_down, _ = mk(pp_lists, None)
+    if replicas > 1:
+        if (dp * cp) % replicas:
+            raise ValueError(f"data ranks per stage ({dp * cp}) not divisible by {replicas} optimizer instances")
+        m.replicas = replicas
+        m.data_shard_group, m.data_shard_size, m.data_shard_rank, m.data_repl_group = _hybrid_split(
+            data_lists, replicas, rank)
+        edp_total = edp_n * cp
+        if edp_total > 1 and edp_total % replicas == 0:
+            m.edp_replicas = replicas
+            m.edp_shard_group, m.edp_shard_size, m.edp_shard_rank, m.edp_repl_group = _hybrid_split(
+                edp_lists, replicas, rank)
     return m

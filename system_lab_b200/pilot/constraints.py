@@ -44,9 +44,14 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
     if tp > 1:
         out.append(_p("tp_not_implemented", f"tensor_model_parallel_size={tp}: tensor parallelism is a config axis "
                       "only (every measured configuration runs tp=1); shard with ep / fsdp / pp / cp instead"))
-    if p.num_distributed_optimizer_instances > 1:
-        out.append(_p("hsdp_not_implemented", "num_distributed_optimizer_instances > 1 (hybrid sharding across "
-                      "replicas) is out of scope for one NVSwitch box"))
+    inst = p.num_distributed_optimizer_instances
+    if inst > 1:
+        # hybrid sharding: shard inside a block of data ranks, replicate across ``inst`` blocks
+        if not p.fsdp:
+            out.append(_p("hsdp_needs_fsdp", "num_distributed_optimizer_instances > 1 needs fsdp=true"))
+        if dp is not None and (dp * cp) % inst:
+            out.append(_p("hsdp_divides_data_ranks", f"data ranks per stage ({dp * cp}) % instances ({inst}) != 0",
+                          "pick instances from divisors(dp*cp)"))
     # 2. model dims
     if m.num_attention_heads % tp:
         out.append(_p("tp_divides_num_heads", f"num_attention_heads={m.num_attention_heads} % tp={tp} != 0"))
@@ -180,8 +185,12 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     dp = max(world_size // (pp * p.tensor_model_parallel_size * p.context_parallel_size), 1)
     ep = min(p.expert_model_parallel_size, dp)
     edp = max(dp // ep, 1)
-    shard_dense = dp if p.fsdp else 1
-    shard_exp = ep * (edp if p.fsdp else 1)
+    inst = max(p.num_distributed_optimizer_instances, 1)
+    data = dp * p.context_parallel_size
+    shard_dense = max(data // inst, 1) if p.fsdp else 1
+    edp_all = edp * p.context_parallel_size
+    edp_shard = (edp_all // inst if edp_all % inst == 0 else edp_all) if p.fsdp else 1
+    shard_exp = ep * max(edp_shard, 1)
     nmb = max(t.global_batch_size // max(t.micro_batch_size * dp, 1), 1)
     bpp = bytes_per_param(pr, t.optimizer_in_backward, nmb)
     state = (pc["non_expert"] / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp

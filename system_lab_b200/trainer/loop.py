@@ -56,7 +56,7 @@ class Trainer:
             rank, world, device = init_distributed(cfg.train.device, timeout_s=max(cfg.train.hang_timeout_s, 60))
             cfg.validate(world)
             mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
-                              cfg.parallel.context_parallel_size)
+                              cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances)
         self.mesh, self.device = mesh, device or torch.device("cpu")
         mode = cfg.train.use_cuda_kernels
         if mode == "false" or self.device.type != "cuda":

@@ -86,9 +86,9 @@ class ShardedAdamW:
 
     # ---- gradient norm ------------------------------------------------------------
     def _replication(self, g) -> int:
-        if g.sharded or g.replica_group is None:
+        if g.replica_group is None:
             return 1
-        return dist.get_world_size(g.replica_group)
+        return dist.get_world_size(g.replica_group)      # unsharded replicas, or the blocks of hybrid sharding
 
     def _add_sumsq(self, acc: torch.Tensor, g) -> torch.Tensor:
         """acc (1-element fp32 tensor) += sum(grad_shard^2) / replication."""

@@ -173,3 +173,36 @@ def test_corrupt_checkpoint_shard_is_detected_and_every_rank_falls_back_together
     (pathlib.Path(root) / "step_000002" / "rank_00000.pt").write_bytes(b"not a checkpoint")
     res = run_ranks(_ckpt_corruption, 2, root, "load")
     assert [r[0] for r in res] == ["corrupt", "corrupt"]
+
+
+def test_hybrid_sharding_matches_and_checkpoints(single_curve, tmp_path):
+    """Two optimizer instances on four data ranks: parameters sharded over blocks of two ranks, gradients
+    reduce-scattered inside a block and all-reduced across the blocks.  Same curve as one process (clipping on, so
+    the gradient norm must not double-count replicas), and a checkpoint written under it reloads on one rank."""
+    ov = BASE + ["expert_model_parallel_size=2", "num_distributed_optimizer_instances=2", "global_batch_size=8",
+                 "micro_batch_size=1"]
+    ck = str(tmp_path / "ck")
+    res = run_ranks(_train, 4, ov, 3, ck, None, 3)
+    for losses, _ in res:
+        assert losses == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+    resumed = run_ranks(_train, 1, BASE + ["expert_model_parallel_size=1"], 3, None, ck)
+    assert resumed[0][0] == pytest.approx(single_curve[3:], rel=2e-5, abs=2e-5)
+
+
+def _layout(rank, world, overrides):
+    import torch.distributed as dist
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu"]))
+    out = {}
+    for g in tr.engine.all_groups():
+        kind = g.name.rsplit("/", 1)[1]
+        out[kind] = (g.world, dist.get_world_size(g.replica_group) if g.replica_group is not None else 1)
+    return out
+
+
+def test_hybrid_sharding_layout():
+    res = run_ranks(_layout, 4, BASE + ["expert_model_parallel_size=1", "num_distributed_optimizer_instances=2"])
+    assert all(r == {"dense": (2, 2), "expert": (2, 2)} for r in res), res
+    res = run_ranks(_layout, 4, BASE + ["expert_model_parallel_size=2", "num_distributed_optimizer_instances=2"])
+    assert all(r == {"dense": (2, 2), "expert": (1, 2)} for r in res), res
