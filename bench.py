@@ -166,7 +166,8 @@ def main() -> int:
     plan = choose_memory_plan(cfg, n, args.plan, args.keep_dispatched)
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
-                      cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances)
+                      cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances,
+                      cfg.parallel.tensor_model_parallel_size)
     trainer = Trainer(cfg, mesh=mesh, device=dev)
     from system_lab_b200.ops import cuda as cops
     tokens_per_step = trainer.tokens_per_step
@@ -257,7 +258,7 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": m.name, "num_layers": m.num_layers, "hidden": m.hidden_size,
                        "num_experts": m.num_experts, "topk": m.moe_router_topk, "global_batch": cfg.train.global_batch_size,
-                       "seq_len": m.seq_length, "parallelism": f"fsdp+ep{mesh.ep}" + (f"+pp{mesh.pp}" if mesh.pp > 1 else ""),
+                       "seq_len": m.seq_length, "parallelism": f"fsdp+ep{mesh.ep}" + (f"+pp{mesh.pp}" if mesh.pp > 1 else "") + (f"+tp{mesh.tp}" if mesh.tp > 1 else ""),
                        "memory_plan": plan, "recompute": cfg.precision.recompute_granularity,
                        "dispatcher": m.moe_token_dispatcher_type, "kernels": args.kernels,
                        "routing": "forced-balanced" if m.moe_router_force_load_balancing else "learned-router",

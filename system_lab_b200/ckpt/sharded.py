@@ -73,6 +73,9 @@ def _owned_pieces(trainer):
             if a >= b:
                 continue
             is_exp = getattr(p, "is_expert", False)
+            if hasattr(p, "tp_segments"):
+                # a tensor-parallel slice is stored as a tensor of its own, named after its rank in the group
+                fqn = f"{fqn}#tp{mesh.tp_rank}of{mesh.tp}"
             gshape, base = _global_view(g, fqn, shape, mesh.ep_rank, mesh.ep, is_exp)
             yield g, fqn, gshape, base + (a - off), b - a, a - lo
 
@@ -80,6 +83,8 @@ def _owned_pieces(trainer):
 def _is_writer(trainer, g) -> bool:
     """Groups replicated across data ranks (unsharded ones, or the blocks of hybrid sharding): only the first
     replica writes."""
+    if getattr(g, "tp_replicas", 1) > 1 and trainer.mesh.tp_rank != 0:
+        return False                      # dense groups are identical on every tensor-parallel rank
     if g.replica_group is None:
         return True
     return dist.get_rank(g.replica_group) == 0
@@ -122,7 +127,7 @@ def save_checkpoint(trainer, root: str) -> str:
     _barrier()
     if mesh.rank == 0:
         meta = {"format": "system_lab_b200.ckpt.v1", "step": trainer.step, "world": mesh.world,
-                "mesh": {"pp": mesh.pp, "dp": mesh.dp, "cp": mesh.cp, "ep": mesh.ep},
+                "mesh": {"pp": mesh.pp, "dp": mesh.dp, "cp": mesh.cp, "ep": mesh.ep, "tp": mesh.tp},
                 "data_cursor": trainer.data.cursor, "loss_curve": trainer.loss_curve,
                 "optimizer_state_dtype": trainer.cfg.precision.optimizer_state_dtype,
                 "config": trainer.cfg.to_dict()}
@@ -199,9 +204,14 @@ def _load_one(trainer, ck: Path) -> None:
     meta = json.loads((ck / "meta.json").read_text())
     if meta.get("format") != "system_lab_b200.ckpt.v1":
         raise ValueError(f"unknown checkpoint format in {ck}")
+    saved = dict(meta["mesh"])
+    saved.setdefault("tp", 1)
+    if saved["tp"] != trainer.mesh.tp:
+        raise ValueError(f"checkpoint was written with tensor_model_parallel_size={saved['tp']}; tensor-parallel slices "
+                         f"are not re-cut on load (this job runs {trainer.mesh.tp})")
     same_layout = (meta["world"] == trainer.mesh.world and
-                   meta["mesh"] == {"pp": trainer.mesh.pp, "dp": trainer.mesh.dp, "cp": trainer.mesh.cp,
-                                    "ep": trainer.mesh.ep})
+                   saved == {"pp": trainer.mesh.pp, "dp": trainer.mesh.dp, "cp": trainer.mesh.cp,
+                             "ep": trainer.mesh.ep, "tp": trainer.mesh.tp})
     own = ck / f"rank_{trainer.mesh.rank:05d}.pt"
     files = sorted(ck.glob("rank_*.pt"))
     if same_layout:                       # own file first; others only if a replica did not write

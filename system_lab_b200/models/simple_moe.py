@@ -80,17 +80,26 @@ class RMSNorm(nn.Module):
 
 
 class GQAttention(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None, tp=None):
         super().__init__()
-        self.nq, self.nkv, self.d = cfg.num_attention_heads, cfg.num_query_groups, cfg.kv_channels
+        nq, nkv, d = cfg.num_attention_heads, cfg.num_query_groups, cfg.kv_channels
         h = cfg.hidden_size
-        self.wqkv = nn.Parameter(torch.empty((self.nq + 2 * self.nkv) * self.d, h))
-        self.wo = nn.Parameter(torch.empty(h, self.nq * self.d))
+        self.tp = tp
+        t = tp.size if tp is not None else 1
+        self.nq, self.nkv, self.d = nq // t, nkv // t, d            # this rank's heads
+        self.wqkv = nn.Parameter(torch.empty((self.nq + 2 * self.nkv) * d, h))
+        self.wo = nn.Parameter(torch.empty(h, self.nq * d))
+        if tp is not None:
+            from ..parallel.tp import mark_sharded
+            mark_sharded(self.wqkv, 0, ((nq + 2 * nkv) * d, h), tp.segments([nq * d, nkv * d, nkv * d]))
+            mark_sharded(self.wo, 1, (h, nq * d), tp.segments([nq * d]))
         self.window = cfg.sliding_window if (cfg.sliding_window and layer_idx % 2 == 0) else 0
         self.cp_group = cp_group
 
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
+        if self.tp is not None:
+            x = self.tp.copy_to(x)
         qkv = F.linear(x, self.wqkv.to(x.dtype))
         qkv = ops.rope_packed(qkv, cos, sin, self.nq + self.nkv, self.d)      # q and k heads, one pass
         q, k, v = qkv.split([self.nq * self.d, self.nkv * self.d, self.nkv * self.d], dim=-1)
@@ -102,16 +111,19 @@ class GQAttention(nn.Module):
             o = ulysses_attention(q, k, v, self.cp_group, window=self.window)
         else:
             o = ops.causal_attention(q, k, v, None, self.window)
-        return F.linear(o.reshape(b, s, self.nq * self.d), self.wo.to(x.dtype))
+        out = F.linear(o.reshape(b, s, self.nq * self.d), self.wo.to(x.dtype))
+        return self.tp.reduce_from(out) if self.tp is not None else out
 
 
 class MLAttention(nn.Module):
     """Multi-head latent attention (DeepSeek-V3): low-rank q and kv projections, a shared rotary
     key of ``qk_rope_head_dim`` and per-head no-position keys of ``qk_nope_head_dim``."""
 
-    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, cp_group=None, tp=None):
         super().__init__()
-        h, nh = cfg.hidden_size, cfg.num_attention_heads
+        h, nh_all = cfg.hidden_size, cfg.num_attention_heads
+        self.tp = tp
+        nh = nh_all // (tp.size if tp is not None else 1)           # this rank's heads
         self.nh, self.nope, self.rope_d, self.vd = nh, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
         self.q_lora, self.kv_lora = cfg.q_lora_rank, cfg.kv_lora_rank
         qk = self.nope + self.rope_d
@@ -125,21 +137,32 @@ class MLAttention(nn.Module):
         self.kv_norm = RMSNorm(self.kv_lora, cfg.norm_epsilon)
         self.wkv_b = nn.Parameter(torch.empty(nh * (self.nope + self.vd), self.kv_lora))
         self.wo = nn.Parameter(torch.empty(h, nh * self.vd))
+        if tp is not None:
+            # heads are split; the low-rank down projections and their norms stay replicated
+            from ..parallel.tp import mark_sharded
+            qp = self.wq_b if self.q_lora else self.wq
+            mark_sharded(qp, 0, (nh_all * qk, qp.shape[1]), tp.segments([nh_all * qk]))
+            mark_sharded(self.wkv_b, 0, (nh_all * (self.nope + self.vd), self.kv_lora),
+                         tp.segments([nh_all * (self.nope + self.vd)]))
+            mark_sharded(self.wo, 1, (h, nh_all * self.vd), tp.segments([nh_all * self.vd]))
         self.scale = 1.0 / math.sqrt(qk)
         self.cp_group = cp_group
 
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
         dt = x.dtype
+        tp = self.tp
+        link = tp.copy_to if tp is not None else (lambda t: t)     # replicated value feeding this rank's heads
         if self.q_lora:
-            q = F.linear(self.q_norm(F.linear(x, self.wq_a.to(dt))), self.wq_b.to(dt))
+            q = F.linear(link(self.q_norm(F.linear(x, self.wq_a.to(dt)))), self.wq_b.to(dt))
         else:
-            q = F.linear(x, self.wq.to(dt))
+            q = F.linear(link(x), self.wq.to(dt))
         q = q.reshape(b, s, self.nh, self.nope + self.rope_d)
         q_nope, q_rope = q.split([self.nope, self.rope_d], dim=-1)
         kv_a = F.linear(x, self.wkv_a.to(dt))
         c_kv, k_rope = kv_a.split([self.kv_lora, self.rope_d], dim=-1)
-        kv = F.linear(self.kv_norm(c_kv), self.wkv_b.to(dt)).reshape(b, s, self.nh, self.nope + self.vd)
+        k_rope = link(k_rope.contiguous())
+        kv = F.linear(link(self.kv_norm(c_kv)), self.wkv_b.to(dt)).reshape(b, s, self.nh, self.nope + self.vd)
         k_nope, v = kv.split([self.nope, self.vd], dim=-1)
         q_rope = ops.rope(q_rope.contiguous(), cos, sin)
         k_rope = ops.rope(k_rope.reshape(b, s, 1, self.rope_d).contiguous(), cos, sin)
@@ -150,17 +173,27 @@ class MLAttention(nn.Module):
             o = ulysses_attention(qf, kf, v.contiguous(), self.cp_group, scale=self.scale)
         else:
             o = ops.causal_attention(qf, kf, v.contiguous(), self.scale, 0)
-        return F.linear(o.reshape(b, s, self.nh * self.vd), self.wo.to(dt))
+        out = F.linear(o.reshape(b, s, self.nh * self.vd), self.wo.to(dt))
+        return tp.reduce_from(out) if tp is not None else out
 
 
 class DenseFFN(nn.Module):
-    def __init__(self, hidden: int, ffn: int):
+    def __init__(self, hidden: int, ffn: int, tp=None):
         super().__init__()
-        self.w1 = nn.Parameter(torch.empty(2 * ffn, hidden))   # [gate | up]
-        self.w2 = nn.Parameter(torch.empty(hidden, ffn))
+        self.tp = tp
+        f = ffn // (tp.size if tp is not None else 1)          # this rank's columns
+        self.w1 = nn.Parameter(torch.empty(2 * f, hidden))     # [gate | up]
+        self.w2 = nn.Parameter(torch.empty(hidden, f))
+        if tp is not None:
+            from ..parallel.tp import mark_sharded
+            mark_sharded(self.w1, 0, (2 * ffn, hidden), tp.segments([ffn, ffn]))
+            mark_sharded(self.w2, 1, (hidden, ffn), tp.segments([ffn]))
 
     def forward(self, x):
-        return F.linear(ops.swiglu(F.linear(x, self.w1.to(x.dtype))), self.w2.to(x.dtype))
+        if self.tp is not None:
+            x = self.tp.copy_to(x)
+        out = F.linear(ops.swiglu(F.linear(x, self.w1.to(x.dtype))), self.w2.to(x.dtype))
+        return self.tp.reduce_from(out) if self.tp is not None else out
 
 
 class MoEFFN(nn.Module):
@@ -300,19 +333,36 @@ class _Recompute(torch.autograd.Function):
 
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, ep_rank: int, ep_size: int, fp8: bool = False,
-                 cp_group=None):
+                 cp_group=None, tp=None):
         super().__init__()
         self.layer_idx = layer_idx
         self.eps = cfg.norm_epsilon
+        self.tp = tp
         self.attn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
         attn_cls = MLAttention if cfg.attention_type == "mla" else GQAttention
-        self.attn = attn_cls(cfg, layer_idx, cp_group)
+        self.attn = attn_cls(cfg, layer_idx, cp_group, tp) if tp is not None else attn_cls(cfg, layer_idx, cp_group)
         self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
         self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense
-        self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8) if self.is_moe else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size)
+        if self.is_moe:
+            self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8)
+            if tp is not None:
+                # the block sees this rank's slice of the tokens: replicated parameters inside it (router, shared
+                # expert) get partial gradients, summed over the tensor-parallel group by the engine
+                for name, p in self.ffn.named_parameters():
+                    if not getattr(p, "is_expert", False):
+                        p.tp_partial_grad = True
+        else:
+            self.ffn = DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size, tp) if tp is not None \
+                else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size)
         self.recompute_ffn = False        # set by the engine for recompute_granularity=selective
 
     def _ffn_block(self, y, h):
+        if self.tp is not None and self.is_moe:
+            # MoE under tensor parallelism: every rank of the group routes 1 / tp of the shared tokens through the
+            # expert-parallel exchange, then the group reassembles the block's output
+            shp = y.shape
+            out = self.tp.gather_rows(self.ffn(self.tp.scatter_rows(y.reshape(-1, shp[-1]))))
+            return h + out.reshape(shp)
         return h + self.ffn(y)
 
     def forward(self, x, cos, sin):
@@ -358,7 +408,7 @@ class SimpleMoE(nn.Module):
     def __init__(self, cfg: ModelConfig, *, ep_rank: int = 0, ep_size: int = 1, fp8: bool = False,
                  layer_start: int = 0, layer_end: int | None = None, first_stage: bool = True,
                  last_stage: bool = True, cp_group=None, cp_rank: int = 0, cp_size: int = 1,
-                 bf16_first_layers: int = 0, bf16_last_layers: int = 0, layer_ids=None):
+                 bf16_first_layers: int = 0, bf16_last_layers: int = 0, layer_ids=None, tp=None):
         super().__init__()
         self.cfg = cfg
         layer_end = cfg.num_layers if layer_end is None else layer_end
@@ -369,7 +419,7 @@ class SimpleMoE(nn.Module):
         def layer_fp8(i):          # the first / last layers of the whole decoder may be kept out of fp8
             return fp8 if bf16_first_layers <= i < cfg.num_layers - bf16_last_layers else False
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group) for i in ids])
+            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group, tp) for i in ids])
         self.head = Head(cfg) if last_stage else None
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.cp_rank, self.cp_size = cp_rank, cp_size

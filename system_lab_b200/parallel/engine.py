@@ -35,6 +35,12 @@ def init_unit_weights(module: nn.Module, global_prefix: str, std: float, seed: i
             gname = f"{global_prefix}.{name}"
             if p.dim() == 1:
                 p.fill_(1.0)
+            elif hasattr(p, "tp_segments"):
+                # draw the global matrix, keep this tensor-parallel rank's rows / columns
+                from .tp import take_segments
+                full = torch.empty(p.tp_global_shape, dtype=p.dtype if p.is_cuda else torch.float32, device=p.device)
+                seeded_normal_(full, std, seed, gname)
+                p.copy_(take_segments(full, p.tp_dim, p.tp_segments))
             elif getattr(p, "is_expert", False):
                 e_local = p.shape[0]
                 for j in range(e_local):
@@ -125,6 +131,10 @@ class Engine:
                                 for c in range(self.vpp)]
         self.layer_start = self.chunk_layer_ids[0][0]
         self.layer_end = self.chunk_layer_ids[-1][-1] + 1
+        self.tp = None
+        if mesh.tp > 1:
+            from .tp import TensorParallel
+            self.tp = TensorParallel(mesh.tp_group, mesh.tp_rank, mesh.tp)
         with torch.device("meta"):
             self.model = SimpleMoE(
                 m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=(cfg.precision.fp8_recipe if cfg.precision.fp8 else False),
@@ -132,7 +142,7 @@ class Engine:
                 first_stage=mesh.is_first_stage(), last_stage=mesh.is_last_stage(),
                 cp_group=mesh.cp_group if mesh.cp > 1 else None, cp_rank=mesh.cp_rank, cp_size=mesh.cp,
                 bf16_first_layers=cfg.precision.num_layers_at_start_in_bf16,
-                bf16_last_layers=cfg.precision.num_layers_at_end_in_bf16)
+                bf16_last_layers=cfg.precision.num_layers_at_end_in_bf16, tp=self.tp)
         self.units: list[Unit] = []
         self.anchor = torch.zeros(1, device=device, requires_grad=True)
         self._aux_out: list[torch.Tensor] = []
@@ -198,7 +208,7 @@ class Engine:
             if fused:
                 if shared is None:
                     from ..moe.fused_dispatch import FusedDispatcher
-                    tokens = self.cfg.train.micro_batch_size * m.seq_length // self.mesh.cp
+                    tokens = self.cfg.train.micro_batch_size * m.seq_length // (self.mesh.cp * self.mesh.tp)
                     shared = FusedDispatcher(self.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,
@@ -236,6 +246,12 @@ class Engine:
 
     def after_unit_backward(self, unit: Unit) -> None:
         in_bwd = self.optimizer is not None and self.cfg.train.optimizer_in_backward
+        if self.tp is not None:
+            import torch.distributed as dist
+            for p in unit.module.parameters():
+                # replicated parameters inside a MoE block saw only this rank's slice of the tokens
+                if getattr(p, "tp_partial_grad", False) and p.grad is not None:
+                    dist.all_reduce(p.grad, group=self.tp.group)
         for g in unit.groups:
             if not (in_bwd and self.optimizer.fusable(g)):
                 g.reduce_grads()              # fusable groups are reduced inside the optimizer kernel

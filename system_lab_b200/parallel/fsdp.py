@@ -71,7 +71,7 @@ class FlatGroup:
         for i, (p, o, shp) in enumerate(zip(self.params, self.offsets, self.shapes)):
             if p.is_meta:
                 newp = nn.Parameter(self.full[o:o + p.numel()].view(shp), requires_grad=p.requires_grad)
-                for attr in ("is_expert",):
+                for attr in ("is_expert", "tp_dim", "tp_global_shape", "tp_segments", "tp_partial_grad"):
                     if hasattr(p, attr):
                         setattr(newp, attr, getattr(p, attr))
                 self.params[i] = newp
@@ -83,6 +83,7 @@ class FlatGroup:
         self.replica_group = None                       # ranks holding the same shard (plain DDP when unsharded,
                                                         # the cross-replica axis of hybrid sharding when sharded)
         self.gathered = True
+        self.tp_replicas = 1                            # tensor-parallel ranks holding identical copies of this group
         self.prefetch_comm = None                       # second peer-comm instance used only by prefetch()
         self._pf_event = None                           # set while a prefetched gather is in flight
 
@@ -283,10 +284,25 @@ class Unit:
 
 def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, master_weights: bool,
                device: torch.device, fsdp: bool = True, dense_comm=None, expert_comm=None) -> Unit:
-    dense, expert = [], []
+    dense, expert, tp_sharded = [], [], []
     for n, p in module.named_parameters():
-        (expert if getattr(p, "is_expert", False) else dense).append((f"{name}.{n}", p))
+        if getattr(p, "is_expert", False):
+            expert.append((f"{name}.{n}", p))
+        elif hasattr(p, "tp_segments"):
+            tp_sharded.append((f"{name}.{n}", p))
+        else:
+            dense.append((f"{name}.{n}", p))
     groups = []
+    if tp_sharded:
+        # this rank's slice of the head- / column-split matrices: sharded over the data ranks like the dense group,
+        # but distinct on every tensor-parallel rank (the dense group is replicated over them)
+        if fsdp and mesh.data_size > 1:
+            groups.append(FlatGroup(f"{name}/tp", tp_sharded, mesh.data_group, mesh.data_size, mesh.data_rank,
+                                    compute_dtype, master_weights, device, dense_comm))
+        else:
+            g = FlatGroup(f"{name}/tp", tp_sharded, None, 1, 0, compute_dtype, master_weights, device)
+            g.replica_group = mesh.data_group if mesh.data_size > 1 else None
+            groups.append(g)
     if dense:
         if fsdp and mesh.replicas > 1 and mesh.data_shard_size > 1:
             # hybrid sharding (``num_distributed_optimizer_instances`` of ``notes/2026-04/2026-04-20_gptoss_14_*``):
@@ -316,6 +332,10 @@ def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, m
             g = FlatGroup(f"{name}/expert", expert, None, 1, 0, compute_dtype, master_weights, device)
             g.replica_group = mesh.edp_group if mesh.edp > 1 else None
             groups.append(g)
+    if mesh.tp > 1:
+        for g in groups:
+            if g.name.endswith("/dense"):
+                g.tp_replicas = mesh.tp
     # parameters that were on the meta device have been re-created as views: re-register them
     for g in groups:
         for full_name, p in zip(g.names, g.params):

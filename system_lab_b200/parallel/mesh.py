@@ -1,7 +1,10 @@
-"""Device mesh: ``world = pp x dp x cp`` with the expert-parallel group folded into ``dp``.
+"""Device mesh: ``world = pp x dp x cp x tp`` with the expert-parallel group folded into ``dp x tp``.
 
-Rank order (fastest varying last): ``rank = (pp_rank * dp + dp_rank) * cp + cp_rank`` and
-``dp_rank = edp_rank * ep + ep_rank``.  Attention-side parameters are sharded over all ``dp * cp``
+Rank order (fastest varying last): ``rank = ((pp_rank * dp + dp_rank) * cp + cp_rank) * tp + tp_rank``.  The MoE
+blocks see the tensor-parallel ranks as extra data ranks (each takes a slice of the tokens its tensor-parallel group
+shares), so the expert axis runs over ``x = dp_rank * tp + tp_rank``: ``ep_rank = x % ep``, ``edp_rank = x // ep``
+(the attention ``tp x cp x dp`` / MoE ``ep x edp`` folding of ``moe/MegatronCore_MoE_reading_notes.md:159-195``).
+With ``tp == 1`` this is ``dp_rank = edp_rank * ep + ep_rank``.  Attention-side parameters are sharded over all ``dp * cp``
 data ranks of a stage; expert parameters are owned by their ``ep`` rank and sharded over the
 ``edp`` ranks that hold the same experts — the dual dense/expert mesh of
 ``moe/MegatronCore_MoE_reading_notes.md:266-284`` and ``summary/torchtitan/*:98-113``.
@@ -39,6 +42,10 @@ class Mesh:
     cp_group: object = None
     pp_group: object = None
     world_group: object = None
+    tp: int = 1
+    tp_rank: int = 0
+    tp_group: object = None        # ranks that split the heads / feed-forward columns of the same tokens
+    stage_group: object = None     # every rank of this pipeline stage (equals data_group when tp == 1)
     data_ranks: tuple = ()
     ep_ranks: tuple = ()
     edp_ranks: tuple = ()
@@ -64,7 +71,7 @@ class Mesh:
 
     @property
     def edp(self) -> int:
-        return (self.dp // self.ep) * self.cp
+        return (self.dp * self.tp // self.ep) * self.cp
 
     @property
     def data_size(self) -> int:
@@ -128,12 +135,14 @@ def _hybrid_split(lists, replicas: int, rank: int):
     return got
 
 
-def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1) -> Mesh:
+def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1, tp: int = 1) -> Mesh:
     if not dist.is_initialized():
-        if pp * cp != 1:
-            raise ValueError("pp/cp > 1 needs an initialised process group")
+        if pp * cp * tp != 1:
+            raise ValueError("pp/cp/tp > 1 needs an initialised process group")
         return single_process_mesh()
     world, rank = dist.get_world_size(), dist.get_rank()
+    if tp > 1:
+        return _build_mesh_tp(pp, ep, cp, replicas, tp)
     if world % (pp * cp):
         raise ValueError(f"world={world} not divisible by pp*cp={pp * cp}")
     dp = world // (pp * cp)
@@ -175,6 +184,7 @@ def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1) -> Mesh
     m.pp_group, m.pp_ranks = mk(pp_lists, None)
     m.pp_group_up, _ = mk(pp_lists, None)
     m.pp_group_down, _ = mk(pp_lists, None)
+    m.stage_group = m.data_group
     if replicas > 1:
         if (dp * cp) % replicas:
             raise ValueError(f"data ranks per stage ({dp * cp}) not divisible by {replicas} optimizer instances")
@@ -186,4 +196,56 @@ def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1) -> Mesh
             m.edp_replicas = replicas
             m.edp_shard_group, m.edp_shard_size, m.edp_shard_rank, m.edp_repl_group = _hybrid_split(
                 edp_lists, replicas, rank)
+    return m
+
+
+def _build_mesh_tp(pp: int, ep: int, cp: int, replicas: int, tp: int) -> Mesh:
+    """The mesh with a tensor-parallel axis (kept apart so that the ``tp == 1`` construction, and the order in which
+    it creates its communicators, stays exactly as it was)."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if world % (pp * cp * tp):
+        raise ValueError(f"world={world} not divisible by pp*cp*tp={pp * cp * tp}")
+    if replicas > 1:
+        raise ValueError("num_distributed_optimizer_instances > 1 is not combined with tensor parallelism")
+    dp = world // (pp * cp * tp)
+    xs = dp * tp                                  # the MoE blocks' data axis
+    ep = min(ep, xs)
+    if xs % ep:
+        raise ValueError(f"dp*tp={xs} not divisible by ep={ep}")
+    edp_n = xs // ep
+
+    def rid(p, d, c, t):
+        return ((p * dp + d) * cp + c) * tp + t
+
+    def rid_x(p, x, c):
+        return rid(p, x // tp, c, x % tp)
+
+    tp_rank = rank % tp
+    cp_rank = (rank // tp) % cp
+    dp_rank = (rank // (tp * cp)) % dp
+    pp_rank = rank // (tp * cp * dp)
+    x = dp_rank * tp + tp_rank
+    m = Mesh(world=world, rank=rank, pp=pp, dp=dp, cp=cp, ep=ep, pp_rank=pp_rank, dp_rank=dp_rank,
+             cp_rank=cp_rank, ep_rank=x % ep, edp_rank=x // ep, world_group=dist.group.WORLD, tp=tp, tp_rank=tp_rank)
+
+    def mk(all_lists):
+        got, got_ranks = None, ()
+        for ranks in all_lists:
+            g = dist.new_group(ranks) if len(ranks) > 1 else None
+            if rank in ranks:
+                got, got_ranks = g, tuple(ranks)
+        return got, got_ranks
+
+    P, D, C, T, X = range(pp), range(dp), range(cp), range(tp), range(xs)
+    m.data_group, m.data_ranks = mk([[rid(p, d, c, t) for d in D for c in C] for p in P for t in T])
+    m.dp_group, _ = mk([[rid(p, d, c, t) for d in D] for p in P for c in C for t in T])
+    m.ep_group, m.ep_ranks = mk([[rid_x(p, g * ep + e, c) for e in range(ep)] for p in P for g in range(edp_n) for c in C])
+    m.edp_group, m.edp_ranks = mk([[rid_x(p, g * ep + e, c) for g in range(edp_n) for c in C] for p in P for e in range(ep)])
+    m.cp_group, _ = mk([[rid(p, d, c, t) for c in C] for p in P for d in D for t in T])
+    pp_lists = [[rid(p, d, c, t) for p in P] for d in D for c in C for t in T]
+    m.pp_group, m.pp_ranks = mk(pp_lists)
+    m.pp_group_up, _ = mk(pp_lists)
+    m.pp_group_down, _ = mk(pp_lists)
+    m.tp_group, _ = mk([[rid(p, d, c, t) for t in T] for p in P for d in D for c in C])
+    m.stage_group, _ = mk([[rid(p, d, c, t) for d in D for c in C for t in T] for p in P])
     return m

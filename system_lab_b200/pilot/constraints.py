@@ -42,8 +42,15 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
                 out.append(_p("ep_divides_dp_or_world", f"ep={ep} divides neither dp={dp} nor world={world_size}",
                               "pick ep from divisors(dp)"))
     if tp > 1:
-        out.append(_p("tp_not_implemented", f"tensor_model_parallel_size={tp}: tensor parallelism is a config axis "
-                      "only (every measured configuration runs tp=1); shard with ep / fsdp / pp / cp instead"))
+        # heads and dense feed-forward columns split over tp; MoE blocks take 1/tp of the tokens per rank
+        if (t.micro_batch_size * m.seq_length // max(cp, 1)) % tp:
+            out.append(_p("tp_divides_tokens", f"tokens per micro-batch % tp={tp} != 0 (MoE blocks slice the tokens)"))
+        if m.ffn_hidden_size % tp:
+            out.append(_p("tp_divides_ffn", f"ffn_hidden_size={m.ffn_hidden_size} % tp={tp} != 0"))
+        if p.num_distributed_optimizer_instances > 1:
+            out.append(_p("tp_excludes_hsdp", "tensor parallelism is not combined with num_distributed_optimizer_instances > 1"))
+        if m.moe_expert_relocation_interval > 0:
+            out.append(_p("tp_excludes_relocation", "expert relocation needs tp == 1"))
     inst = p.num_distributed_optimizer_instances
     if inst > 1:
         # hybrid sharding: shard inside a block of data ranks, replicate across ``inst`` blocks
@@ -183,8 +190,9 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     pc = param_counts(m)
     pp = p.pipeline_model_parallel_size
     dp = max(world_size // (pp * p.tensor_model_parallel_size * p.context_parallel_size), 1)
-    ep = min(p.expert_model_parallel_size, dp)
-    edp = max(dp // ep, 1)
+    tp = max(p.tensor_model_parallel_size, 1)
+    ep = min(p.expert_model_parallel_size, dp * tp)         # the MoE blocks' data axis runs over dp x tp
+    edp = max(dp * tp // ep, 1)
     inst = max(p.num_distributed_optimizer_instances, 1)
     data = dp * p.context_parallel_size
     shard_dense = max(data // inst, 1) if p.fsdp else 1
@@ -193,7 +201,11 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     shard_exp = ep * max(edp_shard, 1)
     nmb = max(t.global_batch_size // max(t.micro_batch_size * dp, 1), 1)
     bpp = bytes_per_param(pr, t.optimizer_in_backward, nmb)
-    state = (pc["non_expert"] / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
+    # tensor parallelism splits the attention / dense feed-forward matrices (most of the non-expert parameters);
+    # embedding, head, norms and routers stay replicated: count them as unsplit to stay on the safe side
+    emb_head = 2 * m.vocab_size * m.hidden_size
+    non_expert = emb_head + max(pc["non_expert"] - emb_head, 0) / tp
+    state = (non_expert / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
     wbytes = _DTYPE_BYTES[pr.params_dtype]
     # transient: one layer's gathered params (+ its grads when optimizer runs in backward)
     layer_params = pc["per_layer_non_expert"] + pc["per_layer_expert"] / ep
@@ -202,7 +214,7 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     h = m.hidden_size
     act_b = 2 if pr.params_dtype == "bf16" else 4
     layers_here = m.num_layers // pp
-    slots = tokens * m.moe_router_topk
+    slots = tokens * m.moe_router_topk // tp               # each tensor-parallel rank routes its slice of the tokens
     f = m.moe_ffn_hidden_size
     per_layer_full = tokens * h * act_b * 10 + slots * (2 * h + 3 * f) * act_b
     if pr.recompute_granularity == "full":

@@ -56,7 +56,8 @@ class Trainer:
             rank, world, device = init_distributed(cfg.train.device, timeout_s=max(cfg.train.hang_timeout_s, 60))
             cfg.validate(world)
             mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
-                              cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances)
+                              cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances,
+                              cfg.parallel.tensor_model_parallel_size)
         self.mesh, self.device = mesh, device or torch.device("cpu")
         mode = cfg.train.use_cuda_kernels
         if mode == "false" or self.device.type != "cuda":
@@ -93,7 +94,7 @@ class Trainer:
         self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
         if cfg.model.moe_expert_relocation_interval > 0 and cfg.model.num_experts > 0:
             from ..moe.relocation import ExpertRelocator
-            if mesh.edp > 1 or mesh.cp > 1:
+            if mesh.edp > 1 or mesh.cp > 1 or mesh.tp > 1:
                 raise ValueError("moe_expert_relocation_interval needs ep == dp on the stage and cp == 1")
             self.relocator = ExpertRelocator(self.engine, self.optimizer, mesh, cfg.model.moe_expert_relocation_interval,
                                              cfg.model.moe_expert_relocation_min_gain,
@@ -167,7 +168,7 @@ class Trainer:
             if mesh.pp > 1:
                 # only last-stage ranks hold a loss; others contribute zero
                 dist.all_reduce(loss_mean)
-                loss_mean = loss_mean / mesh.data_size
+                loss_mean = loss_mean / (mesh.data_size * mesh.tp)
             else:
                 dist.all_reduce(loss_mean)
                 loss_mean = loss_mean / mesh.world
@@ -199,7 +200,7 @@ class Trainer:
         mean = total / max(count, 1)
         if dist.is_initialized() and mesh.world > 1:
             dist.all_reduce(mean)
-            mean = mean / (mesh.data_size if mesh.pp > 1 else mesh.world)
+            mean = mean / (mesh.data_size * mesh.tp if mesh.pp > 1 else mesh.world)
         return float(mean)
 
     def _eval_batches(self, iters: int, offset: int, total: torch.Tensor):
@@ -233,8 +234,8 @@ class Trainer:
         if len(counts) != len(ffns):
             return
         tpe = torch.stack(counts).float()
-        if dist.is_initialized() and self.mesh.data_size > 1:
-            dist.all_reduce(tpe, group=self.mesh.data_group)
+        if dist.is_initialized() and self.mesh.data_size * self.mesh.tp > 1:
+            dist.all_reduce(tpe, group=self.mesh.stage_group)
         self._tpe_accum = tpe if self._tpe_accum is None else self._tpe_accum + tpe
         # load per expert-parallel rank under the placement that was in force during this step
         e_local = tpe.shape[1] // max(self.mesh.ep, 1)

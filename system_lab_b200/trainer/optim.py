@@ -86,9 +86,10 @@ class ShardedAdamW:
 
     # ---- gradient norm ------------------------------------------------------------
     def _replication(self, g) -> int:
+        tp = getattr(g, "tp_replicas", 1)                # dense groups are replicated over the tensor-parallel ranks
         if g.replica_group is None:
-            return 1
-        return dist.get_world_size(g.replica_group)      # unsharded replicas, or the blocks of hybrid sharding
+            return tp
+        return tp * dist.get_world_size(g.replica_group)  # unsharded replicas, or the blocks of hybrid sharding
 
     def _add_sumsq(self, acc: torch.Tensor, g) -> torch.Tensor:
         """acc (1-element fp32 tensor) += sum(grad_shard^2) / replication."""

@@ -69,3 +69,25 @@ def test_param_counts_and_memory_model():
     assert est["fits"] and 110 < est["total_bytes"] / 2**30 < 135
     ds = Config.load(preset="deepseek-v3-proxy")
     assert param_counts(ds.model)["total"] > 80e9
+
+
+def test_tensor_parallel_and_hybrid_sharding_rules():
+    def rules(ov, world):
+        cfg = Config.load(preset="simplemoe-tiny")
+        cfg.train.micro_batch_size = 1
+        for item in ov:                      # set fields directly: Config.load would refuse an illegal combination
+            k, v = item.split("=")
+            sec = cfg.parallel if hasattr(cfg.parallel, k) else cfg.model
+            setattr(sec, k, {"false": False, "true": True}.get(v, int(v) if v.isdigit() else v))
+        return [p["rule"] for p in check_config(cfg, world) if p["severity"] == "error"]
+    assert rules(["tensor_model_parallel_size=2", "expert_model_parallel_size=2"], 2) == []
+    assert "tp_divides_num_heads" in rules(["tensor_model_parallel_size=8", "expert_model_parallel_size=1"], 8)
+    assert "tp_excludes_hsdp" in rules(["tensor_model_parallel_size=2", "num_distributed_optimizer_instances=2"], 8)
+    assert rules(["num_distributed_optimizer_instances=2", "expert_model_parallel_size=2"], 4) == []
+    assert "hsdp_divides_data_ranks" in rules(["num_distributed_optimizer_instances=3", "expert_model_parallel_size=2"], 4)
+    assert "hsdp_needs_fsdp" in rules(["num_distributed_optimizer_instances=2", "fsdp=false",
+                                       "expert_model_parallel_size=2"], 4)
+    # tensor parallelism shrinks the sharded attention state and the MoE activations of a rank
+    big = Config.load(preset="qwen3-30b-a3b", overrides=["expert_model_parallel_size=8"])
+    tp2 = Config.load(preset="qwen3-30b-a3b", overrides=["expert_model_parallel_size=8", "tensor_model_parallel_size=2"])
+    assert estimate_memory(tp2, 8)["activation_bytes"] < estimate_memory(big, 8)["activation_bytes"]

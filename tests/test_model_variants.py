@@ -62,3 +62,13 @@ def test_fp8_expert_forward_tracks_the_unquantised_model():
         assert max(abs(a - b) for a, b in zip(l, ref_l)) < 2e-2
     _, f = run(["fp8=true", "num_layers_at_start_in_bf16=1", "num_layers_at_end_in_bf16=1"])
     assert f == [False, True, False]
+
+
+def test_dsv3_shape_tensor_parallel_with_context_parallel():
+    """MLA under tensor parallelism: heads split, low-rank down projections replicated; dense first layer
+    column-split; shared expert and router see a token slice (gradients summed over the group)."""
+    (single, _), = run_ranks(_train, 1, DSV3_TINY + ["expert_model_parallel_size=1"], 4)
+    res = run_ranks(_train, 4, DSV3_TINY + ["expert_model_parallel_size=2", "tensor_model_parallel_size=2",
+                                            "context_parallel_size=2"], 4)
+    for losses, _ in res:
+        assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)

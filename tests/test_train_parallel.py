@@ -206,3 +206,23 @@ def test_hybrid_sharding_layout():
     assert all(r == {"dense": (2, 2), "expert": (2, 2)} for r in res), res
     res = run_ranks(_layout, 4, BASE + ["expert_model_parallel_size=2", "num_distributed_optimizer_instances=2"])
     assert all(r == {"dense": (2, 2), "expert": (1, 2)} for r in res), res
+
+
+def test_tensor_parallel_matches(single_curve):
+    """Heads split over two ranks; the MoE block takes half of the tokens on each and exchanges them over an
+    expert-parallel group that spans the tensor-parallel ranks."""
+    res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2", "tensor_model_parallel_size=2"], 6)
+    for losses, _ in res:
+        assert losses == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+
+
+def test_tensor_parallel_with_data_parallel_selective_and_resume(single_curve, tmp_path):
+    ov = BASE + ["expert_model_parallel_size=4", "tensor_model_parallel_size=2", "recompute_granularity=selective"]
+    ck = str(tmp_path / "ck")
+    full = run_ranks(_train, 4, ov, 3, ck, None, 3)
+    assert full[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+    resumed = run_ranks(_train, 4, ov, 3, None, ck)
+    assert resumed[0][0] == full[0][0][3:]
+    assert [r[1] for r in resumed] == [r[1] for r in full]
+    with pytest.raises(Exception, match="tensor_model_parallel_size"):
+        run_ranks(_train, 1, BASE + ["expert_model_parallel_size=1"], 1, None, ck)
