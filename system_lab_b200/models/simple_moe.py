@@ -223,6 +223,7 @@ class MoEFFN(nn.Module):
         self.dispatcher = None            # set by the engine (needs the process group)
         self.keep_dispatched = False      # set by the engine: a recomputed block reuses the rows of its first run
         self.aux = None                   # last aux loss (added to the objective by the trainer)
+        self.aux_scale = 1.0
         self.last_tokens_per_expert = None
         self.step_tokens_per_expert = None   # summed over the micro-batches of the current step
 
@@ -243,7 +244,8 @@ class MoEFFN(nn.Module):
             if scores is None:          # the fused router kernel returns only the selection and its weights
                 scores = torch.softmax(logits, -1) if cfg.moe_router_score_function == "softmax" \
                     else torch.sigmoid(logits)
-            self.aux = ref.aux_loss(scores, idx.long(), cfg.num_experts, cfg.moe_aux_loss_coeff)
+            # aux_scale: 1 / tp when the block sees a tensor-parallel slice of the tokens (the slices' terms add up)
+            self.aux = ref.aux_loss(scores, idx.long(), cfg.num_experts, cfg.moe_aux_loss_coeff * self.aux_scale)
         d = self.dispatcher
         kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
         reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
@@ -348,6 +350,7 @@ class DecoderLayer(nn.Module):
             if tp is not None:
                 # the block sees this rank's slice of the tokens: replicated parameters inside it (router, shared
                 # expert) get partial gradients, summed over the tensor-parallel group by the engine
+                self.ffn.aux_scale = 1.0 / tp.size
                 for name, p in self.ffn.named_parameters():
                     if not getattr(p, "is_expert", False):
                         p.tp_partial_grad = True
