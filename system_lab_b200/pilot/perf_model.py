@@ -28,6 +28,8 @@ RATES = {
     "combine_eff": 0.80,
     "fsdp_eff": 0.20,                  # peer all-gather / reduce-scatter of ~40 MB layers (latency and flag waits dominate)
     "launch_gap_ms_per_layer": 0.25,   # residual host / launch gaps per layer per pass
+    "tp_allreduce_eff": 0.55,          # NCCL all-reduce / all-gather of a micro-batch's activations (tens of MB): share of
+                                       # the 725 GB/s bus bandwidth of a 1 GiB all-reduce; not measured under tp yet
 }
 
 
@@ -45,6 +47,7 @@ class StepEstimate:
     t_step: float
     tokens_per_step: int
     tps: float
+    t_tp_comm: float = 0.0
 
     def to_dict(self) -> dict:
         return asdict(self)
@@ -58,8 +61,9 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
     m, p, pr, t = cfg.model, cfg.parallel, cfg.precision, cfg.train
     pp = max(p.pipeline_model_parallel_size, 1)
     cp = max(p.context_parallel_size, 1)
-    dp = max(world // (pp * cp), 1)
-    ep = max(min(p.expert_model_parallel_size, dp), 1)
+    tp = max(p.tensor_model_parallel_size, 1)
+    dp = max(world // (pp * cp * tp), 1)
+    ep = max(min(p.expert_model_parallel_size, dp * tp), 1)     # the MoE blocks' data axis runs over dp x tp
     nmb = max(t.global_batch_size // max(t.micro_batch_size * dp, 1), 1)
     tokens = t.micro_batch_size * m.seq_length // cp           # per micro-batch per rank
     layers = m.num_layers // pp
@@ -72,12 +76,12 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
     attn_fwd = 1.0 + (1.0 if gran == "full" else 0.0)
 
     # ---- compute -------------------------------------------------------------------------------------------------
-    slots = tokens * k                                         # rows per rank at balanced load (EP keeps it constant)
+    slots = tokens * k // tp                                   # rows per rank at balanced load (EP keeps it constant)
     expert_fwd = 2.0 * slots * 3 * h * f                       # fc1 (2f x h) + fc2 (h x f)
     expert_flops = expert_fwd * (ffn_fwd + 2.0) * moe_layers
     shared_f = m.moe_shared_expert_intermediate_size
-    dense_ffn_fwd = 2.0 * tokens * 3 * h * m.ffn_hidden_size
-    shared_fwd = 2.0 * tokens * 3 * h * shared_f
+    dense_ffn_fwd = 2.0 * tokens * 3 * h * m.ffn_hidden_size / tp
+    shared_fwd = 2.0 * tokens * 3 * h * shared_f / tp
     if m.attention_type == "mla":
         qk, vd = m.qk_nope_head_dim + m.qk_rope_head_dim, m.v_head_dim
         proj = h * m.q_lora_rank + m.q_lora_rank * m.num_attention_heads * qk + h * (m.kv_lora_rank + m.qk_rope_head_dim) \
@@ -85,12 +89,12 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
     else:
         qk = vd = m.kv_channels
         proj = h * (m.num_attention_heads + 2 * m.num_query_groups) * m.kv_channels + m.num_attention_heads * m.kv_channels * h
-    proj_fwd = 2.0 * tokens * proj
+    proj_fwd = 2.0 * tokens * proj / tp                        # heads split (the replicated low-rank parts are small)
     head_flops = 3.0 * 2.0 * tokens * h * m.vocab_size
     dense_flops = (proj_fwd * (attn_fwd + 2.0)) * layers + (shared_fwd * (ffn_fwd + 2.0)) * moe_layers \
         + (dense_ffn_fwd * (ffn_fwd + 2.0)) * dense_layers + head_flops / pp
     attn_fwd_flops = 2.0 * tokens * m.seq_length * m.num_attention_heads * (qk + vd) / 2.0      # causal
-    attn_flops = attn_fwd_flops * (attn_fwd + 2.5) * layers
+    attn_flops = attn_fwd_flops * (attn_fwd + 2.5) * layers / tp
     act_b = 2
     ew_bytes = layers * tokens * h * act_b * 30 + moe_layers * slots * f * act_b * 10 * (ffn_fwd + 1.0) / 2.0
     t_expert = expert_flops / (r["expert_gemm_tflops"] * 1e9)
@@ -100,7 +104,8 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
 
     # ---- optimizer (once per step) -----------------------------------------------------------------------------------
     pc = param_counts(m)
-    shard = (pc["non_expert"] / pp / (dp if p.fsdp else 1)) + (pc["experts"] / pp / ep / (max(dp // ep, 1) if p.fsdp else 1))
+    shard = (pc["non_expert"] / pp / (dp if p.fsdp else 1)) + \
+        (pc["experts"] / pp / ep / (max(dp * tp // ep, 1) if p.fsdp else 1))
     wb = 2 if pr.params_dtype == "bf16" else 4
     state_b = {"fp32": 8, "bf16": 4, "fp8": 2}[pr.optimizer_state_dtype]
     master_b = 4 if (wb == 2 and pr.master_weights) else 0
@@ -125,21 +130,27 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
         layer_dense = pc["per_layer_non_expert"] * wb
         gathers = 2.0                                           # forward and backward re-gather
         t_fsdp = layers * layer_dense * (dp - 1) / dp * (gathers + 1.0) / (r["fsdp_eff"] * r["link_gbs"]) / 1e6
-        edp = max(dp // ep, 1)
+        edp = max(dp * tp // ep, 1)
         if edp > 1:
             layer_exp = pc["per_layer_expert"] / ep * wb
             t_fsdp += moe_layers * layer_exp * (edp - 1) / edp * 3.0 / (r["fsdp_eff"] * r["link_gbs"]) / 1e6
     # the most loaded rank of every layer: its share of expert compute and of the ingress traffic
     t_imb = (rank_load_ratio - 1.0) * (t_expert + t_disp) if ep > 1 else 0.0
 
-    per_mb = t_expert + t_dense + t_attn + t_ew + t_disp + t_fsdp + t_imb
+    # tensor parallelism: per layer and pass one all-reduce behind attention and one all-reduce (dense FFN) or
+    # all-gather (MoE block) behind the feed-forward block, each over the micro-batch's activations; nothing hides them
+    t_tp = 0.0
+    if tp > 1:
+        one = tokens * h * act_b * 2.0 * (tp - 1) / tp / (r["tp_allreduce_eff"] * 725.0) / 1e6
+        t_tp = layers * one * ((attn_fwd + 1.0) + (ffn_fwd + 1.0))
+    per_mb = t_expert + t_dense + t_attn + t_ew + t_disp + t_fsdp + t_imb + t_tp
     bubble = (pp - 1) / max(pp - 1 + nmb * max(p.virtual_pipeline_model_parallel_size, 1), 1)
     t_busy = per_mb * nmb
     t_bubble = t_busy * bubble / max(1.0 - bubble, 1e-9) if pp > 1 else 0.0
     t_step = t_busy + t_bubble + t_opt
     tokens_per_step = t.global_batch_size * m.seq_length
     return StepEstimate(t_expert * nmb, t_dense * nmb, t_attn * nmb, t_ew * nmb, t_opt, t_disp * nmb, t_fsdp * nmb,
-                        t_imb * nmb, t_bubble, t_step, tokens_per_step, tokens_per_step / (t_step / 1e3))
+                        t_imb * nmb, t_bubble, t_step, tokens_per_step, tokens_per_step / (t_step / 1e3), t_tp * nmb)
 
 
 def expected_tps(cfg: Any, world: int, **kw) -> float:

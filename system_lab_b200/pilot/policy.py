@@ -45,6 +45,8 @@ LEVERS: dict[str, list[dict]] = {
         {"axis": "runtime.mbs", "op": "halve", "gain": -5.0, "mem": -0.3},
         {"axis": "parallelism.ep", "op": "double", "gain": -2.0, "mem": -0.3},
         {"axis": "runtime.optimizer_in_backward", "op": "set", "values": [True], "gain": 0.0, "mem": -0.15},
+        {"axis": "parallelism.tp", "op": "double", "gain": -8.0, "mem": -0.3,
+         "note": "last resort: splits attention activations and the MoE rows of a rank; two exposed collectives per layer"},
     ],
     "COMM": [
         {"axis": "comm.dispatcher", "op": "set", "values": ["fused"], "gain": 15.0},
@@ -176,6 +178,12 @@ def _apply(plan: dict, lever: dict, value: Any) -> dict | None:
     if new == cur:
         return None
     q[sec][key] = new
+    if lever["axis"] == "parallelism.tp":
+        # the world size is fixed: a wider tensor-parallel group takes its ranks from the data axis
+        dp = q["parallelism"]["dp"] * cur
+        if dp % new:
+            return None
+        q["parallelism"]["dp"] = dp // new
     if lever["axis"] == "runtime.mbs":
         dp = q["parallelism"]["dp"]
         if q["runtime"]["gbs"] % (new * dp):

@@ -12,6 +12,8 @@ tokens/s/GPU, lm loss, grad norm, NaN/skipped iterations, device memory.
 """
 from __future__ import annotations
 
+import os
+
 import json
 import logging
 import time
@@ -100,7 +102,9 @@ class Trainer:
                                              cfg.model.moe_expert_relocation_min_gain,
                                              cfg.model.moe_expert_relocation_first_step)
         from .watchdog import FaultPlan, Heartbeat
-        self.faults = FaultPlan.parse(t.fault_injection)
+        # a job restarted by the supervisor (launch.py) does not repeat the injected failure
+        restarted = int(os.environ.get("SLAB_RESTART_COUNT", "0") or 0) > 0
+        self.faults = FaultPlan.parse("" if restarted else t.fault_injection)
         self.heartbeat = None
         if t.heartbeat and dist.is_initialized() and mesh.world > 1:
             store = dist.PrefixStore("slab_heartbeat", dist.distributed_c10d._get_default_store())
