@@ -1,8 +1,9 @@
 """Causal attention on the GPU.
 
-Order of preference: the hand written kernel (``csrc/attention.cu``) when it is built and the shape is
-one it covers; otherwise the library flash attention (the measured baseline: cuDNN / flash-attn,
-64.3 ms per step in the reference's B200 trace, ``docs/b200-vs-mi355x-ep8-gbs16-trace.html:433``).
+Default: the library's fused attention (cuDNN SDPA first, flash-attn for sliding windows, PyTorch SDPA otherwise),
+the same class of kernel the reference's B200 trace ran (64.3 ms per step, ``docs/b200-vs-mi355x-ep8-gbs16-
+trace.html:433``).  The hand-written forward (``csrc/attention.cu``, bound in ``attention_kernel.py``) takes over
+for the shapes it covers once it is switched on (``attention_kernel.set_enabled`` / ``SLAB_ATTENTION_KERNEL=1``).
 """
 from __future__ import annotations
 
