@@ -62,9 +62,10 @@ def register(name: str, sig: str) -> None:
     """Used by other modules (dispatch, attention) to declare their entry points."""
     _SIGS[name] = sig
     if _lib is not None:
-        fn = getattr(_lib, name)
-        fn.argtypes = [_CT[c] for c in sig]
-        fn.restype = ctypes.c_int
+        fn = getattr(_lib, name, None)       # a library built before the entry point existed simply lacks it
+        if fn is not None:
+            fn.argtypes = [_CT[c] for c in sig]
+            fn.restype = ctypes.c_int
 
 
 def _ptr(t):

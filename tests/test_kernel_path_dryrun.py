@@ -123,3 +123,23 @@ def test_model_variants_walk_the_kernel_route(dry, extra, kw):
         assert out["loss"].shape == ()
     assert "slab_grouped_gemm_bf16" in set(dry) and d._pending_push == {}
     tr.evaluate(1)
+
+
+def test_attention_kernel_binding_argument_list(dry, monkeypatch):
+    """The opt-in attention forward: strides of packed qkv slices, argument list against the registered signature,
+    and the autograd wrapper's library backward."""
+    from system_lab_b200.ops import attention_kernel as ak, cuda as cops
+    monkeypatch.setattr(cops, "status_word", lambda dev: torch.zeros(1, dtype=torch.int32))
+    b, s, hq, hkv, d = 2, 256, 4, 2, 64
+    qkv = torch.randn(b, s, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k, v = q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
+    assert ak._row_stride(q) == ak._row_stride(k) == ak._row_stride(v) == (hq + 2 * hkv) * d
+    assert ak._row_stride(q.transpose(1, 2)) is None                  # heads not contiguous: refused
+    assert not ak.shape_ok(q, k, v, 0)                                 # CPU tensors never take the kernel
+    out, lse = ak.forward(q, k, v, 0.125, 128)
+    assert out.shape == (b, s, hq, d) and lse.shape == (b, hq, s) and dry[-1] == "slab_attn_fwd"
+    q2 = q.detach().float().requires_grad_(True)
+    o = ak.attention(q2, k.float(), v.float(), 0.125, 0)              # backward goes through the library attention
+    o.sum().backward()
+    assert q2.grad is not None and q2.grad.shape == q2.shape
