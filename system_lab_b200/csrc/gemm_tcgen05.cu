@@ -89,7 +89,7 @@ __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmPar
   int local = t - prefix[e];
   ti.e = e;
   if (MODE == MODE_WGRAD) {
-    int m_tiles = p.N / BM;                   // output rows = weights' N
+    int m_tiles = (p.N + BM - 1) / BM;        // output rows = weights' N (a partial last tile when N % 128 == 64)
     ti.m_idx = local % m_tiles;
     ti.n_idx = local / m_tiles;
     ti.row0 = p.seg_offsets[e];
@@ -153,7 +153,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int acc = 0;
     for (int e = 0; e < p.E; ++e) {
       prefix[e] = acc;
-      int per = (MODE == MODE_WGRAD) ? (p.N / BM) : ((seg_rows(p, e) + BM - 1) / BM);
+      int per = (MODE == MODE_WGRAD) ? ((p.N + BM - 1) / BM) : ((seg_rows(p, e) + BM - 1) / BM);
       acc += per * n_tiles;
     }
     prefix[p.E] = acc;
@@ -255,11 +255,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int t = blockIdx.x; get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
       const int col0 = ti.n_idx * BN;
       const int tile_row = (MODE == MODE_WGRAD) ? (ti.e * p.N + ti.m_idx * BM) : ti.row0;
-      const bool direct = (MODE == MODE_WGRAD) && p.accumulate;
+      // wgrad tiles that accumulate (beta = 1), or that hang over the end of an expert's N rows (the 2-D output map
+      // cannot clip at an expert boundary), go through guarded global loads / stores instead of the TMA store
+      const bool partial = (MODE == MODE_WGRAD) && (ti.m_idx * BM + BM > p.N);
+      const bool direct = (MODE == MODE_WGRAD) && (p.accumulate || partial);
       __nv_bfloat16* c_row = p.C + (size_t)(tile_row + r_in_tile) * out_cols;
       const bool row_ok = (MODE == MODE_WGRAD) ? (ti.m_idx * BM + r_in_tile < p.N) : (tile_row + r_in_tile < p.R);
       const bool empty = (ti.ksteps == 0);      // expert without rows (wgrad): the gradient is zero
-      if (empty && direct) continue;
+      if (empty && direct && p.accumulate) continue;
       int* org_tile = origin_s + (tile_ctr & 1) * BM;
       if (PUSH) {
         // padding rows of the segment have no owner; the table is double buffered because a warp may start the
@@ -299,9 +302,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]);
                 bf16x8* dst = reinterpret_cast<bf16x8*>(c_row + col);
-                unpack8(*dst, o);
+                if (p.accumulate) {
+                  unpack8(*dst, o);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] += o[i];
+                  for (int i = 0; i < 8; ++i) f[i] += o[i];
+                }
                 *dst = pack8(f);
               }
             }
@@ -473,13 +478,14 @@ static int launch(const void* A, const void* B, const GemmParams& p, int grid, c
 }  // namespace slab
 
 // mode: 0 fwd, 1 dgrad, 2 wgrad.  Shapes: see the header comment.  Requires K % 64 == 0, N % 64 == 0
-// (N % 128 == 0 for wgrad), at most 512 experts.  `status` is a device int the kernel sets on a
+// (wgrad: a last partial row tile is written with guarded stores), at most 512 experts.  `status` is a device int
+// the kernel sets on a
 // bounded-wait timeout (0 = ok).  Returns a CUDA/driver error code (0 = launched).
 extern "C" int slab_grouped_gemm_bf16(int mode, const void* A, const void* B, void* C, const int* seg_offsets,
                                       const int* seg_counts, int E, int R, int N, int K, int accumulate,
                                       int block_n, int max_ctas, int* status, cudaStream_t stream) {
   using namespace slab;
-  if (E > 512 || K % 64 || N % 64 || (mode == MODE_WGRAD && N % 128)) return -100;
+  if (E > 512 || K % 64 || N % 64) return -100;
   GemmParams p{seg_offsets, seg_counts, E, R, N, K, static_cast<__nv_bfloat16*>(C), accumulate, status};
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;

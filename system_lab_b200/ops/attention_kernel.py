@@ -22,7 +22,7 @@ cuda.register("slab_attn_fwd", "ppppp" + "iiiii" + "lll" + "i" + "f" + "p" + "s"
 cuda._STATUS_NAMES.update({20: "ATTN_Q", 21: "ATTN_KV_FULL", 22: "ATTN_KV_EMPTY", 23: "ATTN_S", 24: "ATTN_P",
                            25: "ATTN_PV"})
 
-_ENABLED = [os.environ.get("SLAB_ATTENTION_KERNEL", "0") == "1"]
+_ENABLED = [os.environ.get("SLAB_ATTENTION_KERNEL", "0") == "1" or os.environ.get("SLAB_EXPERIMENTAL") == "1"]
 
 
 def set_enabled(on: bool) -> None:

@@ -1,4 +1,6 @@
 """tcgen05 grouped GEMM (forward, dgrad, wgrad) vs fp32 PyTorch on the same bf16 inputs."""
+import os
+
 import pytest
 import torch
 
@@ -64,6 +66,22 @@ def test_wgrad(counts, n, k, bn):
     acc = out.clone()
     cuda.grouped_gemm_raw(2, dy, a, off, cnt, n, k, out=acc, accumulate=True, block_n=bn)
     _check(acc, 2 * ref.grouped_gemm_wgrad(dy, a, off, cnt).float(), "wgrad accumulate")
+
+
+@pytest.mark.skipif(os.environ.get("SLAB_EXPERIMENTAL") != "1",
+                    reason="partial row tiles of wgrad are an opt-in path: set SLAB_EXPERIMENTAL=1")
+@pytest.mark.parametrize("counts,n,k", [([130, 250], 2880, 192), ([64, 0, 300], 192, 320)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_wgrad_partial_row_tile(counts, n, k, bn):
+    """N % 128 == 64 (hidden 2880): the last 64 rows of every expert's gradient come from a tile that hangs over
+    the expert boundary; it must be written in full and must not touch the next expert's rows."""
+    from system_lab_b200.ops import cuda, reference as ref
+    a, dy, w, off, cnt = _inputs(counts, n, k, 2)
+    out = cuda.grouped_gemm_raw(2, dy, a, off, cnt, n, k, block_n=bn)
+    _check(out, ref.grouped_gemm_wgrad(dy, a, off, cnt), "wgrad partial")
+    acc = out.clone()
+    cuda.grouped_gemm_raw(2, dy, a, off, cnt, n, k, out=acc, accumulate=True, block_n=bn)
+    _check(acc, 2 * ref.grouped_gemm_wgrad(dy, a, off, cnt).float(), "wgrad partial accumulate")
 
 
 def test_autograd_grouped_linear():
