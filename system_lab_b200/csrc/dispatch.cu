@@ -493,7 +493,8 @@ extern "C" int slab_moe_scatter(const void* x, const float* pair_scalar, const f
                                 int T, int K, int H, const long* peer_ptrs, const long* ws_offsets, int world, int me,
                                 int epoch, const int* expert_offsets, const int* expert_counts, int e_local, int pad,
                                 int fp8, int* done_counter, int n_blocks, cudaStream_t st) {
-  if (H % 128 || world > MAX_WORLD) return -100;
+  // bf16 rows move as 16-byte vectors (any H % 8 == 0); the fp8 payload is quantised in 128-column blocks
+  if ((fp8 ? H % 128 : H % 8) || world > MAX_WORLD) return -100;
   PeerTable pt = make_peers(peer_ptrs, world);
   WsLayout ws = make_layout(ws_offsets);
   if (n_blocks <= 0) n_blocks = 148 * 4;

@@ -143,3 +143,13 @@ def test_attention_kernel_binding_argument_list(dry, monkeypatch):
     o = ak.attention(q2, k.float(), v.float(), 0.125, 0)              # backward goes through the library attention
     o.sum().backward()
     assert q2.grad is not None and q2.grad.shape == q2.shape
+
+
+def test_hidden_with_half_a_row_tile_takes_the_kernel_route_when_opted_in(dry, monkeypatch):
+    """hidden % 128 == 64 (the GPT-OSS width 2880 = 22.5 x 128): with the opt-in switch the expert GEMMs stay on the
+    kernel route (wgrad writes its last row tile with guarded stores) and the bf16 scatter takes any H % 8 == 0."""
+    from system_lab_b200.ops import cuda as cops
+    monkeypatch.setattr(cops, "_N_MULTIPLE", 64)
+    tr, d = _trainer(["recompute_granularity=selective", "hidden_size=320", "moe_ffn_hidden_size=192"], {"push": True})
+    tr.train_step()
+    assert dry.count("slab_grouped_gemm_bf16") + dry.count("slab_grouped_gemm_bf16_push") >= 7 * len(tr.engine.moe_ffns())
