@@ -108,7 +108,8 @@ def save_checkpoint(trainer, root: str) -> str:
         key = f"{fqn}@{gstart}"
         rec = {"fqn": fqn, "global_shape": list(gshape), "start": gstart, "len": length, "key": key}
         tensors[f"w/{key}"] = g.shard[soff:soff + length].detach().cpu().clone()
-        for mom_name, mom in (("m", opt.m[g.name]), ("v", opt.v[g.name])):
+        moments = () if getattr(g, "frozen", False) else (("m", opt.m[g.name]), ("v", opt.v[g.name]))
+        for mom_name, mom in moments:
             tensors[f"{mom_name}/{key}"] = mom.data[soff:soff + length].detach().cpu().clone()
             if mom.kind == "fp8":
                 # scales are per 128 elements of the shard; pieces start on 128-element boundaries
@@ -249,7 +250,10 @@ def _load_one(trainer, ck: Path) -> None:
                 src = slice(a - rec["start"], b - rec["start"])
                 dst = slice(soff + (a - gstart), soff + (b - gstart))
                 g.shard[dst].copy_(payload["tensors"][f"w/{rec['key']}"][src])
-                for mom_name, mom in (("m", opt.m[g.name]), ("v", opt.v[g.name])):
+                moments = () if getattr(g, "frozen", False) else (("m", opt.m[g.name]), ("v", opt.v[g.name]))
+                for mom_name, mom in moments:
+                    if f"{mom_name}/{rec['key']}" not in payload["tensors"]:
+                        continue              # written by a job in which this parameter was frozen: state starts at zero
                     mom.data[dst].copy_(payload["tensors"][f"{mom_name}/{rec['key']}"][src])
                     if mom.kind == "fp8":
                         sc = payload["tensors"][f"{mom_name}s/{rec['key']}"]
@@ -270,6 +274,9 @@ def _load_one(trainer, ck: Path) -> None:
     # replicas of unsharded groups did not write: they read the writer's pieces above (same fqn ranges)
     for g in trainer.engine.all_groups():
         need = sum(l for gg, _, _, _, l, _ in want if gg is g)
+        if filled[id(g)] < need and all(".lora_" in n for n in g.names) and filled[id(g)] == 0:
+            log.info("checkpoint %s has no adapters for %s: they keep their initial values", ck, g.name)
+            continue                      # a base-model checkpoint loaded into a LoRA job
         if filled[id(g)] < need:
             raise ValueError(f"checkpoint {ck} does not cover group {g.name}: {filled[id(g)]}/{need} elements")
         if not g.sharded:

@@ -70,6 +70,11 @@ class ModelConfig:
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
     sliding_window: int = 0              # 0 = full causal; >0 on alternate layers (GPT-OSS style)
+    # low-rank adapters (LoRA fine-tuning): > 0 freezes every other parameter and trains rank-r updates of the
+    # attention projections ("attn") or of the attention and dense feed-forward projections ("attn+mlp")
+    lora_rank: int = 0
+    lora_alpha: float = 32.0
+    lora_targets: str = "attn"
     # dense FFN (used by the first `first_k_dense` layers and by non-MoE models)
     ffn_hidden_size: int = 1024
     first_k_dense: int = 0

@@ -38,6 +38,18 @@ PRESETS: dict[str, dict] = {
                           recompute_granularity="full"),
         "train": dict(micro_batch_size=1, global_batch_size=32, lr=3e-4),
     },
+    # Llama-2-70B with LoRA adapters on the attention projections (the MLPerf fine-tuning workload the reference
+    # traced: notes/mlperf-llama/2026-04-29_llama2_70b_lora_baseline_trace_breakdown.md): dense, GQA 64q/8kv x 128,
+    # 80 layers, sequence 8192; the base model is frozen, rank-16 adapters train.
+    "llama2-70b-lora": {
+        "model": dict(name="llama2-70b-lora", num_layers=80, hidden_size=8192, num_attention_heads=64,
+                      num_query_groups=8, kv_channels=128, vocab_size=32000, seq_length=8192, rotary_base=10000.0,
+                      ffn_hidden_size=28672, num_experts=0, first_k_dense=0, lora_rank=16, lora_alpha=32.0,
+                      lora_targets="attn"),
+        "parallel": dict(expert_model_parallel_size=1, fsdp=True),
+        "precision": dict(params_dtype="bf16", recompute_granularity="selective"),
+        "train": dict(micro_batch_size=1, global_batch_size=8, lr=4e-4),
+    },
     # GPT-OSS-20B shape (the reference's measured workload): hd64 GQA 64q/8kv, 32 experts top-4,
     # sliding window 128 on alternate layers, rotary base 150000.
     "gpt-oss-20b": {

@@ -69,6 +69,21 @@ def _balance_table(like: torch.Tensor) -> torch.Tensor:
     return _BALANCE_TABLES[key]
 
 
+class LoRA(nn.Module):
+    """Rank-r update of a frozen projection: ``y += (alpha / r) * (x A^T) B^T`` with ``A ~ N(0, std)`` and ``B = 0``, so
+    the adapted model starts out equal to the base model (the Llama-2-70B LoRA workload of
+    ``notes/mlperf-llama/2026-04-29_llama2_70b_lora_baseline_trace_breakdown.md``)."""
+
+    def __init__(self, out_features: int, in_features: int, rank: int, alpha: float):
+        super().__init__()
+        self.lora_a = nn.Parameter(torch.empty(rank, in_features))
+        self.lora_b = nn.Parameter(torch.empty(out_features, rank))
+        self.scale = alpha / rank
+
+    def forward(self, x):
+        return F.linear(F.linear(x, self.lora_a.to(x.dtype)), self.lora_b.to(x.dtype)) * self.scale
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float):
         super().__init__()
@@ -95,12 +110,20 @@ class GQAttention(nn.Module):
             mark_sharded(self.wo, 1, (h, nq * d), tp.segments([nq * d]))
         self.window = cfg.sliding_window if (cfg.sliding_window and layer_idx % 2 == 0) else 0
         self.cp_group = cp_group
+        self.qkv_lora = self.o_lora = None
+        if cfg.lora_rank > 0:
+            if tp is not None:
+                raise ValueError("LoRA adapters are not combined with tensor parallelism")
+            self.qkv_lora = LoRA(self.wqkv.shape[0], h, cfg.lora_rank, cfg.lora_alpha)
+            self.o_lora = LoRA(h, self.wo.shape[1], cfg.lora_rank, cfg.lora_alpha)
 
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
         if self.tp is not None:
             x = self.tp.copy_to(x)
         qkv = F.linear(x, self.wqkv.to(x.dtype))
+        if self.qkv_lora is not None:
+            qkv = qkv + self.qkv_lora(x)
         qkv = ops.rope_packed(qkv, cos, sin, self.nq + self.nkv, self.d)      # q and k heads, one pass
         q, k, v = qkv.split([self.nq * self.d, self.nkv * self.d, self.nkv * self.d], dim=-1)
         q = q.unflatten(-1, (self.nq, self.d))
@@ -111,7 +134,10 @@ class GQAttention(nn.Module):
             o = ulysses_attention(q, k, v, self.cp_group, window=self.window)
         else:
             o = ops.causal_attention(q, k, v, None, self.window)
-        out = F.linear(o.reshape(b, s, self.nq * self.d), self.wo.to(x.dtype))
+        o2 = o.reshape(b, s, self.nq * self.d)
+        out = F.linear(o2, self.wo.to(x.dtype))
+        if self.o_lora is not None:
+            out = out + self.o_lora(o2)
         return self.tp.reduce_from(out) if self.tp is not None else out
 
 
@@ -178,9 +204,13 @@ class MLAttention(nn.Module):
 
 
 class DenseFFN(nn.Module):
-    def __init__(self, hidden: int, ffn: int, tp=None):
+    def __init__(self, hidden: int, ffn: int, tp=None, lora_rank: int = 0, lora_alpha: float = 32.0):
         super().__init__()
         self.tp = tp
+        self.w1_lora = self.w2_lora = None
+        if lora_rank > 0 and tp is None:
+            self.w1_lora = LoRA(2 * ffn, hidden, lora_rank, lora_alpha)
+            self.w2_lora = LoRA(hidden, ffn, lora_rank, lora_alpha)
         f = ffn // (tp.size if tp is not None else 1)          # this rank's columns
         self.w1 = nn.Parameter(torch.empty(2 * f, hidden))     # [gate | up]
         self.w2 = nn.Parameter(torch.empty(hidden, f))
@@ -192,7 +222,13 @@ class DenseFFN(nn.Module):
     def forward(self, x):
         if self.tp is not None:
             x = self.tp.copy_to(x)
-        out = F.linear(ops.swiglu(F.linear(x, self.w1.to(x.dtype))), self.w2.to(x.dtype))
+        gu = F.linear(x, self.w1.to(x.dtype))
+        if self.w1_lora is not None:
+            gu = gu + self.w1_lora(x)
+        act = ops.swiglu(gu)
+        out = F.linear(act, self.w2.to(x.dtype))
+        if self.w2_lora is not None:
+            out = out + self.w2_lora(act)
         return self.tp.reduce_from(out) if self.tp is not None else out
 
 
@@ -355,8 +391,9 @@ class DecoderLayer(nn.Module):
                     if not getattr(p, "is_expert", False):
                         p.tp_partial_grad = True
         else:
+            mlp_rank = cfg.lora_rank if "mlp" in cfg.lora_targets else 0
             self.ffn = DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size, tp) if tp is not None \
-                else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size)
+                else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size, None, mlp_rank, cfg.lora_alpha)
         self.recompute_ffn = False        # set by the engine for recompute_granularity=selective
 
     def _ffn_block(self, y, h):
@@ -424,6 +461,11 @@ class SimpleMoE(nn.Module):
         self.layers = nn.ModuleList(
             [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group, tp) for i in ids])
         self.head = Head(cfg) if last_stage else None
+        if cfg.lora_rank > 0:
+            if cfg.attention_type != "gqa":
+                raise ValueError("LoRA adapters are implemented for GQA attention")
+            for name, p in self.named_parameters():          # only the adapters train
+                p.requires_grad_(".lora_" in name or name.startswith("lora_"))
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.cp_rank, self.cp_size = cp_rank, cp_size
         self.rope_dim = cfg.qk_rope_head_dim if cfg.attention_type == "mla" else cfg.kv_channels
@@ -446,6 +488,8 @@ class SimpleMoE(nn.Module):
             gname = self._global_name(name)
             if name.endswith("norm.weight") or ".q_norm." in name or ".kv_norm." in name:
                 p.fill_(1.0)
+            elif name.endswith("lora_b"):
+                p.zero_()
             elif getattr(p, "is_expert", False):
                 e_local = p.shape[0]
                 for j in range(e_local):

@@ -545,21 +545,23 @@ class _LinearCE(torch.autograd.Function):
         v = weight.shape[0]
         loss_sum = torch.zeros(1, dtype=torch.float32, device=h.device)
         dh = torch.empty_like(h)
-        dw = torch.zeros_like(weight)
+        need_dw = ctx.needs_input_grad[1]            # a frozen projection (LoRA fine-tuning) needs no weight gradient
+        dw = torch.zeros_like(weight) if need_dw else None
         gscale = 1.0 / n
         for lo in range(0, n, chunk_rows):
             hi = min(lo + chunk_rows, n)
             logits = h[lo:hi] @ weight.t()
             call("slab_ce_fwd_bwd", logits, targets[lo:hi].contiguous(), loss_sum, hi - lo, v, gscale, stream())
             torch.mm(logits, weight, out=dh[lo:hi])
-            dw.addmm_(logits.t(), h[lo:hi])
+            if need_dw:
+                dw.addmm_(logits.t(), h[lo:hi])
         ctx.save_for_backward(dh, dw)
         return (loss_sum / n).squeeze(0)
 
     @staticmethod
     def backward(ctx, g):
         dh, dw = ctx.saved_tensors
-        return dh * g.to(dh.dtype), dw * g.to(dw.dtype), None, None
+        return dh * g.to(dh.dtype), (dw * g.to(dw.dtype) if dw is not None else None), None, None
 
 
 def linear_cross_entropy(h, weight, targets, chunk_rows: int = 4096):

@@ -35,6 +35,8 @@ def init_unit_weights(module: nn.Module, global_prefix: str, std: float, seed: i
             gname = f"{global_prefix}.{name}"
             if p.dim() == 1:
                 p.fill_(1.0)
+            elif name.endswith("lora_b"):
+                p.zero_()                      # adapters start as a zero update
             elif hasattr(p, "tp_segments"):
                 # draw the global matrix, keep this tensor-parallel rank's rows / columns
                 from .tp import take_segments
@@ -102,7 +104,8 @@ class _UnitFn(torch.autograd.Function):
             xin, inner = ctx.xin, ctx.inner
         unit.prepare_grads()
         pairs = [(t, g) for t, g in zip(inner, grads) if g is not None and t.requires_grad]
-        torch.autograd.backward([t for t, _ in pairs], [g for _, g in pairs])
+        if pairs:                              # a unit without trainable parameters or inputs (a frozen embedding)
+            torch.autograd.backward([t for t, _ in pairs], [g for _, g in pairs])
         gx = xin.grad if ctx.x_needs_grad else None
         engine.after_unit_backward(unit)
         unit.release()

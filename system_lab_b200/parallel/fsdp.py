@@ -54,7 +54,10 @@ class FlatGroup:
         self.total = _round_up(max(off, ALIGN), ALIGN * self.world)
         self.shard_numel = self.total // self.world
         self.sharded = self.world > 1
-        self.keep_master = master_weights and compute_dtype != torch.float32
+        # a group of frozen parameters (LoRA fine-tuning: everything but the adapters) keeps only its compute-dtype
+        # shard: no master copy, no gradient buffers, no optimizer state
+        self.frozen = bool(named_params) and not any(p.requires_grad for _, p in named_params)
+        self.keep_master = master_weights and compute_dtype != torch.float32 and not self.frozen
 
         # full buffer (compute dtype); parameters become views into it.  Parameters created on the
         # meta device carry no values yet: the caller initialises the views, then calls finalize().
@@ -189,6 +192,8 @@ class FlatGroup:
                 and all(getattr(p, "is_expert", False) for p in self.params))
 
     def prepare_grads(self) -> None:
+        if self.frozen:
+            return
         fused = self._fused_wgrad()
         if self.grad_full is None:
             alloc = torch.empty if fused else torch.zeros
@@ -284,15 +289,27 @@ class Unit:
 
 def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, master_weights: bool,
                device: torch.device, fsdp: bool = True, dense_comm=None, expert_comm=None) -> Unit:
-    dense, expert, tp_sharded = [], [], []
+    dense, expert, tp_sharded, frozen = [], [], [], []
     for n, p in module.named_parameters():
         if getattr(p, "is_expert", False):
             expert.append((f"{name}.{n}", p))
         elif hasattr(p, "tp_segments"):
             tp_sharded.append((f"{name}.{n}", p))
+        elif not p.requires_grad:
+            frozen.append((f"{name}.{n}", p))
         else:
             dense.append((f"{name}.{n}", p))
     groups = []
+    if frozen:
+        # frozen dense parameters (the base model under LoRA) are sharded like the trainable ones but own no
+        # gradient or optimizer state; keeping them apart lets the trainable group stay a few megabytes
+        if fsdp and mesh.data_size > 1 and mesh.replicas == 1:
+            groups.append(FlatGroup(f"{name}/frozen", frozen, mesh.data_group, mesh.data_size, mesh.data_rank,
+                                    compute_dtype, False, device, dense_comm))
+        else:
+            g = FlatGroup(f"{name}/frozen", frozen, None, 1, 0, compute_dtype, False, device)
+            g.replica_group = mesh.data_group if mesh.data_size > 1 else None
+            groups.append(g)
     if tp_sharded:
         # this rank's slice of the head- / column-split matrices: sharded over the data ranks like the dense group,
         # but distinct on every tensor-parallel rank (the dense group is replicated over them)
@@ -334,7 +351,7 @@ def build_unit(name: str, module: nn.Module, mesh, compute_dtype: torch.dtype, m
             groups.append(g)
     if mesh.tp > 1:
         for g in groups:
-            if g.name.endswith("/dense"):
+            if g.name.endswith("/dense") or g.name.endswith("/frozen"):
                 g.tp_replicas = mesh.tp
     # parameters that were on the meta device have been re-created as views: re-register them
     for g in groups:

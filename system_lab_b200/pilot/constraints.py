@@ -41,6 +41,13 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
             elif dp % ep != 0 and world_size % ep != 0:
                 out.append(_p("ep_divides_dp_or_world", f"ep={ep} divides neither dp={dp} nor world={world_size}",
                               "pick ep from divisors(dp)"))
+    if m.lora_rank > 0:
+        if m.attention_type != "gqa":
+            out.append(_p("lora_needs_gqa", "lora_rank > 0 is implemented for attention_type=gqa"))
+        if tp > 1:
+            out.append(_p("lora_excludes_tp", "LoRA adapters are not combined with tensor parallelism"))
+        if m.lora_targets not in ("attn", "attn+mlp"):
+            out.append(_p("lora_targets", f"lora_targets={m.lora_targets!r}: use 'attn' or 'attn+mlp'"))
     if tp > 1:
         # heads and dense feed-forward columns split over tp; MoE blocks take 1/tp of the tokens per rank
         if (t.micro_batch_size * m.seq_length // max(cp, 1)) % tp:
@@ -163,9 +170,18 @@ def param_counts(m: Any) -> dict:
     non_expert = (attn + norms) * m.num_layers + dense_ffn * n_dense + (router + shared) * n_moe + embed
     experts = expert * m.num_experts * n_moe
     active = non_expert + expert * m.moe_router_topk * n_moe
-    return {"total": non_expert + experts, "non_expert": non_expert, "experts": experts,
+    lora = 0
+    r = getattr(m, "lora_rank", 0)
+    if r > 0:
+        d = m.kv_channels
+        qkv_out = (m.num_attention_heads + 2 * m.num_query_groups) * d
+        lora = m.num_layers * r * (h + qkv_out + m.num_attention_heads * d + h)
+        if "mlp" in getattr(m, "lora_targets", ""):
+            lora += n_dense * r * (h + 2 * m.ffn_hidden_size + m.ffn_hidden_size + h)
+    return {"total": non_expert + experts + lora, "non_expert": non_expert, "experts": experts,
             "active_per_token": active, "per_layer_expert": expert * m.num_experts,
-            "per_layer_non_expert": attn + norms + router + shared}
+            "per_layer_non_expert": attn + norms + router + shared + (dense_ffn if n_moe == 0 else 0),
+            "lora": lora, "trainable": lora if r > 0 else non_expert + experts}
 
 
 def bytes_per_param(pr: Any, optimizer_in_backward: bool = False, microbatches: int = 1) -> float:
@@ -205,7 +221,12 @@ def estimate_memory(cfg: Any, world_size: int) -> dict:
     # embedding, head, norms and routers stay replicated: count them as unsplit to stay on the safe side
     emb_head = 2 * m.vocab_size * m.hidden_size
     non_expert = emb_head + max(pc["non_expert"] - emb_head, 0) / tp
-    state = (non_expert / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
+    if pc["lora"]:
+        # LoRA: the base model is frozen (compute-dtype shard only); adapters carry master, gradient and moments
+        state = (non_expert / pp / shard_dense + pc["experts"] / pp / shard_exp) * _DTYPE_BYTES[pr.params_dtype] \
+            + pc["lora"] / pp / shard_dense * bpp
+    else:
+        state = (non_expert / pp / shard_dense + pc["experts"] / pp / shard_exp) * bpp
     wbytes = _DTYPE_BYTES[pr.params_dtype]
     # transient: one layer's gathered params (+ its grads when optimizer runs in backward)
     layer_params = pc["per_layer_non_expert"] + pc["per_layer_expert"] / ep

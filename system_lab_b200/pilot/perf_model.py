@@ -90,9 +90,12 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
         qk = vd = m.kv_channels
         proj = h * (m.num_attention_heads + 2 * m.num_query_groups) * m.kv_channels + m.num_attention_heads * m.kv_channels * h
     proj_fwd = 2.0 * tokens * proj / tp                        # heads split (the replicated low-rank parts are small)
-    head_flops = 3.0 * 2.0 * tokens * h * m.vocab_size
-    dense_flops = (proj_fwd * (attn_fwd + 2.0)) * layers + (shared_fwd * (ffn_fwd + 2.0)) * moe_layers \
-        + (dense_ffn_fwd * (ffn_fwd + 2.0)) * dense_layers + head_flops / pp
+    # LoRA fine-tuning: the frozen projections need their input gradient but no weight gradient (the rank-r adapter
+    # GEMMs are negligible)
+    bwd = 1.0 if getattr(m, "lora_rank", 0) > 0 else 2.0
+    head_flops = (1.0 + bwd) * 2.0 * tokens * h * m.vocab_size
+    dense_flops = (proj_fwd * (attn_fwd + bwd)) * layers + (shared_fwd * (ffn_fwd + bwd)) * moe_layers \
+        + (dense_ffn_fwd * (ffn_fwd + bwd)) * dense_layers + head_flops / pp
     attn_fwd_flops = 2.0 * tokens * m.seq_length * m.num_attention_heads * (qk + vd) / 2.0      # causal
     attn_flops = attn_fwd_flops * (attn_fwd + 2.5) * layers / tp
     act_b = 2
@@ -109,6 +112,8 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
     wb = 2 if pr.params_dtype == "bf16" else 4
     state_b = {"fp32": 8, "bf16": 4, "fp8": 2}[pr.optimizer_state_dtype]
     master_b = 4 if (wb == 2 and pr.master_weights) else 0
+    if pc.get("lora"):
+        shard = pc["lora"] / pp / (dp if p.fsdp else 1)         # only the adapters are updated
     adam_bytes = shard * (2 * (master_b or wb) + 2 * state_b + 2 + (2 if master_b else 0))
     t_opt = adam_bytes / (r["adamw_tbs"] * 1e9)
     # An update that runs beside backward on a side stream is not free on this part: it shares HBM bandwidth and

@@ -74,6 +74,8 @@ class ShardedAdamW:
         self.m, self.v = {}, {}
         dev = engine.device
         for g in engine.all_groups():
+            if getattr(g, "frozen", False):
+                continue                  # frozen groups (the base model under LoRA) own no optimizer state
             n = g.shard.numel()
             self.m[g.name] = _Moment(n, state_dtype, dev)
             self.v[g.name] = _Moment(n, state_dtype, dev, sqrt_domain=(state_dtype != "fp32"))
