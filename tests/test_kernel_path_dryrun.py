@@ -153,3 +153,18 @@ def test_hidden_with_half_a_row_tile_takes_the_kernel_route_when_opted_in(dry, m
     tr, d = _trainer(["recompute_granularity=selective", "hidden_size=320", "moe_ffn_hidden_size=192"], {"push": True})
     tr.train_step()
     assert dry.count("slab_grouped_gemm_bf16") + dry.count("slab_grouped_gemm_bf16_push") >= 7 * len(tr.engine.moe_ffns())
+
+
+def test_lora_dense_model_on_the_kernel_route(dry):
+    """A dense bf16 model with LoRA adapters: the fused cross entropy skips the frozen head's weight gradient and the
+    optimizer only sees the adapter groups."""
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "params_dtype=bf16", "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=1",
+        "num_experts=0", "ffn_hidden_size=256", "lora_rank=4", "lora_targets=attn+mlp", "device=cpu",
+        "recompute_granularity=selective"])
+    tr = Trainer(cfg)
+    tr.train_step()
+    assert "slab_ce_fwd_bwd" in dry and "slab_adamw" in dry
+    assert dry.count("slab_adamw") == sum(1 for g in tr.engine.all_groups() if not g.frozen)
