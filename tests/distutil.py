@@ -43,10 +43,23 @@ def run_ranks(fn, world: int, *args, timeout: float = 240.0):
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q)) for r in range(world)]
     for p in procs:
         p.start()
+    import queue
+    import time
     results = {}
+    deadline = time.monotonic() + timeout
     try:
-        for _ in range(world):
-            rank, status, payload = q.get(timeout=timeout)
+        while len(results) < world:
+            try:
+                rank, status, payload = q.get(timeout=1.0)
+            except queue.Empty:
+                # a child that died without reporting (a crash in native code) would otherwise cost the whole timeout
+                dead = [(r, p.exitcode) for r, p in enumerate(procs)
+                        if r not in results and p.exitcode not in (None, 0)]
+                if dead:
+                    raise RuntimeError(f"rank(s) died without a result: {dead}")
+                if time.monotonic() > deadline:
+                    raise
+                continue
             if status == "err":
                 raise RuntimeError(f"rank {rank} failed:\n{payload}")
             results[rank] = payload
