@@ -36,24 +36,9 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _save_dir(train_args: list[str]) -> str:
-    """The checkpoint directory the job writes to (``checkpoint.save`` / ``save=`` override), or ''."""
-    for a in train_args:
-        if a.startswith("save=") or a.startswith("checkpoint.save="):
-            return a.split("=", 1)[1]
-    return ""
-
-
-def newest_checkpoint(root: str) -> str:
-    """Newest complete checkpoint under ``root`` (a ``step_*`` directory with its ``meta.json``), or ''."""
-    if not root or not Path(root).is_dir():
-        return ""
-    done = [d for d in sorted(Path(root).glob("step_*")) if (d / "meta.json").exists()]
-    return str(done[-1]) if done else ""
-
-
-def _legal(train_args: list[str], world: int) -> bool:
-    from .config import Config, ConfigError
+def _resolve(train_args: list[str]):
+    """The job's configuration, resolved the way ``train.py`` resolves it (defaults < preset < YAML < overrides)."""
+    from .config import Config
     preset, config, overrides = None, None, []
     it = iter(train_args)
     for a in it:
@@ -65,8 +50,30 @@ def _legal(train_args: list[str], world: int) -> bool:
             next(it)
         elif not a.startswith("--"):
             overrides.append(a)
+    return Config.load(config, overrides, preset)
+
+
+def _save_dir(train_args: list[str]) -> str:
+    """The checkpoint directory the job writes to (``checkpoint.save``, from any configuration layer), or ''."""
+    from .config import ConfigError
     try:
-        Config.load(config, overrides, preset).validate(world)
+        return _resolve(train_args).checkpoint.save
+    except ConfigError:
+        return ""
+
+
+def newest_checkpoint(root: str) -> str:
+    """Newest complete checkpoint under ``root`` (a ``step_*`` directory with its ``meta.json``), or ''."""
+    if not root or not Path(root).is_dir():
+        return ""
+    done = [d for d in sorted(Path(root).glob("step_*")) if (d / "meta.json").exists()]
+    return str(done[-1]) if done else ""
+
+
+def _legal(train_args: list[str], world: int) -> bool:
+    from .config import ConfigError
+    try:
+        _resolve(train_args).validate(world)
         return True
     except ConfigError:
         return False
