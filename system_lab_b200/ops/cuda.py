@@ -10,7 +10,6 @@ import os
 from pathlib import Path
 
 import torch
-import torch.nn.functional as F
 
 from . import reference as ref
 

@@ -27,7 +27,7 @@ from ..config import Config
 from ..parallel.engine import Engine
 from ..parallel.mesh import Mesh, build_mesh, init_distributed
 from ..pilot.constraints import param_counts
-from .data import SyntheticData, make_data
+from .data import make_data
 from .optim import ShardedAdamW, lr_at
 
 log = logging.getLogger("system_lab_b200.train")
