@@ -23,17 +23,17 @@ from collections import defaultdict
 
 # (category, substrings) — first match wins; names are lower-cased first.
 RULES: list[tuple[str, tuple[str, ...]]] = [
-    ("slab_grouped_gemm", ("grouped_gemm_kernel",)),
+    ("slab_grouped_gemm", ("grouped_gemm_kernel", "grouped_gemm_fp8")),
     ("slab_dispatch", ("moe_scatter_kernel", "moe_combine", "moe_count", "moe_publish", "moe_plan", "moe_slots",
-                       "moe_wait", "moe_signal")),
+                       "moe_wait", "moe_signal", "moe_reduce", "moe_check", "moe_gather")),
     ("slab_norm", ("rmsnorm_fwd_kernel", "rmsnorm_bwd_kernel", "colsum_to_bf16")),
     ("slab_act", ("swiglu_fwd_kernel", "swiglu_bwd_kernel", "rope_kernel")),
     ("slab_router", ("router_topk_kernel",)),
     ("slab_ce", ("ce_fwd_bwd_kernel",)),
-    ("slab_quant", ("quant_1x128_kernel", "quant_128x128_kernel")),
+    ("slab_quant", ("quant_1x128_kernel", "quant_128x128_kernel", "quant_rowwise_kernel")),
     ("slab_optimizer", ("adamw_kernel", "sumsq_kernel")),
     ("slab_attn", ("slab_attn", "attn_fwd_kernel", "attn_bwd_kernel")),
-    ("slab_fsdp", ("fsdp_gather_kernel", "fsdp_reduce_scatter_kernel")),
+    ("slab_fsdp", ("fsdp_gather_kernel", "fsdp_reduce_scatter_kernel", "fsdp_stage_kernel", "fsdp_rs_adamw")),
     ("nccl_rs", ()), ("nccl_ar", ()), ("nccl_ag", ()), ("nccl_a2a", ()), ("nccl_bcast", ()), ("nccl_generic", ()),
     ("grouped_gemm", ("_grouped", "groupedgemm", "grouped_gemm", "groupedlinear", "te_grouped")),
     ("attn_kernel", ("fmha", "fmhca", "flash", "scaled_dot_product", "_sdpa_", "_attn_", "attention", "ck_v3")),
