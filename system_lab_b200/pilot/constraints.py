@@ -135,6 +135,24 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
                       "fp8 compute with non-fp32 optimizer state: updates may stall", severity="warning"))
     if pr.recompute_granularity not in ("none", "selective", "full"):
         out.append(_p("recompute_granularity", f"recompute_granularity={pr.recompute_granularity!r}"))
+    # knobs kept for vocabulary compatibility with Megatron-style launch files: a value that asks for behaviour this
+    # trainer does not have is reported instead of being ignored silently
+    if m.tie_embeddings:
+        out.append(_p("tie_embeddings", "tie_embeddings=true is not implemented: embedding and head are separate matrices"))
+    inert = [(m.moe_router_dtype != "fp32", "moe_router_dtype", "the router always runs in fp32"),
+             (not m.moe_grouped_gemm, "moe_grouped_gemm", "experts always run as one grouped GEMM"),
+             (not m.moe_permute_fusion, "moe_permute_fusion", "dispatch writes rows in their final order: no permute kernels"),
+             (not p.use_distributed_optimizer, "use_distributed_optimizer",
+              "optimizer state lives with the parameter shards (fsdp=true) or is replicated (fsdp=false)"),
+             (not p.overlap_grad_reduce, "overlap_grad_reduce", "gradients are reduced per layer inside backward"),
+             (not p.overlap_param_gather, "overlap_param_gather", "parameters are gathered per layer; see fsdp_prefetch"),
+             (not p.grad_reduce_in_bf16 and pr.params_dtype == "bf16", "grad_reduce_in_bf16",
+              "gradients are reduced in the parameter dtype and accumulated in fp32"),
+             (not p.ddp_average_in_collective, "ddp_average_in_collective", "the loss is pre-scaled, sums need no average")]
+    for hit, knob, why in inert:
+        if hit:
+            out.append(_p("knob_has_no_effect", f"{knob} is set to a non-default value but has no effect: {why}",
+                          severity="warning"))
     # 6. sequence length
     if cp > 1 and m.seq_length % cp:
         out.append(_p("cp_divides_seq_len", f"seq_length={m.seq_length} % cp={cp} != 0"))

@@ -31,6 +31,10 @@ def main(argv=None) -> int:
     from .trainer.loop import Trainer
     tr = Trainer(cfg)
     if tr.mesh.rank == 0:
+        from .pilot.constraints import check_config
+        for prob in check_config(cfg, tr.mesh.world):
+            if prob["severity"] == "warning":
+                logging.getLogger("system_lab_b200.config").warning("%s: %s", prob["rule"], prob["message"])
         out_dir = Path(cfg.checkpoint.save or ".")
         cfg.dump(out_dir / "resolved_config.json")
     resume = args.resume or cfg.checkpoint.load

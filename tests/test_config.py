@@ -91,3 +91,12 @@ def test_tensor_parallel_and_hybrid_sharding_rules():
     big = Config.load(preset="qwen3-30b-a3b", overrides=["expert_model_parallel_size=8"])
     tp2 = Config.load(preset="qwen3-30b-a3b", overrides=["expert_model_parallel_size=8", "tensor_model_parallel_size=2"])
     assert estimate_memory(tp2, 8)["activation_bytes"] < estimate_memory(big, 8)["activation_bytes"]
+
+
+def test_inert_knobs_are_reported_not_ignored():
+    cfg = Config.load(preset="simplemoe-tiny", overrides=["overlap_grad_reduce=false", "moe_permute_fusion=false"])
+    warns = [p for p in check_config(cfg, 2) if p["rule"] == "knob_has_no_effect"]
+    assert len(warns) == 2 and all(p["severity"] == "warning" for p in warns)
+    assert not [p for p in check_config(Config.load(preset="simplemoe-tiny"), 2) if p["rule"] == "knob_has_no_effect"]
+    with pytest.raises(ConfigError, match="tie_embeddings"):
+        Config.load(preset="simplemoe-tiny", overrides=["tie_embeddings=true"])
