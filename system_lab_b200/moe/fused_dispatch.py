@@ -17,6 +17,7 @@ All ranks must issue the same sequence of calls: flags carry a call counter (epo
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -110,6 +111,10 @@ class FusedDispatcher:
         self.push = push
         self.push_epoch = 0
         self._pending_push = {}           # GEMM mode (0 fwd / 1 dgrad) -> push epoch not yet reduced by its consumer
+        # debug aid (SLAB_POISON=1): fill the receive regions with NaN patterns at the points where the protocol says
+        # nobody reads or writes them, so a row consumed without having been written this round, or a flag that let a
+        # reader through early, shows up as a NaN loss instead of a plausible number
+        self.poison = os.environ.get("SLAB_POISON", "0") == "1"
         if dtype != torch.bfloat16:
             raise ValueError("the fused dispatcher moves bf16 rows")
         self.capacity, off, cur = compute_layout(self.ep, num_experts, topk, hidden, max_tokens, self.pad,
@@ -175,6 +180,11 @@ class FusedDispatcher:
         if t > self.T or k != self.K:
             raise ValueError(f"plan for {t}x{k} pairs exceeds the dispatcher's {self.T}x{self.K}")
         ep = self._next_epoch()
+        if self.poison:
+            # forward rows: their last readers (this rank's GEMMs of the previous layer) are earlier in this stream, and
+            # no peer writes them before it has seen the counts published below
+            self.rows[0].view(torch.int16).fill_(-1)
+            self.scalars[0].fill_(float("nan"))
         cops.call("slab_moe_count_publish", idx, t * k, self.E, self.block_hist, self.send_counts,
                   ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, ep,
                   cops.stream())
@@ -193,6 +203,11 @@ class FusedDispatcher:
         cops.call("slab_moe_plan_slots", idx, t * k, self.E, self.block_hist, ctypes.addressof(self._peer_ptrs),
                   ctypes.addressof(self._lay[0]), self.ep, self.me, ep, self.pad, self.capacity, expert_offsets,
                   expert_counts, self.send_base, meta, pair_loc, self.status, cops.stream())
+        if self.poison:
+            # result regions: every peer has published this layer's counts, so it has finished pulling / pushing the
+            # previous layer's results; the next writers (this rank's GEMM, the peers' push epilogues) come later
+            self.out_rows.view(torch.int16).fill_(-1)
+            self.comb.view(torch.int16).fill_(-1)
         return FusedPlan(t, k, self.E, self.ep, self.pad, self.capacity, expert_offsets, expert_counts, pair_loc,
                          meta, self.send_counts.clone(), self.capacity)
 

@@ -168,3 +168,13 @@ def test_lora_dense_model_on_the_kernel_route(dry):
     tr.train_step()
     assert "slab_ce_fwd_bwd" in dry and "slab_adamw" in dry
     assert dry.count("slab_adamw") == sum(1 for g in tr.engine.all_groups() if not g.frozen)
+
+
+def test_poison_fill_debug_mode_walks_the_host_path(dry, monkeypatch):
+    """SLAB_POISON=1 fills the dispatcher's receive regions with NaN patterns between uses (a debug aid against stale
+    reads); the host side must not disturb a step."""
+    monkeypatch.setenv("SLAB_POISON", "1")
+    tr, d = _trainer(["recompute_granularity=selective"], {"push": True})
+    assert d.poison
+    tr.train_step()
+    assert torch.isnan(d.scalars[0]).all() and (d.comb.view(torch.int16) == -1).all()
