@@ -100,3 +100,12 @@ def test_inert_knobs_are_reported_not_ignored():
     assert not [p for p in check_config(Config.load(preset="simplemoe-tiny"), 2) if p["rule"] == "knob_has_no_effect"]
     with pytest.raises(ConfigError, match="tie_embeddings"):
         Config.load(preset="simplemoe-tiny", overrides=["tie_embeddings=true"])
+
+
+@pytest.mark.parametrize("name,world", [("qwen3_30b_a3b_8gpu", 8), ("deepseek_v3_proxy_pp2_ep4", 8),
+                                        ("llama2_70b_lora_8gpu", 8), ("simplemoe_tiny_cpu", 2)])
+def test_example_configs_load_and_fit(name, world):
+    from pathlib import Path
+    cfg = Config.load(Path(__file__).resolve().parent.parent / "configs" / f"{name}.yaml")
+    cfg.validate(world)
+    assert estimate_memory(cfg, world)["fits"]
