@@ -36,6 +36,8 @@ LEVERS: dict[str, list[dict]] = {
     "COMPUTE": [
         {"axis": "runtime.mbs", "op": "double", "gain": 8.0, "risk": "memory"},
         {"axis": "runtime.recompute", "op": "relax", "gain": 10.0, "risk": "memory"},
+        {"axis": "parallelism.tp", "op": "halve", "gain": 6.0, "needs": "tp>1",
+         "note": "fewer exposed all-reduces per layer, larger GEMMs per rank"},
         {"axis": "parallelism.vpp", "op": "set", "values": [2], "gain": 3.0, "needs": "pp>1"},
         {"axis": "precision.fp8", "op": "set", "values": [True], "gain": 20.0, "risk": "numeric"},
     ],
@@ -51,6 +53,7 @@ LEVERS: dict[str, list[dict]] = {
     "COMM": [
         {"axis": "comm.dispatcher", "op": "set", "values": ["fused"], "gain": 15.0},
         {"axis": "comm.fsdp_fused_collectives", "op": "set", "values": [True], "gain": 4.0},
+        {"axis": "parallelism.tp", "op": "halve", "gain": 8.0, "needs": "tp>1", "risk": "memory"},
         {"axis": "parallelism.ep", "op": "halve", "gain": 6.0, "risk": "memory"},
         {"axis": "comm.bucket_size_mb", "op": "set", "values": [64, 160], "gain": 2.0},
         {"axis": "env.NCCL_NVLS_ENABLE", "op": "set", "values": ["1"], "gain": 2.0},
@@ -184,6 +187,8 @@ def _apply(plan: dict, lever: dict, value: Any) -> dict | None:
         if dp % new:
             return None
         q["parallelism"]["dp"] = dp // new
+        if q["runtime"]["gbs"] % (q["runtime"]["mbs"] * q["parallelism"]["dp"]):
+            return None
     if lever["axis"] == "runtime.mbs":
         dp = q["parallelism"]["dp"]
         if q["runtime"]["gbs"] % (new * dp):
@@ -209,6 +214,8 @@ def replan(champion: dict, diagnosis: dict, graph: "PlanGraph", *, check, estima
     for src in sources:
         for lever in levers:
             if lever.get("needs") == "pp>1" and src["parallelism"]["pp"] <= 1:
+                continue
+            if lever.get("needs") == "tp>1" and src["parallelism"].get("tp", 1) <= 1:
                 continue
             for value in lever.get("values", [None]):
                 q = _apply(src, lever, value)

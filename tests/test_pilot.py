@@ -314,3 +314,16 @@ def test_mcp_tool_server_lists_and_calls_tools(tmp_path):
     assert json.loads(resp[2]["result"]["content"][0]["text"])["valid"] is True
     assert json.loads(resp[3]["result"]["content"][0]["text"])["valid"] is False
     assert "error" in resp[4] and "unknown method" in resp[4]["error"]["message"]
+
+
+def test_tensor_parallel_levers_keep_the_world_size():
+    from system_lab_b200.pilot import policy
+    base = policy.default_plan(8, ep=8, mbs=2, gbs=32)
+    up = [l for l in policy.LEVERS["MEMORY"] if l["axis"] == "parallelism.tp"][0]
+    wide = policy._apply(base, up, None)
+    assert wide["parallelism"]["tp"] == 2 and wide["parallelism"]["dp"] == 4          # ranks come from the data axis
+    down = [l for l in policy.LEVERS["COMPUTE"] if l["axis"] == "parallelism.tp"][0]
+    assert policy._apply(wide, down, None)["parallelism"] == base["parallelism"]
+    assert policy._apply(base, down, None) is None                                    # tp = 1 cannot shrink
+    ov, _ = policy.plan_to_overrides(wide)
+    assert "tensor_model_parallel_size=2" in ov
