@@ -92,6 +92,7 @@ class Trainer:
         self.tokens_per_step = t.global_batch_size * cfg.model.seq_length
         self._tpe_accum = None
         self.reached_target = False
+        self.stopped_on_time = False
         self.relocator = None
         self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
         if cfg.model.moe_expert_relocation_interval > 0 and cfg.model.num_experts > 0:
@@ -182,6 +183,13 @@ class Trainer:
         if self.heartbeat is not None:
             self.heartbeat.beat(step)
         return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
+
+    def _time_is_up(self, started: float, minutes: float) -> bool:
+        """Rank 0 looks at the clock; everyone follows its decision so that no rank enters a step alone."""
+        flag = torch.tensor([1.0 if (time.time() - started) > 60.0 * minutes else 0.0], device=self.device)
+        if dist.is_initialized() and self.mesh.world > 1:
+            dist.broadcast(flag, src=0)
+        return bool(flag.item() > 0)
 
     EVAL_STEP_OFFSET = 1 << 40            # held-out region of the (seed, step) -> batch map
 
@@ -276,6 +284,11 @@ class Trainer:
             from ..observe.profiler import StepProfiler
             prof = StepProfiler(cfg.profile, self.mesh.rank)
         target = self.step + iters
+        import gc
+        if t.manual_gc:
+            gc.disable()
+            gc.collect()
+        started = time.time()
         while self.step < target:
             if is_cuda:
                 torch.cuda.synchronize()
@@ -310,6 +323,13 @@ class Trainer:
             ck = cfg.checkpoint
             if ck.save and ck.save_interval and self.step % ck.save_interval == 0:
                 self.save_checkpoint(ck.save)
+            if t.manual_gc and self.step % max(t.manual_gc_interval, 1) == 0:
+                gc.collect()                          # same step on every rank: one aligned pause instead of scattered ones
+            if t.exit_duration_in_mins > 0 and self._time_is_up(started, t.exit_duration_in_mins):
+                self.stopped_on_time = True
+                break
+        if t.manual_gc:
+            gc.enable()
         if cfg.checkpoint.save and not cfg.checkpoint.disable_last_saving:
             self.save_checkpoint(cfg.checkpoint.save)
         if self.events:

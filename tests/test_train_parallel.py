@@ -226,3 +226,23 @@ def test_tensor_parallel_with_data_parallel_selective_and_resume(single_curve, t
     assert [r[1] for r in resumed] == [r[1] for r in full]
     with pytest.raises(Exception, match="tensor_model_parallel_size"):
         run_ranks(_train, 1, BASE + ["expert_model_parallel_size=1"], 1, None, ck)
+
+
+def _fit(rank, world, overrides):
+    import gc
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu"]))
+    tr.fit()
+    return tr.step, tr.stopped_on_time, gc.isenabled()
+
+
+def test_wall_clock_exit_is_collective_and_manual_gc_restores_the_collector():
+    """Rank 0 decides that the time is up and every rank leaves after the same step; manual garbage collection runs
+    with the collector off and turns it back on."""
+    ov = BASE + ["expert_model_parallel_size=2", "train_iters=50", "exit_duration_in_mins=0.0005", "manual_gc=true",
+                 "manual_gc_interval=1", "log_interval=100"]
+    res = run_ranks(_fit, 2, ov)
+    steps = {r[0] for r in res}
+    assert len(steps) == 1 and 1 <= steps.pop() < 50
+    assert all(r[1] and r[2] for r in res)
