@@ -82,12 +82,16 @@ def _legal(train_args: list[str], world: int) -> bool:
 class Supervisor:
     def __init__(self, nproc: int, train_args: list[str], *, max_restarts: int = 3, shrink: bool = False,
                  min_nproc: int = 1, grace_s: float = 10.0, poll_s: float = 0.2, log_dir: str = "",
-                 python: str = sys.executable):
+                 python: str = sys.executable, bind_cores: bool = False):
         self.nproc, self.train_args = nproc, list(train_args)
         self.max_restarts, self.shrink, self.min_nproc = max_restarts, shrink, min_nproc
         self.grace_s, self.poll_s = grace_s, poll_s
         self.log_dir = Path(log_dir) if log_dir else None
         self.python = python
+        # bind_cores: every rank gets its own contiguous slice of the host's cores (the data-loader and launch
+        # threads of different ranks then do not migrate onto each other's cores; the reference's large-job notes
+        # bind ranks to the NUMA node of their GPU, ``summary/training-1024g*:41-101``)
+        self.bind_cores = bind_cores
         self.history: list[dict] = []
 
     # ---- one attempt -----------------------------------------------------------------------------------
@@ -108,8 +112,19 @@ class Supervisor:
                 out = open(self.log_dir / f"attempt{attempt}_rank{rank}.log", "w")
             # a session of its own: stopping the rank signals this process group and nothing else
             procs.append(subprocess.Popen([self.python, "-m", "system_lab_b200.train"] + args, env=env, stdout=out,
-                                          stderr=subprocess.STDOUT, start_new_session=True))
+                                          stderr=subprocess.STDOUT, start_new_session=True,
+                                          preexec_fn=self._binder(rank, world)))
         return procs
+
+    def _binder(self, rank: int, world: int):
+        if not self.bind_cores or not hasattr(os, "sched_setaffinity"):
+            return None
+        cores = sorted(os.sched_getaffinity(0))
+        per = len(cores) // world
+        if per < 1:
+            return None
+        mine = set(cores[rank * per:(rank + 1) * per])
+        return lambda: os.sched_setaffinity(0, mine)
 
     def _stop(self, procs: list[subprocess.Popen]) -> None:
         for sig, wait in ((signal.SIGTERM, self.grace_s), (signal.SIGKILL, 5.0)):
@@ -180,9 +195,10 @@ def main(argv=None) -> int:
     ap.add_argument("--min-nproc", type=int, default=1)
     ap.add_argument("--grace-s", type=float, default=10.0)
     ap.add_argument("--log-dir", default="")
+    ap.add_argument("--bind-cores", action="store_true", help="give every rank its own slice of the host's cores")
     a = ap.parse_args(argv)
     sup = Supervisor(a.nproc, train_args, max_restarts=a.max_restarts, shrink=a.shrink, min_nproc=a.min_nproc,
-                     grace_s=a.grace_s, log_dir=a.log_dir)
+                     grace_s=a.grace_s, log_dir=a.log_dir, bind_cores=a.bind_cores)
     return sup.run()
 
 
