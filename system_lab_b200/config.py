@@ -167,6 +167,7 @@ class TrainConfig:
     manual_gc: bool = False              # turn the cyclic garbage collector off and collect every `manual_gc_interval` steps on every rank at once (a collection on one rank otherwise stalls all: `summary/training-1024g*:41-101`)
     manual_gc_interval: int = 50
     exit_duration_in_mins: float = 0.0   # > 0: stop (after saving) once the job has run this long; decided on rank 0, applied by all
+    exit_signal_handler: bool = False    # SIGTERM on any rank: all ranks finish the step, save a checkpoint and leave (preemption)
 
 
 @dataclass

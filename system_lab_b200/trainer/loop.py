@@ -93,6 +93,7 @@ class Trainer:
         self._tpe_accum = None
         self.reached_target = False
         self.stopped_on_time = False
+        self.stopped_on_signal = False
         self.relocator = None
         self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
         if cfg.model.moe_expert_relocation_interval > 0 and cfg.model.num_experts > 0:
@@ -184,12 +185,16 @@ class Trainer:
             self.heartbeat.beat(step)
         return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
 
-    def _time_is_up(self, started: float, minutes: float) -> bool:
-        """Rank 0 looks at the clock; everyone follows its decision so that no rank enters a step alone."""
-        flag = torch.tensor([1.0 if (time.time() - started) > 60.0 * minutes else 0.0], device=self.device)
+    def _should_leave(self, started: float, minutes: float) -> bool:
+        """One small collective after a step: has rank 0's clock passed the limit, has any rank received SIGTERM?
+        Every rank gets the same answer, so no rank enters the next step alone."""
+        late = minutes > 0 and self.mesh.rank == 0 and (time.time() - started) > 60.0 * minutes
+        flags = torch.tensor([1.0 if late else 0.0, 1.0 if self._term_seen else 0.0], device=self.device)
         if dist.is_initialized() and self.mesh.world > 1:
-            dist.broadcast(flag, src=0)
-        return bool(flag.item() > 0)
+            dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+        self.stopped_on_time = bool(flags[0] > 0)
+        self.stopped_on_signal = bool(flags[1] > 0)
+        return self.stopped_on_time or self.stopped_on_signal
 
     EVAL_STEP_OFFSET = 1 << 40            # held-out region of the (seed, step) -> batch map
 
@@ -289,6 +294,13 @@ class Trainer:
             gc.disable()
             gc.collect()
         started = time.time()
+        self._term_seen = False
+        old_handler = None
+        if t.exit_signal_handler:
+            import signal
+            import threading
+            if threading.current_thread() is threading.main_thread():
+                old_handler = signal.signal(signal.SIGTERM, lambda *_: setattr(self, "_term_seen", True))
         while self.step < target:
             if is_cuda:
                 torch.cuda.synchronize()
@@ -325,11 +337,14 @@ class Trainer:
                 self.save_checkpoint(ck.save)
             if t.manual_gc and self.step % max(t.manual_gc_interval, 1) == 0:
                 gc.collect()                          # same step on every rank: one aligned pause instead of scattered ones
-            if t.exit_duration_in_mins > 0 and self._time_is_up(started, t.exit_duration_in_mins):
-                self.stopped_on_time = True
+            if (t.exit_duration_in_mins > 0 or t.exit_signal_handler) and \
+                    self._should_leave(started, t.exit_duration_in_mins):
                 break
         if t.manual_gc:
             gc.enable()
+        if old_handler is not None:
+            import signal
+            signal.signal(signal.SIGTERM, old_handler)
         if cfg.checkpoint.save and not cfg.checkpoint.disable_last_saving:
             self.save_checkpoint(cfg.checkpoint.save)
         if self.events:

@@ -246,3 +246,30 @@ def test_wall_clock_exit_is_collective_and_manual_gc_restores_the_collector():
     steps = {r[0] for r in res}
     assert len(steps) == 1 and 1 <= steps.pop() < 50
     assert all(r[1] and r[2] for r in res)
+
+
+def _fit_with_sigterm(rank, world, overrides, save):
+    import os
+    import signal
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu", f"save={save}"]))
+    if rank == 1:                      # the scheduler's preemption notice reaches one rank only
+        orig = tr.train_step
+
+        def step_then_signal(*a, **k):
+            out = orig(*a, **k)
+            if tr.step == 2:
+                os.kill(os.getpid(), signal.SIGTERM)
+            return out
+        tr.train_step = step_then_signal
+    tr.fit()
+    return tr.step, tr.stopped_on_signal
+
+
+def test_sigterm_on_one_rank_makes_every_rank_save_and_leave(tmp_path):
+    from system_lab_b200.launch import newest_checkpoint
+    ov = BASE + ["expert_model_parallel_size=2", "train_iters=30", "exit_signal_handler=true", "log_interval=100"]
+    res = run_ranks(_fit_with_sigterm, 2, ov, str(tmp_path / "ck"))
+    assert [r[0] for r in res] == [2, 2] and all(r[1] for r in res)
+    assert newest_checkpoint(str(tmp_path / "ck")).endswith("step_000002")
