@@ -90,17 +90,9 @@ def _is_writer(trainer, g) -> bool:
     return dist.get_rank(g.replica_group) == 0
 
 
-def save_checkpoint(trainer, root: str) -> str:
-    mesh = trainer.mesh
-    root_p = Path(root)
-    final = root_p / f"step_{trainer.step:06d}"
-    tmp = root_p / f".tmp_step_{trainer.step:06d}"
-    if mesh.rank == 0:
-        if tmp.exists():
-            shutil.rmtree(tmp)
-        tmp.mkdir(parents=True, exist_ok=True)
-    _barrier()
-    opt = trainer.optimizer
+def _snapshot(trainer) -> tuple[dict, dict]:
+    """Host copies of everything this rank writes, plus the metadata rank 0 adds: the state of the job at this step."""
+    mesh, opt = trainer.mesh, trainer.optimizer
     tensors, index = {}, []
     for g, fqn, gshape, gstart, length, soff in _owned_pieces(trainer):
         if not _is_writer(trainer, g):
@@ -119,28 +111,102 @@ def save_checkpoint(trainer, root: str) -> str:
     for u in trainer.engine.units:
         for bn, b in u.module.named_buffers():
             buffers[f"{u.name}.{bn}"] = b.detach().cpu().clone()
+    prev = opt._prev_norm
     payload = {"tensors": tensors, "index": index, "buffers": buffers,
-               "opt_step": opt.step_count, "prev_norm": opt._prev_norm,
+               "opt_step": opt.step_count, "prev_norm": prev.detach().cpu().clone() if torch.is_tensor(prev) else prev,
                "torch_rng": torch.get_rng_state()}
-    mine = tmp / f"rank_{mesh.rank:05d}.pt"
+    meta = {"format": "system_lab_b200.ckpt.v1", "step": trainer.step, "world": mesh.world,
+            "mesh": {"pp": mesh.pp, "dp": mesh.dp, "cp": mesh.cp, "ep": mesh.ep, "tp": mesh.tp},
+            "data_cursor": trainer.data.cursor, "loss_curve": list(trainer.loss_curve),
+            "optimizer_state_dtype": trainer.cfg.precision.optimizer_state_dtype,
+            "config": trainer.cfg.to_dict()}
+    return payload, meta
+
+
+def _write_rank_file(tmp: Path, rank: int, payload: dict) -> None:
+    mine = tmp / f"rank_{rank:05d}.pt"
     torch.save(payload, mine)
     mine.with_suffix(".sha256").write_text(_sha256(mine))
+
+
+def _publish(root_p: Path, tmp: Path, final: Path, meta: dict, keep_last: int) -> None:
+    """Rank 0, after every rank's file is on disk: metadata, atomic rename, ``latest`` pointer, retention."""
+    (tmp / "meta.json").write_text(json.dumps(meta, indent=2))
+    if final.exists():
+        shutil.rmtree(final)
+    os.replace(tmp, final)
+    (root_p / "latest.tmp").write_text(final.name)
+    os.replace(root_p / "latest.tmp", root_p / "latest")
+    _prune(root_p, keep_last)
+
+
+def save_checkpoint(trainer, root: str) -> str:
+    """Synchronous by default.  With ``checkpoint.async_save`` the state is copied to host memory here and written
+    by a background thread while training goes on; the checkpoint becomes visible (metadata, rename) at a later step
+    boundary, once every rank's file is complete (``finish_pending``).  The reference's runs paid 6 minutes per
+    268 GB save with training stopped (``notes/2026-04/2026-04-22_gptoss_22_*:170,180-181``)."""
+    finish_pending(trainer, wait=True)                # at most one save in flight
+    mesh = trainer.mesh
+    root_p = Path(root)
+    final = root_p / f"step_{trainer.step:06d}"
+    tmp = root_p / f".tmp_step_{trainer.step:06d}"
+    if mesh.rank == 0:
+        if tmp.exists():
+            shutil.rmtree(tmp)
+        tmp.mkdir(parents=True, exist_ok=True)
+    _barrier()
+    payload, meta = _snapshot(trainer)
+    keep = trainer.cfg.checkpoint.keep_last
+    if getattr(trainer.cfg.checkpoint, "async_save", False):
+        import threading
+        box = {"error": None}
+
+        def work():
+            try:
+                _write_rank_file(tmp, mesh.rank, payload)
+            except BaseException as e:                # surfaced by finish_pending on the main thread
+                box["error"] = e
+        th = threading.Thread(target=work, name="slab-ckpt-writer", daemon=False)
+        th.start()
+        trainer._pending_ckpt = {"thread": th, "box": box, "root": root_p, "tmp": tmp, "final": final, "meta": meta,
+                                 "keep": keep}
+        return str(final)
+    _write_rank_file(tmp, mesh.rank, payload)
     _barrier()
     if mesh.rank == 0:
-        meta = {"format": "system_lab_b200.ckpt.v1", "step": trainer.step, "world": mesh.world,
-                "mesh": {"pp": mesh.pp, "dp": mesh.dp, "cp": mesh.cp, "ep": mesh.ep, "tp": mesh.tp},
-                "data_cursor": trainer.data.cursor, "loss_curve": trainer.loss_curve,
-                "optimizer_state_dtype": trainer.cfg.precision.optimizer_state_dtype,
-                "config": trainer.cfg.to_dict()}
-        (tmp / "meta.json").write_text(json.dumps(meta, indent=2))
-        if final.exists():
-            shutil.rmtree(final)
-        os.replace(tmp, final)
-        (root_p / "latest.tmp").write_text(final.name)
-        os.replace(root_p / "latest.tmp", root_p / "latest")
-        _prune(root_p, trainer.cfg.checkpoint.keep_last)
+        _publish(root_p, tmp, final, meta, keep)
     _barrier()
     return str(final)
+
+
+def finish_pending(trainer, wait: bool = False) -> bool:
+    """Complete an asynchronous save if every rank's writer has finished (``wait``: block until they have).
+    Collective: every rank calls it at the same points (step boundaries, the next save, the end of ``fit``).
+    Returns True if nothing is pending any more."""
+    pend = getattr(trainer, "_pending_ckpt", None)
+    if pend is None:
+        return True
+    th = pend["thread"]
+    if wait:
+        th.join()
+    done = torch.tensor([0.0 if th.is_alive() else 1.0])
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        done = done.to(trainer.device)
+        dist.all_reduce(done, op=dist.ReduceOp.MIN)
+    if float(done) < 1.0:
+        return False
+    th.join()
+    trainer._pending_ckpt = None
+    err = torch.tensor([1.0 if pend["box"]["error"] is not None else 0.0])
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        err = err.to(trainer.device)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    if float(err) > 0:
+        raise RuntimeError(f"asynchronous checkpoint {pend['final']} failed on some rank: {pend['box']['error']!r}")
+    if trainer.mesh.rank == 0:
+        _publish(pend["root"], pend["tmp"], pend["final"], pend["meta"], pend["keep"])
+    _barrier()
+    return True
 
 
 def _prune(root: Path, keep: int) -> None:
@@ -270,7 +336,8 @@ def _load_one(trainer, ck: Path) -> None:
         if same_layout and f == own:
             torch.set_rng_state(payload["torch_rng"])
         opt.step_count = payload["opt_step"]
-        opt._prev_norm = payload.get("prev_norm")
+        pn = payload.get("prev_norm")
+        opt._prev_norm = pn.to(trainer.device) if torch.is_tensor(pn) else pn
     # replicas of unsharded groups did not write: they read the writer's pieces above (same fqn ranges)
     for g in trainer.engine.all_groups():
         need = sum(l for gg, _, _, _, l, _ in want if gg is g)

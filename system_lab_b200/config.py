@@ -177,6 +177,7 @@ class CheckpointConfig:
     save_interval: int = 0
     disable_last_saving: bool = False
     keep_last: int = 2
+    async_save: bool = False             # copy the state to host memory, write it in the background, publish it at a later step boundary
 
 
 @dataclass

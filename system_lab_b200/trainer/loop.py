@@ -333,6 +333,9 @@ class Trainer:
                     self.reached_target = True
                     break
             ck = cfg.checkpoint
+            if getattr(self, "_pending_ckpt", None) is not None:
+                from ..ckpt.sharded import finish_pending
+                finish_pending(self)                  # publishes an asynchronous save once every rank has written
             if ck.save and ck.save_interval and self.step % ck.save_interval == 0:
                 self.save_checkpoint(ck.save)
             if t.manual_gc and self.step % max(t.manual_gc_interval, 1) == 0:
@@ -347,6 +350,9 @@ class Trainer:
             signal.signal(signal.SIGTERM, old_handler)
         if cfg.checkpoint.save and not cfg.checkpoint.disable_last_saving:
             self.save_checkpoint(cfg.checkpoint.save)
+        if getattr(self, "_pending_ckpt", None) is not None:
+            from ..ckpt.sharded import finish_pending
+            finish_pending(self, wait=True)
         if self.events:
             ok = self.reached_target or not t.eval_target_loss
             self.events.stop(self.tokens_per_step * self.step, status="success" if ok else "aborted")

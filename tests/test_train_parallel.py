@@ -273,3 +273,27 @@ def test_sigterm_on_one_rank_makes_every_rank_save_and_leave(tmp_path):
     res = run_ranks(_fit_with_sigterm, 2, ov, str(tmp_path / "ck"))
     assert [r[0] for r in res] == [2, 2] and all(r[1] for r in res)
     assert newest_checkpoint(str(tmp_path / "ck")).endswith("step_000002")
+
+
+def _fit_async(rank, world, overrides, save, load=None):
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu", f"save={save}"]))
+    if load:
+        tr.load_checkpoint(load)
+    tr.fit(max(tr.cfg.train.train_iters - tr.step, 0))
+    return tr.loss_curve, getattr(tr, "_pending_ckpt", None) is None
+
+
+def test_async_checkpoint_is_published_later_and_resumes_bit_exactly(tmp_path):
+    from pathlib import Path
+    ov = BASE + ["expert_model_parallel_size=2", "train_iters=5", "save_interval=2", "log_interval=100", "keep_last=5"]
+    sync = run_ranks(_fit_async, 2, ov, str(tmp_path / "sync"))
+    asyn = run_ranks(_fit_async, 2, ov + ["async_save=true"], str(tmp_path / "async"))
+    assert asyn[0][0] == sync[0][0] and all(r[1] for r in asyn)          # same training, nothing left pending
+    names = sorted(p.name for p in Path(tmp_path / "async").glob("step_*"))
+    assert names == ["step_000002", "step_000004", "step_000005"]
+    assert not list(Path(tmp_path / "async").glob(".tmp_step_*"))
+    # resume from the asynchronously written step 4 and reproduce step 5
+    res = run_ranks(_fit_async, 2, ov, str(tmp_path / "resumed"), str(tmp_path / "async" / "step_000004"))
+    assert res[0][0][-1] == sync[0][0][-1]
