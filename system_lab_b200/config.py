@@ -164,6 +164,7 @@ class TrainConfig:
     heartbeat: bool = True               # ranks publish per-step heartbeats; a peer stuck for hang_timeout_s is reported
     fault_injection: str = ""            # host-side test faults, e.g. "delay:rank=1,step=3,seconds=5;nan:rank=0,step=4"
     mllog: bool = False
+    metrics_file: str = ""               # rank 0 appends one JSON line per logged step (loss, step time, tokens/s, memory, MoE load)
     manual_gc: bool = False              # turn the cyclic garbage collector off and collect every `manual_gc_interval` steps on every rank at once (a collection on one rank otherwise stalls all: `summary/training-1024g*:41-101`)
     manual_gc_interval: int = 50
     exit_duration_in_mins: float = 0.0   # > 0: stop (after saving) once the job has run this long; decided on rank 0, applied by all

@@ -369,6 +369,14 @@ class Trainer:
         log.info("iteration %6d | elapsed ms/iter %9.1f | TFLOP/s/GPU %7.1f | tokens/s/GPU %9.0f | lm loss %.6f | "
                  "grad norm %.4f | lr %.3e | nan iters %d | mem GiB %.1f",
                  self.step, dt_ms, tflops, tps_gpu, loss, gn, lr, self.nan_iters, mem)
+        path = self.cfg.train.metrics_file
+        if path:
+            rec = {"step": self.step, "time": time.time(), "step_ms": dt_ms, "loss": loss, "grad_norm": gn, "lr": lr,
+                   "tokens_per_s": self.tokens_per_step / (dt_ms / 1e3), "tflops_per_gpu": tflops, "mem_gib": mem,
+                   "nan_iters": self.nan_iters, "ep_rank_load_max_over_mean": self.rank_load_ratio()}
+            Path(path).parent.mkdir(parents=True, exist_ok=True)
+            with open(path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
 
     # ---- the tuner's Snapshot (metric contract: skills/pilot/workflow/observe.md:36-112) ------------
     def snapshot(self) -> dict:

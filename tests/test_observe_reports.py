@@ -97,3 +97,18 @@ def test_trace_reader_streams_large_files_in_small_chunks(tmp_path):
     p = tmp_path / "t.json"
     p.write_text(doc)
     assert sum(1 for _ in tb._events(str(p))) == 3000
+
+
+def test_metrics_file_gets_one_json_line_per_logged_step(tmp_path):
+    import json
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    path = tmp_path / "m" / "metrics.jsonl"
+    cfg = Config.load(preset="simplemoe-tiny", overrides=["device=cpu", "train_iters=4", "log_interval=2",
+                                                         "expert_model_parallel_size=1", f"metrics_file={path}"])
+    tr = Trainer(cfg)
+    tr.fit()
+    tr.close()
+    recs = [json.loads(l) for l in path.read_text().splitlines()]
+    assert [r["step"] for r in recs] == [2, 4]
+    assert all(r["loss"] > 0 and r["tokens_per_s"] > 0 and r["ep_rank_load_max_over_mean"] >= 1.0 for r in recs)
