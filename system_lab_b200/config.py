@@ -144,7 +144,8 @@ class TrainConfig:
     min_lr: float = 0.0
     lr_warmup_iters: int = 0
     lr_decay_iters: int = 0
-    lr_decay_style: str = "constant"     # constant | cosine | linear
+    lr_decay_style: str = "constant"     # constant | cosine | linear | wsd (flat, then linear over the last lr_wsd_decay_iters)
+    lr_wsd_decay_iters: int = 0
     weight_decay: float = 0.1
     adam_beta1: float = 0.9
     adam_beta2: float = 0.95

@@ -146,7 +146,8 @@ class Trainer:
         dev = self.device
         dev_batches = [(tok.to(dev, non_blocking=True), tgt.to(dev, non_blocking=True)) for tok, tgt in batches]
         lr = lr_at(step, lr=cfg.train.lr, min_lr=cfg.train.min_lr, warmup=cfg.train.lr_warmup_iters,
-                   decay_iters=cfg.train.lr_decay_iters, style=cfg.train.lr_decay_style)
+                   decay_iters=cfg.train.lr_decay_iters, style=cfg.train.lr_decay_style,
+                   wsd_decay_iters=cfg.train.lr_wsd_decay_iters)
         in_bwd = cfg.train.optimizer_in_backward
         if in_bwd:
             self.optimizer.begin_step(lr)

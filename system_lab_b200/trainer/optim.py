@@ -233,7 +233,8 @@ class ShardedAdamW:
         self._prev_norm = sd.get("prev_norm")
 
 
-def lr_at(step: int, *, lr: float, min_lr: float, warmup: int, decay_iters: int, style: str) -> float:
+def lr_at(step: int, *, lr: float, min_lr: float, warmup: int, decay_iters: int, style: str,
+          wsd_decay_iters: int = 0) -> float:
     """Learning rate for 1-based ``step``.  ``constant`` ignores decay; a launcher default must never
     silently change the schedule (``notes/2026-04/2026-04-28_gptoss_27_mlperf_legal_baseline.md:193-214``)."""
     if warmup > 0 and step <= warmup:
@@ -245,4 +246,9 @@ def lr_at(step: int, *, lr: float, min_lr: float, warmup: int, decay_iters: int,
         return min_lr + 0.5 * (lr - min_lr) * (1 + math.cos(math.pi * t))
     if style == "linear":
         return lr + (min_lr - lr) * t
+    if style == "wsd":
+        # warm-up, stable, decay: flat at `lr` until the last `wsd_decay_iters` of `decay_iters`, then linear to min_lr
+        tail = max(min(wsd_decay_iters, decay_iters - warmup), 1)
+        into = step - (decay_iters - tail)
+        return lr if into <= 0 else lr + (min_lr - lr) * min(into / tail, 1.0)
     raise ValueError(f"unknown lr_decay_style {style!r}")

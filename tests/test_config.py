@@ -109,3 +109,14 @@ def test_example_configs_load_and_fit(name, world):
     cfg = Config.load(Path(__file__).resolve().parent.parent / "configs" / f"{name}.yaml")
     cfg.validate(world)
     assert estimate_memory(cfg, world)["fits"]
+
+
+def test_lr_schedules():
+    from system_lab_b200.trainer.optim import lr_at
+    kw = dict(lr=1.0, min_lr=0.1, warmup=2, decay_iters=10)
+    assert [round(lr_at(s, style="wsd", wsd_decay_iters=4, **kw), 3) for s in (1, 2, 6, 7, 10, 12)] == \
+        [0.5, 1.0, 1.0, 0.775, 0.1, 0.1]
+    assert lr_at(10, style="cosine", **kw) == pytest.approx(0.1) and lr_at(6, style="linear", **kw) == pytest.approx(0.55)
+    assert lr_at(50, style="constant", **kw) == 1.0
+    with pytest.raises(ValueError):
+        lr_at(5, style="nope", **kw)
