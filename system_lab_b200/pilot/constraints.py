@@ -133,6 +133,8 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
     if pr.fp8 and pr.optimizer_state_dtype != "fp32":
         out.append(_p("optim_state_dtype_for_dtype",
                       "fp8 compute with non-fp32 optimizer state: updates may stall", severity="warning"))
+    if t.lr_decay_style not in ("constant", "cosine", "linear", "wsd"):
+        out.append(_p("lr_decay_style", f"lr_decay_style={t.lr_decay_style!r} not in (constant, cosine, linear, wsd)"))
     if pr.recompute_granularity not in ("none", "selective", "full"):
         out.append(_p("recompute_granularity", f"recompute_granularity={pr.recompute_granularity!r}"))
     # knobs kept for vocabulary compatibility with Megatron-style launch files: a value that asks for behaviour this
