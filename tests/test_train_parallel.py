@@ -297,3 +297,28 @@ def test_async_checkpoint_is_published_later_and_resumes_bit_exactly(tmp_path):
     # resume from the asynchronously written step 4 and reproduce step 5
     res = run_ranks(_fit_async, 2, ov, str(tmp_path / "resumed"), str(tmp_path / "async" / "step_000004"))
     assert res[0][0][-1] == sync[0][0][-1]
+
+
+def test_checkpoint_cli_inspect_verify_consolidate(tmp_path, capsys):
+    """Offline tools: the consolidated tensors of a checkpoint written by two ranks (experts split) equal those of a
+    checkpoint written by one rank after the same training; a damaged rank file fails `verify`."""
+    import json
+    from system_lab_b200.ckpt.__main__ import main as ckpt_cli
+    two, one = str(tmp_path / "two"), str(tmp_path / "one")
+    run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2"], 2, two)
+    run_ranks(_train, 1, BASE + ["expert_model_parallel_size=1"], 2, one)
+    assert ckpt_cli(["verify", two]) == 0
+    capsys.readouterr()
+    assert ckpt_cli(["inspect", two, "--json"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["step"] == 2 and info["world"] == 2 and info["parameters"] == 17
+    assert all(t["covered"] >= t["elements"] for t in info["tensors"])
+    assert ckpt_cli(["consolidate", two, "--out", str(tmp_path / "a.pt")]) == 0
+    assert ckpt_cli(["consolidate", one, "--out", str(tmp_path / "b.pt")]) == 0
+    a, b = torch.load(tmp_path / "a.pt"), torch.load(tmp_path / "b.pt")
+    assert a.keys() == b.keys() and a["layers.0.ffn.experts_w1"].shape == (8, 1024, 256)
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)      # two layouts, two summation orders
+    victim = next((tmp_path / "two").glob("step_*/rank_00001.pt"))
+    victim.write_bytes(victim.read_bytes()[:-100])
+    assert ckpt_cli(["verify", two]) == 1
