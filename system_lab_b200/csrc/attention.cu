@@ -314,6 +314,296 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
+// ================================================================ backward
+// One CTA owns 128 key/value rows of one (batch, kv head) and walks the query tiles that can see them, for every
+// query head of the group.  Per query tile (five GEMMs, FlashAttention-2 order):
+//   MMA      S = Q K^T  and  dP = dO V^T                         (TMEM columns [0,128) and [128,256))
+//   softmax  P = exp2(S * scale_log2 - lse2),  dS = P * (dP - delta) * scale   -> bf16 tiles in shared memory
+//   MMA      dV += P^T dO,  dK += dS^T Q  (accumulate over all query tiles and heads of the group, TMEM columns
+//            [256, 256+D) and [256+D, 256+2D)),  dQ = dS K  (fresh, into the columns S occupied)
+//   softmax  drains dQ and adds it to the fp32 dQ buffer with global atomics (other CTAs add their key tiles)
+// At the end the softmax threads (thread = key row) write dK and dV.  The pipeline is serial per query tile (one
+// stage of Q / dO, one S region): a first version for correctness, not yet for speed.
+// Operand forms: every tile is loaded K-major ([128 rows][64 columns] boxes).  The GEMMs that reduce over rows
+// (P^T dO, dS^T Q, dS K's B operand) read the same bytes through MN-major descriptors: a 128-byte row of a box is
+// 64 consecutive MN elements of one reduction index, 8 rows form a swizzle atom (stride 1024), the next 64 MN
+// elements are the next box (leading-dimension stride 16384).
+enum : int {
+  ST_ATTNB_KV = 30, ST_ATTNB_QDO_FULL = 31, ST_ATTNB_QDO_EMPTY = 32, ST_ATTNB_SDP = 33, ST_ATTNB_PDS = 34,
+  ST_ATTNB_MMA2 = 35, ST_ATTNB_DQ = 36,
+};
+
+struct AttnBwdParams {
+  const float* lse;     // [B, Hq, S] natural log
+  const float* delta;   // [B, Hq, S] rowsum(dO * O)
+  float* dq_acc;        // [B, S, Hq, D] fp32, zero-initialised by the caller
+  __nv_bfloat16* dK;    // [B, S, Hkv, D]
+  __nv_bfloat16* dV;    // [B, S, Hkv, D]
+  int B, S, Hq, Hkv;
+  int window;
+  float scale;          // softmax scale
+  float scale_log2;     // scale * log2(e)
+  int* status;
+};
+
+template <int D>
+struct AttnBwdSmem {
+  static constexpr int CTRL_BYTES = 1024;
+  static constexpr int TILE_BYTES = 128 * D * 2;          // K, V, Q, dO tiles
+  static constexpr int PS_BYTES = 128 * 128 * 2;          // P, dS tiles
+  static constexpr int K_OFFSET = CTRL_BYTES;
+  static constexpr int V_OFFSET = K_OFFSET + TILE_BYTES;
+  static constexpr int Q_OFFSET = V_OFFSET + TILE_BYTES;
+  static constexpr int DO_OFFSET = Q_OFFSET + TILE_BYTES;
+  static constexpr int P_OFFSET = DO_OFFSET + TILE_BYTES;
+  static constexpr int DS_OFFSET = P_OFFSET + PS_BYTES;
+  static constexpr int TOTAL = DS_OFFSET + PS_BYTES;
+};
+static_assert(AttnBwdSmem<128>::TOTAL <= 232448, "shared memory budget");
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const AttnBwdParams p) {
+  using L = AttnBwdSmem<D>;
+  constexpr int DB = D / 64;
+  constexpr int COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_INDEX);
+    return;
+  }
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* qdo_full = kv_full + 1;
+  uint64_t* qdo_empty = qdo_full + 1;
+  uint64_t* sdp_full = qdo_empty + 1;
+  uint64_t* pds_ready = sdp_full + 1;
+  uint64_t* mma2_done = pds_ready + 1;
+  uint64_t* dq_drained = mma2_done + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* k_s = smem + L::K_OFFSET;
+  uint8_t* v_s = smem + L::V_OFFSET;
+  uint8_t* q_s = smem + L::Q_OFFSET;
+  uint8_t* do_s = smem + L::DO_OFFSET;
+  uint8_t* p_s = smem + L::P_OFFSET;
+  uint8_t* ds_s = smem + L::DS_OFFSET;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = p.S / AT_BM;
+  const int j = blockIdx.x;                                // key tile (small j = most query tiles: scheduled first)
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int kv0 = j * AT_BN;
+  const int i_lo = j;
+  int i_hi = n_tiles - 1;
+  if (p.window > 0) {
+    const int last_q = kv0 + AT_BN - 1 + p.window - 1;     // last query row that sees the tile's last key
+    i_hi = min(i_hi, last_q / AT_BM);
+  }
+  const int per_head = i_hi - i_lo + 1;
+  const int n_it = G * per_head;
+  const int row_base = b * p.S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 4);
+    mbar_init(mma2_done, 1);
+    mbar_init(dq_drained, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * L::TILE_BYTES);
+#pragma unroll
+      for (int jb = 0; jb < DB; ++jb) {
+        tma_load_2d(k_s + jb * 16384, &tmap_k, kv_full, hk * D + jb * 64, row_base + kv0);
+        tma_load_2d(v_s + jb * 16384, &tmap_v, kv_full, hk * D + jb * 64, row_base + kv0);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int h = hk * G + it / per_head;
+        const int q0 = (i_lo + it % per_head) * AT_BM;
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, p.status, ST_ATTNB_QDO_EMPTY)) break;
+        mbar_arrive_expect_tx(qdo_full, 2 * L::TILE_BYTES);
+#pragma unroll
+        for (int jb = 0; jb < DB; ++jb) {
+          tma_load_2d(q_s + jb * 16384, &tmap_q, qdo_full, h * D + jb * 64, row_base + q0);
+          tma_load_2d(do_s + jb * 16384, &tmap_do, qdo_full, h * D + jb * 64, row_base + q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc(1, 1, 0, 0, 128, 128);     // S, dP: both operands K-major
+      constexpr uint32_t idesc_mm = make_idesc(1, 1, 1, 1, 128, D);       // dV, dK: both operands MN-major views
+      constexpr uint32_t idesc_km = make_idesc(1, 1, 0, 1, 128, D);       // dQ: dS K-major, K tile as MN-major view
+      const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s), q_addr = smem_u32(q_s), do_addr = smem_u32(do_s);
+      const uint32_t p_addr = smem_u32(p_s), ds_addr = smem_u32(ds_s);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_ATTNB_KV);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(qdo_full, ph, abort_flag, p.status, ST_ATTNB_QDO_FULL)) break;
+        if (it > 0 && !mbar_wait(dq_drained, (it - 1) & 1, abort_flag, p.status, ST_ATTNB_DQ)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int jb = kk >> 2, k4 = kk & 3;
+          const uint32_t off = jb * 16384 + k4 * 32;
+          umma_f16(tmem_base, make_smem_desc(q_addr + off, 16, 1024, 2), make_smem_desc(k_addr + off, 16, 1024, 2),
+                   idesc_kk, kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int jb = kk >> 2, k4 = kk & 3;
+          const uint32_t off = jb * 16384 + k4 * 32;
+          umma_f16(tmem_base + COL_DP, make_smem_desc(do_addr + off, 16, 1024, 2),
+                   make_smem_desc(v_addr + off, 16, 1024, 2), idesc_kk, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_ready, ph, abort_flag, p.status, ST_ATTNB_PDS)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {          // reduce over the 128 query rows, 16 at a time
+          const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+          umma_f16(tmem_base + COL_DV, make_smem_desc(p_addr + kk * 2048, 16384, 1024, 2),
+                   make_smem_desc(do_addr + kk * 2048, 16384, 1024, 2), idesc_mm, acc);
+          umma_f16(tmem_base + COL_DK, make_smem_desc(ds_addr + kk * 2048, 16384, 1024, 2),
+                   make_smem_desc(q_addr + kk * 2048, 16384, 1024, 2), idesc_mm, acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {          // dQ = dS K: reduce over the 128 key rows
+          const int half = kk >> 2, k4 = kk & 3;
+          umma_f16(tmem_base, make_smem_desc(ds_addr + half * 16384 + k4 * 32, 16, 1024, 2),
+                   make_smem_desc(k_addr + kk * 2048, 16384, 1024, 2), idesc_km, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(qdo_empty);                            // Q / dO (and P / dS) may be overwritten
+        umma_commit(mma2_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / dS / drains (warps 2..5)
+    const int lg = warp & 3;
+    const int r = lg * 32 + lane;                          // query row inside the tile; key row for the final drain
+    const uint32_t lane_addr = tmem_base + (uint32_t(lg * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = hk * G + it / per_head;
+      const int i = i_lo + it % per_head;
+      const int q_idx = i * AT_BM + r;
+      const uint32_t ph = it & 1;
+      const size_t stat = ((size_t)b * p.Hq + h) * p.S + q_idx;
+      const float lse2 = p.lse[stat] * 1.4426950408889634f;
+      const float delta = p.delta[stat];
+      const bool masked_tile = (i == j) || (p.window > 0);
+      const int k_last = q_idx - kv0;
+      const int k_first = p.window > 0 ? q_idx - p.window + 1 - kv0 : -1;
+      if (!mbar_wait(sdp_full, ph, abort_flag, p.status, ST_ATTNB_SDP)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < AT_BN; c += 32) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(lane_addr + c, sv);
+        tmem_ld_32x32(lane_addr + COL_DP + c, dv);
+        tmem_ld_wait();
+        uint8_t* p_row = p_s + (c >> 6) * 16384 + r * 128;
+        uint8_t* ds_row = ds_s + (c >> 6) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float pf[8], df[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = c + g * 8 + e;
+            const bool vis = !masked_tile || (col <= k_last && col >= k_first);
+            const float pv = vis ? exp2f(__uint_as_float(sv[g * 8 + e]) * p.scale_log2 - lse2) : 0.f;
+            pf[e] = pv;
+            df[e] = pv * (__uint_as_float(dv[g * 8 + e]) - delta) * p.scale;
+          }
+          const int g64 = ((c & 32) >> 3) + g;
+          const int sw = (g64 ^ (r & 7)) << 4;
+          *reinterpret_cast<bf16x8*>(p_row + sw) = pack8(pf);
+          *reinterpret_cast<bf16x8*>(ds_row + sw) = pack8(df);
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+      // dQ of this (query tile, key tile) pair: add into the fp32 buffer other key tiles add to as well
+      if (!mbar_wait(mma2_done, ph, abort_flag, p.status, ST_ATTNB_MMA2)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((size_t)(row_base + q_idx) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_addr + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) atomicAdd(dq_row + c + e, __uint_as_float(v[e]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_drained);
+    }
+    if (ok && n_it > 0) {
+      // every MMA has completed (the last mma2_done was waited for): thread r owns key row kv0 + r of dK and dV
+      tc_fence_after();
+      const size_t out_row = ((size_t)(row_base + kv0 + r) * p.Hkv + hk) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t vv[32], kk[32];
+        tmem_ld_32x32(lane_addr + COL_DV + c, vv);
+        tmem_ld_32x32(lane_addr + COL_DK + c, kk);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float fv[8], fk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            fv[e] = __uint_as_float(vv[g * 8 + e]);
+            fk[e] = __uint_as_float(kk[g * 8 + e]);
+          }
+          *reinterpret_cast<bf16x8*>(p.dV + out_row + c + g * 8) = pack8(fv);
+          *reinterpret_cast<bf16x8*>(p.dK + out_row + c + g * 8) = pack8(fk);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*AttnEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -368,6 +658,24 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
   return static_cast<int>(cudaGetLastError());
 }
 
+
+template <int D>
+static int launch_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const AttnBwdParams& p,
+                           long q_stride, long k_stride, long v_stride, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  const uint64_t rows = (uint64_t)p.B * p.S;
+  if ((rc = attn_map(&mq, q, rows, (uint64_t)p.Hq * D, q_stride, 128))) return rc;
+  if ((rc = attn_map(&mk, k, rows, (uint64_t)p.Hkv * D, k_stride, 128))) return rc;
+  if ((rc = attn_map(&mv, v, rows, (uint64_t)p.Hkv * D, v_stride, 128))) return rc;
+  if ((rc = attn_map(&mdo, dout, rows, (uint64_t)p.Hq * D, (uint64_t)p.Hq * D, 128))) return rc;
+  const int smem = AttnBwdSmem<D>::TOTAL > 120 * 1024 ? AttnBwdSmem<D>::TOTAL : 120 * 1024;
+  SLAB_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid(p.S / AT_BN, p.Hkv, p.B);
+  attn_bwd_kernel<D><<<grid, AT_THREADS, smem, stream>>>(mq, mk, mv, mdo, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace slab
 
 // q, k, v: bf16 [B, S, heads, D] views with contiguous heads*D and the given row strides (elements between
@@ -389,4 +697,31 @@ extern "C" int slab_attn_fwd(const void* q, const void* k, const void* v, void* 
   p.status = status;
   return D == 64 ? launch_attn_fwd<64>(q, k, v, p, q_stride, k_stride, v_stride, stream)
                  : launch_attn_fwd<128>(q, k, v, p, q_stride, k_stride, v_stride, stream);
+}
+
+// Backward of the same attention.  q, k, v as in the forward; dout: [B, S, Hq, D] contiguous bf16; lse: the forward's
+// [B, Hq, S]; delta: [B, Hq, S] fp32 = rowsum(dout * out); dq_acc: [B, S, Hq, D] fp32, zeroed by the caller (key
+// tiles add into it); dk, dv: [B, S, Hkv, D] contiguous bf16.  Same limits as the forward.
+extern "C" int slab_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                             const float* delta, float* dq_acc, void* dk, void* dv, int B, int S, int Hq, int Hkv,
+                             int D, long q_stride, long k_stride, long v_stride, int window, float scale, int* status,
+                             cudaStream_t stream) {
+  using namespace slab;
+  if (B <= 0 || S <= 0 || S % AT_BM || Hq <= 0 || Hkv <= 0 || Hq % Hkv || (D != 64 && D != 128)) return -10;
+  if ((q_stride | k_stride | v_stride) & 7) return -11;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dk | (uintptr_t)dv |
+       (uintptr_t)dq_acc) & 15) return -12;
+  AttnBwdParams p;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq_acc = dq_acc;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  return D == 64 ? launch_attn_bwd<64>(q, k, v, dout, p, q_stride, k_stride, v_stride, stream)
+                 : launch_attn_bwd<128>(q, k, v, dout, p, q_stride, k_stride, v_stride, stream);
 }

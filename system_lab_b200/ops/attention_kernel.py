@@ -1,10 +1,11 @@
-"""Binding of the hand-written causal attention forward (``csrc/attention.cu``: tcgen05 Q K^T and P V with TMEM
-accumulators, online softmax in registers, GQA, sliding window, head dim 64 / 128).
+"""Binding of the hand-written causal attention kernels (``csrc/attention.cu``: tcgen05 GEMMs with TMEM accumulators,
+softmax with one row per thread, GQA, sliding window, head dim 64 / 128): the forward (online softmax, output and
+log-sum-exp) and the backward (five GEMMs per tile pair, dK / dV accumulated in TMEM, dQ through fp32 atomics).
 
-State: the kernel is compiled with the rest of the library; it is **off by default** (``set_enabled(True)`` or
-``SLAB_ATTENTION_KERNEL=1`` turns it on) because it has not yet been timed against the library's fused attention,
-which stays the default path.  The backward pass of the autograd wrapper re-runs the library's attention under
-autograd (one extra forward): the kernel covers the forward only.
+State: the kernels are compiled with the rest of the library; they are **off by default** (``set_enabled(True)`` or
+``SLAB_ATTENTION_KERNEL=1`` turns the forward on; ``SLAB_ATTENTION_KERNEL_BWD=1`` additionally routes the backward
+to the kernel) because they have not yet been timed against the library's fused attention, which stays the default
+path.  With only the forward enabled, the backward re-runs the library's attention under autograd.
 
 Reference: attention in the measured runs is a library FMHA as well (aiter / CK-tile on MI355X,
 ``notes/2026-04/2026-04-21_gptoss_13_*:19-105``; cuDNN flash attention on B200,
@@ -19,10 +20,13 @@ import torch
 from . import cuda
 
 cuda.register("slab_attn_fwd", "ppppp" + "iiiii" + "lll" + "i" + "f" + "p" + "s")
+cuda.register("slab_attn_bwd", "p" * 9 + "iiiii" + "lll" + "i" + "f" + "p" + "s")
 cuda._STATUS_NAMES.update({20: "ATTN_Q", 21: "ATTN_KV_FULL", 22: "ATTN_KV_EMPTY", 23: "ATTN_S", 24: "ATTN_P",
-                           25: "ATTN_PV"})
+                           25: "ATTN_PV", 30: "ATTNB_KV", 31: "ATTNB_QDO_FULL", 32: "ATTNB_QDO_EMPTY", 33: "ATTNB_SDP",
+                           34: "ATTNB_PDS", 35: "ATTNB_MMA2", 36: "ATTNB_DQ"})
 
 _ENABLED = [os.environ.get("SLAB_ATTENTION_KERNEL", "0") == "1" or os.environ.get("SLAB_EXPERIMENTAL") == "1"]
+_ENABLED_BWD = [os.environ.get("SLAB_ATTENTION_KERNEL_BWD", "0") == "1"]
 
 
 def set_enabled(on: bool) -> None:
@@ -78,16 +82,39 @@ def forward(q, k, v, scale: float, window: int = 0):
     return out, lse
 
 
+def backward(q, k, v, out, lse, dout, scale: float, window: int = 0):
+    """``(dq, dk, dv)`` from the forward's inputs, output and log-sum-exp.  ``delta = rowsum(dout * out)`` and the
+    final cast of dq are library elementwise ops; the five GEMMs per tile pair run in the kernel."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    dout = dout.contiguous()
+    delta = (dout.float() * out.float()).sum(-1).transpose(1, 2).contiguous()          # [B, Hq, S]
+    dq_acc = torch.zeros((b, s, hq, d), dtype=torch.float32, device=q.device)
+    dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device)
+    cuda.call("slab_attn_bwd", q, k, v, dout, lse, delta, dq_acc, dk, dv, b, s, hq, hkv, d, _row_stride(q),
+              _row_stride(k), _row_stride(v), int(window), float(scale), cuda.status_word(q.device), cuda.stream())
+    return dq_acc.to(torch.bfloat16), dk, dv
+
+
 class _KernelAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, window):
-        out, _ = forward(q, k, v, scale, window)
-        ctx.save_for_backward(q, k, v)
+        out, lse = forward(q, k, v, scale, window)
+        ctx.kernel_bwd = _ENABLED_BWD[0]
+        if ctx.kernel_bwd:
+            ctx.save_for_backward(q, k, v, out, lse)
+        else:
+            ctx.save_for_backward(q, k, v)
         ctx.scale, ctx.window = scale, window
         return out
 
     @staticmethod
     def backward(ctx, g):
+        if ctx.kernel_bwd:
+            q, k, v, out, lse = ctx.saved_tensors
+            dq, dk, dv = backward(q, k, v, out, lse, g, ctx.scale, ctx.window)
+            return dq, dk, dv, None, None
         from .attention import _library
         q, k, v = (t.detach().requires_grad_(True) for t in ctx.saved_tensors)
         with torch.enable_grad():

@@ -178,3 +178,15 @@ def test_poison_fill_debug_mode_walks_the_host_path(dry, monkeypatch):
     assert d.poison
     tr.train_step()
     assert torch.isnan(d.scalars[0]).all() and (d.comb.view(torch.int16) == -1).all()
+
+
+def test_attention_backward_binding_argument_list(dry, monkeypatch):
+    from system_lab_b200.ops import attention_kernel as ak, cuda as cops
+    monkeypatch.setattr(cops, "status_word", lambda dev: torch.zeros(1, dtype=torch.int32))
+    monkeypatch.setattr(ak, "_ENABLED_BWD", [True])
+    b, s, hq, hkv, d = 1, 128, 4, 2, 64
+    qkv = torch.randn(b, s, (hq + 2 * hkv) * d, dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k, v = q.unflatten(-1, (hq, d)), k.unflatten(-1, (hkv, d)), v.unflatten(-1, (hkv, d))
+    ak.attention(q, k, v, 0.125, 0).sum().backward()
+    assert dry[-2:] == ["slab_attn_fwd", "slab_attn_bwd"] and qkv.grad.shape == qkv.shape
