@@ -4,7 +4,8 @@
         [--iters 10] [--json out.json]
 
 Times the library path of ``ops/attention.py`` (cuDNN SDPA / flash-attn) and, when the hand-written forward is
-switched on (``SLAB_ATTENTION_KERNEL=1``), ``csrc/attention.cu`` on the same packed-qkv inputs, checks the two outputs
+switched on (``SLAB_ATTENTION_KERNEL=1``; ``SLAB_ATTENTION_KERNEL_BWD=1`` adds its backward), ``csrc/attention.cu`` on the
+same packed-qkv inputs, checks the two outputs
 against each other, and reports TFLOP/s (causal: half of the dense FLOPs; a window counts only the visible keys)
 against the measured bf16 GEMM peak.  CUDA events, 3 warm-ups, median, 256 MB write between iterations (cold L2).
 
@@ -100,6 +101,17 @@ def main(argv=None) -> int:
         line("kernel forward (csrc/attention.cu)", time_cuda(lambda: ak.forward(q, k, v, scale, a.window), flush, a.iters),
              flops_fwd)
         cops.check_status()
+        if ak._ENABLED_BWD[0]:
+            dq, dk, dv = ak.backward(q, k, v, out, lse, g, scale, a.window)
+            torch.cuda.synchronize()
+            cops.check_status()
+            fwd_bwd()
+            errs = [(x.float() - y.float()).abs().max().item() for x, y in ((dq, qg.grad), (dk, kg.grad), (dv, vg.grad))]
+            print(f"kernel vs library gradients: max abs difference dq {errs[0]:.4f} dk {errs[1]:.4f} dv {errs[2]:.4f}")
+            res["grad_max_abs_diff"] = errs
+            line("kernel backward (csrc/attention.cu)",
+                 time_cuda(lambda: ak.backward(q, k, v, out, lse, g, scale, a.window), flush, a.iters), 2.5 * flops_fwd)
+            cops.check_status()
     else:
         print("kernel forward: skipped (set SLAB_ATTENTION_KERNEL=1; needs head dim 64 / 128 and seq % 128 == 0)")
     if a.json:

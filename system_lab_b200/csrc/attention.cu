@@ -1,5 +1,6 @@
-// Causal attention forward for sm_100a: S = Q K^T and O = P V on tcgen05 with TMEM accumulators, operands staged by
-// TMA (no cluster multicast), online softmax in registers.  GQA, optional sliding window, head dim 64 or 128.
+// Causal attention for sm_100a, forward and (further down) backward.
+// Forward: S = Q K^T and O = P V on tcgen05 with TMEM accumulators, operands staged by TMA (no cluster multicast),
+// online softmax in registers.  GQA, optional sliding window, head dim 64 or 128.
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key/value tiles its rows may see.  Roles
 // (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation), warps 2..5 = softmax (thread
