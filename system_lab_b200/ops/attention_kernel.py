@@ -25,7 +25,7 @@ cuda._STATUS_NAMES.update({20: "ATTN_Q", 21: "ATTN_KV_FULL", 22: "ATTN_KV_EMPTY"
                            25: "ATTN_PV", 30: "ATTNB_KV", 31: "ATTNB_QDO_FULL", 32: "ATTNB_QDO_EMPTY", 33: "ATTNB_SDP",
                            34: "ATTNB_PDS", 35: "ATTNB_MMA2", 36: "ATTNB_DQ"})
 
-_ENABLED = [os.environ.get("SLAB_ATTENTION_KERNEL", "0") == "1" or os.environ.get("SLAB_EXPERIMENTAL") == "1"]
+_ENABLED = [os.environ.get("SLAB_ATTENTION_KERNEL", "0") == "1"]
 _ENABLED_BWD = [os.environ.get("SLAB_ATTENTION_KERNEL_BWD", "0") == "1"]
 
 

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("SLAB_ATTENTION_KERNEL") != "1" and os.environ.get("SLAB_EXPERIMENTAL") != "1",
+              pytest.mark.skipif(os.environ.get("SLAB_ATTENTION_KERNEL") != "1",
                                  reason="attention kernel is opt-in: set SLAB_ATTENTION_KERNEL=1")]
 
 
