@@ -83,9 +83,11 @@ def decompose(cfg: Any, world: int, sample: VramSample | None = None, trainable_
               mode: str | None = None) -> Buckets:
     """Bucket table for ``cfg`` on ``world`` GPUs; reconciled against ``sample.pmax_gb`` when given."""
     from ..pilot.constraints import estimate_memory, param_counts
+    pc = param_counts(cfg.model)
+    if trainable_fraction >= 1.0 and pc.get("lora"):
+        trainable_fraction = pc["trainable"] / max(pc["total"], 1)      # LoRA: only the adapters train
     mode = mode or pick_mode(cfg, trainable_fraction)
     est = estimate_memory(cfg, world)
-    pc = param_counts(cfg.model)
     pr, par = cfg.precision, cfg.parallel
     pp = max(par.pipeline_model_parallel_size, 1)
     dp = max(world // (pp * max(par.context_parallel_size, 1)), 1)

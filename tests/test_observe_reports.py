@@ -112,3 +112,12 @@ def test_metrics_file_gets_one_json_line_per_logged_step(tmp_path):
     recs = [json.loads(l) for l in path.read_text().splitlines()]
     assert [r["step"] for r in recs] == [2, 4]
     assert all(r["loss"] > 0 and r["tokens_per_s"] > 0 and r["ep_rank_load_max_over_mean"] >= 1.0 for r in recs)
+
+
+def test_vram_buckets_pick_the_adapter_mode_for_lora():
+    from system_lab_b200.config import Config
+    from system_lab_b200.observe.vram import decompose
+    b = decompose(Config.load(preset="llama2-70b-lora"), 8)
+    assert b.mode == "A"
+    rows = {r["bucket"]: r["gb"] for r in b.rows}
+    assert 15 < rows["Weights (frozen base)"] < 20 and rows["Adapter grads + Adam state"] < 1.0
