@@ -139,6 +139,42 @@ def fsdp_comm_equivalence(rank, world):
     return out
 
 
+def layout_equivalence(rank, world):
+    """The same tiny bf16 model under expert parallel only, under tensor parallel 2 and (4+ GPUs) hybrid sharding."""
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    import torch.distributed as dist
+    out = {}
+    variants = [("ep", []), ("tp2", ["tensor_model_parallel_size=2"])]
+    if world >= 4:
+        variants.append(("hsdp2", ["num_distributed_optimizer_instances=2", "expert_model_parallel_size=2"]))
+    for name, extra in variants:
+        cfg = Config.load(preset="qwen3-30b-a3b", overrides=[
+            "num_layers=2", "num_experts=16", "seq_length=512", "vocab_size=4096", "micro_batch_size=2",
+            f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}", "recompute_granularity=selective",
+            "device=cuda", "moe_token_dispatcher_type=alltoall", "fsdp_fused_collectives=false"] + extra)
+        # every variant builds its own process groups on the job's default group
+        tr = Trainer(cfg)
+        out[name] = [float(tr.train_step()["loss"]) for _ in range(3)]
+        torch.cuda.synchronize()
+        cops.check_status()
+        tr.close()
+        del tr
+        dist.barrier()
+    return out
+
+
+@pytest.mark.skipif(os.environ.get("SLAB_EXPERIMENTAL") != "1",
+                    reason="layouts verified on CPU ranks only so far: set SLAB_EXPERIMENTAL=1 for their first GPU run")
+def test_tensor_parallel_and_hybrid_sharding_match_expert_parallel():
+    world = min(torch.cuda.device_count(), 4)
+    for r in _run("layout_equivalence", world):
+        assert r["tp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
+        if "hsdp2" in r:
+            assert r["hsdp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
+
+
 def test_fsdp_peer_collectives_match_nccl():
     world = min(torch.cuda.device_count(), 4)
     for r in _run("fsdp_comm_equivalence", world):
