@@ -21,6 +21,7 @@
 // alternate layers, notes/2026-04/2026-04-21_gptoss_13_*:19-105; cuDNN flash attention in the B200 trace,
 // docs/b200-vs-mi355x-ep8-gbs16-trace.html:433).
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace slab {
 
@@ -605,41 +606,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
-// ---------------------------------------------------------------- host side
-typedef CUresult (*AttnEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static AttnEncodeFn attn_encode() {
-  static AttnEncodeFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<AttnEncodeFn>(ptr);
-  }
-  return fn;
-}
-
+// ---------------------------------------------------------------- host side (tensor maps: tma_host.cuh)
 // bf16 view [rows, cols] whose rows are `row_stride` elements apart (a column slice of a packed qkv tensor).
 static int attn_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                     uint32_t box_rows) {
-  AttnEncodeFn enc = attn_encode();
-  if (!enc) return -1;
-  static thread_local bool ctx_ready = false;
-  if (!ctx_ready) {
-    cudaFree(0);
-    ctx_ready = true;
-  }
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {row_stride * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
+  return tma_make_map_2d(m, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols, row_stride, box_rows, 64);
 }
 
 template <int D>

@@ -13,9 +13,6 @@
 
 namespace slab {
 
-constexpr int NORM_THREADS = 256;
-constexpr int NORM_MAXV_LIMIT = 8;   // vec8 chunks per thread: H <= 256*8*8 = 16384
-
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -31,127 +28,260 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[0];
 }
 
-// y = (x [+ res]) * rstd * w ; optionally writes xpr = x + res and rstd.  One block per row (grid-stride).
-template <bool RESIDUAL, int NORM_MAXV>
-__global__ void __launch_bounds__(NORM_THREADS)
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_WARPS = NORM_THREADS / 32;
+constexpr int NORM_MAX_H = 16384;            // 8 warps x 32 lanes x 8 chunks x 8 elements
+constexpr int NORM_GROUP = 8;                // blocks per first-level group of the gain-gradient reduction
+constexpr int NORM_MAX_GRID = 296;           // two resident blocks on each of 148 SMs
+constexpr int NORM_MAX_GROUPS = (NORM_MAX_GRID + NORM_GROUP - 1) / NORM_GROUP;
+constexpr int NORM_COUNTERS = NORM_MAX_GROUPS + 1;   // one ticket counter per group + one for the groups
+
+// Thread mapping shared by the forward and the backward: RW warps cooperate on one row (RW in {1, 2, 4, 8}), so a
+// 256-thread block works on RPB = 8 / RW rows at a time; thread `li` of a row (0 .. 32 * RW) owns the 16-byte
+// chunks li, li + 32 * RW, ... (CH of them).  A whole row is in flight per warp group, so the row sums need one
+// warp shuffle reduction plus, for RW > 1, one exchange through shared memory (double buffered by iteration
+// parity: one __syncthreads per row).
+__device__ __forceinline__ float row_sum(float v, float (*red)[NORM_WARPS], int it, int warp, int rw, int rg) {
+  v = warp_sum(v);
+  if (rw == 1) return v;
+  if ((threadIdx.x & 31) == 0) red[it & 1][warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int k = 0; k < rw; ++k) t += red[it & 1][rg * rw + k];
+  return t;
+}
+
+// y = (x [+ res]) * rstd * w ; optionally writes xpr = x + res and rstd.
+template <bool RESIDUAL, int RW, int CH>
+__global__ void __launch_bounds__(NORM_THREADS, CH <= 4 ? 2 : 1)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ xpr, float* __restrict__ rstd_out, int rows, int H, float eps) {
-  __shared__ float red[32];
+  __shared__ float red[2][NORM_WARPS];
+  constexpr int RPB = NORM_WARPS / RW;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rg = warp / RW;
+  const int li = (warp % RW) * 32 + lane;
   const int nvec = H >> 3;
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * H);
-    const bf16x8* rr = RESIDUAL ? reinterpret_cast<const bf16x8*>(res + (size_t)r * H) : nullptr;
-    float vals[NORM_MAXV][8];
+  bf16x8 wv[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = li + i * 32 * RW;
+    if (c < nvec) wv[i] = reinterpret_cast<const bf16x8*>(w)[c];
+  }
+  int it = 0;
+  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += (long)gridDim.x * RPB, ++it) {
+    const long r = r0 + rg;
+    const bool active = r < rows;
+    float vals[CH][8];
     float ss = 0.f;
+    if (active) {
+      const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * H);
+      const bf16x8* rr = RESIDUAL ? reinterpret_cast<const bf16x8*>(res + (size_t)r * H) : nullptr;
+      bf16x8 xv[CH], rv[CH];
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        unpack8(xr[c], vals[i]);
-        if (RESIDUAL) {
-          float rv[8];
-          unpack8(rr[c], rv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] += rv[j];
-          // the normalised value is computed from the fp32 sum; the stored sum is its bf16 rounding
-          reinterpret_cast<bf16x8*>(xpr + (size_t)r * H)[c] = pack8(vals[i]);
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          xv[i] = xr[c];
+          if (RESIDUAL) rv[i] = rr[c];
         }
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          unpack8(xv[i], vals[i]);
+          if (RESIDUAL) {
+            float e[8];
+            unpack8(rv[i], e);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[i][j] += e[j];
+            // the normalised value is computed from the fp32 sum; the stored sum is its bf16 rounding
+            reinterpret_cast<bf16x8*>(xpr + (size_t)r * H)[c] = pack8(vals[i]);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+        }
       }
     }
-    ss = block_sum(ss, red);
-    const float rstd = rsqrtf(ss / H + eps);
-    if (threadIdx.x == 0 && rstd_out) rstd_out[r] = rstd;
+    ss = row_sum(ss, red, it, warp, RW, rg);
+    if (active) {
+      const float rstd = rsqrtf(ss / H + eps);
+      if (li == 0 && rstd_out) rstd_out[r] = rstd;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        float wv[8], o[8];
-        unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv);
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          float wf[8], o[8];
+          unpack8(wv[i], wf);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
-        reinterpret_cast<bf16x8*>(y + (size_t)r * H)[c] = pack8(o);
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wf[j];
+          reinterpret_cast<bf16x8*>(y + (size_t)r * H)[c] = pack8(o);
+        }
       }
     }
   }
 }
 
-// dx = rstd * (g*w) - x * rstd^3 * mean(g*w*x) [+ gres] ; dw partial per block (fp32 [gridDim, H]).
-template <bool ADD_RES, int NORM_MAXV>
-__global__ void __launch_bounds__(NORM_THREADS)
+// dx = rstd * (g*w) - x * rstd^3 * mean(g*w*x) [+ gres] ;  dw = sum_r g * x * rstd, finished inside this launch:
+// every block leaves its fp32 partial in `scratch` (row blockIdx.x), the last block of each group of NORM_GROUP
+// blocks to arrive sums the group's rows into row gridDim.x + group, and the last group to arrive sums those into
+// the bf16 result -- a fixed summation order, so the result does not depend on which block arrives when.
+// `scratch`: fp32 [gridDim.x + groups, H], contents irrelevant on entry.  `counters`: int [NORM_COUNTERS], all zero
+// on entry and all zero again when the kernel ends.
+template <bool ADD_RES, int RW, int CH>
+__global__ void __launch_bounds__(NORM_THREADS, CH <= 4 ? 2 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ gres, __nv_bfloat16* __restrict__ dx,
-                   float* __restrict__ dw_partial, int rows, int H) {
-  __shared__ float red[32];
+                   float* __restrict__ scratch, int* __restrict__ counters, __nv_bfloat16* __restrict__ dw_out,
+                   int rows, int H) {
+  __shared__ float red[2][NORM_WARPS];
+  __shared__ float dw_s[RW == NORM_WARPS ? 8 : 32 * RW * CH * 8];   // block partial when several rows run side by side
+  __shared__ int last_flag;
+  constexpr int RPB = NORM_WARPS / RW;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rg = warp / RW;
+  const int li = (warp % RW) * 32 + lane;
   const int nvec = H >> 3;
-  float dw[NORM_MAXV][8];
-  float wv[NORM_MAXV][8];
+  const bf16x8* wp = reinterpret_cast<const bf16x8*>(w);   // re-read per row: a few KB that stay in L1
+  float dw[CH][8];
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
-    int c = threadIdx.x + i * NORM_THREADS;
+  for (int i = 0; i < CH; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
-    if (c < nvec) unpack8(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
   }
-  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float rstd = rstd_in[r];
-    float xv[NORM_MAXV][8], gv[NORM_MAXV][8];
-    float dot = 0.f;
+  int it = 0;
+  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += (long)gridDim.x * RPB, ++it) {
+    const long r = r0 + rg;
+    const bool active = r < rows;
+    bf16x8 xv[CH], gv[CH], ev[CH];
+    float rstd = 0.f, dot = 0.f;
+    if (active) {
+      rstd = rstd_in[r];
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        unpack8(reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c], xv[i]);
-        unpack8(reinterpret_cast<const bf16x8*>(g + (size_t)r * H)[c], gv[i]);
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c];
+          gv[i] = reinterpret_cast<const bf16x8*>(g + (size_t)r * H)[c];
+          if (ADD_RES) ev[i] = reinterpret_cast<const bf16x8*>(gres + (size_t)r * H)[c];
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          dw[i][j] += gv[i][j] * xv[i][j] * rstd;
-          gv[i][j] *= wv[i][j];
-          dot += gv[i][j] * xv[i][j];
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          float xf[8], gf[8], wf[8];
+          unpack8(xv[i], xf);
+          unpack8(gv[i], gf);
+          unpack8(wp[c], wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            dw[i][j] += gf[j] * xf[j] * rstd;
+            dot += gf[j] * wf[j] * xf[j];
+          }
         }
       }
     }
-    dot = block_sum(dot, red);
-    const float coef = dot * rstd * rstd * rstd / H;
+    dot = row_sum(dot, red, it, warp, RW, rg);
+    if (active) {
+      const float coef = dot * rstd * rstd * rstd / H;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nvec) {
-        float o[8];
+      for (int i = 0; i < CH; ++i) {
+        const int c = li + i * 32 * RW;
+        if (c < nvec) {
+          float xf[8], gf[8], wf[8], o[8];
+          unpack8(xv[i], xf);
+          unpack8(gv[i], gf);
+          unpack8(wp[c], wf);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * rstd - xv[i][j] * coef;
-        if (ADD_RES) {
-          float e[8];
-          unpack8(reinterpret_cast<const bf16x8*>(gres + (size_t)r * H)[c], e);
+          for (int j = 0; j < 8; ++j) o[j] = gf[j] * wf[j] * rstd - xf[j] * coef;
+          if (ADD_RES) {
+            float e[8];
+            unpack8(ev[i], e);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += e[j];
+            for (int j = 0; j < 8; ++j) o[j] += e[j];
+          }
+          reinterpret_cast<bf16x8*>(dx + (size_t)r * H)[c] = pack8(o);
         }
-        reinterpret_cast<bf16x8*>(dx + (size_t)r * H)[c] = pack8(o);
       }
     }
   }
+  // ---- this block's partial -> scratch row blockIdx.x
+  float* my_row = scratch + (size_t)blockIdx.x * H;
+  if (RPB == 1) {
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
-    int c = threadIdx.x + i * NORM_THREADS;
-    if (c < nvec) {
-      float* dst = dw_partial + (size_t)blockIdx.x * H + c * 8;
-      *reinterpret_cast<float4*>(dst) = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
-      *reinterpret_cast<float4*>(dst + 4) = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+    for (int i = 0; i < CH; ++i) {
+      const int c = li + i * 32 * RW;
+      if (c < nvec) {
+        *reinterpret_cast<float4*>(my_row + c * 8) = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
+        *reinterpret_cast<float4*>(my_row + c * 8 + 4) = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+      }
     }
+  } else {
+    for (int sgrp = 0; sgrp < RPB; ++sgrp) {      // the row slots add their registers in turn (fixed order)
+      __syncthreads();
+      if (rg == sgrp) {
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int c = li + i * 32 * RW;
+          if (c < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (sgrp == 0) dw_s[c * 8 + j] = dw[i][j];
+              else dw_s[c * 8 + j] += dw[i][j];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    for (int c4 = threadIdx.x; c4 < (H >> 2); c4 += NORM_THREADS)
+      reinterpret_cast<float4*>(my_row)[c4] = reinterpret_cast<const float4*>(dw_s)[c4];
   }
-}
-
-// out[p, H] = sum over partial rows; converts to bf16.
-__global__ void colsum_to_bf16_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nrows,
-                                      int H) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
-  float s = 0.f;
-  for (int r = 0; r < nrows; ++r) s += partial[(size_t)r * H + c];
-  out[c] = __float2bfloat16(s);
+  // ---- two-level reduction by the last arrivers
+  const int grid = gridDim.x;
+  const int n_groups = (grid + NORM_GROUP - 1) / NORM_GROUP;
+  const int grp = blockIdx.x / NORM_GROUP;
+  const int grp_first = grp * NORM_GROUP;
+  const int grp_size = min(NORM_GROUP, grid - grp_first);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[grp], 1) == grp_size - 1);
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  float* grp_row = scratch + (size_t)(grid + grp) * H;
+  for (int c4 = threadIdx.x; c4 < (H >> 2); c4 += NORM_THREADS) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < grp_size; ++k) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(scratch + (size_t)(grp_first + k) * H) + c4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(grp_row)[c4] = acc;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    counters[grp] = 0;                            // ready for the next launch
+    last_flag = (atomicAdd(&counters[NORM_MAX_GROUPS], 1) == n_groups - 1);
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int c4 = threadIdx.x; c4 < (H >> 2); c4 += NORM_THREADS) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < n_groups; ++k) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(scratch + (size_t)(grid + k) * H) + c4);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(dw_out + c4 * 4);
+    o[0] = __floats2bfloat162_rn(acc.x, acc.y);
+    o[1] = __floats2bfloat162_rn(acc.z, acc.w);
+  }
+  if (threadIdx.x == 0) counters[NORM_MAX_GROUPS] = 0;
 }
 
 // ------------------------------------------------------------------ SwiGLU (* probs)
@@ -523,10 +653,18 @@ adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_ra
   }
 }
 
+static inline int sm_count_cached() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
+  return sms;
+}
+
 static inline int grid_for(long work_items, int threads, int per_sm = 8) {
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count_cached();
   long blocks = (work_items + threads - 1) / threads;
   long cap = (long)sms * per_sm;
   return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
@@ -536,58 +674,100 @@ static inline int grid_for(long work_items, int threads, int per_sm = 8) {
 
 using namespace slab;
 
-template <int MAXV>
-static void launch_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xpr, float* rstd,
-                               int rows, int H, float eps, int grid, cudaStream_t st) {
-  if (res)
-    rmsnorm_fwd_kernel<true, MAXV><<<grid, NORM_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-        (__nv_bfloat16*)xpr, rstd, rows, H, eps);
-  else
-    rmsnorm_fwd_kernel<false, MAXV><<<grid, NORM_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr, rstd, rows, H, eps);
+// Warps per row and chunks per thread for a hidden size (see the thread mapping above): at most 4 chunks per
+// thread up to H = 8192, 8 beyond.
+static void norm_shape(int H, int* rw, int* ch) {
+  const int nvec = H / 8;
+  int r = 1;
+  while (r < NORM_WARPS && nvec > 32 * r * 4) r *= 2;
+  int per = (nvec + 32 * r - 1) / (32 * r);
+  int c = 1;
+  while (c < per) c *= 2;
+  *rw = r;
+  *ch = c;
 }
+
+static int norm_grid(int rows, int rw, int ch, int max_grid) {
+  const int rpb = NORM_WARPS / rw;
+  long want = ((long)rows + rpb - 1) / rpb;
+  int cap = sm_count_cached() * (ch <= 4 ? 2 : 1);
+  if (cap > NORM_MAX_GRID) cap = NORM_MAX_GRID;
+  if (cap > max_grid) cap = sm_count_cached() <= max_grid ? sm_count_cached() : max_grid;   // whole waves where possible
+  if (want < 1) want = 1;
+  return (int)(want < cap ? want : cap);
+}
+
+#define SLAB_NORM_DISPATCH(LAUNCH)                     \
+  do {                                                 \
+    if (rw == 1 && ch == 1) LAUNCH(1, 1);              \
+    else if (rw == 1 && ch == 2) LAUNCH(1, 2);         \
+    else if (rw == 1 && ch == 4) LAUNCH(1, 4);         \
+    else if (rw == 2) LAUNCH(2, 4);                    \
+    else if (rw == 4) LAUNCH(4, 4);                    \
+    else if (ch <= 4) LAUNCH(8, 4);                    \
+    else LAUNCH(8, 8);                                 \
+  } while (0)
 
 extern "C" int slab_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xpr, float* rstd,
                                 int rows, int H, float eps, cudaStream_t st) {
-  if (H % 8 || H > NORM_THREADS * NORM_MAXV_LIMIT * 8) return -100;
-  int grid = rows < 148 * 8 ? rows : 148 * 8;
-  if (grid < 1) return 0;
-  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
-  if (chunks <= 1) launch_rmsnorm_fwd<1>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
-  else if (chunks <= 2) launch_rmsnorm_fwd<2>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
-  else if (chunks <= 4) launch_rmsnorm_fwd<4>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
-  else launch_rmsnorm_fwd<8>(x, res, w, y, xpr, rstd, rows, H, eps, grid, st);
+  if (H % 8 || H > NORM_MAX_H) return -100;
+  if (rows < 1) return 0;
+  int rw, ch;
+  norm_shape(H, &rw, &ch);
+  const int grid = norm_grid(rows, rw, ch, NORM_MAX_GRID);
+#define SLAB_FWD(RW, CH)                                                                                             \
+  do {                                                                                                               \
+    if (res)                                                                                                         \
+      rmsnorm_fwd_kernel<true, RW, CH><<<grid, NORM_THREADS, 0, st>>>(                                               \
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,            \
+          (__nv_bfloat16*)xpr, rstd, rows, H, eps);                                                                  \
+    else                                                                                                             \
+      rmsnorm_fwd_kernel<false, RW, CH><<<grid, NORM_THREADS, 0, st>>>(                                              \
+          (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr, rstd, rows, H, eps); \
+  } while (0)
+  SLAB_NORM_DISPATCH(SLAB_FWD);
+#undef SLAB_FWD
   return (int)cudaGetLastError();
 }
 
-// dw_partial: fp32 [nblocks, H] scratch owned by the caller; nblocks = slab_rmsnorm_bwd_blocks(rows).
-extern "C" int slab_rmsnorm_bwd_blocks(int rows) { return rows < 148 * 2 ? (rows < 1 ? 1 : rows) : 148 * 2; }
+// Rows of fp32 [*, H] scratch and ints of zeroed counters a backward call needs, whatever its row count.
+extern "C" int slab_rmsnorm_bwd_blocks(int rows) { (void)rows; return NORM_MAX_GRID + NORM_MAX_GROUPS; }
+extern "C" int slab_rmsnorm_bwd_counters() { return NORM_COUNTERS; }
 
-template <int MAXV>
-static void launch_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, const void* gres,
-                               void* dx, float* dw_partial, int rows, int H, int grid, cudaStream_t st) {
-  if (gres)
-    rmsnorm_bwd_kernel<true, MAXV><<<grid, NORM_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)gres,
-        (__nv_bfloat16*)dx, dw_partial, rows, H);
-  else
-    rmsnorm_bwd_kernel<false, MAXV><<<grid, NORM_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, nullptr,
-        (__nv_bfloat16*)dx, dw_partial, rows, H);
+static int launch_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, const void* gres,
+                              void* dx, float* scratch, int* counters, void* dw, int rows, int H, int max_rows,
+                              cudaStream_t st) {
+  int rw, ch;
+  norm_shape(H, &rw, &ch);
+  // scratch rows in use: grid + ceil(grid / NORM_GROUP) <= max_rows
+  int max_grid = max_rows * NORM_GROUP / (NORM_GROUP + 1);
+  while (max_grid > 1 && max_grid + (max_grid + NORM_GROUP - 1) / NORM_GROUP > max_rows) --max_grid;
+  const int grid = norm_grid(rows < 1 ? 1 : rows, rw, ch, max_grid);
+#define SLAB_BWD(RW, CH)                                                                                            \
+  do {                                                                                                              \
+    if (gres)                                                                                                       \
+      rmsnorm_bwd_kernel<true, RW, CH><<<grid, NORM_THREADS, 0, st>>>(                                              \
+          (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,                          \
+          (const __nv_bfloat16*)gres, (__nv_bfloat16*)dx, scratch, counters, (__nv_bfloat16*)dw, rows, H);          \
+    else                                                                                                            \
+      rmsnorm_bwd_kernel<false, RW, CH><<<grid, NORM_THREADS, 0, st>>>(                                             \
+          (const __nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, nullptr,                 \
+          (__nv_bfloat16*)dx, scratch, counters, (__nv_bfloat16*)dw, rows, H);                                      \
+  } while (0)
+  SLAB_NORM_DISPATCH(SLAB_BWD);
+#undef SLAB_BWD
+  return (int)cudaGetLastError();
 }
 
+// dw_partial: fp32 [slab_rmsnorm_bwd_blocks(rows), H] scratch owned by the caller (contents irrelevant);
+// counters: int [slab_rmsnorm_bwd_counters()], zero before the first call (every call leaves them zero).  Calls that
+// share scratch or counters must not overlap on the GPU.  rows == 0 writes dw = 0.
 extern "C" int slab_rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, const void* gres,
-                                void* dx, float* dw_partial, void* dw, int rows, int H, cudaStream_t st) {
-  if (H % 8 || H > NORM_THREADS * NORM_MAXV_LIMIT * 8) return -100;
-  int grid = slab_rmsnorm_bwd_blocks(rows);
-  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
-  if (chunks <= 1) launch_rmsnorm_bwd<1>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
-  else if (chunks <= 2) launch_rmsnorm_bwd<2>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
-  else if (chunks <= 4) launch_rmsnorm_bwd<4>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
-  else launch_rmsnorm_bwd<8>(g, x, w, rstd, gres, dx, dw_partial, rows, H, grid, st);
-  colsum_to_bf16_kernel<<<(H + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, grid, H);
-  return (int)cudaGetLastError();
+                                void* dx, float* dw_partial, int* counters, void* dw, int rows, int H,
+                                cudaStream_t st) {
+  if (H % 8 || H > NORM_MAX_H) return -100;
+  return launch_rmsnorm_bwd(g, x, w, rstd, gres, dx, dw_partial, counters, dw, rows, H,
+                            NORM_MAX_GRID + NORM_MAX_GROUPS, st);
 }
 
 extern "C" int slab_swiglu_fwd(const void* gu, const float* probs, void* out, long rows, int F, const int* rows_dev,
@@ -687,13 +867,18 @@ extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, 
 }
 
 // ------------------------------------------------------------------ allocation-free RMSNorm backward
-// Scratch for the per-block gain-gradient partials lives in the module image (see slab_noalloc.h).
+// Scratch for the gain-gradient partials and the ticket counters of the in-kernel reduction live in the module
+// image (see slab_noalloc.h).  The counters start at zero (static storage) and every launch leaves them at zero.
+static_assert(SLAB_NOALLOC_MAX_BLOCKS >= 148 + (148 + NORM_GROUP - 1) / NORM_GROUP,
+              "the built-in scratch must hold one partial row per SM plus the group rows");
 static __device__ __align__(256) float g_noalloc_dw_partial[SLAB_NOALLOC_MAX_BLOCKS * SLAB_NOALLOC_MAX_H];
+static __device__ __align__(256) int g_noalloc_counters[NORM_COUNTERS];
 
-// In host code `g_noalloc_dw_partial` is only a handle for the symbol, never a device address: the address
-// is looked up once per device and cached here.
+// In host code `g_noalloc_dw_partial` / `g_noalloc_counters` are only handles for the symbols, never device
+// addresses: the addresses are looked up once per device and cached here.
 constexpr int NOALLOC_MAX_DEVICES = 64;
 static float* g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+static int* g_noalloc_counter_addr[NOALLOC_MAX_DEVICES] = {nullptr};
 
 extern "C" int slab_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd,
                                         const void* gres, void* dx, void* dw, int rows, int H, cudaStream_t st) {
@@ -708,20 +893,16 @@ extern "C" int slab_rmsnorm_bwd_noalloc(const void* g, const void* x, const void
   int dev = 0;
   SLAB_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SLAB_NOALLOC_ERR_DEVICE;
-  if (g_noalloc_scratch_addr[dev] == nullptr) {
-    // first call on this device (it is the current one): resolve the symbol's device address
+  if (g_noalloc_scratch_addr[dev] == nullptr || g_noalloc_counter_addr[dev] == nullptr) {
+    // first call on this device (it is the current one): resolve the symbols' device addresses
     float* addr = nullptr;
+    int* caddr = nullptr;
     SLAB_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_noalloc_dw_partial));
+    SLAB_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&caddr), g_noalloc_counters));
+    g_noalloc_counter_addr[dev] = caddr;
     g_noalloc_scratch_addr[dev] = addr;
   }
-  float* scratch = g_noalloc_scratch_addr[dev];
-  if (rows <= 0) return 0;
-  const int grid = slab_rmsnorm_bwd_blocks(rows);          // <= SLAB_NOALLOC_MAX_BLOCKS
-  const int chunks = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
-  // the partial rows are `H` floats apart; every block writes its whole row before the column sum reads it
-  if (chunks <= 1) launch_rmsnorm_bwd<1>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
-  else if (chunks <= 2) launch_rmsnorm_bwd<2>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
-  else launch_rmsnorm_bwd<4>(g, x, w, rstd, gres, dx, scratch, rows, H, grid, st);
-  colsum_to_bf16_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, grid, H);
-  return (int)cudaGetLastError();
+  // rows <= 0: one block runs, finds no rows and writes dw = 0, exactly as slab_rmsnorm_bwd does
+  return launch_rmsnorm_bwd(g, x, w, rstd, gres, dx, g_noalloc_scratch_addr[dev], g_noalloc_counter_addr[dev], dw,
+                            rows < 0 ? 0 : rows, H, SLAB_NOALLOC_MAX_BLOCKS, st);
 }

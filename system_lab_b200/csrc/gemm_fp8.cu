@@ -13,6 +13,7 @@
 // summary/fp8_expert_gemm_optimization.md:84-116) and the blockwise recipe that was the slowest variant there
 // (notes/2026-04/2026-04-21_gptoss_10_moe_fp8_grouped_gemm_diagnosis.md:74-85).
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace slab {
 
@@ -415,46 +416,7 @@ grouped_gemm_fp8_rowwise_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
 
 }  // namespace slab
 
-// ---------------------------------------------------------------- host side
-namespace slab {
-
-typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn8 f8_encode() {
-  static EncodeTiledFn8 fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn8>(p);
-  }
-  return fn;
-}
-
-// row-major [rows, cols] of `esize`-byte elements, box [box_rows, box_cols], 128-byte swizzle
-static int f8_make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esize, uint64_t rows,
-                       uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
-  EncodeTiledFn8 enc = f8_encode();
-  if (!enc) return -1;
-  static thread_local bool ctx_ready = false;
-  if (!ctx_ready) {
-    cudaFree(0);
-    ctx_ready = true;
-  }
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * (uint64_t)esize};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
-}
-
-}  // namespace slab
-
+// ---------------------------------------------------------------- host side (tensor maps: tma_host.cuh)
 // Forward only.  Requires K % 128 == 0, N % 128 == 0, E <= 512; expert segments start on multiples of 128 rows.
 extern "C" int slab_grouped_gemm_fp8(const void* A, const float* sa, const void* B, const float* sb, void* C,
                                      const int* seg_offsets, const int* seg_counts, int E, int R, int N, int K,
@@ -464,9 +426,9 @@ extern "C" int slab_grouped_gemm_fp8(const void* A, const float* sa, const void*
   Fp8Params p{seg_offsets, seg_counts, sa, sb, E, R, N, K, status};
   CUtensorMap ma, mb, mc;
   int rc;
-  if ((rc = f8_make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, R, K, F8_BM, F8_BK))) return rc;
-  if ((rc = f8_make_map(&mb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K, F8_BN, F8_BK))) return rc;
-  if ((rc = f8_make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, F8_BM, 64))) return rc;
+  if ((rc = tma_make_map_2d(&ma, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, R, K, K, F8_BM, F8_BK))) return rc;
+  if ((rc = tma_make_map_2d(&mb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K, K, F8_BN, F8_BK))) return rc;
+  if ((rc = tma_make_map_2d(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, N, F8_BM, 64))) return rc;
   static bool attr_set = false;
   if (!attr_set) {
     SLAB_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM));
@@ -489,9 +451,9 @@ extern "C" int slab_grouped_gemm_fp8_rowwise(const void* A, const float* sa, con
   R8Params p{seg_offsets, seg_counts, sa, sb, E, R, N, K, status};
   CUtensorMap ma, mb, mc;
   int rc;
-  if ((rc = f8_make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, R, K, R8_BM, R8_BK))) return rc;
-  if ((rc = f8_make_map(&mb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K, R8_BN, R8_BK))) return rc;
-  if ((rc = f8_make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, R8_BM, 64))) return rc;
+  if ((rc = tma_make_map_2d(&ma, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, R, K, K, R8_BM, R8_BK))) return rc;
+  if ((rc = tma_make_map_2d(&mb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)E * N, K, K, R8_BN, R8_BK))) return rc;
+  if ((rc = tma_make_map_2d(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, N, R8_BM, 64))) return rc;
   static bool attr_set = false;
   if (!attr_set) {
     SLAB_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_rowwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -16,6 +16,7 @@
 // notes/2026-04/2026-04-10-mfma-gemm-optimization.md:35-109) and the variable-K wgrad kernel of
 // notes/2026-04/2026-04-21_gptoss_10_moe_fp8_grouped_gemm_diagnosis.md:64-85.
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace slab {
 
@@ -393,77 +394,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
 }
 
-// ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// 2-D bf16 row-major tensor [rows, cols]; box = [box_rows, box_cols]; 128-byte swizzle.
-static int make_map_bf16(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                         uint32_t box_cols) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return -1;
-  // the driver entry point needs a current context; threads that have only been handed tensors (the
-  // autograd engine's workers) may not have touched the runtime yet
-  static thread_local bool ctx_ready = false;
-  if (!ctx_ready) {
-    cudaFree(0);
-    ctx_ready = true;
-  }
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
-}
-
-static int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
-
+// ---------------------------------------------------------------- host side (tensor maps: tma_host.cuh)
 template <int MODE, int BN, bool PUSH = false>
 static int launch(const void* A, const void* B, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   CUtensorMap ma, mb;
   int rc;
   if (MODE == MODE_FWD) {
-    if ((rc = make_map_bf16(&ma, A, p.R, p.K, BM, BK))) return rc;
-    if ((rc = make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BN, BK))) return rc;
+    if ((rc = tma_make_map_bf16(&ma, A, p.R, p.K, BM, BK))) return rc;
+    if ((rc = tma_make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BN, BK))) return rc;
   } else if (MODE == MODE_DGRAD) {
-    if ((rc = make_map_bf16(&ma, A, p.R, p.N, BM, BK))) return rc;
-    if ((rc = make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BK, 64))) return rc;
+    if ((rc = tma_make_map_bf16(&ma, A, p.R, p.N, BM, BK))) return rc;
+    if ((rc = tma_make_map_bf16(&mb, B, (uint64_t)p.E * p.N, p.K, BK, 64))) return rc;
   } else {
-    if ((rc = make_map_bf16(&ma, A, p.R, p.N, BK, 64))) return rc;
-    if ((rc = make_map_bf16(&mb, B, p.R, p.K, BK, 64))) return rc;
+    if ((rc = tma_make_map_bf16(&ma, A, p.R, p.N, BK, 64))) return rc;
+    if ((rc = tma_make_map_bf16(&mb, B, p.R, p.K, BK, 64))) return rc;
   }
   CUtensorMap mc;
   if (PUSH) {
     mc = ma;                                  // the push epilogue stores with plain peer writes: no output map
   } else if (MODE == MODE_WGRAD) {
-    if ((rc = make_map_bf16(&mc, p.C, (uint64_t)p.E * p.N, p.K, BM, 64))) return rc;
+    if ((rc = tma_make_map_bf16(&mc, p.C, (uint64_t)p.E * p.N, p.K, BM, 64))) return rc;
   } else {
-    if ((rc = make_map_bf16(&mc, p.C, p.R, (MODE == MODE_FWD) ? p.N : p.K, BM, 64))) return rc;
+    if ((rc = tma_make_map_bf16(&mc, p.C, p.R, (MODE == MODE_FWD) ? p.N : p.K, BM, 64))) return rc;
   }
   static bool attr_set = false;
   auto kern = grouped_gemm_kernel<MODE, BN, PUSH>;

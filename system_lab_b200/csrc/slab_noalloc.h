@@ -18,8 +18,10 @@ extern "C" {
 #endif
 
 // Largest hidden size the built-in scratch covers.  The array holds SLAB_NOALLOC_MAX_BLOCKS rows of
-// SLAB_NOALLOC_MAX_H floats (296 x 8192 x 4 bytes = 9.25 MiB); every GPU that loads the library keeps that
-// much reserved until the process exits, whether or not this entry point is ever called.
+// SLAB_NOALLOC_MAX_H floats (296 x 8192 x 4 bytes = 9.25 MiB) plus a few dozen ticket counters; every GPU that
+// loads the library keeps that much reserved until the process exits, whether or not this entry point is ever
+// called.  The kernel sizes its grid so that its partial rows (one per thread block plus one per group of eight
+// blocks) fit those SLAB_NOALLOC_MAX_BLOCKS rows; elementwise.cu checks the tie at compile time.
 #define SLAB_NOALLOC_MAX_H 8192
 #define SLAB_NOALLOC_MAX_BLOCKS 296
 
@@ -42,8 +44,10 @@ extern "C" {
 //   stream capture, and not from two threads at once for the same device.
 // * Every call on a device uses the same scratch.  Two calls whose kernels may run at the same time on one
 //   GPU (different streams, or different processes' threads sharing this library instance) race on it and
-//   give wrong dw; serialise them.  Nothing in the scratch has to start at zero -- each launch rewrites
-//   every row it later reads -- so what the previous call left behind is harmless.
+//   give wrong dw; serialise them.  The partial rows need not start at zero -- each launch rewrites every row
+//   it later reads -- so what the previous call left behind is harmless.  The ticket counters of the in-kernel
+//   reduction start at zero when the library is loaded and every completed launch leaves them at zero.
+// * rows <= 0 is valid: dx is not touched and dw is written as zeros, as slab_rmsnorm_bwd does.
 // * H above SLAB_NOALLOC_MAX_H is refused with SLAB_NOALLOC_ERR_TOO_LARGE and a line on stderr; nothing is
 //   launched in that case.
 int slab_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd, const void* gres,

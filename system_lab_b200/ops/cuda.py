@@ -20,7 +20,8 @@ _lib = None
 _SIGS = {
     "slab_rmsnorm_fwd": "ppppppiifs",
     "slab_rmsnorm_bwd_blocks": "i",
-    "slab_rmsnorm_bwd": "ppppppppiis",
+    "slab_rmsnorm_bwd": "pppppppppiis",
+    "slab_rmsnorm_bwd_counters": "",
     "slab_swiglu_fwd": "ppplips",
     "slab_swiglu_bwd": "ppppplips",
     "slab_rope": "ppppliiillfs",
@@ -77,7 +78,7 @@ def _ptr(t):
 
 
 # kernels launched per entry point (entry points not listed launch one); LAUNCHES[0] counts launches
-_KERNELS_PER_CALL = {"slab_rmsnorm_bwd": 2}
+_KERNELS_PER_CALL = {}
 LAUNCHES = [0]
 
 
@@ -127,6 +128,25 @@ def _bf16(*ts) -> bool:
 
 
 # ------------------------------------------------------------------------------ RMSNorm
+_NORM_SCRATCH = {}
+
+
+def _norm_scratch(device, h: int):
+    """Per (device, stream) scratch of the RMSNorm backward: fp32 partial rows (contents irrelevant) and the zeroed
+    ticket counters of its in-kernel reduction (every launch leaves them zero).  Calls on one stream run in order,
+    so they can share both; another stream gets its own."""
+    key = (str(device), stream())
+    ent = _NORM_SCRATCH.get(key)
+    if ent is None or ent[0].shape[1] < h:
+        nb = lib().slab_rmsnorm_bwd_blocks(0)
+        part = torch.empty(nb, max(h, 2048), dtype=torch.float32, device=device)
+        counters = ent[1] if ent is not None else torch.zeros(lib().slab_rmsnorm_bwd_counters(), dtype=torch.int32,
+                                                              device=device)
+        ent = (part, counters)
+        _NORM_SCRATCH[key] = ent
+    return ent
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps):
@@ -145,11 +165,10 @@ class _RMSNorm(torch.autograd.Function):
         x2, w, rstd = ctx.saved_tensors
         rows, h = x2.shape
         g2 = g.reshape(rows, h).contiguous()
-        nb = lib().slab_rmsnorm_bwd_blocks(rows)
-        part = torch.empty(nb, h, dtype=torch.float32, device=g.device)
+        part, counters = _norm_scratch(g.device, h)
         dx = torch.empty_like(x2)
         dw = torch.empty_like(w)
-        call("slab_rmsnorm_bwd", g2, x2, w, rstd, None, dx, part, dw, rows, h, stream())
+        call("slab_rmsnorm_bwd", g2, x2, w, rstd, None, dx, part, counters, dw, rows, h, stream())
         return dx.reshape(ctx.shp), dw, None
 
 
@@ -174,11 +193,10 @@ class _RMSNormResidual(torch.autograd.Function):
         rows, h = xpr.shape
         gy2 = gy.reshape(rows, h).contiguous()
         gx2 = gxpr.reshape(rows, h).contiguous() if gxpr is not None else None
-        nb = lib().slab_rmsnorm_bwd_blocks(rows)
-        part = torch.empty(nb, h, dtype=torch.float32, device=gy.device)
+        part, counters = _norm_scratch(gy.device, h)
         dx = torch.empty_like(xpr)
         dw = torch.empty_like(w)
-        call("slab_rmsnorm_bwd", gy2, xpr, w, rstd, gx2, dx, part, dw, rows, h, stream())
+        call("slab_rmsnorm_bwd", gy2, xpr, w, rstd, gx2, dx, part, counters, dw, rows, h, stream())
         dx = dx.reshape(ctx.shp)
         return dx, dx, dw, None          # the same tensor is the gradient of x and of the residual
 

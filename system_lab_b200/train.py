@@ -1,7 +1,8 @@
 """``python -m system_lab_b200.train --config cfg.yaml [--preset NAME] [key=value ...]``
 
 Resolution order: defaults < preset < YAML < ``key=value`` overrides; the resolved config is
-written to ``<save dir or cwd>/resolved_config.json`` before the first step.  Under ``torchrun`` each
+written to ``resolved_config.json`` in the job's own directory (the checkpoint save directory, else the directory of
+the snapshot or metrics file) before the first step; a job that names none of them writes no file.  Under ``torchrun`` each
 process drives one GPU (NCCL); without GPUs the same command runs on CPU ranks over gloo.
 """
 from __future__ import annotations
@@ -13,6 +14,16 @@ import sys
 from pathlib import Path
 
 from .config import Config
+
+
+def _job_dir(cfg) -> Path | None:
+    """Directory that belongs to this job: where it saves checkpoints, else where it writes its snapshot or metrics."""
+    if cfg.checkpoint.save:
+        return Path(cfg.checkpoint.save)
+    for f in (cfg.profile.snapshot_path, cfg.train.metrics_file):
+        if f:
+            return Path(f).parent
+    return None
 
 
 def main(argv=None) -> int:
@@ -35,8 +46,9 @@ def main(argv=None) -> int:
         for prob in check_config(cfg, tr.mesh.world):
             if prob["severity"] == "warning":
                 logging.getLogger("system_lab_b200.config").warning("%s: %s", prob["rule"], prob["message"])
-        out_dir = Path(cfg.checkpoint.save or ".")
-        cfg.dump(out_dir / "resolved_config.json")
+        out_dir = _job_dir(cfg)
+        if out_dir is not None:
+            cfg.dump(out_dir / "resolved_config.json")
     resume = args.resume or cfg.checkpoint.load
     if resume:
         tr.load_checkpoint(resume)
