@@ -57,14 +57,18 @@ struct PeerTable {
 
 // ---------------------------------------------------------------- count
 __global__ void __launch_bounds__(COUNT_THREADS)
-moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int* __restrict__ block_hist) {
+moe_count_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int* __restrict__ block_hist, int* status) {
   __shared__ int hist[MAX_EXPERTS];
   for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
   __syncthreads();
   const int base = blockIdx.x * PAIRS_PER_BLOCK;
   for (int i = threadIdx.x; i < PAIRS_PER_BLOCK; i += blockDim.x) {
     int p = base + i;
-    if (p < n_pairs) atomicAdd(&hist[topk_idx[p]], 1);
+    if (p < n_pairs) {
+      const int e = topk_idx[p];
+      if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+      else atomicCAS(status, 0, ST_BAD_INDEX);       // an id outside [0, E): reported, never used as an index
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) block_hist[blockIdx.x * E + e] = hist[e];
@@ -170,12 +174,19 @@ moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world
     __syncthreads();
     const int p = base + chunk + threadIdx.x;
     const bool valid = p < n_pairs;
-    const int e = valid ? topk_idx[p] : -1 - lane;  // distinct dummies never match
+    int e = valid ? topk_idx[p] : -1 - lane;        // distinct dummies never match
+    const bool bad = valid && (e < 0 || e >= E);    // counted by nobody (moe_count_kernel skipped it too)
+    if (bad) e = -64 - lane;
+    const bool valid_e = valid && !bad;
     const unsigned peers_mask = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(peers_mask & ((1u << lane) - 1));
-    if (valid && rank_in_warp == 0) warp_hist[warp][e] = __popc(peers_mask);
+    if (valid_e && rank_in_warp == 0) warp_hist[warp][e] = __popc(peers_mask);
     __syncthreads();
-    if (valid) {
+    if (bad) {
+      pair_loc[p] = -1;
+      atomicCAS(status, 0, ST_BAD_INDEX);
+    }
+    if (valid_e) {
       int off = run[e] + rank_in_warp;
       for (int w = 0; w < warp; ++w) off += warp_hist[w][e];
       const int row = send_base[e] + off;
@@ -461,11 +472,11 @@ extern "C" int slab_moe_count_blocks(int n_pairs) { return (n_pairs + PAIRS_PER_
 // host arrays (world pointers, 12 region offsets).
 extern "C" int slab_moe_count_publish(const int* topk_idx, int n_pairs, int E, int* block_hist, int* send_counts,
                                       const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
-                                      cudaStream_t st) {
+                                      int* status, cudaStream_t st) {
   if (E > MAX_EXPERTS || world > MAX_WORLD || E % world) return -100;
   int nb = slab_moe_count_blocks(n_pairs);
   if (nb < 1) nb = 1;
-  moe_count_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, block_hist);
+  moe_count_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, block_hist, status);
   moe_publish_kernel<<<1, 512, 0, st>>>(block_hist, nb, E, send_counts, make_peers(peer_ptrs, world),
                                         make_layout(ws_offsets), world, me, epoch);
   return (int)cudaGetLastError();

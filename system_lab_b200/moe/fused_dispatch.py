@@ -27,7 +27,7 @@ from ..ops import cuda as cops
 
 for _name, _sig in {
     "slab_moe_count_blocks": "i",
-    "slab_moe_count_publish": "piippppiiis",
+    "slab_moe_count_publish": "piippppiiips",
     "slab_moe_plan_slots": "piip" + "pp" + "iii" + "ii" + "pppppp" + "s",
     "slab_moe_scatter": "pppp" + "iii" + "pp" + "iii" + "pp" + "iii" + "p" + "i" + "s",
     "slab_moe_wait": "ppiiiips",
@@ -187,7 +187,7 @@ class FusedDispatcher:
             self.scalars[0].fill_(float("nan"))
         cops.call("slab_moe_count_publish", idx, t * k, self.E, self.block_hist, self.send_counts,
                   ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[0]), self.ep, self.me, ep,
-                  cops.stream())
+                  self.status, cops.stream())
         return idx, ep
 
     @torch.no_grad()

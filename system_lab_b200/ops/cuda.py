@@ -112,15 +112,33 @@ class DeviceHang(RuntimeError):
     """A kernel's bounded wait ran out (failure kind HANG): the kernel returned, the context is usable."""
 
 
-def check_status(device=None) -> None:
-    """Host read of the status word; raises a typed error.  Call between steps, not per kernel."""
+def peek_status(device=None) -> int:
+    """Host read of the status word(s): the first non-zero code, 0 if every kernel so far was happy."""
     for key, t in _STATUS.items():
         if device is not None and key != str(device):
             continue
         v = int(t.item())
         if v:
+            return v
+    return 0
+
+
+def status_name(code: int) -> str:
+    return str(_STATUS_NAMES.get(code, code))
+
+
+def clear_status(device=None) -> None:
+    for key, t in _STATUS.items():
+        if device is None or key == str(device):
             t.zero_()
-            raise DeviceHang(f"device kernel reported {_STATUS_NAMES.get(v, v)} on {key}")
+
+
+def check_status(device=None) -> None:
+    """Host read of the status word; raises a typed error.  Call between steps, not per kernel."""
+    v = peek_status(device)
+    if v:
+        clear_status(device)
+        raise DeviceHang(f"device kernel reported {status_name(v)} on {device if device is not None else 'a device'}")
 
 
 def _bf16(*ts) -> bool:

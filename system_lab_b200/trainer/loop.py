@@ -186,6 +186,24 @@ class Trainer:
             self.heartbeat.beat(step)
         return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
 
+    def check_device_status(self) -> None:
+        """Read the status word the kernels write when a bounded wait runs out or a bounds check fails (a lost peer
+        flag leaves zeroed combine outputs and a skipped update behind; a capacity overflow drops token-expert
+        pairs), agree on it across ranks and stop the run before the damaged state is trained on or checkpointed.
+        Call at a point where the device is idle anyway (``fit`` does, right after it has read the loss)."""
+        from ..ops import cuda as cops
+        code = cops.peek_status(self.device)
+        if dist.is_initialized() and self.mesh.world > 1:
+            t = torch.tensor([float(code)], device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)       # every rank leaves the step together
+            code = int(t.item())
+        if code:
+            cops.clear_status(self.device)
+            msg = f"step {self.step}: a device kernel reported {cops.status_name(code)}"
+            if self.heartbeat is not None:
+                self.heartbeat.fail(msg)                    # the supervisor restarts from the last good checkpoint
+            raise cops.DeviceHang(msg)
+
     def _should_leave(self, started: float, minutes: float) -> bool:
         """One small collective after a step: has rank 0's clock passed the limit, has any rank received SIGTERM?
         Every rank gets the same answer, so no rank enters the next step alone."""
@@ -311,6 +329,7 @@ class Trainer:
             out = self.train_step()
             loss = float(out["loss"])              # host read: also the step's device sync
             gn = float(out["grad_norm"])
+            self.check_device_status()             # before anything is logged, evaluated or saved from this step
             if prof:
                 prof.step_end(self.step)
             dt_ms = (time.perf_counter() - t0) * 1e3

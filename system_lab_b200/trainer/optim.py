@@ -119,7 +119,10 @@ class ShardedAdamW:
 
     # ---- update -----------------------------------------------------------------------
     def fusable(self, g) -> bool:
-        return self.state_dtype == "fp32" and g.device.type == "cuda" and g.can_fuse_rs_adamw()
+        # the fused kernel adds the undivided sum of squares to the norm accumulator: only for groups that no other
+        # rank holds a copy of (a dense group under tensor parallelism is replicated and goes the two-kernel way)
+        return (self.state_dtype == "fp32" and g.device.type == "cuda" and g.can_fuse_rs_adamw()
+                and self._replication(g) == 1)
 
     def _fused_rs_update(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor) -> None:
         """One kernel: pull every rank's gradient slice over NVLink, sum in fp32, AdamW on the master shard and

@@ -120,3 +120,19 @@ def test_lr_schedules():
     assert lr_at(50, style="constant", **kw) == 1.0
     with pytest.raises(ValueError):
         lr_at(5, style="nope", **kw)
+
+
+def test_fused_reduce_scatter_update_is_refused_for_replicated_groups():
+    """The fused reduce-scatter + AdamW kernel accumulates the undivided sum of squared gradients; a group that other
+    ranks hold copies of (dense parameters under tensor parallelism) must take the path that divides by its
+    replication, or the global norm (and the next step's clip coefficient) would count it twice."""
+    import types
+    import torch
+    from system_lab_b200.trainer.optim import ShardedAdamW
+    opt = ShardedAdamW.__new__(ShardedAdamW)
+    opt.state_dtype = "fp32"
+    g = types.SimpleNamespace(device=torch.device("cuda"), can_fuse_rs_adamw=lambda: True, replica_group=None,
+                              tp_replicas=1)
+    assert opt.fusable(g)
+    g.tp_replicas = 2
+    assert not opt.fusable(g)

@@ -210,3 +210,49 @@ def test_gemm_push_epilogue_matches_pull_combine(world, T, K, E, H, F):
     for r in range(world):
         err = (got[r].float() - want[r]).abs().max().item()
         assert err <= 2e-2 * want[r].abs().max().item() + 1e-3, f"dgrad rank {r}: {err}"
+
+
+def test_fit_raises_after_a_wait_that_ran_out():
+    """The training loop reads the status word after every step: a bounded wait that ran out between two steps (a flag
+    nothing sets, 20 ms limit; the kernel returns, nothing faults) stops ``fit`` with a typed error."""
+    import ctypes
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "params_dtype=bf16", "device=cuda", "global_batch_size=2", "micro_batch_size=2",
+        "expert_model_parallel_size=1", "moe_token_dispatcher_type=fused", "moe_pad_expert_rows_to=128",
+        "train_iters=4"])
+    tr = Trainer(cfg)
+    try:
+        tr.fit(1)
+        d = tr.engine.dispatcher
+        cops.register("slab_moe_wait_limit", "ppiiiipls")
+        cops.call("slab_moe_wait_limit", ctypes.addressof(d._peer_ptrs), ctypes.addressof(d._lay[0]), d.ep, d.me,
+                  1 << 30, 0, d.status, 20_000_000, cops.stream())
+        with pytest.raises(cops.DeviceHang, match="TIMEOUT_PEER_FLAG"):
+            tr.fit(1)
+        cops.check_status()                    # consumed
+        tr.fit(1)                              # the context and the trainer are still usable
+    finally:
+        cops.clear_status()
+        tr.close()
+
+
+def test_out_of_range_expert_id_is_reported_not_written():
+    """An expert id outside [0, E) (a corrupt expert map, logical ids passed with the wrong E) is skipped by the
+    histogram and the slot assignment, its pair gets no destination and the status word says BAD_INDEX."""
+    from system_lab_b200.ops import cuda as cops
+    ds = _make(1, 64, 2, 8, 256)
+    d = ds[0]
+    idx = torch.stack([torch.randperm(8, device="cuda")[:2] for _ in range(64)]).int()
+    idx[5, 1] = 8
+    idx[9, 0] = -3
+    plan = d.plan(idx)
+    torch.cuda.synchronize()
+    assert cops.peek_status() == 6
+    cops.clear_status()
+    loc = plan.pair_loc.cpu().view(64, 2)
+    assert loc[5, 1] == -1 and loc[9, 0] == -1
+    assert (loc.flatten() >= 0).sum() == 64 * 2 - 2
+    assert int(plan.expert_counts.sum()) == 64 * 2 - 2

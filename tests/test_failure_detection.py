@@ -96,3 +96,54 @@ def test_runner_classifies_numerical_and_crash(tmp_path):
     r3 = _runner(tmp_path / "c", "")
     snap3 = r3.wait(r3.submit(_plan(), 3), hang_timeout_s=60)
     assert snap3["status"] == "ok" and snap3["metrics"]["tps"] > 0
+
+
+def test_fit_stops_on_a_device_status_code_before_it_checkpoints(tmp_path):
+    """A kernel that gave up (bounded wait, bounds check, capacity) leaves a code in the status word; ``fit`` reads it
+    right after the step's loss and raises before the step is logged or saved."""
+    import torch
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=1", "train_iters=4",
+        f"save={tmp_path / 'ck'}", "save_interval=1"])
+    tr = Trainer(cfg)
+    tr.fit(1)                                                    # a healthy step saves its checkpoint
+    saved = sorted(p.name for p in (tmp_path / "ck").iterdir())
+    word = cops.status_word(tr.device)
+    word.fill_(5)                                                # what a timed-out peer-flag wait writes
+    try:
+        with pytest.raises(cops.DeviceHang, match="TIMEOUT_PEER_FLAG"):
+            tr.fit(1)
+        assert sorted(p.name for p in (tmp_path / "ck").iterdir()) == saved     # nothing written after the failure
+        assert int(word.item()) == 0                             # consumed: a restarted loop starts clean
+    finally:
+        word.zero_()
+        tr.close()
+
+
+def _fit_with_status_on_one_rank(rank, world):
+    import torch
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "global_batch_size=4", "micro_batch_size=2", f"expert_model_parallel_size={world}", "train_iters=3"])
+    tr = Trainer(cfg)
+    if rank == 1:
+        cops.status_word(tr.device).fill_(7)                     # only rank 1's kernels overflowed a buffer
+    try:
+        tr.fit(2)
+    except cops.DeviceHang as e:
+        return ("hang", str(e), tr.step)
+    finally:
+        cops.status_word(tr.device).zero_()
+        tr.close()
+    return ("done", "", tr.step)
+
+
+def test_every_rank_leaves_the_step_when_one_rank_reports_a_status_code():
+    res = run_ranks(_fit_with_status_on_one_rank, 2, timeout=120)
+    assert [r[0] for r in res] == ["hang", "hang"]
+    assert all("CAPACITY" in r[1] and r[2] == 1 for r in res)
