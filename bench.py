@@ -101,26 +101,36 @@ class ClockSampler:
 def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = False) -> dict:
     """Highest-fidelity optimizer/weight layout that fits 92 % of 180 GB per GPU."""
     from system_lab_b200.pilot.constraints import estimate_memory
+    # With one micro-batch per step the update runs inside backward in every plan: a layer's reduce-scatter is fused
+    # with its AdamW step (dense groups, fp32 masters) or its AdamW runs on a side stream beside the next layer's
+    # backward (expert groups), and no gradient buffer outlives its layer.  Several micro-batches (pipeline runs)
+    # accumulate gradients and update after the last one.
+    one_mb = cfg.train.global_batch_size == cfg.train.micro_batch_size * max(
+        world // (cfg.parallel.pipeline_model_parallel_size * cfg.parallel.tensor_model_parallel_size
+                  * cfg.parallel.context_parallel_size), 1)
     plans = [
-        ("fp32-master+fp32-moments", dict(master_weights=True, optimizer_state_dtype="fp32"), False),
-        ("fp32-master+bf16-moments", dict(master_weights=True, optimizer_state_dtype="bf16"), False),
-        ("bf16-weights+bf16-moments", dict(master_weights=False, optimizer_state_dtype="bf16"), False),
-        ("bf16-weights+bf16-moments+optimizer-in-backward", dict(master_weights=False, optimizer_state_dtype="bf16"), True),
-        ("bf16-weights+8bit-moments+optimizer-in-backward", dict(master_weights=False, optimizer_state_dtype="fp8"), True),
+        ("fp32-master+fp32-moments", dict(master_weights=True, optimizer_state_dtype="fp32"), one_mb),
+        ("fp32-master+bf16-moments", dict(master_weights=True, optimizer_state_dtype="bf16"), one_mb),
+        ("bf16-weights+bf16-moments", dict(master_weights=False, optimizer_state_dtype="bf16"), one_mb),
+        ("bf16-weights+8bit-moments", dict(master_weights=False, optimizer_state_dtype="fp8"), one_mb),
     ]
     last = None
-    for name, prec, in_bwd in plans:
-        if force and name != force:
-            continue
-        for k, v in prec.items():
-            setattr(cfg.precision, k, v)
-        cfg.train.optimizer_in_backward = in_bwd
-        for gran in ("selective", "full"):
+    # selective recompute (attention kept, feed-forward block re-run) with the best optimizer format that fits comes
+    # before full recompute with a better format: re-running attention costs more than the format buys
+    for gran in ("selective", "full"):
+        for name, prec, in_bwd in plans:
+            if force and name != force:
+                continue
+            for k, v in prec.items():
+                setattr(cfg.precision, k, v)
+            cfg.train.optimizer_in_backward = in_bwd
             cfg.precision.recompute_granularity = gran
             est = estimate_memory(cfg, world)
-            last = {"name": name, "recompute": gran, "est_gb": round(est["total_bytes"] / 2**30, 1),
-                    "fits": est["fits"]}
-            if est["fits"]:
+            # the estimate has been within a few GiB of the measured peaks; a plan must clear the 92 % line by 8 GiB
+            roomy = est["fits"] and est["total_bytes"] + (8 << 30) <= 0.92 * est["hbm_bytes"]
+            last = {"name": name, "optimizer_in_backward": in_bwd, "recompute": gran,
+                    "est_gb": round(est["total_bytes"] / 2**30, 1), "fits": bool(roomy)}
+            if roomy:
                 if allow_keep and gran == "selective" and cfg.model.num_experts > 0 \
                         and cfg.model.moe_keep_dispatched_factor == 0:
                     # spare memory buys speed: keep every layer's dispatched rows so the recomputed block needs

@@ -96,7 +96,7 @@ class ModelConfig:
     moe_pad_expert_rows_to: int = 128    # expert segments start on tile boundaries
     moe_router_force_load_balancing: bool = False  # benchmarking aid: route by fixed random logits
     moe_capacity_factor: float = 0.0     # fused dispatcher buffers: 0 = dropless worst case, >0 = x balanced load
-    moe_expert_relocation_interval: int = 0   # > 0: every that many steps, re-place experts on ranks by measured load
+    moe_expert_relocation_interval: int = 0   # > 0: every that many steps, re-place experts on ranks by measured load; -1: automatic (every 50 steps plus once at step 3 where the layout supports it: ep > 1, ep == dp, cp == tp == 1; off elsewhere)
     moe_expert_relocation_first_step: int = 0    # > 0: also decide once at this step (early skew of a fresh router)
     moe_expert_relocation_min_gain: float = 0.05  # relative drop of max/mean rank load that justifies moving experts
     moe_combine_push: bool = True        # expert GEMM epilogues push result rows to the token owners (fused combine)
@@ -161,6 +161,7 @@ class TrainConfig:
     eval_target_loss: float = 0.0        # > 0: training stops when the evaluation loss reaches it
     device: str = "auto"                 # auto | cpu | cuda
     use_cuda_kernels: str = "auto"       # auto | true | false : hand written sm_100a ops vs PyTorch oracle path
+    dense_gemm_kernels: bool = True      # dense projections and the vocabulary GEMMs on the hand-written tcgen05 GEMM (false: library GEMM, the comparison path)
     hang_timeout_s: float = 300.0
     heartbeat: bool = True               # ranks publish per-step heartbeats; a peer stuck for hang_timeout_s is reported
     fault_injection: str = ""            # host-side test faults, e.g. "delay:rank=1,step=3,seconds=5;nan:rank=0,step=4"

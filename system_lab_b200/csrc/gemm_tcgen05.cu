@@ -349,7 +349,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         } else if (store_thread) {
-          tma_store_2d(&tmap_c, sb, col0 + c, tile_row);
+          if (col0 + c < out_cols) tma_store_2d(&tmap_c, sb, col0 + c, tile_row);   // a chunk past the last column has nothing to store
           tma_store_commit();
         }
         ++chunk_ctr;

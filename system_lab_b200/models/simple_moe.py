@@ -121,7 +121,7 @@ class GQAttention(nn.Module):
         b, s, _ = x.shape
         if self.tp is not None:
             x = self.tp.copy_to(x)
-        qkv = F.linear(x, self.wqkv.to(x.dtype))
+        qkv = ops.linear(x, self.wqkv)
         if self.qkv_lora is not None:
             qkv = qkv + self.qkv_lora(x)
         qkv = ops.rope_packed(qkv, cos, sin, self.nq + self.nkv, self.d)      # q and k heads, one pass
@@ -135,7 +135,7 @@ class GQAttention(nn.Module):
         else:
             o = ops.causal_attention(q, k, v, None, self.window)
         o2 = o.reshape(b, s, self.nq * self.d)
-        out = F.linear(o2, self.wo.to(x.dtype))
+        out = ops.linear(o2, self.wo)
         if self.o_lora is not None:
             out = out + self.o_lora(o2)
         return self.tp.reduce_from(out) if self.tp is not None else out
@@ -180,15 +180,15 @@ class MLAttention(nn.Module):
         tp = self.tp
         link = tp.copy_to if tp is not None else (lambda t: t)     # replicated value feeding this rank's heads
         if self.q_lora:
-            q = F.linear(link(self.q_norm(F.linear(x, self.wq_a.to(dt)))), self.wq_b.to(dt))
+            q = ops.linear(link(self.q_norm(ops.linear(x, self.wq_a))), self.wq_b)
         else:
-            q = F.linear(link(x), self.wq.to(dt))
+            q = ops.linear(link(x), self.wq)
         q = q.reshape(b, s, self.nh, self.nope + self.rope_d)
         q_nope, q_rope = q.split([self.nope, self.rope_d], dim=-1)
-        kv_a = F.linear(x, self.wkv_a.to(dt))
+        kv_a = ops.linear(x, self.wkv_a)
         c_kv, k_rope = kv_a.split([self.kv_lora, self.rope_d], dim=-1)
         k_rope = link(k_rope.contiguous())
-        kv = F.linear(link(self.kv_norm(c_kv)), self.wkv_b.to(dt)).reshape(b, s, self.nh, self.nope + self.vd)
+        kv = ops.linear(link(self.kv_norm(c_kv)), self.wkv_b).reshape(b, s, self.nh, self.nope + self.vd)
         k_nope, v = kv.split([self.nope, self.vd], dim=-1)
         q_rope = ops.rope(q_rope.contiguous(), cos, sin)
         k_rope = ops.rope(k_rope.reshape(b, s, 1, self.rope_d).contiguous(), cos, sin)
@@ -199,7 +199,7 @@ class MLAttention(nn.Module):
             o = ulysses_attention(qf, kf, v.contiguous(), self.cp_group, scale=self.scale)
         else:
             o = ops.causal_attention(qf, kf, v.contiguous(), self.scale, 0)
-        out = F.linear(o.reshape(b, s, self.nh * self.vd), self.wo.to(dt))
+        out = ops.linear(o.reshape(b, s, self.nh * self.vd), self.wo)
         return tp.reduce_from(out) if tp is not None else out
 
 
@@ -222,11 +222,11 @@ class DenseFFN(nn.Module):
     def forward(self, x):
         if self.tp is not None:
             x = self.tp.copy_to(x)
-        gu = F.linear(x, self.w1.to(x.dtype))
+        gu = ops.linear(x, self.w1)
         if self.w1_lora is not None:
             gu = gu + self.w1_lora(x)
         act = ops.swiglu(gu)
-        out = F.linear(act, self.w2.to(x.dtype))
+        out = ops.linear(act, self.w2)
         if self.w2_lora is not None:
             out = out + self.w2_lora(act)
         return self.tp.reduce_from(out) if self.tp is not None else out
@@ -263,6 +263,10 @@ class MoEFFN(nn.Module):
         self.last_tokens_per_expert = None
         self.step_tokens_per_expert = None   # summed over the micro-batches of the current step
 
+    def aux_enabled(self) -> bool:
+        cfg = self.cfg
+        return cfg.moe_router_load_balancing_type == "aux_loss" and cfg.moe_aux_loss_coeff > 0 and self.training
+
     def forward(self, x):
         cfg = self.cfg
         shp = x.shape
@@ -273,15 +277,13 @@ class MoEFFN(nn.Module):
             # table of random logits instead (same table in forward and in the recomputed forward), keeping the
             # router GEMM and its gradient path in the graph.
             logits = _balance_table(logits) + (logits - logits.detach())
-        w, idx, scores = ops.router_topk(logits, cfg.moe_router_topk, cfg.moe_router_score_function,
-                                         self.router_bias, cfg.moe_norm_topk_prob,
-                                         cfg.moe_router_topk_scaling_factor)
-        if cfg.moe_router_load_balancing_type == "aux_loss" and cfg.moe_aux_loss_coeff > 0 and self.training:
-            if scores is None:          # the fused router kernel returns only the selection and its weights
-                scores = torch.softmax(logits, -1) if cfg.moe_router_score_function == "softmax" \
-                    else torch.sigmoid(logits)
-            # aux_scale: 1 / tp when the block sees a tensor-parallel slice of the tokens (the slices' terms add up)
-            self.aux = ref.aux_loss(scores, idx.long(), cfg.num_experts, cfg.moe_aux_loss_coeff * self.aux_scale)
+        # one kernel: scores, selection, gate weights, per-expert counts and the load-balancing loss
+        # (aux_scale: 1 / tp when the block sees a tensor-parallel slice of the tokens; the slices' terms add up)
+        aux_coeff = cfg.moe_aux_loss_coeff * self.aux_scale if self.aux_enabled() else 0.0
+        w, idx, aux = ops.router_fused(logits, cfg.moe_router_topk, cfg.moe_router_score_function, self.router_bias,
+                                       cfg.moe_norm_topk_prob, cfg.moe_router_topk_scaling_factor, aux_coeff)
+        if aux_coeff:
+            self.aux = aux
         d = self.dispatcher
         kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
         reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
@@ -339,6 +341,7 @@ class MoEFFN(nn.Module):
 class _Recompute(torch.autograd.Function):
     """Run ``fn(*inputs)`` without keeping its graph; rebuild and back-propagate it in backward.  Parameter
     gradients accumulate where the engine pointed them (``p.grad`` / ``main_grad`` views of the flat buffer).
+    ``fn`` may return one tensor or a tuple (the block's output and its load-balancing loss).
     A plain Function instead of ``torch.utils.checkpoint``: no per-tensor hooks on the hot path."""
 
     @staticmethod
@@ -354,7 +357,7 @@ class _Recompute(torch.autograd.Function):
             KEPT[0] = None
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, *grads):
         ins = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
         prev, RECOMPUTE_PHASE[0] = RECOMPUTE_PHASE[0], True
         KEPT[0] = ctx.kept
@@ -365,7 +368,9 @@ class _Recompute(torch.autograd.Function):
             RECOMPUTE_PHASE[0] = prev
             KEPT[0] = None
             ctx.kept = None
-        torch.autograd.backward(out, g)
+        outs = out if isinstance(out, tuple) else (out,)
+        pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and o.requires_grad]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         return (None,) + tuple(t.grad for t in ins)
 
 
@@ -405,12 +410,26 @@ class DecoderLayer(nn.Module):
             return h + out.reshape(shp)
         return h + self.ffn(y)
 
+    def _ffn_block_aux(self, y, h):
+        """The block plus the load-balancing loss its router produced, as a second output: inside a recomputed block
+        the loss cannot leave through the module attribute (the first run builds no graph), so it travels through
+        the recompute node like the block's output does."""
+        out = self._ffn_block(y, h)
+        aux, self.ffn.aux = self.ffn.aux, None
+        if aux is None:
+            aux = torch.zeros((), dtype=torch.float32, device=out.device)
+        return out, aux
+
     def forward(self, x, cos, sin):
         a = self.attn(self.attn_norm(x), cos, sin)
         y, h = ops.rmsnorm_residual(a, x, self.ffn_norm.weight, self.eps)
         if self.recompute_ffn and torch.is_grad_enabled():
             # selective recompute: attention activations are kept, the feed-forward block (for MoE layers the
             # dispatch, both grouped GEMMs and the combine) is re-run in backward
+            if self.is_moe and self.ffn.aux_enabled():
+                out, aux = _Recompute.apply(self._ffn_block_aux, y, h)
+                self.ffn.aux = aux            # picked up by the engine and added to the objective
+                return out
             return _Recompute.apply(self._ffn_block, y, h)
         return self._ffn_block(y, h)
 

@@ -26,6 +26,19 @@ def kernel_mode() -> str:
     return _MODE
 
 
+_DENSE_KERNELS = [True]
+
+
+def set_dense_kernels(on: bool) -> None:
+    """Dense projections and the vocabulary GEMMs of the fused cross entropy on the hand-written GEMM (default) or
+    on the library GEMM (the comparison path)."""
+    _DENSE_KERNELS[0] = bool(on)
+
+
+def dense_kernels() -> bool:
+    return _DENSE_KERNELS[0]
+
+
 def use_kernels(t: torch.Tensor) -> bool:
     return _MODE == "auto" and t.is_cuda
 
@@ -59,12 +72,36 @@ def swiglu_probs(gate_up, probs, rows_dev=None):
     return ref.swiglu_probs(gate_up, probs)
 
 
+def linear(x, weight):
+    """``x @ weight^T`` for a dense projection (no bias).  bf16 CUDA operands whose shapes the tile sizes cover run on
+    the hand-written tcgen05 GEMM (forward, input gradient and weight gradient); everything else is the library."""
+    if weight.dtype != x.dtype:
+        weight = weight.to(x.dtype)
+    if use_kernels(x) and _DENSE_KERNELS[0] and _cuda().linear_ok(x, weight):
+        return _cuda().linear(x, weight)
+    return torch.nn.functional.linear(x, weight)
+
+
 def router_logits(x, router_weight):
     """fp32 router logits ``x @ Wr^T``.  On the GPU the product runs on tensor cores from bf16 operands
     with fp32 accumulation and fp32 output; the oracle casts both operands to fp32 first."""
     if use_kernels(x) and x.dtype == torch.bfloat16 and router_weight.dtype == torch.bfloat16:
         return _cuda().router_logits(x, router_weight)
     return torch.nn.functional.linear(x.float(), router_weight.float())
+
+
+def router_fused(logits, topk, score_function="softmax", bias=None, norm_topk_prob=True, scaling_factor=1.0,
+                 aux_coeff=0.0):
+    """Router selection plus the Switch-style load-balancing loss ``aux_coeff * E * sum_e f_e * P_e`` (zero when
+    ``aux_coeff`` is): ``(weights [T, K] fp32, idx [T, K], aux scalar)``.  One kernel forward, one backward on the GPU."""
+    if use_kernels(logits):
+        w, idx, aux, _ = _cuda().router_fused(logits, topk, score_function, bias, norm_topk_prob, scaling_factor,
+                                              aux_coeff)
+        return w, idx, aux
+    w, idx, scores = ref.router_topk(logits, topk, score_function, bias, norm_topk_prob, scaling_factor)
+    aux = ref.aux_loss(scores, idx.long(), logits.shape[-1], aux_coeff) if aux_coeff else \
+        torch.zeros((), dtype=torch.float32, device=logits.device)
+    return w, idx, aux
 
 
 def router_topk(logits, topk, score_function="softmax", bias=None, norm_topk_prob=True, scaling_factor=1.0):

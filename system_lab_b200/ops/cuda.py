@@ -31,6 +31,8 @@ _SIGS = {
     "slab_sumsq": "pilfps",
     "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "is",
     "slab_router_topk": "ppppiiiiifs",
+    "slab_router_fused_fwd": "ppppiiiiifpfps",
+    "slab_router_fused_bwd": "pppppfpiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
     "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
     "slab_grouped_gemm_fp8": "p" * 7 + "iiiii" + "ps",
@@ -355,6 +357,51 @@ class _RouterTopK(torch.autograd.Function):
         return gl, None, None, None, None, None
 
 
+class _RouterFused(torch.autograd.Function):
+    """Score function, selection bias, top-k, gate normalisation, per-expert load counts and the load-balancing loss
+    in one launch; its backward (gate-weight path plus the dense loss term through the score function) in one more.
+    The fused router with aux score of ``notes/2026-04/2026-04-25_gptoss_22_sync_free_moe_stage_audit.md:118-127``."""
+
+    @staticmethod
+    def forward(ctx, logits, topk, score_function, bias, norm, scaling, aux_coeff):
+        t, e = logits.shape
+        lc = logits.contiguous()
+        dev = logits.device
+        w = torch.empty(t, topk, dtype=torch.float32, device=dev)
+        idx = torch.empty(t, topk, dtype=torch.int32, device=dev)
+        e2 = e + (e & 1)
+        stats = torch.zeros(e2 + 2 * e + 2, dtype=torch.int32, device=dev)   # counts | 64-bit score sums | ticket
+        aux = torch.empty(1, dtype=torch.float32, device=dev)
+        sc = 0 if score_function == "softmax" else 1
+        call("slab_router_fused_fwd", lc, bias, w, idx, t, e, topk, sc, 1 if norm else 0, float(scaling), stats,
+             float(aux_coeff), aux, stream())
+        counts = stats[:e]
+        ctx.save_for_backward(lc, idx, counts)
+        ctx.cfg = (topk, sc, norm, float(scaling), float(aux_coeff))
+        ctx.mark_non_differentiable(idx, counts)
+        return w, idx, aux.squeeze(0), counts
+
+    @staticmethod
+    def backward(ctx, gw, _gidx, g_aux, _gcounts):
+        logits, idx, counts = ctx.saved_tensors
+        topk, sc, norm, scaling, aux_coeff = ctx.cfg
+        t, e = logits.shape
+        dl = torch.empty_like(logits)
+        gw = gw.contiguous() if gw is not None else torch.zeros(t, topk, dtype=torch.float32, device=logits.device)
+        use_aux = g_aux is not None and aux_coeff != 0.0
+        ga = g_aux.float().reshape(1).contiguous() if use_aux else None
+        call("slab_router_fused_bwd", logits, idx, gw, counts if use_aux else None, ga, aux_coeff, dl, t, e, topk, sc,
+             1 if norm else 0, scaling, stream())
+        return dl, None, None, None, None, None, None
+
+
+def router_fused(logits, topk, score_function, bias, norm_topk_prob, scaling_factor, aux_coeff):
+    """``(weights [T, K] fp32, idx [T, K] int32, aux scalar, counts [E] int32)``; see :class:`_RouterFused`."""
+    return _RouterFused.apply(logits.float(), topk, score_function,
+                              bias.float().contiguous() if bias is not None else None, norm_topk_prob,
+                              scaling_factor, aux_coeff)
+
+
 class _RouterLogits(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
@@ -538,9 +585,9 @@ def _fp8_recipe(fp8) -> str:
     return fp8 if isinstance(fp8, str) else "rowwise"
 
 
-# wgrad with N % 128 == 64 (hidden 2880) writes its last row tile with guarded stores; until that path has been
-# checked on a GPU such shapes stay on the library path unless SLAB_EXPERIMENTAL=1
-_N_MULTIPLE = 64 if os.environ.get("SLAB_EXPERIMENTAL") == "1" else 128
+# the weights' N must be a multiple of 64; with N % 128 == 64 (hidden 2880, MLA's 576-wide projection) wgrad writes
+# its last row tile with guarded stores
+_N_MULTIPLE = 64
 
 
 def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, dead: bool = False):
@@ -562,6 +609,77 @@ def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, d
     return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
 
 
+# ------------------------------------------------------------------------------ dense linear on the same kernel
+_DENSE_SEG = {}
+
+
+def _dense_segments(device, rows: int):
+    """A dense GEMM is the grouped GEMM with one segment that starts at row 0: ``(offsets [1], counts [1])``."""
+    key = (str(device), rows)
+    seg = _DENSE_SEG.get(key)
+    if seg is None:
+        if len(_DENSE_SEG) > 256:
+            _DENSE_SEG.clear()
+        seg = (torch.zeros(1, dtype=torch.int32, device=device),
+               torch.full((1,), rows, dtype=torch.int32, device=device))
+        _DENSE_SEG[key] = seg
+    return seg
+
+
+class _Linear(torch.autograd.Function):
+    """``y = x @ w^T`` for the dense projections (attention qkv / output, dense and shared-expert feed-forward, MLA
+    low-rank projections) on the tcgen05 kernel of the expert GEMMs run with a single segment: forward, input
+    gradient (the weight read as an MN-major operand, no transposed copy) and weight gradient (both operands
+    MN-major), the last one written or accumulated straight into the flat gradient buffer when the parameter
+    carries ``main_grad``."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        shp = x.shape
+        n, k = w.shape
+        x2 = x.reshape(-1, k)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        off, cnt = _dense_segments(x.device, x2.shape[0])
+        # the result is allocated in its final shape (callers rotate q and k in place: it must not be a view made here)
+        out = torch.empty(*shp[:-1], n, dtype=torch.bfloat16, device=x.device)
+        grouped_gemm_raw(0, x2, w, off, cnt, n, k, out=out.view(-1, n), block_n=_pick_bn(n))
+        ctx.save_for_backward(x2, w, off, cnt)
+        ctx.w_ref = w
+        ctx.shp = shp
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x2, w, off, cnt = ctx.saved_tensors
+        n, k = w.shape
+        g2 = g.reshape(-1, n)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(ctx.shp, dtype=torch.bfloat16, device=g.device)
+            grouped_gemm_raw(1, g2, w, off, cnt, n, k, out=dx.view(-1, k), block_n=_pick_bn(k))
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                grouped_gemm_raw(2, g2, x2, off, cnt, n, k, out=mg, accumulate=ctx.w_ref.main_grad_written,
+                                 block_n=_pick_bn(k))
+                ctx.w_ref.main_grad_written = True
+            else:
+                dw = grouped_gemm_raw(2, g2, x2, off, cnt, n, k, block_n=_pick_bn(k)).view(n, k)
+        return dx, dw
+
+
+def linear_ok(x, w) -> bool:
+    return (_bf16(x, w) and w.dim() == 2 and x.shape[-1] == w.shape[1] and w.shape[1] % 64 == 0
+            and w.shape[0] % _N_MULTIPLE == 0 and x.numel() > 0 and w.is_contiguous())
+
+
+def linear(x, w):
+    return _Linear.apply(x, w)
+
+
 # ------------------------------------------------------------------------------ attention
 def causal_attention(q, k, v, scale, window):
     from .attention import causal_attention as impl
@@ -570,9 +688,10 @@ def causal_attention(q, k, v, scale, window):
 
 # ------------------------------------------------------------------------------ linear + cross entropy
 class _LinearCE(torch.autograd.Function):
-    """loss = mean CE(h @ W^T, targets), chunked over rows: logits of one chunk are produced by a
-    library GEMM, turned into their own gradient in place by one kernel, and consumed by the two
-    gradient GEMMs before the next chunk; the full [tokens, vocab] matrix never exists."""
+    """loss = mean CE(h @ W^T, targets), chunked over rows: logits of one chunk are produced by the tcgen05 GEMM
+    (one segment), turned into their own gradient in place by one kernel, and consumed by the two gradient GEMMs
+    (input gradient; weight gradient overwriting on the first chunk, accumulating on later ones) before the next
+    chunk, so at most ``chunk_rows x vocab`` logits exist at a time."""
 
     @staticmethod
     def forward(ctx, h, weight, targets, chunk_rows):
@@ -583,8 +702,21 @@ class _LinearCE(torch.autograd.Function):
         need_dw = ctx.needs_input_grad[1]            # a frozen projection (LoRA fine-tuning) needs no weight gradient
         dw = torch.zeros_like(weight) if need_dw else None
         gscale = 1.0 / n
+        from . import dense_kernels
+        own = dense_kernels() and hd % 64 == 0 and v % _N_MULTIPLE == 0
+        if own and need_dw:
+            dw = torch.empty_like(weight)            # the first chunk's wgrad overwrites, later chunks accumulate
         for lo in range(0, n, chunk_rows):
             hi = min(lo + chunk_rows, n)
+            if own:
+                off, cnt = _dense_segments(h.device, hi - lo)
+                hc = h[lo:hi]
+                logits = grouped_gemm_raw(0, hc, weight, off, cnt, v, hd, block_n=256)
+                call("slab_ce_fwd_bwd", logits, targets[lo:hi].contiguous(), loss_sum, hi - lo, v, gscale, stream())
+                grouped_gemm_raw(1, logits, weight, off, cnt, v, hd, out=dh[lo:hi], block_n=_pick_bn(hd))
+                if need_dw:
+                    grouped_gemm_raw(2, logits, hc, off, cnt, v, hd, out=dw, accumulate=lo > 0, block_n=_pick_bn(hd))
+                continue
             logits = h[lo:hi] @ weight.t()
             call("slab_ce_fwd_bwd", logits, targets[lo:hi].contiguous(), loss_sum, hi - lo, v, gscale, stream())
             torch.mm(logits, weight, out=dh[lo:hi])
@@ -599,7 +731,7 @@ class _LinearCE(torch.autograd.Function):
         return dh * g.to(dh.dtype), (dw * g.to(dw.dtype) if dw is not None else None), None, None
 
 
-def linear_cross_entropy(h, weight, targets, chunk_rows: int = 4096):
+def linear_cross_entropy(h, weight, targets, chunk_rows: int = 8192):
     if not _bf16(h, weight) or weight.shape[0] % 8:
         return ref.linear_cross_entropy(h, weight, targets)
     return _LinearCE.apply(h.contiguous(), weight.contiguous(), targets.contiguous(), chunk_rows)

@@ -120,11 +120,10 @@ class Engine:
         m = cfg.model
         self.compute_dtype = _DT[cfg.precision.params_dtype]
         gran = cfg.precision.recompute_granularity
-        aux_on = m.moe_router_load_balancing_type == "aux_loss" and m.moe_aux_loss_coeff > 0
-        # selective = keep attention activations, re-run the feed-forward block in backward.  The aux loss leaves
-        # the MoE block through a side channel a nested checkpoint cannot carry, so it falls back to full.
-        self.selective = gran == "selective" and not aux_on
-        self.recompute = gran == "full" or (gran == "selective" and aux_on)
+        # selective = keep attention activations, re-run the feed-forward block in backward (the block's
+        # load-balancing loss travels through the recompute node as a second output); full = re-run the whole layer
+        self.selective = gran == "selective"
+        self.recompute = gran == "full"
         pp = mesh.pp
         # Virtual pipeline stages: the decoder is cut into pp * vpp equal blocks, block v lives on rank v % pp as
         # that rank's chunk v // pp, so a micro-batch visits every rank vpp times (interleaved schedule).
@@ -253,7 +252,11 @@ class Engine:
             import torch.distributed as dist
             for p in unit.module.parameters():
                 # replicated parameters inside a MoE block saw only this rank's slice of the tokens
-                if getattr(p, "tp_partial_grad", False) and p.grad is not None:
+                if not getattr(p, "tp_partial_grad", False):
+                    continue
+                if getattr(p, "main_grad", None) is not None and getattr(p, "main_grad_written", False):
+                    dist.all_reduce(p.main_grad, group=self.tp.group)      # written in place by a wgrad kernel
+                if p.grad is not None:
                     dist.all_reduce(p.grad, group=self.tp.group)
         for g in unit.groups:
             if not (in_bwd and self.optimizer.fusable(g)):

@@ -53,6 +53,9 @@ class FlatGroup:
             off += _round_up(p.numel(), ALIGN)
         self.total = _round_up(max(off, ALIGN), ALIGN * self.world)
         self.shard_numel = self.total // self.world
+        # elements of the flat buffer that belong to no parameter (alignment between parameters, tail padding)
+        self.gaps = [(o + p.numel(), nxt) for p, o, nxt in zip(self.params, self.offsets, self.offsets[1:] + [self.total])
+                     if o + p.numel() < nxt]
         self.sharded = self.world > 1
         # a group of frozen parameters (LoRA fine-tuning: everything but the adapters) keeps only its compute-dtype
         # shard: no master copy, no gradient buffers, no optimizer state
@@ -186,10 +189,11 @@ class FlatGroup:
 
     # ---- gradients ----------------------------------------------------------
     def _fused_wgrad(self) -> bool:
-        """Expert groups on the kernel path: the wgrad GEMM writes straight into the flat gradient buffer."""
+        """On the kernel path the weight-gradient GEMMs (expert and dense) write straight into the flat gradient
+        buffer through ``p.main_grad``; gradients that arrive the ordinary way (norm gains, the router, anything that
+        took a library route) are copied in by ``_collect_fused_grads``."""
         from .. import ops
-        return (self.compute_dtype == torch.bfloat16 and self.device.type == "cuda" and ops.kernel_mode() == "auto"
-                and all(getattr(p, "is_expert", False) for p in self.params))
+        return self.compute_dtype == torch.bfloat16 and self.device.type == "cuda" and ops.kernel_mode() == "auto"
 
     def prepare_grads(self) -> None:
         if self.frozen:
@@ -198,6 +202,9 @@ class FlatGroup:
         if self.grad_full is None:
             alloc = torch.empty if fused else torch.zeros
             self.grad_full = alloc(self.total, dtype=self.compute_dtype, device=self.device)
+            if fused:
+                for lo, hi in self.gaps:             # nobody writes the padding; the reduction and the norm read it
+                    self.grad_full[lo:hi].zero_()
             for p in self.params:
                 p.main_grad_written = False
         for p, o, shp in zip(self.params, self.offsets, self.shapes):

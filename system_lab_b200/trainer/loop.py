@@ -66,6 +66,7 @@ class Trainer:
             ops.set_kernel_mode("reference")
         else:
             ops.set_kernel_mode("auto")
+        ops.set_dense_kernels(cfg.train.dense_gemm_kernels)
         torch.manual_seed(cfg.train.seed)
         self.engine = Engine(cfg, mesh, self.device)
         t = cfg.train
@@ -96,13 +97,16 @@ class Trainer:
         self.stopped_on_signal = False
         self.relocator = None
         self._rank_load_accum = None      # [layers, ep]: tokens each expert-parallel rank received
-        if cfg.model.moe_expert_relocation_interval > 0 and cfg.model.num_experts > 0:
+        reloc, reloc_first = cfg.model.moe_expert_relocation_interval, cfg.model.moe_expert_relocation_first_step
+        reloc_ok = mesh.edp == 1 and mesh.cp == 1 and mesh.tp == 1
+        if reloc < 0:                           # automatic: on where whole experts can move inside one group
+            reloc, reloc_first = (50, reloc_first or 3) if (reloc_ok and mesh.ep > 1) else (0, 0)
+        if reloc > 0 and cfg.model.num_experts > 0 and mesh.ep > 1:
             from ..moe.relocation import ExpertRelocator
-            if mesh.edp > 1 or mesh.cp > 1 or mesh.tp > 1:
+            if not reloc_ok:
                 raise ValueError("moe_expert_relocation_interval needs ep == dp on the stage and cp == 1")
-            self.relocator = ExpertRelocator(self.engine, self.optimizer, mesh, cfg.model.moe_expert_relocation_interval,
-                                             cfg.model.moe_expert_relocation_min_gain,
-                                             cfg.model.moe_expert_relocation_first_step)
+            self.relocator = ExpertRelocator(self.engine, self.optimizer, mesh, reloc,
+                                             cfg.model.moe_expert_relocation_min_gain, reloc_first)
         from .watchdog import FaultPlan, Heartbeat
         # a job restarted by the supervisor (launch.py) does not repeat the injected failure
         restarted = int(os.environ.get("SLAB_RESTART_COUNT", "0") or 0) > 0

@@ -52,8 +52,9 @@ def test_memory_plan_prefers_fidelity_and_fits():
         assert plan["fits"] and plan["est_gb"] < 0.92 * 180 * 1e9 / 2**30
         names[n] = plan["name"]
         assert cfg.model.moe_keep_dispatched_factor == 0          # kept dispatch is opt-in
+        assert plan["optimizer_in_backward"]                       # one micro-batch per step: update inside backward
     assert names[8] == names[4] == "fp32-master+fp32-moments"
-    assert "optimizer-in-backward" in names[1]
+    assert names[1] == "bf16-weights+8bit-moments"
 
 
 def test_moe_layer_benchmark_runs_on_cpu(tmp_path, capsys):

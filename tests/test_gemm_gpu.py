@@ -68,8 +68,6 @@ def test_wgrad(counts, n, k, bn):
     _check(acc, 2 * ref.grouped_gemm_wgrad(dy, a, off, cnt).float(), "wgrad accumulate")
 
 
-@pytest.mark.skipif(os.environ.get("SLAB_EXPERIMENTAL") != "1",
-                    reason="partial row tiles of wgrad are an opt-in path: set SLAB_EXPERIMENTAL=1")
 @pytest.mark.parametrize("counts,n,k", [([130, 250], 2880, 192), ([64, 0, 300], 192, 320)])
 @pytest.mark.parametrize("bn", [128, 256])
 def test_wgrad_partial_row_tile(counts, n, k, bn):
@@ -145,3 +143,57 @@ def test_autograd_grouped_linear_fp8_forward_bf16_backward(recipe):
     assert 1e-4 < rel < 0.06, rel                 # quantised, but within e4m3 noise of the bf16 product
     _check(a.grad, ref.grouped_gemm_dgrad(dy, w.detach(), off, cnt), "dgrad")
     _check(w.grad, ref.grouped_gemm_wgrad(dy, a.detach(), off, cnt), "wgrad")
+
+
+@pytest.mark.parametrize("lead,n,k", [((300,), 5120, 2048), ((2, 130), 1024, 512), ((4096,), 576, 7168), ((77,), 128, 64)])
+def test_dense_linear_forward_and_both_gradients(lead, n, k):
+    """``ops.linear`` = the grouped kernel with one segment: forward, input gradient and weight gradient against fp32
+    PyTorch; the result is a fresh tensor (callers modify it in place)."""
+    from system_lab_b200 import ops
+    torch.manual_seed(7)
+    x = torch.randn(*lead, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn(*lead, n, device="cuda", dtype=torch.bfloat16)
+    y = ops.linear(x, w)
+    assert y._base is None and y.shape == (*lead, n)
+    y.mul_(1.0)                                    # in-place use of the result must be legal
+    y.backward(g)
+    xf, wf, gf = x.detach().float(), w.detach().float(), g.float()
+    _check(y, xf @ wf.t(), "linear fwd")
+    _check(x.grad, gf @ wf, "linear dgrad")
+    _check(w.grad, gf.reshape(-1, n).t() @ xf.reshape(-1, k), "linear wgrad")
+
+
+def test_dense_linear_writes_and_accumulates_into_main_grad():
+    from system_lab_b200 import ops
+    torch.manual_seed(8)
+    n, k = 512, 256
+    x = torch.randn(200, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.nn.Parameter((0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16))
+    w.main_grad = torch.full((n, k), 123.0, device="cuda", dtype=torch.bfloat16)     # garbage: the first write overwrites
+    w.main_grad_written = False
+    g = torch.randn(200, n, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):                                                              # the weight is used twice
+        ops.linear(x, w).backward(g)
+    assert w.grad is None and w.main_grad_written
+    _check(w.main_grad, 2 * (g.float().t() @ x.float()), "linear wgrad into main_grad, twice")
+
+
+def test_linear_cross_entropy_on_own_gemms_matches_reference():
+    from system_lab_b200 import ops
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(9)
+    rows, hd, v = 700, 256, 1024
+    h = torch.randn(rows, hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(v, hd, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    t = torch.randint(0, v, (rows,), device="cuda")
+    from system_lab_b200.ops import cuda
+    loss = cuda._LinearCE.apply(h, w, t, 256)          # three chunks: the weight gradient overwrites, then accumulates
+    (loss * 2.0).backward()
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    lr = ref.linear_cross_entropy(hr, wr, t)
+    (lr * 2.0).backward()
+    assert abs(float(loss) - float(lr)) < 2e-2
+    _check(h.grad, hr.grad, "ce dh")
+    _check(w.grad, wr.grad, "ce dw")

@@ -106,7 +106,7 @@ MLA = ["attention_type=mla", "q_lora_rank=64", "kv_lora_rank=64", "qk_nope_head_
 @pytest.mark.parametrize("extra,kw", [
     (MLA + ["recompute_granularity=selective"], {"push": True}),
     (["sliding_window=16", "recompute_granularity=full", "num_layers=2"], {}),
-    (["moe_aux_loss_coeff=0.01", "recompute_granularity=selective"], {"push": True}),      # aux loss: falls back to full
+    (["moe_aux_loss_coeff=0.01", "recompute_granularity=selective"], {"push": True}),      # aux loss carried through the recompute node
     (["moe_router_force_load_balancing=true", "recompute_granularity=selective"], {}),
     (["moe_expert_relocation_interval=1", "moe_expert_relocation_min_gain=0.0", "recompute_granularity=selective"], {}),
     (MLA + ["recompute_granularity=selective", "moe_keep_dispatched_factor=-1"], {"push": True, "keep_factor": -1.0}),

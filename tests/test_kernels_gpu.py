@@ -112,6 +112,40 @@ def test_router_topk(cops, score, e, k, bias):
     _close(logits.grad, lr.grad, 1e-3, 1e-5)
 
 
+@pytest.mark.parametrize("score,e,k,bias,norm,coeff", [("softmax", 128, 8, False, True, 0.01),
+                                                        ("sigmoid", 256, 8, True, True, 0.05),
+                                                        ("softmax", 8, 2, False, False, 0.0),
+                                                        ("softmax", 33, 4, False, True, 0.3)])
+def test_router_fused_forward_stats_aux_and_backward(cops, score, e, k, bias, norm, coeff):
+    """One launch gives selection, gate weights, per-expert counts and the load-balancing loss; one more gives the
+    logit gradient of the gate weights and of the loss together.  Against the fp32 PyTorch formulas."""
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(5)
+    t = 517
+    logits = torch.randn(t, e, device="cuda", requires_grad=True)
+    b = 0.1 * torch.randn(e, device="cuda") if bias else None
+    w, idx, aux, counts = cops.router_fused(logits, k, score, b, norm, 2.5, coeff)
+    gw = torch.randn_like(w)
+    (w * gw).sum().add(aux * 3.0).backward()
+    lr = logits.detach().clone().requires_grad_(True)
+    wr, idxr, scores = ref.router_topk(lr, k, score, b, norm, 2.5)
+    auxr = ref.aux_loss(scores, idxr, e, coeff)
+    gw_r = torch.gather(gw, 1, _match(idx.long(), idxr))     # the same upstream gradient, expert by expert
+    ((wr * gw_r).sum() + auxr * 3.0).backward()
+    assert torch.equal(idx.long().sort(-1).values, idxr.sort(-1).values)
+    assert torch.equal(counts.long(), torch.bincount(idxr.reshape(-1), minlength=e))
+    _close(aux, auxr, 1e-4, 1e-6)
+    _close(logits.grad, lr.grad, 2e-3, 1e-5)
+    # the statistics are integer sums: a second run gives the same bits whatever the block order
+    _, _, aux2, _ = cops.router_fused(logits.detach(), k, score, b, norm, 2.5, coeff)
+    assert torch.equal(aux.detach(), aux2)
+
+
+def _match(idx, idxr):
+    """For every reference selection (row-wise), the column of the same expert in the kernel's selection."""
+    return (idxr.unsqueeze(-1) == idx.unsqueeze(1)).float().argmax(-1)
+
+
 def test_quant_roundtrip(cops):
     from system_lab_b200.ops import reference as ref
     torch.manual_seed(5)

@@ -72,3 +72,24 @@ def test_dsv3_shape_tensor_parallel_with_context_parallel():
                                             "context_parallel_size=2"], 4)
     for losses, _ in res:
         assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)
+
+
+def test_aux_loss_is_carried_through_every_recompute_mode():
+    """The load-balancing loss reaches the objective (and the router's gradient) whether the MoE block is kept,
+    recomputed alone (selective: the loss leaves the recompute node as a second output) or with its whole layer
+    (full): same loss curve, and a different one from the run without the loss term."""
+    import torch
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    base = ["global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=1", "device=cpu", "lr=1e-2"]
+
+    def run(extra):
+        torch.manual_seed(0)
+        tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=base + extra))
+        return [float(tr.train_step()["loss"]) for _ in range(5)]
+
+    plain = run(["moe_aux_loss_coeff=0.5", "recompute_granularity=none"])
+    assert run(["moe_aux_loss_coeff=0.5", "recompute_granularity=selective"]) == pytest.approx(plain, rel=2e-6, abs=2e-6)
+    assert run(["moe_aux_loss_coeff=0.5", "recompute_granularity=full"]) == pytest.approx(plain, rel=2e-6, abs=2e-6)
+    without = run(["moe_aux_loss_coeff=0.0", "recompute_granularity=selective"])
+    assert max(abs(a - b) for a, b in zip(plain[1:], without[1:])) > 1e-5      # the term moved the router
