@@ -223,7 +223,8 @@ def test_fit_raises_after_a_wait_that_ran_out():
         "params_dtype=bf16", "device=cuda", "global_batch_size=2", "micro_batch_size=2",
         "expert_model_parallel_size=1", "moe_token_dispatcher_type=fused", "moe_pad_expert_rows_to=128",
         "train_iters=4"])
-    tr = Trainer(cfg)
+    from system_lab_b200.parallel.mesh import single_process_mesh
+    tr = Trainer(cfg, mesh=single_process_mesh(), device=torch.device("cuda", 0))
     try:
         tr.fit(1)
         d = tr.engine.dispatcher
