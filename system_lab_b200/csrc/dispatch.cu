@@ -49,6 +49,7 @@ struct WsLayout {
   long origin;         // int   [cap]          (source rank << 24) | pair index of every received row; < 0: not kept
   long comb;           // bf16  [T*K][H]       pair-major rows pushed back by the owners' GEMM epilogues
   long push_flag;      // int   [world]        epoch flags: owner finished pushing its rows
+  long eflag;          // int   [world][E_local] epoch flags: source s finished writing its rows of local expert j
 };
 
 struct PeerTable {
@@ -101,14 +102,58 @@ __global__ void moe_publish_kernel(int* __restrict__ block_hist, int n_blocks, i
 
 // ---------------------------------------------------------------- plan (one block)
 // Outputs (local memory): expert_offsets[E_local], expert_counts[E_local], send_base[E], meta[0] = rows used.
+//
+// For the expert-ordered scatter it also derives, from this rank's own counts:
+//   send_prefix[e]  = pairs this rank routes to experts < e (position of expert e's run in `perm`)
+//   item_prefix[oi] = work items (chunks of SCATTER_CHUNK rows) before position oi of the send order.  The send order
+//                     walks the local expert index j outermost and the destination rank innermost, starting at the
+//                     right-hand neighbour ((me + 1 + ph) % world): every rank is writing a different peer at any
+//                     moment, and local expert j of every rank is complete after (j + 1) / E_local of the exchange.
+constexpr int SCATTER_CHUNK = 32;
+
+__device__ __forceinline__ int send_order_expert(int oi, int world, int me, int e_local) {
+  const int j = oi / world, ph = oi % world;
+  return ((me + 1 + ph) % world) * e_local + j;
+}
+
+// exclusive prefix sum over blockDim.x values (blockDim.x <= 1024); `tmp` holds 33 ints
+__device__ __forceinline__ int block_exclusive_scan(int v, int* tmp, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  __syncthreads();
+  if (lane == 31) tmp[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (int)((blockDim.x + 31) >> 5) ? tmp[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    tmp[lane] = winc - w;
+    if (lane == 31) tmp[32] = winc;
+  }
+  __syncthreads();
+  *total = tmp[32];
+  return tmp[warp] + inc - v;
+}
+
 __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me, int E, int pad, int capacity,
                                 int epoch, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
                                 int* __restrict__ send_base, int* __restrict__ meta, int* status,
-                                unsigned long long limit_ns) {
+                                unsigned long long limit_ns, const int* __restrict__ send_counts,
+                                int* __restrict__ send_prefix, int* __restrict__ item_prefix) {
   __shared__ int total[MAX_EXPERTS];      // rows of expert e over all sources
   __shared__ int before[MAX_EXPERTS];     // rows of expert e from sources < me
   __shared__ int seg_off[MAX_EXPERTS];    // aligned offset of expert e inside its owner's buffer
   __shared__ int ok;
+  __shared__ int scan_tmp[33];
   const int e_local = E / world;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
@@ -123,8 +168,22 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
       send_base[e] = -(1 << 30);
       if (e < e_local) { expert_offsets[e] = 0; expert_counts[e] = 0; }
     }
+    if (send_prefix)
+      for (int e = threadIdx.x; e <= E; e += blockDim.x) { send_prefix[e] = 0; item_prefix[e] = 0; }
     if (threadIdx.x == 0) meta[0] = 0;
     return;
+  }
+  if (send_prefix) {                      // blockDim.x >= E (512 threads, E <= 512)
+    int tot;
+    const int e = threadIdx.x;
+    const int c_nat = e < E ? send_counts[e] : 0;
+    const int pre = block_exclusive_scan(c_nat, scan_tmp, &tot);
+    if (e < E) send_prefix[e] = pre;
+    if (e == 0) send_prefix[E] = tot;
+    const int c_ord = e < E ? send_counts[send_order_expert(e, world, me, e_local)] : 0;
+    const int ipre = block_exclusive_scan((c_ord + SCATTER_CHUNK - 1) / SCATTER_CHUNK, scan_tmp, &tot);
+    if (e < E) item_prefix[e] = ipre;
+    if (e == 0) item_prefix[E] = tot;
   }
   const int* call = reinterpret_cast<const int*>(peers.base[me] + ws.counts_all);
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -162,7 +221,8 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
 // pair_loc[p] = (owner << 24) | row   (row < 2^24).  Stable: pairs of one expert keep their pair order.
 __global__ void __launch_bounds__(COUNT_THREADS)
 moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world, const int* __restrict__ block_base,
-                 const int* __restrict__ send_base, int capacity, int* __restrict__ pair_loc, int* status) {
+                 const int* __restrict__ send_base, int capacity, int* __restrict__ pair_loc, int* status,
+                 const int* __restrict__ send_prefix, int* __restrict__ perm) {
   __shared__ int run[MAX_EXPERTS];                 // pairs of e seen so far in this block
   __shared__ int warp_hist[COUNT_THREADS / 32][MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -189,6 +249,7 @@ moe_slots_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int world
     if (valid_e) {
       int off = run[e] + rank_in_warp;
       for (int w = 0; w < warp; ++w) off += warp_hist[w][e];
+      if (perm) perm[send_prefix[e] + off] = p;      // pairs grouped by expert, in pair order inside an expert
       const int row = send_base[e] + off;
       if (row >= capacity || row < 0) {
         if (row >= capacity) atomicCAS(status, 0, ST_CAPACITY);
@@ -329,6 +390,166 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 }
 
+// ---------------------------------------------------------------- scatter, expert by expert
+// Same row movement as moe_scatter_kernel, but in the send order of the plan (item_prefix): a work item is a chunk
+// of SCATTER_CHUNK consecutive rows of one destination expert, a thread block takes items in ascending order and
+// its warps copy one row each.  The block that completes the last chunk of expert e releases
+// eflag[me][local index of e] on e's owner, so the owner's expert GEMM can start on an expert as soon as every
+// source has delivered that expert's rows (reference: expert_ready[src][e] of the Layout-C receive buffer,
+// notes/2026-04/2026-04-14_data_layout_analysis.md:322-367), instead of after the whole exchange.
+// `part`: 0 = every destination, 1 = other ranks only, 2 = this rank only (the two halves can be launched
+// separately, e.g. the local half first and the remote half beside the expert GEMM).
+// `chunk_done`: int [E], zero on entry, zero again on exit.
+template <bool FP8, int VPL>
+__global__ void __launch_bounds__(256)
+moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ pair_scalar,
+                          const float* __restrict__ scale_in, const int* __restrict__ pair_loc,
+                          const int* __restrict__ perm, const int* __restrict__ send_counts,
+                          const int* __restrict__ send_prefix, const int* __restrict__ item_prefix, int T, int K,
+                          int H, int E, PeerTable peers, WsLayout ws, int world, int me, int epoch,
+                          const int* __restrict__ expert_offsets, const int* __restrict__ expert_counts, int e_local,
+                          int pad, int* __restrict__ chunk_done, int part) {
+  __shared__ int ip[MAX_EXPERTS + 1];
+  __shared__ int last_chunk;
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) ip[i] = item_prefix[i];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int gwarp = blockIdx.x * warps_per_block + warp;
+  const int n_warps = gridDim.x * warps_per_block;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  // (source, expert) pairs without rows: nothing will ever complete them, so they are released up front
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int d = e / e_local;
+      const bool mine = part == 0 || (part == 1 ? d != me : d == me);
+      if (mine && send_counts[e] == 0)
+        st_release_sys(reinterpret_cast<int*>(peers.base[d] + ws.eflag) + me * e_local + (e - d * e_local), epoch);
+    }
+  }
+  // zero this rank's own alignment padding rows (and their scalars): rows [count, roundup(count, pad))
+  if (part != 1) {
+    uint8_t* mine = peers.base[me];
+    const int row_bytes = FP8 ? H : 2 * H;
+    for (int j = 0; j < e_local; ++j) {
+      const int cnt = expert_counts[j];
+      const int first = expert_offsets[j] + cnt;
+      const int n_pad = (cnt + pad - 1) / pad * pad - cnt;
+      for (int r = gwarp; r < n_pad; r += n_warps) {
+        uint4* dst = reinterpret_cast<uint4*>(mine + ws.rows + (size_t)(first + r) * row_bytes);
+        for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+        if (FP8) {
+          float* sd = reinterpret_cast<float*>(mine + ws.row_scales) + (size_t)(first + r) * (H >> 7);
+          for (int c = lane; c < (H >> 7); c += 32) sd[c] = 0.f;
+        }
+        if (lane == 0) reinterpret_cast<float*>(mine + ws.scalars)[first + r] = 0.f;
+      }
+    }
+  }
+  __syncthreads();
+  const int total_items = ip[E];
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    int lo = 0, hi = E;                      // largest position oi with ip[oi] <= item
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (ip[mid] <= item) lo = mid; else hi = mid;
+    }
+    const int oi = lo;
+    const int e = send_order_expert(oi, world, me, e_local);
+    const int d = e / e_local;
+    if ((part == 1 && d == me) || (part == 2 && d != me)) continue;
+    const int cnt = send_counts[e];
+    const int n_chunks = (cnt + SCATTER_CHUNK - 1) / SCATTER_CHUNK;
+    const int r0 = (item - ip[oi]) * SCATTER_CHUNK;
+    const int r1 = min(cnt, r0 + SCATTER_CHUNK);
+    uint8_t* pb = peers.base[d];
+    for (int i = r0 + warp; i < r1; i += warps_per_block) {
+      const int p = perm[send_prefix[e] + i];
+      const int loc = pair_loc[p];
+      if (loc < 0 || (loc >> 24) != d) continue;         // dropped pair, or a corrupt table: never written
+      const int row = loc & 0xFFFFFF;
+      const int t = p / K;
+      const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)t * H);
+      const float sc = scale_in ? scale_in[p] : 1.f;
+      if (!FP8) {
+        bf16x8* dst = reinterpret_cast<bf16x8*>(pb + ws.rows) + (size_t)row * nvec;
+        bf16x8 regs[VPL];
+#pragma unroll
+        for (int q = 0; q < VPL; ++q) {
+          const int c = lane + 32 * q;
+          if (c < nvec) regs[q] = src[c];
+        }
+#pragma unroll
+        for (int q = 0; q < VPL; ++q) {
+          const int c = lane + 32 * q;
+          if (c < nvec) {
+            bf16x8 v = regs[q];
+            if (scale_in) {
+              float f[8];
+              unpack8(v, f);
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) f[jj] *= sc;
+              v = pack8(f);
+            }
+            dst[c] = v;
+          }
+        }
+      } else {
+        uint2* dst = reinterpret_cast<uint2*>(pb + ws.rows) + (size_t)row * nvec;
+        float* sdst = reinterpret_cast<float*>(pb + ws.row_scales) + (size_t)row * (H >> 7);
+#pragma unroll
+        for (int q = 0; q < VPL; ++q) {
+          const int c = lane + 32 * q;
+          float f[8];
+          float amax = 0.f;
+          if (c < nvec) {
+            unpack8(src[c], f);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              f[jj] *= sc;
+              amax = fmaxf(amax, fabsf(f[jj]));
+            }
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          amax = fmaxf(amax, 1e-12f);
+          if (c < nvec) {
+            const float inv = 448.f / amax;
+            __nv_fp8_e4m3 qv[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) qv[jj] = __nv_fp8_e4m3(f[jj] * inv);
+            dst[c] = *reinterpret_cast<uint2*>(qv);
+            if ((lane & 15) == 0) sdst[c >> 4] = amax / 448.f;
+          }
+        }
+      }
+      if (pair_scalar && lane == 0) reinterpret_cast<float*>(pb + ws.scalars)[row] = pair_scalar[p];
+      if (ws.origin >= 0 && lane == 0) reinterpret_cast<int*>(pb + ws.origin)[row] = (me << 24) | p;
+    }
+    // chunk complete: fence this block's peer stores, count it, and let the last chunk of the expert release the flag
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(&chunk_done[e], 1);
+      last_chunk = (done == n_chunks - 1);
+      if (last_chunk) {
+        chunk_done[e] = 0;
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(pb + ws.eflag) + me * e_local + (e - d * e_local), epoch);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Wait until every source has released every local expert (the consumer-side counterpart of the expert-ordered
+// scatter when no kernel downstream does the waiting itself).
+__global__ void moe_wait_eflags_kernel(PeerTable peers, long eflag_offset, int n_flags, int me, int epoch, int* status,
+                                       unsigned long long limit_ns) {
+  const int* flags = reinterpret_cast<const int*>(peers.base[me] + eflag_offset);
+  for (int i = threadIdx.x; i < n_flags; i += blockDim.x) wait_flag_ge(flags + i, epoch, status, limit_ns);
+}
+
 // Rows in use beyond a caller's fixed-size copy of the receive buffer are reported, never silently cut.
 __global__ void moe_check_rows_kernel(const int* __restrict__ meta, int limit, int* status, int* rows_seen) {
   if (threadIdx.x == 0) {
@@ -462,7 +683,7 @@ static WsLayout make_layout(const long* off) {
   WsLayout w;
   w.counts_all = off[0]; w.counts_flag = off[1]; w.data_flag = off[2]; w.out_flag = off[3];
   w.rows = off[4]; w.row_scales = off[5]; w.scalars = off[6]; w.out_rows = off[7]; w.out_scalars = off[8];
-  w.origin = off[9]; w.comb = off[10]; w.push_flag = off[11];
+  w.origin = off[9]; w.comb = off[10]; w.push_flag = off[11]; w.eflag = off[12];
   return w;
 }
 
@@ -483,19 +704,23 @@ extern "C" int slab_moe_count_publish(const int* topk_idx, int n_pairs, int E, i
 }
 
 // Phase 2: wait for all counts, derive segments and send bases, assign every pair its destination row.
+// `send_counts` (this rank's pairs per expert, written by phase 1), `send_prefix` / `item_prefix` (int [E + 1]) and
+// `perm` (int [n_pairs]) feed the expert-ordered scatter; pass null for the last three to skip them.
 extern "C" int slab_moe_plan_slots(const int* topk_idx, int n_pairs, int E, const int* block_base,
                                    const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
                                    int pad, int capacity, int* expert_offsets, int* expert_counts, int* send_base,
-                                   int* meta, int* pair_loc, int* status, cudaStream_t st) {
+                                   int* meta, int* pair_loc, int* status, const int* send_counts, int* send_prefix,
+                                   int* item_prefix, int* perm, cudaStream_t st) {
   if (E > MAX_EXPERTS || world > MAX_WORLD || capacity >= (1 << 24)) return -100;
+  if ((send_prefix == nullptr) != (item_prefix == nullptr) || (send_prefix == nullptr) != (perm == nullptr)) return -101;
   PeerTable pt = make_peers(peer_ptrs, world);
   WsLayout ws = make_layout(ws_offsets);
   moe_plan_kernel<<<1, 512, 0, st>>>(pt, ws, world, me, E, pad, capacity, epoch, expert_offsets, expert_counts,
-                                     send_base, meta, status, g_wait_limit_ns);
+                                     send_base, meta, status, g_wait_limit_ns, send_counts, send_prefix, item_prefix);
   int nb = slab_moe_count_blocks(n_pairs);
   if (nb < 1) nb = 1;
   moe_slots_kernel<<<nb, COUNT_THREADS, 0, st>>>(topk_idx, n_pairs, E, world, block_base, send_base, capacity,
-                                                 pair_loc, status);
+                                                 pair_loc, status, send_prefix, perm);
   return (int)cudaGetLastError();
 }
 
@@ -527,6 +752,49 @@ extern "C" int slab_moe_scatter(const void* x, const float* pair_scalar, const f
 #undef SLAB_SCATTER
   return (int)cudaGetLastError();
 }
+
+// Expert-ordered scatter with per-(source, expert) completion flags (see moe_scatter_sorted_kernel).  `perm`,
+// `send_counts`, `send_prefix`, `item_prefix` come from the plan; `chunk_done` is a zeroed int [E] the kernel leaves
+// zeroed.  part: 0 all destinations, 1 remote only, 2 local only.
+extern "C" int slab_moe_scatter_sorted(const void* x, const float* pair_scalar, const float* scale_in,
+                                       const int* pair_loc, const int* perm, const int* send_counts,
+                                       const int* send_prefix, const int* item_prefix, int T, int K, int H, int E,
+                                       const long* peer_ptrs, const long* ws_offsets, int world, int me, int epoch,
+                                       const int* expert_offsets, const int* expert_counts, int e_local, int pad,
+                                       int fp8, int* chunk_done, int part, int n_blocks, cudaStream_t st) {
+  if ((fp8 ? H % 128 : H % 8) || world > MAX_WORLD || E > MAX_EXPERTS || part < 0 || part > 2) return -100;
+  PeerTable pt = make_peers(peer_ptrs, world);
+  WsLayout ws = make_layout(ws_offsets);
+  if (n_blocks <= 0) n_blocks = 148 * 4;
+  const int vpl = (H / 8 + 31) / 32;
+  if (vpl > 32) return -100;
+#define SLAB_SCATTER_S(FP8, VPL)                                                                                     \
+  moe_scatter_sorted_kernel<FP8, VPL><<<n_blocks, 256, 0, st>>>(                                                     \
+      (const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, perm, send_counts, send_prefix, item_prefix, T, K, H, \
+      E, pt, ws, world, me, epoch, expert_offsets, expert_counts, e_local, pad, chunk_done, part)
+  if (fp8) {
+    if (vpl <= 8) SLAB_SCATTER_S(true, 8);
+    else if (vpl <= 16) SLAB_SCATTER_S(true, 16);
+    else SLAB_SCATTER_S(true, 32);
+  } else {
+    if (vpl <= 8) SLAB_SCATTER_S(false, 8);
+    else if (vpl <= 16) SLAB_SCATTER_S(false, 16);
+    else SLAB_SCATTER_S(false, 32);
+  }
+#undef SLAB_SCATTER_S
+  return (int)cudaGetLastError();
+}
+
+// Wait for all per-(source, expert) flags of this rank (world * e_local of them) to reach `epoch`.
+extern "C" int slab_moe_wait_experts(const long* peer_ptrs, const long* ws_offsets, int world, int me, int e_local,
+                                     int epoch, int* status, cudaStream_t st) {
+  WsLayout ws = make_layout(ws_offsets);
+  moe_wait_eflags_kernel<<<1, 256, 0, st>>>(make_peers(peer_ptrs, world), ws.eflag, world * e_local, me, epoch, status,
+                                            g_wait_limit_ns);
+  return (int)cudaGetLastError();
+}
+
+extern "C" unsigned long long slab_moe_wait_limit_ns() { return g_wait_limit_ns; }
 
 extern "C" int slab_moe_check_rows(const int* meta, int limit, int* status, int* rows_seen, cudaStream_t st) {
   moe_check_rows_kernel<<<1, 32, 0, st>>>(meta, limit, status, rows_seen);

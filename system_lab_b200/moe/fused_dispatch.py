@@ -28,7 +28,7 @@ from ..ops import cuda as cops
 for _name, _sig in {
     "slab_moe_count_blocks": "i",
     "slab_moe_count_publish": "piippppiiips",
-    "slab_moe_plan_slots": "piip" + "pp" + "iii" + "ii" + "pppppp" + "s",
+    "slab_moe_plan_slots": "piip" + "pp" + "iii" + "ii" + "pppppp" + "pppp" + "s",
     "slab_moe_scatter": "pppp" + "iii" + "pp" + "iii" + "pp" + "iii" + "p" + "i" + "s",
     "slab_moe_wait": "ppiiiips",
     "slab_moe_signal_out": "ppiiis",
@@ -67,7 +67,7 @@ def compute_layout(ep: int, num_experts: int, topk: int, hidden: int, max_tokens
                          ("row_scales", cap * (hidden // 128) * 4 if fp8_payload else 256),
                          ("scalars0", cap * 4), ("scalars1", cap * 4), ("out_rows", cap * hidden * 2),
                          ("out_scalars", cap * 4), ("origin", cap * 4), ("comb", pairs * hidden * 2),
-                         ("push_flag", ep * 4)):
+                         ("push_flag", ep * 4), ("eflag0", num_experts * 4), ("eflag1", num_experts * 4)):
         off[name] = cur
         cur = _align(cur + nbytes)
     return cap, off, cur
@@ -88,6 +88,9 @@ class FusedPlan:
     tokens_per_expert_global: torch.Tensor   # [E] pairs routed from this rank
     num_rows: int                     # == capacity (host-side bound)
     origin: torch.Tensor | None = None       # [capacity] int32: (source rank << 24) | pair index of received rows
+    send_prefix: torch.Tensor | None = None  # [E + 1] int32: start of every expert's run in `perm`
+    item_prefix: torch.Tensor | None = None  # [E + 1] int32: scatter work items before each position of the send order
+    perm: torch.Tensor | None = None         # [T*K] int32: pair indices grouped by expert (pair order inside an expert)
 
     @property
     def e_local(self) -> int:
@@ -164,8 +167,8 @@ class FusedDispatcher:
         vals = [o["counts_all"], o["counts_flag"], o[f"data_flag{channel}"], o["out_flag"], o[f"rows{channel}"],
                 o["row_scales"], o[f"scalars{channel}"], o["out_rows"], o["out_scalars"],
                 o["origin"] if channel == 0 else -1,       # only forward rows are ever pushed back
-                o["comb"], o["push_flag"]]
-        return (ctypes.c_long * 12)(*vals)
+                o["comb"], o["push_flag"], o[f"eflag{channel}"]]
+        return (ctypes.c_long * 13)(*vals)
 
     def _next_epoch(self) -> int:
         self.epoch += 1
@@ -200,16 +203,20 @@ class FusedDispatcher:
         expert_counts = torch.empty(e_local, **i32)
         meta = torch.zeros(4, **i32)
         pair_loc = torch.empty(t * k, **i32)
+        prefixes = torch.empty(2, self.E + 1, **i32)
+        perm = torch.empty(t * k, **i32)
         cops.call("slab_moe_plan_slots", idx, t * k, self.E, self.block_hist, ctypes.addressof(self._peer_ptrs),
                   ctypes.addressof(self._lay[0]), self.ep, self.me, ep, self.pad, self.capacity, expert_offsets,
-                  expert_counts, self.send_base, meta, pair_loc, self.status, cops.stream())
+                  expert_counts, self.send_base, meta, pair_loc, self.status, self.send_counts, prefixes[0],
+                  prefixes[1], perm, cops.stream())
         if self.poison:
             # result regions: every peer has published this layer's counts, so it has finished pulling / pushing the
             # previous layer's results; the next writers (this rank's GEMM, the peers' push epilogues) come later
             self.out_rows.view(torch.int16).fill_(-1)
             self.comb.view(torch.int16).fill_(-1)
         return FusedPlan(t, k, self.E, self.ep, self.pad, self.capacity, expert_offsets, expert_counts, pair_loc,
-                         meta, self.send_counts.clone(), self.capacity)
+                         meta, self.send_counts.clone(), self.capacity, send_prefix=prefixes[0],
+                         item_prefix=prefixes[1], perm=perm)
 
     def plan(self, topk_idx: torch.Tensor) -> FusedPlan:
         idx, ep = self.plan_publish(topk_idx)

@@ -49,7 +49,7 @@ def test_construction_in_every_mode(keep, push):
         assert d.keep_rows >= min(d.capacity, int(keep * 128))
     else:
         assert d.keep_rows == 0
-    assert len(d._lay[0]) == 12 and d._lay[1][9] == -1 and d._lay[0][9] == d.off["origin"]
+    assert len(d._lay[0]) == 13 and d._lay[1][9] == -1 and d._lay[0][9] == d.off["origin"]
     assert isinstance(d.push_target(object()), PushTarget)
     # views alias the workspace, not copies of it
     d.rows[0][0, 0] = 3.0
