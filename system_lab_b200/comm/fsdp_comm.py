@@ -23,7 +23,7 @@ for _name, _sig in {
     "slab_fsdp_stage": "plppiiiiipps",
     "slab_fsdp_all_gather": "plppiiiipps",
     "slab_fsdp_reduce_scatter": "plppiiiifpps",
-    "slab_fsdp_reduce_scatter_adamw": "lppiiiif" + "ppppp" + "p" + "fffffff" + "pps",
+    "slab_fsdp_reduce_scatter_adamw": "lppiiiif" + "ppppp" + "p" + "fffffff" + "l" + "pps",
     "slab_fsdp_set_wait_limit_ms": "l",
 }.items():
     cops.register(_name, _sig)
@@ -85,7 +85,7 @@ class FsdpPeerComm:
         return piece
 
     def reduce_scatter_adamw(self, grad_full, master, m, v, out_bf16, coef, sq_out, *, lr, beta1, beta2, eps,
-                             weight_decay, step, scale: float = 1.0) -> None:
+                             weight_decay, step, scale: float = 1.0, decay_end: int | None = None) -> None:
         """Reduce-scatter fused with the AdamW update of this rank's fp32 master shard and moments."""
         shard = grad_full.numel() // self.world
         self._ensure(grad_full.numel() * 2)
@@ -94,7 +94,8 @@ class FsdpPeerComm:
         cops.call("slab_fsdp_reduce_scatter_adamw", shard, ctypes.addressof(self._ptrs), ctypes.addressof(self._lay),
                   self.world, self.rank, slot, ep, float(scale), master, m, v, out_bf16, coef, sq_out, float(lr),
                   float(beta1), float(beta2), float(eps), float(weight_decay), float(1 - beta1 ** step),
-                  float(1 - beta2 ** step), self.status, self.done, cops.stream())
+                  float(1 - beta2 ** step), int(shard if decay_end is None else decay_end), self.status, self.done,
+                  cops.stream())
 
 
 def make_fsdp_comms(mesh, device):

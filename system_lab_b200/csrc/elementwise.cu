@@ -508,6 +508,8 @@ __global__ void sumsq_kernel(const G* __restrict__ g, long n, float scale, float
 // scale; v is stored as sqrt(v)).  `coef` is the clip coefficient on the device (no host sync).
 struct AdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
+  long decay_end;      // elements [0, decay_end) of the shard get weight decay, the rest (norm gains: 1-D parameters,
+                       // packed at the tail of a flat group on 128-element boundaries) do not
 };
 
 // 16 consecutive elements per thread (16-byte accesses for every storage type); the 8 threads that share a
@@ -574,6 +576,7 @@ adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_ra
       continue;
     }
     const long e0 = i << 4;
+    const float decay = e0 < a.decay_end ? 1.f - a.lr * a.wd : 1.f;
     float gv[16], mv[16], vv[16], pv[16];
     load16<G>(g, i, gv);
     load16<P>(p, i, pv);
@@ -608,7 +611,7 @@ adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_ra
       mv[j] = a.beta1 * mv[j] + (1.f - a.beta1) * gv[j];
       vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gv[j] * gv[j];
       const float denom = sqrtf(vv[j] / a.bc2) + a.eps;
-      pv[j] = pv[j] * (1.f - a.lr * a.wd) - a.lr * (mv[j] / a.bc1) / denom;
+      pv[j] = pv[j] * decay - a.lr * (mv[j] / a.bc1) / denom;
       if (KIND != 0) vv[j] = sqrtf(vv[j]);        // stored in the sqrt domain
       m_amax = fmaxf(m_amax, fabsf(mv[j]));
       v_amax = fmaxf(v_amax, vv[j]);
@@ -848,13 +851,14 @@ static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scal
 extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
                           float* v_scale, void* out_bf16, const float* coef, float* sq_out, long n, int state_kind,
                           float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
-                          int ctas_per_sm, cudaStream_t st) {
+                          long decay_end, int ctas_per_sm, cudaStream_t st) {
   // ctas_per_sm bounds the resident footprint of this grid-stride kernel.  A kernel that fills every thread slot
   // of every SM (8 x 256) keeps CTAs of kernels launched later on other streams from being scheduled until it
   // exits; an update that runs beside the backward pass asks for 2-3 and leaves the rest to the compute stream.
   if (n % 128) return -100;
   if (n == 0) return 0;
-  AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2};
+  if (decay_end % 128) return -101;
+  AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, decay_end};
   int grid = grid_for(n / 16, 256, ctas_per_sm > 0 && ctas_per_sm < 8 ? ctas_per_sm : 8);
   if (p_is_bf16) {
     if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);

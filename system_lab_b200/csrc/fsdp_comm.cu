@@ -108,6 +108,7 @@ fsdp_gather_kernel(uint4* __restrict__ dst, long n16, FsPeers peers, FsLayout la
 
 struct FsAdam {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
+  long decay_end;     // elements [0, decay_end) of the shard get weight decay (the tail holds the 1-D parameters)
 };
 
 // piece[i] = scale * sum_r peer r's staged grad[me * n8 * 8 + i]  (bf16 in, fp32 accumulate).
@@ -147,6 +148,7 @@ fsdp_reduce_scatter_kernel(float* __restrict__ piece, long n8, FsPeers peers, Fs
       float4* mm = reinterpret_cast<float4*>(m) + 2 * i;
       float4* vm = reinterpret_cast<float4*>(v) + 2 * i;
       float p8[8], m8[8], v8[8];
+      const float decay = (i << 3) < a.decay_end ? 1.f - a.lr * a.wd : 1.f;
       *reinterpret_cast<float4*>(p8) = pm[0]; *reinterpret_cast<float4*>(p8 + 4) = pm[1];
       *reinterpret_cast<float4*>(m8) = mm[0]; *reinterpret_cast<float4*>(m8 + 4) = mm[1];
       *reinterpret_cast<float4*>(v8) = vm[0]; *reinterpret_cast<float4*>(v8 + 4) = vm[1];
@@ -156,7 +158,7 @@ fsdp_reduce_scatter_kernel(float* __restrict__ piece, long n8, FsPeers peers, Fs
         const float g = acc[j] * c;
         m8[j] = a.beta1 * m8[j] + (1.f - a.beta1) * g;
         v8[j] = a.beta2 * v8[j] + (1.f - a.beta2) * g * g;
-        p8[j] = p8[j] * (1.f - a.lr * a.wd) - a.lr * (m8[j] / a.bc1) / (sqrtf(v8[j] / a.bc2) + a.eps);
+        p8[j] = p8[j] * decay - a.lr * (m8[j] / a.bc1) / (sqrtf(v8[j] / a.bc2) + a.eps);
       }
       pm[0] = *reinterpret_cast<float4*>(p8); pm[1] = *reinterpret_cast<float4*>(p8 + 4);
       mm[0] = *reinterpret_cast<float4*>(m8); mm[1] = *reinterpret_cast<float4*>(m8 + 4);
@@ -245,9 +247,9 @@ extern "C" int slab_fsdp_reduce_scatter_adamw(long shard_numel, const long* peer
                                               int me, int slot, int epoch, float scale, float* master, float* m,
                                               float* v, void* out_bf16, const float* coef, float* sq_out, float lr,
                                               float beta1, float beta2, float eps, float wd, float bc1, float bc2,
-                                              int* status, int* done_counter, cudaStream_t st) {
-  if (shard_numel % 8 || world > FS_MAX_WORLD) return -100;
-  FsAdam a{lr, beta1, beta2, eps, wd, bc1, bc2};
+                                              long decay_end, int* status, int* done_counter, cudaStream_t st) {
+  if (shard_numel % 8 || world > FS_MAX_WORLD || decay_end % 8) return -100;
+  FsAdam a{lr, beta1, beta2, eps, wd, bc1, bc2, decay_end};
   fsdp_reduce_scatter_kernel<true><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
       nullptr, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, master,
       m, v, (__nv_bfloat16*)out_bf16, coef, sq_out, a, status, g_fs_limit_ns, done_counter);

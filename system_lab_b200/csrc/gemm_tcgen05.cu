@@ -45,6 +45,11 @@ struct GemmParams {
   int world, me, epoch;
   int pairs;                // rows of the pair-major region (a row origin outside it is reported, not written)
   int* counter;             // CTAs that finished pushing (reset by the last one)
+  // per-(source, expert) arrival flags of the row operand A (FWD / DGRAD): the rows of expert e were written by
+  // `ready_world` sources, source s releases ready[s * E + e] = ready_epoch when its rows of e are complete
+  const int* ready;
+  int ready_world, ready_epoch;
+  unsigned long long ready_limit_ns;
 };
 
 // Shared memory map (exactly the 227 KB a CTA may have): [0, 3072) barriers, TMEM slot, abort flag and the
@@ -173,12 +178,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      TileInfo ti;
-      bool ok = true;
-      for (int t = blockIdx.x; ok && get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
+    // Lane 0 issues the copies.  When the row operand arrives from other GPUs expert by expert (`ready`), the whole
+    // warp first polls the flags of the tile's expert, one source per lane: the GEMM starts on an expert as soon as
+    // every source has delivered it, while rows of later experts are still in flight.  The rows were written by
+    // peers' generic-proxy stores; the proxy fence orders the TMA (async proxy) reads after the acquire.
+    int s = 0;
+    uint32_t ph = 0;
+    int last_e = -1;
+    TileInfo ti;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && get_tile<MODE, BN>(t, prefix, p, n_tiles, ti); t += gridDim.x) {
+      if (MODE != MODE_WGRAD && p.ready != nullptr && ti.e != last_e) {
+        bool mine = true;
+        if (lane < p.ready_world)
+          mine = wait_flag_ge(p.ready + lane * p.E + ti.e, p.ready_epoch, p.status, p.ready_limit_ns);
+        ok = __all_sync(0xffffffffu, mine);
+        if (!ok) {
+          if (lane == 0) *abort_flag = 1;
+          break;
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        last_e = ti.e;
+      }
+      if (lane == 0) {
         for (int ks = 0; ks < ti.ksteps; ++ks) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* a_dst = ring + s * L::STAGE_BYTES;
@@ -203,6 +225,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -434,12 +457,23 @@ static int launch(const void* A, const void* B, const GemmParams& p, int grid, c
 // (wgrad: a last partial row tile is written with guarded stores), at most 512 experts.  `status` is a device int
 // the kernel sets on a
 // bounded-wait timeout (0 = ok).  Returns a CUDA/driver error code (0 = launched).
+// `ready` (optional, modes 0 and 1): per-(source, expert) arrival flags of the row operand, int [ready_world][E] in
+// this GPU's memory; the kernel waits (bounded) for all `ready_world` flags of an expert to reach `ready_epoch`
+// before it loads that expert's first row tile.  Null: the operand is complete when the kernel starts.
+extern "C" unsigned long long slab_moe_wait_limit_ns();
+
 extern "C" int slab_grouped_gemm_bf16(int mode, const void* A, const void* B, void* C, const int* seg_offsets,
                                       const int* seg_counts, int E, int R, int N, int K, int accumulate,
-                                      int block_n, int max_ctas, int* status, cudaStream_t stream) {
+                                      int block_n, int max_ctas, const int* ready, int ready_world, int ready_epoch,
+                                      int* status, cudaStream_t stream) {
   using namespace slab;
   if (E > 512 || K % 64 || N % 64) return -100;
+  if (ready && (ready_world < 1 || ready_world > 32 || mode == MODE_WGRAD)) return -102;
   GemmParams p{seg_offsets, seg_counts, E, R, N, K, static_cast<__nv_bfloat16*>(C), accumulate, status};
+  p.ready = ready;
+  p.ready_world = ready_world;
+  p.ready_epoch = ready_epoch;
+  p.ready_limit_ns = slab_moe_wait_limit_ns();
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   const bool wide = block_n != 128;
@@ -468,6 +502,7 @@ extern "C" int slab_grouped_gemm_bf16_push(int mode, const void* A, const void* 
   if (E > 256 || K % 64 || N % 64 || world > 16 || world < 1 || me < 0 || me >= world) return -100;
   if (mode != MODE_FWD && mode != MODE_DGRAD) return -101;
   GemmParams p{seg_offsets, seg_counts, E, R, N, K, nullptr, 0, status};
+  p.ready = nullptr;
   p.origin = origin;
   for (int i = 0; i < 16; ++i) p.peer[i] = i < world ? reinterpret_cast<uint8_t*>(peer_ptrs[i]) : nullptr;
   p.comb_off = comb_off;

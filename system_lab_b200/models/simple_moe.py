@@ -304,6 +304,11 @@ class MoEFFN(nn.Module):
             out_buf = d.push_target(plan) if (getattr(d, "push", False) and ops.use_kernels(x2)) else \
                 (d.expert_output_buffer() if hasattr(d, "expert_output_buffer") else None)
         elif hasattr(d, "dispatch"):            # fused path: rows and gate probabilities travel together
+            # rows arrive expert by expert; when both expert GEMMs run on the hand-written kernel, the first one waits
+            # for each expert's rows inside the kernel instead of this stream waiting for the whole exchange
+            plan.defer_ready = defer = (getattr(d, "expert_ordered", False) and not self.fp8
+                                        and ops.grouped_kernel_ok(x2, self.experts_w1)
+                                        and ops.grouped_kernel_ok(x2, self.experts_w2))
             xe, pe = d.dispatch(plan, x2, w)
             # push mode: the GEMM epilogues write result rows into the token owners' memory themselves;
             # otherwise the GEMMs write the peer-visible buffer the owners pull from
@@ -312,18 +317,27 @@ class MoEFFN(nn.Module):
             xe = d.dispatch_rows(plan, x2)
             pe = d.dispatch_scalars(plan, w)
             out_buf = None
+        ready = getattr(plan, "ready", None)
         if kept is not None and not RECOMPUTE_PHASE[0] and not torch.is_grad_enabled():
+            if ready is not None:                   # the copy reads every row
+                ready.wait()
+                d.join_side()
+                ready = plan.ready = None
             kept["plan"] = plan
             kept["xe"], kept["pe"] = d.keep_dispatched(plan, xe, pe)
         h1 = ops.grouped_linear(xe, self.experts_w1.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
-                                dgrad_out=out_buf)
+                                dgrad_out=out_buf, ready=ready)
+        if ready is not None:
+            plan.ready = None
+            d.join_side()
         act = ops.swiglu_probs(h1, pe, rows_dev=getattr(plan, "meta", None))
         # In a recomputed forward nothing reads the block's result (it only feeds a residual add), so the second
         # expert GEMM and the combine exchange are skipped: their autograd nodes are all that backward needs.
         dead = RECOMPUTE_PHASE[0]
+        defer_bwd = bool(getattr(plan, "defer_ready", False)) and hasattr(d, "take_bwd_ready")
         ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
-                                out=out_buf, dead=dead)
-        out = d.combine_rows(plan, ye, dead=dead)
+                                out=out_buf, dead=dead, bwd_ready=d if defer_bwd else None)
+        out = d.combine_rows(plan, ye, dead=dead, defer_bwd=True) if defer_bwd else d.combine_rows(plan, ye, dead=dead)
         if self.shared is not None:
             out = out + self.shared(x2)
         return out.reshape(shp)

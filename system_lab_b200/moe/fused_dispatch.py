@@ -31,6 +31,8 @@ for _name, _sig in {
     "slab_moe_plan_slots": "piip" + "pp" + "iii" + "ii" + "pppppp" + "pppp" + "s",
     "slab_moe_scatter": "pppp" + "iii" + "pp" + "iii" + "pp" + "iii" + "p" + "i" + "s",
     "slab_moe_wait": "ppiiiips",
+    "slab_moe_scatter_sorted": "pppp" + "pppp" + "iiii" + "pp" + "iii" + "pp" + "iii" + "p" + "ii" + "s",
+    "slab_moe_wait_experts": "ppiiiips",
     "slab_moe_signal_out": "ppiiis",
     "slab_moe_combine": "pppiiippiiipis",
     "slab_moe_combine_scalars": "ppippiiips",
@@ -91,10 +93,35 @@ class FusedPlan:
     send_prefix: torch.Tensor | None = None  # [E + 1] int32: start of every expert's run in `perm`
     item_prefix: torch.Tensor | None = None  # [E + 1] int32: scatter work items before each position of the send order
     perm: torch.Tensor | None = None         # [T*K] int32: pair indices grouped by expert (pair order inside an expert)
+    ready: "ReadyFlags | None" = None        # arrival flags of the forward rows while their consumer has not waited yet
+    defer_ready: bool = False                # the consumer of the forward rows (expert GEMM) does the waiting
 
     @property
     def e_local(self) -> int:
         return self.num_experts // self.ep
+
+
+class ReadyFlags:
+    """Arrival flags of the rows one expert-ordered scatter is delivering to this rank: ``flags[s, j] >= epoch`` once
+    source ``s`` has written all its rows of local expert ``j``.  Handed to the grouped GEMM that consumes the rows
+    (it waits expert by expert inside the kernel); any other consumer calls :meth:`wait` first."""
+
+    def __init__(self, d: "FusedDispatcher", channel: int, epoch: int):
+        self.d, self.channel, self.epoch = d, channel, epoch
+        self.flags = d.eflags[channel]
+        self.world = d.ep
+        self.consumed = False
+
+    def mark_consumed(self) -> None:
+        self.consumed = True
+
+    def wait(self) -> None:
+        """One small kernel that waits for every (source, expert) flag: afterwards every row has arrived."""
+        if not self.consumed:
+            d = self.d
+            cops.call("slab_moe_wait_experts", ctypes.addressof(d._peer_ptrs), ctypes.addressof(d._lay[self.channel]),
+                      d.ep, d.me, d.E // d.ep, self.epoch, d.status, cops.stream())
+            self.consumed = True
 
 
 class FusedDispatcher:
@@ -147,7 +174,16 @@ class FusedDispatcher:
         self.send_counts = torch.zeros(num_experts, **i32)
         self.send_base = torch.zeros(num_experts, **i32)
         self.done_counter = torch.zeros(1, **i32)
+        self.chunk_done = torch.zeros(num_experts, **i32)       # expert-ordered scatter: finished chunks per expert
         self.status = cops.status_word(device)
+        # expert_ordered: rows are sent expert by expert with one completion flag per (source, expert), and the expert
+        # GEMM that consumes them waits per expert inside the kernel (no wait for the whole exchange in between)
+        self.expert_ordered = True
+        # overlap: with real peers the remote half of a scatter runs on a side stream beside the consuming GEMM (the
+        # local half goes first on the compute stream; the GEMM waits only on flags other GPUs set)
+        self.overlap = False
+        self._side = None
+        self._bwd_ready = None
         # typed views of this rank's regions
         self.rows = [workspace.view(off["rows0"], (cap, H), torch.bfloat16),
                      workspace.view(off["rows1"], (cap, H), torch.bfloat16)]
@@ -158,6 +194,8 @@ class FusedDispatcher:
         self.origin = workspace.view(off["origin"], (cap,), torch.int32)
         self.comb = workspace.view(off["comb"], (pairs, H), torch.bfloat16)
         self.push_counter = torch.zeros(1, **i32)
+        self.eflags = [workspace.view(off["eflag0"], (self.ep, num_experts // self.ep), torch.int32),
+                       workspace.view(off["eflag1"], (self.ep, num_experts // self.ep), torch.int32)]
         if fp8_payload:
             self.rows_fp8 = workspace.view(off["rows0"], (cap, H), torch.float8_e4m3fn)
             self.row_scales = workspace.view(off["row_scales"], (cap, H // 128), torch.float32)
@@ -230,6 +268,48 @@ class FusedDispatcher:
                   plan.expert_offsets, plan.expert_counts, plan.e_local, self.pad, 1 if fp8 else 0,
                   self.done_counter, 0, cops.stream())
         return ep
+
+    def scatter_ordered(self, plan: FusedPlan, x, scalars, channel: int, scale_in=None, fp8: bool = False) -> ReadyFlags:
+        """Expert-ordered scatter (``csrc/dispatch.cu: moe_scatter_sorted_kernel``); returns the arrival flags the
+        consumer of this rank's receive buffer has to honour.  With ``overlap`` the rows for this rank are written
+        first on the compute stream and the rows for the peers on a side stream, which the compute stream joins
+        after the consumer has been launched (:meth:`join_side`)."""
+        ep = self._next_epoch()
+
+        def launch(part: int) -> None:
+            cops.call("slab_moe_scatter_sorted", x, scalars, scale_in, plan.pair_loc, plan.perm,
+                      plan.tokens_per_expert_global, plan.send_prefix, plan.item_prefix, plan.num_tokens, plan.topk,
+                      self.H, self.E, ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[channel]), self.ep,
+                      self.me, ep, plan.expert_offsets, plan.expert_counts, plan.e_local, self.pad, 1 if fp8 else 0,
+                      self.chunk_done, part, 0, cops.stream())
+
+        if self.overlap and self.ep > 1 and self.device is not None and torch.device(self.device).type == "cuda":
+            launch(2)                                     # this rank's own rows: the consumer needs them in order
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            main = torch.cuda.current_stream(self.device)
+            self._side.wait_stream(main)
+            for t in (x, scalars, scale_in):              # keep the inputs alive until the side stream has read them
+                if isinstance(t, torch.Tensor):
+                    t.record_stream(self._side)
+            with torch.cuda.stream(self._side):
+                launch(1)                                 # rows for the peers, beside whatever the compute stream runs next
+            self._side_pending = True
+        else:
+            launch(0)
+        return ReadyFlags(self, channel, ep)
+
+    def join_side(self) -> None:
+        """The compute stream waits for the side-stream half of the last scatter (call after the consumer of the
+        received rows has been launched; later kernels may reuse the scatter's inputs and counters)."""
+        if getattr(self, "_side_pending", False):
+            torch.cuda.current_stream(self.device).wait_stream(self._side)
+            self._side_pending = False
+
+    def take_bwd_ready(self):
+        """Arrival flags of the gradient rows the last backward of combine is delivering (None if it already waited)."""
+        r, self._bwd_ready = self._bwd_ready, None
+        return r
 
     def wait_rows(self, channel: int, ep: int) -> None:
         cops.call("slab_moe_wait", ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[channel]), self.ep,
@@ -312,10 +392,12 @@ class FusedDispatcher:
         raise NotImplementedError("use dispatch(plan, x, probs): rows and gate probabilities travel together")
 
     def combine_rows(self, plan: FusedPlan, ye: torch.Tensor, weights: torch.Tensor | None = None,
-                     dead: bool = False):
+                     dead: bool = False, defer_bwd: bool = False):
         """``dead``: only the autograd node is wanted (recomputed forward whose result nobody reads): no signal, no
-        wait, no pull; the returned values are unspecified.  Every rank of the group must pass the same flag."""
-        return _FusedCombine.apply(ye, weights, self, plan, dead and weights is None)
+        wait, no pull; the returned values are unspecified.  Every rank of the group must pass the same flag.
+        ``defer_bwd``: in backward, hand the arrival flags of the gradient rows to the consumer (the expert GEMM that
+        produced ``ye`` calls :meth:`take_bwd_ready`) instead of waiting for the whole exchange here."""
+        return _FusedCombine.apply(ye, weights, self, plan, dead and weights is None, defer_bwd)
 
 
 class PushTarget:
@@ -347,8 +429,17 @@ class _FusedDispatch(torch.autograd.Function):
         ctx.d, ctx.plan, ctx.has_probs = d, plan, probs is not None
         xc = x.contiguous()
         pc = probs.float().contiguous() if probs is not None else None
-        ep = d.scatter(plan, xc, pc, channel=0)
-        d.wait_rows(0, ep)
+        plan.ready = None
+        if d.expert_ordered and plan.perm is not None:
+            rdy = d.scatter_ordered(plan, xc, pc, channel=0)
+            if d.clone_outputs or not getattr(plan, "defer_ready", False):
+                rdy.wait()                       # the caller reads the rows itself
+                d.join_side()
+            else:
+                plan.ready = rdy                 # the expert GEMM waits expert by expert
+        else:
+            ep = d.scatter(plan, xc, pc, channel=0)
+            d.wait_rows(0, ep)
         xe, pe = d.rows[0], d.scalars[0]
         plan.origin = d.origin
         if d.clone_outputs:
@@ -388,8 +479,9 @@ class _FusedKept(torch.autograd.Function):
 
 class _FusedCombine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ye, weights, d: FusedDispatcher, plan: FusedPlan, dead: bool = False):
+    def forward(ctx, ye, weights, d: FusedDispatcher, plan: FusedPlan, dead: bool = False, defer_bwd: bool = False):
         ctx.d, ctx.plan = d, plan
+        ctx.defer_bwd = defer_bwd
         if weights is not None:
             weights = weights.float().contiguous()
             ctx.save_for_backward(weights)
@@ -410,12 +502,20 @@ class _FusedCombine(torch.autograd.Function):
     def backward(ctx, g):
         d, plan = ctx.d, ctx.plan
         w = ctx.saved_tensors[0] if ctx.weighted else None
-        ep = d.scatter(plan, g.contiguous(), None, channel=1, scale_in=w)
-        d.wait_rows(1, ep)
+        if d.expert_ordered and plan.perm is not None:
+            rdy = d.scatter_ordered(plan, g.contiguous(), None, channel=1, scale_in=w)
+            if ctx.defer_bwd and not d.clone_outputs:
+                d._bwd_ready = rdy               # taken by the expert GEMM's backward (dgrad waits expert by expert)
+            else:
+                rdy.wait()
+                d.join_side()
+        else:
+            ep = d.scatter(plan, g.contiguous(), None, channel=1, scale_in=w)
+            d.wait_rows(1, ep)
         g_ye = d.rows[1][:ctx.ye_rows]
         if d.clone_outputs:
             g_ye = g_ye.clone()
         if ctx.weighted and ctx.needs_input_grad[1]:
             raise NotImplementedError("gate-weighted fused combine has no weight gradient: apply the gate "
                                       "inside SwiGLU (swiglu_probs) for training")
-        return g_ye, None, None, None, None
+        return g_ye, None, None, None, None, None

@@ -122,14 +122,25 @@ def rope_packed(qkv, cos, sin, n_heads: int, head_dim: int):
     return torch.cat([rot.reshape(b, s, n_heads * head_dim), qkv[..., n_heads * head_dim:]], dim=-1)
 
 
-def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None, dead: bool = False):
+def grouped_linear(a, w, offsets, counts, fp8: bool = False, out=None, dgrad_out=None, dead: bool = False,
+                   ready=None, bwd_ready=None):
     """``out[rows of e] = a[rows of e] @ w[e].T`` (``w: [E, N, K]``), differentiable in ``a`` and ``w``.
     ``out`` (kernel path only) names the buffer the result is written to, e.g. the peer-visible
     expert-output buffer of the fused dispatcher.  ``dead``: only the autograd node is wanted (a recomputed
-    forward whose result nobody reads); the product is not computed and the returned values are unspecified."""
+    forward whose result nobody reads); the product is not computed and the returned values are unspecified.
+    ``ready`` / ``bwd_ready``: arrival flags of rows that peers are still delivering (fused dispatcher): the kernel
+    waits for them expert by expert; every other route waits for the whole exchange before it reads a row."""
     if use_kernels(a):
-        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out, dead)
+        return _cuda().grouped_linear(a, w, offsets, counts, fp8, out, dgrad_out, dead, ready, bwd_ready)
+    if ready is not None:
+        ready.wait()
     return _GroupedLinearRef.apply(a, w, offsets, counts, dead, fp8)
+
+
+def grouped_kernel_ok(a, w) -> bool:
+    """True if ``grouped_linear(a, w, ...)`` runs on the hand-written grouped GEMM (and can therefore wait for rows
+    that are still arriving inside the kernel)."""
+    return use_kernels(a) and _cuda().grouped_kernel_ok(a, w)
 
 
 def causal_attention(q, k, v, scale=None, window=0):

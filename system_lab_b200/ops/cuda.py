@@ -29,12 +29,12 @@ _SIGS = {
     "slab_quant_128x128": "pppiiis",
     "slab_quant_rowwise": "ppplis",
     "slab_sumsq": "pilfps",
-    "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "is",
+    "slab_adamw": "pipi" + "p" * 7 + "li" + "f" * 7 + "lis",
     "slab_router_topk": "ppppiiiiifs",
     "slab_router_fused_fwd": "ppppiiiiifpfps",
     "slab_router_fused_bwd": "pppppfpiiiiifs",
     "slab_ce_fwd_bwd": "pppiifs",
-    "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "ps",
+    "slab_grouped_gemm_bf16": "i" + "p" * 5 + "i" * 7 + "pii" + "ps",
     "slab_grouped_gemm_fp8": "p" * 7 + "iiiii" + "ps",
     "slab_grouped_gemm_fp8_rowwise": "p" * 7 + "iiiii" + "ps",
 }
@@ -438,8 +438,12 @@ def _check_segments(offsets, counts):
 
 
 def grouped_gemm_raw(mode: int, a, b, offsets, counts, n: int, k: int, out=None, accumulate=False,
-                     block_n: int = 256, max_ctas: int = 0):
-    """mode 0: out[R,N] = a[R,K] @ b[e]^T ; 1: out[R,K] = a[R,N] @ b[e] ; 2: out[E,N,K] = a[R,N]^T @ b[R,K]."""
+                     block_n: int = 256, max_ctas: int = 0, ready=None):
+    """mode 0: out[R,N] = a[R,K] @ b[e]^T ; 1: out[R,K] = a[R,N] @ b[e] ; 2: out[E,N,K] = a[R,N]^T @ b[R,K].
+
+    ``ready`` (modes 0 and 1): arrival flags of the row operand (an object with ``flags`` int32 [world, E], ``world``,
+    ``epoch`` and ``mark_consumed()``): the kernel waits per expert for every source instead of the caller waiting
+    for the whole exchange."""
     e = offsets.numel()
     r = a.shape[0]
     if out is None:
@@ -449,8 +453,15 @@ def grouped_gemm_raw(mode: int, a, b, offsets, counts, n: int, k: int, out=None,
             out = torch.empty(r, k, dtype=torch.bfloat16, device=a.device)
         else:
             out = torch.empty(e, n, k, dtype=torch.bfloat16, device=a.device)
+    if ready is not None and mode != 2:
+        call("slab_grouped_gemm_bf16", mode, a, b, out, offsets, counts, e, r, n, k, 1 if accumulate else 0,
+             block_n, max_ctas, ready.flags, int(ready.world), int(ready.epoch), status_word(a.device), stream())
+        ready.mark_consumed()
+        return out
+    if ready is not None:
+        ready.wait()
     call("slab_grouped_gemm_bf16", mode, a, b, out, offsets, counts, e, r, n, k, 1 if accumulate else 0,
-         block_n, max_ctas, status_word(a.device), stream())
+         block_n, max_ctas, None, 0, 0, status_word(a.device), stream())
     return out
 
 
@@ -493,13 +504,17 @@ class _GroupedLinear(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, out=None, dgrad_out=None, dead=False):
+    def forward(ctx, a, w, offsets, counts, out=None, dgrad_out=None, dead=False, ready=None, bwd_ready=None):
         e, n, k = w.shape
         a = a.contiguous()
         w = w.contiguous() if not w.is_contiguous() else w
         push = out if hasattr(out, "launch") else None      # a dispatcher PushTarget: rows go to the token owners
         if push is not None:
             out = None
+        ctx.bwd_ready = bwd_ready            # source of the arrival flags of this node's incoming gradient rows
+        if ready is not None and (dead or push is not None):
+            ready.wait()                     # no kernel here takes the flags: wait for the whole exchange
+            ready = None
         if dead or push is not None:
             # node only: the caller never reads the product (recomputed forward), or the rows leave through the
             # push epilogue; either way the returned tensor is a shape carrier without storage behind every row
@@ -507,7 +522,7 @@ class _GroupedLinear(torch.autograd.Function):
                 push.launch(0, a, w, offsets, counts, n, k, _pick_bn(n))
             out = out if out is not None else torch.empty(1, dtype=torch.bfloat16, device=a.device).expand(a.shape[0], n)
         else:
-            out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n))
+            out = grouped_gemm_raw(0, a, w, offsets, counts, n, k, out=out, block_n=_pick_bn(n), ready=ready)
         ctx.save_for_backward(a, w, offsets, counts)
         ctx.w_ref = w
         ctx.dgrad_out = dgrad_out
@@ -519,19 +534,34 @@ class _GroupedLinear(torch.autograd.Function):
     def backward(ctx, g):
         a, w, offsets, counts = ctx.saved_tensors
         e, n, k = w.shape
+        # the gradient rows may still be arriving from the peers (backward of combine): the dgrad kernel waits for
+        # them expert by expert; anything else waits for all of them first
+        src = getattr(ctx, "bwd_ready", None)
+        rdy = src.take_bwd_ready() if src is not None else None
+        if rdy is not None and not g.is_contiguous():
+            rdy.wait()
+            rdy = None
         g = g.contiguous()
         da = dw = None
         if ctx.needs_input_grad[0]:
             do = ctx.dgrad_out
             if hasattr(do, "launch"):                  # PushTarget: the input gradient goes to the token owners
+                if rdy is not None:
+                    rdy.wait()
+                    rdy = None
                 do.launch(1, g, w, offsets, counts, n, k, _pick_bn(k))
                 da = torch.empty(1, dtype=torch.bfloat16, device=g.device).expand(g.shape[0], k)
             else:
                 if do is not None and (do.shape[0] < g.shape[0] or do.shape[1] != k):
                     do = None
-                da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, out=do, block_n=_pick_bn(k))
+                da = grouped_gemm_raw(1, g, w, offsets, counts, n, k, out=do, block_n=_pick_bn(k), ready=rdy)
+                rdy = None
+                if src is not None:
+                    src.join_side()          # the side-stream half of the gradient scatter, if there was one
                 if do is not None:
                     da = do[:g.shape[0]]
+        if rdy is not None:
+            rdy.wait()
         if ctx.needs_input_grad[1]:
             mg = getattr(ctx.w_ref, "main_grad", None)
             if mg is not None:
@@ -540,7 +570,7 @@ class _GroupedLinear(torch.autograd.Function):
                 ctx.w_ref.main_grad_written = True
             else:
                 dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
-        return da, dw, None, None, None, None, None
+        return da, dw, None, None, None, None, None, None, None
 
 
 class _GroupedLinearFp8(torch.autograd.Function):
@@ -550,10 +580,13 @@ class _GroupedLinearFp8(torch.autograd.Function):
     constant along K so the kernel accumulates all of K in TMEM), or 1x128 / 128x128 blocks (``"blockwise"``)."""
 
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, recipe, out=None, dgrad_out=None):
+    def forward(ctx, a, w, offsets, counts, recipe, out=None, dgrad_out=None, ready=None, bwd_ready=None):
         e, n, k = w.shape
         a = a.contiguous()
         w = w.contiguous() if not w.is_contiguous() else w
+        ctx.bwd_ready = bwd_ready
+        if ready is not None:
+            ready.wait()                     # the quantiser reads every row
         if recipe == "blockwise":
             aq, sa = quant_1x128(a)
             wq, sw = quant_128x128(w)
@@ -575,7 +608,7 @@ class _GroupedLinearFp8(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        return _GroupedLinear.backward(ctx, g)
+        return _GroupedLinear.backward(ctx, g)          # same arity: (da, dw) + one None per remaining input
 
 
 def _fp8_recipe(fp8) -> str:
@@ -590,9 +623,19 @@ def _fp8_recipe(fp8) -> str:
 _N_MULTIPLE = 64
 
 
-def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, dead: bool = False):
+def grouped_kernel_ok(a, w) -> bool:
+    """Shapes and dtypes the tcgen05 grouped GEMM takes (everything else goes to the library loop)."""
+    return _bf16(a, w) and w.shape[2] % 64 == 0 and w.shape[1] % _N_MULTIPLE == 0
+
+
+def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, dead: bool = False, ready=None,
+                   bwd_ready=None):
+    """``ready``: arrival flags of ``a``'s rows (see ``grouped_gemm_raw``); ``bwd_ready``: the dispatcher that will hold
+    the arrival flags of this node's incoming gradient rows when backward runs (``take_bwd_ready()``)."""
     e, n, k = w.shape
-    if not _bf16(a, w) or k % 64 or n % _N_MULTIPLE:
+    if not grouped_kernel_ok(a, w):
+        if ready is not None:
+            ready.wait()
         from . import _GroupedLinearRef
         return _GroupedLinearRef.apply(a, w, offsets, counts, dead)
     offsets, counts = _check_segments(offsets, counts)
@@ -603,9 +646,9 @@ def grouped_linear(a, w, offsets, counts, fp8=False, out=None, dgrad_out=None, d
     fp8_ok = recipe and not dead and not hasattr(out, "launch") and \
         (k % 128 == 0 and n % (128 if recipe == "blockwise" else 64) == 0)          # rowwise / tensorwise share a kernel
     if fp8_ok:           # a pushed output stays on the bf16 kernel: the fp8 kernels store through TMA only
-        res = _GroupedLinearFp8.apply(a, w, offsets, counts, recipe, out, dgrad_out)
+        res = _GroupedLinearFp8.apply(a, w, offsets, counts, recipe, out, dgrad_out, ready, bwd_ready)
     else:
-        res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead)
+        res = _GroupedLinear.apply(a, w, offsets, counts, out, dgrad_out, dead, ready, bwd_ready)
     return res[:a.shape[0]] if res.shape[0] != a.shape[0] else res
 
 
@@ -809,4 +852,4 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, 
          m.data, v.data, getattr(m, "scale", None), getattr(v, "scale", None), out_bf16, coef, sq_out, n,
          _KIND[m.kind],
          float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
-         int(ctas_per_sm), stream())
+         int(group.shard_decay_end() if hasattr(group, "shard_decay_end") else n), int(ctas_per_sm), stream())

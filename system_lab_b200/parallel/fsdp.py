@@ -43,6 +43,9 @@ class FlatGroup:
         self.compute_dtype = compute_dtype
         self.device = device
         self.comm = comm                          # optional fused peer-memory collectives
+        # matrices first, 1-D parameters (norm gains) at the tail: weight decay applies to [0, decay_numel) only,
+        # one boundary the fused AdamW kernels take as an argument
+        named_params = [np for np in named_params if np[1].dim() > 1] + [np for np in named_params if np[1].dim() <= 1]
         self.names = [n for n, _ in named_params]
         self.params = [p for _, p in named_params]
         self.shapes = [tuple(p.shape) for p in self.params]
@@ -51,6 +54,7 @@ class FlatGroup:
         for p in self.params:
             self.offsets.append(off)
             off += _round_up(p.numel(), ALIGN)
+        self.decay_numel = next((o for p, o in zip(self.params, self.offsets) if p.dim() <= 1), off)
         self.total = _round_up(max(off, ALIGN), ALIGN * self.world)
         self.shard_numel = self.total // self.world
         # elements of the flat buffer that belong to no parameter (alignment between parameters, tail padding)
@@ -111,6 +115,12 @@ class FlatGroup:
             self.release()
 
     # ---- parameters -------------------------------------------------------
+    def shard_decay_end(self) -> int:
+        """Elements at the head of this rank's shard that get weight decay (the group's 1-D parameters sit at the tail
+        of the flat buffer; every parameter starts on a 128-element boundary, so this is a multiple of 128)."""
+        lo = self.rank * self.shard_numel if self.sharded else 0
+        return min(max(self.decay_numel - lo, 0), self.shard_numel if self.sharded else self.total)
+
     def shard_in_compute_dtype(self) -> torch.Tensor:
         if getattr(self, "shard_lp", None) is not None:
             return self.shard_lp

@@ -130,7 +130,8 @@ class ShardedAdamW:
         grad_full = g.take_grad_full()
         g.comm.reduce_scatter_adamw(grad_full, g.shard, self.m[g.name].data, self.v[g.name].data, g.shard_lp, coef,
                                     sq_out, lr=lr, beta1=self.beta1, beta2=self.beta2, eps=self.eps,
-                                    weight_decay=self.weight_decay, step=self.step_count)
+                                    weight_decay=self.weight_decay, step=self.step_count,
+                                    decay_end=g.shard_decay_end())
 
     def _update_group(self, g, coef: torch.Tensor, lr: float, sq_out: torch.Tensor | None = None,
                       background: bool = False) -> None:
@@ -155,8 +156,12 @@ class ShardedAdamW:
             m, v = self.m[g.name].load(), self.v[g.name].load()
             m = m.clone() if m is not self.m[g.name].data else m
             v = v.clone() if v is not self.v[g.name].data else v
-            ref.adamw_step(p32, g.grad_shard.float() * coef, m, v, lr=lr, beta1=self.beta1, beta2=self.beta2,
-                           eps=self.eps, weight_decay=self.weight_decay, step=self.step_count)
+            gs = g.grad_shard.float() * coef
+            de = g.shard_decay_end()                     # matrices [0, de) decay, the 1-D parameters behind them do not
+            for lo, hi, wd in ((0, de, self.weight_decay), (de, p32.numel(), 0.0)):
+                if hi > lo:
+                    ref.adamw_step(p32[lo:hi], gs[lo:hi], m[lo:hi], v[lo:hi], lr=lr, beta1=self.beta1,
+                                   beta2=self.beta2, eps=self.eps, weight_decay=wd, step=self.step_count)
             self.m[g.name].store(m)
             self.v[g.name].store(v)
             if p32 is not g.shard:

@@ -257,3 +257,86 @@ def test_out_of_range_expert_id_is_reported_not_written():
     assert loc[5, 1] == -1 and loc[9, 0] == -1
     assert (loc.flatten() >= 0).sum() == 64 * 2 - 2
     assert int(plan.expert_counts.sum()) == 64 * 2 - 2
+
+
+@pytest.mark.parametrize("world,T,K,E,H,skew", [(1, 200, 2, 8, 256, False), (2, 300, 4, 16, 512, False),
+                                                (4, 257, 8, 32, 1024, False), (4, 513, 4, 16, 2048, True)])
+def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H, skew):
+    """The expert-ordered scatter writes the same rows, scalars and origins into the same places as the token-ordered
+    one, releases one flag per (source, expert) -- also for pairs without rows -- and leaves its chunk counters at
+    zero; a grouped GEMM handed those flags gives the fp32 oracle's result.  Ranks are emulated phase by phase (all
+    scatters are enqueued before any GEMM, so no kernel waits for a later launch)."""
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.ops import reference as ref
+    torch.manual_seed(20 + world)
+    ds = _make(world, T, K, E, H)
+    dev = torch.device("cuda")
+    if skew:       # most pairs go to two experts: many chunks for some (source, expert) pairs, none for others
+        idx = [torch.stack([torch.cat([torch.tensor([0, E - 1], device=dev),
+                                       1 + torch.randperm(E - 2, device=dev)[:K - 2]]) for _ in range(T)]).int()
+               for _ in range(world)]
+    else:
+        idx = [torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(T)]).int() for _ in range(world)]
+    x = [torch.randn(T, H, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    pr = [torch.rand(T, K, device=dev) for _ in range(world)]
+    plans = [d.plan_finish(*p) for d, p in zip(ds, [d.plan_publish(i) for d, i in zip(ds, idx)])]
+    # the permutation groups the pairs by expert, in pair order
+    for r in range(world):
+        flat = idx[r].reshape(-1).cpu()
+        perm, pre = plans[r].perm.cpu(), plans[r].send_prefix.cpu()
+        for e in range(E):
+            want = (flat == e).nonzero().flatten()
+            assert torch.equal(perm[pre[e]:pre[e + 1]].long(), want)
+    readies = [d.scatter_ordered(pl, xx, pp.contiguous(), 0) for d, pl, xx, pp in zip(ds, plans, x, pr)]
+    n, e_local = 256, E // world
+    w = (0.05 * torch.randn(world, e_local, n, H, device=dev)).to(torch.bfloat16)
+    outs = [cops.grouped_gemm_raw(0, d.rows[0], w[r], pl.expert_offsets, pl.expert_counts, n, H, ready=rd)
+            for r, (d, pl, rd) in enumerate(zip(ds, plans, readies))]
+    torch.cuda.synchronize()
+    cops.check_status()
+    exp = _expected_layout([i.cpu() for i in idx], world, E)
+    for owner, (offs, cnts, rows) in enumerate(exp):
+        d = ds[owner]
+        assert readies[owner].consumed
+        assert bool((d.eflags[0] >= readies[owner].epoch).all()), "a (source, expert) flag was never released"
+        assert int(d.chunk_done.abs().sum()) == 0
+        got_rows, got_sc, org = d.rows[0], d.scalars[0], d.origin.cpu()
+        for row, (src, p) in list(rows.items())[::5]:
+            assert torch.equal(got_rows[row], x[src][p // K]), f"owner {owner} row {row}"
+            assert got_sc[row].item() == pr[src].reshape(-1)[p].item()
+            assert org[row].item() == (src << 24) | p
+        for o, c in zip(offs, cnts):
+            padded = (c + 127) // 128 * 128
+            if padded > c:
+                assert not got_rows[o + c:o + padded].any()
+        want = ref.grouped_gemm(got_rows, w[owner], plans[owner].expert_offsets, plans[owner].expert_counts)
+        for o, c in zip(offs, cnts):
+            err = (outs[owner][o:o + c].float() - want[o:o + c].float()).abs().max().item() if c else 0.0
+            assert err < 2e-2 * (want.float().abs().max().item() + 1e-6)
+
+
+def test_gemm_that_waits_for_rows_gives_up_with_a_status_code():
+    """Per-expert arrival flags nobody sets (epoch far in the future), 30 ms limit: the producer warp's wait runs out,
+    the kernel unwinds (no copy was issued, the accumulators are released) and the status word says so."""
+    from system_lab_b200.ops import cuda as cops
+    ds = _make(2, 64, 2, 8, 256)
+    d = ds[0]
+    idx = torch.stack([torch.randperm(8, device="cuda")[:2] for _ in range(64)]).int()
+    plans = [dd.plan_finish(*dd.plan_publish(idx)) for dd in ds]
+    rdy = d.scatter_ordered(plans[0], torch.randn(64, 256, device="cuda", dtype=torch.bfloat16), None, 0)
+    ds[1].scatter_ordered(plans[1], torch.randn(64, 256, device="cuda", dtype=torch.bfloat16), None, 0)
+    rdy.epoch = 1 << 30
+    w = torch.zeros(4, 128, 256, device="cuda", dtype=torch.bfloat16)
+    cops.register("slab_moe_set_wait_limit_ms", "l")
+    cops.lib().slab_moe_set_wait_limit_ms(30)
+    try:
+        cops.grouped_gemm_raw(0, d.rows[0], w, plans[0].expert_offsets, plans[0].expert_counts, 128, 256, ready=rdy)
+        torch.cuda.synchronize()
+        assert cops.peek_status() == 5
+    finally:
+        cops.lib().slab_moe_set_wait_limit_ms(60000)
+        cops.clear_status()
+    out = cops.grouped_gemm_raw(0, d.rows[0], w, plans[0].expert_offsets, plans[0].expert_counts, 128, 256)
+    torch.cuda.synchronize()
+    cops.check_status()                     # the next launch on the same context is healthy
+    assert float(out.float().abs().max()) == 0.0

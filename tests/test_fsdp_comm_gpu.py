@@ -61,6 +61,7 @@ def test_all_gather_and_reduce_scatter(world):
 def test_reduce_scatter_fused_adamw_matches_two_step():
     from system_lab_b200.ops import cuda as cops, reference as ref
     world, shard = 2, 128 * 20
+    decay_end = 128 * 15
     cs = _comms(world, shard * world * 2)
     torch.manual_seed(3)
     grads = [torch.randn(shard * world, device="cuda").to(torch.bfloat16) * 0.01 for _ in range(world)]
@@ -80,14 +81,16 @@ def test_reduce_scatter_fused_adamw_matches_two_step():
     for r, (c, (slot, ep)) in enumerate(zip(cs, meta)):
         cops.call("slab_fsdp_reduce_scatter_adamw", shard, ctypes.addressof(c._ptrs), ctypes.addressof(c._lay), world,
                   c.rank, slot, ep, 1.0, masters[r], ms[r], vs[r], outs[r], coef, sq, 1e-2, 0.9, 0.95, 1e-8, 0.1,
-                  1 - 0.9, 1 - 0.95, c.status, c.done, cops.stream())
+                  1 - 0.9, 1 - 0.95, decay_end, c.status, c.done, cops.stream())
     torch.cuda.synchronize()
     cops.check_status()
     total = sum(g.float() for g in grads)
     for r in range(world):
         gr = total[r * shard:(r + 1) * shard]
         m0, v0 = torch.zeros(shard, device="cuda"), torch.zeros(shard, device="cuda")
-        ref.adamw_step(refs[r], gr * 0.7, m0, v0, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1)
+        for lo, hi, wd in ((0, decay_end, 0.1), (decay_end, shard, 0.0)):       # no decay behind the boundary
+            ref.adamw_step(refs[r][lo:hi], gr[lo:hi] * 0.7, m0[lo:hi], v0[lo:hi], lr=1e-2, beta1=0.9, beta2=0.95,
+                           eps=1e-8, weight_decay=wd, step=1)
         assert torch.allclose(masters[r], refs[r], atol=1e-6)
         assert torch.allclose(outs[r].float(), refs[r], atol=2e-3)
     assert abs(sq.item() - total.pow(2).sum().item()) / total.pow(2).sum().item() < 1e-4

@@ -15,7 +15,10 @@ def dry(monkeypatch):
         cops.lib()
     except Exception as e:
         pytest.skip(f"kernel library not built: {e}")
-    calls = []
+    class Calls(list):
+        waited_in_kernel = 0
+
+    calls = Calls()
 
     def fake_call(name, *args):
         assert name in cops._SIGS, f"unregistered entry point {name}"
@@ -31,6 +34,8 @@ def dry(monkeypatch):
             if isinstance(a, torch.Tensor) and a.dtype in (torch.int32, torch.int64):
                 a.data.zero_()
         calls.append(name)
+        if name == "slab_grouped_gemm_bf16" and args[13] is not None:
+            calls.waited_in_kernel += 1               # the GEMM took per-expert arrival flags
         cops.LAUNCHES[0] += 1
         return 0
 
@@ -80,7 +85,8 @@ def test_one_step_walks_the_kernel_route(dry, extra, kw):
     out = tr.train_step()
     assert out["loss"].shape == ()
     names = set(dry)
-    assert {"slab_grouped_gemm_bf16", "slab_moe_scatter", "slab_moe_plan_slots", "slab_adamw"} <= names
+    assert {"slab_grouped_gemm_bf16", "slab_moe_plan_slots", "slab_adamw"} <= names
+    assert "slab_moe_scatter_sorted" in names            # rows travel expert by expert, one flag per (source, expert)
     if kw.get("push"):
         assert "slab_grouped_gemm_bf16_push" in names and "slab_moe_reduce_pairs" in names
         assert d._pending_push == {}                        # every push was consumed by its reduction
@@ -89,7 +95,12 @@ def test_one_step_walks_the_kernel_route(dry, extra, kw):
         assert ("slab_grouped_gemm_fp8_rowwise" in names) or ("slab_grouped_gemm_fp8" in names)
     gbs = next((int(x.split("=")[1]) for x in extra if x.startswith("global_batch_size=")), 4)
     layers, nmb = 2, gbs // 2                                   # micro-batches of 2 sequences on one rank
-    scatters = dry.count("slab_moe_scatter")
+    scatters = dry.count("slab_moe_scatter") + dry.count("slab_moe_scatter_sorted")
+    # every expert-ordered scatter is honoured exactly once: by a GEMM that waits inside the kernel or by a wait kernel
+    assert dry.count("slab_moe_scatter_sorted") == dry.waited_in_kernel + dry.count("slab_moe_wait_experts")
+    if "fp8=true" not in extra and not any(x.startswith("moe_keep_dispatched_factor=") for x in extra) \
+            and "recompute_granularity=none" not in extra:        # kept activations are copies: those wait first
+        assert dry.count("slab_moe_wait_experts") == 0          # bf16 route: no wait for a whole exchange anywhere
     if any(x.startswith("moe_keep_dispatched_factor=") for x in extra):
         assert scatters == layers * nmb * 2                  # forward dispatch + backward of combine; no re-dispatch
     elif "recompute_granularity=none" in extra:

@@ -193,6 +193,8 @@ def test_adamw_flat(cops, kind, p_dtype):
     g.shard = (0.02 * torch.randn(n, device="cuda")).to(p_dtype)
     g.full = g.shard
     g.sharded = True
+    de = 128 * 30                                   # the tail of the shard holds 1-D parameters: no weight decay there
+    g.shard_decay_end = lambda: de
     p_ref = g.shard.float().clone()
     m_ref, v_ref = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
     m, v = _Moment(n, kind, "cuda"), _Moment(n, kind, "cuda", sqrt_domain=(kind != "fp32"))
@@ -201,13 +203,17 @@ def test_adamw_flat(cops, kind, p_dtype):
         grad = torch.randn(n, device="cuda") * 1e-2
         g.grad_shard = grad.clone()
         cops.adamw_flat(g, m, v, coef, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
-        ref.adamw_step(p_ref, grad * 0.5, m_ref, v_ref, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
-                       weight_decay=0.1, step=step)
+        for lo, hi, wd in ((0, de, 0.1), (de, n, 0.0)):
+            ref.adamw_step(p_ref[lo:hi], grad[lo:hi] * 0.5, m_ref[lo:hi], v_ref[lo:hi], lr=1e-2, beta1=0.9, beta2=0.95,
+                           eps=1e-8, weight_decay=wd, step=step)
     tol = {"fp32": 1e-5, "bf16": 3e-2, "fp8": 0.3}[kind]
     if p_dtype == torch.bfloat16:
         tol = max(tol, 2e-2)
     # compare the *update* (p - p0 is O(lr)); relative tolerance on the parameter itself
     _close(g.shard, p_ref, tol, 1e-2 * tol + (1e-3 if p_dtype == torch.bfloat16 else 0))
+    if kind == "fp32" and p_dtype == torch.float32:
+        # the boundary is exact: with decay everywhere the tail would differ by lr * wd * p per step
+        assert torch.allclose(g.shard[de:], p_ref[de:], atol=1e-7)
 
 
 def test_sumsq(cops):

@@ -322,3 +322,23 @@ def test_checkpoint_cli_inspect_verify_consolidate(tmp_path, capsys):
     victim = next((tmp_path / "two").glob("step_*/rank_00001.pt"))
     victim.write_bytes(victim.read_bytes()[:-100])
     assert ckpt_cli(["verify", two]) == 1
+
+
+def test_norm_gains_are_excluded_from_weight_decay():
+    """1-D parameters sit at the tail of their flat group and get no weight decay: with a zero learning-rate effect
+    removed (huge eps kills the Adam term) a matrix shrinks by (1 - lr * wd) per step and a norm gain does not move."""
+    import torch
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "global_batch_size=4", "micro_batch_size=4", "expert_model_parallel_size=1", "device=cpu", "lr=0.1",
+        "weight_decay=0.5", "adam_eps=1e30", "clip_grad=0.0"])
+    tr = Trainer(cfg)
+    layer = tr.engine.model.layers[0]
+    g0, w0 = layer.attn_norm.weight.detach().clone(), layer.attn.wqkv.detach().clone()
+    for grp in tr.engine.all_groups():
+        assert all(p.dim() > 1 for p, o in zip(grp.params, grp.offsets) if o < grp.decay_numel)
+        assert all(p.dim() <= 1 for p, o in zip(grp.params, grp.offsets) if o >= grp.decay_numel)
+    tr.train_step()
+    assert torch.allclose(layer.attn_norm.weight, g0, atol=1e-6)
+    assert torch.allclose(layer.attn.wqkv, w0 * (1 - 0.1 * 0.5), rtol=1e-5, atol=1e-7)
