@@ -104,12 +104,17 @@ def train_equivalence(rank, world):
     out = {}
     # fused+push: the expert GEMM epilogues push result rows to the token owners (with the selective recompute
     # that skips the dead second GEMM and combine in the recomputed forward)
-    for name, disp, push, gran in (("alltoall", "alltoall", "false", "full"), ("fused", "fused", "false", "full"),
-                                   ("fused+push", "fused", "true", "selective")):
+    # fused+push+overlap: the remote half of every scatter on a side stream beside the expert GEMM that waits for the
+    # rows expert by expert; token-ordered: the earlier scatter with one flag per source and a wait kernel
+    for name, disp, push, gran, extra in (
+            ("alltoall", "alltoall", "false", "full", []), ("fused", "fused", "false", "full", []),
+            ("fused+push", "fused", "true", "selective", []),
+            ("fused+push+overlap", "fused", "true", "selective", ["moe_scatter_overlap=true"]),
+            ("token-ordered", "fused", "true", "selective", ["moe_expert_ordered_dispatch=false"])):
         cfg = Config.load(preset="qwen3-30b-a3b", overrides=[
             "num_layers=2", "num_experts=16", "seq_length=512", "vocab_size=4096", "micro_batch_size=2",
             f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}", f"recompute_granularity={gran}",
-            "device=cuda", f"moe_token_dispatcher_type={disp}", f"moe_combine_push={push}"])
+            "device=cuda", f"moe_token_dispatcher_type={disp}", f"moe_combine_push={push}"] + extra)
         tr = Trainer(cfg) if name == "alltoall" else Trainer(cfg, mesh=mesh, device=dev)
         mesh, dev = tr.mesh, tr.device
         out[name] = [float(tr.train_step()["loss"]) for _ in range(3)]
@@ -165,8 +170,6 @@ def layout_equivalence(rank, world):
     return out
 
 
-@pytest.mark.skipif(os.environ.get("SLAB_EXPERIMENTAL") != "1",
-                    reason="layouts verified on CPU ranks only so far: set SLAB_EXPERIMENTAL=1 for their first GPU run")
 def test_tensor_parallel_and_hybrid_sharding_match_expert_parallel():
     world = min(torch.cuda.device_count(), 4)
     for r in _run("layout_equivalence", world):
@@ -194,3 +197,5 @@ def test_training_loss_matches_between_dispatchers():
     for r in res:
         assert r["fused"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
         assert r["fused+push"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
+        assert r["fused+push+overlap"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
+        assert r["token-ordered"] == pytest.approx(r["alltoall"], rel=2e-2, abs=5e-2)
