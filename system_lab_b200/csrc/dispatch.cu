@@ -410,7 +410,6 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
                           const int* __restrict__ expert_offsets, const int* __restrict__ expert_counts, int e_local,
                           int pad, int* __restrict__ chunk_done, int part) {
   __shared__ int ip[MAX_EXPERTS + 1];
-  __shared__ int last_chunk;
   for (int i = threadIdx.x; i <= E; i += blockDim.x) ip[i] = item_prefix[i];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
@@ -526,19 +525,19 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
       if (pair_scalar && lane == 0) reinterpret_cast<float*>(pb + ws.scalars)[row] = pair_scalar[p];
       if (ws.origin >= 0 && lane == 0) reinterpret_cast<int*>(pb + ws.origin)[row] = (me << 24) | p;
     }
-    // chunk complete: fence this block's peer stores, count it, and let the last chunk of the expert release the flag
-    __threadfence_system();
+    // chunk complete: the barrier orders every thread's peer stores before thread 0, whose system-scope fence
+    // (cumulative) publishes them ahead of the chunk count; the block that counts the expert's last chunk fences
+    // again (acquiring the other blocks' chunks) and releases the flag
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const int done = atomicAdd(&chunk_done[e], 1);
-      last_chunk = (done == n_chunks - 1);
-      if (last_chunk) {
+      if (done == n_chunks - 1) {
         chunk_done[e] = 0;
         __threadfence_system();
         st_release_sys(reinterpret_cast<int*>(pb + ws.eflag) + me * e_local + (e - d * e_local), epoch);
       }
     }
-    __syncthreads();
   }
 }
 

@@ -218,7 +218,8 @@ class Engine:
                                              capacity_factor=m.moe_capacity_factor,
                                              push=m.moe_combine_push and self.mesh.ep > 1,   # nothing to overlap on one rank
                                              keep_factor=m.moe_keep_dispatched_factor if self.selective else 0.0)
-                    shared.expert_ordered = m.moe_expert_ordered_dispatch
+                    # (one rank: nothing arrives from anywhere, the token-ordered scatter reads every row once)
+                    shared.expert_ordered = m.moe_expert_ordered_dispatch and self.mesh.ep > 1
                     shared.overlap = m.moe_scatter_overlap and self.mesh.ep > 1
                 layer.ffn.dispatcher = shared
             else:

@@ -322,7 +322,9 @@ def test_gemm_that_waits_for_rows_gives_up_with_a_status_code():
     ds = _make(2, 64, 2, 8, 256)
     d = ds[0]
     idx = torch.stack([torch.randperm(8, device="cuda")[:2] for _ in range(64)]).int()
-    plans = [dd.plan_finish(*dd.plan_publish(idx)) for dd in ds]
+    plans = [dd.plan_finish(*p) for dd, p in zip(ds, [dd.plan_publish(idx) for dd in ds])]   # publish all, then finish all
+    torch.cuda.synchronize()
+    cops.check_status()
     rdy = d.scatter_ordered(plans[0], torch.randn(64, 256, device="cuda", dtype=torch.bfloat16), None, 0)
     ds[1].scatter_ordered(plans[1], torch.randn(64, 256, device="cuda", dtype=torch.bfloat16), None, 0)
     rdy.epoch = 1 << 30
@@ -336,7 +338,10 @@ def test_gemm_that_waits_for_rows_gives_up_with_a_status_code():
     finally:
         cops.lib().slab_moe_set_wait_limit_ms(60000)
         cops.clear_status()
+    w.fill_(1.0)
     out = cops.grouped_gemm_raw(0, d.rows[0], w, plans[0].expert_offsets, plans[0].expert_counts, 128, 256)
     torch.cuda.synchronize()
     cops.check_status()                     # the next launch on the same context is healthy
-    assert float(out.float().abs().max()) == 0.0
+    o0, c0 = int(plans[0].expert_offsets[0]), int(plans[0].expert_counts[0])
+    want = d.rows[0][o0:o0 + c0].float().sum(-1, keepdim=True).expand(c0, 128)
+    assert torch.allclose(out[o0:o0 + c0].float(), want, rtol=2e-2, atol=0.25)
