@@ -192,6 +192,8 @@ def main() -> int:
     for _ in range(args.warmup):
         out = trainer.train_step()
         float(out["loss"])
+        if dev.type == "cuda":
+            trainer.check_device_status()      # a kernel that gave up (bounded wait, capacity) ends the run here
     # ---- device-timed region: K steps, inputs already on the device, no host read inside ----------------
     staged = []
     for i in range(args.steps):
