@@ -111,6 +111,7 @@ class ReadyFlags:
         self.flags = d.eflags[channel]
         self.world = d.ep
         self.consumed = False
+        self.gemm_max_ctas = 0               # > 0: SMs the consuming GEMM may take (the rest run the held-back scatter)
 
     def mark_consumed(self) -> None:
         self.consumed = True
@@ -119,6 +120,7 @@ class ReadyFlags:
         """One small kernel that waits for every (source, expert) flag: afterwards every row has arrived."""
         if not self.consumed:
             d = self.d
+            d.join_side()                    # a held-back remote half must be under way before anything waits for rows
             cops.call("slab_moe_wait_experts", ctypes.addressof(d._peer_ptrs), ctypes.addressof(d._lay[self.channel]),
                       d.ep, d.me, d.E // d.ep, self.epoch, d.status, cops.stream())
             self.consumed = True
@@ -182,7 +184,12 @@ class FusedDispatcher:
         # overlap: with real peers the remote half of a scatter runs on a side stream beside the consuming GEMM (the
         # local half goes first on the compute stream; the GEMM waits only on flags other GPUs set)
         self.overlap = False
+        self.overlap_sms = 16             # SMs the consuming GEMM leaves to the remote half of the scatter
+        self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
+                         if (device is not None and torch.device(device).type == "cuda" and torch.cuda.is_available())
+                         else 148)
         self._side = None
+        self._deferred = None
         self._bwd_ready = None
         # typed views of this rank's regions
         self.rows = [workspace.view(off["rows0"], (cap, H), torch.bfloat16),
@@ -271,40 +278,57 @@ class FusedDispatcher:
 
     def scatter_ordered(self, plan: FusedPlan, x, scalars, channel: int, scale_in=None, fp8: bool = False) -> ReadyFlags:
         """Expert-ordered scatter (``csrc/dispatch.cu: moe_scatter_sorted_kernel``); returns the arrival flags the
-        consumer of this rank's receive buffer has to honour.  With ``overlap`` the rows for this rank are written
-        first on the compute stream and the rows for the peers on a side stream, which the compute stream joins
-        after the consumer has been launched (:meth:`join_side`)."""
+        consumer of this rank's receive buffer has to honour.
+
+        With ``overlap`` (real peers only) the exchange runs beside the expert GEMM that consumes it.  A persistent
+        GEMM block takes a whole SM's shared memory, so nothing else can share an SM with it: the two kernels get
+        disjoint SMs instead.  The rows for this rank are written now, on the compute stream; the rows for the peers
+        are held back until the consumer has been launched on ``sm_count - overlap_sms`` SMs (``ReadyFlags.
+        gemm_max_ctas``), then :meth:`join_side` launches them on a side stream, sized to fit the SMs left over, and
+        makes the compute stream wait for that stream.  Every rank's GEMM waits only for flags that other GPUs'
+        scatters set, and every rank's scatter always has SMs of its own, so the exchange cannot wait for itself."""
         ep = self._next_epoch()
 
-        def launch(part: int) -> None:
+        def launch(part: int, n_blocks: int = 0) -> None:
             cops.call("slab_moe_scatter_sorted", x, scalars, scale_in, plan.pair_loc, plan.perm,
                       plan.tokens_per_expert_global, plan.send_prefix, plan.item_prefix, plan.num_tokens, plan.topk,
                       self.H, self.E, ctypes.addressof(self._peer_ptrs), ctypes.addressof(self._lay[channel]), self.ep,
                       self.me, ep, plan.expert_offsets, plan.expert_counts, plan.e_local, self.pad, 1 if fp8 else 0,
-                      self.chunk_done, part, 0, cops.stream())
+                      self.chunk_done, part, n_blocks, cops.stream())
 
+        rdy = ReadyFlags(self, channel, ep)
         if self.overlap and self.ep > 1 and self.device is not None and torch.device(self.device).type == "cuda":
-            launch(2)                                     # this rank's own rows: the consumer needs them in order
-            if self._side is None:
-                self._side = torch.cuda.Stream(device=self.device)
-            main = torch.cuda.current_stream(self.device)
-            self._side.wait_stream(main)
-            for t in (x, scalars, scale_in):              # keep the inputs alive until the side stream has read them
-                if isinstance(t, torch.Tensor):
-                    t.record_stream(self._side)
-            with torch.cuda.stream(self._side):
-                launch(1)                                 # rows for the peers, beside whatever the compute stream runs next
-            self._side_pending = True
+            self.join_side()                              # a previous exchange nobody joined yet
+            launch(2)                                     # this rank's own rows: the consumer finds them in stream order
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            keep = [t for t in (x, scalars, scale_in) if isinstance(t, torch.Tensor)]
+            self._deferred = (lambda: launch(1, self.overlap_sms * self.SCATTER_CTAS_PER_SM), ev, keep)
+            rdy.gemm_max_ctas = max(self.sm_count - self.overlap_sms, 1)
         else:
             launch(0)
-        return ReadyFlags(self, channel, ep)
+        return rdy
+
+    SCATTER_CTAS_PER_SM = 3          # 256-thread blocks of the scatter kernel one SM holds (80 registers per thread)
 
     def join_side(self) -> None:
-        """The compute stream waits for the side-stream half of the last scatter (call after the consumer of the
-        received rows has been launched; later kernels may reuse the scatter's inputs and counters)."""
-        if getattr(self, "_side_pending", False):
-            torch.cuda.current_stream(self.device).wait_stream(self._side)
-            self._side_pending = False
+        """Launch the held-back remote half of the last scatter on the side stream (it starts after this rank's own
+        rows were written, not after what the compute stream has enqueued since) and make the compute stream wait
+        for it.  Call right after the consumer of the received rows has been launched."""
+        pending = getattr(self, "_deferred", None)
+        if pending is None:
+            return
+        self._deferred = None
+        fn, ev, keep = pending
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        main = torch.cuda.current_stream(self.device)
+        self._side.wait_event(ev)
+        for t in keep:                                    # inputs stay allocated until the side stream has read them
+            t.record_stream(self._side)
+        with torch.cuda.stream(self._side):
+            fn()
+        main.wait_stream(self._side)
 
     def take_bwd_ready(self):
         """Arrival flags of the gradient rows the last backward of combine is delivering (None if it already waited)."""

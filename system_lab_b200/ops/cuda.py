@@ -455,8 +455,10 @@ def grouped_gemm_raw(mode: int, a, b, offsets, counts, n: int, k: int, out=None,
             out = torch.empty(e, n, k, dtype=torch.bfloat16, device=a.device)
     if ready is not None and mode != 2:
         call("slab_grouped_gemm_bf16", mode, a, b, out, offsets, counts, e, r, n, k, 1 if accumulate else 0,
-             block_n, max_ctas, ready.flags, int(ready.world), int(ready.epoch), status_word(a.device), stream())
+             block_n, int(getattr(ready, "gemm_max_ctas", 0) or max_ctas), ready.flags, int(ready.world),
+             int(ready.epoch), status_word(a.device), stream())
         ready.mark_consumed()
+        ready.d.join_side()              # the remote half of the exchange, held back until this launch, starts now
         return out
     if ready is not None:
         ready.wait()
