@@ -25,6 +25,8 @@ for _name, _sig in {
     "slab_fsdp_reduce_scatter": "plppiiiifpps",
     "slab_fsdp_reduce_scatter_adamw": "lppiiiif" + "ppppp" + "p" + "fffffff" + "l" + "pps",
     "slab_fsdp_set_wait_limit_ms": "l",
+    "slab_fsdp_gather_range": "plllppiiiips",
+    "slab_dense_gemm_gather": "pppp" + "iiii" + "p" + "llll" + "pp" + "iiii" + "pip" + "ps",
 }.items():
     cops.register(_name, _sig)
 
@@ -70,6 +72,43 @@ class FsdpPeerComm:
         self._stage(src, slot, ep, ack)
         cops.call("slab_fsdp_all_gather", dst, nbytes, ctypes.addressof(self._ptrs), ctypes.addressof(self._lay),
                   self.world, self.rank, slot, ep, self.status, self.done, cops.stream())
+
+    # ---- all-gather fused into the first GEMM that consumes the gathered weights -----------------------------------
+    PIECE_BYTES = 256 * 1024
+
+    def begin_gather(self, dst: torch.Tensor, src: torch.Tensor, head_bytes: int):
+        """First half of a fused all-gather: stage this rank's shard and pull only the bytes behind ``head_bytes`` of
+        the gathered buffer (the group's 1-D parameters, which the layer's norm reads before its first GEMM).  The
+        head -- the matrices -- is gathered by :meth:`gemm_gather`, inside the GEMM that multiplies the first of them
+        (or by :meth:`finish_gather` if no such GEMM comes).  Returns the ticket both take."""
+        src = src.contiguous()
+        nbytes = src.numel() * src.element_size()
+        self._ensure(nbytes)
+        slot, ep, ack = self._next()
+        self._stage(src, slot, ep, ack)
+        total = nbytes * self.world
+        head = min(max(head_bytes, 0), total) // 512 * 512          # the GEMM gathers [0, head_up), the tail kernel the rest
+        head_up = min((head_bytes + 511) // 512 * 512, total // 512 * 512)
+        if head < total:
+            cops.call("slab_fsdp_gather_range", dst, head, total, nbytes, ctypes.addressof(self._ptrs),
+                      ctypes.addressof(self._lay), self.world, self.rank, slot, ep, self.status, cops.stream())
+        return {"slot": slot, "epoch": ep, "shard_bytes": nbytes, "head_bytes": head_up, "total": total}
+
+    def gemm_gather(self, ticket, x2: torch.Tensor, w: torch.Tensor, out2: torch.Tensor, flat: torch.Tensor, w_off: int,
+                    seg, pieces: torch.Tensor, call_index: int, block_n: int) -> None:
+        """``out2 = x2 @ w^T`` while the kernel gathers bytes ``[0, head_bytes)`` of ``flat`` from the staged shards
+        (``csrc/gemm_tcgen05.cu``, gather warp) and acknowledges the slot."""
+        n, k = w.shape
+        cops.call("slab_dense_gemm_gather", x2, out2, seg[0], seg[1], x2.shape[0], n, k, block_n, flat,
+                  w_off * 2, ticket["head_bytes"], ticket["shard_bytes"], self.PIECE_BYTES,
+                  ctypes.addressof(self._ptrs), ctypes.addressof(self._lay), self.world, self.rank, ticket["slot"],
+                  ticket["epoch"], pieces, call_index, self.done, self.status, cops.stream())
+
+    def finish_gather(self, ticket, dst: torch.Tensor) -> None:
+        """Plain gather of everything (and the acknowledgement) for a ticket no GEMM consumed."""
+        cops.call("slab_fsdp_all_gather", dst, ticket["shard_bytes"], ctypes.addressof(self._ptrs),
+                  ctypes.addressof(self._lay), self.world, self.rank, ticket["slot"], ticket["epoch"], self.status,
+                  self.done, cops.stream())
 
     def reduce_scatter(self, grad_full: torch.Tensor, fg=None, scale: float = 1.0) -> torch.Tensor:
         """bf16 ``grad_full`` (``world * shard`` elements) -> fp32 sum of every rank's slice ``rank``."""

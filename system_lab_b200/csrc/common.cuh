@@ -216,6 +216,26 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status
   return true;
 }
 
+// Wait until *p >= want for a counter other blocks of this GPU advance (device scope).  Bounded.
+__device__ __forceinline__ bool wait_count_ge(const int* p, int want, int* status, uint64_t limit_ns = SLAB_WAIT_NS) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  if (v >= want) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v >= want) return true;
+    if ((++spins & 63u) == 0) {
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+        return false;
+      }
+      __nanosleep(32);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

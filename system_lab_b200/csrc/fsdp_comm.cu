@@ -106,6 +106,22 @@ fsdp_gather_kernel(uint4* __restrict__ dst, long n16, FsPeers peers, FsLayout la
   fs_ack(peers, lay, world, me, slot, epoch, done_counter);
 }
 
+// dst[lo .. hi) (byte offsets inside the gathered buffer) <- the staged shards that hold those bytes.  No
+// acknowledgement: the kernel that gathers the rest of the buffer (the fused dense GEMM, or fsdp_gather_kernel)
+// acknowledges the slot.  Used for the small tail of a flat group (its 1-D parameters), which the layer reads before
+// its first GEMM.
+__global__ void __launch_bounds__(256)
+fsdp_gather_range_kernel(uint8_t* __restrict__ dst, long lo, long hi, long shard_bytes, FsPeers peers, FsLayout lay,
+                         int world, int me, int slot, int epoch, int* status, unsigned long long limit_ns) {
+  __shared__ int ok;
+  if (!fs_wait_ready(peers, lay, world, me, slot, epoch, status, limit_ns, &ok)) return;
+  for (long o = lo + (blockIdx.x * (long)blockDim.x + threadIdx.x) * 16; o < hi; o += (long)gridDim.x * blockDim.x * 16) {
+    const int r = (int)(o / shard_bytes);
+    *reinterpret_cast<uint4*>(dst + o) =
+        *reinterpret_cast<const uint4*>(peers.base[r] + lay.slots + slot * lay.slot_bytes + (o - (long)r * shard_bytes));
+  }
+}
+
 struct FsAdam {
   float lr, beta1, beta2, eps, wd, bc1, bc2;
   long decay_end;     // elements [0, decay_end) of the shard get weight decay (the tail holds the 1-D parameters)
@@ -253,5 +269,19 @@ extern "C" int slab_fsdp_reduce_scatter_adamw(long shard_numel, const long* peer
   fsdp_reduce_scatter_kernel<true><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
       nullptr, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, master,
       m, v, (__nv_bfloat16*)out_bf16, coef, sq_out, a, status, g_fs_limit_ns, done_counter);
+  return (int)cudaGetLastError();
+}
+
+// dst[lo, hi) <- staged shards (see fsdp_gather_range_kernel); lo and hi multiples of 16, the slot not acknowledged.
+extern "C" int slab_fsdp_gather_range(void* dst, long lo, long hi, long shard_bytes, const long* peer_ptrs,
+                                      const long* layout, int world, int me, int slot, int epoch, int* status,
+                                      cudaStream_t st) {
+  if (lo % 16 || hi % 16 || shard_bytes % 16 || world > FS_MAX_WORLD || hi > shard_bytes * world) return -100;
+  if (hi <= lo) return 0;
+  long items = (hi - lo) / 16;
+  int grid = (int)((items + 255) / 256);
+  if (grid > 296) grid = 296;
+  fsdp_gather_range_kernel<<<grid, 256, 0, st>>>((uint8_t*)dst, lo, hi, shard_bytes, fs_peers(peer_ptrs, world),
+                                                 fs_layout(layout), world, me, slot, epoch, status, g_fs_limit_ns);
   return (int)cudaGetLastError();
 }

@@ -50,6 +50,20 @@ struct GemmParams {
   const int* ready;
   int ready_world, ready_epoch;
   unsigned long long ready_limit_ns;
+  // fused all-gather of the weight operand's flat buffer (GATHER, forward only): a seventh warp in every CTA pulls
+  // this CTA's share of every piece of [0, g_bytes) of the flat parameter buffer from the ranks' staged shards
+  // (plain 16-byte peer loads) and counts the piece; the TMA producer loads a weight tile only after the pieces
+  // that cover it are complete.  Pieces are visited starting at the multiplied weight, so the GEMM's first tiles
+  // wait for a few hundred KB, and the rest of the buffer (the layer's other matrices) arrives while it runs.
+  const uint8_t* g_src[16];   // every rank's staging slot (this call's slot), peer pointers
+  uint8_t* g_dst;             // local flat buffer
+  long g_bytes, g_shard_bytes, g_piece_bytes, g_w_off;
+  int g_pieces, g_first_piece, g_target;
+  int* g_piece_count;         // [g_pieces] monotonic: a complete piece holds g_target
+  const int* g_ready;         // [world] staged flags of this slot (epoch valued), set by the peers' stage kernels
+  int* g_ack[16];             // every rank's ack word for (slot, me): released when this rank has read the slot
+  int g_world, g_epoch;
+  int* g_done;                // CTAs that finished gathering (reset by the last one)
 };
 
 // Shared memory map (exactly the 227 KB a CTA may have): [0, 3072) barriers, TMEM slot, abort flag and the
@@ -115,8 +129,8 @@ __device__ __forceinline__ bool get_tile(int t, const int* prefix, const GemmPar
 // row's pair index, over NVLink with plain peer stores: the transfer of tile i overlaps the MMAs of tile i+1.
 // When the last CTA has fenced its stores it releases this rank's push flag on every peer; the token owners
 // wait for all flags and reduce their K rows locally (moe_combine_kernel<., true>).
-template <int MODE, int BN, bool PUSH = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int MODE, int BN, bool PUSH = false, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? GEMM_THREADS + 32 : GEMM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using L = SmemLayout<BN>;
@@ -200,6 +214,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         asm volatile("fence.proxy.async.global;" ::: "memory");
         last_e = ti.e;
       }
+      if (GATHER && MODE == MODE_FWD) {
+        // the weight tile's bytes inside the flat buffer -> the pieces that cover them, one piece per lane
+        const long t0 = p.g_w_off + ((long)ti.e * p.N + (long)ti.n_idx * BN) * p.K * 2;
+        long t1 = t0 + (long)BN * p.K * 2;
+        const long w_end = p.g_w_off + (long)p.E * p.N * p.K * 2;
+        if (t1 > w_end) t1 = w_end;
+        const int p0 = (int)(t0 / p.g_piece_bytes), p1 = (int)((t1 - 1) / p.g_piece_bytes);
+        bool mine = true;
+        for (int q = p0 + lane; q <= p1 && mine; q += 32) {
+          if (q < p.g_pieces) mine = wait_count_ge(p.g_piece_count + q, p.g_target, p.status, p.ready_limit_ns);
+        }
+        ok = __all_sync(0xffffffffu, mine);
+        if (!ok) {
+          if (lane == 0) *abort_flag = 1;
+          break;
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
       if (lane == 0) {
         for (int ks = 0; ks < ti.ksteps; ++ks) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -262,6 +294,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!ok) break;
         umma_commit(&tfull_bar[buf]);           // accumulator complete
         ++it;
+      }
+    }
+  } else if (GATHER && warp == 6) {
+    // ------------------------------------------------------------ gather warp (see GemmParams)
+    bool good = true;
+    if (lane < p.g_world) good = wait_flag_ge(p.g_ready + lane, p.g_epoch, p.status, p.ready_limit_ns);
+    good = __all_sync(0xffffffffu, good);
+    const long unit = 512;                                  // one warp iteration: 32 lanes x 16 bytes
+    for (int i = 0; i < p.g_pieces; ++i) {
+      const int piece = (p.g_first_piece + i) % p.g_pieces;
+      const long lo = (long)piece * p.g_piece_bytes;
+      long hi = lo + p.g_piece_bytes;
+      if (hi > p.g_bytes) hi = p.g_bytes;
+      if (good) {
+        for (long u = lo + (long)blockIdx.x * unit; u < hi; u += (long)gridDim.x * unit) {
+          const long o = u + lane * 16;
+          if (o < hi) {
+            const int r = (int)(o / p.g_shard_bytes);
+            const uint4 v = *reinterpret_cast<const uint4*>(p.g_src[r] + (o - (long)r * p.g_shard_bytes));
+            *reinterpret_cast<uint4*>(p.g_dst + o) = v;
+          }
+        }
+      }
+      __threadfence();                                      // this warp's stores before the count (device scope)
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.g_piece_count + piece, 1); // counted even after a timeout: waiters never hang on us
+    }
+    // the slot has been read by this CTA; the last CTA tells every peer it may reuse it
+    __syncwarp();
+    if (lane == 0) {
+      const int ticket = atomicAdd(p.g_done, 1);
+      if (ticket == (int)gridDim.x - 1) {
+        *p.g_done = 0;
+        __threadfence_system();
+        for (int r = 0; r < p.g_world; ++r) st_release_sys(p.g_ack[r], p.g_epoch);
       }
     }
   } else {
@@ -418,7 +485,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 }
 
 // ---------------------------------------------------------------- host side (tensor maps: tma_host.cuh)
-template <int MODE, int BN, bool PUSH = false>
+template <int MODE, int BN, bool PUSH = false, bool GATHER = false>
 static int launch(const void* A, const void* B, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   CUtensorMap ma, mb;
@@ -442,12 +509,12 @@ static int launch(const void* A, const void* B, const GemmParams& p, int grid, c
     if ((rc = tma_make_map_bf16(&mc, p.C, p.R, (MODE == MODE_FWD) ? p.N : p.K, BM, 64))) return rc;
   }
   static bool attr_set = false;
-  auto kern = grouped_gemm_kernel<MODE, BN, PUSH>;
+  auto kern = grouped_gemm_kernel<MODE, BN, PUSH, GATHER>;
   if (!attr_set) {
     SLAB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_set = true;
   }
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
+  kern<<<grid, GATHER ? GEMM_THREADS + 32 : GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
   return (int)cudaGetLastError();
 }
 
@@ -518,4 +585,58 @@ extern "C" int slab_grouped_gemm_bf16_push(int mode, const void* A, const void* 
   if (mode == MODE_FWD)
     return wide ? launch<MODE_FWD, 256, true>(A, B, p, grid, stream) : launch<MODE_FWD, 128, true>(A, B, p, grid, stream);
   return wide ? launch<MODE_DGRAD, 256, true>(A, B, p, grid, stream) : launch<MODE_DGRAD, 128, true>(A, B, p, grid, stream);
+}
+
+// Dense forward GEMM C[R, N] = A[R, K] * W[N, K]^T fused with the all-gather of the flat parameter buffer W lives
+// in (FSDP): every rank has staged its shard of the buffer in its symmetric slot (slab_fsdp_stage); this kernel
+// pulls bytes [0, gather_bytes) of the buffer from the ranks' slots into `flat` while it multiplies, loading a
+// weight tile as soon as the pieces that cover it have arrived, and acknowledges the slot to every peer at the end.
+//   W = flat + w_off_bytes; shard_bytes = bytes of the buffer every rank stages (multiple of 256);
+//   layout = {ready_flags, ack_flags, slots, slot_bytes} byte offsets inside a workspace (fsdp_comm.cu);
+//   piece_count: int [ceil(gather_bytes / piece_bytes)], zero before the first call, never reset: call number c
+//   (1-based, every call with the same SM count) passes target = c * number of SMs;  done_counter: zeroed int.
+//   seg_offsets / seg_counts: device ints {0} and {R} (the single segment of a dense GEMM).
+extern "C" int slab_dense_gemm_gather(const void* A, void* C, const int* seg_offsets, const int* seg_counts, int R,
+                                      int N, int K, int block_n, void* flat,
+                                      long w_off_bytes, long gather_bytes, long shard_bytes, long piece_bytes,
+                                      const long* peer_ptrs, const long* layout, int world, int me, int slot,
+                                      int epoch, int* piece_count, int call_index, int* done_counter, int* status,
+                                      cudaStream_t stream) {
+  using namespace slab;
+  if (K % 64 || N % 64 || world < 1 || world > 16 || me < 0 || me >= world) return -100;
+  if (gather_bytes % 512 || shard_bytes % 256 || piece_bytes % 512 || piece_bytes <= 0 || w_off_bytes % 256) return -101;
+  if (gather_bytes > shard_bytes * world || w_off_bytes + (long)N * K * 2 > gather_bytes) return -102;
+  GemmParams p{};
+  p.seg_offsets = seg_offsets;
+  p.seg_counts = seg_counts;
+  p.E = 1;
+  p.R = R;
+  p.N = N;
+  p.K = K;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.status = status;
+  p.ready_limit_ns = slab_moe_wait_limit_ns();
+  const long ready_off = layout[0], ack_off = layout[1], slots_off = layout[2], slot_bytes = layout[3];
+  for (int r = 0; r < 16; ++r) {
+    p.g_src[r] = r < world ? reinterpret_cast<const uint8_t*>(peer_ptrs[r]) + slots_off + (long)slot * slot_bytes : nullptr;
+    p.g_ack[r] = r < world ? reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(peer_ptrs[r]) + ack_off) + slot * 16 + me
+                           : nullptr;
+  }
+  p.g_dst = static_cast<uint8_t*>(flat);
+  p.g_bytes = gather_bytes;
+  p.g_shard_bytes = shard_bytes;
+  p.g_piece_bytes = piece_bytes;
+  p.g_w_off = w_off_bytes;
+  p.g_pieces = (int)((gather_bytes + piece_bytes - 1) / piece_bytes);
+  p.g_first_piece = (int)(w_off_bytes / piece_bytes);
+  p.g_piece_count = piece_count;
+  p.g_ready = reinterpret_cast<const int*>(reinterpret_cast<const uint8_t*>(peer_ptrs[me]) + ready_off) + slot * 16;
+  p.g_world = world;
+  p.g_epoch = epoch;
+  p.g_done = done_counter;
+  const int grid = sm_count();
+  p.g_target = call_index * grid;
+  const void* B = static_cast<const uint8_t*>(flat) + w_off_bytes;
+  return block_n != 128 ? launch<MODE_FWD, 256, false, true>(A, B, p, grid, stream)
+                        : launch<MODE_FWD, 128, false, true>(A, B, p, grid, stream);
 }

@@ -75,10 +75,15 @@ def swiglu_probs(gate_up, probs, rows_dev=None):
 def linear(x, weight):
     """``x @ weight^T`` for a dense projection (no bias).  bf16 CUDA operands whose shapes the tile sizes cover run on
     the hand-written tcgen05 GEMM (forward, input gradient and weight gradient); everything else is the library."""
+    fg = getattr(weight, "_flat_group", None)
+    pending = fg is not None and fg.pending_gather is not None      # the group's matrices are still on their owners
     if weight.dtype != x.dtype:
         weight = weight.to(x.dtype)
     if use_kernels(x) and _DENSE_KERNELS[0] and _cuda().linear_ok(x, weight):
-        return _cuda().linear(x, weight)
+        # FSDP: this GEMM pulls the layer's matrices from the peers while it multiplies the first of them
+        return _cuda().linear(x, weight, fg.take_pending_gather(weight) if pending else None)
+    if pending:
+        fg.finish_pending_gather()
     return torch.nn.functional.linear(x, weight)
 
 

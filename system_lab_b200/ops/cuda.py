@@ -679,7 +679,7 @@ class _Linear(torch.autograd.Function):
     carries ``main_grad``."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, gather=None):
         shp = x.shape
         n, k = w.shape
         x2 = x.reshape(-1, k)
@@ -688,7 +688,13 @@ class _Linear(torch.autograd.Function):
         off, cnt = _dense_segments(x.device, x2.shape[0])
         # the result is allocated in its final shape (callers rotate q and k in place: it must not be a view made here)
         out = torch.empty(*shp[:-1], n, dtype=torch.bfloat16, device=x.device)
-        grouped_gemm_raw(0, x2, w, off, cnt, n, k, out=out.view(-1, n), block_n=_pick_bn(n))
+        if gather is not None:
+            # FSDP all-gather fused into this GEMM: the kernel's gather warps pull the flat buffer's matrices from the
+            # ranks' staged shards while its tiles are multiplied (csrc/gemm_tcgen05.cu, GATHER)
+            gather["comm"].gemm_gather(gather["ticket"], x2, w, out.view(-1, n), gather["flat"], gather["w_off"],
+                                       (off, cnt), gather["pieces"], gather["call"], _pick_bn(n))
+        else:
+            grouped_gemm_raw(0, x2, w, off, cnt, n, k, out=out.view(-1, n), block_n=_pick_bn(n))
         ctx.save_for_backward(x2, w, off, cnt)
         ctx.w_ref = w
         ctx.shp = shp
@@ -713,7 +719,7 @@ class _Linear(torch.autograd.Function):
                 ctx.w_ref.main_grad_written = True
             else:
                 dw = grouped_gemm_raw(2, g2, x2, off, cnt, n, k, block_n=_pick_bn(k)).view(n, k)
-        return dx, dw
+        return dx, dw, None
 
 
 def linear_ok(x, w) -> bool:
@@ -721,8 +727,8 @@ def linear_ok(x, w) -> bool:
             and w.shape[0] % _N_MULTIPLE == 0 and x.numel() > 0 and w.is_contiguous())
 
 
-def linear(x, w):
-    return _Linear.apply(x, w)
+def linear(x, w, gather=None):
+    return _Linear.apply(x, w, gather)
 
 
 # ------------------------------------------------------------------------------ attention

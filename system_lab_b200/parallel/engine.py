@@ -60,7 +60,7 @@ class _UnitFn(torch.autograd.Function):
         ctx.engine, ctx.unit, ctx.extra = engine, unit, extra
         recompute = engine.recompute or engine.inference      # forward-only passes keep no graph
         ctx.recompute = recompute
-        unit.gather()
+        unit.gather(fused=True)          # dense matrices may arrive inside the first GEMM that multiplies one of them
         engine.after_gather(unit, forward=True)
         engine.prefetch_neighbour(unit, +1)
         x_needs_grad = x.is_floating_point()
@@ -179,6 +179,11 @@ class Engine:
             if l.is_moe:
                 l.ffn.keep_dispatched = self.selective and cfg.model.moe_keep_dispatched_factor != 0
         self.head_unit = add("head", self.model.head) if self.model.head is not None else None
+        if cfg.parallel.fsdp_gather_in_gemm and dense_comm is not None and not cfg.parallel.fsdp_prefetch:
+            for u in self.layer_units:
+                for g in u.groups:
+                    if g.comm is dense_comm and g.name.endswith("/dense") and g.sharded:
+                        g.fuse_gather = True
         self._make_dispatchers()
         self._unit_index = {u.name: i for i, u in enumerate(self.units)}
         self._prefetch_stream = None

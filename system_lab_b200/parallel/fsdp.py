@@ -96,6 +96,14 @@ class FlatGroup:
         self.tp_replicas = 1                            # tensor-parallel ranks holding identical copies of this group
         self.prefetch_comm = None                       # second peer-comm instance used only by prefetch()
         self._pf_event = None                           # set while a prefetched gather is in flight
+        # all-gather fused into the first GEMM that multiplies one of the group's matrices (forward passes of decoder
+        # layers; set by the engine): gather() stages the shard and pulls only the 1-D tail, the GEMM pulls the rest
+        self.fuse_gather = False
+        self.pending_gather = None                      # ticket of a gather whose matrices have not been pulled yet
+        self._gather_pieces = None
+        self._gather_calls = 0
+        for p in self.params:
+            p._flat_group = self
 
     def finalize(self) -> None:
         """Take the owned shard (the optimizer's source of truth) from the initialised full buffer."""
@@ -165,7 +173,40 @@ class FlatGroup:
             ev.record(stream)
         self._pf_event = ev
 
-    def gather(self) -> None:
+    def param_offset(self, p) -> int:
+        for q, o in zip(self.params, self.offsets):
+            if q is p:
+                return o
+        raise KeyError("parameter is not part of this flat group")
+
+    def take_pending_gather(self, w):
+        """Called by the dense linear op before it multiplies ``w``: the ticket of a gather that still has to pull the
+        group's matrices, plus what the fused kernel needs, if ``w`` can be the GEMM that does it; otherwise the
+        gather is completed the plain way first and None is returned."""
+        ticket = self.pending_gather
+        if ticket is None:
+            return None
+        self.pending_gather = None
+        try:
+            w_off = self.param_offset(w)
+        except KeyError:
+            w_off = -1
+        if w_off < 0 or w.dim() != 2 or (w_off + w.numel()) * 2 > ticket["head_bytes"]:
+            self.comm.finish_gather(ticket, self.full.data)
+            return None
+        if self._gather_pieces is None:
+            n = (self.total * 2 + self.comm.PIECE_BYTES - 1) // self.comm.PIECE_BYTES
+            self._gather_pieces = torch.zeros(n, dtype=torch.int32, device=self.device)
+        self._gather_calls += 1
+        return {"ticket": ticket, "w_off": w_off, "pieces": self._gather_pieces, "call": self._gather_calls,
+                "flat": self.full.data, "comm": self.comm, "group": self}
+
+    def finish_pending_gather(self) -> None:
+        if self.pending_gather is not None:
+            ticket, self.pending_gather = self.pending_gather, None
+            self.comm.finish_gather(ticket, self.full.data)
+
+    def gather(self, fused: bool = False) -> None:
         if self.gathered:
             return
         if self._pf_event is not None:
@@ -181,13 +222,17 @@ class FlatGroup:
             # write through an alias with its own version counter: autograd may hold parameter views
             # saved by a forward that ran before this (re-)gather, and the values are the same
             dst = self.full.data
-            if self.comm is not None:
+            if fused and self.fuse_gather and self.comm is not None and hasattr(self.comm, "begin_gather") \
+                    and self.compute_dtype == torch.bfloat16:
+                self.pending_gather = self.comm.begin_gather(dst, src, self.decay_numel * 2)
+            elif self.comm is not None:
                 self.comm.all_gather(dst, src, self)
             else:
                 dist.all_gather_into_tensor(dst, src.contiguous(), group=self.group)
         self.gathered = True
 
     def release(self) -> None:
+        self.finish_pending_gather()          # a staged slot must be read and acknowledged even if nobody multiplied
         if self.sharded and self.gathered:
             self.full.untyped_storage().resize_(0)
             self.gathered = False
@@ -283,9 +328,9 @@ class Unit:
     def __init__(self, name: str, module: nn.Module, groups: list[FlatGroup]):
         self.name, self.module, self.groups = name, module, groups
 
-    def gather(self):
+    def gather(self, fused: bool = False):
         for g in self.groups:
-            g.gather()
+            g.gather(fused)
 
     def prefetch(self, stream):
         for g in self.groups:

@@ -94,3 +94,48 @@ def test_reduce_scatter_fused_adamw_matches_two_step():
         assert torch.allclose(masters[r], refs[r], atol=1e-6)
         assert torch.allclose(outs[r].float(), refs[r], atol=2e-3)
     assert abs(sq.item() - total.pow(2).sum().item()) / total.pow(2).sum().item() < 1e-4
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_fused_into_the_consuming_gemm(world):
+    """A flat parameter buffer (three matrices, then a tail of 1-D parameters) sharded over `world` ranks: every rank
+    stages its shard and pulls the tail, then multiplies by the second matrix with the kernel whose gather warps pull
+    all matrices from the staged shards.  Afterwards every rank holds the whole buffer, the product equals the fp32
+    reference, and the slots have been acknowledged (six rounds reuse the four slots).  Ranks are emulated phase by
+    phase: every rank stages before any rank's GEMM starts."""
+    from system_lab_b200.ops import cuda as cops
+    torch.manual_seed(11)
+    dev = torch.device("cuda")
+    k, n0, n1, n2 = 512, 256, 1152, 384                       # matrices [n, k]; the GEMM multiplies the second one
+    mats = (n0 + n1 + n2) * k
+    tail = 128 * 5
+    total = (mats + tail + 128 * world - 1) // (128 * world) * (128 * world)
+    shard = total // world
+    cs = _comms(world, shard * 2)
+    pieces = [torch.zeros((total * 2 + cs[0].PIECE_BYTES - 1) // cs[0].PIECE_BYTES, dtype=torch.int32, device=dev)
+              for _ in range(world)]
+    rows = 777
+    for call in range(1, 7):
+        flat_ref = (0.05 * torch.randn(total, device=dev)).to(torch.bfloat16)
+        x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+        fulls = [torch.full((total,), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+        tickets = [c.begin_gather(fulls[r], flat_ref[r * shard:(r + 1) * shard].clone(), mats * 2)
+                   for r, c in enumerate(cs)]
+        torch.cuda.synchronize()
+        for r in range(world):                                 # the tail is there before any GEMM runs
+            assert torch.equal(fulls[r][mats:], flat_ref[mats:])
+        outs = []
+        for r, c in enumerate(cs):
+            w_off = n0 * k
+            w = fulls[r][w_off:w_off + n1 * k].view(n1, k)
+            out = torch.empty(rows, n1, device=dev, dtype=torch.bfloat16)
+            c.gemm_gather(tickets[r], x, w, out, fulls[r], w_off, cops._dense_segments(dev, rows), pieces[r], call,
+                          cops._pick_bn(n1))
+            outs.append(out)
+        torch.cuda.synchronize()
+        cops.check_status()
+        want = x.float() @ flat_ref[n0 * k:(n0 + n1) * k].view(n1, k).float().t()
+        for r in range(world):
+            assert torch.equal(fulls[r], flat_ref), f"rank {r}: gathered buffer differs (call {call})"
+            err = (outs[r].float() - want).abs().max().item()
+            assert err < 2e-2 * (want.abs().max().item() + 1e-6), (r, call, err)
