@@ -74,13 +74,19 @@ class FsdpPeerComm:
                   self.world, self.rank, slot, ep, self.status, self.done, cops.stream())
 
     # ---- all-gather fused into the first GEMM that consumes the gathered weights -----------------------------------
-    PIECE_BYTES = 256 * 1024
+    PIECE_BYTES = 1024 * 1024
 
     def begin_gather(self, dst: torch.Tensor, src: torch.Tensor, head_bytes: int):
         """First half of a fused all-gather: stage this rank's shard and pull only the bytes behind ``head_bytes`` of
         the gathered buffer (the group's 1-D parameters, which the layer's norm reads before its first GEMM).  The
         head -- the matrices -- is gathered by :meth:`gemm_gather`, inside the GEMM that multiplies the first of them
         (or by :meth:`finish_gather` if no such GEMM comes).  Returns the ticket both take."""
+        ticket = self.stage_for_gather(src, head_bytes)
+        self.gather_tail(ticket, dst)
+        return ticket
+
+    def stage_for_gather(self, src: torch.Tensor, head_bytes: int):
+        """Stage this rank's shard (sets flags only: the emulated-rank tests run this phase for every rank first)."""
         src = src.contiguous()
         nbytes = src.numel() * src.element_size()
         self._ensure(nbytes)
@@ -89,10 +95,14 @@ class FsdpPeerComm:
         total = nbytes * self.world
         head = min(max(head_bytes, 0), total) // 512 * 512          # the GEMM gathers [0, head_up), the tail kernel the rest
         head_up = min((head_bytes + 511) // 512 * 512, total // 512 * 512)
-        if head < total:
-            cops.call("slab_fsdp_gather_range", dst, head, total, nbytes, ctypes.addressof(self._ptrs),
-                      ctypes.addressof(self._lay), self.world, self.rank, slot, ep, self.status, cops.stream())
-        return {"slot": slot, "epoch": ep, "shard_bytes": nbytes, "head_bytes": head_up, "total": total}
+        return {"slot": slot, "epoch": ep, "shard_bytes": nbytes, "head_bytes": head_up, "tail_from": head, "total": total}
+
+    def gather_tail(self, ticket, dst: torch.Tensor) -> None:
+        """Pull the bytes behind the matrices (waits for every rank's staged flag)."""
+        if ticket["tail_from"] < ticket["total"]:
+            cops.call("slab_fsdp_gather_range", dst, ticket["tail_from"], ticket["total"], ticket["shard_bytes"],
+                      ctypes.addressof(self._ptrs), ctypes.addressof(self._lay), self.world, self.rank, ticket["slot"],
+                      ticket["epoch"], self.status, cops.stream())
 
     def gemm_gather(self, ticket, x2: torch.Tensor, w: torch.Tensor, out2: torch.Tensor, flat: torch.Tensor, w_off: int,
                     seg, pieces: torch.Tensor, call_index: int, block_n: int) -> None:

@@ -96,11 +96,24 @@ fsdp_gather_kernel(uint4* __restrict__ dst, long n16, FsPeers peers, FsLayout la
                    int epoch, int* status, unsigned long long limit_ns, int* done_counter) {
   __shared__ int ok;
   if (fs_wait_ready(peers, lay, world, me, slot, epoch, status, limit_ns, &ok)) {
+    // four peer loads per thread are issued before the first store: four times the bytes in flight over NVLink
     const long total = n16 * world;
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-      const int r = int(i / n16);
-      const long j = i - r * n16;
-      dst[i] = reinterpret_cast<const uint4*>(peers.base[r] + lay.slots + slot * lay.slot_bytes)[j];
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i0 = blockIdx.x * (long)blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const long i = i0 + q * stride;
+        if (i < total) {
+          const int r = int(i / n16);
+          v[q] = reinterpret_cast<const uint4*>(peers.base[r] + lay.slots + slot * lay.slot_bytes)[i - r * n16];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const long i = i0 + q * stride;
+        if (i < total) dst[i] = v[q];
+      }
     }
   }
   fs_ack(peers, lay, world, me, slot, epoch, done_counter);

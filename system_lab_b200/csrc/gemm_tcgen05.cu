@@ -301,19 +301,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     bool good = true;
     if (lane < p.g_world) good = wait_flag_ge(p.g_ready + lane, p.g_epoch, p.status, p.ready_limit_ns);
     good = __all_sync(0xffffffffu, good);
-    const long unit = 512;                                  // one warp iteration: 32 lanes x 16 bytes
+    // One warp per CTA moves this CTA's share of a piece in units of 512 bytes (32 lanes x 16 bytes), GU units at a
+    // time: all GU peer loads of a lane are issued before the first store, so a lane keeps GU x 16 bytes in flight
+    // over NVLink instead of one load per round trip.
+    constexpr int GU = 16;
+    const long unit = 512;
     for (int i = 0; i < p.g_pieces; ++i) {
       const int piece = (p.g_first_piece + i) % p.g_pieces;
       const long lo = (long)piece * p.g_piece_bytes;
       long hi = lo + p.g_piece_bytes;
       if (hi > p.g_bytes) hi = p.g_bytes;
       if (good) {
-        for (long u = lo + (long)blockIdx.x * unit; u < hi; u += (long)gridDim.x * unit) {
-          const long o = u + lane * 16;
-          if (o < hi) {
-            const int r = (int)(o / p.g_shard_bytes);
-            const uint4 v = *reinterpret_cast<const uint4*>(p.g_src[r] + (o - (long)r * p.g_shard_bytes));
-            *reinterpret_cast<uint4*>(p.g_dst + o) = v;
+        const long step = (long)gridDim.x * unit;
+        for (long u0 = lo + (long)blockIdx.x * unit; u0 < hi; u0 += GU * step) {
+          uint4 v[GU];
+#pragma unroll
+          for (int q = 0; q < GU; ++q) {
+            const long o = u0 + q * step + lane * 16;
+            if (o < hi) {
+              const int r = (int)(o / p.g_shard_bytes);
+              v[q] = *reinterpret_cast<const uint4*>(p.g_src[r] + (o - (long)r * p.g_shard_bytes));
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < GU; ++q) {
+            const long o = u0 + q * step + lane * 16;
+            if (o < hi) *reinterpret_cast<uint4*>(p.g_dst + o) = v[q];
           }
         }
       }

@@ -119,8 +119,9 @@ def test_all_gather_fused_into_the_consuming_gemm(world):
         flat_ref = (0.05 * torch.randn(total, device=dev)).to(torch.bfloat16)
         x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
         fulls = [torch.full((total,), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
-        tickets = [c.begin_gather(fulls[r], flat_ref[r * shard:(r + 1) * shard].clone(), mats * 2)
-                   for r, c in enumerate(cs)]
+        tickets = [c.stage_for_gather(flat_ref[r * shard:(r + 1) * shard].clone(), mats * 2) for r, c in enumerate(cs)]
+        for r, c in enumerate(cs):                             # every rank has staged: now the tails can be pulled
+            c.gather_tail(tickets[r], fulls[r])
         torch.cuda.synchronize()
         for r in range(world):                                 # the tail is there before any GEMM runs
             assert torch.equal(fulls[r][mats:], flat_ref[mats:])
