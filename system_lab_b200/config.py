@@ -122,7 +122,7 @@ class ParallelConfig:
     num_distributed_optimizer_instances: int = 1
     fsdp_fused_collectives: bool = True  # peer-memory all-gather / reduce-scatter kernels instead of NCCL
     fsdp_prefetch: bool = False          # gather the next unit's parameters on a side stream while this one computes
-    fsdp_gather_in_gemm: bool = False    # forward: a decoder layer's dense matrices are all-gathered inside the first GEMM that multiplies one of them (peer collectives only)
+    fsdp_gather_in_gemm: bool = True     # forward: a decoder layer's dense matrices are all-gathered inside the first GEMM that multiplies one of them (peer collectives only)
 
 
 @dataclass
