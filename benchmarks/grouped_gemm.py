@@ -138,6 +138,16 @@ def main():
                                              args.iters, flush=flush, name="fc1_fwd_fp8_rowwise"), fl1)
         rec("fc2_fwd_fp8_rowwise", time_cuda(lambda: cops.grouped_gemm_fp8_rowwise_raw(ar, ars, w2r, w2rs, off_d, cnt_d),
                                              args.iters, flush=flush, name="fc2_fwd_fp8_rowwise"), fl2)
+        # input gradients on the fp8 path: dY quantised per row, the weight from its cached [E, K, N] e4m3 copy
+        g1q, g1s = cops.quant_rowwise(dy1)
+        g2q, g2s = cops.quant_rowwise(dy2)
+        w1t, w1ts = cops._transposed_rowwise_weight(w1)
+        w2t, w2ts = cops._transposed_rowwise_weight(w2)
+        rec("fc1_dgrad_fp8_rowwise", time_cuda(lambda: cops.grouped_gemm_fp8_rowwise_raw(g1q, g1s, w1t, w1ts, off_d, cnt_d),
+                                               args.iters, flush=flush, name="fc1_dgrad_fp8_rowwise"), fl1)
+        rec("fc2_dgrad_fp8_rowwise", time_cuda(lambda: cops.grouped_gemm_fp8_rowwise_raw(g2q, g2s, w2t, w2ts, off_d, cnt_d),
+                                               args.iters, flush=flush, name="fc2_dgrad_fp8_rowwise"), fl2)
+        rec("quant_rowwise dY1", time_cuda(lambda: cops.quant_rowwise(dy1), args.iters, flush=flush, name="quant_row_dy1"), 0.0)
         rec("quant_rowwise x", time_cuda(lambda: cops.quant_rowwise(x), args.iters, flush=flush, name="quant_row_x"), 0.0)
         rec("quant_1x128 x", time_cuda(lambda: cops.quant_1x128(x), args.iters, flush=flush, name="quant_x"), 0.0)
         rec("quant_128x128 w1", time_cuda(lambda: cops.quant_128x128(w1), args.iters, flush=flush, name="quant_w1"), 0.0)

@@ -129,6 +129,7 @@ class ParallelConfig:
 class PrecisionConfig:
     params_dtype: str = "fp32"           # fp32 | bf16
     fp8: bool = False                    # fp8 (e4m3) forward of the expert GEMMs, bf16 backward
+    fp8_dgrad: bool = False              # with fp8: input gradients of the expert GEMMs in e4m3 as well (row-scaled, transposed weight copy cached per optimizer step); weight gradients stay bf16
     fp8_recipe: str = "rowwise"          # rowwise (per token row / per output channel, full fp8 rate) | tensorwise (one scale per tensor, same kernel) | blockwise (1x128 act, 128x128 weight)
     num_layers_at_start_in_bf16: int = 0
     num_layers_at_end_in_bf16: int = 0

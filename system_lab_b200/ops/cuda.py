@@ -575,6 +575,40 @@ class _GroupedLinear(torch.autograd.Function):
         return da, dw, None, None, None, None, None, None, None
 
 
+_WT_CACHE = {}
+FP8_DGRAD = [False]
+WEIGHT_GENERATION = [0]      # bumped by the optimizer every step: kernels update weights without autograd noticing
+
+
+def set_fp8_dgrad(on: bool) -> None:
+    """Input gradients of the fp8 expert GEMMs in e4m3 too (row-scaled recipe; weight gradients stay bf16)."""
+    FP8_DGRAD[0] = bool(on)
+
+
+def _transposed_rowwise_weight(w):
+    """e4m3 copy of ``w`` in the layout its input gradient needs: ``[E, K, N]`` with one scale per (expert, k) row, so
+    the reduction over N keeps constant scales.  Cached per weight storage and version: it is rebuilt once after each
+    optimizer step, not per GEMM (the NK-layout cache of ``summary/fp8_expert_gemm_optimization.md:107-116``)."""
+    key = (w.data_ptr(), tuple(w.shape))
+    ver = (w._version, WEIGHT_GENERATION[0])
+    ent = _WT_CACHE.get(key)
+    if ent is None or ent[0] != ver:
+        if len(_WT_CACHE) > 512:
+            _WT_CACHE.clear()
+        q, s = quant_rowwise(w.transpose(1, 2).contiguous())
+        ent = (ver, q, s.contiguous())
+        _WT_CACHE[key] = ent
+    return ent[1], ent[2]
+
+
+def grouped_gemm_fp8_dgrad_rowwise(g, w, offsets, counts, out=None):
+    """``da[r, k] = sum_n g[r, n] * w[e, n, k]`` on the fp8 tensor path: ``g`` quantised per row, ``w`` per (expert, k)
+    from its cached transposed copy, the row-scaled forward kernel run with N as the reduction."""
+    gq, gs = quant_rowwise(g)
+    wq, ws = _transposed_rowwise_weight(w)
+    return grouped_gemm_fp8_rowwise_raw(gq, gs, wq, ws, offsets, counts, out=out)
+
+
 class _GroupedLinearFp8(torch.autograd.Function):
     """Forward in e4m3 on the tensor cores' fp8 path, backward in bf16 on the saved bf16 operands (the reference's
     fused fp8 grouped GEMM keeps dW in bf16 too, ``summary/fp8_expert_gemm_optimization.md:137-143``).  Operands
@@ -610,6 +644,27 @@ class _GroupedLinearFp8(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
+        a, w, offsets, counts = ctx.saved_tensors
+        e, n, k = w.shape
+        if (FP8_DGRAD[0] and ctx.needs_input_grad[0] and not hasattr(ctx.dgrad_out, "launch") and n % 128 == 0
+                and k % 64 == 0 and getattr(ctx, "bwd_ready", None) is None):
+            # input gradient in e4m3 (row-scaled), weight gradient in bf16 on the saved bf16 operands
+            g = g.contiguous()
+            do = ctx.dgrad_out
+            if do is not None and (do.shape[0] < g.shape[0] or do.shape[1] != k):
+                do = None
+            da = grouped_gemm_fp8_dgrad_rowwise(g, w, offsets, counts, out=do)
+            da = da[:g.shape[0]]
+            dw = None
+            if ctx.needs_input_grad[1]:
+                mg = getattr(ctx.w_ref, "main_grad", None)
+                if mg is not None:
+                    grouped_gemm_raw(2, g, a, offsets, counts, n, k, out=mg, accumulate=ctx.w_ref.main_grad_written,
+                                     block_n=_pick_bn(k))
+                    ctx.w_ref.main_grad_written = True
+                else:
+                    dw = grouped_gemm_raw(2, g, a, offsets, counts, n, k, block_n=_pick_bn(k))
+            return (da, dw) + (None,) * 7
         return _GroupedLinear.backward(ctx, g)          # same arity: (da, dw) + one None per remaining input
 
 

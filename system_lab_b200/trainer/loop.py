@@ -67,6 +67,9 @@ class Trainer:
         else:
             ops.set_kernel_mode("auto")
         ops.set_dense_kernels(cfg.train.dense_gemm_kernels)
+        if self.device.type == "cuda":
+            from ..ops import cuda as _cops
+            _cops.set_fp8_dgrad(cfg.precision.fp8 and cfg.precision.fp8_dgrad)
         torch.manual_seed(cfg.train.seed)
         self.engine = Engine(cfg, mesh, self.device)
         t = cfg.train

@@ -169,8 +169,18 @@ class ShardedAdamW:
             g.sync_low_precision()
         g.grad_shard = None
 
+    @staticmethod
+    def _new_weight_generation() -> None:
+        """Cached derivatives of the weights (quantised copies) are stale after this step's update."""
+        try:
+            from ..ops import cuda as cops
+            cops.WEIGHT_GENERATION[0] += 1
+        except Exception:
+            pass
+
     def begin_step(self, lr: float | None = None) -> None:
         """Call before backward when the update runs inside backward."""
+        self._new_weight_generation()
         self.step_count += 1
         self._cur_lr = self.lr if lr is None else lr
         self._sq_accum = torch.zeros(1, dtype=torch.float32, device=self.engine.device)
@@ -214,6 +224,7 @@ class ShardedAdamW:
         return self.last_grad_norm
 
     def step(self, lr: float | None = None) -> torch.Tensor:
+        self._new_weight_generation()
         self.step_count += 1
         lr = self.lr if lr is None else lr
         norm = self.global_grad_norm()

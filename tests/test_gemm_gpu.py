@@ -197,3 +197,20 @@ def test_linear_cross_entropy_on_own_gemms_matches_reference():
     assert abs(float(loss) - float(lr)) < 2e-2
     _check(h.grad, hr.grad, "ce dh")
     _check(w.grad, wr.grad, "ce dw")
+
+
+@pytest.mark.parametrize("counts,n,k", [([100, 0, 300, 129], 512, 256), ([5, 700, 64, 1], 768, 2048)])
+def test_fp8_row_scaled_input_gradient(counts, n, k):
+    """dgrad on the fp8 path: dY quantised per row, the weight from its transposed e4m3 copy (one scale per expert and
+    k), against the fp32 product of the same bf16 operands; the cached copy is rebuilt when the weight changes."""
+    from system_lab_b200.ops import cuda, reference as ref
+    a, dy, w, off, cnt = _inputs(counts, n, k, 5)
+    out = cuda.grouped_gemm_fp8_dgrad_rowwise(dy, w, off, cnt)
+    want = ref.grouped_gemm_dgrad(dy, w, off, cnt)
+    cuda.check_status()
+    err = (out.float() - want.float()).abs().max().item()
+    assert err < 8e-2 * (want.float().abs().max().item() + 1e-6), err          # e4m3 operands: ~6 % relative noise
+    w.mul_(2.0)                                                                 # version bump: the cache must notice
+    out2 = cuda.grouped_gemm_fp8_dgrad_rowwise(dy, w, off, cnt)
+    err2 = (out2.float() - 2 * want.float()).abs().max().item()
+    assert err2 < 8e-2 * (2 * want.float().abs().max().item() + 1e-6), err2
