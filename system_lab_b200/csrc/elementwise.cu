@@ -51,10 +51,9 @@ __device__ __forceinline__ float row_sum(float v, float (*red)[NORM_WARPS], int 
   return t;
 }
 
-// y = (x [+ res]) * rstd * w ; optionally writes xpr = x + res and rstd.  The loads of the next row are issued
-// before the current row is reduced and written, so every warp keeps two rows' worth of requests in flight.
+// y = (x [+ res]) * rstd * w ; optionally writes xpr = x + res and rstd.
 template <bool RESIDUAL, int RW, int CH>
-__global__ void __launch_bounds__(NORM_THREADS, CH <= 2 ? 2 : 1)
+__global__ void __launch_bounds__(NORM_THREADS, CH <= 4 ? 2 : 1)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ xpr, float* __restrict__ rstd_out, int rows, int H, float eps) {
@@ -64,38 +63,30 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int rg = warp / RW;
   const int li = (warp % RW) * 32 + lane;
   const int nvec = H >> 3;
-  const bf16x8* wp = reinterpret_cast<const bf16x8*>(w);
-  const long stride = (long)gridDim.x * RPB;
-  long r = (long)blockIdx.x * RPB + rg;
-  bf16x8 xv[CH], rv[CH];
-  if (r < rows) {
+  bf16x8 wv[CH];
 #pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const int c = li + i * 32 * RW;
-      if (c < nvec) {
-        xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c];
-        if (RESIDUAL) rv[i] = reinterpret_cast<const bf16x8*>(res + (size_t)r * H)[c];
-      }
-    }
+  for (int i = 0; i < CH; ++i) {
+    const int c = li + i * 32 * RW;
+    if (c < nvec) wv[i] = reinterpret_cast<const bf16x8*>(w)[c];
   }
   int it = 0;
-  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += stride, r += stride, ++it) {
+  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += (long)gridDim.x * RPB, ++it) {
+    const long r = r0 + rg;
     const bool active = r < rows;
-    const long rn = r + stride;
-    bf16x8 xn[CH], rn_v[CH];
-    if (CH <= 4 && rn < rows) {
+    float vals[CH][8];
+    float ss = 0.f;
+    if (active) {
+      const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)r * H);
+      const bf16x8* rr = RESIDUAL ? reinterpret_cast<const bf16x8*>(res + (size_t)r * H) : nullptr;
+      bf16x8 xv[CH], rv[CH];
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int c = li + i * 32 * RW;
         if (c < nvec) {
-          xn[i] = reinterpret_cast<const bf16x8*>(x + (size_t)rn * H)[c];
-          if (RESIDUAL) rn_v[i] = reinterpret_cast<const bf16x8*>(res + (size_t)rn * H)[c];
+          xv[i] = xr[c];
+          if (RESIDUAL) rv[i] = rr[c];
         }
       }
-    }
-    float vals[CH][8];
-    float ss = 0.f;
-    if (active) {
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int c = li + i * 32 * RW;
@@ -123,26 +114,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         const int c = li + i * 32 * RW;
         if (c < nvec) {
           float wf[8], o[8];
-          unpack8(wp[c], wf);
+          unpack8(wv[i], wf);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wf[j];
           reinterpret_cast<bf16x8*>(y + (size_t)r * H)[c] = pack8(o);
-        }
-      }
-    }
-    if (CH <= 4) {
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        xv[i] = xn[i];
-        if (RESIDUAL) rv[i] = rn_v[i];
-      }
-    } else if (rn < rows) {            // very wide rows: no room to hold two rows, load the next one now
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int c = li + i * 32 * RW;
-        if (c < nvec) {
-          xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)rn * H)[c];
-          if (RESIDUAL) rv[i] = reinterpret_cast<const bf16x8*>(res + (size_t)rn * H)[c];
         }
       }
     }
@@ -154,10 +129,9 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // blocks to arrive sums the group's rows into row gridDim.x + group, and the last group to arrive sums those into
 // the bf16 result -- a fixed summation order, so the result does not depend on which block arrives when.
 // `scratch`: fp32 [gridDim.x + groups, H], contents irrelevant on entry.  `counters`: int [NORM_COUNTERS], all zero
-// on entry and all zero again when the kernel ends.  x and g of the next row are requested before the current row
-// is reduced (two rows in flight per warp group).
+// on entry and all zero again when the kernel ends.
 template <bool ADD_RES, int RW, int CH>
-__global__ void __launch_bounds__(NORM_THREADS, CH <= 2 ? 2 : 1)
+__global__ void __launch_bounds__(NORM_THREADS, CH <= 4 ? 2 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ gres, __nv_bfloat16* __restrict__ dx,
@@ -178,45 +152,27 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __r
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
   }
-  const long stride = (long)gridDim.x * RPB;
-  long r = (long)blockIdx.x * RPB + rg;
-  bf16x8 xv[CH], gv[CH];
-  float rstd = 0.f;
-  if (r < rows) {
-    rstd = rstd_in[r];
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const int c = li + i * 32 * RW;
-      if (c < nvec) {
-        xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c];
-        gv[i] = reinterpret_cast<const bf16x8*>(g + (size_t)r * H)[c];
-      }
-    }
-  }
   int it = 0;
-  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += stride, r += stride, ++it) {
+  for (long r0 = (long)blockIdx.x * RPB; r0 < rows; r0 += (long)gridDim.x * RPB, ++it) {
+    const long r = r0 + rg;
     const bool active = r < rows;
-    const long rn = r + stride;
-    bf16x8 xn[CH], gn[CH], ev[CH];
-    float rstd_n = 0.f;
-    if (CH <= 4 && rn < rows) {
-      rstd_n = rstd_in[rn];
+    bf16x8 xv[CH], gv[CH], ev[CH];
+    float rstd = 0.f, dot = 0.f;
+    if (active) {
+      rstd = rstd_in[r];
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int c = li + i * 32 * RW;
         if (c < nvec) {
-          xn[i] = reinterpret_cast<const bf16x8*>(x + (size_t)rn * H)[c];
-          gn[i] = reinterpret_cast<const bf16x8*>(g + (size_t)rn * H)[c];
+          xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)r * H)[c];
+          gv[i] = reinterpret_cast<const bf16x8*>(g + (size_t)r * H)[c];
+          if (ADD_RES) ev[i] = reinterpret_cast<const bf16x8*>(gres + (size_t)r * H)[c];
         }
       }
-    }
-    float dot = 0.f;
-    if (active) {
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int c = li + i * 32 * RW;
         if (c < nvec) {
-          if (ADD_RES) ev[i] = reinterpret_cast<const bf16x8*>(gres + (size_t)r * H)[c];
           float xf[8], gf[8], wf[8];
           unpack8(xv[i], xf);
           unpack8(gv[i], gf);
@@ -249,24 +205,6 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __r
             for (int j = 0; j < 8; ++j) o[j] += e[j];
           }
           reinterpret_cast<bf16x8*>(dx + (size_t)r * H)[c] = pack8(o);
-        }
-      }
-    }
-    if (CH <= 4) {
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        xv[i] = xn[i];
-        gv[i] = gn[i];
-      }
-      rstd = rstd_n;
-    } else if (rn < rows) {            // very wide rows: no room to hold two rows, load the next one now
-      rstd = rstd_in[rn];
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int c = li + i * 32 * RW;
-        if (c < nvec) {
-          xv[i] = reinterpret_cast<const bf16x8*>(x + (size_t)rn * H)[c];
-          gv[i] = reinterpret_cast<const bf16x8*>(g + (size_t)rn * H)[c];
         }
       }
     }
@@ -739,12 +677,12 @@ static inline int grid_for(long work_items, int threads, int per_sm = 8) {
 
 using namespace slab;
 
-// Warps per row and chunks per thread for a hidden size (see the thread mapping above): at most 2 chunks per
-// thread up to H = 4096, 4 up to 8192, 8 beyond.
+// Warps per row and chunks per thread for a hidden size (see the thread mapping above): at most 4 chunks per
+// thread up to H = 8192, 8 beyond.
 static void norm_shape(int H, int* rw, int* ch) {
   const int nvec = H / 8;
   int r = 1;
-  while (r < NORM_WARPS && nvec > 32 * r * 2) r *= 2;
+  while (r < NORM_WARPS && nvec > 32 * r * 4) r *= 2;
   int per = (nvec + 32 * r - 1) / (32 * r);
   int c = 1;
   while (c < per) c *= 2;
@@ -755,7 +693,7 @@ static void norm_shape(int H, int* rw, int* ch) {
 static int norm_grid(int rows, int rw, int ch, int max_grid) {
   const int rpb = NORM_WARPS / rw;
   long want = ((long)rows + rpb - 1) / rpb;
-  int cap = sm_count_cached() * (ch <= 2 ? 2 : 1);
+  int cap = sm_count_cached() * (ch <= 4 ? 2 : 1);
   if (cap > NORM_MAX_GRID) cap = NORM_MAX_GRID;
   if (cap > max_grid) cap = sm_count_cached() <= max_grid ? sm_count_cached() : max_grid;   // whole waves where possible
   if (want < 1) want = 1;
@@ -765,10 +703,10 @@ static int norm_grid(int rows, int rw, int ch, int max_grid) {
 #define SLAB_NORM_DISPATCH(LAUNCH)                     \
   do {                                                 \
     if (rw == 1 && ch == 1) LAUNCH(1, 1);              \
-    else if (rw == 1) LAUNCH(1, 2);                    \
-    else if (rw == 2) LAUNCH(2, 2);                    \
-    else if (rw == 4) LAUNCH(4, 2);                    \
-    else if (ch <= 2) LAUNCH(8, 2);                    \
+    else if (rw == 1 && ch == 2) LAUNCH(1, 2);         \
+    else if (rw == 1 && ch == 4) LAUNCH(1, 4);         \
+    else if (rw == 2) LAUNCH(2, 4);                    \
+    else if (rw == 4) LAUNCH(4, 4);                    \
     else if (ch <= 4) LAUNCH(8, 4);                    \
     else LAUNCH(8, 8);                                 \
   } while (0)
