@@ -94,6 +94,10 @@ def test_relocation_interval_runs_and_reports():
     assert ratio is not None and ratio >= 1.0
     base = run_ranks(_train, 2, [], 6, False, timeout=400)[0][0]
     assert losses == pytest.approx(base, rel=3e-5, abs=3e-5)
-    early = run_ranks(_train, 1, ["moe_expert_relocation_interval=100", "moe_expert_relocation_first_step=3"], 5, False,
+    early = run_ranks(_train, 2, ["moe_expert_relocation_interval=100", "moe_expert_relocation_first_step=3"], 5, False,
                       timeout=400)[0][1]
     assert [h["step"] for h in early] == [3]
+    # automatic mode: on (once at step 3, then every 50) where experts can move, off on a single rank
+    auto = run_ranks(_train, 2, ["moe_expert_relocation_interval=-1"], 4, False, timeout=400)[0][1]
+    assert [h["step"] for h in auto] == [3]
+    assert run_ranks(_train, 1, ["moe_expert_relocation_interval=-1"], 3, False, timeout=400)[0][1] == []
