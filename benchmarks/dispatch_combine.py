@@ -11,7 +11,7 @@ the launching stream after warm-up, max over ranks:
 * dispatch end to end: fused router kernel (top-k, counts, aux statistics) + plan (count exchange, slot
   assignment) + expert-ordered scatter + wait for every (source, expert) flag -- the whole path from router logits
   to rows in the owners' expert-major buffers;
-* its parts: plan alone; scatter + wait alone, expert-ordered (bf16) and token-ordered (bf16, and the 1x128
+* its parts: plan alone; scatter + wait alone, expert-ordered (bf16; per-lane stores and bulk stores) and token-ordered (bf16, and the 1x128
   block-scaled e4m3 payload with fp32 scales);
 * fused combine (pull + gate-weighted top-k reduction, bf16);
 * the library baseline: sort + `all_to_all_single` + receiver re-sort for dispatch, and the reverse path plus
@@ -110,6 +110,11 @@ def one_case(args, mesh, world, rank, dev, T, routing, link_gbs, sync):
     rec("  plan (count exchange + slots)", timed(lambda: fused.plan(idx), args.iters, args.warmup, sync))
     rec("  scatter + wait, expert-ordered bf16", timed(lambda: fused.scatter_ordered(plan, x, w, 0).wait(),
                                                       args.iters, args.warmup, sync), b_bf16)
+    from system_lab_b200.moe.fused_dispatch import set_scatter_bulk
+    set_scatter_bulk(True)
+    rec("  scatter + wait, expert-ordered bf16, bulk stores", timed(lambda: fused.scatter_ordered(plan, x, w, 0).wait(),
+                                                                   args.iters, args.warmup, sync), b_bf16)
+    set_scatter_bulk(False)
 
     def f_tok():
         ep = fused.scatter(plan, x, w, 0)

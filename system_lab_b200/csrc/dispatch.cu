@@ -400,7 +400,16 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 // `part`: 0 = every destination, 1 = other ranks only, 2 = this rank only (the two halves can be launched
 // separately, e.g. the local half first and the remote half beside the expert GEMM).
 // `chunk_done`: int [E], zero on entry, zero again on exit.
-template <bool FP8, int VPL>
+//
+// BULK (bf16 payload only): a warp stages a row in shared memory, 4 KB at a time in two alternating buffers, and lane 0
+// sends each piece with one bulk store (cp.async.bulk, shared -> global).  The copy engine of the SM then writes the
+// peer's memory in large requests while the warp already loads the next piece; with per-lane 16-byte stores the
+// same warp issues 256 store instructions per 4 KB.  A chunk is complete when every warp's bulk groups are.
+constexpr int SCATTER_SEG_VEC = 256;                     // 16-byte vectors per staged piece (4 KB)
+constexpr int SCATTER_SEG_BYTES = SCATTER_SEG_VEC * 16;
+constexpr int SCATTER_BULK_SMEM = 8 * 2 * SCATTER_SEG_BYTES;      // 8 warps x 2 buffers
+
+template <bool FP8, int VPL, bool BULK>
 __global__ void __launch_bounds__(256)
 moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ pair_scalar,
                           const float* __restrict__ scale_in, const int* __restrict__ pair_loc,
@@ -410,6 +419,8 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
                           const int* __restrict__ expert_offsets, const int* __restrict__ expert_counts, int e_local,
                           int pad, int* __restrict__ chunk_done, int part) {
   __shared__ int ip[MAX_EXPERTS + 1];
+  extern __shared__ __align__(128) uint8_t scatter_smem[];        // BULK: SCATTER_BULK_SMEM bytes, else none
+  int seg_parity = 0;
   for (int i = threadIdx.x; i <= E; i += blockDim.x) ip[i] = item_prefix[i];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
@@ -470,7 +481,44 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
       const int t = p / K;
       const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)t * H);
       const float sc = scale_in ? scale_in[p] : 1.f;
-      if (!FP8) {
+      if (BULK && !FP8) {
+        uint8_t* dst_row = pb + ws.rows + (size_t)row * nvec * 16;
+        for (int s0 = 0; s0 < nvec; s0 += SCATTER_SEG_VEC) {
+          const int nv = min(SCATTER_SEG_VEC, nvec - s0);
+          bf16x8* buf = reinterpret_cast<bf16x8*>(scatter_smem + (size_t)(warp * 2 + seg_parity) * SCATTER_SEG_BYTES);
+          seg_parity ^= 1;
+          bf16x8 regs[SCATTER_SEG_VEC / 32];
+#pragma unroll
+          for (int q = 0; q < SCATTER_SEG_VEC / 32; ++q) {
+            const int c = lane + 32 * q;
+            if (c < nv) regs[q] = src[s0 + c];
+          }
+          // the piece sent two pieces ago from this buffer must have been read out of shared memory
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < SCATTER_SEG_VEC / 32; ++q) {
+            const int c = lane + 32 * q;
+            if (c < nv) {
+              bf16x8 v = regs[q];
+              if (scale_in) {
+                float f[8];
+                unpack8(v, f);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) f[jj] *= sc;
+                v = pack8(f);
+              }
+              buf[c] = v;
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            bulk_store(dst_row + (size_t)s0 * 16, buf, (uint32_t)nv * 16);
+            tma_store_commit();
+          }
+        }
+      } else if (!FP8) {
         bf16x8* dst = reinterpret_cast<bf16x8*>(pb + ws.rows) + (size_t)row * nvec;
         bf16x8 regs[VPL];
 #pragma unroll
@@ -528,6 +576,10 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
     // chunk complete: the barrier orders every thread's peer stores before thread 0, whose system-scope fence
     // (cumulative) publishes them ahead of the chunk count; the block that counts the expert's last chunk fences
     // again (acquiring the other blocks' chunks) and releases the flag
+    if (BULK && !FP8 && lane == 0) {
+      tma_store_wait<0>();                   // this warp's bulk stores have been written, not only read out
+      __threadfence_system();
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
@@ -667,6 +719,14 @@ using namespace slab;
 // is generous; tests that make a wait run out on purpose pass their own short limit.
 static unsigned long long g_wait_limit_ns = 60ull * 1000000000ull;
 
+// Whether the expert-ordered bf16 scatter sends rows with bulk stores out of shared memory (1) or with per-lane
+// 16-byte stores (0).
+static int g_scatter_bulk = 0;
+extern "C" int slab_moe_set_scatter_bulk(int on) {
+  g_scatter_bulk = on ? 1 : 0;
+  return 0;
+}
+
 extern "C" int slab_moe_set_wait_limit_ms(long ms) {
   g_wait_limit_ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
   return 0;
@@ -767,18 +827,27 @@ extern "C" int slab_moe_scatter_sorted(const void* x, const float* pair_scalar, 
   if (n_blocks <= 0) n_blocks = 148 * 4;
   const int vpl = (H / 8 + 31) / 32;
   if (vpl > 32) return -100;
-#define SLAB_SCATTER_S(FP8, VPL)                                                                                     \
-  moe_scatter_sorted_kernel<FP8, VPL><<<n_blocks, 256, 0, st>>>(                                                     \
+#define SLAB_SCATTER_S(FP8, VPL, BULK, SMEM)                                                                         \
+  moe_scatter_sorted_kernel<FP8, VPL, BULK><<<n_blocks, 256, SMEM, st>>>(                                            \
       (const __nv_bfloat16*)x, pair_scalar, scale_in, pair_loc, perm, send_counts, send_prefix, item_prefix, T, K, H, \
       E, pt, ws, world, me, epoch, expert_offsets, expert_counts, e_local, pad, chunk_done, part)
   if (fp8) {
-    if (vpl <= 8) SLAB_SCATTER_S(true, 8);
-    else if (vpl <= 16) SLAB_SCATTER_S(true, 16);
-    else SLAB_SCATTER_S(true, 32);
+    if (vpl <= 8) SLAB_SCATTER_S(true, 8, false, 0);
+    else if (vpl <= 16) SLAB_SCATTER_S(true, 16, false, 0);
+    else SLAB_SCATTER_S(true, 32, false, 0);
+  } else if (g_scatter_bulk) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t err = cudaFuncSetAttribute(moe_scatter_sorted_kernel<false, 8, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SCATTER_BULK_SMEM);
+      if (err != cudaSuccess) return (int)err;
+      attr_set = true;
+    }
+    SLAB_SCATTER_S(false, 8, true, SCATTER_BULK_SMEM);
   } else {
-    if (vpl <= 8) SLAB_SCATTER_S(false, 8);
-    else if (vpl <= 16) SLAB_SCATTER_S(false, 16);
-    else SLAB_SCATTER_S(false, 32);
+    if (vpl <= 8) SLAB_SCATTER_S(false, 8, false, 0);
+    else if (vpl <= 16) SLAB_SCATTER_S(false, 16, false, 0);
+    else SLAB_SCATTER_S(false, 32, false, 0);
   }
 #undef SLAB_SCATTER_S
   return (int)cudaGetLastError();

@@ -33,6 +33,7 @@ for _name, _sig in {
     "slab_moe_wait": "ppiiiips",
     "slab_moe_scatter_sorted": "pppp" + "pppp" + "iiii" + "pp" + "iii" + "pp" + "iii" + "p" + "ii" + "s",
     "slab_moe_wait_experts": "ppiiiips",
+    "slab_moe_set_scatter_bulk": "i",
     "slab_moe_signal_out": "ppiiis",
     "slab_moe_combine": "pppiiippiiipis",
     "slab_moe_combine_scalars": "ppippiiips",
@@ -41,6 +42,12 @@ for _name, _sig in {
     "slab_grouped_gemm_bf16_push": "ipppp" + "iiii" + "ii" + "pp" + "ll" + "iiii" + "pp" + "s",
 }.items():
     cops.register(_name, _sig)
+
+
+def set_scatter_bulk(on: bool) -> None:
+    """Expert-ordered bf16 scatter: send rows with bulk stores out of shared memory (``cp.async.bulk``) instead of
+    per-lane 16-byte stores.  A setting of the kernel library, shared by every dispatcher of the process."""
+    cops.lib().slab_moe_set_scatter_bulk(1 if on else 0)
 
 
 def _align(x: int, a: int = 256) -> int:

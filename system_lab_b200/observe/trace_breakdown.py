@@ -158,6 +158,8 @@ def _union_len(intervals: list[tuple[float, float]]) -> float:
 def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: int = 80) -> dict:
     split_nccl = os.environ.get("SPLIT_NCCL_BY_CPU", "1") != "0"
     steps, kernels, c10d = {}, [], []
+    launches = {}                     # correlation id -> host time of the runtime call that launched it
+    runtime_calls = []                # (ts, dur, name) of every CUDA runtime / driver call on the host
     for ev in _events(path):
         if ev.get("ph") != "X":
             continue
@@ -167,8 +169,14 @@ def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: i
         if name.startswith("ProfilerStep#") and cat in ("user_annotation", "cpu_op", ""):
             steps.setdefault(name, (ts, ts + dur))
         elif cat in ("kernel", "gpu_memcpy", "gpu_memset"):
-            stream = (ev.get("args") or {}).get("stream", ev.get("tid"))
-            kernels.append((ts, dur, name, stream))
+            a = ev.get("args") or {}
+            stream = a.get("stream", ev.get("tid"))
+            kernels.append((ts, dur, name, stream, a.get("correlation")))
+        elif cat in ("cuda_runtime", "cuda_driver"):
+            corr = (ev.get("args") or {}).get("correlation")
+            if corr is not None:
+                launches[corr] = ts
+            runtime_calls.append((ts, dur, name))
         elif cat == "cpu_op" and (name.startswith("c10d::") or name.startswith("nccl:")):
             c10d.append((ts, ts + dur, name))
     if not kernels:
@@ -203,7 +211,7 @@ def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: i
     stream_cat = defaultdict(lambda: defaultdict(float))
     comm_iv, comp_iv = [], []
     timeline = []
-    for ts, dur, name, stream in kernels:
+    for ts, dur, name, stream, _corr in kernels:
         s, e = max(ts, w0), min(ts + dur, w1)
         if e <= s:
             continue
@@ -240,7 +248,7 @@ def analyze(path: str, window: str | None = None, slot_us: float = 50.0, bins: i
             lo, hi = w0 + b * bin_w, w0 + (b + 1) * bin_w
             mix[b][cat] += max(0.0, min(e, hi) - max(s, lo))
     total_kernel = sum(by_cat.values())
-    gaps = _gap_report(kernels, w0, w1, by_stream)
+    gaps = _gap_report(kernels, w0, w1, by_stream, launches, runtime_calls)
     return {
         "main_stream_gaps": gaps,
         "trace": path, "window": window, "window_ms": span / 1e3,
@@ -270,14 +278,22 @@ def _short(name: str) -> str:
     return name[:60]
 
 
-def _gap_report(kernels, w0: float, w1: float, by_stream: dict, min_gap_us: float = 5.0, top: int = 12) -> dict:
+def _gap_report(kernels, w0: float, w1: float, by_stream: dict, launches: dict | None = None,
+                runtime_calls: list | None = None, min_gap_us: float = 5.0, top: int = 12) -> dict:
     """Idle gaps of the busiest stream inside the window: how much of the step the critical stream spends
     not running anything, how much of that another stream covers, and which kernel pairs the gaps sit between
-    (a large total under one pair points at a host sync, an event wait or launch latency at that spot)."""
+    (a large total under one pair points at a host sync, an event wait or launch latency at that spot).
+
+    Each gap is also split by where the kernel that ends it was when the stream went idle: the part of the gap
+    before the host issued that kernel's launch call is ``host_late`` (the host had not got there yet: a host
+    sync, an allocation, Python time), the rest is ``held_on_device`` (launched already, but kept back by an event
+    wait on another stream, by the work distributor, or by launch latency).  ``host_calls`` of a pair lists the
+    runtime calls the host spent the most time in while those gaps were open."""
     if not by_stream:
         return {}
+    launches = launches or {}
     main = max(by_stream, key=lambda k: _union_len(by_stream[k]))
-    evs = sorted((max(ts, w0), min(ts + dur, w1), name) for ts, dur, name, st in kernels
+    evs = sorted((max(ts, w0), min(ts + dur, w1), name, launches.get(corr)) for ts, dur, name, st, corr in kernels
                  if st == main and min(ts + dur, w1) > max(ts, w0))
     others = sorted(iv for st, ivs in by_stream.items() if st != main for iv in ivs)
     o_starts = [iv[0] for iv in others]
@@ -291,12 +307,25 @@ def _gap_report(kernels, w0: float, w1: float, by_stream: dict, min_gap_us: floa
             i += 1
         return _union_len(ivs) if ivs else tot
 
-    pairs, pair_n = defaultdict(float), defaultdict(int)
-    total = cov = 0.0
+    pairs, pair_n, pair_host = defaultdict(float), defaultdict(int), defaultdict(float)
+    pair_calls = defaultdict(lambda: defaultdict(float))
+    rt = sorted(runtime_calls or [])
+    rt_starts = [c[0] for c in rt]
+
+    def host_calls_in(a: float, b: float, into) -> None:
+        i = max(bisect.bisect_left(rt_starts, a) - 32, 0)
+        while i < len(rt) and rt[i][0] < b:
+            ts, dur, name = rt[i]
+            ov = min(ts + dur, b) - max(ts, a)
+            if ov > 0:
+                into[name] += ov
+            i += 1
+
+    total = cov = host_late = 0.0
     hist = {"5-20us": 0.0, "20-100us": 0.0, "100us-1ms": 0.0, ">1ms": 0.0}
     end, prev = (evs[0][0], "window start") if evs else (w0, "window start")
     end = w0
-    for s, e, name in evs:
+    for s, e, name, launched in evs:
         g = s - end
         if g >= min_gap_us:
             total += g
@@ -304,6 +333,12 @@ def _gap_report(kernels, w0: float, w1: float, by_stream: dict, min_gap_us: floa
             key = f"{_short(prev)} -> {_short(name)}"
             pairs[key] += g
             pair_n[key] += 1
+            if launched is not None:
+                late = min(max(launched - end, 0.0), g)
+                host_late += late
+                pair_host[key] += late
+            if g >= 100.0:
+                host_calls_in(end, s, pair_calls[key])
             hist["5-20us" if g < 20 else "20-100us" if g < 100 else "100us-1ms" if g < 1000 else ">1ms"] += g
         if e > end:
             end, prev = e, name
@@ -314,8 +349,11 @@ def _gap_report(kernels, w0: float, w1: float, by_stream: dict, min_gap_us: floa
         pairs[f"{_short(prev)} -> window end"] += tail
         pair_n[f"{_short(prev)} -> window end"] += 1
     return {"stream": str(main), "gap_ms": total / 1e3, "gap_covered_by_other_streams_ms": cov / 1e3,
+            "host_late_ms": host_late / 1e3, "held_on_device_ms": (total - host_late) / 1e3,
             "by_size_ms": {k: v / 1e3 for k, v in hist.items()},
-            "top_pairs": [{"between": k, "ms": v / 1e3, "count": pair_n[k]}
+            "top_pairs": [{"between": k, "ms": v / 1e3, "count": pair_n[k], "host_late_ms": pair_host[k] / 1e3,
+                           "host_calls": [{"name": n, "ms": t / 1e3} for n, t in
+                                          sorted(pair_calls[k].items(), key=lambda kv: -kv[1])[:4]]}
                           for k, v in sorted(pairs.items(), key=lambda kv: -kv[1])[:top]]}
 
 
@@ -333,9 +371,15 @@ def format_report(r: dict) -> str:
     g = r.get("main_stream_gaps") or {}
     if g:
         out += ["", f"idle gaps of stream {g['stream']}: {g['gap_ms']:.2f} ms "
-                    f"({g['gap_covered_by_other_streams_ms']:.2f} ms of it covered by other streams); by gap size: "
+                    f"({g['gap_covered_by_other_streams_ms']:.2f} ms of it covered by other streams; "
+                    f"{g.get('host_late_ms', 0.0):.2f} ms before the host had launched the next kernel, "
+                    f"{g.get('held_on_device_ms', 0.0):.2f} ms with it launched but held back); by gap size: "
                     + ", ".join(f"{k} {v:.2f}" for k, v in g["by_size_ms"].items())]
-        out += [f"  {p['ms']:9.2f} ms  x{p['count']:<5d} {p['between']}" for p in g["top_pairs"]]
+        for p in g["top_pairs"]:
+            out.append(f"  {p['ms']:9.2f} ms  x{p['count']:<5d} host-late {p.get('host_late_ms', 0.0):7.2f} ms  {p['between']}")
+            if p.get("host_calls"):
+                out.append("             host during these gaps: " +
+                           ", ".join(f"{c['name']} {c['ms']:.2f} ms" for c in p["host_calls"]))
     return "\n".join(out)
 
 

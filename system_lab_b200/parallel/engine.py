@@ -226,6 +226,9 @@ class Engine:
                     # (one rank: nothing arrives from anywhere, the token-ordered scatter reads every row once)
                     shared.expert_ordered = m.moe_expert_ordered_dispatch and self.mesh.ep > 1
                     shared.overlap = m.moe_scatter_overlap and self.mesh.ep > 1
+                    if shared.expert_ordered:
+                        from ..moe.fused_dispatch import set_scatter_bulk
+                        set_scatter_bulk(m.moe_scatter_bulk_store)
                 layer.ffn.dispatcher = shared
             else:
                 if shared is None:

@@ -259,10 +259,15 @@ def test_out_of_range_expert_id_is_reported_not_written():
     assert int(plan.expert_counts.sum()) == 64 * 2 - 2
 
 
+@pytest.mark.parametrize("bulk", [False, True])
 @pytest.mark.parametrize("world,T,K,E,H,skew", [(1, 200, 2, 8, 256, False), (2, 300, 4, 16, 512, False),
-                                                (4, 257, 8, 32, 1024, False), (4, 513, 4, 16, 2048, True)])
-def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H, skew):
-    """The expert-ordered scatter writes the same rows, scalars and origins into the same places as the token-ordered
+                                                (4, 257, 8, 32, 1024, False), (4, 513, 4, 16, 2048, True),
+                                                (2, 130, 4, 16, 7168, False)])
+def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H, skew, bulk):
+    """``bulk``: rows leave through bulk stores out of shared memory, 4 KB at a time (hidden 7168 makes a row three
+    and a half pieces), instead of per-lane 16-byte stores; same result.
+
+    The expert-ordered scatter writes the same rows, scalars and origins into the same places as the token-ordered
     one, releases one flag per (source, expert) -- also for pairs without rows -- and leaves its chunk counters at
     zero; a grouped GEMM handed those flags gives the fp32 oracle's result.  Ranks are emulated phase by phase (all
     scatters are enqueued before any GEMM, so no kernel waits for a later launch)."""
@@ -287,7 +292,12 @@ def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H
         for e in range(E):
             want = (flat == e).nonzero().flatten()
             assert torch.equal(perm[pre[e]:pre[e + 1]].long(), want)
-    readies = [d.scatter_ordered(pl, xx, pp.contiguous(), 0) for d, pl, xx, pp in zip(ds, plans, x, pr)]
+    from system_lab_b200.moe.fused_dispatch import set_scatter_bulk
+    set_scatter_bulk(bulk)
+    try:
+        readies = [d.scatter_ordered(pl, xx, pp.contiguous(), 0) for d, pl, xx, pp in zip(ds, plans, x, pr)]
+    finally:
+        set_scatter_bulk(False)
     n, e_local = 256, E // world
     w = (0.05 * torch.randn(world, e_local, n, H, device=dev)).to(torch.bfloat16)
     outs = [cops.grouped_gemm_raw(0, d.rows[0], w[r], pl.expert_offsets, pl.expert_counts, n, H, ready=rd)
@@ -301,7 +311,7 @@ def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H
         assert bool((d.eflags[0] >= readies[owner].epoch).all()), "a (source, expert) flag was never released"
         assert int(d.chunk_done.abs().sum()) == 0
         got_rows, got_sc, org = d.rows[0], d.scalars[0], d.origin.cpu()
-        for row, (src, p) in list(rows.items())[::5]:
+        for row, (src, p) in list(rows.items())[::1 if bulk else 5]:
             assert torch.equal(got_rows[row], x[src][p // K]), f"owner {owner} row {row}"
             assert got_sc[row].item() == pr[src].reshape(-1)[p].item()
             assert org[row].item() == (src << 24) | p

@@ -83,6 +83,27 @@ def test_trace_gap_analysis(tmp_path):
     assert "idle gaps of stream 7" in tb.format_report(r)
 
 
+def test_trace_gaps_are_split_into_host_late_and_held_on_device(tmp_path):
+    """The kernel that ends a gap carries the correlation id of its launch call: the part of the gap before that
+    call is the host's, the rest is the device holding a kernel that was already launched."""
+    from system_lab_b200.observe import trace_breakdown as tb
+    k = lambda name, ts, dur, corr, stream=7: {"ph": "X", "name": name, "cat": "kernel", "ts": ts, "dur": dur,
+                                                "args": {"stream": stream, "correlation": corr}}
+    rt = lambda ts, corr: {"ph": "X", "name": "cudaLaunchKernel", "cat": "cuda_runtime", "ts": ts, "dur": 4,
+                           "args": {"correlation": corr}}
+    ev = [{"ph": "X", "name": "ProfilerStep#0", "cat": "user_annotation", "ts": 0, "dur": 1000},
+          rt(0, 1), k("a_kernel", 0, 100, 1),
+          rt(160, 2), k("b_kernel", 200, 100, 2),          # gap 100..200: host launched at 160 -> 60 late, 40 held
+          rt(20, 3), k("c_kernel", 500, 500, 3)]           # gap 300..500: launched long before -> all held on the device
+    p = tmp_path / "t.json"
+    p.write_text(json.dumps({"traceEvents": ev}))
+    g = tb.analyze(str(p))["main_stream_gaps"]
+    assert abs(g["gap_ms"] - 0.3) < 1e-9
+    assert abs(g["host_late_ms"] - 0.06) < 1e-9 and abs(g["held_on_device_ms"] - 0.24) < 1e-9
+    ab = next(x for x in g["top_pairs"] if "a_kernel" in x["between"])
+    assert abs(ab["host_late_ms"] - 0.06) < 1e-9
+
+
 def test_trace_reader_streams_large_files_in_small_chunks(tmp_path):
     import io
     from system_lab_b200.observe import trace_breakdown as tb
