@@ -109,6 +109,7 @@ class ModelConfig:
 @dataclass
 class ParallelConfig:
     tensor_model_parallel_size: int = 1
+    sequence_parallel: bool = False      # with tp > 1: residual stream, norms and MoE blocks hold 1/tp of every sequence; all-gather / reduce-scatter around the split matrices instead of all-reduces
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: int = 1
     expert_model_parallel_size: int = 1

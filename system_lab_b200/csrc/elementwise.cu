@@ -557,13 +557,14 @@ template <typename P, int KIND, typename G>
 __global__ void __launch_bounds__(256)
 adamw_kernel(P* __restrict__ p, const G* __restrict__ g, void* __restrict__ m_raw, void* __restrict__ v_raw,
              float* __restrict__ m_scale, float* __restrict__ v_scale, __nv_bfloat16* __restrict__ out_bf16,
-             const float* __restrict__ coef, float* __restrict__ sq_out, long n, AdamArgs a) {
+             const float* __restrict__ coef, float* __restrict__ sq_out, long q_begin, long nq, AdamArgs a) {
+  // One launch covers the 16-element items [q_begin, nq); q_begin is a multiple of 32.
   __shared__ float red[32];
   const float c = coef ? *coef : 1.f;
-  const long nq = n >> 4;
   float sq = 0.f;
   // warp-uniform trip count: lanes past the end idle through the body so the block-scale shuffles stay full-warp
-  for (long i0 = blockIdx.x * (long)blockDim.x + (threadIdx.x & ~31); i0 < nq; i0 += (long)gridDim.x * blockDim.x) {
+  for (long i0 = q_begin + blockIdx.x * (long)blockDim.x + (threadIdx.x & ~31); i0 < nq;
+       i0 += (long)gridDim.x * blockDim.x) {
     const long i = i0 + (threadIdx.x & 31);
     const bool act = i < nq;
     if (!act && KIND != 2) continue;
@@ -836,17 +837,32 @@ extern "C" int slab_sumsq(const void* g, int g_is_bf16, long n, float scale, flo
 
 // p_is_bf16: weights updated in place are bf16 (no fp32 master); g_is_bf16: gradient dtype;
 // state_kind: 0 fp32, 1 bf16, 2 fp8.  n must be a multiple of 128.
+// A background update (ctas_per_sm > 0) is cut into launches of this many elements.  The kernel is a grid-stride
+// loop whose blocks stay resident until the launch ends, and two of them hold most of an SM's registers: a kernel
+// of the compute stream with large blocks (a GEMM, attention) cannot be placed beside them and waits for the launch
+// to end.  With pieces of about a hundred microseconds that wait is bounded by one piece instead of the whole update.
+constexpr long ADAMW_BACKGROUND_PIECE = 1L << 23;
+
 template <typename P, typename G>
 static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scale, float* v_scale, void* out_bf16,
-                         const float* coef, float* sq_out, long n, int state_kind, AdamArgs a, int grid,
+                         const float* coef, float* sq_out, long n, int state_kind, AdamArgs a, int ctas_per_sm,
                          cudaStream_t st) {
-  if (state_kind == 0)
-    adamw_kernel<P, 0, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
-  else if (state_kind == 1)
-    adamw_kernel<P, 1, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
-  else
-    adamw_kernel<P, 2, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, n, a);
+  const bool background = ctas_per_sm > 0 && ctas_per_sm < 8;
+  const long nq = n >> 4;
+  const long piece = background ? (ADAMW_BACKGROUND_PIECE >> 4) : nq;
+  for (long q0 = 0; q0 < nq; q0 += piece) {
+    const long q1 = q0 + piece < nq ? q0 + piece : nq;
+    const int grid = grid_for(q1 - q0, 256, background ? ctas_per_sm : 8);
+    if (state_kind == 0)
+      adamw_kernel<P, 0, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, q0, q1, a);
+    else if (state_kind == 1)
+      adamw_kernel<P, 1, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, q0, q1, a);
+    else
+      adamw_kernel<P, 2, G><<<grid, 256, 0, st>>>((P*)p, (const G*)g, m, v, m_scale, v_scale, (__nv_bfloat16*)out_bf16, coef, sq_out, q0, q1, a);
+  }
 }
+
+extern "C" long slab_adamw_background_piece() { return ADAMW_BACKGROUND_PIECE; }
 
 extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
                           float* v_scale, void* out_bf16, const float* coef, float* sq_out, long n, int state_kind,
@@ -859,13 +875,12 @@ extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, 
   if (n == 0) return 0;
   if (decay_end % 128) return -101;
   AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, decay_end};
-  int grid = grid_for(n / 16, 256, ctas_per_sm > 0 && ctas_per_sm < 8 ? ctas_per_sm : 8);
   if (p_is_bf16) {
-    if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
-    else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
+    if (g_is_bf16) launch_adamw<__nv_bfloat16, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, ctas_per_sm, st);
+    else launch_adamw<__nv_bfloat16, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, ctas_per_sm, st);
   } else {
-    if (g_is_bf16) launch_adamw<float, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
-    else launch_adamw<float, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, grid, st);
+    if (g_is_bf16) launch_adamw<float, __nv_bfloat16>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, ctas_per_sm, st);
+    else launch_adamw<float, float>(p, g, m, v, m_scale, v_scale, out_bf16, coef, sq_out, n, state_kind, a, ctas_per_sm, st);
   }
   return (int)cudaGetLastError();
 }

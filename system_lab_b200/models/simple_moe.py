@@ -118,9 +118,9 @@ class GQAttention(nn.Module):
             self.o_lora = LoRA(h, self.wo.shape[1], cfg.lora_rank, cfg.lora_alpha)
 
     def forward(self, x, cos, sin):
-        b, s, _ = x.shape
         if self.tp is not None:
-            x = self.tp.copy_to(x)
+            x = self.tp.enter(x)              # sequence parallel: whole sequences from here to the output projection
+        b, s, _ = x.shape
         qkv = ops.linear(x, self.wqkv)
         if self.qkv_lora is not None:
             qkv = qkv + self.qkv_lora(x)
@@ -138,7 +138,7 @@ class GQAttention(nn.Module):
         out = ops.linear(o2, self.wo)
         if self.o_lora is not None:
             out = out + self.o_lora(o2)
-        return self.tp.reduce_from(out) if self.tp is not None else out
+        return self.tp.leave(out) if self.tp is not None else out
 
 
 class MLAttention(nn.Module):
@@ -175,9 +175,12 @@ class MLAttention(nn.Module):
         self.cp_group = cp_group
 
     def forward(self, x, cos, sin):
+        tp = self.tp
+        if tp is not None:
+            # the low-rank down projections are repeated on every rank and need whole sequences as well
+            x = tp.gather_seq(x)
         b, s, _ = x.shape
         dt = x.dtype
-        tp = self.tp
         link = tp.copy_to if tp is not None else (lambda t: t)     # replicated value feeding this rank's heads
         if self.q_lora:
             q = ops.linear(link(self.q_norm(ops.linear(x, self.wq_a))), self.wq_b)
@@ -200,7 +203,7 @@ class MLAttention(nn.Module):
         else:
             o = ops.causal_attention(qf, kf, v.contiguous(), self.scale, 0)
         out = ops.linear(o.reshape(b, s, self.nh * self.vd), self.wo)
-        return tp.reduce_from(out) if tp is not None else out
+        return tp.leave(out) if tp is not None else out
 
 
 class DenseFFN(nn.Module):
@@ -221,7 +224,7 @@ class DenseFFN(nn.Module):
 
     def forward(self, x):
         if self.tp is not None:
-            x = self.tp.copy_to(x)
+            x = self.tp.enter(x)
         gu = ops.linear(x, self.w1)
         if self.w1_lora is not None:
             gu = gu + self.w1_lora(x)
@@ -229,7 +232,7 @@ class DenseFFN(nn.Module):
         out = ops.linear(act, self.w2)
         if self.w2_lora is not None:
             out = out + self.w2_lora(act)
-        return self.tp.reduce_from(out) if self.tp is not None else out
+        return self.tp.leave(out) if self.tp is not None else out
 
 
 class MoEFFN(nn.Module):
@@ -413,10 +416,14 @@ class DecoderLayer(nn.Module):
             mlp_rank = cfg.lora_rank if "mlp" in cfg.lora_targets else 0
             self.ffn = DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size, tp) if tp is not None \
                 else DenseFFN(cfg.hidden_size, cfg.ffn_hidden_size, None, mlp_rank, cfg.lora_alpha)
+        if tp is not None and tp.sequence_parallel:
+            # the norms see this rank's part of every sequence only
+            self.attn_norm.weight.tp_partial_grad = True
+            self.ffn_norm.weight.tp_partial_grad = True
         self.recompute_ffn = False        # set by the engine for recompute_granularity=selective
 
     def _ffn_block(self, y, h):
-        if self.tp is not None and self.is_moe:
+        if self.tp is not None and self.is_moe and not self.tp.sequence_parallel:
             # MoE under tensor parallelism: every rank of the group routes 1 / tp of the shared tokens through the
             # expert-parallel exchange, then the group reassembles the block's output
             shp = y.shape
@@ -494,6 +501,12 @@ class SimpleMoE(nn.Module):
         self.layers = nn.ModuleList(
             [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group, tp) for i in ids])
         self.head = Head(cfg) if last_stage else None
+        if tp is not None and tp.sequence_parallel:
+            # embedding, final norm and vocabulary projection run on this rank's part of every sequence
+            for mod in (self.embed, self.head):
+                if mod is not None:
+                    for p in mod.parameters():
+                        p.tp_partial_grad = True
         if cfg.lora_rank > 0:
             if cfg.attention_type != "gqa":
                 raise ValueError("LoRA adapters are implemented for GQA attention")

@@ -896,6 +896,9 @@ def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
 _KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
 
 
+_ADAMW_PIECE = 1 << 23      # csrc/elementwise.cu: ADAMW_BACKGROUND_PIECE
+
+
 def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, sq_out=None,
                ctas_per_sm: int = 0) -> None:
     """Fused AdamW on one flat shard: reads the (fp32 or bf16) gradient shard, updates moments (any storage
@@ -916,3 +919,5 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, 
          _KIND[m.kind],
          float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
          int(group.shard_decay_end() if hasattr(group, "shard_decay_end") else n), int(ctas_per_sm), stream())
+    if 0 < ctas_per_sm < 8:             # a background update is cut into launches of at most _ADAMW_PIECE elements
+        LAUNCHES[0] += max((n + _ADAMW_PIECE - 1) // _ADAMW_PIECE - 1, 0)

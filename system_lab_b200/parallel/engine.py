@@ -136,7 +136,7 @@ class Engine:
         self.tp = None
         if mesh.tp > 1:
             from .tp import TensorParallel
-            self.tp = TensorParallel(mesh.tp_group, mesh.tp_rank, mesh.tp)
+            self.tp = TensorParallel(mesh.tp_group, mesh.tp_rank, mesh.tp, cfg.parallel.sequence_parallel)
         with torch.device("meta"):
             self.model = SimpleMoE(
                 m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=(cfg.precision.fp8_recipe if cfg.precision.fp8 else False),
@@ -287,9 +287,12 @@ class Engine:
         x = inp
         first_chunk = chunk is None or chunk == 0
         last_chunk = chunk is None or chunk == self.vpp - 1
+        sp = self.tp.size if self.tp is not None and self.tp.sequence_parallel else 1
         if self.embed_unit is not None and first_chunk:
+            if sp > 1:
+                x = self.tp.local_seq(x)          # every rank of the group got the same token ids
             x = self.run_unit(self.embed_unit, x, self.compute_dtype)
-        cos, sin = self.model.rope_tables(x.shape[1], x.device)
+        cos, sin = self.model.rope_tables(x.shape[1] * sp, x.device)     # attention sees whole sequences
         if chunk is None:
             units = self.layer_units
         else:
@@ -303,8 +306,15 @@ class Engine:
             else:
                 x = out
         if self.head_unit is not None and last_chunk:
-            x = self.run_unit(self.head_unit, x, targets)
+            if sp > 1:
+                x = self.tp.mean_loss(self.run_unit(self.head_unit, x, self.tp.local_seq(targets)))
+            else:
+                x = self.run_unit(self.head_unit, x, targets)
         return x, aux_all
+
+    def seq_shards(self) -> int:
+        """Into how many parts sequence parallelism cuts the sequences this rank's stage receives and sends."""
+        return self.tp.size if self.tp is not None and self.tp.sequence_parallel else 1
 
     def all_groups(self):
         for u in self.units:

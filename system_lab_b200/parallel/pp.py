@@ -30,7 +30,7 @@ def pipeline_1f1b(engine, mesh, batches, scale: float, cfg) -> torch.Tensor:
     prev_r = mesh.prev_stage_rank() if not first else None
     next_r = mesh.next_stage_rank() if not last else None
     mbs, seq = batches[0][0].shape
-    act_shape = (mbs, seq, cfg.model.hidden_size)
+    act_shape = (mbs, seq // engine.seq_shards(), cfg.model.hidden_size)
     dt = engine.compute_dtype
     loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
     pending = []            # (input hidden or None, output, aux list) awaiting backward
@@ -120,7 +120,7 @@ def pipeline_forward_only(engine, mesh, batches, cfg) -> torch.Tensor:
     prev_r = mesh.prev_stage_rank() if not first else None
     next_r = mesh.next_stage_rank() if not last else None
     mbs, seq = batches[0][0].shape
-    act_shape = (mbs, seq, cfg.model.hidden_size)
+    act_shape = (mbs, seq // engine.seq_shards(), cfg.model.hidden_size)
     loss_sum = torch.zeros((), dtype=torch.float32, device=dev)
     for tok, tgt in batches:
         if first:
@@ -161,7 +161,7 @@ def pipeline_interleaved(engine, mesh, batches, scale: float, cfg, forward_only:
         raise ValueError(f"interleaved stages need micro-batches per step ({nmb}) to be a multiple of pp ({pp})")
     right, left = mesh.pp_ranks[(r + 1) % pp], mesh.pp_ranks[(r - 1) % pp]
     mbs, seq = batches[0][0].shape
-    act_shape = (mbs, seq, cfg.model.hidden_size)
+    act_shape = (mbs, seq // engine.seq_shards(), cfg.model.hidden_size)
     dt = engine.compute_dtype
     last_v = pp * vpp - 1
     loss_sum = torch.zeros((), dtype=torch.float32, device=dev)

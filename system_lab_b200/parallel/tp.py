@@ -7,6 +7,14 @@ of a column-split matrix, ``reduce_from`` (all-reduce forward, identity backward
 forward, slice backward) behind it.  Parameters that stay replicated but see only a slice of the tokens (router,
 shared expert) are marked ``tp_partial_grad``; the engine sums their gradients over the group.
 
+Sequence parallelism (``sequence_parallel``, needs ``tp > 1``): between the tensor-parallel regions the residual
+stream, the norms and the MoE blocks hold ``1 / tp`` of every sequence (``[B, S / tp, H]``).  ``enter`` then is an
+all-gather along the sequence in front of a column-split matrix (reduce-scatter in backward) and ``leave`` a
+reduce-scatter behind a row-split one (all-gather in backward): the same bytes as the two all-reduces of plain tensor
+parallelism, with ``tp`` times less activation memory outside the attention and feed-forward matrices.  Parameters that
+are replicated but see only the local part of the sequence (norm gains, embedding, head) get partial gradients like
+the router's (``tp_partial_grad``), and the loss is the mean over the group of the per-rank means.
+
 Reference: tensor parallelism is a configuration axis of the tuner (legality rules
 ``skills/pilot/constraints/config.md:41-48``); every measured configuration of the reference ran ``tp = 1``.  The
 attention ``tp x cp x dp`` / MoE ``ep x edp`` folding follows ``moe/MegatronCore_MoE_reading_notes.md:159-195``.
@@ -72,11 +80,103 @@ class _GatherRows(torch.autograd.Function):
         return g[ctx.rank * per:(ctx.rank + 1) * per].contiguous(), None, None, None
 
 
+def _gather_seq(x, group, size):
+    """[B, S/size, ...] on every rank -> [B, S, ...] (rank r holds positions [r S/size, (r+1) S/size))."""
+    x = x.contiguous()
+    out = torch.empty((size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x, group=group)
+    out = out.view((size,) + tuple(x.shape))
+    return out.transpose(0, 1).reshape((x.shape[0], size * x.shape[1]) + tuple(x.shape[2:]))
+
+
+def _reduce_scatter_seq(x, group, size):
+    """Sum over the group of [B, S, ...], this rank keeps its [B, S/size, ...]."""
+    b, s = x.shape[0], x.shape[1]
+    parts = x.reshape((b, size, s // size) + tuple(x.shape[2:])).transpose(0, 1).contiguous()
+    out = torch.empty(parts.shape[1:], dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, parts.view((size * b,) + tuple(parts.shape[2:])), group=group)
+    return out
+
+
+class _GatherSeq(torch.autograd.Function):
+    """All-gather along the sequence; backward reduce-scatters (the consumers are this rank's slices of a
+    column-split matrix, so the gradients of the ranks add up) or, with ``reduce=False``, keeps this rank's slice
+    (the consumers compute the same thing on every rank)."""
+
+    @staticmethod
+    def forward(ctx, x, group, rank, size, reduce):
+        ctx.group, ctx.rank, ctx.size, ctx.reduce = group, rank, size, reduce
+        return _gather_seq(x, group, size)
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.reduce:
+            return _reduce_scatter_seq(g, ctx.group, ctx.size), None, None, None, None
+        per = g.shape[1] // ctx.size
+        return g[:, ctx.rank * per:(ctx.rank + 1) * per].contiguous(), None, None, None, None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, size):
+        ctx.group, ctx.size = group, size
+        return _reduce_scatter_seq(x, group, size)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_seq(g, ctx.group, ctx.size), None, None
+
+
+class _MeanOverGroup(torch.autograd.Function):
+    """The scalar loss of a sequence-parallel group: mean of the per-rank means (every rank holds the same number of
+    positions); each rank's own loss gets ``1 / size`` of the gradient."""
+
+    @staticmethod
+    def forward(ctx, loss, group, size):
+        ctx.size = size
+        out = loss.detach().clone()
+        dist.all_reduce(out, group=group)
+        return out / size
+
+    @staticmethod
+    def backward(ctx, g):
+        return g / ctx.size, None, None
+
+
 class TensorParallel:
     """The group as the model sees it.  ``None`` stands for ``tp == 1`` everywhere in the model code."""
 
-    def __init__(self, group, rank: int, size: int):
+    def __init__(self, group, rank: int, size: int, sequence_parallel: bool = False):
         self.group, self.rank, self.size = group, rank, size
+        self.sequence_parallel = sequence_parallel
+
+    def enter(self, x):
+        """In front of a column-split matrix whose input nothing else on this rank consumes."""
+        if self.sequence_parallel:
+            return _GatherSeq.apply(x, self.group, self.rank, self.size, True)
+        return _CopyTo.apply(x, self.group)
+
+    def leave(self, x):
+        """Behind a row-split matrix: sum the partial products over the group."""
+        if self.sequence_parallel:
+            return _ReduceScatterSeq.apply(x, self.group, self.size)
+        return _ReduceFrom.apply(x, self.group)
+
+    def gather_seq(self, x):
+        """Whole sequences for a computation every rank repeats (identity without sequence parallelism)."""
+        if self.sequence_parallel:
+            return _GatherSeq.apply(x, self.group, self.rank, self.size, False)
+        return x
+
+    def local_seq(self, x):
+        """This rank's positions of ``[B, S, ...]`` data that every rank of the group holds (token ids, targets)."""
+        if not self.sequence_parallel:
+            return x
+        per = x.shape[1] // self.size
+        return x[:, self.rank * per:(self.rank + 1) * per].contiguous()
+
+    def mean_loss(self, loss):
+        return _MeanOverGroup.apply(loss, self.group, self.size) if self.sequence_parallel else loss
 
     def copy_to(self, x):
         return _CopyTo.apply(x, self.group)

@@ -48,6 +48,13 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
             out.append(_p("lora_excludes_tp", "LoRA adapters are not combined with tensor parallelism"))
         if m.lora_targets not in ("attn", "attn+mlp"):
             out.append(_p("lora_targets", f"lora_targets={m.lora_targets!r}: use 'attn' or 'attn+mlp'"))
+    if getattr(p, "sequence_parallel", False):
+        if tp <= 1:
+            out.append(_p("sp_needs_tp", "sequence_parallel needs tensor_model_parallel_size > 1",
+                          "set tp >= 2 or turn sequence_parallel off"))
+        elif (m.seq_length // max(cp, 1)) % tp:
+            out.append(_p("tp_divides_sequence", f"seq_length / cp = {m.seq_length // max(cp, 1)} % tp={tp} != 0 "
+                                                 "(sequence_parallel shards every sequence over tp)"))
     if tp > 1:
         # heads and dense feed-forward columns split over tp; MoE blocks take 1/tp of the tokens per rank
         if (t.micro_batch_size * m.seq_length // max(cp, 1)) % tp:

@@ -82,6 +82,8 @@ def test_tensor_parallel_and_hybrid_sharding_rules():
         return [p["rule"] for p in check_config(cfg, world) if p["severity"] == "error"]
     assert rules(["tensor_model_parallel_size=2", "expert_model_parallel_size=2"], 2) == []
     assert "tp_divides_num_heads" in rules(["tensor_model_parallel_size=8", "expert_model_parallel_size=1"], 8)
+    assert "sp_needs_tp" in rules(["sequence_parallel=true", "expert_model_parallel_size=1"], 1)
+    assert rules(["tensor_model_parallel_size=2", "expert_model_parallel_size=2", "sequence_parallel=true"], 2) == []
     assert "tp_excludes_hsdp" in rules(["tensor_model_parallel_size=2", "num_distributed_optimizer_instances=2"], 8)
     assert rules(["num_distributed_optimizer_instances=2", "expert_model_parallel_size=2"], 4) == []
     assert "hsdp_divides_data_ranks" in rules(["num_distributed_optimizer_instances=3", "expert_model_parallel_size=2"], 4)

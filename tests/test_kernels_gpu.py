@@ -216,6 +216,41 @@ def test_adamw_flat(cops, kind, p_dtype):
         assert torch.allclose(g.shard[de:], p_ref[de:], atol=1e-7)
 
 
+@pytest.mark.parametrize("kind", ["fp32", "fp8"])
+def test_background_adamw_in_pieces_equals_one_launch(cops, kind):
+    """An update that runs beside other streams' kernels (``ctas_per_sm`` > 0) is cut into launches of 2^23 elements;
+    two and a bit pieces give bit for bit what the single full-width launch gives, sum of squares included."""
+    from system_lab_b200.trainer.optim import _Moment
+    torch.manual_seed(11)
+    n = 2 * (1 << 23) + 128 * 4101
+    de = (1 << 23) + 128 * 77                      # the decay boundary falls inside the second piece
+
+    def run(ctas):
+        class G:
+            pass
+        g = G()
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        g.shard = 0.02 * torch.randn(n, device="cuda", generator=gen)
+        g.full, g.sharded = g.shard, True
+        g.shard_decay_end = lambda: de
+        g.shard_lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        m, v = _Moment(n, kind, "cuda"), _Moment(n, kind, "cuda", sqrt_domain=(kind != "fp32"))
+        sq = torch.zeros(1, device="cuda")
+        before = cops.LAUNCHES[0]
+        for step in (1, 2):
+            g.grad_shard = 1e-2 * torch.randn(n, device="cuda", generator=gen)
+            cops.adamw_flat(g, m, v, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                            sq_out=sq, ctas_per_sm=ctas)
+        return g.shard, m.data, v.data, sq, cops.LAUNCHES[0] - before
+
+    p0, m0, v0, sq0, l0 = run(0)
+    p1, m1, v1, sq1, l1 = run(2)
+    raw = lambda t: t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+    assert torch.equal(p0, p1) and torch.equal(raw(m0), raw(m1)) and torch.equal(raw(v0), raw(v1))
+    assert abs(sq0.item() - sq1.item()) <= 1e-5 * sq0.item()
+    assert l0 == 2 and l1 == 6                     # three launches per background update
+
+
 def test_sumsq(cops):
     x = torch.randn(1_000_003, device="cuda")
     out = torch.zeros(1, device="cuda")

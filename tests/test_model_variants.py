@@ -74,6 +74,16 @@ def test_dsv3_shape_tensor_parallel_with_context_parallel():
         assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)
 
 
+def test_dsv3_shape_sequence_parallel():
+    """MLA under sequence parallelism: the repeated low-rank projections get whole sequences through a gather whose
+    backward keeps the local slice; the dense first layer gathers and reduce-scatters."""
+    (single, _), = run_ranks(_train, 1, DSV3_TINY + ["expert_model_parallel_size=1"], 4)
+    res = run_ranks(_train, 2, DSV3_TINY + ["expert_model_parallel_size=2", "tensor_model_parallel_size=2",
+                                            "sequence_parallel=true"], 4)
+    for losses, _ in res:
+        assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)
+
+
 def test_aux_loss_is_carried_through_every_recompute_mode():
     """The load-balancing loss reaches the objective (and the router's gradient) whether the MoE block is kept,
     recomputed alone (selective: the loss leaves the recompute node as a second output) or with its whole layer

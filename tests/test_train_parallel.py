@@ -216,6 +216,24 @@ def test_tensor_parallel_matches(single_curve):
         assert losses == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
 
 
+def test_sequence_parallel_matches(single_curve):
+    """Residual stream, norms and MoE blocks on half of every sequence per rank; all-gather in front of the
+    column-split matrices, reduce-scatter behind the row-split ones; norm gains, embedding and head sum their partial
+    gradients over the group; the loss is the mean of the two ranks' means."""
+    res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=2", "tensor_model_parallel_size=2",
+                                       "sequence_parallel=true"], 6)
+    for losses, _ in res:
+        assert losses == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+
+
+def test_sequence_parallel_with_pipeline_and_selective_recompute(single_curve):
+    """Stages exchange [B, S / tp, H] activations."""
+    ov = BASE + ["expert_model_parallel_size=2", "tensor_model_parallel_size=2", "sequence_parallel=true",
+                 "pipeline_model_parallel_size=2", "recompute_granularity=selective"]
+    res = run_ranks(_train, 4, ov, 4)
+    assert res[-1][0] == pytest.approx(single_curve[:4], rel=2e-5, abs=2e-5)
+
+
 def test_tensor_parallel_with_data_parallel_selective_and_resume(single_curve, tmp_path):
     ov = BASE + ["expert_model_parallel_size=4", "tensor_model_parallel_size=2", "recompute_granularity=selective"]
     ck = str(tmp_path / "ck")
