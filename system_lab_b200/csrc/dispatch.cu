@@ -473,14 +473,27 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
     const int r0 = (item - ip[oi]) * SCATTER_CHUNK;
     const int r1 = min(cnt, r0 + SCATTER_CHUNK);
     uint8_t* pb = peers.base[d];
-    for (int i = r0 + warp; i < r1; i += warps_per_block) {
-      const int p = perm[send_prefix[e] + i];
-      const int loc = pair_loc[p];
+    // lane l fetches the pair, the slot and the scale of the l-th row this warp will copy, so the chain of
+    // dependent index loads (perm -> pair_loc -> row) is paid once per chunk and not once per row
+    int p_l = 0, loc_l = -1;
+    float sc_l = 1.f;
+    {
+      const int i_l = r0 + warp + warps_per_block * lane;
+      if (i_l < r1) {
+        p_l = perm[send_prefix[e] + i_l];
+        loc_l = pair_loc[p_l];
+        if (scale_in) sc_l = scale_in[p_l];
+      }
+    }
+    int it = 0;
+    for (int i = r0 + warp; i < r1; i += warps_per_block, ++it) {
+      const int p = __shfl_sync(0xffffffffu, p_l, it);
+      const int loc = __shfl_sync(0xffffffffu, loc_l, it);
+      const float sc = __shfl_sync(0xffffffffu, sc_l, it);
       if (loc < 0 || (loc >> 24) != d) continue;         // dropped pair, or a corrupt table: never written
       const int row = loc & 0xFFFFFF;
       const int t = p / K;
       const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (size_t)t * H);
-      const float sc = scale_in ? scale_in[p] : 1.f;
       if (BULK && !FP8) {
         uint8_t* dst_row = pb + ws.rows + (size_t)row * nvec * 16;
         for (int s0 = 0; s0 < nvec; s0 += SCATTER_SEG_VEC) {
