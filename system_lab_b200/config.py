@@ -158,6 +158,7 @@ class TrainConfig:
     adam_eps: float = 1e-8
     clip_grad: float = 1.0
     optimizer_in_backward: bool = False  # apply AdamW per layer during backward (no grad buffer kept)
+    optimizer_background_piece: int = 33554432   # elements per launch of a side-stream AdamW update (multiple of 512; 0 = one launch): bounds how long a compute-stream kernel with large blocks waits for room on the SMs
     eval_interval: int = 0
     eval_iters: int = 0
     log_interval: int = 1

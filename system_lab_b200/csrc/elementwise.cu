@@ -840,8 +840,13 @@ extern "C" int slab_sumsq(const void* g, int g_is_bf16, long n, float scale, flo
 // A background update (ctas_per_sm > 0) is cut into launches of this many elements.  The kernel is a grid-stride
 // loop whose blocks stay resident until the launch ends, and two of them hold most of an SM's registers: a kernel
 // of the compute stream with large blocks (a GEMM, attention) cannot be placed beside them and waits for the launch
-// to end.  With pieces of about a hundred microseconds that wait is bounded by one piece instead of the whole update.
-constexpr long ADAMW_BACKGROUND_PIECE = 1L << 23;
+// to end.  With pieces of a few hundred microseconds that wait is bounded by one piece instead of the whole update.
+static long g_adamw_background_piece = 1L << 25;          // elements, a multiple of 512; 0 = one launch
+extern "C" int slab_set_adamw_background_piece(long elements) {
+  if (elements < 0 || elements % 512) return -100;
+  g_adamw_background_piece = elements;
+  return 0;
+}
 
 template <typename P, typename G>
 static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scale, float* v_scale, void* out_bf16,
@@ -849,7 +854,7 @@ static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scal
                          cudaStream_t st) {
   const bool background = ctas_per_sm > 0 && ctas_per_sm < 8;
   const long nq = n >> 4;
-  const long piece = background ? (ADAMW_BACKGROUND_PIECE >> 4) : nq;
+  const long piece = background && g_adamw_background_piece > 0 ? (g_adamw_background_piece >> 4) : nq;
   for (long q0 = 0; q0 < nq; q0 += piece) {
     const long q1 = q0 + piece < nq ? q0 + piece : nq;
     const int grid = grid_for(q1 - q0, 256, background ? ctas_per_sm : 8);
@@ -862,7 +867,7 @@ static void launch_adamw(void* p, const void* g, void* m, void* v, float* m_scal
   }
 }
 
-extern "C" long slab_adamw_background_piece() { return ADAMW_BACKGROUND_PIECE; }
+extern "C" long slab_adamw_background_piece() { return g_adamw_background_piece; }
 
 extern "C" int slab_adamw(void* p, int p_is_bf16, const void* g, int g_is_bf16, void* m, void* v, float* m_scale,
                           float* v_scale, void* out_bf16, const float* coef, float* sq_out, long n, int state_kind,

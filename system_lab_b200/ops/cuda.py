@@ -896,7 +896,17 @@ def sumsq(g: torch.Tensor, scale: float, out: torch.Tensor) -> None:
 _KIND = {"fp32": 0, "bf16": 1, "fp8": 2}
 
 
-_ADAMW_PIECE = 1 << 23      # csrc/elementwise.cu: ADAMW_BACKGROUND_PIECE
+_ADAMW_PIECE = [1 << 25]    # elements per launch of a background update (csrc/elementwise.cu); 0 = one launch
+
+
+def set_adamw_background_piece(elements: int) -> None:
+    """A side-stream AdamW update is cut into launches of this many elements (a multiple of 512; 0: one launch), so
+    that a compute-stream kernel with large blocks waits for one piece at most before it finds room on the SMs."""
+    register("slab_set_adamw_background_piece", "l")
+    rc = lib().slab_set_adamw_background_piece(int(elements))
+    if rc != 0:
+        raise KernelError(f"slab_set_adamw_background_piece({elements}) failed with code {rc}")
+    _ADAMW_PIECE[0] = int(elements)
 
 
 def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, sq_out=None,
@@ -919,5 +929,5 @@ def adamw_flat(group, m, v, coef, *, lr, beta1, beta2, eps, weight_decay, step, 
          _KIND[m.kind],
          float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
          int(group.shard_decay_end() if hasattr(group, "shard_decay_end") else n), int(ctas_per_sm), stream())
-    if 0 < ctas_per_sm < 8:             # a background update is cut into launches of at most _ADAMW_PIECE elements
-        LAUNCHES[0] += max((n + _ADAMW_PIECE - 1) // _ADAMW_PIECE - 1, 0)
+    if 0 < ctas_per_sm < 8 and _ADAMW_PIECE[0] > 0:        # a background update is cut into several launches
+        LAUNCHES[0] += max((n + _ADAMW_PIECE[0] - 1) // _ADAMW_PIECE[0] - 1, 0)

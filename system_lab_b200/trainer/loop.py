@@ -78,6 +78,9 @@ class Trainer:
                                       state_dtype=cfg.precision.optimizer_state_dtype)
         if t.optimizer_in_backward:
             self.engine.optimizer = self.optimizer
+            if self.device.type == "cuda" and ops.kernel_mode() == "auto":
+                from ..ops import cuda as _cops
+                _cops.set_adamw_background_piece(t.optimizer_background_piece)
         data_kw = dict(vocab_size=cfg.model.vocab_size, seq_length=cfg.model.seq_length,
                        global_batch_size=t.global_batch_size, micro_batch_size=t.micro_batch_size,
                        dp_rank=mesh.dp_rank, dp_size=mesh.dp, cp_rank=mesh.cp_rank, cp_size=mesh.cp, seed=t.seed,
