@@ -109,7 +109,7 @@ __global__ void moe_publish_kernel(int* __restrict__ block_hist, int n_blocks, i
 //                     walks the local expert index j outermost and the destination rank innermost, starting at the
 //                     right-hand neighbour ((me + 1 + ph) % world): every rank is writing a different peer at any
 //                     moment, and local expert j of every rank is complete after (j + 1) / E_local of the exchange.
-constexpr int SCATTER_CHUNK = 32;
+constexpr int SCATTER_CHUNK = 16;
 
 __device__ __forceinline__ int send_order_expert(int oi, int world, int me, int e_local) {
   const int j = oi / world, ph = oi % world;

@@ -48,7 +48,8 @@ def _expected_layout(idx_all, world, E, pad=128):
     return out
 
 
-@pytest.mark.parametrize("world,T,K,E,H", [(1, 200, 2, 8, 256), (2, 300, 4, 16, 512), (4, 257, 8, 32, 1024)])
+@pytest.mark.parametrize("world,T,K,E,H", [(1, 200, 2, 8, 256), (2, 300, 4, 16, 512), (4, 257, 8, 32, 1024),
+                                           (8, 190, 8, 128, 2048)])
 def test_dispatch_combine_roundtrip(world, T, K, E, H):
     from system_lab_b200.ops import cuda as cops
     torch.manual_seed(world)
@@ -133,7 +134,8 @@ def test_missing_flag_times_out_with_status_not_hang():
     assert torch.ones(4, device="cuda").sum().item() == 4
 
 
-@pytest.mark.parametrize("world,T,K,E,H,F", [(1, 200, 2, 8, 256, 128), (2, 300, 4, 16, 512, 256), (4, 257, 8, 32, 1024, 192)])
+@pytest.mark.parametrize("world,T,K,E,H,F", [(1, 200, 2, 8, 256, 128), (2, 300, 4, 16, 512, 256), (4, 257, 8, 32, 1024, 192),
+                                             (8, 150, 8, 64, 512, 128)])
 def test_gemm_push_epilogue_matches_pull_combine(world, T, K, E, H, F):
     """Expert GEMMs whose epilogue pushes result rows to the token owners (forward: act @ w2^T, width H; dgrad:
     dY @ w1, width H), reduced by the owners, against an fp32 oracle on the same bf16 inputs.  Ranks are
@@ -262,7 +264,7 @@ def test_out_of_range_expert_id_is_reported_not_written():
 @pytest.mark.parametrize("bulk", [False, True])
 @pytest.mark.parametrize("world,T,K,E,H,skew", [(1, 200, 2, 8, 256, False), (2, 300, 4, 16, 512, False),
                                                 (4, 257, 8, 32, 1024, False), (4, 513, 4, 16, 2048, True),
-                                                (2, 130, 4, 16, 7168, False)])
+                                                (2, 130, 4, 16, 7168, False), (8, 200, 8, 128, 2048, False)])
 def test_expert_ordered_scatter_and_gemm_that_waits_per_expert(world, T, K, E, H, skew, bulk):
     """``bulk``: rows leave through bulk stores out of shared memory, 4 KB at a time (hidden 7168 makes a row three
     and a half pieces), instead of per-lane 16-byte stores; same result.

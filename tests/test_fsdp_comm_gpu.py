@@ -16,7 +16,7 @@ def _comms(world, nbytes):
     return [FsdpPeerComm(None, world, r, dev, workspace_factory=lambda n, r=r: emu.workspace(r)) for r in range(world)]
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_all_gather_and_reduce_scatter(world):
     from system_lab_b200.ops import cuda as cops
     shard = 128 * 37
@@ -96,7 +96,7 @@ def test_reduce_scatter_fused_adamw_matches_two_step():
     assert abs(sq.item() - total.pow(2).sum().item()) / total.pow(2).sum().item() < 1e-4
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_all_gather_fused_into_the_consuming_gemm(world):
     """A flat parameter buffer (three matrices, then a tail of 1-D parameters) sharded over `world` ranks: every rank
     stages its shard and pulls the tail, then multiplies by the second matrix with the kernel whose gather warps pull
