@@ -145,13 +145,15 @@ def fsdp_comm_equivalence(rank, world):
 
 
 def layout_equivalence(rank, world):
-    """The same tiny bf16 model under expert parallel only, under tensor parallel 2 and (4+ GPUs) hybrid sharding."""
+    """The same tiny bf16 model under expert parallel only, under tensor parallel 2 (without and with sequence
+    parallelism) and (4+ GPUs) hybrid sharding."""
     from system_lab_b200.config import Config
     from system_lab_b200.ops import cuda as cops
     from system_lab_b200.trainer.loop import Trainer
     import torch.distributed as dist
     out = {}
-    variants = [("ep", []), ("tp2", ["tensor_model_parallel_size=2"])]
+    variants = [("ep", []), ("tp2", ["tensor_model_parallel_size=2"]),
+                ("tp2sp", ["tensor_model_parallel_size=2", "sequence_parallel=true"])]
     if world >= 4:
         variants.append(("hsdp2", ["num_distributed_optimizer_instances=2", "expert_model_parallel_size=2"]))
     for name, extra in variants:
@@ -174,6 +176,7 @@ def test_tensor_parallel_and_hybrid_sharding_match_expert_parallel():
     world = min(torch.cuda.device_count(), 4)
     for r in _run("layout_equivalence", world):
         assert r["tp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
+        assert r["tp2sp"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
         if "hsdp2" in r:
             assert r["hsdp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
 
