@@ -110,6 +110,7 @@ class ModelConfig:
 class ParallelConfig:
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False      # with tp > 1: residual stream, norms and MoE blocks hold 1/tp of every sequence; all-gather / reduce-scatter around the split matrices instead of all-reduces
+    tp_fused_gemm_reduce_scatter: bool = True   # sequence_parallel on GPUs: row-split GEMMs push their tiles to the rows' owners over peer memory (GEMM + reduce-scatter in one exchange) instead of GEMM then NCCL reduce-scatter
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: int = 1
     expert_model_parallel_size: int = 1

@@ -135,10 +135,12 @@ class GQAttention(nn.Module):
         else:
             o = ops.causal_attention(q, k, v, None, self.window)
         o2 = o.reshape(b, s, self.nq * self.d)
+        if self.tp is not None:
+            return self.tp.linear_leave(o2, self.wo)
         out = ops.linear(o2, self.wo)
         if self.o_lora is not None:
             out = out + self.o_lora(o2)
-        return self.tp.leave(out) if self.tp is not None else out
+        return out
 
 
 class MLAttention(nn.Module):
@@ -202,8 +204,8 @@ class MLAttention(nn.Module):
             o = ulysses_attention(qf, kf, v.contiguous(), self.cp_group, scale=self.scale)
         else:
             o = ops.causal_attention(qf, kf, v.contiguous(), self.scale, 0)
-        out = ops.linear(o.reshape(b, s, self.nh * self.vd), self.wo)
-        return tp.leave(out) if tp is not None else out
+        o2 = o.reshape(b, s, self.nh * self.vd)
+        return tp.linear_leave(o2, self.wo) if tp is not None else ops.linear(o2, self.wo)
 
 
 class DenseFFN(nn.Module):
@@ -229,10 +231,12 @@ class DenseFFN(nn.Module):
         if self.w1_lora is not None:
             gu = gu + self.w1_lora(x)
         act = ops.swiglu(gu)
+        if self.tp is not None:
+            return self.tp.linear_leave(act, self.w2)
         out = ops.linear(act, self.w2)
         if self.w2_lora is not None:
             out = out + self.w2_lora(act)
-        return self.tp.leave(out) if self.tp is not None else out
+        return out
 
 
 class MoEFFN(nn.Module):

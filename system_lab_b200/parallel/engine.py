@@ -137,6 +137,7 @@ class Engine:
         if mesh.tp > 1:
             from .tp import TensorParallel
             self.tp = TensorParallel(mesh.tp_group, mesh.tp_rank, mesh.tp, cfg.parallel.sequence_parallel)
+            self.tp.fused_gemm_rs = cfg.parallel.tp_fused_gemm_reduce_scatter and device.type == "cuda"
         with torch.device("meta"):
             self.model = SimpleMoE(
                 m, ep_rank=mesh.ep_rank, ep_size=mesh.ep, fp8=(cfg.precision.fp8_recipe if cfg.precision.fp8 else False),

@@ -149,6 +149,8 @@ class TensorParallel:
     def __init__(self, group, rank: int, size: int, sequence_parallel: bool = False):
         self.group, self.rank, self.size = group, rank, size
         self.sequence_parallel = sequence_parallel
+        self.fused_gemm_rs = False        # set by the engine (``tp_fused_gemm_reduce_scatter``)
+        self._gemm_rs = {}                # (batch, sequence, output width) -> GemmReduceScatter
 
     def enter(self, x):
         """In front of a column-split matrix whose input nothing else on this rank consumes."""
@@ -161,6 +163,23 @@ class TensorParallel:
         if self.sequence_parallel:
             return _ReduceScatterSeq.apply(x, self.group, self.size)
         return _ReduceFrom.apply(x, self.group)
+
+    def linear_leave(self, x, w):
+        """``leave(x @ w^T)`` for a row-split ``w``.  With sequence parallelism on the GPU kernel path
+        (``fused_gemm_rs``) the GEMM's epilogue pushes its tiles to the owners of the rows over peer memory and the
+        owners sum the partial rows: one exchange inside the GEMM instead of a GEMM followed by a reduce-scatter."""
+        from .. import ops
+        if self.sequence_parallel and self.fused_gemm_rs and x.dim() == 3 and x.is_cuda and ops.dense_kernels() \
+                and ops.kernel_mode() == "auto":
+            from ..ops import cuda as cops
+            if cops.linear_ok(x, w) and x.shape[1] % self.size == 0:
+                from ..comm.gemm_rs import GemmReduceScatter
+                key = (x.shape[0], x.shape[1], w.shape[0])
+                op = self._gemm_rs.get(key)
+                if op is None:
+                    op = self._gemm_rs[key] = GemmReduceScatter(self.group, self.size, self.rank, x.device, *key)
+                return op(x, w)
+        return self.leave(ops.linear(x, w))
 
     def gather_seq(self, x):
         """Whole sequences for a computation every rank repeats (identity without sequence parallelism)."""

@@ -140,3 +140,30 @@ def test_all_gather_fused_into_the_consuming_gemm(world):
             assert torch.equal(fulls[r], flat_ref), f"rank {r}: gathered buffer differs (call {call})"
             err = (outs[r].float() - want).abs().max().item()
             assert err < 2e-2 * (want.abs().max().item() + 1e-6), (r, call, err)
+
+
+@pytest.mark.parametrize("world,batch,seq,n,k", [(2, 2, 256, 256, 128), (4, 1, 1024, 2048, 192), (8, 2, 512, 576, 64)])
+def test_gemm_fused_with_reduce_scatter(world, batch, seq, n, k):
+    """Row-parallel GEMM whose epilogue pushes every output row to the rank that owns it (sequence split over the
+    group) and owners that sum the partial rows: equal to the fp32 sum of the ranks' products, three calls in a row
+    so that both receive regions and the acknowledgement wait are used.  Ranks are emulated phase by phase."""
+    from system_lab_b200.comm.gemm_rs import GemmReduceScatter
+    from system_lab_b200.comm.symm import EmulatedWorld
+    from system_lab_b200.ops import cuda as cops
+    dev = torch.device("cuda")
+    torch.manual_seed(world)
+    emu = EmulatedWorld(GemmReduceScatter.nbytes(batch, seq, n, world), world, dev)
+    ops = [GemmReduceScatter(None, world, r, dev, batch, seq, n, workspace=emu.workspace(r)) for r in range(world)]
+    s_local = seq // world
+    for _ in range(3):
+        a = [torch.randn(batch * seq, k, device=dev).to(torch.bfloat16) for _ in range(world)]
+        w = [(0.1 * torch.randn(n, k, device=dev)).to(torch.bfloat16) for _ in range(world)]
+        eps = [op.push(a[r], w[r]) for r, op in enumerate(ops)]
+        ys = [op.reduce(e) for op, e in zip(ops, eps)]
+        torch.cuda.synchronize()
+        cops.check_status()
+        full = sum(a[r].float() @ w[r].float().t() for r in range(world)).view(batch, seq, n)
+        for r in range(world):
+            want = full[:, r * s_local:(r + 1) * s_local].reshape(-1, n)
+            err = (ys[r].float() - want).abs().max().item()
+            assert err < 2e-2 * want.abs().max().item(), (r, err)

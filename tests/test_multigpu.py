@@ -153,7 +153,9 @@ def layout_equivalence(rank, world):
     import torch.distributed as dist
     out = {}
     variants = [("ep", []), ("tp2", ["tensor_model_parallel_size=2"]),
-                ("tp2sp", ["tensor_model_parallel_size=2", "sequence_parallel=true"])]
+                ("tp2sp", ["tensor_model_parallel_size=2", "sequence_parallel=true"]),
+                ("tp2sp_nccl", ["tensor_model_parallel_size=2", "sequence_parallel=true",
+                                "tp_fused_gemm_reduce_scatter=false"])]
     if world >= 4:
         variants.append(("hsdp2", ["num_distributed_optimizer_instances=2", "expert_model_parallel_size=2"]))
     for name, extra in variants:
@@ -176,7 +178,8 @@ def test_tensor_parallel_and_hybrid_sharding_match_expert_parallel():
     world = min(torch.cuda.device_count(), 4)
     for r in _run("layout_equivalence", world):
         assert r["tp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
-        assert r["tp2sp"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
+        assert r["tp2sp"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)        # GEMM + reduce-scatter over peer memory
+        assert r["tp2sp_nccl"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
         if "hsdp2" in r:
             assert r["hsdp2"] == pytest.approx(r["ep"], rel=2e-2, abs=5e-2)
 
