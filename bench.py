@@ -177,7 +177,7 @@ def main() -> int:
     cfg.validate(n)
     mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
                       cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances,
-                      cfg.parallel.tensor_model_parallel_size)
+                      cfg.parallel.tensor_model_parallel_size, cfg.parallel.expert_tensor_parallel_size)
     trainer = Trainer(cfg, mesh=mesh, device=dev)
     from system_lab_b200.ops import cuda as cops
     tokens_per_step = trainer.tokens_per_step

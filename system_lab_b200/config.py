@@ -111,6 +111,7 @@ class ParallelConfig:
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False      # with tp > 1: residual stream, norms and MoE blocks hold 1/tp of every sequence; all-gather / reduce-scatter around the split matrices instead of all-reduces
     tp_fused_gemm_reduce_scatter: bool = True   # sequence_parallel on GPUs: row-split GEMMs push their tiles to the rows' owners over peer memory (GEMM + reduce-scatter in one exchange) instead of GEMM then NCCL reduce-scatter
+    expert_tensor_parallel_size: int = 1   # 1: MoE blocks take 1/tp of the tokens per tensor-parallel rank; tp: every rank routes all tokens and holds 1/tp of each local expert's feed-forward columns
     pipeline_model_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: int = 1
     expert_model_parallel_size: int = 1

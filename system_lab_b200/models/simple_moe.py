@@ -242,23 +242,31 @@ class DenseFFN(nn.Module):
 class MoEFFN(nn.Module):
     """Routed experts (this rank owns ``num_experts / ep`` of them) plus an optional shared expert."""
 
-    def __init__(self, cfg: ModelConfig, ep_rank: int, ep_size: int, fp8: bool = False):
+    def __init__(self, cfg: ModelConfig, ep_rank: int, ep_size: int, fp8: bool = False, etp=None):
         super().__init__()
-        h, f = cfg.hidden_size, cfg.moe_ffn_hidden_size
+        h, f_all = cfg.hidden_size, cfg.moe_ffn_hidden_size
         self.cfg = cfg
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.e_local = cfg.num_experts // ep_size
         self.fp8 = fp8
+        # expert tensor parallelism: this rank holds 1 / etp.size of every local expert's feed-forward columns and
+        # routes all of the group's tokens; the partial outputs are summed over the group
+        self.etp = etp
+        f = f_all // (etp.size if etp is not None else 1)
         self.router = nn.Parameter(torch.empty(cfg.num_experts, h))
         self.experts_w1 = nn.Parameter(torch.empty(self.e_local, 2 * f, h))
         self.experts_w2 = nn.Parameter(torch.empty(self.e_local, h, f))
         self.experts_w1.is_expert = True
         self.experts_w2.is_expert = True
+        if etp is not None:
+            from ..parallel.tp import mark_sharded
+            mark_sharded(self.experts_w1, 1, (self.e_local, 2 * f_all, h), etp.segments([f_all, f_all]))
+            mark_sharded(self.experts_w2, 2, (self.e_local, h, f_all), etp.segments([f_all]))
         if cfg.moe_router_load_balancing_type == "bias":
             self.register_buffer("router_bias", torch.zeros(cfg.num_experts), persistent=True)
         else:
             self.router_bias = None
-        self.shared = DenseFFN(h, cfg.moe_shared_expert_intermediate_size) \
+        self.shared = DenseFFN(h, cfg.moe_shared_expert_intermediate_size, etp) \
             if cfg.moe_shared_expert_intermediate_size else None
         # logical (router) expert id -> physical slot (rank * E_local + local index); changed by expert relocation
         self.register_buffer("expert_map", torch.arange(cfg.num_experts), persistent=True)
@@ -276,6 +284,11 @@ class MoEFFN(nn.Module):
 
     def forward(self, x):
         cfg = self.cfg
+        x_in = x
+        if self.etp is not None:
+            # whole sequences for the router, which every rank of the group repeats (identity without sequence
+            # parallelism; its backward keeps this rank's slice: the repeated computation's gradients are equal)
+            x = self.etp.gather_seq(x)
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         logits = ops.router_logits(x2, self.router)
@@ -291,6 +304,11 @@ class MoEFFN(nn.Module):
                                        cfg.moe_norm_topk_prob, cfg.moe_router_topk_scaling_factor, aux_coeff)
         if aux_coeff:
             self.aux = aux
+        if self.etp is not None:
+            # the experts below are this rank's column slices: gradients of the rows and of the gate weights are
+            # partial sums, added up over the group on the way back
+            x2 = self.etp.copy_to(x2)
+            w = self.etp.copy_to(w)
         d = self.dispatcher
         kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
         reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
@@ -345,6 +363,11 @@ class MoEFFN(nn.Module):
         ye = ops.grouped_linear(act, self.experts_w2.to(x.dtype), plan.expert_offsets, plan.expert_counts, self.fp8,
                                 out=out_buf, dead=dead, bwd_ready=d if defer_bwd else None)
         out = d.combine_rows(plan, ye, dead=dead, defer_bwd=True) if defer_bwd else d.combine_rows(plan, ye, dead=dead)
+        if self.etp is not None:
+            out = self.etp.leave(out.reshape(shp))          # sum of the column slices' partial outputs
+            if self.shared is not None:
+                out = out + self.shared(x_in)               # column-split like a dense block, with its own links
+            return out
         if self.shared is not None:
             out = out + self.shared(x2)
         return out.reshape(shp)
@@ -397,8 +420,9 @@ class _Recompute(torch.autograd.Function):
 
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, ep_rank: int, ep_size: int, fp8: bool = False,
-                 cp_group=None, tp=None):
+                 cp_group=None, tp=None, expert_tp: bool = False):
         super().__init__()
+        self.expert_tp = expert_tp and tp is not None
         self.layer_idx = layer_idx
         self.eps = cfg.norm_epsilon
         self.tp = tp
@@ -408,8 +432,8 @@ class DecoderLayer(nn.Module):
         self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.norm_epsilon)
         self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense
         if self.is_moe:
-            self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8)
-            if tp is not None:
+            self.ffn = MoEFFN(cfg, ep_rank, ep_size, fp8, tp if self.expert_tp else None)
+            if tp is not None and not self.expert_tp:
                 # the block sees this rank's slice of the tokens: replicated parameters inside it (router, shared
                 # expert) get partial gradients, summed over the tensor-parallel group by the engine
                 self.ffn.aux_scale = 1.0 / tp.size
@@ -427,7 +451,7 @@ class DecoderLayer(nn.Module):
         self.recompute_ffn = False        # set by the engine for recompute_granularity=selective
 
     def _ffn_block(self, y, h):
-        if self.tp is not None and self.is_moe and not self.tp.sequence_parallel:
+        if self.tp is not None and self.is_moe and not self.tp.sequence_parallel and not self.expert_tp:
             # MoE under tensor parallelism: every rank of the group routes 1 / tp of the shared tokens through the
             # expert-parallel exchange, then the group reassembles the block's output
             shp = y.shape
@@ -492,7 +516,8 @@ class SimpleMoE(nn.Module):
     def __init__(self, cfg: ModelConfig, *, ep_rank: int = 0, ep_size: int = 1, fp8: bool = False,
                  layer_start: int = 0, layer_end: int | None = None, first_stage: bool = True,
                  last_stage: bool = True, cp_group=None, cp_rank: int = 0, cp_size: int = 1,
-                 bf16_first_layers: int = 0, bf16_last_layers: int = 0, layer_ids=None, tp=None):
+                 bf16_first_layers: int = 0, bf16_last_layers: int = 0, layer_ids=None, tp=None,
+                 expert_tp: bool = False):
         super().__init__()
         self.cfg = cfg
         layer_end = cfg.num_layers if layer_end is None else layer_end
@@ -503,7 +528,7 @@ class SimpleMoE(nn.Module):
         def layer_fp8(i):          # the first / last layers of the whole decoder may be kept out of fp8
             return fp8 if bf16_first_layers <= i < cfg.num_layers - bf16_last_layers else False
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group, tp) for i in ids])
+            [DecoderLayer(cfg, i, ep_rank, ep_size, layer_fp8(i), cp_group, tp, expert_tp) for i in ids])
         self.head = Head(cfg) if last_stage else None
         if tp is not None and tp.sequence_parallel:
             # embedding, final norm and vocabulary projection run on this rank's part of every sequence

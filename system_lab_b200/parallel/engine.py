@@ -37,6 +37,15 @@ def init_unit_weights(module: nn.Module, global_prefix: str, std: float, seed: i
                 p.fill_(1.0)
             elif name.endswith("lora_b"):
                 p.zero_()                      # adapters start as a zero update
+            elif hasattr(p, "tp_segments") and getattr(p, "is_expert", False):
+                # expert tensor parallelism: draw every local expert's global matrices, keep this rank's columns
+                from .tp import take_segments
+                e_local = p.shape[0]
+                for j in range(e_local):
+                    full = torch.empty(p.tp_global_shape[1:], dtype=p.dtype if p.is_cuda else torch.float32,
+                                       device=p.device)
+                    seeded_normal_(full, std, seed, f"{gname}.{ep_rank * e_local + j}")
+                    p[j].copy_(take_segments(full, p.tp_dim - 1, p.tp_segments))
             elif hasattr(p, "tp_segments"):
                 # draw the global matrix, keep this tensor-parallel rank's rows / columns
                 from .tp import take_segments
@@ -145,7 +154,7 @@ class Engine:
                 first_stage=mesh.is_first_stage(), last_stage=mesh.is_last_stage(),
                 cp_group=mesh.cp_group if mesh.cp > 1 else None, cp_rank=mesh.cp_rank, cp_size=mesh.cp,
                 bf16_first_layers=cfg.precision.num_layers_at_start_in_bf16,
-                bf16_last_layers=cfg.precision.num_layers_at_end_in_bf16, tp=self.tp)
+                bf16_last_layers=cfg.precision.num_layers_at_end_in_bf16, tp=self.tp, expert_tp=mesh.etp > 1)
         self.units: list[Unit] = []
         self.anchor = torch.zeros(1, device=device, requires_grad=True)
         self._aux_out: list[torch.Tensor] = []
@@ -216,7 +225,9 @@ class Engine:
             if fused:
                 if shared is None:
                     from ..moe.fused_dispatch import FusedDispatcher
-                    tokens = self.cfg.train.micro_batch_size * m.seq_length // (self.mesh.cp * self.mesh.tp)
+                    # tokens one MoE block sees: 1 / tp of the group's tokens, or all of them under expert tensor parallelism
+                    tokens = self.cfg.train.micro_batch_size * m.seq_length // (
+                        self.mesh.cp * (self.mesh.tp // self.mesh.etp))
                     shared = FusedDispatcher(self.mesh, m.num_experts, m.moe_router_topk, m.hidden_size,
                                              max_tokens=tokens, pad_to=m.moe_pad_expert_rows_to,
                                              device=self.device, dtype=self.compute_dtype,

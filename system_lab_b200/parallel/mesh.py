@@ -44,6 +44,7 @@ class Mesh:
     world_group: object = None
     tp: int = 1
     tp_rank: int = 0
+    etp: int = 1                   # expert tensor parallelism: 1 (MoE blocks fold tp into their data axis) or tp
     tp_group: object = None        # ranks that split the heads / feed-forward columns of the same tokens
     stage_group: object = None     # every rank of this pipeline stage (equals data_group when tp == 1)
     data_ranks: tuple = ()
@@ -71,7 +72,7 @@ class Mesh:
 
     @property
     def edp(self) -> int:
-        return (self.dp * self.tp // self.ep) * self.cp
+        return (self.dp * self.tp // (self.ep * self.etp)) * self.cp
 
     @property
     def data_size(self) -> int:
@@ -135,14 +136,16 @@ def _hybrid_split(lists, replicas: int, rank: int):
     return got
 
 
-def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1, tp: int = 1) -> Mesh:
+def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1, tp: int = 1, etp: int = 1) -> Mesh:
+    if etp not in (1, tp):
+        raise ValueError(f"expert tensor parallel size {etp}: use 1 or the tensor parallel size {tp}")
     if not dist.is_initialized():
         if pp * cp * tp != 1:
             raise ValueError("pp/cp/tp > 1 needs an initialised process group")
         return single_process_mesh()
     world, rank = dist.get_world_size(), dist.get_rank()
     if tp > 1:
-        return _build_mesh_tp(pp, ep, cp, replicas, tp)
+        return _build_mesh_tp(pp, ep, cp, replicas, tp, etp)
     if world % (pp * cp):
         raise ValueError(f"world={world} not divisible by pp*cp={pp * cp}")
     dp = world // (pp * cp)
@@ -199,16 +202,22 @@ def build_mesh(pp: int = 1, ep: int = 1, cp: int = 1, replicas: int = 1, tp: int
     return m
 
 
-def _build_mesh_tp(pp: int, ep: int, cp: int, replicas: int, tp: int) -> Mesh:
+def _build_mesh_tp(pp: int, ep: int, cp: int, replicas: int, tp: int, etp: int = 1) -> Mesh:
     """The mesh with a tensor-parallel axis (kept apart so that the ``tp == 1`` construction, and the order in which
-    it creates its communicators, stays exactly as it was)."""
+    it creates its communicators, stays exactly as it was).
+
+    ``etp == 1``: the MoE blocks treat the tensor-parallel ranks as data ranks (each takes ``1 / tp`` of the tokens)
+    and the expert axis runs over ``dp * tp``.  ``etp == tp`` (expert tensor parallelism, the ``ETP x EP x EDP``
+    folding of ``moe/MegatronCore_MoE_reading_notes.md:159-195``): every tensor-parallel rank routes all the group's
+    tokens and holds ``1 / tp`` of every local expert's feed-forward columns; the expert axis runs over ``dp`` inside
+    each tensor-parallel plane."""
     world, rank = dist.get_world_size(), dist.get_rank()
     if world % (pp * cp * tp):
         raise ValueError(f"world={world} not divisible by pp*cp*tp={pp * cp * tp}")
     if replicas > 1:
         raise ValueError("num_distributed_optimizer_instances > 1 is not combined with tensor parallelism")
     dp = world // (pp * cp * tp)
-    xs = dp * tp                                  # the MoE blocks' data axis
+    xs = dp * tp if etp == 1 else dp              # the MoE blocks' data axis
     ep = min(ep, xs)
     if xs % ep:
         raise ValueError(f"dp*tp={xs} not divisible by ep={ep}")
@@ -217,16 +226,18 @@ def _build_mesh_tp(pp: int, ep: int, cp: int, replicas: int, tp: int) -> Mesh:
     def rid(p, d, c, t):
         return ((p * dp + d) * cp + c) * tp + t
 
-    def rid_x(p, x, c):
-        return rid(p, x // tp, c, x % tp)
-
     tp_rank = rank % tp
+
+    def rid_x(p, x, c, t=0):
+        return rid(p, x // tp, c, x % tp) if etp == 1 else rid(p, x, c, t)
+
     cp_rank = (rank // tp) % cp
     dp_rank = (rank // (tp * cp)) % dp
     pp_rank = rank // (tp * cp * dp)
-    x = dp_rank * tp + tp_rank
+    x = dp_rank * tp + tp_rank if etp == 1 else dp_rank
     m = Mesh(world=world, rank=rank, pp=pp, dp=dp, cp=cp, ep=ep, pp_rank=pp_rank, dp_rank=dp_rank,
-             cp_rank=cp_rank, ep_rank=x % ep, edp_rank=x // ep, world_group=dist.group.WORLD, tp=tp, tp_rank=tp_rank)
+             cp_rank=cp_rank, ep_rank=x % ep, edp_rank=x // ep, world_group=dist.group.WORLD, tp=tp, tp_rank=tp_rank,
+             etp=etp)
 
     def mk(all_lists):
         got, got_ranks = None, ()
@@ -239,8 +250,11 @@ def _build_mesh_tp(pp: int, ep: int, cp: int, replicas: int, tp: int) -> Mesh:
     P, D, C, T, X = range(pp), range(dp), range(cp), range(tp), range(xs)
     m.data_group, m.data_ranks = mk([[rid(p, d, c, t) for d in D for c in C] for p in P for t in T])
     m.dp_group, _ = mk([[rid(p, d, c, t) for d in D] for p in P for c in C for t in T])
-    m.ep_group, m.ep_ranks = mk([[rid_x(p, g * ep + e, c) for e in range(ep)] for p in P for g in range(edp_n) for c in C])
-    m.edp_group, m.edp_ranks = mk([[rid_x(p, g * ep + e, c) for g in range(edp_n) for c in C] for p in P for e in range(ep)])
+    planes = range(1) if etp == 1 else T          # with expert tensor parallelism every plane has expert groups of its own
+    m.ep_group, m.ep_ranks = mk([[rid_x(p, g * ep + e, c, t) for e in range(ep)]
+                                 for p in P for g in range(edp_n) for c in C for t in planes])
+    m.edp_group, m.edp_ranks = mk([[rid_x(p, g * ep + e, c, t) for g in range(edp_n) for c in C]
+                                   for p in P for e in range(ep) for t in planes])
     m.cp_group, _ = mk([[rid(p, d, c, t) for c in C] for p in P for d in D for t in T])
     pp_lists = [[rid(p, d, c, t) for p in P] for d in D for c in C for t in T]
     m.pp_group, m.pp_ranks = mk(pp_lists)

@@ -55,6 +55,14 @@ def check_config(cfg: Any, world_size: int | None = None) -> list[dict]:
         elif (m.seq_length // max(cp, 1)) % tp:
             out.append(_p("tp_divides_sequence", f"seq_length / cp = {m.seq_length // max(cp, 1)} % tp={tp} != 0 "
                                                  "(sequence_parallel shards every sequence over tp)"))
+    etp = getattr(p, "expert_tensor_parallel_size", 1)
+    if etp not in (1, tp):
+        out.append(_p("etp_is_one_or_tp", f"expert_tensor_parallel_size={etp}: use 1 or tensor_model_parallel_size={tp}"))
+    elif etp > 1:
+        if m.num_experts > 0 and m.moe_ffn_hidden_size % etp:
+            out.append(_p("etp_divides_moe_ffn", f"moe_ffn_hidden_size={m.moe_ffn_hidden_size} % etp={etp} != 0"))
+        if dp is not None and dp % ep:
+            out.append(_p("etp_ep_divides_dp", f"with expert tensor parallelism ep={ep} must divide dp={dp}"))
     if tp > 1:
         # heads and dense feed-forward columns split over tp; MoE blocks take 1/tp of the tokens per rank
         if (t.micro_batch_size * m.seq_length // max(cp, 1)) % tp:

@@ -59,7 +59,7 @@ class Trainer:
             cfg.validate(world)
             mesh = build_mesh(cfg.parallel.pipeline_model_parallel_size, cfg.parallel.expert_model_parallel_size,
                               cfg.parallel.context_parallel_size, cfg.parallel.num_distributed_optimizer_instances,
-                              cfg.parallel.tensor_model_parallel_size)
+                              cfg.parallel.tensor_model_parallel_size, cfg.parallel.expert_tensor_parallel_size)
         self.mesh, self.device = mesh, device or torch.device("cpu")
         mode = cfg.train.use_cuda_kernels
         if mode == "false" or self.device.type != "cuda":

@@ -82,6 +82,9 @@ def test_tensor_parallel_and_hybrid_sharding_rules():
         return [p["rule"] for p in check_config(cfg, world) if p["severity"] == "error"]
     assert rules(["tensor_model_parallel_size=2", "expert_model_parallel_size=2"], 2) == []
     assert "tp_divides_num_heads" in rules(["tensor_model_parallel_size=8", "expert_model_parallel_size=1"], 8)
+    assert "etp_is_one_or_tp" in rules(["tensor_model_parallel_size=2", "expert_tensor_parallel_size=4",
+                                        "expert_model_parallel_size=1"], 2)
+    assert rules(["tensor_model_parallel_size=2", "expert_tensor_parallel_size=2", "expert_model_parallel_size=1"], 2) == []
     assert "sp_needs_tp" in rules(["sequence_parallel=true", "expert_model_parallel_size=1"], 1)
     assert rules(["tensor_model_parallel_size=2", "expert_model_parallel_size=2", "sequence_parallel=true"], 2) == []
     assert "tp_excludes_hsdp" in rules(["tensor_model_parallel_size=2", "num_distributed_optimizer_instances=2"], 8)

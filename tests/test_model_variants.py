@@ -84,6 +84,15 @@ def test_dsv3_shape_sequence_parallel():
         assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)
 
 
+def test_dsv3_shape_expert_tensor_parallel():
+    """Shared expert column-split with the routed experts; MLA heads split; first layer dense."""
+    (single, _), = run_ranks(_train, 1, DSV3_TINY + ["expert_model_parallel_size=1"], 4)
+    res = run_ranks(_train, 2, DSV3_TINY + ["expert_model_parallel_size=1", "tensor_model_parallel_size=2",
+                                            "expert_tensor_parallel_size=2"], 4)
+    for losses, _ in res:
+        assert losses == pytest.approx(single, rel=5e-5, abs=5e-5)
+
+
 def test_aux_loss_is_carried_through_every_recompute_mode():
     """The load-balancing loss reaches the objective (and the router's gradient) whether the MoE block is kept,
     recomputed alone (selective: the loss leaves the recompute node as a second output) or with its whole layer

@@ -234,6 +234,22 @@ def test_sequence_parallel_with_pipeline_and_selective_recompute(single_curve):
     assert res[-1][0] == pytest.approx(single_curve[:4], rel=2e-5, abs=2e-5)
 
 
+def test_expert_tensor_parallel_matches(single_curve, tmp_path):
+    """Every tensor-parallel rank routes all tokens and holds half of each expert's feed-forward columns; the expert
+    axis runs over the data ranks inside each tensor-parallel plane; partial outputs are summed over the group.
+    Plain, with sequence parallelism, and resumed from a checkpoint."""
+    etp = ["tensor_model_parallel_size=2", "expert_tensor_parallel_size=2"]
+    res = run_ranks(_train, 2, BASE + ["expert_model_parallel_size=1"] + etp, 6)
+    for losses, _ in res:
+        assert losses == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+    ov = BASE + ["expert_model_parallel_size=2", "sequence_parallel=true"] + etp
+    ck = str(tmp_path / "ck")
+    full = run_ranks(_train, 4, ov, 3, ck, None, 3)
+    assert full[0][0] == pytest.approx(single_curve, rel=2e-5, abs=2e-5)
+    resumed = run_ranks(_train, 4, ov, 3, None, ck)
+    assert resumed[0][0] == full[0][0][3:]
+
+
 def test_tensor_parallel_with_data_parallel_selective_and_resume(single_curve, tmp_path):
     ov = BASE + ["expert_model_parallel_size=4", "tensor_model_parallel_size=2", "recompute_granularity=selective"]
     ck = str(tmp_path / "ck")
