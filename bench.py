@@ -226,12 +226,15 @@ def main() -> int:
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
     t0 = time.perf_counter()
+    step_ms = []                                                 # every step ends in a host read: host clock per step
     for i in range(args.steps):
+        ts = time.perf_counter()
         mbs = trainer.data.microbatches(trainer.step)          # pinned host tensors
         h2d = sum(a.numel() * a.element_size() + b.numel() * b.element_size() for a, b in mbs)
         out = trainer.train_step(batches=mbs)
         loss_host = out["loss"].cpu()                            # device -> host read of the step's result
         d2h = loss_host.numel() * loss_host.element_size()
+        step_ms.append((time.perf_counter() - ts) * 1e3)
     if dev.type == "cuda":
         f1.record()
         torch.cuda.synchronize()
@@ -282,7 +285,9 @@ def main() -> int:
                                         "EP8 step of 966.76 ms = 135.6k tokens/s/box (a different model)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms / args.steps,
+                    "rank0_step_ms_min_median_max": [round(sorted(step_ms)[0], 2), round(sorted(step_ms)[len(step_ms) // 2], 2),
+                                                     round(sorted(step_ms)[-1], 2)] if step_ms else None},
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
             "expert_relocations": trainer.relocator.history if trainer.relocator else [],

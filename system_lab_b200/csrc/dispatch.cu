@@ -109,7 +109,7 @@ __global__ void moe_publish_kernel(int* __restrict__ block_hist, int n_blocks, i
 //                     walks the local expert index j outermost and the destination rank innermost, starting at the
 //                     right-hand neighbour ((me + 1 + ph) % world): every rank is writing a different peer at any
 //                     moment, and local expert j of every rank is complete after (j + 1) / E_local of the exchange.
-constexpr int SCATTER_CHUNK = 16;
+constexpr int SCATTER_CHUNK = 16;          // rows per work item; at most 32 (one lane per row in places)
 
 __device__ __forceinline__ int send_order_expert(int oi, int world, int me, int e_local) {
   const int j = oi / world, ph = oi % world;
@@ -583,8 +583,20 @@ moe_scatter_sorted_kernel(const __nv_bfloat16* __restrict__ x, const float* __re
           }
         }
       }
-      if (pair_scalar && lane == 0) reinterpret_cast<float*>(pb + ws.scalars)[row] = pair_scalar[p];
-      if (ws.origin >= 0 && lane == 0) reinterpret_cast<int*>(pb + ws.origin)[row] = (me << 24) | p;
+    }
+    // the chunk's per-row scalars and origins: one lane per row, so that rows in consecutive slots (the usual case:
+    // slots are handed out in pair order) leave as one 64-byte store instead of sixteen 4-byte ones
+    if (warp == 0 && (pair_scalar || ws.origin >= 0)) {
+      const int i = r0 + lane;
+      if (i < r1) {
+        const int pp = perm[send_prefix[e] + i];
+        const int ll = pair_loc[pp];
+        if (ll >= 0 && (ll >> 24) == d) {
+          const int rr = ll & 0xFFFFFF;
+          if (pair_scalar) reinterpret_cast<float*>(pb + ws.scalars)[rr] = pair_scalar[pp];
+          if (ws.origin >= 0) reinterpret_cast<int*>(pb + ws.origin)[rr] = (me << 24) | pp;
+        }
+      }
     }
     // chunk complete: the barrier orders every thread's peer stores before thread 0, whose system-scope fence
     // (cumulative) publishes them ahead of the chunk count; the block that counts the expert's last chunk fences
