@@ -41,6 +41,9 @@ class FsdpPeerComm:
         self.done = torch.zeros(1, dtype=torch.int32, device=device)
         self.status = cops.status_word(device)
         self._factory = workspace_factory or (lambda nbytes: SymmetricWorkspace(nbytes, group, world, rank, device))
+        # reduce-scatter through the switch (``multimem.ld_reduce`` on the workspaces' multicast address) instead of
+        # one peer load per rank; needs a multicast mapping (NVSwitch) and a free entry in the pointer table
+        self.nvls = False
 
     def _ensure(self, nbytes: int) -> None:
         if self.ws is not None and nbytes <= self.slot_bytes:
@@ -48,6 +51,10 @@ class FsdpPeerComm:
         self.slot_bytes = (max(nbytes, 1 << 20) + 255) // 256 * 256
         self.ws = self._factory(4096 + NSLOT * self.slot_bytes)
         self._ptrs = (ctypes.c_long * _MAXW)(*(list(self.ws.ptrs) + [0] * (_MAXW - len(self.ws.ptrs))))
+        mc = int(getattr(self.ws, "multicast_ptr", 0) or 0)
+        self.nvls_active = bool(self.nvls and mc and self.world < _MAXW)
+        if self.nvls_active:
+            self._ptrs[self.world] = mc         # the entry behind the last rank: multicast address (csrc/fsdp_comm.cu)
         self._lay = (ctypes.c_long * 4)(0, 1024, 4096, self.slot_bytes)
         self.slot_last = [0] * NSLOT
 
@@ -147,8 +154,16 @@ class FsdpPeerComm:
                   cops.stream())
 
 
-def make_fsdp_comms(mesh, device):
+def make_fsdp_comms(mesh, device, nvls: bool = False):
     """(dense_comm, expert_comm) for the engine; ``None`` where the group has a single rank."""
+    dense, expert = _make_fsdp_comms(mesh, device)
+    for c in (dense, expert):
+        if c is not None:
+            c.nvls = nvls
+    return dense, expert
+
+
+def _make_fsdp_comms(mesh, device):
     if mesh.replicas > 1:          # hybrid sharding: the peer collectives span one block of the data axis
         dense = (FsdpPeerComm(mesh.data_shard_group, mesh.data_shard_size, mesh.data_shard_rank, device)
                  if mesh.data_shard_size > 1 else None)

@@ -125,6 +125,7 @@ class ParallelConfig:
     ddp_average_in_collective: bool = True
     num_distributed_optimizer_instances: int = 1
     fsdp_fused_collectives: bool = True  # peer-memory all-gather / reduce-scatter kernels instead of NCCL
+    fsdp_nvls_reduce: bool = False       # peer reduce-scatter sums through the switch (multimem.ld_reduce on the workspaces' multicast address) instead of one peer load per rank
     fsdp_prefetch: bool = False          # gather the next unit's parameters on a side stream while this one computes
     fsdp_gather_in_gemm: bool = True     # forward: a decoder layer's dense matrices are all-gathered inside the first GEMM that multiplies one of them (peer collectives only)
 

@@ -143,9 +143,25 @@ struct FsAdam {
 // piece[i] = scale * sum_r peer r's staged grad[me * n8 * 8 + i]  (bf16 in, fp32 accumulate).
 // FUSE_ADAM: instead of writing the reduced gradient, apply AdamW to the fp32 master shard / fp32 moments and
 // write the bf16 compute copy; sum(g^2) goes to sq_out.
+// `mc`: multicast address of the workspaces (the same offsets reach every rank's copy through the switch), or null.
+// With it the sum over the ranks is one `multimem.ld_reduce` per 16 bytes: the switch reads every rank's slot, adds in
+// fp32 and returns bf16, so a rank's NVLink ingress is its shard once instead of once per peer.
+__device__ __forceinline__ void multimem_sum_bf16x8(const void* mc_addr, float (&f)[8]) {
+  uint32_t r0, r1, r2, r3;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "l"(mc_addr)
+               : "memory");
+  bf16x8 v;
+  uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+  u[0] = r0; u[1] = r1; u[2] = r2; u[3] = r3;
+  unpack8(v, f);
+}
+
 template <bool FUSE_ADAM>
 __global__ void __launch_bounds__(512)
-fsdp_reduce_scatter_kernel(float* __restrict__ piece, long n8, FsPeers peers, FsLayout lay, int world, int me, int slot,
+fsdp_reduce_scatter_kernel(const uint8_t* __restrict__ mc, float* __restrict__ piece, long n8, FsPeers peers,
+                           FsLayout lay, int world, int me, int slot,
                            int epoch, float scale, float* __restrict__ master, float* __restrict__ m,
                            float* __restrict__ v, __nv_bfloat16* __restrict__ out_bf16, const float* __restrict__ coef,
                            float* __restrict__ sq_out, FsAdam a, int* status, unsigned long long limit_ns,
@@ -157,7 +173,9 @@ fsdp_reduce_scatter_kernel(float* __restrict__ piece, long n8, FsPeers peers, Fs
   const float c = (FUSE_ADAM && coef) ? *coef : 1.f;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (good) {
+    if (good && mc) {
+      multimem_sum_bf16x8(reinterpret_cast<const bf16x8*>(mc + lay.slots + slot * lay.slot_bytes) + (long)me * n8 + i, acc);
+    } else if (good) {
       for (int r = 0; r < world; ++r) {
         const bf16x8* src = reinterpret_cast<const bf16x8*>(peers.base[r] + lay.slots + slot * lay.slot_bytes) + (long)me * n8 + i;
         float f[8];
@@ -224,6 +242,10 @@ static FsPeers fs_peers(const long* ptrs, int world) {
   for (int i = 0; i < FS_MAX_WORLD; ++i) p.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
   return p;
 }
+// peer_ptrs[world], when world < FS_MAX_WORLD: multicast address of the workspaces, or 0 (plain peer loads).
+static const uint8_t* fs_multicast(const long* ptrs, int world) {
+  return world < FS_MAX_WORLD ? reinterpret_cast<const uint8_t*>(ptrs[world]) : nullptr;
+}
 static FsLayout fs_layout(const long* o) {
   FsLayout l;
   l.ready_flags = o[0]; l.ack_flags = o[1]; l.slots = o[2]; l.slot_bytes = o[3];
@@ -266,7 +288,7 @@ extern "C" int slab_fsdp_reduce_scatter(float* piece, long shard_numel, const lo
   if (shard_numel % 8 || world > FS_MAX_WORLD) return -100;
   FsAdam a{};
   fsdp_reduce_scatter_kernel<false><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
-      piece, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, nullptr,
+      fs_multicast(peer_ptrs, world), piece, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, nullptr,
       nullptr, nullptr, nullptr, nullptr, nullptr, a, status, g_fs_limit_ns, done_counter);
   return (int)cudaGetLastError();
 }
@@ -280,7 +302,7 @@ extern "C" int slab_fsdp_reduce_scatter_adamw(long shard_numel, const long* peer
   if (shard_numel % 8 || world > FS_MAX_WORLD || decay_end % 8) return -100;
   FsAdam a{lr, beta1, beta2, eps, wd, bc1, bc2, decay_end};
   fsdp_reduce_scatter_kernel<true><<<fs_grid(shard_numel / 8), 512, 0, st>>>(
-      nullptr, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, master,
+      fs_multicast(peer_ptrs, world), nullptr, shard_numel / 8, fs_peers(peer_ptrs, world), fs_layout(layout), world, me, slot, epoch, scale, master,
       m, v, (__nv_bfloat16*)out_bf16, coef, sq_out, a, status, g_fs_limit_ns, done_counter);
   return (int)cudaGetLastError();
 }

@@ -212,7 +212,7 @@ class Engine:
         if (self.device.type == "cuda" and self.cfg.parallel.fsdp_fused_collectives
                 and self.cfg.parallel.fsdp and self.mesh.world > 1 and self.compute_dtype == torch.bfloat16):
             from ..comm.fsdp_comm import make_fsdp_comms
-            return make_fsdp_comms(self.mesh, self.device)
+            return make_fsdp_comms(self.mesh, self.device, self.cfg.parallel.fsdp_nvls_reduce)
         return None, None
 
     def _make_dispatchers(self):

@@ -126,20 +126,35 @@ def train_equivalence(rank, world):
 
 def fsdp_comm_equivalence(rank, world):
     """Peer-memory all-gather / reduce-scatter vs NCCL under FSDP with experts sharded too (ep=1)."""
+    return _fsdp_variants(world, (("false", "false", ""), ("true", "false", ""), ("false", "true", ""),
+                                  ("true", "true", "")))
+
+
+def fsdp_nvls_equivalence(rank, world):
+    """The peer reduce-scatter with the sum done by the switch (multimem) against the same kernels on peer loads."""
+    return _fsdp_variants(world, (("true", "false", ""), ("true", "true", ""), ("true", "false", "nvls"),
+                                  ("true", "true", "nvls")))
+
+
+def _fsdp_variants(world, variants):
     from system_lab_b200.config import Config
     from system_lab_b200.ops import cuda as cops
     from system_lab_b200.trainer.loop import Trainer
     out, mesh, dev = {}, None, None
-    for fused, in_bwd in (("false", "false"), ("true", "false"), ("false", "true"), ("true", "true")):
+    for fused, in_bwd, nvls in variants:
         cfg = Config.load(preset="qwen3-30b-a3b", overrides=[
             "num_layers=2", "num_experts=8", "seq_length=256", "vocab_size=2048", "micro_batch_size=2",
             f"global_batch_size={2 * world}", "expert_model_parallel_size=1", "recompute_granularity=full",
-            "device=cuda", f"fsdp_fused_collectives={fused}", f"optimizer_in_backward={in_bwd}"])
+            "device=cuda", f"fsdp_fused_collectives={fused}", f"optimizer_in_backward={in_bwd}",
+            f"fsdp_nvls_reduce={'true' if nvls else 'false'}"])
         tr = Trainer(cfg) if mesh is None else Trainer(cfg, mesh=mesh, device=dev)
         mesh, dev = tr.mesh, tr.device
-        out[fused + in_bwd] = [float(tr.train_step()["loss"]) for _ in range(4)]
+        out[fused + in_bwd + nvls] = [float(tr.train_step()["loss"]) for _ in range(4)]
         torch.cuda.synchronize()
         cops.check_status()
+        if nvls:      # whether the reduce-scatter really went through the switch (needs a multicast mapping)
+            comms = [g.comm for g in tr.engine.all_groups() if getattr(g, "comm", None) is not None]
+            out["nvls_active"] = bool(comms) and all(getattr(c, "nvls_active", False) for c in comms if c.ws is not None)
         del tr
     return out
 
@@ -190,6 +205,15 @@ def test_fsdp_peer_collectives_match_nccl():
         assert r["truefalse"] == pytest.approx(r["falsefalse"], rel=2e-2, abs=5e-2)
         # optimizer inside backward: reduce-scatter + cast + AdamW in one peer-memory kernel vs NCCL + AdamW
         assert r["truetrue"] == pytest.approx(r["falsetrue"], rel=2e-2, abs=5e-2)
+
+
+def test_fsdp_reduce_scatter_through_the_switch_matches_peer_loads():
+    world = min(torch.cuda.device_count(), 4)
+    for r in _run("fsdp_nvls_equivalence", world):
+        if not r["nvls_active"]:
+            pytest.skip("no multicast mapping for the symmetric workspaces on this machine")
+        assert r["truefalsenvls"] == pytest.approx(r["truefalse"], rel=2e-2, abs=5e-2)
+        assert r["truetruenvls"] == pytest.approx(r["truetrue"], rel=2e-2, abs=5e-2)
 
 
 def test_fused_dispatch_matches_nccl_baseline():
