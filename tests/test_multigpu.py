@@ -207,6 +207,57 @@ def test_fsdp_peer_collectives_match_nccl():
         assert r["truetrue"] == pytest.approx(r["falsetrue"], rel=2e-2, abs=5e-2)
 
 
+def seldom_used_paths(rank, world):
+    """Paths that the headline benchmark leaves off, each against the default run of the same tiny model: parameter
+    prefetch on a side stream, the poison-fill debug mode of the dispatcher, and (two pipeline stages, two virtual
+    stages each) the interleaved schedule over NCCL point-to-point."""
+    import os
+    import torch.distributed as dist
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.trainer.loop import Trainer
+    base = ["num_layers=4", "num_experts=16", "seq_length=512", "vocab_size=4096", "micro_batch_size=2",
+            "recompute_granularity=selective", "device=cuda"]
+    variants = [("default", [f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}"], {}),
+                ("prefetch", [f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}",
+                              "fsdp_prefetch=true", "fsdp_gather_in_gemm=false"], {}),
+                ("poison", [f"global_batch_size={2 * world}", f"expert_model_parallel_size={world}"],
+                 {"SLAB_POISON": "1"}),
+                ("pp1", ["global_batch_size=4", "expert_model_parallel_size=1"], {}),
+                ("pp2vpp2", ["global_batch_size=4", "expert_model_parallel_size=1", "pipeline_model_parallel_size=2",
+                             "virtual_pipeline_model_parallel_size=2"], {})]
+    out = {}
+    for name, extra, env in variants:
+        if world != 2 and name in ("pp1", "pp2vpp2"):
+            continue
+        for k, v in env.items():
+            os.environ[k] = v
+        try:
+            cfg = Config.load(preset="qwen3-30b-a3b", overrides=base + extra)
+            tr = Trainer(cfg)
+            out[name] = [float(tr.train_step()["loss"]) for _ in range(3)]
+            torch.cuda.synchronize()
+            cops.check_status()
+            tr.close()
+            del tr
+        finally:
+            for k in env:
+                os.environ.pop(k, None)
+        dist.barrier()
+    return out
+
+
+def test_prefetch_poison_fill_and_interleaved_pipeline_on_gpus():
+    world = min(torch.cuda.device_count(), 4)
+    res = _run("seldom_used_paths", world)
+    for r in res:
+        assert r["prefetch"] == pytest.approx(r["default"], rel=2e-2, abs=5e-2)
+        assert r["poison"] == pytest.approx(r["default"], rel=2e-2, abs=5e-2)
+    if world == 2:
+        # the same four samples per step, as two data-parallel ranks and as two micro-batches through two stages
+        assert res[1]["pp2vpp2"] == pytest.approx(res[1]["pp1"], rel=3e-2, abs=8e-2)
+
+
 def test_fsdp_reduce_scatter_through_the_switch_matches_peer_loads():
     world = min(torch.cuda.device_count(), 4)
     for r in _run("fsdp_nvls_equivalence", world):
