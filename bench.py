@@ -39,9 +39,9 @@ def parse():
     ap.add_argument("--ep", type=int, default=0, help="expert parallel size (default: all data ranks)")
     ap.add_argument("--gbs", type=int, default=0, help="global batch in sequences (default: seqs-per-gpu x N)")
     ap.add_argument("--mbs", type=int, default=0, help="micro-batch in sequences (default: seqs-per-gpu)")
-    ap.add_argument("--keep-dispatched", action="store_true",
-                    help="when memory allows, keep every layer's dispatched rows for the recomputed block (exactly "
-                         "the rows in use: one host read of the row count per layer and forward pass)")
+    ap.add_argument("--no-keep-dispatched", dest="keep_dispatched", action="store_false",
+                    help="never keep the layers' dispatched rows for the recomputed block (default: keep them, in "
+                         "fixed-size copies, when the memory estimate leaves room)")
     ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
@@ -134,11 +134,14 @@ def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = Fals
                 if allow_keep and gran == "selective" and cfg.model.num_experts > 0 \
                         and cfg.model.moe_keep_dispatched_factor == 0:
                     # spare memory buys speed: keep every layer's dispatched rows so the recomputed block needs
-                    # no second plan exchange and dispatch; -1 = exactly the rows in use (one host read per layer)
-                    cfg.model.moe_keep_dispatched_factor = -1.0
+                    # no second plan exchange and dispatch.  A fixed-size copy of 1.5 x the balanced load (one rank:
+                    # the load itself); a layer whose rows do not fit on some rank is dispatched again instead.
+                    ep = cfg.parallel.expert_model_parallel_size
+                    cfg.model.moe_keep_dispatched_factor = 1.0 if ep <= 1 else 1.5
                     est2 = estimate_memory(cfg, world)
-                    if est2["total_bytes"] <= 0.75 * est2["hbm_bytes"]:       # optional: only with real headroom
-                        last.update(keep_dispatched="exact", est_gb=round(est2["total_bytes"] / 2**30, 1))
+                    if est2["total_bytes"] + (8 << 30) <= 0.88 * est2["hbm_bytes"]:   # optional: only with headroom
+                        last.update(keep_dispatched=cfg.model.moe_keep_dispatched_factor,
+                                    est_gb=round(est2["total_bytes"] / 2**30, 1))
                     else:
                         cfg.model.moe_keep_dispatched_factor = 0.0
                 return last
@@ -291,6 +294,7 @@ def main() -> int:
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
             "expert_relocations": trainer.relocator.history if trainer.relocator else [],
+            "kept_dispatch_fallbacks": getattr(trainer.engine.dispatcher, "keep_fallbacks", 0),
         }
         print(json.dumps(line))
     if world > 1:

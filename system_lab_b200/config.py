@@ -103,7 +103,7 @@ class ModelConfig:
     moe_expert_ordered_dispatch: bool = True   # rows travel expert by expert with one arrival flag per (source, expert); the expert GEMM waits per expert inside the kernel
     moe_scatter_bulk_store: bool = False  # expert-ordered bf16 scatter sends rows with cp.async.bulk stores out of shared memory instead of per-lane 16-byte stores
     moe_scatter_overlap: bool = False    # ep > 1: the remote half of a dispatch scatter runs on a side stream beside the expert GEMM that consumes the rows
-    moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = fixed copy of x balanced load (no host sync, overflow is an error), <0 = exactly the rows in use (one host read per layer), 0 = off
+    moe_keep_dispatched_factor: float = 0.0  # selective recompute keeps the dispatched rows instead of re-dispatching: >0 = fixed copy of x balanced load (one host wait per step at the start of backward; a layer whose rows did not fit the copy on some rank is dispatched again on every rank), <0 = exactly the rows in use (one host read per layer), 0 = off
 
 
 @dataclass

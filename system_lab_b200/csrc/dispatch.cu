@@ -153,9 +153,10 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
   __shared__ int before[MAX_EXPERTS];     // rows of expert e from sources < me
   __shared__ int seg_off[MAX_EXPERTS];    // aligned offset of expert e inside its owner's buffer
   __shared__ int ok;
+  __shared__ int max_rows;                // most rows (with alignment padding) any rank receives
   __shared__ int scan_tmp[33];
   const int e_local = E / world;
-  if (threadIdx.x == 0) ok = 1;
+  if (threadIdx.x == 0) { ok = 1; max_rows = 0; }
   __syncthreads();
   if (threadIdx.x < world) {
     const int* flag = reinterpret_cast<const int*>(peers.base[me] + ws.counts_flag) + threadIdx.x;
@@ -170,7 +171,7 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
     }
     if (send_prefix)
       for (int e = threadIdx.x; e <= E; e += blockDim.x) { send_prefix[e] = 0; item_prefix[e] = 0; }
-    if (threadIdx.x == 0) meta[0] = 0;
+    if (threadIdx.x == 0) { meta[0] = 0; meta[1] = 0; }
     return;
   }
   if (send_prefix) {                      // blockDim.x >= E (512 threads, E <= 512)
@@ -206,8 +207,12 @@ __global__ void moe_plan_kernel(PeerTable peers, WsLayout ws, int world, int me,
     }
     if (acc > capacity) atomicCAS(status, 0, ST_CAPACITY);
     if (d == me) meta[0] = acc;
+    atomicMax(&max_rows, acc);
   }
   __syncthreads();
+  // the same number on every rank (all of them see all counts): lets the ranks take the same decision about anything
+  // that depends on whether every rank's rows fit a fixed-size buffer, without talking to each other
+  if (threadIdx.x == 0) meta[1] = max_rows;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     send_base[e] = seg_off[e] + before[e];
     if (e / e_local == me) {

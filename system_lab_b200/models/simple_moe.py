@@ -312,6 +312,9 @@ class MoEFFN(nn.Module):
         d = self.dispatcher
         kept = KEPT[0] if (self.keep_dispatched and getattr(d, "keep_rows", 1) > 0) else None
         reuse = kept is not None and RECOMPUTE_PHASE[0] and "plan" in kept
+        if reuse and hasattr(d, "kept_rows_fit") and not d.kept_rows_fit(kept["plan"]):
+            kept.clear()                 # some rank received more rows than the fixed-size copy holds: dispatch again
+            reuse = False
         if self.relocated and not reuse:
             idx = self.expert_map[idx.long()].to(idx.dtype)      # experts live where the placement put them
         plan = kept["plan"] if reuse else d.plan(idx)

@@ -176,6 +176,12 @@ class FusedDispatcher:
         self.keep_rows = cap if self.keep_exact else 0
         if keep_factor > 0:
             self.set_keep_rows(int(keep_factor * pairs))
+        # fixed-size copies: whether every rank's rows fitted is known on every rank from the plan (meta[1], the most
+        # rows any rank receives); it reaches the host through a pinned ring filled on a copy stream, read when the
+        # recomputed block needs it.  A layer whose rows did not fit is dispatched again, on every rank alike.
+        self.keep_fallbacks = 0
+        self._fits_host = self._fits_stream = None
+        self._fits_next = 0
         self.rows_seen = torch.zeros(1, dtype=torch.int32, device=device)
         n_blocks = max(cops.lib().slab_moe_count_blocks(pairs), 1)
         i32 = dict(dtype=torch.int32, device=device)
@@ -390,9 +396,42 @@ class FusedDispatcher:
             n = min(max(used, self.pad), self.capacity)
         else:
             n = self.keep_rows
-            cops.call("slab_moe_check_rows", plan.meta, n, self.status, self.rows_seen, cops.stream())
+            cops.call("slab_moe_check_rows", plan.meta, 0, self.status, self.rows_seen, cops.stream())   # high-water mark only
+            plan.kept_fits = self._fits_ticket(plan)
         plan.origin = self.origin[:n].clone() if self.keep_exact else self.origin.clone()
         return xe[:n].clone(), (pe[:n].clone() if pe is not None else None)
+
+    def _fits_ticket(self, plan: FusedPlan):
+        """Start the copy of ``plan.meta[1]`` (most rows on any rank) to the host; ``(slot, event)``."""
+        if torch.device(self.device).type != "cuda":
+            return None
+        if self._fits_host is None:
+            self._fits_host = torch.zeros(1024, dtype=torch.int32).pin_memory()
+            self._fits_stream = torch.cuda.Stream(device=self.device)
+        slot = self._fits_next % self._fits_host.numel()
+        self._fits_next += 1
+        self._fits_stream.wait_stream(torch.cuda.current_stream(self.device))
+        ev = torch.cuda.Event()
+        with torch.cuda.stream(self._fits_stream):
+            self._fits_host[slot:slot + 1].copy_(plan.meta[1:2], non_blocking=True)
+            ev.record(self._fits_stream)
+        return slot, ev
+
+    def kept_rows_fit(self, plan: FusedPlan) -> bool:
+        """Whether the fixed-size copy taken in the first run holds every rank's rows of this layer (the same answer
+        on every rank).  Waits, on the host, until the device has got as far as that run's plan: in backward that is
+        the past, except for the first layer it is asked about."""
+        if self.keep_exact:
+            return True
+        t = getattr(plan, "kept_fits", None)
+        if t is None:
+            return True
+        slot, ev = t
+        ev.synchronize()
+        ok = int(self._fits_host[slot]) <= self.keep_rows
+        if not ok:
+            self.keep_fallbacks += 1
+        return ok
 
     def redispatch_kept(self, plan: FusedPlan, x: torch.Tensor, probs: torch.Tensor | None, xs: torch.Tensor,
                         ps: torch.Tensor | None):

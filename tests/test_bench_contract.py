@@ -51,7 +51,14 @@ def test_memory_plan_prefers_fidelity_and_fits():
         plan = choose_memory_plan(cfg, n)
         assert plan["fits"] and plan["est_gb"] < 0.92 * 180 * 1e9 / 2**30
         names[n] = plan["name"]
-        assert cfg.model.moe_keep_dispatched_factor == 0          # kept dispatch is opt-in
+        assert cfg.model.moe_keep_dispatched_factor == 0          # not without being allowed to
+        cfg2 = Config.load(preset="qwen3-30b-a3b", overrides=[f"global_batch_size={2 * n}", "micro_batch_size=2",
+                                                             f"expert_model_parallel_size={n}"])
+        plan2 = choose_memory_plan(cfg2, n, allow_keep=True)
+        assert plan2["name"] == plan["name"] and plan2["est_gb"] < 0.88 * 180 * 1e9 / 2**30
+        if "keep_dispatched" in plan2:                            # a fixed-size copy, never the host-synchronising mode
+            assert cfg2.model.moe_keep_dispatched_factor == (1.0 if n == 1 else 1.5) == plan2["keep_dispatched"]
+            print(n, plan2)
         assert plan["optimizer_in_backward"]                       # one micro-batch per step: update inside backward
     assert names[8] == names[4] == "fp32-master+fp32-moments"
     assert names[1] == "bf16-weights+8bit-moments"

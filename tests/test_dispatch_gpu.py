@@ -357,3 +357,30 @@ def test_gemm_that_waits_for_rows_gives_up_with_a_status_code():
     o0, c0 = int(plans[0].expert_offsets[0]), int(plans[0].expert_counts[0])
     want = d.rows[0][o0:o0 + c0].float().sum(-1, keepdim=True).expand(c0, 128)
     assert torch.allclose(out[o0:o0 + c0].float(), want, rtol=2e-2, atol=0.25)
+
+
+def test_kept_dispatch_falls_back_when_the_copy_is_too_small():
+    """Selective recompute with a fixed-size copy of the dispatched rows: a copy that holds the rows is reused in the
+    recomputed block, a copy that is too small makes every layer dispatch again (decided from the plan's row count,
+    which reaches the host through a pinned buffer); either way the losses equal those of the run that keeps nothing."""
+    from system_lab_b200.config import Config
+    from system_lab_b200.ops import cuda as cops
+    from system_lab_b200.parallel.mesh import single_process_mesh
+    from system_lab_b200.trainer.loop import Trainer
+    curves, fallbacks = {}, {}
+    for factor in (0.0, 1.5, 0.5):
+        cfg = Config.load(preset="simplemoe-tiny", overrides=[
+            "params_dtype=bf16", "device=cuda", "global_batch_size=2", "micro_batch_size=2",
+            "expert_model_parallel_size=1", "moe_token_dispatcher_type=fused", "moe_pad_expert_rows_to=128",
+            "recompute_granularity=selective", f"moe_keep_dispatched_factor={factor}"])
+        tr = Trainer(cfg, mesh=single_process_mesh(), device=torch.device("cuda", 0))
+        try:
+            curves[factor] = [float(tr.train_step()["loss"]) for _ in range(3)]
+            torch.cuda.synchronize()
+            cops.check_status()
+            fallbacks[factor] = tr.engine.dispatcher.keep_fallbacks
+        finally:
+            tr.close()
+    assert curves[1.5] == pytest.approx(curves[0.0], rel=1e-3, abs=1e-3)
+    assert curves[0.5] == pytest.approx(curves[0.0], rel=1e-3, abs=1e-3)
+    assert fallbacks[1.5] == 0 and fallbacks[0.5] > 0
