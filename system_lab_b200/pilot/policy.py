@@ -49,6 +49,8 @@ LEVERS: dict[str, list[dict]] = {
         {"axis": "runtime.optimizer_in_backward", "op": "set", "values": [True], "gain": 0.0, "mem": -0.15},
         {"axis": "parallelism.tp", "op": "double", "gain": -8.0, "mem": -0.3,
          "note": "last resort: splits attention activations and the MoE rows of a rank; two exposed collectives per layer"},
+        {"axis": "parallelism.sp", "op": "set", "values": [True], "gain": 0.0, "mem": -0.1, "needs": "tp>1",
+         "note": "sequence parallelism: norms and residual stream on 1/tp of every sequence (SP requires TP > 1)"},
     ],
     "COMM": [
         {"axis": "comm.dispatcher", "op": "set", "values": ["fused"], "gain": 15.0},
@@ -119,7 +121,7 @@ def diagnose(snapshot: dict, *, multi_node: bool = False, expected_tps: float | 
 def default_plan(world: int, *, ep: int | None = None, mbs: int = 2, gbs: int | None = None) -> dict:
     ep = ep or world
     return {"id": "r0_p0", "parent": None,
-            "parallelism": {"tp": 1, "pp": 1, "dp": world, "ep": ep, "vpp": 1, "cp": 1},
+            "parallelism": {"tp": 1, "pp": 1, "dp": world, "ep": ep, "vpp": 1, "cp": 1, "sp": False},
             "runtime": {"mbs": mbs, "gbs": gbs or mbs * world, "recompute": "full", "optimizer_in_backward": False},
             "precision": {"fp8": False, "optimizer_state_dtype": "fp32", "master_weights": True},
             "comm": {"dispatcher": "fused", "fsdp_fused_collectives": False, "bucket_size_mb": 160},
@@ -133,7 +135,8 @@ def plan_to_overrides(plan: dict) -> tuple[list[str], dict[str, str]]:
     p, r, pr, c, mo = plan["parallelism"], plan["runtime"], plan["precision"], plan["comm"], plan["moe"]
     ov = [f"tensor_model_parallel_size={p['tp']}", f"pipeline_model_parallel_size={p['pp']}",
           f"expert_model_parallel_size={p['ep']}", f"virtual_pipeline_model_parallel_size={p['vpp']}",
-          f"context_parallel_size={p.get('cp', 1)}", f"micro_batch_size={r['mbs']}", f"global_batch_size={r['gbs']}",
+          f"context_parallel_size={p.get('cp', 1)}", f"sequence_parallel={str(bool(p.get('sp', False))).lower()}",
+          f"micro_batch_size={r['mbs']}", f"global_batch_size={r['gbs']}",
           f"recompute_granularity={r['recompute']}", f"optimizer_in_backward={str(r['optimizer_in_backward']).lower()}",
           f"fp8={str(pr['fp8']).lower()}", f"optimizer_state_dtype={pr['optimizer_state_dtype']}",
           f"master_weights={str(pr['master_weights']).lower()}", f"moe_token_dispatcher_type={c['dispatcher']}",
@@ -158,7 +161,7 @@ def _apply(plan: dict, lever: dict, value: Any) -> dict | None:
     if sec == "env":
         q["env"]["diff"][key] = value
         return q
-    cur = q[sec][key]
+    cur = q[sec].get(key, False) if key == "sp" else q[sec][key]
     op = lever["op"]
     if op == "double":
         new = cur * 2
@@ -187,6 +190,8 @@ def _apply(plan: dict, lever: dict, value: Any) -> dict | None:
         if dp % new:
             return None
         q["parallelism"]["dp"] = dp // new
+        if new <= 1:
+            q["parallelism"]["sp"] = False          # sequence parallelism needs a tensor-parallel group
         if q["runtime"]["gbs"] % (q["runtime"]["mbs"] * q["parallelism"]["dp"]):
             return None
     if lever["axis"] == "runtime.mbs":

@@ -326,4 +326,10 @@ def test_tensor_parallel_levers_keep_the_world_size():
     assert policy._apply(wide, down, None)["parallelism"] == base["parallelism"]
     assert policy._apply(base, down, None) is None                                    # tp = 1 cannot shrink
     ov, _ = policy.plan_to_overrides(wide)
-    assert "tensor_model_parallel_size=2" in ov
+    assert "tensor_model_parallel_size=2" in ov and "sequence_parallel=false" in ov
+    # sequence parallelism is a memory lever of a plan that already has a tensor-parallel group, and goes with it
+    sp = [l for l in policy.LEVERS["MEMORY"] if l["axis"] == "parallelism.sp"][0]
+    assert sp["needs"] == "tp>1"
+    seq = policy._apply(wide, sp, True)
+    assert seq["parallelism"]["sp"] is True and "sequence_parallel=true" in policy.plan_to_overrides(seq)[0]
+    assert policy._apply(seq, down, None)["parallelism"]["sp"] is False
