@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--keep-dispatched", action="store_true",
                     help="when the memory estimate leaves room, keep every layer's dispatched rows (fixed-size copies of "
                          "1.5 x the balanced load) for the recomputed block; measured neutral at 2 GPUs, hence opt-in")
+    ap.add_argument("--sync-loss-read", action="store_true",
+                    help="end-to-end region: read each step's loss before launching the next step (default: the read "
+                         "is collected one step later, with the next step already queued)")
     ap.add_argument("--plan", default="", help="force a memory plan by name instead of the first that fits")
     ap.add_argument("--dispatcher", default=None, help="fused | alltoall (default: preset)")
     ap.add_argument("--kernels", default="auto", help="auto | false (PyTorch/library baseline path)")
@@ -229,15 +232,30 @@ def main() -> int:
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
     t0 = time.perf_counter()
-    step_ms = []                                                 # every step ends in a host read: host clock per step
+    # Every step's loss and gradient norm are read on the host, through the trainer's pinned read tickets: the copy is
+    # queued behind the step, and the host collects it after it has launched the following step, so the device is not
+    # left idle while the host waits (--sync-loss-read reads at once instead, as Trainer.fit does by default).
+    step_ms, e2e_losses = [], []                                 # host clock between two completed reads
+    pending = None
+    ts = time.perf_counter()
     for i in range(args.steps):
-        ts = time.perf_counter()
         mbs = trainer.data.microbatches(trainer.step)          # pinned host tensors
         h2d = sum(a.numel() * a.element_size() + b.numel() * b.element_size() for a, b in mbs)
         out = trainer.train_step(batches=mbs)
-        loss_host = out["loss"].cpu()                            # device -> host read of the step's result
-        d2h = loss_host.numel() * loss_host.element_size()
-        step_ms.append((time.perf_counter() - ts) * 1e3)
+        ticket = trainer.begin_loss_read(out)                    # device -> host copy of the step's result
+        d2h = 3 * 4
+        if args.sync_loss_read:
+            e2e_losses.append(trainer.finish_loss_read(ticket)[0])
+        else:
+            if pending is not None:
+                e2e_losses.append(trainer.finish_loss_read(pending)[0])
+            pending = ticket
+        if len(e2e_losses) > len(step_ms):
+            now = time.perf_counter()
+            step_ms.append((now - ts) * 1e3)
+            ts = now
+    if pending is not None:
+        e2e_losses.append(trainer.finish_loss_read(pending)[0])  # the last step's numbers, inside the timed region
     if dev.type == "cuda":
         f1.record()
         torch.cuda.synchronize()
@@ -289,6 +307,8 @@ def main() -> int:
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
+                    "loss_read": "at once" if args.sync_loss_read else "pinned buffer, collected after the next step's launch",
+                    "losses_read": len(e2e_losses), "last_loss": e2e_losses[-1] if e2e_losses else None,
                     "rank0_step_ms_min_median_max": [round(sorted(step_ms)[0], 2), round(sorted(step_ms)[len(step_ms) // 2], 2),
                                                      round(sorted(step_ms)[-1], 2)] if step_ms else None},
             "gpu_launches": launches,

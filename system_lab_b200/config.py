@@ -160,6 +160,7 @@ class TrainConfig:
     adam_beta2: float = 0.95
     adam_eps: float = 1e-8
     clip_grad: float = 1.0
+    deferred_loss_read: bool = False     # fit(): read a step's loss and gradient norm (pinned buffer) after the next step has been launched, so the device never idles between steps; steps that evaluate, save or may leave are read at once; log lines appear one step late
     optimizer_in_backward: bool = False  # apply AdamW per layer during backward (no grad buffer kept)
     optimizer_background_piece: int = 33554432   # elements per launch of a side-stream AdamW update (multiple of 512; 0 = one launch): bounds how long a compute-stream kernel with large blocks waits for room on the SMs
     eval_interval: int = 0

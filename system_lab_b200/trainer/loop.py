@@ -93,6 +93,8 @@ class Trainer:
             dist.barrier()                     # ranks leave construction together (peer kernels wait on each other)
         self.step = 0
         self.loss_curve: list[float] = []
+        self._read_ring, self._read_next = None, 0       # pinned slots of begin_loss_read
+        self.last_status_any = False
         self.step_times_ms: list[float] = []
         self.nan_iters = 0
         self.flops_per_token = model_flops_per_token(cfg.model)
@@ -181,20 +183,57 @@ class Trainer:
         self._update_router_bias()
         # mean loss over micro-batches and data ranks (reported from the last pipeline stage)
         loss_mean = loss_sum / nmb
+        # the kernels' status word travels with the loss: after the sum every rank knows, without a host read of its
+        # own, whether a bounded wait ran out or a bounds check failed anywhere in this step
+        status_any = None
+        if dev.type == "cuda" and ops.kernel_mode() == "auto":
+            from ..ops import cuda as _cops
+            status_any = (_cops.status_word(dev) != 0).float().reshape(())
         if dist.is_initialized() and mesh.world > 1:
-            if mesh.pp > 1:
-                # only last-stage ranks hold a loss; others contribute zero
-                dist.all_reduce(loss_mean)
-                loss_mean = loss_mean / (mesh.data_size * mesh.tp)
-            else:
-                dist.all_reduce(loss_mean)
-                loss_mean = loss_mean / mesh.world
+            pack = torch.stack([loss_mean.reshape(()), status_any if status_any is not None else torch.zeros_like(loss_mean).reshape(())])
+            dist.all_reduce(pack)
+            # pipeline: only last-stage ranks hold a loss, the others contribute zero
+            loss_mean = pack[0] / ((mesh.data_size * mesh.tp) if mesh.pp > 1 else mesh.world)
+            status_any = pack[1]
         if flags.get("nan"):
             loss_mean = loss_mean * float("nan")
         self.step = step
         if self.heartbeat is not None:
             self.heartbeat.beat(step)
-        return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr}
+        return {"loss": loss_mean, "grad_norm": grad_norm, "lr": lr, "status_any": status_any}
+
+    # ---- reading a step's numbers without stalling the launch of the next step -------------------------
+    def begin_loss_read(self, out: dict):
+        """Start copying the step's loss and gradient norm into pinned host memory (on the current stream, after the
+        step's kernels) and return a ticket for :meth:`finish_loss_read`.  Taking the ticket of step ``s`` only after
+        step ``s + 1`` has been launched keeps the device busy while the host waits: the host then blocks until step
+        ``s`` is done with all of step ``s + 1`` already queued."""
+        dev = out["loss"].device
+        st = out.get("status_any")
+        vals = torch.stack([out["loss"].detach().float().reshape(()),
+                            torch.as_tensor(out["grad_norm"], dtype=torch.float32, device=dev).detach().reshape(()),
+                            st.float().reshape(()) if st is not None else torch.zeros((), device=dev)])
+        if self.device.type != "cuda":
+            return vals, None
+        if self._read_ring is None:
+            self._read_ring = torch.zeros(16, 3, dtype=torch.float32).pin_memory()
+        slot = self._read_next % self._read_ring.shape[0]
+        self._read_next += 1
+        self._read_ring[slot].copy_(vals, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return slot, ev
+
+    def finish_loss_read(self, ticket) -> tuple[float, float]:
+        """``(loss, grad_norm)`` of the step the ticket was taken for; waits on the host until that step is done."""
+        slot, ev = ticket
+        if ev is None:
+            row = slot
+        else:
+            ev.synchronize()
+            row = self._read_ring[slot]
+        self.last_status_any = float(row[2]) > 0          # some rank's kernels reported an error in that step
+        return float(row[0]), float(row[1])
 
     def check_device_status(self) -> None:
         """Read the status word the kernels write when a bounded wait runs out or a bounds check fails (a lost peer
@@ -330,28 +369,62 @@ class Trainer:
             import threading
             if threading.current_thread() is threading.main_thread():
                 old_handler = signal.signal(signal.SIGTERM, lambda *_: setattr(self, "_term_seen", True))
-        while self.step < target:
-            if is_cuda:
-                torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            if prof:
-                prof.step_begin(self.step + 1)
-            out = self.train_step()
-            loss = float(out["loss"])              # host read: also the step's device sync
-            gn = float(out["grad_norm"])
-            self.check_device_status()             # before anything is logged, evaluated or saved from this step
-            if prof:
-                prof.step_end(self.step)
-            dt_ms = (time.perf_counter() - t0) * 1e3
+        # deferred_loss_read: the numbers of step s are read after step s + 1 has been launched, so the device never
+        # waits for the host between steps; steps that evaluate, save, may leave, or end the run are read at once
+        deferred = bool(t.deferred_loss_read) and prof is None
+        pending = None                                  # (step, ticket, lr, host time at launch) of the unread step
+        t_prev = time.perf_counter()
+
+        def account(step: int, loss: float, gn: float, lr: float, dt_ms: float) -> None:
             self.step_times_ms.append(dt_ms)
             self.loss_curve.append(loss)
             bad = not (loss == loss and abs(loss) != float("inf") and gn == gn and gn != float("inf"))
             if bad:
                 self.nan_iters += 1
                 if t.check_for_nan_in_loss_and_grad:
-                    raise NumericalError(f"step {self.step}: loss={loss} grad_norm={gn}")
-            if self.mesh.rank == 0 and (self.step % max(t.log_interval, 1) == 0):
-                self._log_line(dt_ms, loss, gn, out["lr"])
+                    raise NumericalError(f"step {step}: loss={loss} grad_norm={gn}")
+            if self.mesh.rank == 0 and (step % max(t.log_interval, 1) == 0):
+                self._log_line(dt_ms, loss, gn, lr, step)
+
+        def drain() -> None:
+            nonlocal pending, t_prev
+            if pending is not None:
+                st, ticket, lr_, _ = pending
+                loss_, gn_ = self.finish_loss_read(ticket)
+                now = time.perf_counter()
+                if self.last_status_any:                  # the same answer on every rank: all of them stop here together
+                    self.check_device_status()
+                account(st, loss_, gn_, lr_, (now - t_prev) * 1e3)      # time between two steps' completions
+                t_prev, pending = now, None
+
+        while self.step < target:
+            if deferred:
+                out = self.train_step()
+                ticket = self.begin_loss_read(out)
+                drain()                                  # the previous step, with this one already queued
+                pending = (self.step, ticket, out["lr"], time.perf_counter())
+                ck_ = cfg.checkpoint
+                boundary = (self.step >= target or (t.eval_interval and self.step % t.eval_interval == 0)
+                            or (ck_.save and ck_.save_interval and self.step % ck_.save_interval == 0)
+                            or getattr(self, "_pending_ckpt", None) is not None
+                            or t.exit_duration_in_mins > 0 or t.exit_signal_handler
+                            or (t.manual_gc and self.step % max(t.manual_gc_interval, 1) == 0))
+                if not boundary:
+                    continue
+                drain()
+            else:
+                if is_cuda:
+                    torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                if prof:
+                    prof.step_begin(self.step + 1)
+                out = self.train_step()
+                loss = float(out["loss"])              # host read: also the step's device sync
+                gn = float(out["grad_norm"])
+                self.check_device_status()             # before anything is logged, evaluated or saved from this step
+                if prof:
+                    prof.step_end(self.step)
+                account(self.step, loss, gn, out["lr"], (time.perf_counter() - t0) * 1e3)
             if t.eval_interval and self.step % t.eval_interval == 0:
                 ev = self.evaluate()
                 self.eval_curve.append((self.step, ev))
@@ -392,16 +465,17 @@ class Trainer:
             Path(cfg.profile.snapshot_path).write_text(json.dumps(snap, indent=2))
         return snap
 
-    def _log_line(self, dt_ms: float, loss: float, gn: float, lr: float) -> None:
+    def _log_line(self, dt_ms: float, loss: float, gn: float, lr: float, step: int | None = None) -> None:
+        step = self.step if step is None else step
         tps_gpu = self.tokens_per_step / (dt_ms / 1e3) / self.mesh.world
         tflops = tps_gpu * self.flops_per_token / 1e12
         mem = torch.cuda.max_memory_allocated() / 2**30 if self.device.type == "cuda" else 0.0
         log.info("iteration %6d | elapsed ms/iter %9.1f | TFLOP/s/GPU %7.1f | tokens/s/GPU %9.0f | lm loss %.6f | "
                  "grad norm %.4f | lr %.3e | nan iters %d | mem GiB %.1f",
-                 self.step, dt_ms, tflops, tps_gpu, loss, gn, lr, self.nan_iters, mem)
+                 step, dt_ms, tflops, tps_gpu, loss, gn, lr, self.nan_iters, mem)
         path = self.cfg.train.metrics_file
         if path:
-            rec = {"step": self.step, "time": time.time(), "step_ms": dt_ms, "loss": loss, "grad_norm": gn, "lr": lr,
+            rec = {"step": step, "time": time.time(), "step_ms": dt_ms, "loss": loss, "grad_norm": gn, "lr": lr,
                    "tokens_per_s": self.tokens_per_step / (dt_ms / 1e3), "tflops_per_gpu": tflops, "mem_gib": mem,
                    "nan_iters": self.nan_iters, "ep_rank_load_max_over_mean": self.rank_load_ratio()}
             Path(path).parent.mkdir(parents=True, exist_ok=True)

@@ -35,7 +35,7 @@ def test_json_line_has_the_contract_keys():
     tokens = d["config"]["global_batch"] * d["config"]["seq_len"]
     assert abs(d["value"] - tokens / (d["ms_per_step"] / 1e3)) < 1e-6 * d["value"]
     e = d["e2e"]
-    assert e["h2d_bytes_per_step"] == tokens * 8 * 2 and e["d2h_bytes_per_step"] == 4     # int64 tokens + targets; fp32 loss
+    assert e["h2d_bytes_per_step"] == tokens * 8 * 2 and e["d2h_bytes_per_step"] == 12    # int64 tokens + targets; fp32 loss, gradient norm, status
     assert e["value"] > 0 and e["value"] != d["value"]
     assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
 

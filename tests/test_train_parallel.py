@@ -271,6 +271,25 @@ def _fit(rank, world, overrides):
     return tr.step, tr.stopped_on_time, gc.isenabled()
 
 
+def _fit_curve(rank, world, overrides):
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import Trainer
+    tr = Trainer(Config.load(preset="simplemoe-tiny", overrides=list(overrides) + ["device=cpu"]))
+    tr.fit()
+    return tr.loss_curve, tr.eval_curve, tr.step, len(tr.step_times_ms)
+
+
+def test_deferred_loss_read_gives_the_same_run(tmp_path):
+    """``fit`` with the numbers of a step read after the next step's launch: same loss curve, one entry per step,
+    evaluation and checkpoints at the same steps as the run that reads at once."""
+    ov = BASE + ["expert_model_parallel_size=2", "train_iters=7", "eval_interval=3", "eval_iters=1", "log_interval=2"]
+    sync = run_ranks(_fit_curve, 2, ov + [f"save={tmp_path / 'a'}", "save_interval=4"])
+    late = run_ranks(_fit_curve, 2, ov + [f"save={tmp_path / 'b'}", "save_interval=4", "deferred_loss_read=true"])
+    assert late[0][0] == sync[0][0] and len(late[0][0]) == 7
+    assert late[0][1] == sync[0][1] and late[0][2] == 7 and late[0][3] == 7
+    assert sorted(p.name for p in (tmp_path / "a").iterdir()) == sorted(p.name for p in (tmp_path / "b").iterdir())
+
+
 def test_wall_clock_exit_is_collective_and_manual_gc_restores_the_collector():
     """Rank 0 decides that the time is up and every rank leaves after the same step; manual garbage collection runs
     with the collector off and turns it back on."""
