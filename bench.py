@@ -197,7 +197,7 @@ def main() -> int:
     # ---- warm-up --------------------------------------------------------------------------------
     for _ in range(args.warmup):
         out = trainer.train_step()
-        float(out["loss"])
+        trainer.finish_loss_read(trainer.begin_loss_read(out))     # the read path of the end-to-end region, warmed up too
         if dev.type == "cuda":
             trainer.check_device_status()      # a kernel that gave up (bounded wait, capacity) ends the run here
     # ---- device-timed region: K steps, inputs already on the device, no host read inside ----------------
