@@ -101,6 +101,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def _min_median_max(xs):
+    if not xs:
+        return None
+    xs = sorted(xs)
+    return [round(xs[0], 2), round(xs[len(xs) // 2], 2), round(xs[-1], 2)]
+
+
 def choose_memory_plan(cfg, world: int, force: str = "", allow_keep: bool = False) -> dict:
     """Highest-fidelity optimizer/weight layout that fits 92 % of 180 GB per GPU."""
     from system_lab_b200.pilot.constraints import estimate_memory
@@ -309,8 +316,9 @@ def main() -> int:
                     "ms_per_step": e2e_ms / args.steps,
                     "loss_read": "at once" if args.sync_loss_read else "pinned buffer, collected after the next step's launch",
                     "losses_read": len(e2e_losses), "last_loss": e2e_losses[-1] if e2e_losses else None,
-                    "rank0_step_ms_min_median_max": [round(sorted(step_ms)[0], 2), round(sorted(step_ms)[len(step_ms) // 2], 2),
-                                                     round(sorted(step_ms)[-1], 2)] if step_ms else None},
+                    # host time between two collected reads; the first interval also holds the launch of the second
+                    # step (reads are collected one step behind) and is left out
+                    "rank0_step_ms_min_median_max": _min_median_max(step_ms[1:] if len(step_ms) > 2 else step_ms)},
             "gpu_launches": launches,
             "mem_peak_gb": torch.cuda.max_memory_allocated() / 2**30 if dev.type == "cuda" else 0.0,
             "expert_relocations": trainer.relocator.history if trainer.relocator else [],
