@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--keep-dispatched", action="store_true",
                     help="when the memory estimate leaves room, keep every layer's dispatched rows (fixed-size copies of "
                          "1.5 x the balanced load) for the recomputed block; measured neutral at 2 GPUs, hence opt-in")
+    ap.add_argument("--host-profile", default="",
+                    help="write a cProfile summary (rank 0, by own time) of the host side of the device-timed loop to "
+                         "this file; the run's numbers are then not benchmark values")
     ap.add_argument("--sync-loss-read", action="store_true",
                     help="end-to-end region: read each step's loss before launching the next step (default: the read "
                          "is collected one step later, with the next step already queued)")
@@ -220,8 +223,24 @@ def main() -> int:
         e0.record()
     t0 = time.perf_counter()
     last = None
+    host_prof = None
+    if args.host_profile and rank == 0:
+        import cProfile
+        host_prof = cProfile.Profile()
+        host_prof.enable()
     for i in range(args.steps):
         last = trainer.train_step(batches=staged[i])
+    if host_prof is not None:
+        host_prof.disable()
+        host_s = time.perf_counter() - t0
+        import io
+        import pstats
+        buf = io.StringIO()
+        buf.write(f"host time to launch {args.steps} steps: {host_s * 1e3 / args.steps:.1f} ms per step (under cProfile)\n")
+        pstats.Stats(host_prof, stream=buf).sort_stats("tottime").print_stats(70)
+        os.makedirs(os.path.dirname(args.host_profile) or ".", exist_ok=True)
+        with open(args.host_profile, "w") as f:
+            f.write(buf.getvalue())
     if dev.type == "cuda":
         e1.record()
         torch.cuda.synchronize()

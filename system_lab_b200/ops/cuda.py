@@ -84,16 +84,29 @@ _KERNELS_PER_CALL = {}
 LAUNCHES = [0]
 
 
+_Tensor = torch.Tensor
+
+
 def call(name: str, *args) -> int:
-    fn = getattr(lib(), name)
+    # on the launch path of every kernel (about two thousand calls per training step): no helper calls per argument
+    fn = getattr(_lib if _lib is not None else lib(), name)
     LAUNCHES[0] += _KERNELS_PER_CALL.get(name, 1)
-    rc = fn(*[_ptr(a) for a in args])
+    rc = fn(*[a.data_ptr() if isinstance(a, _Tensor) else a for a in args])
     if rc != 0:
         raise KernelError(f"{name} failed with code {rc}")
     return rc
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream() -> int:
+    """Handle of the current stream of the current device.  Asked once per kernel launch, so it goes to the two C
+    entry points directly; ``torch.cuda.current_stream()`` builds a Python stream object and re-derives the device
+    from the environment every time (about 8 us a call)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
