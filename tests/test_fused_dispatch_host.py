@@ -66,3 +66,30 @@ def test_push_target_checks_width_before_launching():
     with pytest.raises(ValueError, match="wide"):
         tgt.launch(0, a, w, torch.zeros(8, dtype=torch.int32), torch.zeros(8, dtype=torch.int32), 128, 64, 128)
     assert d.push_epoch == 0 and d._pending_push == {}
+
+
+def test_gemm_reduce_scatter_row_table():
+    """Row b * S + s of the full product belongs to the rank that holds positions [r S/w, (r+1) S/w) and lands in slot
+    (local row) * world + sender of that rank's receive region: every slot of every rank is written exactly once when
+    all senders are taken together."""
+    from system_lab_b200.comm.gemm_rs import GemmReduceScatter
+    from system_lab_b200.comm.symm import EmulatedWorld
+    world, batch, seq, n = 4, 2, 16, 64
+    dev = torch.device("cpu")
+    emu = EmulatedWorld(GemmReduceScatter.nbytes(batch, seq, n, world), world, dev)
+    ops_ = [GemmReduceScatter(None, world, r, dev, batch, seq, n, workspace=emu.workspace(r)) for r in range(world)]
+    s_local = seq // world
+    seen = {r: set() for r in range(world)}
+    for sender, op in enumerate(ops_):
+        assert op.rows == batch * seq and op.rows_local == batch * s_local
+        org = op.origin.tolist()
+        for row, o in enumerate(org):
+            b, s = divmod(row, seq)
+            dst, slot = o >> 24, o & 0xFFFFFF
+            assert dst == s // s_local
+            assert slot == (b * s_local + s % s_local) * world + sender
+            assert slot not in seen[dst]
+            seen[dst].add(slot)
+    assert all(seen[r] == set(range(batch * s_local * world)) for r in range(world))
+    with pytest.raises(ValueError, match="multiple"):
+        GemmReduceScatter(None, 3, 0, dev, 1, 16, 64, workspace=emu.workspace(0))
