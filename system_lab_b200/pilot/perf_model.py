@@ -28,6 +28,11 @@ RATES = {
     "combine_eff": 0.80,
     "fsdp_eff": 0.20,                  # peer all-gather / reduce-scatter of ~40 MB layers (latency and flag waits dominate)
     "launch_gap_ms_per_layer": 0.25,   # residual host / launch gaps per layer per pass
+    # Waiting at the cross-rank meeting points of a MoE layer (five per layer: three exchanges of rows one way, two the
+    # other) beyond what load imbalance explains, per layer, by expert-parallel size.  Fitted to the measured
+    # Qwen3-30B-A3B steps (354 / 384 / 430 / 539 ms at 1 / 2 / 4 / 8 GPUs): the other terms reproduce 1 to 4 GPUs within
+    # 5 % and leave 2.3 ms per layer at 8 unexplained (arrival skew among eight ranks; no 8-GPU trace exists).
+    "meeting_wait_ms_per_layer": {8: 2.3},
     "tp_allreduce_eff": 0.55,          # NCCL all-reduce / all-gather of a micro-batch's activations (tens of MB): share of
                                        # the 725 GB/s bus bandwidth of a 1 GiB all-reduce; not measured under tp yet
 }
@@ -141,6 +146,12 @@ def estimate_step(cfg: Any, world: int, *, rank_load_ratio: float = 1.0, rates: 
             t_fsdp += moe_layers * layer_exp * (edp - 1) / edp * 3.0 / (r["fsdp_eff"] * r["link_gbs"]) / 1e6
     # the most loaded rank of every layer: its share of expert compute and of the ingress traffic
     t_imb = (rank_load_ratio - 1.0) * (t_expert + t_disp) if ep > 1 else 0.0
+    waits = r.get("meeting_wait_ms_per_layer") or {}
+    if ep > 1 and waits:
+        known = sorted(waits)
+        at = max([k for k in known if k <= ep], default=None)       # the largest measured size not above ep
+        if at is not None:
+            t_imb += moe_layers * float(waits[at]) * (ep / at)      # grows with the number of ranks met
 
     # tensor parallelism: per layer and pass one all-reduce behind attention and one all-reduce (dense FFN) or
     # all-gather (MoE block) behind the feed-forward block, each over the micro-batch's activations; nothing hides them

@@ -193,8 +193,9 @@ def test_failed_worker_aborts_after_three_same_failures(tmp_path):
 
 
 def test_perf_model_matches_measured_b200_steps():
-    """The analytic execution model reproduces the measured Qwen3-30B-A3B-shape step times on B200 (1, 2 and 8
-    GPUs) within 15 % and attributes the 8-GPU slowdown to dispatch traffic and rank imbalance."""
+    """The analytic execution model reproduces the measured Qwen3-30B-A3B-shape step times on B200 (1, 2, 4 and 8
+    GPUs) within 10 % and attributes the 8-GPU slowdown to dispatch traffic, rank imbalance and waiting at the
+    layers' meeting points."""
     from system_lab_b200.config import Config
     from system_lab_b200.pilot.perf_model import estimate_step, expected_tps
     sel = ["params_dtype=bf16", "recompute_granularity=selective"]
@@ -204,11 +205,14 @@ def test_perf_model_matches_measured_b200_steps():
     n2 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
         "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=2", "master_weights=false",
         "optimizer_state_dtype=bf16"])
+    n4 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
+        "global_batch_size=8", "micro_batch_size=2", "expert_model_parallel_size=4", "optimizer_in_backward=true"])
     n8 = Config.load(preset="qwen3-30b-a3b", overrides=sel + [
-        "global_batch_size=16", "micro_batch_size=2", "expert_model_parallel_size=8"])
-    for cfg, world, ratio, measured_ms in ((n1, 1, 1.0, 351.5), (n2, 2, 1.1, 389.3), (n8, 8, 1.49, 482.8)):
+        "global_batch_size=16", "micro_batch_size=2", "expert_model_parallel_size=8", "optimizer_in_backward=true"])
+    for cfg, world, ratio, measured_ms in ((n1, 1, 1.0, 353.9), (n2, 2, 1.03, 384.3), (n4, 4, 1.07, 430.5),
+                                           (n8, 8, 1.12, 539.0)):
         e = estimate_step(cfg, world, rank_load_ratio=ratio)
-        assert abs(e.t_step / measured_ms - 1.0) < 0.15, (world, e.t_step, measured_ms)
+        assert abs(e.t_step / measured_ms - 1.0) < 0.10, (world, e.t_step, measured_ms)
     e8 = estimate_step(n8, 8, rank_load_ratio=1.49)
     assert e8.t_imbalance > 0.15 * e8.t_step and e8.t_dispatch > e8.t_fsdp
     assert estimate_step(n8, 8).t_step < e8.t_step                      # balanced routing is faster
