@@ -108,7 +108,8 @@ def test_inert_knobs_are_reported_not_ignored():
 
 
 @pytest.mark.parametrize("name,world", [("qwen3_30b_a3b_8gpu", 8), ("deepseek_v3_proxy_pp2_ep4", 8),
-                                        ("llama2_70b_lora_8gpu", 8), ("simplemoe_tiny_cpu", 2)])
+                                        ("llama2_70b_lora_8gpu", 8), ("simplemoe_tiny_cpu", 2),
+                                        ("gpt_oss_20b_tp2_sp_8gpu", 8)])
 def test_example_configs_load_and_fit(name, world):
     from pathlib import Path
     cfg = Config.load(Path(__file__).resolve().parent.parent / "configs" / f"{name}.yaml")
