@@ -147,3 +147,19 @@ def test_every_rank_leaves_the_step_when_one_rank_reports_a_status_code():
     res = run_ranks(_fit_with_status_on_one_rank, 2, timeout=120)
     assert [r[0] for r in res] == ["hang", "hang"]
     assert all("CAPACITY" in r[1] and r[2] == 1 for r in res)
+
+
+def test_deferred_loss_read_still_stops_on_a_non_finite_loss():
+    """With the numbers of a step read one step late, a NaN injected at step 3 (on the host) stops ``fit`` when step 3
+    is accounted for, i.e. after step 4 has been launched: the error names step 3 and the curve ends there."""
+    import pytest
+    from system_lab_b200.config import Config
+    from system_lab_b200.trainer.loop import NumericalError, Trainer
+    cfg = Config.load(preset="simplemoe-tiny", overrides=[
+        "global_batch_size=4", "micro_batch_size=2", "expert_model_parallel_size=1", "train_iters=8", "device=cpu",
+        "deferred_loss_read=true", "fault_injection=nan:rank=0,step=3"])
+    tr = Trainer(cfg)
+    with pytest.raises(NumericalError, match="step 3"):
+        tr.fit()
+    assert len(tr.loss_curve) == 3 and tr.loss_curve[2] != tr.loss_curve[2] and tr.step == 4
+    tr.close()
